@@ -1,0 +1,108 @@
+// Internal definitions shared by the kernels and the C-ABI glue of libpetb200.
+#pragma once
+#include "../../include/petb200.h"
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+struct petb200_ctx {
+    int device = 0;
+    int sm_count = 148;
+    int cc_major = 0, cc_minor = 0;
+    size_t smem_optin = 0;
+    uint64_t launches = 0;
+    std::string err;
+    int *d_status = nullptr; // device word kernels write when a bounded wait expires
+};
+
+struct petb200_plan {
+    petb200_ctx *ctx = nullptr;
+    const char *kernel = "none";
+    size_t device_bytes = 0;
+    virtual ~petb200_plan() {}
+    // Launch once on plan-owned scratch operands (for petb200_plan_time).
+    virtual int bench_launch(cudaStream_t) { return PETB200_ERR_UNSUPPORTED; }
+};
+
+namespace petb200 {
+
+inline int fail(petb200_ctx *ctx, int status, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (ctx)
+        ctx->err = buf;
+    return status;
+}
+
+#define PETB200_CUDA(ctx, call)                                                                              \
+    do {                                                                                                     \
+        cudaError_t e_ = (call);                                                                             \
+        if (e_ != cudaSuccess)                                                                               \
+            return petb200::fail((ctx), PETB200_ERR_CUDA, "%s failed: %s (%s:%d)", #call,                    \
+                                 cudaGetErrorString(e_), __FILE__, __LINE__);                                \
+    } while (0)
+
+// Records a launch and converts a launch error into a status.
+inline int launched(petb200_ctx *ctx, const char *what) {
+    ctx->launches++;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return fail(ctx, PETB200_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
+    return PETB200_OK;
+}
+
+struct DevBuf {
+    void *p = nullptr;
+    size_t bytes = 0;
+    ~DevBuf() {
+        if (p)
+            cudaFree(p);
+    }
+    cudaError_t alloc(size_t n) {
+        if (p) {
+            cudaFree(p);
+            p = nullptr;
+        }
+        bytes = n;
+        return n ? cudaMalloc(&p, n) : cudaSuccess;
+    }
+};
+
+__host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// ---- shared activation definition (host mirror lives in the tests' oracle) ----
+__device__ __forceinline__ float apply_act(float v, int act) {
+    switch (act) {
+    case PETB200_ACT_RELU:
+        return fmaxf(v, 0.f);
+    case PETB200_ACT_SIGMOID:
+        return 1.f / (1.f + expf(-v));
+    case PETB200_ACT_TANH:
+        return tanhf(v);
+    case PETB200_ACT_GELU:
+        return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
+    default:
+        return v;
+    }
+}
+
+// ---- plan factories implemented in the kernel files ----
+int make_conv_plan(petb200_ctx *ctx, int nsp, const int *in_dims /*n,c,[d],h,w*/, int f, const int *k /*[t],r,s*/,
+                   const int *pad, const int *stride, const int *dil, int groups, int has_bias, int act, int algo,
+                   petb200_plan **out);
+int conv_set_weights(petb200_plan *plan, const float *w, cudaStream_t s);
+int conv_run(petb200_plan *plan, const float *x, const float *bias, float *y, const int *win /*oh0,ohn,ow0,own or null*/,
+             cudaStream_t s);
+int conv_out_dims(const petb200_plan *plan, int *dims5);
+
+int make_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int n, int k, int has_bias, int act,
+                     int algo, petb200_plan **out);
+int matmul_run(petb200_plan *plan, const float *a, const float *b, const float *bias, float *c, cudaStream_t s);
+
+} // namespace petb200

@@ -1,0 +1,405 @@
+// Convolution and matmul plans: argument checking as the reference's operators do it, kernel-family selection
+// (tcgen05 3xTF32 implicit GEMM, or the CUDA-core fp32 kernels below for shapes the tensor-core path does not
+// take), weight preprocessing, correction windows, and the operands used by the timing entry point.
+#include "common.h"
+#include <algorithm>
+
+namespace petb200 {
+
+// implemented in igemm_tc.cu
+int tc_conv_create(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const int *k, const int *pad, const int *stride,
+                   const int *dil, int groups, int has_bias, int act, void **out, size_t *dev_bytes);
+void tc_conv_destroy(void *h);
+int tc_conv_set_weights(void *h, const float *w, cudaStream_t s);
+int tc_conv_run(void *h, const float *x, const float *bias, float *y, const int *win, cudaStream_t s);
+int tc_conv_row_pitch(void *h);
+const char *tc_conv_variant(void *h);
+int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transB, int has_bias, int act, void **out,
+                     size_t *dev_bytes);
+void tc_matmul_destroy(void *h);
+int tc_matmul_pack_b(void *h, const float *b, cudaStream_t s);
+int tc_matmul_run(void *h, const float *a_t, const float *bias, float *cmat, cudaStream_t s);
+
+// -------------------------------------------------------------------------------------------------------------
+// CUDA-core kernels (exact fp32 products, sequential accumulation in the reference's loop order cc,tt,rr,ss)
+// -------------------------------------------------------------------------------------------------------------
+struct SimtConv {
+    int N, C, D, H, W, F, T, R, S, pd, ph, pw, sd, sh, sw, dd, dh, dw, groups, OD, OH, OW;
+    int oh0, ohn, ow0, own;
+    int act, has_bias;
+};
+
+__global__ void __launch_bounds__(256) k_conv_simt(const float *__restrict__ x, const float *__restrict__ w,
+                                                   const float *__restrict__ bias, float *__restrict__ y, SimtConv c) {
+    const int cpg = c.C / c.groups, fpg = c.F / c.groups;
+    const long long total = (long long)c.N * c.F * c.OD * c.ohn * c.own;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        long long rem = i;
+        const int ww = c.ow0 + (int)(rem % c.own);
+        rem /= c.own;
+        const int hh = c.oh0 + (int)(rem % c.ohn);
+        rem /= c.ohn;
+        const int zz = (int)(rem % c.OD);
+        rem /= c.OD;
+        const int ff = (int)(rem % c.F);
+        const int nn = (int)(rem / c.F);
+        const int gidx = ff / fpg;
+        float acc = 0.f;
+        for (int cc = 0; cc < cpg; ++cc)
+            for (int tt = 0; tt < c.T; ++tt) {
+                const int pz = zz * c.sd + tt * c.dd - c.pd;
+                if (pz < 0 || pz >= c.D)
+                    continue;
+                for (int rr = 0; rr < c.R; ++rr) {
+                    const int py = hh * c.sh + rr * c.dh - c.ph;
+                    if (py < 0 || py >= c.H)
+                        continue;
+                    for (int ss = 0; ss < c.S; ++ss) {
+                        const int px = ww * c.sw + ss * c.dw - c.pw;
+                        if (px < 0 || px >= c.W)
+                            continue;
+                        const long long io = px + (long long)c.W * (py + (long long)c.H * (pz + (long long)c.D * ((cc + gidx * cpg) + (long long)c.C * nn)));
+                        const long long wo = ss + (long long)c.S * (rr + (long long)c.R * (tt + (long long)c.T * (cc + (long long)cpg * ff)));
+                        acc = fmaf(__ldg(w + wo), __ldg(x + io), acc);
+                    }
+                }
+            }
+        if (c.has_bias)
+            acc += __ldg(bias + ff);
+        y[ww + (long long)c.OW * (hh + (long long)c.OH * (zz + (long long)c.OD * (ff + (long long)c.F * nn)))] = apply_act(acc, c.act);
+    }
+}
+
+__global__ void __launch_bounds__(256) k_matmul_simt(const float *__restrict__ a, const float *__restrict__ b,
+                                                     const float *__restrict__ bias, float *__restrict__ c, int bs, int m,
+                                                     int n, int k, int transA, int transB, int act) {
+    const long long total = (long long)bs * m * n;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int nn = (int)(i % n);
+        const int mm = (int)((i / n) % m);
+        const int bb = (int)(i / ((long long)n * m));
+        float acc = 0.f;
+        for (int kk = 0; kk < k; ++kk) {
+            const float lhs = transA ? __ldg(a + mm + (long long)m * (kk + (long long)k * bb)) : __ldg(a + kk + (long long)k * (mm + (long long)m * bb));
+            const float rhs = transB ? __ldg(b + kk + (long long)k * (nn + (long long)n * bb)) : __ldg(b + nn + (long long)n * (kk + (long long)k * bb));
+            acc = fmaf(lhs, rhs, acc);
+        }
+        if (bias)
+            acc += __ldg(bias + nn);
+        c[i] = apply_act(acc, act);
+    }
+}
+
+// Re-pitches [planes, H, W] rows to a pitch divisible by 4 (zero fill), so TMA's 16-byte stride rule holds.
+__global__ void __launch_bounds__(256) k_repitch(const float *__restrict__ x, float *__restrict__ y, long long rows, int w, int wp) {
+    const long long total = rows * wp;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int col = (int)(i % wp);
+        const long long row = i / wp;
+        y[i] = col < w ? __ldg(x + row * w + col) : 0.f;
+    }
+}
+
+// [b][m][k] -> [b][k][m]
+__global__ void __launch_bounds__(256) k_transpose_a(const float *__restrict__ a, float *__restrict__ at, int bs, int m, int k) {
+    __shared__ float tile[32][33];
+    const int tiles_k = (k + 31) / 32, tiles_m = (m + 31) / 32;
+    const long long ntiles = (long long)bs * tiles_k * tiles_m;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+        const int tk = (int)(t % tiles_k);
+        const int tm = (int)((t / tiles_k) % tiles_m);
+        const int bb = (int)(t / ((long long)tiles_k * tiles_m));
+        for (int r = ty; r < 32; r += 8) {
+            const int mm = tm * 32 + r, kk = tk * 32 + tx;
+            tile[r][tx] = (mm < m && kk < k) ? __ldg(a + ((long long)bb * m + mm) * k + kk) : 0.f;
+        }
+        __syncthreads();
+        for (int r = ty; r < 32; r += 8) {
+            const int kk = tk * 32 + r, mm = tm * 32 + tx;
+            if (kk < k && mm < m)
+                at[((long long)bb * k + kk) * m + mm] = tile[tx][r];
+        }
+        __syncthreads();
+    }
+}
+
+static int grid_for(petb200_ctx *ctx, long long work, int per_block) {
+    long long blocks = (work + per_block - 1) / per_block;
+    return (int)std::max<long long>(1, std::min<long long>(blocks, (long long)ctx->sm_count * 16));
+}
+
+// -------------------------------------------------------------------------------------------------------------
+struct ConvPlan : petb200_plan {
+    int nsp = 2;
+    SimtConv sc{};
+    int algo = 0; // resolved: PETB200_ALGO_TC_3XTF32 or PETB200_ALGO_SIMT_FP32
+    void *tc = nullptr;
+    const float *w_simt = nullptr; // SIMT path keeps the caller's weight pointer
+    DevBuf xpad;                   // re-pitched input when W % 4 != 0 (tensor-core path only)
+    int wp = 0;
+    DevBuf bx, bw, bb, by; // timing operands
+    ~ConvPlan() override {
+        if (tc)
+            tc_conv_destroy(tc);
+    }
+    int bench_launch(cudaStream_t s) override;
+};
+
+int make_conv_plan(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const int *k, const int *pad, const int *stride,
+                   const int *dil, int groups, int has_bias, int act, int algo, petb200_plan **out) {
+    if (!ctx || !out)
+        return PETB200_ERR_INVALID;
+    const int nd = nsp + 2;
+    for (int i = 0; i < nd; ++i)
+        if (in_dims[i] <= 0)
+            return fail(ctx, PETB200_ERR_INVALID, "conv plan: non-positive input dim");
+    for (int i = 0; i < nsp; ++i)
+        if (k[i] <= 0 || stride[i] <= 0 || dil[i] <= 0 || pad[i] < 0)
+            return fail(ctx, PETB200_ERR_INVALID, "conv plan: bad kernel/stride/dilation/pad");
+    const int C = in_dims[1];
+    // ref: ConvOp::compute returns nullptr when f % g != 0 (src/Graph/operator.cc:108-110); groups = C / cpg
+    if (f <= 0 || groups <= 0 || C % groups != 0 || f % groups != 0)
+        return fail(ctx, PETB200_ERR_INVALID, "conv plan: channels %d / filters %d not divisible by groups %d", C, f, groups);
+    if (act < 0 || act > PETB200_ACT_GELU)
+        return fail(ctx, PETB200_ERR_INVALID, "conv plan: unknown activation %d", act);
+    auto *pl = new ConvPlan();
+    pl->ctx = ctx;
+    pl->nsp = nsp;
+    SimtConv &c = pl->sc;
+    c.N = in_dims[0];
+    c.C = C;
+    c.F = f;
+    c.groups = groups;
+    c.act = act;
+    c.has_bias = has_bias;
+    if (nsp == 3) {
+        c.D = in_dims[2], c.H = in_dims[3], c.W = in_dims[4];
+        c.T = k[0], c.R = k[1], c.S = k[2];
+        c.pd = pad[0], c.ph = pad[1], c.pw = pad[2];
+        c.sd = stride[0], c.sh = stride[1], c.sw = stride[2];
+        c.dd = dil[0], c.dh = dil[1], c.dw = dil[2];
+    } else {
+        c.D = 1, c.H = in_dims[2], c.W = in_dims[3];
+        c.T = 1, c.R = k[0], c.S = k[1];
+        c.pd = 0, c.ph = pad[0], c.pw = pad[1];
+        c.sd = 1, c.sh = stride[0], c.sw = stride[1];
+        c.dd = 1, c.dh = dil[0], c.dw = dil[1];
+    }
+    // ref: ConvOp::computeShape, src/Graph/operator.cc:220-221
+    c.OD = (c.D - (c.T - c.sd) * c.dd + 2 * c.pd) / c.sd;
+    c.OH = (c.H - (c.R - c.sh) * c.dh + 2 * c.ph) / c.sh;
+    c.OW = (c.W - (c.S - c.sw) * c.dw + 2 * c.pw) / c.sw;
+    if (c.OD <= 0 || c.OH <= 0 || c.OW <= 0) {
+        delete pl;
+        return fail(ctx, PETB200_ERR_INVALID, "conv plan: empty output");
+    }
+    c.oh0 = 0, c.ohn = c.OH, c.ow0 = 0, c.own = c.OW;
+    if (algo == PETB200_ALGO_TC_1XTF32) {
+        delete pl;
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "single-pass TF32 is not built");
+    }
+    int rc = PETB200_ERR_UNSUPPORTED;
+    if (algo == PETB200_ALGO_AUTO || algo == PETB200_ALGO_TC_3XTF32) {
+        size_t bytes = 0;
+        rc = tc_conv_create(ctx, nsp, in_dims, f, k, pad, stride, dil, groups, has_bias, act, &pl->tc, &bytes);
+        if (rc == PETB200_OK) {
+            pl->algo = PETB200_ALGO_TC_3XTF32;
+            pl->kernel = tc_conv_variant(pl->tc);
+            pl->device_bytes = bytes;
+            pl->wp = tc_conv_row_pitch(pl->tc);
+            if (pl->wp != c.W) {
+                size_t n = (size_t)c.N * c.C * c.D * c.H * pl->wp * 4;
+                if (pl->xpad.alloc(n) != cudaSuccess) {
+                    delete pl;
+                    return fail(ctx, PETB200_ERR_NOMEM, "re-pitch scratch allocation failed");
+                }
+                pl->device_bytes += n;
+            }
+        } else if (algo == PETB200_ALGO_TC_3XTF32 || rc != PETB200_ERR_UNSUPPORTED) {
+            delete pl;
+            return rc;
+        }
+    }
+    if (rc != PETB200_OK) {
+        pl->algo = PETB200_ALGO_SIMT_FP32;
+        pl->kernel = "simt_fp32";
+    }
+    *out = pl;
+    return PETB200_OK;
+}
+
+int conv_set_weights(petb200_plan *plan, const float *w, cudaStream_t s) {
+    auto *pl = dynamic_cast<ConvPlan *>(plan);
+    if (!pl || !w)
+        return PETB200_ERR_INVALID;
+    if (pl->algo == PETB200_ALGO_TC_3XTF32)
+        return tc_conv_set_weights(pl->tc, w, s);
+    pl->w_simt = w;
+    return PETB200_OK;
+}
+
+int conv_run(petb200_plan *plan, const float *x, const float *bias, float *y, const int *win, cudaStream_t s) {
+    auto *pl = dynamic_cast<ConvPlan *>(plan);
+    if (!pl)
+        return PETB200_ERR_INVALID;
+    petb200_ctx *ctx = pl->ctx;
+    if (!x || !y)
+        return fail(ctx, PETB200_ERR_INVALID, "conv run: null buffer");
+    if (pl->sc.has_bias && !bias)
+        return fail(ctx, PETB200_ERR_INVALID, "conv run: plan was made with a bias but none was passed");
+    if (pl->algo == PETB200_ALGO_TC_3XTF32) {
+        const float *xin = x;
+        if (pl->xpad.p) {
+            const SimtConv &c = pl->sc;
+            long long rows = (long long)c.N * c.C * c.D * c.H;
+            k_repitch<<<grid_for(ctx, rows * pl->wp, 256), 256, 0, s>>>(x, (float *)pl->xpad.p, rows, c.W, pl->wp);
+            int rc = launched(ctx, "k_repitch");
+            if (rc)
+                return rc;
+            xin = (const float *)pl->xpad.p;
+        }
+        return tc_conv_run(pl->tc, xin, bias, y, win, s);
+    }
+    if (!pl->w_simt)
+        return fail(ctx, PETB200_ERR_INVALID, "conv run before set_weights");
+    SimtConv c = pl->sc;
+    if (win) {
+        if (win[0] < 0 || win[1] <= 0 || win[0] + win[1] > c.OH || win[2] < 0 || win[3] <= 0 || win[2] + win[3] > c.OW)
+            return fail(ctx, PETB200_ERR_INVALID, "correction window outside the output");
+        c.oh0 = win[0], c.ohn = win[1], c.ow0 = win[2], c.own = win[3];
+    }
+    long long total = (long long)c.N * c.F * c.OD * c.ohn * c.own;
+    k_conv_simt<<<grid_for(ctx, total, 256), 256, 0, s>>>(x, pl->w_simt, bias, y, c);
+    return launched(ctx, "k_conv_simt");
+}
+
+int conv_out_dims(const petb200_plan *plan, int *d5) {
+    auto *pl = dynamic_cast<const ConvPlan *>(plan);
+    if (!pl)
+        return PETB200_ERR_INVALID;
+    d5[0] = pl->sc.N, d5[1] = pl->sc.F, d5[2] = pl->sc.OD, d5[3] = pl->sc.OH, d5[4] = pl->sc.OW;
+    return PETB200_OK;
+}
+
+int ConvPlan::bench_launch(cudaStream_t s) {
+    const SimtConv &c = sc;
+    if (!bx.p) {
+        size_t nx = (size_t)c.N * c.C * c.D * c.H * c.W, nw = (size_t)c.F * (c.C / c.groups) * c.T * c.R * c.S;
+        size_t ny = (size_t)c.N * c.F * c.OD * c.OH * c.OW;
+        if (bx.alloc(nx * 4) != cudaSuccess || bw.alloc(nw * 4) != cudaSuccess || by.alloc(ny * 4) != cudaSuccess ||
+            bb.alloc((size_t)c.F * 4) != cudaSuccess)
+            return fail(ctx, PETB200_ERR_NOMEM, "scratch allocation for timing failed");
+        // 0x3c3c3c3c is 0.0115 as fp32: finite, non-trivial operands
+        cudaMemsetAsync(bx.p, 0x3c, nx * 4, s);
+        cudaMemsetAsync(bw.p, 0x3c, nw * 4, s);
+        cudaMemsetAsync(bb.p, 0, (size_t)c.F * 4, s);
+        int rc = conv_set_weights(this, (const float *)bw.p, s);
+        if (rc)
+            return rc;
+    }
+    return conv_run(this, (const float *)bx.p, c.has_bias ? (const float *)bb.p : nullptr, (float *)by.p, nullptr, s);
+}
+
+// -------------------------------------------------------------------------------------------------------------
+struct MatmulPlan : petb200_plan {
+    int transA, transB, bs, m, n, k, has_bias, act;
+    int algo = 0;
+    void *tc = nullptr;
+    DevBuf at; // A re-laid as [b][k][m] when the caller's A is [b][m][k]
+    DevBuf ba, bbm, bbias, bc;
+    ~MatmulPlan() override {
+        if (tc)
+            tc_matmul_destroy(tc);
+    }
+    int bench_launch(cudaStream_t s) override;
+};
+
+int make_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int n, int k, int has_bias, int act, int algo,
+                     petb200_plan **out) {
+    if (!ctx || !out)
+        return PETB200_ERR_INVALID;
+    if (b <= 0 || m <= 0 || n <= 0 || k <= 0)
+        return fail(ctx, PETB200_ERR_INVALID, "matmul plan: non-positive extent");
+    if (act < 0 || act > PETB200_ACT_GELU)
+        return fail(ctx, PETB200_ERR_INVALID, "matmul plan: unknown activation %d", act);
+    auto *pl = new MatmulPlan();
+    pl->ctx = ctx;
+    pl->transA = transA != 0, pl->transB = transB != 0, pl->bs = b, pl->m = m, pl->n = n, pl->k = k;
+    pl->has_bias = has_bias, pl->act = act;
+    int rc = PETB200_ERR_UNSUPPORTED;
+    if (algo == PETB200_ALGO_AUTO || algo == PETB200_ALGO_TC_3XTF32) {
+        size_t bytes = 0;
+        rc = (m % 4 == 0) ? tc_matmul_create(ctx, b, m, n, k, pl->transB, has_bias, act, &pl->tc, &bytes)
+                          : fail(ctx, PETB200_ERR_UNSUPPORTED, "tensor-core matmul needs m %% 4 == 0");
+        if (rc == PETB200_OK) {
+            pl->algo = PETB200_ALGO_TC_3XTF32;
+            pl->kernel = "tc_3xtf32_ss";
+            pl->device_bytes = bytes;
+            if (!pl->transA) {
+                if (pl->at.alloc((size_t)b * m * k * 4) != cudaSuccess) {
+                    delete pl;
+                    return fail(ctx, PETB200_ERR_NOMEM, "A re-layout scratch allocation failed");
+                }
+                pl->device_bytes += pl->at.bytes;
+            }
+        } else if (algo == PETB200_ALGO_TC_3XTF32 || rc != PETB200_ERR_UNSUPPORTED) {
+            delete pl;
+            return rc;
+        }
+    } else if (algo != PETB200_ALGO_SIMT_FP32) {
+        delete pl;
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "matmul plan: algo %d is not built", algo);
+    }
+    if (rc != PETB200_OK) {
+        pl->algo = PETB200_ALGO_SIMT_FP32;
+        pl->kernel = "simt_fp32";
+    }
+    *out = pl;
+    return PETB200_OK;
+}
+
+int matmul_run(petb200_plan *plan, const float *a, const float *b, const float *bias, float *c, cudaStream_t s) {
+    auto *pl = dynamic_cast<MatmulPlan *>(plan);
+    if (!pl)
+        return PETB200_ERR_INVALID;
+    petb200_ctx *ctx = pl->ctx;
+    if (!a || !b || !c)
+        return fail(ctx, PETB200_ERR_INVALID, "matmul run: null buffer");
+    if (pl->has_bias && !bias)
+        return fail(ctx, PETB200_ERR_INVALID, "matmul run: plan was made with a bias but none was passed");
+    if (pl->algo == PETB200_ALGO_TC_3XTF32) {
+        int rc = tc_matmul_pack_b(pl->tc, b, s);
+        if (rc)
+            return rc;
+        const float *at = a;
+        if (!pl->transA) {
+            long long tiles = (long long)pl->bs * ((pl->k + 31) / 32) * ((pl->m + 31) / 32);
+            k_transpose_a<<<(int)std::min<long long>(tiles, (long long)ctx->sm_count * 8), 256, 0, s>>>(a, (float *)pl->at.p, pl->bs, pl->m, pl->k);
+            rc = launched(ctx, "k_transpose_a");
+            if (rc)
+                return rc;
+            at = (const float *)pl->at.p;
+        }
+        return tc_matmul_run(pl->tc, at, pl->has_bias ? bias : nullptr, c, s);
+    }
+    long long total = (long long)pl->bs * pl->m * pl->n;
+    k_matmul_simt<<<grid_for(ctx, total, 256), 256, 0, s>>>(a, b, pl->has_bias ? bias : nullptr, c, pl->bs, pl->m, pl->n, pl->k,
+                                                            pl->transA, pl->transB, pl->act);
+    return launched(ctx, "k_matmul_simt");
+}
+
+int MatmulPlan::bench_launch(cudaStream_t s) {
+    if (!ba.p) {
+        size_t na = (size_t)bs * m * k, nb = (size_t)bs * k * n, nc = (size_t)bs * m * n;
+        if (ba.alloc(na * 4) != cudaSuccess || bbm.alloc(nb * 4) != cudaSuccess || bc.alloc(nc * 4) != cudaSuccess ||
+            bbias.alloc((size_t)n * 4) != cudaSuccess)
+            return fail(ctx, PETB200_ERR_NOMEM, "scratch allocation for timing failed");
+        cudaMemsetAsync(ba.p, 0x3c, na * 4, s);
+        cudaMemsetAsync(bbm.p, 0x3c, nb * 4, s);
+        cudaMemsetAsync(bbias.p, 0, (size_t)n * 4, s);
+    }
+    return matmul_run(this, (const float *)ba.p, (const float *)bbm.p, has_bias ? (const float *)bbias.p : nullptr, (float *)bc.p, s);
+}
+
+} // namespace petb200

@@ -1,0 +1,279 @@
+// Elementwise, activation, batch-norm, pooling, softmax and LayerNorm kernels.  All are bandwidth-bound:
+// 128-bit accesses where the shape allows, grids sized in multiples of the SM count, warp-shuffle reductions.
+#include "common.h"
+#include <algorithm>
+#include <cfloat>
+
+namespace petb200 {
+
+constexpr int kMaxIn = 4;
+struct EltArgs {
+    const float *in[kMaxIn];
+    unsigned long long size[kMaxIn];
+    int n_in, kind, act;
+};
+
+__device__ __forceinline__ float combine(int kind, float a, float b) {
+    return kind == 0 ? a + b : (kind == 1 ? a - b : a * b);
+}
+
+// Operand j is read at i % size_j (the reference's broadcast rule).  vec4 path: every operand either spans the whole
+// output or has a size divisible by 4 that divides into aligned groups.
+__global__ void __launch_bounds__(256) k_eltwise_v4(EltArgs a, float4 *__restrict__ out, size_t n4) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        size_t e = i * 4;
+        float4 v = __ldg(reinterpret_cast<const float4 *>(a.in[0] + e % a.size[0]));
+#pragma unroll
+        for (int j = 1; j < kMaxIn; ++j)
+            if (j < a.n_in) {
+                float4 w = __ldg(reinterpret_cast<const float4 *>(a.in[j] + e % a.size[j]));
+                v.x = combine(a.kind, v.x, w.x);
+                v.y = combine(a.kind, v.y, w.y);
+                v.z = combine(a.kind, v.z, w.z);
+                v.w = combine(a.kind, v.w, w.w);
+            }
+        v.x = apply_act(v.x, a.act);
+        v.y = apply_act(v.y, a.act);
+        v.z = apply_act(v.z, a.act);
+        v.w = apply_act(v.w, a.act);
+        out[i] = v;
+    }
+}
+
+__global__ void __launch_bounds__(256) k_eltwise(EltArgs a, float *__restrict__ out, size_t n) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float v = __ldg(a.in[0] + i % a.size[0]);
+#pragma unroll
+        for (int j = 1; j < kMaxIn; ++j)
+            if (j < a.n_in)
+                v = combine(a.kind, v, __ldg(a.in[j] + i % a.size[j]));
+        out[i] = apply_act(v, a.act);
+    }
+}
+
+__global__ void __launch_bounds__(256) k_batchnorm(const float *__restrict__ x, const float *__restrict__ scale,
+                                                   const float *__restrict__ bias, const float *__restrict__ mean,
+                                                   const float *__restrict__ var, float *__restrict__ y, size_t total,
+                                                   int c, size_t inner, float eps) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        int cc = (int)((i / inner) % c);
+        // the reference forms scale/sqrt(var+eps) in double (src/Graph/operator.cc:2669-2671)
+        double k = (double)__ldg(scale + cc) / sqrt((double)__ldg(var + cc) + (double)eps);
+        y[i] = (float)(((double)__ldg(x + i) - (double)__ldg(mean + cc)) * k + (double)__ldg(bias + cc));
+    }
+}
+
+__global__ void __launch_bounds__(256) k_pool2d(int kind, const float *__restrict__ x, float *__restrict__ y, int nc,
+                                                int h, int w, int oh, int ow, int kh, int kw, int ph, int pw, int sh,
+                                                int sw) {
+    size_t total = (size_t)nc * oh * ow;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        int j = (int)(i % ow);
+        size_t r = i / ow;
+        int ii = (int)(r % oh);
+        size_t plane = r / oh;
+        const float *xp = x + plane * (size_t)h * w;
+        float best = -INFINITY, acc = 0.f;
+        int cnt = 0;
+        for (int a = 0; a < kh; ++a) {
+            int yy = ii * sh + a - ph;
+            if (yy < 0 || yy >= h)
+                continue;
+            for (int b = 0; b < kw; ++b) {
+                int xx = j * sw + b - pw;
+                if (xx < 0 || xx >= w)
+                    continue;
+                float v = __ldg(xp + (size_t)yy * w + xx);
+                best = fmaxf(best, v);
+                acc += v;
+                cnt++;
+            }
+        }
+        y[i] = kind == 0 ? best : (cnt ? acc / (float)cnt : 0.f);
+    }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// One warp per row; rows are short (<= a few thousand) in every PET workload, so the row stays in registers/L1.
+__global__ void __launch_bounds__(256) k_rowmean(const float *__restrict__ x, float *__restrict__ y, size_t rows, int cols) {
+    size_t warp = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    for (size_t r = warp; r < rows; r += nwarps) {
+        const float *xp = x + r * (size_t)cols;
+        float s = 0.f;
+        for (int i = lane; i < cols; i += 32)
+            s += __ldg(xp + i);
+        s = warp_sum(s);
+        if (lane == 0)
+            y[r] = s / (float)cols;
+    }
+}
+
+__global__ void __launch_bounds__(256) k_softmax(const float *__restrict__ x, float *__restrict__ y, size_t rows, int cols) {
+    size_t warp = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    for (size_t r = warp; r < rows; r += nwarps) {
+        const float *xp = x + r * (size_t)cols;
+        float *yp = y + r * (size_t)cols;
+        float mx = -INFINITY;
+        for (int i = lane; i < cols; i += 32)
+            mx = fmaxf(mx, __ldg(xp + i));
+        mx = warp_max(mx);
+        float den = 0.f;
+        for (int i = lane; i < cols; i += 32)
+            den += expf(__ldg(xp + i) - mx);
+        den = warp_sum(den);
+        float inv = 1.f / den;
+        for (int i = lane; i < cols; i += 32)
+            yp[i] = expf(__ldg(xp + i) - mx) * inv;
+    }
+}
+
+__global__ void __launch_bounds__(256) k_layernorm(const float *__restrict__ x, const float *__restrict__ gamma,
+                                                   const float *__restrict__ beta, float *__restrict__ y, size_t rows,
+                                                   int cols, float eps) {
+    size_t warp = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    for (size_t r = warp; r < rows; r += nwarps) {
+        const float *xp = x + r * (size_t)cols;
+        float *yp = y + r * (size_t)cols;
+        float s = 0.f;
+        for (int i = lane; i < cols; i += 32)
+            s += __ldg(xp + i);
+        float mean = warp_sum(s) / (float)cols;
+        float v = 0.f;
+        for (int i = lane; i < cols; i += 32) {
+            float d = __ldg(xp + i) - mean;
+            v += d * d;
+        }
+        float inv = rsqrtf(warp_sum(v) / (float)cols + eps);
+        for (int i = lane; i < cols; i += 32) {
+            float o = (__ldg(xp + i) - mean) * inv;
+            if (gamma)
+                o *= __ldg(gamma + i);
+            if (beta)
+                o += __ldg(beta + i);
+            yp[i] = o;
+        }
+    }
+}
+
+static int grid_for(petb200_ctx *ctx, size_t work_items, int per_block) {
+    size_t blocks = (work_items + per_block - 1) / per_block;
+    size_t cap = (size_t)ctx->sm_count * 16;
+    return (int)std::max<size_t>(1, std::min(blocks, cap));
+}
+
+} // namespace petb200
+
+using namespace petb200;
+
+extern "C" int petb200_eltwise_run(petb200_ctx *ctx, int kind, int n_in, const float *const *ins, const size_t *sizes,
+                                   float *out, size_t out_size, int act, petb200_stream stream) {
+    if (!ctx || !ins || !sizes || !out || kind < 0 || kind > 2 || n_in < 1 || n_in > kMaxIn || (kind == 1 && n_in != 2))
+        return fail(ctx, PETB200_ERR_INVALID, "eltwise_run: bad arguments");
+    if (out_size == 0)
+        return PETB200_OK;
+    EltArgs a{};
+    a.n_in = n_in;
+    a.kind = kind;
+    a.act = act;
+    bool v4 = (out_size % 4 == 0) && (((uintptr_t)out & 15) == 0);
+    for (int j = 0; j < n_in; ++j) {
+        if (!ins[j] || sizes[j] == 0)
+            return fail(ctx, PETB200_ERR_INVALID, "eltwise_run: operand %d empty", j);
+        a.in[j] = ins[j];
+        a.size[j] = sizes[j];
+        v4 = v4 && (sizes[j] % 4 == 0) && (((uintptr_t)ins[j] & 15) == 0);
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    if (v4) {
+        k_eltwise_v4<<<grid_for(ctx, out_size / 4, 256), 256, 0, s>>>(a, (float4 *)out, out_size / 4);
+        return launched(ctx, "k_eltwise_v4");
+    }
+    k_eltwise<<<grid_for(ctx, out_size, 256), 256, 0, s>>>(a, out, out_size);
+    return launched(ctx, "k_eltwise");
+}
+
+extern "C" int petb200_activation_run(petb200_ctx *ctx, const float *x, float *y, size_t n, int act,
+                                      petb200_stream stream) {
+    const float *ins[1] = {x};
+    size_t sizes[1] = {n};
+    if (!x || !y)
+        return fail(ctx, PETB200_ERR_INVALID, "activation_run: null buffer");
+    if (act < 0 || act > PETB200_ACT_GELU)
+        return fail(ctx, PETB200_ERR_INVALID, "activation_run: unknown activation %d", act);
+    return petb200_eltwise_run(ctx, 0, 1, ins, sizes, y, n, act, stream);
+}
+
+extern "C" int petb200_batchnorm_run(petb200_ctx *ctx, const float *x, const float *scale, const float *bias,
+                                     const float *mean, const float *var, float *y, size_t outer, int c, size_t inner,
+                                     float eps, petb200_stream stream) {
+    if (!ctx || !x || !scale || !bias || !mean || !var || !y || c <= 0)
+        return fail(ctx, PETB200_ERR_INVALID, "batchnorm_run: bad arguments");
+    size_t total = outer * (size_t)c * inner;
+    if (!total)
+        return PETB200_OK;
+    k_batchnorm<<<grid_for(ctx, total, 256), 256, 0, (cudaStream_t)stream>>>(x, scale, bias, mean, var, y, total, c,
+                                                                             inner, eps);
+    return launched(ctx, "k_batchnorm");
+}
+
+extern "C" int petb200_pool2d_run(petb200_ctx *ctx, int kind, const float *x, float *y, int n, int c, int h, int w,
+                                  int kh, int kw, int ph, int pw, int sh, int sw, petb200_stream stream) {
+    if (!ctx || !x || !y || kind < 0 || kind > 1 || n <= 0 || c <= 0 || h <= 0 || w <= 0 || kh <= 0 || kw <= 0 ||
+        sh <= 0 || sw <= 0 || ph < 0 || pw < 0)
+        return fail(ctx, PETB200_ERR_INVALID, "pool2d_run: bad arguments");
+    int oh = (h - (kh - sh) + 2 * ph) / sh, ow = (w - (kw - sw) + 2 * pw) / sw;
+    if (oh <= 0 || ow <= 0)
+        return fail(ctx, PETB200_ERR_INVALID, "pool2d_run: empty output");
+    size_t total = (size_t)n * c * oh * ow;
+    k_pool2d<<<grid_for(ctx, total, 256), 256, 0, (cudaStream_t)stream>>>(kind, x, y, n * c, h, w, oh, ow, kh, kw, ph,
+                                                                          pw, sh, sw);
+    return launched(ctx, "k_pool2d");
+}
+
+extern "C" int petb200_rowmean_run(petb200_ctx *ctx, const float *x, float *y, size_t rows, int cols,
+                                   petb200_stream stream) {
+    if (!ctx || !x || !y || cols <= 0)
+        return fail(ctx, PETB200_ERR_INVALID, "rowmean_run: bad arguments");
+    if (!rows)
+        return PETB200_OK;
+    k_rowmean<<<grid_for(ctx, rows, 8), 256, 0, (cudaStream_t)stream>>>(x, y, rows, cols);
+    return launched(ctx, "k_rowmean");
+}
+
+extern "C" int petb200_softmax_run(petb200_ctx *ctx, const float *x, float *y, size_t rows, int cols,
+                                   petb200_stream stream) {
+    if (!ctx || !x || !y || cols <= 0)
+        return fail(ctx, PETB200_ERR_INVALID, "softmax_run: bad arguments");
+    if (!rows)
+        return PETB200_OK;
+    k_softmax<<<grid_for(ctx, rows, 8), 256, 0, (cudaStream_t)stream>>>(x, y, rows, cols);
+    return launched(ctx, "k_softmax");
+}
+
+extern "C" int petb200_layernorm_run(petb200_ctx *ctx, const float *x, const float *gamma, const float *beta, float *y,
+                                     size_t rows, int cols, float eps, petb200_stream stream) {
+    if (!ctx || !x || !y || cols <= 0)
+        return fail(ctx, PETB200_ERR_INVALID, "layernorm_run: bad arguments");
+    if (!rows)
+        return PETB200_OK;
+    k_layernorm<<<grid_for(ctx, rows, 8), 256, 0, (cudaStream_t)stream>>>(x, gamma, beta, y, rows, cols, eps);
+    return launched(ctx, "k_layernorm");
+}

@@ -1,0 +1,913 @@
+// Implicit-GEMM convolution / matmul on the 5th-generation tensor cores (tcgen05) with error-compensated TF32.
+//
+//   D[pixel, filter] = sum_k A[pixel, k] * B[filter, k]            k = (channel chunk, tap, channel in chunk)
+//
+// One CTA computes a 128-pixel x BN-filter tile; the fp32 accumulator lives in tensor memory (TMEM).
+//   warp 0   : TMA producer for the packed weights: per 32-wide K stage one 2-D tile of B_hi and one of B_lo,
+//              straight into 128-byte-swizzled K-major shared memory.
+//   warp 2   : TMA producer for the RAW activation tile of one channel chunk (all taps share it): a 5-D box
+//              [images, channels, depth, rows, cols] of the NC(D)HW input, zero-filled outside the tensor, which
+//              is exactly the convolution's zero padding.  Box start along W is rounded down to 16 bytes.
+//   warps 3-6: transform.  Thread p owns pixel p of the tile: for every K stage it gathers its 32 values from the
+//              raw tile through a precomputed offset table (tap shift, dilation, channel plane), splits each fp32
+//              into hi (top 19 bits) and lo = x - hi, and writes the two K-major operand tiles — into swizzled
+//              shared memory (SS variant) or directly into TMEM with tcgen05.st (TS variant, which leaves the
+//              shared-memory read port to B alone).  The same warps run the epilogue.
+//   warp 1   : one thread issues, per K=8 step, three MMAs  lo*hi + hi*lo + hi*hi  (3xTF32) and commits stage
+//              release barriers.
+// Epilogue: tcgen05.ld -> +bias -> activation -> global stores, coalesced across the 32 pixels of a warp (conv)
+// or 128-bit per thread (row-major matmul output).
+//
+// Every wait on an mbarrier is bounded (~2 s) and reports through a status word instead of hanging the GPU.
+// No cluster launch, no multicast.
+#include "common.h"
+#include "tc_ptx.cuh"
+#include <algorithm>
+#include <cstdlib>
+#include <map>
+
+namespace petb200 {
+
+constexpr int kTileM = 128;
+constexpr int kStageK = 32;               // fp32/TF32 values per K stage = one 128-byte swizzle row
+constexpr int kAHalfBytes = kTileM * 128; // one 128 x 32 operand tile
+constexpr int kThreads = 224;
+
+struct IgemmParams {
+    int M_total, Pw;        // pixels in the whole problem (per image-batch z when z_is_batch); pixels per image
+    int OD, OH, OW;         // full output extents (for addressing y)
+    int ohn, own, oh0, ow0; // output window actually computed (ohn*own*OD = Pw)
+    int sd, sh, sw, pd, ph, pw;
+    int x0;                 // box origin along W (multiple of 4, may be negative)
+    int RN, RD, RH, RW, BC; // raw box extents
+    int nchunks, spc;       // channel chunks; K stages per chunk
+    int cpg, Fg, BN;        // channels per group, filters per group, tile N
+    int z_is_batch;         // blockIdx.z: 0 = conv group, 1 = matmul batch
+    int wide, row_tiles;    // wide mode: a tile is 128 consecutive pixels of ONE output row (rows wider than a tile)
+    int NA, NB;             // ring depths
+    int raw_bytes;          // bytes of one raw buffer (128-aligned)
+    long long ys_n, ys_f, ys_p;
+    int act, has_bias;
+    const int *koff;
+    const float *bias;
+    float *y;
+    int *status;
+};
+
+struct SmemLayout {
+    uint32_t a_off, b_off, raw_off, koff_off, bar_off, total;
+};
+__host__ __device__ inline SmemLayout smem_layout(const IgemmParams &P, bool a_tmem) {
+    SmemLayout L;
+    uint32_t o = 0;
+    L.a_off = o;
+    o += a_tmem ? 0 : (uint32_t)P.NA * 2 * kAHalfBytes;
+    L.b_off = o;
+    o += (uint32_t)P.NB * 2 * (uint32_t)P.BN * 128;
+    L.raw_off = o;
+    o += 2u * (uint32_t)P.raw_bytes;
+    L.koff_off = o;
+    o += (uint32_t)P.spc * kStageK * 4;
+    L.bar_off = (o + 15) & ~15u;
+    L.total = L.bar_off + 256;
+    return L;
+}
+
+// Which images / depth slices / rows a tile of pixels [m_lo, m_hi] touches; shared by the raw producer, the
+// transform threads and the host-side sizing of the raw box.
+__host__ __device__ inline void tile_span(const IgemmParams &P, int m_lo, int m_hi, int &n_lo, int &n_hi, int &zl_lo,
+                                          int &zl_hi, int &yl_lo, int &yl_hi) {
+    int plane = P.ohn * P.own;
+    n_lo = m_lo / P.Pw;
+    n_hi = m_hi / P.Pw;
+    int q_lo = m_lo - n_lo * P.Pw, q_hi = m_hi - n_hi * P.Pw;
+    if (n_lo != n_hi) {
+        zl_lo = 0;
+        zl_hi = P.OD - 1;
+        yl_lo = 0;
+        yl_hi = P.ohn - 1;
+        return;
+    }
+    zl_lo = q_lo / plane;
+    zl_hi = q_hi / plane;
+    if (zl_lo != zl_hi) {
+        yl_lo = 0;
+        yl_hi = P.ohn - 1;
+        return;
+    }
+    yl_lo = (q_lo - zl_lo * plane) / P.own;
+    yl_hi = (q_hi - zl_hi * plane) / P.own;
+}
+
+template <bool A_TMEM>
+__global__ void __launch_bounds__(kThreads, 1)
+k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_bhi,
+        const __grid_constant__ CUtensorMap tmap_blo, const IgemmParams P) {
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment for the swizzled operand tiles
+    uint8_t *smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
+    const SmemLayout L = smem_layout(P, A_TMEM);
+    uint8_t *sA = smem + L.a_off;
+    uint8_t *sB = smem + L.b_off;
+    uint8_t *sRaw = smem + L.raw_off;
+    int *sKoff = reinterpret_cast<int *>(smem + L.koff_off);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L.bar_off);
+    // barrier slots
+    uint64_t *raw_full = bars, *raw_empty = bars + 2;
+    uint64_t *b_full = bars + 4, *b_empty = bars + 8;   // up to 4 stages
+    uint64_t *a_full = bars + 12, *a_empty = bars + 16; // up to 4 stages
+    uint64_t *acc_full = bars + 20;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 21);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 22);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * kTileM;
+    const int ntile = blockIdx.y;
+    const int zb = blockIdx.z;
+    const int KS = P.nchunks * P.spc;
+    const uint32_t b_half = (uint32_t)P.BN * 128u;
+    const uint32_t tmem_cols = A_TMEM ? 512u : (P.BN <= 32 ? 32u : (P.BN <= 64 ? 64u : (P.BN <= 128 ? 128u : 256u)));
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(raw_full + i, 1);
+            ptx::mbar_init(raw_empty + i, 4);
+        }
+        for (int i = 0; i < 4; ++i) {
+            ptx::mbar_init(b_full + i, 1);
+            ptx::mbar_init(b_empty + i, 1);
+            ptx::mbar_init(a_full + i, 4);
+            ptx::mbar_init(a_empty + i, 1);
+        }
+        ptx::mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tmap(&tmap_x);
+        ptx::prefetch_tmap(&tmap_bhi);
+        ptx::prefetch_tmap(&tmap_blo);
+    }
+    for (int i = threadIdx.x; i < P.spc * kStageK; i += kThreads)
+        sKoff[i] = P.koff[i];
+    if (warp == 2) {
+        ptx::tmem_alloc(tmem_slot, tmem_cols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // Tile origin in the input: first image, depth slice, row and (16-byte aligned) column of the raw box.
+    int n_lo = 0, z_start, y_start, x_start, w_zl = 0, w_yl = 0, w_tx = 0;
+    if (P.wide) {
+        const int row = blockIdx.x / P.row_tiles;
+        w_tx = blockIdx.x - row * P.row_tiles;
+        n_lo = row / (P.OD * P.ohn);
+        w_zl = (row / P.ohn) % P.OD;
+        w_yl = row % P.ohn;
+        z_start = w_zl * P.sd - P.pd;
+        y_start = (P.oh0 + w_yl) * P.sh - P.ph;
+        const int xs = (P.ow0 + w_tx * kTileM) * P.sw - P.pw;
+        x_start = (xs >= 0) ? (xs & ~3) : -(((-xs) + 3) & ~3);
+    } else {
+        const int m_hi = min(m0 + kTileM, P.M_total) - 1;
+        int n_hi, zl_lo, zl_hi, yl_lo, yl_hi;
+        tile_span(P, m0, m_hi, n_lo, n_hi, zl_lo, zl_hi, yl_lo, yl_hi);
+        z_start = zl_lo * P.sd - P.pd;
+        y_start = (P.oh0 + yl_lo) * P.sh - P.ph;
+        x_start = P.x0;
+    }
+
+    if (warp == 0) {
+        // ---------------- packed-weight producer ----------------
+        const int row0 = zb * P.Fg + ntile * P.BN;
+        for (int ks = 0; ks < KS; ++ks) {
+            const int sb = ks % P.NB;
+            const uint32_t ph = (uint32_t)((ks / P.NB) & 1);
+            if (lane == 0) {
+                if (ptx::mbar_wait(b_empty + sb, ph ^ 1u, abort_flag)) {
+                    ptx::mbar_expect_tx(b_full + sb, 2u * b_half);
+                    ptx::tma_load_2d(sB + (size_t)sb * 2 * b_half, &tmap_bhi, b_full + sb, ks * kStageK, row0);
+                    ptx::tma_load_2d(sB + (size_t)sb * 2 * b_half + b_half, &tmap_blo, b_full + sb, ks * kStageK, row0);
+                }
+            }
+            __syncwarp();
+            if (*abort_flag)
+                break;
+        }
+    } else if (warp == 2) {
+        // ---------------- raw activation producer ----------------
+        const int c_base = P.z_is_batch ? 0 : zb * P.cpg;
+        const int n_start = P.z_is_batch ? zb : n_lo;
+        for (int ch = 0; ch < P.nchunks; ++ch) {
+            const int rb = ch & 1;
+            const uint32_t ph = (uint32_t)((ch >> 1) & 1);
+            if (lane == 0) {
+                if (ptx::mbar_wait(raw_empty + rb, ph ^ 1u, abort_flag)) {
+                    ptx::mbar_expect_tx(raw_full + rb, (uint32_t)P.RN * P.BC * P.RD * P.RH * P.RW * 4u);
+                    ptx::tma_load_5d(sRaw + (size_t)rb * P.raw_bytes, &tmap_x, raw_full + rb, x_start, y_start, z_start,
+                                     c_base + ch * P.BC, n_start);
+                }
+            }
+            __syncwarp();
+            if (*abort_flag)
+                break;
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t idesc = ptx::idesc_tf32(kTileM, P.BN);
+        uint32_t accumulate = 0;
+        for (int ks = 0; ks < KS; ++ks) {
+            const int sa = ks % P.NA, sb = ks % P.NB;
+            if (lane == 0) {
+                bool ok = ptx::mbar_wait(a_full + sa, (uint32_t)((ks / P.NA) & 1), abort_flag) &&
+                          ptx::mbar_wait(b_full + sb, (uint32_t)((ks / P.NB) & 1), abort_flag);
+                if (ok) {
+                    ptx::tc_fence_after();
+                    const uint64_t bhi = ptx::smem_desc_k128(ptx::smem_u32(sB + (size_t)sb * 2 * b_half));
+                    const uint64_t blo = ptx::smem_desc_k128(ptx::smem_u32(sB + (size_t)sb * 2 * b_half + b_half));
+                    if (A_TMEM) {
+                        const uint32_t ahi = tmem_base + 256u + (uint32_t)sa * 64u, alo = ahi + 32u;
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            ptx::mma_tf32_ts(tmem_base, alo + kk * 8, bhi + 2 * kk, idesc, accumulate);
+                            ptx::mma_tf32_ts(tmem_base, ahi + kk * 8, blo + 2 * kk, idesc, 1u);
+                            ptx::mma_tf32_ts(tmem_base, ahi + kk * 8, bhi + 2 * kk, idesc, 1u);
+                            accumulate = 1u;
+                        }
+                    } else {
+                        const uint64_t ahi = ptx::smem_desc_k128(ptx::smem_u32(sA + (size_t)sa * 2 * kAHalfBytes));
+                        const uint64_t alo = ptx::smem_desc_k128(ptx::smem_u32(sA + (size_t)sa * 2 * kAHalfBytes + kAHalfBytes));
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            ptx::mma_tf32_ss(tmem_base, alo + 2 * kk, bhi + 2 * kk, idesc, accumulate);
+                            ptx::mma_tf32_ss(tmem_base, ahi + 2 * kk, blo + 2 * kk, idesc, 1u);
+                            ptx::mma_tf32_ss(tmem_base, ahi + 2 * kk, bhi + 2 * kk, idesc, 1u);
+                            accumulate = 1u;
+                        }
+                    }
+                    ptx::mma_commit(a_empty + sa);
+                    ptx::mma_commit(b_empty + sb);
+                }
+            }
+            __syncwarp();
+            if (*abort_flag)
+                break;
+        }
+        if (lane == 0 && !*abort_flag)
+            ptx::mma_commit(acc_full);
+        __syncwarp();
+    } else {
+        // ---------------- transform + epilogue (warps 3..6) ----------------
+        const int quarter = warp & 3;         // TMEM lane quarter this warp may access
+        const int p = quarter * 32 + lane;    // pixel row inside the tile
+        bool valid;
+        int base_p = 0;
+        long long y_off = 0;
+        if (P.wide) {
+            const int xl = w_tx * kTileM + p;
+            valid = xl < P.own;
+            if (valid) {
+                const int oh = P.oh0 + w_yl, ow = P.ow0 + xl;
+                base_p = ow * P.sw - P.pw - x_start;
+                const long long img = P.z_is_batch ? (long long)zb : (long long)n_lo;
+                y_off = img * P.ys_n + ((long long)(w_zl * P.OH + oh) * P.OW + ow) * P.ys_p;
+            }
+        } else {
+            const int m = m0 + p;
+            valid = m < P.M_total;
+            if (valid) {
+                const int plane = P.ohn * P.own;
+                const int n = m / P.Pw;
+                int q = m - n * P.Pw;
+                const int zl = q / plane;
+                q -= zl * plane;
+                const int yl = q / P.own;
+                const int xl = q - yl * P.own;
+                const int oh = P.oh0 + yl, ow = P.ow0 + xl;
+                base_p = (((n - n_lo) * P.BC * P.RD + (zl * P.sd - P.pd - z_start)) * P.RH + (oh * P.sh - P.ph - y_start)) * P.RW +
+                         (ow * P.sw - P.pw - x_start);
+                const long long img = P.z_is_batch ? (long long)zb : (long long)n;
+                y_off = img * P.ys_n + ((long long)(zl * P.OH + oh) * P.OW + ow) * P.ys_p;
+            }
+        }
+        bool alive = true;
+        for (int ch = 0; ch < P.nchunks && alive; ++ch) {
+            const int rb = ch & 1;
+            alive = ptx::mbar_wait(raw_full + rb, (uint32_t)((ch >> 1) & 1), abort_flag);
+            const float *raw = reinterpret_cast<const float *>(sRaw + (size_t)rb * P.raw_bytes) + base_p;
+            for (int st = 0; st < P.spc && alive; ++st) {
+                const int ks = ch * P.spc + st;
+                const int sa = ks % P.NA;
+                alive = ptx::mbar_wait(a_empty + sa, (uint32_t)(((ks / P.NA) & 1) ^ 1), abort_flag);
+                if (!alive)
+                    break;
+                const int4 *ko = reinterpret_cast<const int4 *>(sKoff + st * kStageK);
+                if (A_TMEM) {
+                    ptx::tc_fence_after();
+                    uint32_t hi[32], lo[32];
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4) {
+                        const int4 o = ko[c4];
+                        float v0 = o.x >= 0 ? raw[o.x] : 0.f, v1 = o.y >= 0 ? raw[o.y] : 0.f;
+                        float v2 = o.z >= 0 ? raw[o.z] : 0.f, v3 = o.w >= 0 ? raw[o.w] : 0.f;
+                        hi[4 * c4 + 0] = __float_as_uint(v0) & 0xffffe000u;
+                        hi[4 * c4 + 1] = __float_as_uint(v1) & 0xffffe000u;
+                        hi[4 * c4 + 2] = __float_as_uint(v2) & 0xffffe000u;
+                        hi[4 * c4 + 3] = __float_as_uint(v3) & 0xffffe000u;
+                        lo[4 * c4 + 0] = __float_as_uint(v0 - __uint_as_float(hi[4 * c4 + 0]));
+                        lo[4 * c4 + 1] = __float_as_uint(v1 - __uint_as_float(hi[4 * c4 + 1]));
+                        lo[4 * c4 + 2] = __float_as_uint(v2 - __uint_as_float(hi[4 * c4 + 2]));
+                        lo[4 * c4 + 3] = __float_as_uint(v3 - __uint_as_float(hi[4 * c4 + 3]));
+                    }
+                    const uint32_t t = tmem_base + ((uint32_t)(quarter * 32) << 16) + 256u + (uint32_t)sa * 64u;
+                    ptx::tmem_st_32x32(t, hi);
+                    ptx::tmem_st_32x32(t + 32u, lo);
+                    ptx::tmem_st_wait();
+                    ptx::tc_fence_before();
+                } else {
+                    uint8_t *rowh = sA + (size_t)sa * 2 * kAHalfBytes + (size_t)p * 128;
+                    uint8_t *rowl = rowh + kAHalfBytes;
+#pragma unroll
+                    for (int c4 = 0; c4 < 8; ++c4) {
+                        const int4 o = ko[c4];
+                        float v0 = o.x >= 0 ? raw[o.x] : 0.f, v1 = o.y >= 0 ? raw[o.y] : 0.f;
+                        float v2 = o.z >= 0 ? raw[o.z] : 0.f, v3 = o.w >= 0 ? raw[o.w] : 0.f;
+                        float4 h, l;
+                        h.x = __uint_as_float(__float_as_uint(v0) & 0xffffe000u);
+                        h.y = __uint_as_float(__float_as_uint(v1) & 0xffffe000u);
+                        h.z = __uint_as_float(__float_as_uint(v2) & 0xffffe000u);
+                        h.w = __uint_as_float(__float_as_uint(v3) & 0xffffe000u);
+                        l.x = v0 - h.x;
+                        l.y = v1 - h.y;
+                        l.z = v2 - h.z;
+                        l.w = v3 - h.w;
+                        const int phys = (c4 ^ (p & 7)) << 4;
+                        *reinterpret_cast<float4 *>(rowh + phys) = h;
+                        *reinterpret_cast<float4 *>(rowl + phys) = l;
+                    }
+                    ptx::fence_proxy_async_smem();
+                }
+                __syncwarp();
+                if (lane == 0)
+                    ptx::mbar_arrive(a_full + sa);
+            }
+            __syncwarp();
+            if (lane == 0 && alive)
+                ptx::mbar_arrive(raw_empty + rb);
+        }
+        // ---------------- epilogue ----------------
+        if (alive)
+            alive = ptx::mbar_wait(acc_full, 0u, abort_flag);
+        if (alive) {
+            ptx::tc_fence_after();
+            const int f_tile0 = ntile * P.BN;
+            const long long f_glob0 = P.z_is_batch ? 0 : (long long)zb * P.Fg;
+            float *yp = P.y + y_off;
+            const bool vec_ok = (P.ys_f == 1) && ((P.ys_p & 3) == 0) && ((P.ys_n & 3) == 0) && ((P.Fg & 3) == 0) &&
+                                ((reinterpret_cast<uintptr_t>(P.y) & 15) == 0);
+            for (int cc = 0; cc < P.BN; cc += 32) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)cc, r);
+                ptx::tmem_ld_wait();
+                if (!valid)
+                    continue;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int fl = f_tile0 + cc + j;
+                    float v = __uint_as_float(r[j]);
+                    if (fl < P.Fg) {
+                        if (P.has_bias)
+                            v += __ldg(P.bias + f_glob0 + fl);
+                        v = apply_act(v, P.act);
+                    }
+                    r[j] = __float_as_uint(v);
+                }
+                if (vec_ok) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const int fl = f_tile0 + cc + j;
+                        if (fl < P.Fg)
+                            *reinterpret_cast<uint4 *>(yp + f_glob0 + fl) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int fl = f_tile0 + cc + j;
+                        if (fl < P.Fg)
+                            yp[(f_glob0 + fl) * P.ys_f] = __uint_as_float(r[j]);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    if (*abort_flag) {
+        // give copies that may still be in flight time to land before the CTA's shared memory is released
+        uint64_t t0 = ptx::globaltimer_ns();
+        while (ptx::globaltimer_ns() - t0 < 200000ull)
+            __nanosleep(1000);
+        if (threadIdx.x == 0 && P.status)
+            atomicExch(P.status, 1);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 2)
+        ptx::tmem_dealloc(tmem_base, tmem_cols);
+}
+
+// -------------------------------------------------------------------------------------------------------------
+// weight packing: W[F][cpg][T] (conv) or B[b][k][n] / B[b][n][k] (matmul) -> hi/lo [rows][Ktot], K ordered as the
+// kernel consumes it: k = chunk*Kc_pad + tap*BC + ci, zero where there is no such element.
+// -------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) k_pack_conv_w(const float *__restrict__ w, float *__restrict__ hi,
+                                                     float *__restrict__ lo, int F, int cpg, int T, int BC, int Kc_pad,
+                                                     int nchunks) {
+    const long long Ktot = (long long)Kc_pad * nchunks;
+    const long long total = (long long)F * Ktot;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int f = (int)(i / Ktot);
+        const int k = (int)(i - (long long)f * Ktot);
+        const int ch = k / Kc_pad, kc = k - ch * Kc_pad;
+        const int tap = kc / BC, ci = kc - tap * BC;
+        const int c = ch * BC + ci;
+        float v = 0.f;
+        if (tap < T && c < cpg)
+            v = __ldg(w + ((long long)f * cpg + c) * T + tap);
+        const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+        hi[i] = h;
+        lo[i] = v - h;
+    }
+}
+
+__global__ void __launch_bounds__(256) k_pack_mm_b(const float *__restrict__ b, float *__restrict__ hi,
+                                                   float *__restrict__ lo, int bs, int n, int k, int Kpad, int transB) {
+    const long long total = (long long)bs * n * Kpad;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int kk = (int)(i % Kpad);
+        const long long row = i / Kpad;
+        const int nn = (int)(row % n);
+        const int bb = (int)(row / n);
+        float v = 0.f;
+        if (kk < k)
+            v = transB ? __ldg(b + ((long long)bb * n + nn) * k + kk) : __ldg(b + ((long long)bb * k + kk) * n + nn);
+        const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+        hi[i] = h;
+        lo[i] = v - h;
+    }
+}
+
+// -------------------------------------------------------------------------------------------------------------
+// host side
+// -------------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+struct TcCore {
+    petb200_ctx *ctx = nullptr;
+    IgemmParams P{};
+    bool a_tmem = false;
+    int single_pass = 0;
+    dim3 grid;
+    size_t smem = 0;
+    // geometry needed to (re)encode the activation map
+    int xd[5]{}; // W,H,D,C,N of the activation tensor as the kernel sees it
+    long long Ktot = 0;
+    int rows_b = 0;
+    DevBuf whi, wlo, koff;
+    CUtensorMap map_x{}, map_bhi{}, map_blo{};
+    const void *map_x_ptr = nullptr;
+    bool weights_ready = false;
+
+    int encode_x(const float *x) {
+        if (x == map_x_ptr)
+            return PETB200_OK;
+        EncodeTiledFn enc = encode_fn();
+        if (!enc)
+            return fail(ctx, PETB200_ERR_CUDA, "cuTensorMapEncodeTiled entry point unavailable");
+        cuuint64_t dims[5] = {(cuuint64_t)xd[0], (cuuint64_t)xd[1], (cuuint64_t)xd[2], (cuuint64_t)xd[3], (cuuint64_t)xd[4]};
+        cuuint64_t str[4] = {(cuuint64_t)xd[0] * 4, (cuuint64_t)xd[0] * xd[1] * 4, (cuuint64_t)xd[0] * xd[1] * xd[2] * 4,
+                             (cuuint64_t)xd[0] * xd[1] * xd[2] * xd[3] * 4};
+        cuuint32_t box[5] = {(cuuint32_t)P.RW, (cuuint32_t)P.RH, (cuuint32_t)P.RD, (cuuint32_t)P.BC, (cuuint32_t)P.RN};
+        cuuint32_t es[5] = {1, 1, 1, 1, 1};
+        CUresult r = enc(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float *>(x), dims, str, box, es,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS)
+            return fail(ctx, PETB200_ERR_CUDA, "cuTensorMapEncodeTiled(activations) failed with %d", (int)r);
+        map_x_ptr = x;
+        return PETB200_OK;
+    }
+    int encode_b() {
+        EncodeTiledFn enc = encode_fn();
+        if (!enc)
+            return fail(ctx, PETB200_ERR_CUDA, "cuTensorMapEncodeTiled entry point unavailable");
+        cuuint64_t dims[2] = {(cuuint64_t)Ktot, (cuuint64_t)rows_b};
+        cuuint64_t str[1] = {(cuuint64_t)Ktot * 4};
+        cuuint32_t box[2] = {(cuuint32_t)kStageK, (cuuint32_t)P.BN};
+        cuuint32_t es[2] = {1, 1};
+        for (int i = 0; i < 2; ++i) {
+            CUresult r = enc(i ? &map_blo : &map_bhi, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, i ? wlo.p : whi.p, dims, str, box,
+                             es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS)
+                return fail(ctx, PETB200_ERR_CUDA, "cuTensorMapEncodeTiled(weights) failed with %d", (int)r);
+        }
+        return PETB200_OK;
+    }
+    int launch(const float *x, const float *bias, float *y, cudaStream_t s) {
+        int rc = encode_x(x);
+        if (rc)
+            return rc;
+        IgemmParams p = P;
+        p.bias = bias;
+        p.y = y;
+        p.koff = (const int *)koff.p;
+        p.status = ctx->d_status;
+        p.has_bias = (P.has_bias && bias) ? 1 : 0;
+        if (a_tmem)
+            k_igemm<true><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
+        else
+            k_igemm<false><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
+        return launched(ctx, "k_igemm");
+    }
+};
+
+// Geometry of the convolution as the tensor-core kernel sees it.
+struct ConvGeom {
+    int N, C, D, H, W, Wst /*row pitch of the stored tensor, >= W*/, F, T3[3] /*t,r,s*/, pad[3], stride[3], dil[3], groups;
+    int OD, OH, OW;
+};
+
+static int env_int(const char *name, int dflt) {
+    const char *v = getenv(name);
+    return v ? atoi(v) : dflt;
+}
+
+// Fills core.P (tiling, raw box, stage counts) for a window [oh0,ohn) x [ow0,own) of the output; returns
+// PETB200_ERR_UNSUPPORTED when the shape does not fit this kernel's constraints.
+static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int oh0, int ohn, int ow0, int own,
+                        int z_is_batch, int images, long long ys_n, long long ys_f, long long ys_p, int has_bias, int act,
+                        int force_bc = 0) {
+    IgemmParams &P = core.P;
+    const int cpg = g.C / g.groups, Fg = g.F / g.groups;
+    if (g.Wst % 4 != 0)
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "tensor-core path needs a row pitch divisible by 4 (TMA stride rule), got %d", g.Wst);
+    P.OD = g.OD;
+    P.OH = g.OH;
+    P.OW = g.OW;
+    P.oh0 = oh0;
+    P.ohn = ohn;
+    P.ow0 = ow0;
+    P.own = own;
+    P.Pw = g.OD * ohn * own;
+    P.M_total = z_is_batch ? P.Pw : images * P.Pw;
+    P.sd = g.stride[0];
+    P.sh = g.stride[1];
+    P.sw = g.stride[2];
+    P.pd = g.pad[0];
+    P.ph = g.pad[1];
+    P.pw = g.pad[2];
+    P.cpg = cpg;
+    P.Fg = Fg;
+    P.z_is_batch = z_is_batch;
+    P.ys_n = ys_n;
+    P.ys_f = ys_f;
+    P.ys_p = ys_p;
+    P.has_bias = has_bias;
+    P.act = act;
+    // tile N
+    int BN = Fg <= 32 ? 32 : (Fg <= 64 ? 64 : 128);
+    BN = env_int("PETB200_TC_BN", BN);
+    if (BN != 32 && BN != 64 && BN != 128 && BN != 256)
+        return fail(ctx, PETB200_ERR_INVALID, "PETB200_TC_BN must be 32, 64, 128 or 256");
+    P.BN = BN;
+    P.wide = (own > kTileM) ? 1 : 0;
+    P.row_tiles = (own + kTileM - 1) / kTileM;
+    const int xs = ow0 * P.sw - P.pw;
+    P.x0 = (xs >= 0) ? (xs / 4) * 4 : -(((-xs) + 3) / 4) * 4;
+    if (P.wide) {
+        // one output row per tile: the box covers 128 pixels of one row (one depth slice, one image)
+        const int wneed = (kTileM - 1) * P.sw + (g.T3[2] - 1) * g.dil[2] + 1 + (xs - P.x0);
+        P.RW = (wneed + 3) / 4 * 4;
+        P.RN = 1;
+        P.RD = (g.T3[0] - 1) * g.dil[0] + 1;
+        P.RH = (g.T3[1] - 1) * g.dil[1] + 1;
+    } else {
+        const int wneed = (own - 1) * P.sw + (g.T3[2] - 1) * g.dil[2] + 1 + (xs - P.x0);
+        P.RW = (wneed + 3) / 4 * 4;
+        // raw box along images / depth / rows: maxima over all tiles (in OUTPUT units first)
+        int RN = 1, RDo = 1, RHo = 1;
+        for (int m0 = 0; m0 < P.M_total; m0 += kTileM) {
+            int m_hi = std::min(m0 + kTileM, P.M_total) - 1;
+            int n_lo, n_hi, zl_lo, zl_hi, yl_lo, yl_hi;
+            tile_span(P, m0, m_hi, n_lo, n_hi, zl_lo, zl_hi, yl_lo, yl_hi);
+            RN = std::max(RN, n_hi - n_lo + 1);
+            RDo = std::max(RDo, zl_hi - zl_lo + 1);
+            RHo = std::max(RHo, yl_hi - yl_lo + 1);
+        }
+        P.RN = z_is_batch ? 1 : RN;
+        P.RD = (RDo - 1) * P.sd + (g.T3[0] - 1) * g.dil[0] + 1;
+        P.RH = (RHo - 1) * P.sh + (g.T3[1] - 1) * g.dil[1] + 1;
+    }
+    if (P.RW > 256 || P.RH > 256 || P.RD > 256 || P.RN > 256)
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "raw activation box %dx%dx%dx%d exceeds the TMA box limit", P.RN, P.RD, P.RH, P.RW);
+    const int T = g.T3[0] * g.T3[1] * g.T3[2];
+    const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 1024; // alignment slack
+    core.a_tmem = env_int("PETB200_TC_A_TMEM", 0) != 0;
+    if (core.a_tmem && BN > 256)
+        return fail(ctx, PETB200_ERR_INVALID, "TS variant supports BN <= 256");
+    int BC = std::min(cpg, 32);
+    const int forced_bc = force_bc > 0 ? force_bc : env_int("PETB200_TC_BC", 0);
+    if (forced_bc > 0)
+        BC = std::min(forced_bc, cpg);
+    for (;; BC = std::max(1, BC / 2)) {
+        P.BC = BC;
+        P.spc = (T * BC + kStageK - 1) / kStageK;
+        P.nchunks = (cpg + BC - 1) / BC;
+        size_t raw = (size_t)P.RN * BC * P.RD * P.RH * P.RW * 4;
+        P.raw_bytes = (int)((raw + 127) / 128 * 128);
+        P.NA = core.a_tmem ? 4 : 2;
+        P.NB = 2;
+        bool fits = smem_layout(P, core.a_tmem).total <= budget;
+        if (fits) {
+            // deepen the rings while there is room: B first (it hides TMA latency), then A
+            for (bool grew = true; grew;) {
+                grew = false;
+                if (P.NB < 4) {
+                    P.NB++;
+                    if (smem_layout(P, core.a_tmem).total <= budget)
+                        grew = true;
+                    else
+                        P.NB--;
+                }
+                if (!core.a_tmem && P.NA < 3 && P.NB >= 3) {
+                    P.NA++;
+                    if (smem_layout(P, core.a_tmem).total <= budget)
+                        grew = true;
+                    else
+                        P.NA--;
+                }
+            }
+            break;
+        }
+        if (BC == 1 || forced_bc > 0)
+            return fail(ctx, PETB200_ERR_UNSUPPORTED, "raw activation tile does not fit shared memory");
+    }
+    core.smem = smem_layout(P, core.a_tmem).total + 1024;
+    const int mtiles = P.wide ? (z_is_batch ? 1 : images) * g.OD * ohn * P.row_tiles : (P.M_total + kTileM - 1) / kTileM;
+    core.grid = dim3((unsigned)mtiles, (unsigned)((Fg + BN - 1) / BN),
+                     (unsigned)(z_is_batch ? images : g.groups));
+    core.Ktot = (long long)P.nchunks * P.spc * kStageK;
+    core.xd[0] = g.Wst;
+    core.xd[1] = g.H;
+    core.xd[2] = g.D;
+    core.xd[3] = g.C;
+    core.xd[4] = g.N;
+    // offset table for one chunk
+    std::vector<int> koff((size_t)P.spc * kStageK, -1);
+    const int plane_w = P.RW, plane_h = P.RH * P.RW, plane_d = P.RD * plane_h;
+    for (int tap = 0; tap < T; ++tap) {
+        int t = tap / (g.T3[1] * g.T3[2]), r = (tap / g.T3[2]) % g.T3[1], s = tap % g.T3[2];
+        for (int ci = 0; ci < BC; ++ci)
+            koff[(size_t)tap * BC + ci] = ci * plane_d + t * g.dil[0] * plane_h + r * g.dil[1] * plane_w + s * g.dil[2];
+    }
+    if (core.koff.alloc(koff.size() * 4) != cudaSuccess)
+        return fail(ctx, PETB200_ERR_NOMEM, "koff allocation failed");
+    PETB200_CUDA(ctx, cudaMemcpy(core.koff.p, koff.data(), koff.size() * 4, cudaMemcpyHostToDevice));
+    cudaError_t e = core.a_tmem ? cudaFuncSetAttribute(k_igemm<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)core.smem)
+                                : cudaFuncSetAttribute(k_igemm<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)core.smem);
+    if (e != cudaSuccess)
+        return fail(ctx, PETB200_ERR_CUDA, "cudaFuncSetAttribute(%zu bytes) failed: %s", core.smem, cudaGetErrorString(e));
+    return PETB200_OK;
+}
+
+// ---- exported to conv.cu -------------------------------------------------------------------------------------
+struct TcConv {
+    TcCore full;                 // the whole output
+    ConvGeom g{};
+    int has_bias = 0, act = 0;
+    std::map<long long, TcCore *> windows; // correction windows, keyed by (oh0,ohn,ow0,own)
+    ~TcConv() {
+        for (auto &kv : windows)
+            delete kv.second;
+    }
+};
+
+int tc_conv_create(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const int *k, const int *pad, const int *stride,
+                   const int *dil, int groups, int has_bias, int act, void **out, size_t *dev_bytes) {
+    if (ctx->cc_major != 10)
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "tcgen05 kernels need compute capability 10.x, device has %d.%d", ctx->cc_major, ctx->cc_minor);
+    auto *t = new TcConv();
+    ConvGeom &g = t->g;
+    g.N = in_dims[0];
+    g.C = in_dims[1];
+    if (nsp == 3) {
+        g.D = in_dims[2];
+        g.H = in_dims[3];
+        g.W = in_dims[4];
+        for (int i = 0; i < 3; ++i) {
+            g.T3[i] = k[i];
+            g.pad[i] = pad[i];
+            g.stride[i] = stride[i];
+            g.dil[i] = dil[i];
+        }
+    } else {
+        g.D = 1;
+        g.H = in_dims[2];
+        g.W = in_dims[3];
+        g.T3[0] = 1;
+        g.pad[0] = 0;
+        g.stride[0] = 1;
+        g.dil[0] = 1;
+        for (int i = 0; i < 2; ++i) {
+            g.T3[i + 1] = k[i];
+            g.pad[i + 1] = pad[i];
+            g.stride[i + 1] = stride[i];
+            g.dil[i + 1] = dil[i];
+        }
+    }
+    g.F = f;
+    g.groups = groups;
+    auto oext = [](int in, int kk, int p, int s, int d) { return (in - (kk - s) * d + 2 * p) / s; };
+    g.OD = nsp == 3 ? oext(g.D, g.T3[0], g.pad[0], g.stride[0], g.dil[0]) : 1;
+    g.OH = oext(g.H, g.T3[1], g.pad[1], g.stride[1], g.dil[1]);
+    g.OW = oext(g.W, g.T3[2], g.pad[2], g.stride[2], g.dil[2]);
+    g.Wst = (g.W + 3) / 4 * 4; // the caller re-pitches the input when this differs from W
+    t->has_bias = has_bias;
+    t->act = act;
+    t->full.ctx = ctx;
+    const long long plane = (long long)g.OD * g.OH * g.OW;
+    int rc = tc_configure(ctx, t->full, g, 0, g.OH, 0, g.OW, 0, g.N, (long long)g.F * plane, plane, 1, has_bias, act);
+    if (rc) {
+        delete t;
+        return rc;
+    }
+    TcCore &c = t->full;
+    c.rows_b = g.F;
+    size_t wbytes = (size_t)g.F * c.Ktot * 4;
+    if (c.whi.alloc(wbytes) != cudaSuccess || c.wlo.alloc(wbytes) != cudaSuccess) {
+        delete t;
+        return fail(ctx, PETB200_ERR_NOMEM, "packed weight allocation (%zu bytes) failed", 2 * wbytes);
+    }
+    rc = c.encode_b();
+    if (rc) {
+        delete t;
+        return rc;
+    }
+    *dev_bytes = 2 * wbytes + c.koff.bytes;
+    *out = t;
+    return PETB200_OK;
+}
+
+void tc_conv_destroy(void *h) { delete (TcConv *)h; }
+
+int tc_conv_set_weights(void *h, const float *w, cudaStream_t s) {
+    auto *t = (TcConv *)h;
+    TcCore &c = t->full;
+    const int cpg = t->g.C / t->g.groups, T = t->g.T3[0] * t->g.T3[1] * t->g.T3[2];
+    long long total = (long long)t->g.F * c.Ktot;
+    int blocks = (int)std::min<long long>((total + 255) / 256, (long long)c.ctx->sm_count * 16);
+    k_pack_conv_w<<<blocks, 256, 0, s>>>(w, (float *)c.whi.p, (float *)c.wlo.p, t->g.F, cpg, T, c.P.BC, c.P.spc * kStageK,
+                                         c.P.nchunks);
+    c.weights_ready = true;
+    return launched(c.ctx, "k_pack_conv_w");
+}
+
+int tc_conv_run(void *h, const float *x, const float *bias, float *y, const int *win, cudaStream_t s) {
+    auto *t = (TcConv *)h;
+    if (!t->full.weights_ready)
+        return fail(t->full.ctx, PETB200_ERR_INVALID, "conv run before set_weights");
+    if (!win)
+        return t->full.launch(x, bias, y, s);
+    const ConvGeom &g = t->g;
+    if (win[0] < 0 || win[1] <= 0 || win[0] + win[1] > g.OH || win[2] < 0 || win[3] <= 0 || win[2] + win[3] > g.OW)
+        return fail(t->full.ctx, PETB200_ERR_INVALID, "correction window outside the output");
+    long long key = (((long long)win[0] * 4096 + win[1]) * 4096 + win[2]) * 4096 + win[3];
+    TcCore *&wc = t->windows[key];
+    if (!wc) {
+        wc = new TcCore();
+        wc->ctx = t->full.ctx;
+        const long long plane = (long long)g.OD * g.OH * g.OW;
+        // A window must consume K in exactly the order of the full operator (same BC / chunking), otherwise the
+        // two would round differently; the raw box only shrinks for a window, so the full plan's BC always fits.
+        int rc = tc_configure(wc->ctx, *wc, g, win[0], win[1], win[2], win[3], 0, g.N, (long long)g.F * plane, plane, 1,
+                              t->has_bias, t->act, t->full.P.BC);
+        if (rc == PETB200_OK && (wc->P.BN != t->full.P.BN || wc->P.BC != t->full.P.BC || wc->Ktot != t->full.Ktot))
+            rc = fail(wc->ctx, PETB200_ERR_UNSUPPORTED, "window plan diverged from the full plan");
+        if (rc) {
+            delete wc;
+            t->windows.erase(key);
+            return rc;
+        }
+        wc->map_bhi = t->full.map_bhi;
+        wc->map_blo = t->full.map_blo;
+        wc->weights_ready = true;
+    }
+    return wc->launch(x, bias, y, s);
+}
+
+void tc_conv_out_dims(void *h, int *d5) {
+    auto *t = (TcConv *)h;
+    d5[0] = t->g.N;
+    d5[1] = t->g.F;
+    d5[2] = t->g.OD;
+    d5[3] = t->g.OH;
+    d5[4] = t->g.OW;
+}
+int tc_conv_row_pitch(void *h) { return ((TcConv *)h)->g.Wst; }
+const char *tc_conv_variant(void *h) { return ((TcConv *)h)->full.a_tmem ? "tc_3xtf32_ts" : "tc_3xtf32_ss"; }
+
+// ---- matmul on the same kernel ------------------------------------------------------------------------------
+// C[b,m,n] = A·B with A supplied as [b,k,m] (i.e. transA): a 1x1 "convolution" whose image is one batch entry,
+// channels = k, width = m; B is packed per call (or once, for weights) into hi/lo [b*n][Kpad].
+struct TcMatmul {
+    TcCore core;
+    int bs, m, n, k, transB;
+};
+
+int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transB, int has_bias, int act, void **out,
+                     size_t *dev_bytes) {
+    if (ctx->cc_major != 10)
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "tcgen05 kernels need compute capability 10.x");
+    auto *t = new TcMatmul();
+    t->bs = bs;
+    t->m = m;
+    t->n = n;
+    t->k = k;
+    t->transB = transB;
+    ConvGeom g{};
+    g.N = bs;
+    g.C = k;
+    g.D = 1;
+    g.H = 1;
+    g.W = m;
+    g.Wst = m;
+    g.F = n;
+    g.groups = 1;
+    for (int i = 0; i < 3; ++i) {
+        g.T3[i] = 1;
+        g.pad[i] = 0;
+        g.stride[i] = 1;
+        g.dil[i] = 1;
+    }
+    g.OD = 1;
+    g.OH = 1;
+    g.OW = m;
+    t->core.ctx = ctx;
+    int rc = tc_configure(ctx, t->core, g, 0, 1, 0, m, 1, bs, (long long)m * n, 1, n, has_bias, act);
+    if (rc) {
+        delete t;
+        return rc;
+    }
+    TcCore &c = t->core;
+    if (c.P.BC != std::min(k, 32)) {
+        delete t;
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "matmul K chunking diverged from the packing order");
+    }
+    c.rows_b = bs * n;
+    // rows of different batch entries are adjacent: Fg = n rows per z
+    size_t wbytes = (size_t)bs * n * c.Ktot * 4;
+    if (c.whi.alloc(wbytes) != cudaSuccess || c.wlo.alloc(wbytes) != cudaSuccess) {
+        delete t;
+        return fail(ctx, PETB200_ERR_NOMEM, "packed B allocation failed");
+    }
+    rc = c.encode_b();
+    if (rc) {
+        delete t;
+        return rc;
+    }
+    *dev_bytes = 2 * wbytes + c.koff.bytes;
+    *out = t;
+    return PETB200_OK;
+}
+void tc_matmul_destroy(void *h) { delete (TcMatmul *)h; }
+int tc_matmul_pack_b(void *h, const float *b, cudaStream_t s) {
+    auto *t = (TcMatmul *)h;
+    TcCore &c = t->core;
+    long long total = (long long)t->bs * t->n * c.Ktot;
+    int blocks = (int)std::min<long long>((total + 255) / 256, (long long)c.ctx->sm_count * 16);
+    k_pack_mm_b<<<blocks, 256, 0, s>>>(b, (float *)c.whi.p, (float *)c.wlo.p, t->bs, t->n, t->k, (int)c.Ktot, t->transB);
+    c.weights_ready = true;
+    return launched(c.ctx, "k_pack_mm_b");
+}
+int tc_matmul_run(void *h, const float *a_t, const float *bias, float *cmat, cudaStream_t s) {
+    auto *t = (TcMatmul *)h;
+    return t->core.launch(a_t, bias, cmat, s);
+}
+
+} // namespace petb200
