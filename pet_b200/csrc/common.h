@@ -76,7 +76,7 @@ struct DevBuf {
 
 __host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
-// ---- shared activation definition (host mirror lives in the tests' oracle) ----
+// ---- shared activation definition ----
 __device__ __forceinline__ float apply_act(float v, int act) {
     switch (act) {
     case PETB200_ACT_RELU:

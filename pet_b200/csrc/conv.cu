@@ -13,6 +13,7 @@ void tc_conv_destroy(void *h);
 int tc_conv_set_weights(void *h, const float *w, cudaStream_t s);
 int tc_conv_run(void *h, const float *x, const float *bias, float *y, const int *win, cudaStream_t s);
 int tc_conv_row_pitch(void *h);
+void tc_conv_set_prof(void *h, long long *p);
 const char *tc_conv_variant(void *h);
 int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transB, int has_bias, int act, void **out,
                      size_t *dev_bytes);
@@ -403,3 +404,12 @@ int MatmulPlan::bench_launch(cudaStream_t s) {
 }
 
 } // namespace petb200
+
+// Tuning aid (not part of the public header): per-CTA cycle counters of the tensor-core conv kernel, 8 per CTA.
+extern "C" int petb200_debug_conv_prof(petb200_plan *plan, long long *dev_counters) {
+    auto *pl = dynamic_cast<petb200::ConvPlan *>(plan);
+    if (!pl || !pl->tc)
+        return PETB200_ERR_INVALID;
+    petb200::tc_conv_set_prof(pl->tc, dev_counters);
+    return PETB200_OK;
+}

@@ -32,6 +32,7 @@ constexpr int kTileM = 128;
 constexpr int kStageK = 32;               // fp32/TF32 values per K stage = one 128-byte swizzle row
 constexpr int kAHalfBytes = kTileM * 128; // one 128 x 32 operand tile
 constexpr int kThreads = 224;
+constexpr int kMaxNB = 6;
 
 struct IgemmParams {
     int M_total, Pw;        // pixels in the whole problem (per image-batch z when z_is_batch); pixels per image
@@ -44,6 +45,7 @@ struct IgemmParams {
     int cpg, Fg, BN;        // channels per group, filters per group, tile N
     int z_is_batch;         // blockIdx.z: 0 = conv group, 1 = matmul batch
     int wide, row_tiles;    // wide mode: a tile is 128 consecutive pixels of ONE output row (rows wider than a tile)
+    int tpi, ipt, images;   // otherwise: tiles per image (image larger than a tile) or whole images per tile
     int NA, NB;             // ring depths
     int raw_bytes;          // bytes of one raw buffer (128-aligned)
     long long ys_n, ys_f, ys_p;
@@ -52,6 +54,7 @@ struct IgemmParams {
     const float *bias;
     float *y;
     int *status;
+    long long *prof; // optional per-CTA cycle counters (8 per CTA), for tuning only
 };
 
 struct SmemLayout {
@@ -73,30 +76,74 @@ __host__ __device__ inline SmemLayout smem_layout(const IgemmParams &P, bool a_t
     return L;
 }
 
-// Which images / depth slices / rows a tile of pixels [m_lo, m_hi] touches; shared by the raw producer, the
-// transform threads and the host-side sizing of the raw box.
-__host__ __device__ inline void tile_span(const IgemmParams &P, int m_lo, int m_hi, int &n_lo, int &n_hi, int &zl_lo,
-                                          int &zl_hi, int &yl_lo, int &yl_hi) {
-    int plane = P.ohn * P.own;
-    n_lo = m_lo / P.Pw;
-    n_hi = m_hi / P.Pw;
-    int q_lo = m_lo - n_lo * P.Pw, q_hi = m_hi - n_hi * P.Pw;
-    if (n_lo != n_hi) {
-        zl_lo = 0;
-        zl_hi = P.OD - 1;
-        yl_lo = 0;
-        yl_hi = P.ohn - 1;
+// Which depth slices / rows of an image the pixels [q_lo, q_hi] of that image touch (everything when the tile
+// holds several whole images); shared by the raw producer, the transform threads and the host-side box sizing.
+__host__ __device__ inline void tile_span(const IgemmParams &P, int q_lo, int q_hi, bool whole, int &zl_lo, int &zl_hi,
+                                          int &yl_lo, int &yl_hi) {
+    const int plane = P.ohn * P.own;
+    zl_lo = 0;
+    zl_hi = P.OD - 1;
+    yl_lo = 0;
+    yl_hi = P.ohn - 1;
+    if (whole)
         return;
-    }
     zl_lo = q_lo / plane;
     zl_hi = q_hi / plane;
-    if (zl_lo != zl_hi) {
-        yl_lo = 0;
-        yl_hi = P.ohn - 1;
+    if (zl_lo != zl_hi)
         return;
-    }
     yl_lo = (q_lo - zl_lo * plane) / P.own;
     yl_hi = (q_hi - zl_hi * plane) / P.own;
+}
+
+template <int ACT> __device__ __forceinline__ float act_fn(float v) {
+    if (ACT == PETB200_ACT_RELU)
+        return fmaxf(v, 0.f);
+    if (ACT == PETB200_ACT_SIGMOID)
+        return 1.f / (1.f + expf(-v));
+    if (ACT == PETB200_ACT_TANH)
+        return tanhf(v);
+    if (ACT == PETB200_ACT_GELU)
+        return 0.5f * v * (1.f + erff(v * 0.70710678118654752440f));
+    return v;
+}
+
+// TMEM accumulator rows -> (+bias, activation) -> global.  `yp` already points at this thread's pixel and the first
+// filter of the group; column j of the tile is filter f_tile0 + j.  The activation is a template parameter so that
+// the common no-activation case carries none of the transcendental code.
+template <int ACT>
+__device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile0, int Fg, bool valid, const float *bias,
+                                               float *yp, long long ys_f, bool vec_ok) {
+    uint32_t r[32], nx[32];
+    ptx::tmem_ld_32x32(tacc, nx);
+    for (int cc = 0; cc < BN; cc += 32) {
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            r[j] = nx[j];
+        if (cc + 32 < BN)
+            ptx::tmem_ld_32x32(tacc + (uint32_t)(cc + 32), nx); // in flight while this chunk is stored
+        if (!valid)
+            continue;
+        const int f0 = f_tile0 + cc;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            float v = __uint_as_float(r[j]);
+            if (bias != nullptr && f0 + j < Fg)
+                v += __ldg(bias + f0 + j);
+            r[j] = __float_as_uint(act_fn<ACT>(v));
+        }
+        if (vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                if (f0 + j < Fg)
+                    *reinterpret_cast<uint4 *>(yp + f0 + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (f0 + j < Fg)
+                    yp[(long long)(f0 + j) * ys_f] = __uint_as_float(r[j]);
+        }
+    }
 }
 
 template <bool A_TMEM>
@@ -114,14 +161,13 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L.bar_off);
     // barrier slots
     uint64_t *raw_full = bars, *raw_empty = bars + 2;
-    uint64_t *b_full = bars + 4, *b_empty = bars + 8;   // up to 4 stages
-    uint64_t *a_full = bars + 12, *a_empty = bars + 16; // up to 4 stages
-    uint64_t *acc_full = bars + 20;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 21);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(bars + 22);
+    uint64_t *b_full = bars + 4, *b_empty = bars + 4 + kMaxNB; // up to kMaxNB stages
+    uint64_t *a_full = bars + 4 + 2 * kMaxNB, *a_empty = a_full + 4; // up to 4 stages
+    uint64_t *acc_full = a_empty + 4;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(acc_full + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * kTileM;
     const int ntile = blockIdx.y;
     const int zb = blockIdx.z;
     const int KS = P.nchunks * P.spc;
@@ -133,9 +179,11 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             ptx::mbar_init(raw_full + i, 1);
             ptx::mbar_init(raw_empty + i, 4);
         }
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < kMaxNB; ++i) {
             ptx::mbar_init(b_full + i, 1);
             ptx::mbar_init(b_empty + i, 1);
+        }
+        for (int i = 0; i < 4; ++i) {
             ptx::mbar_init(a_full + i, 4);
             ptx::mbar_init(a_empty + i, 1);
         }
@@ -158,7 +206,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     const uint32_t tmem_base = *tmem_slot;
 
     // Tile origin in the input: first image, depth slice, row and (16-byte aligned) column of the raw box.
-    int n_lo = 0, z_start, y_start, x_start, w_zl = 0, w_yl = 0, w_tx = 0;
+    int n_lo = 0, q0 = 0, z_start, y_start, x_start, w_zl = 0, w_yl = 0, w_tx = 0;
     if (P.wide) {
         const int row = blockIdx.x / P.row_tiles;
         w_tx = blockIdx.x - row * P.row_tiles;
@@ -170,93 +218,141 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         const int xs = (P.ow0 + w_tx * kTileM) * P.sw - P.pw;
         x_start = (xs >= 0) ? (xs & ~3) : -(((-xs) + 3) & ~3);
     } else {
-        const int m_hi = min(m0 + kTileM, P.M_total) - 1;
-        int n_hi, zl_lo, zl_hi, yl_lo, yl_hi;
-        tile_span(P, m0, m_hi, n_lo, n_hi, zl_lo, zl_hi, yl_lo, yl_hi);
+        const int tn = blockIdx.x / P.tpi;
+        q0 = (blockIdx.x - tn * P.tpi) * kTileM;
+        n_lo = tn * P.ipt;
+        int zl_lo, zl_hi, yl_lo, yl_hi;
+        tile_span(P, q0, min(q0 + kTileM, P.Pw) - 1, P.ipt > 1, zl_lo, zl_hi, yl_lo, yl_hi);
         z_start = zl_lo * P.sd - P.pd;
         y_start = (P.oh0 + yl_lo) * P.sh - P.ph;
         x_start = P.x0;
     }
 
     if (warp == 0) {
-        // ---------------- packed-weight producer ----------------
-        const int row0 = zb * P.Fg + ntile * P.BN;
-        for (int ks = 0; ks < KS; ++ks) {
-            const int sb = ks % P.NB;
-            const uint32_t ph = (uint32_t)((ks / P.NB) & 1);
-            if (lane == 0) {
-                if (ptx::mbar_wait(b_empty + sb, ph ^ 1u, abort_flag)) {
-                    ptx::mbar_expect_tx(b_full + sb, 2u * b_half);
-                    ptx::tma_load_2d(sB + (size_t)sb * 2 * b_half, &tmap_bhi, b_full + sb, ks * kStageK, row0);
-                    ptx::tma_load_2d(sB + (size_t)sb * 2 * b_half + b_half, &tmap_blo, b_full + sb, ks * kStageK, row0);
+        // ---------------- packed-weight producer (one thread) ----------------
+        if (lane == 0) {
+            const int row0 = zb * P.Fg + ntile * P.BN;
+            int sb = 0;
+            uint32_t pb = 1; // first pass over the ring: every slot is free
+            for (int ks = 0; ks < KS; ++ks) {
+                if (!ptx::mbar_wait(b_empty + sb, pb, abort_flag))
+                    break;
+                uint8_t *dst = sB + (size_t)sb * 2 * b_half;
+                ptx::mbar_expect_tx(b_full + sb, 2u * b_half);
+                ptx::tma_load_2d(dst, &tmap_bhi, b_full + sb, ks * kStageK, row0);
+                ptx::tma_load_2d(dst + b_half, &tmap_blo, b_full + sb, ks * kStageK, row0);
+                if (++sb == P.NB) {
+                    sb = 0;
+                    pb ^= 1u;
                 }
             }
-            __syncwarp();
-            if (*abort_flag)
-                break;
         }
     } else if (warp == 2) {
-        // ---------------- raw activation producer ----------------
-        const int c_base = P.z_is_batch ? 0 : zb * P.cpg;
-        const int n_start = P.z_is_batch ? zb : n_lo;
-        for (int ch = 0; ch < P.nchunks; ++ch) {
-            const int rb = ch & 1;
-            const uint32_t ph = (uint32_t)((ch >> 1) & 1);
-            if (lane == 0) {
-                if (ptx::mbar_wait(raw_empty + rb, ph ^ 1u, abort_flag)) {
-                    ptx::mbar_expect_tx(raw_full + rb, (uint32_t)P.RN * P.BC * P.RD * P.RH * P.RW * 4u);
-                    ptx::tma_load_5d(sRaw + (size_t)rb * P.raw_bytes, &tmap_x, raw_full + rb, x_start, y_start, z_start,
-                                     c_base + ch * P.BC, n_start);
-                }
+        // ---------------- raw activation producer (one thread) ----------------
+        if (lane == 0) {
+            const int c_base = P.z_is_batch ? 0 : zb * P.cpg;
+            const int n_start = P.z_is_batch ? zb : n_lo;
+            const uint32_t bytes = (uint32_t)P.RN * P.BC * P.RD * P.RH * P.RW * 4u;
+            for (int ch = 0; ch < P.nchunks; ++ch) {
+                const int rb = ch & 1;
+                if (!ptx::mbar_wait(raw_empty + rb, (uint32_t)(((ch >> 1) & 1) ^ 1), abort_flag))
+                    break;
+                ptx::mbar_expect_tx(raw_full + rb, bytes);
+                ptx::tma_load_5d(sRaw + (size_t)rb * P.raw_bytes, &tmap_x, raw_full + rb, x_start, y_start, z_start,
+                                 c_base + ch * P.BC, n_start);
             }
-            __syncwarp();
-            if (*abort_flag)
-                break;
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        const uint32_t idesc = ptx::idesc_tf32(kTileM, P.BN);
-        uint32_t accumulate = 0;
-        for (int ks = 0; ks < KS; ++ks) {
-            const int sa = ks % P.NA, sb = ks % P.NB;
-            if (lane == 0) {
-                bool ok = ptx::mbar_wait(a_full + sa, (uint32_t)((ks / P.NA) & 1), abort_flag) &&
-                          ptx::mbar_wait(b_full + sb, (uint32_t)((ks / P.NB) & 1), abort_flag);
-                if (ok) {
-                    ptx::tc_fence_after();
-                    const uint64_t bhi = ptx::smem_desc_k128(ptx::smem_u32(sB + (size_t)sb * 2 * b_half));
-                    const uint64_t blo = ptx::smem_desc_k128(ptx::smem_u32(sB + (size_t)sb * 2 * b_half + b_half));
-                    if (A_TMEM) {
-                        const uint32_t ahi = tmem_base + 256u + (uint32_t)sa * 64u, alo = ahi + 32u;
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {
-                            ptx::mma_tf32_ts(tmem_base, alo + kk * 8, bhi + 2 * kk, idesc, accumulate);
-                            ptx::mma_tf32_ts(tmem_base, ahi + kk * 8, blo + 2 * kk, idesc, 1u);
-                            ptx::mma_tf32_ts(tmem_base, ahi + kk * 8, bhi + 2 * kk, idesc, 1u);
-                            accumulate = 1u;
-                        }
+        // ---------------- MMA issuer (one thread) ----------------
+        if (lane == 0) {
+            const uint32_t idesc = ptx::idesc_tf32(kTileM, P.BN);
+            const uint64_t bdesc0 = ptx::smem_desc_k128(ptx::smem_u32(sB));
+            const uint64_t adesc0 = A_TMEM ? 0ull : ptx::smem_desc_k128(ptx::smem_u32(sA));
+            const uint32_t b_half16 = b_half >> 4;
+            uint32_t accumulate = 0;
+            int sa = 0, sb = 0;
+            uint32_t pa = 0, pb = 0;
+            long long t_wa = 0, t_wb = 0;
+            const long long t_begin = P.prof ? clock64() : 0;
+            bool ok = true;
+            // Software pipelining of the bookkeeping: the stage-release commits of stage s are issued right after the
+            // first MMA of stage s+1, and the barriers of stage s+1 are polled while the last MMAs of stage s are
+            // still queued, so that the tensor pipe never waits on this thread's housekeeping.
+            int prev_sa = -1, prev_sb = -1;
+            bool ready_next = false;
+            for (int ks = 0; ks < KS; ++ks) {
+                if (!ready_next) {
+                    if (P.prof) {
+                        const long long c0 = clock64();
+                        ok = ptx::mbar_wait(a_full + sa, pa, abort_flag);
+                        const long long c1 = clock64();
+                        ok = ok && ptx::mbar_wait(b_full + sb, pb, abort_flag);
+                        t_wa += c1 - c0;
+                        t_wb += clock64() - c1;
                     } else {
-                        const uint64_t ahi = ptx::smem_desc_k128(ptx::smem_u32(sA + (size_t)sa * 2 * kAHalfBytes));
-                        const uint64_t alo = ptx::smem_desc_k128(ptx::smem_u32(sA + (size_t)sa * 2 * kAHalfBytes + kAHalfBytes));
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {
-                            ptx::mma_tf32_ss(tmem_base, alo + 2 * kk, bhi + 2 * kk, idesc, accumulate);
-                            ptx::mma_tf32_ss(tmem_base, ahi + 2 * kk, blo + 2 * kk, idesc, 1u);
-                            ptx::mma_tf32_ss(tmem_base, ahi + 2 * kk, bhi + 2 * kk, idesc, 1u);
-                            accumulate = 1u;
-                        }
+                        ok = ptx::mbar_wait(a_full + sa, pa, abort_flag) && ptx::mbar_wait(b_full + sb, pb, abort_flag);
                     }
-                    ptx::mma_commit(a_empty + sa);
-                    ptx::mma_commit(b_empty + sb);
+                    if (!ok)
+                        break;
                 }
+                ptx::tc_fence_after();
+                const uint64_t bhi = bdesc0 + (uint64_t)((uint32_t)sb * 2u * b_half16);
+                const uint64_t blo = bhi + b_half16;
+                const uint32_t ahi_t = tmem_base + 256u + (uint32_t)sa * 64u, alo_t = ahi_t + 32u;
+                const uint64_t ahi_s = adesc0 + (uint64_t)((uint32_t)sa * 2u * (kAHalfBytes >> 4));
+                const uint64_t alo_s = ahi_s + (kAHalfBytes >> 4);
+                // next stage's ring positions
+                int nsa = sa + 1, nsb = sb + 1;
+                uint32_t npa = pa, npb = pb;
+                if (nsa == P.NA) {
+                    nsa = 0;
+                    npa ^= 1u;
+                }
+                if (nsb == P.NB) {
+                    nsb = 0;
+                    npb ^= 1u;
+                }
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    if (A_TMEM) {
+                        ptx::mma_tf32_ts(tmem_base, alo_t + kk * 8, bhi + 2 * kk, idesc, accumulate);
+                    } else {
+                        ptx::mma_tf32_ss(tmem_base, alo_s + 2 * kk, bhi + 2 * kk, idesc, accumulate);
+                    }
+                    accumulate = 1u;
+                    if (kk == 0 && prev_sa >= 0) {
+                        ptx::mma_commit(a_empty + prev_sa);
+                        ptx::mma_commit(b_empty + prev_sb);
+                    }
+                    if (A_TMEM) {
+                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, blo + 2 * kk, idesc, 1u);
+                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, 1u);
+                    } else {
+                        ptx::mma_tf32_ss(tmem_base, ahi_s + 2 * kk, blo + 2 * kk, idesc, 1u);
+                        ptx::mma_tf32_ss(tmem_base, ahi_s + 2 * kk, bhi + 2 * kk, idesc, 1u);
+                    }
+                }
+                ready_next = (ks + 1 < KS) && ptx::mbar_try_wait(a_full + nsa, npa) && ptx::mbar_try_wait(b_full + nsb, npb);
+                prev_sa = sa;
+                prev_sb = sb;
+                sa = nsa;
+                sb = nsb;
+                pa = npa;
+                pb = npb;
             }
-            __syncwarp();
-            if (*abort_flag)
-                break;
+            if (ok && prev_sa >= 0) {
+                ptx::mma_commit(a_empty + prev_sa);
+                ptx::mma_commit(b_empty + prev_sb);
+            }
+            if (ok)
+                ptx::mma_commit(acc_full);
+            if (P.prof) {
+                long long *pr = P.prof + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8;
+                pr[0] = t_wa;
+                pr[1] = t_wb;
+                pr[2] = clock64() - t_begin;
+            }
         }
-        if (lane == 0 && !*abort_flag)
-            ptx::mma_commit(acc_full);
-        __syncwarp();
     } else {
         // ---------------- transform + epilogue (warps 3..6) ----------------
         const int quarter = warp & 3;         // TMEM lane quarter this warp may access
@@ -274,12 +370,15 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 y_off = img * P.ys_n + ((long long)(w_zl * P.OH + oh) * P.OW + ow) * P.ys_p;
             }
         } else {
-            const int m = m0 + p;
-            valid = m < P.M_total;
+            int nl = 0, q = q0 + p;
+            if (P.ipt > 1) {
+                nl = p / P.Pw;
+                q = p - nl * P.Pw;
+            }
+            const int n = n_lo + nl;
+            valid = (nl < P.ipt) && (n < P.images) && (q < P.Pw);
             if (valid) {
                 const int plane = P.ohn * P.own;
-                const int n = m / P.Pw;
-                int q = m - n * P.Pw;
                 const int zl = q / plane;
                 q -= zl * plane;
                 const int yl = q / P.own;
@@ -292,14 +391,22 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             }
         }
         bool alive = true;
+        long long t_we = 0, t_wr = 0;
+        const long long t_begin = P.prof ? clock64() : 0;
+        int sa = 0;
+        uint32_t pa = 1; // first pass over the ring: every slot is free
         for (int ch = 0; ch < P.nchunks && alive; ++ch) {
             const int rb = ch & 1;
+            const long long cr0 = P.prof ? clock64() : 0;
             alive = ptx::mbar_wait(raw_full + rb, (uint32_t)((ch >> 1) & 1), abort_flag);
+            if (P.prof)
+                t_wr += clock64() - cr0;
             const float *raw = reinterpret_cast<const float *>(sRaw + (size_t)rb * P.raw_bytes) + base_p;
             for (int st = 0; st < P.spc && alive; ++st) {
-                const int ks = ch * P.spc + st;
-                const int sa = ks % P.NA;
-                alive = ptx::mbar_wait(a_empty + sa, (uint32_t)(((ks / P.NA) & 1) ^ 1), abort_flag);
+                const long long ce0 = P.prof ? clock64() : 0;
+                alive = ptx::mbar_wait(a_empty + sa, pa, abort_flag);
+                if (P.prof)
+                    t_we += clock64() - ce0;
                 if (!alive)
                     break;
                 const int4 *ko = reinterpret_cast<const int4 *>(sKoff + st * kStageK);
@@ -351,54 +458,54 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 __syncwarp();
                 if (lane == 0)
                     ptx::mbar_arrive(a_full + sa);
+                if (++sa == P.NA) {
+                    sa = 0;
+                    pa ^= 1u;
+                }
             }
             __syncwarp();
             if (lane == 0 && alive)
                 ptx::mbar_arrive(raw_empty + rb);
         }
         // ---------------- epilogue ----------------
+        const long long t_loop = P.prof ? clock64() - t_begin : 0;
         if (alive)
             alive = ptx::mbar_wait(acc_full, 0u, abort_flag);
+        const long long t_epi0 = P.prof ? clock64() : 0;
         if (alive) {
             ptx::tc_fence_after();
             const int f_tile0 = ntile * P.BN;
             const long long f_glob0 = P.z_is_batch ? 0 : (long long)zb * P.Fg;
-            float *yp = P.y + y_off;
+            float *yp = P.y + y_off + f_glob0 * P.ys_f;
+            const float *bp = P.has_bias ? P.bias + f_glob0 : nullptr;
             const bool vec_ok = (P.ys_f == 1) && ((P.ys_p & 3) == 0) && ((P.ys_n & 3) == 0) && ((P.Fg & 3) == 0) &&
                                 ((reinterpret_cast<uintptr_t>(P.y) & 15) == 0);
-            for (int cc = 0; cc < P.BN; cc += 32) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)cc, r);
-                ptx::tmem_ld_wait();
-                if (!valid)
-                    continue;
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int fl = f_tile0 + cc + j;
-                    float v = __uint_as_float(r[j]);
-                    if (fl < P.Fg) {
-                        if (P.has_bias)
-                            v += __ldg(P.bias + f_glob0 + fl);
-                        v = apply_act(v, P.act);
-                    }
-                    r[j] = __float_as_uint(v);
-                }
-                if (vec_ok) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        const int fl = f_tile0 + cc + j;
-                        if (fl < P.Fg)
-                            *reinterpret_cast<uint4 *>(yp + f_glob0 + fl) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int fl = f_tile0 + cc + j;
-                        if (fl < P.Fg)
-                            yp[(f_glob0 + fl) * P.ys_f] = __uint_as_float(r[j]);
-                    }
-                }
+            const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            switch (P.act) {
+            case PETB200_ACT_RELU:
+                epilogue_store<PETB200_ACT_RELU>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok);
+                break;
+            case PETB200_ACT_SIGMOID:
+                epilogue_store<PETB200_ACT_SIGMOID>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok);
+                break;
+            case PETB200_ACT_TANH:
+                epilogue_store<PETB200_ACT_TANH>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok);
+                break;
+            case PETB200_ACT_GELU:
+                epilogue_store<PETB200_ACT_GELU>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok);
+                break;
+            default:
+                epilogue_store<PETB200_ACT_NONE>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok);
+                break;
             }
+        }
+        if (P.prof && threadIdx.x == 96) {
+            long long *pr = P.prof + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8;
+            pr[3] = t_we;
+            pr[4] = t_wr;
+            pr[5] = t_loop;
+            pr[6] = clock64() - t_epi0;
+            pr[7] = t_epi0 - t_begin;
         }
     }
 
@@ -492,6 +599,7 @@ struct TcCore {
     CUtensorMap map_x{}, map_bhi{}, map_blo{};
     const void *map_x_ptr = nullptr;
     bool weights_ready = false;
+    long long *prof = nullptr;
 
     int encode_x(const float *x) {
         if (x == map_x_ptr)
@@ -538,6 +646,7 @@ struct TcCore {
         p.y = y;
         p.koff = (const int *)koff.p;
         p.status = ctx->d_status;
+        p.prof = prof;
         p.has_bias = (P.has_bias && bias) ? 1 : 0;
         if (a_tmem)
             k_igemm<true><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
@@ -596,6 +705,9 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     if (BN != 32 && BN != 64 && BN != 128 && BN != 256)
         return fail(ctx, PETB200_ERR_INVALID, "PETB200_TC_BN must be 32, 64, 128 or 256");
     P.BN = BN;
+    P.images = z_is_batch ? 1 : images;
+    P.ipt = (!z_is_batch && 2 * P.Pw <= kTileM) ? kTileM / P.Pw : 1;
+    P.tpi = (P.Pw + kTileM - 1) / kTileM;
     P.wide = (own > kTileM) ? 1 : 0;
     P.row_tiles = (own + kTileM - 1) / kTileM;
     const int xs = ow0 * P.sw - P.pw;
@@ -610,13 +722,11 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     } else {
         const int wneed = (own - 1) * P.sw + (g.T3[2] - 1) * g.dil[2] + 1 + (xs - P.x0);
         P.RW = (wneed + 3) / 4 * 4;
-        // raw box along images / depth / rows: maxima over all tiles (in OUTPUT units first)
-        int RN = 1, RDo = 1, RHo = 1;
-        for (int m0 = 0; m0 < P.M_total; m0 += kTileM) {
-            int m_hi = std::min(m0 + kTileM, P.M_total) - 1;
-            int n_lo, n_hi, zl_lo, zl_hi, yl_lo, yl_hi;
-            tile_span(P, m0, m_hi, n_lo, n_hi, zl_lo, zl_hi, yl_lo, yl_hi);
-            RN = std::max(RN, n_hi - n_lo + 1);
+        // raw box along images / depth / rows: maxima over the tiles of one image (in OUTPUT units first)
+        int RN = P.ipt, RDo = 1, RHo = 1;
+        for (int tq = 0; tq < P.tpi; ++tq) {
+            int zl_lo, zl_hi, yl_lo, yl_hi;
+            tile_span(P, tq * kTileM, std::min((tq + 1) * kTileM, P.Pw) - 1, P.ipt > 1, zl_lo, zl_hi, yl_lo, yl_hi);
             RDo = std::max(RDo, zl_hi - zl_lo + 1);
             RHo = std::max(RHo, yl_hi - yl_lo + 1);
         }
@@ -628,7 +738,7 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "raw activation box %dx%dx%dx%d exceeds the TMA box limit", P.RN, P.RD, P.RH, P.RW);
     const int T = g.T3[0] * g.T3[1] * g.T3[2];
     const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 1024; // alignment slack
-    core.a_tmem = env_int("PETB200_TC_A_TMEM", 0) != 0;
+    core.a_tmem = env_int("PETB200_TC_A_TMEM", 1) != 0;
     if (core.a_tmem && BN > 256)
         return fail(ctx, PETB200_ERR_INVALID, "TS variant supports BN <= 256");
     int BC = std::min(cpg, 32);
@@ -648,7 +758,7 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
             // deepen the rings while there is room: B first (it hides TMA latency), then A
             for (bool grew = true; grew;) {
                 grew = false;
-                if (P.NB < 4) {
+                if (P.NB < kMaxNB) {
                     P.NB++;
                     if (smem_layout(P, core.a_tmem).total <= budget)
                         grew = true;
@@ -669,7 +779,7 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
             return fail(ctx, PETB200_ERR_UNSUPPORTED, "raw activation tile does not fit shared memory");
     }
     core.smem = smem_layout(P, core.a_tmem).total + 1024;
-    const int mtiles = P.wide ? (z_is_batch ? 1 : images) * g.OD * ohn * P.row_tiles : (P.M_total + kTileM - 1) / kTileM;
+    const int mtiles = P.wide ? P.images * g.OD * ohn * P.row_tiles : ((P.images + P.ipt - 1) / P.ipt) * P.tpi;
     core.grid = dim3((unsigned)mtiles, (unsigned)((Fg + BN - 1) / BN),
                      (unsigned)(z_is_batch ? images : g.groups));
     core.Ktot = (long long)P.nchunks * P.spc * kStageK;
@@ -829,6 +939,7 @@ void tc_conv_out_dims(void *h, int *d5) {
     d5[3] = t->g.OH;
     d5[4] = t->g.OW;
 }
+void tc_conv_set_prof(void *h, long long *p) { ((TcConv *)h)->full.prof = p; }
 int tc_conv_row_pitch(void *h) { return ((TcConv *)h)->g.Wst; }
 const char *tc_conv_variant(void *h) { return ((TcConv *)h)->full.a_tmem ? "tc_3xtf32_ts" : "tc_3xtf32_ss"; }
 

@@ -1,0 +1,63 @@
+"""Recipes of the inputs behind tests/golden/ref_vectors.npz (shared by the generator and the tests)."""
+import numpy as np
+
+TRANSPOSES = {  # name: (input shape, split, after, factor) — constructor arguments of the reference's TransposeOp
+    "N2H": ((4, 6, 8, 10), 0, [0, 1, [-1, 2], 3], 2),
+    "H2N": ((4, 6, 8, 10), 2, [[0, 2], 1, -1, 3], -2),
+    "N2W": ((4, 6, 8, 10), 0, [0, 1, 2, [-1, 3]], 2),
+    "W2N": ((4, 6, 8, 10), 3, [[0, 3], 1, 2, -1], -2),
+    "C2H": ((4, 6, 8, 10), 1, [0, 1, [2, -1], 3], 2),
+    "C2W": ((4, 6, 8, 10), 1, [0, 1, 2, [3, -1]], 2),
+    "D2H": ((4, 6, 8, 10), 2, [0, 1, [-1, 2], 3], 2),
+    "D2H_inv": ((4, 6, 8, 10), 2, [0, 1, [-1, 2], 3], -2),
+    "D2W": ((4, 6, 8, 10), 3, [0, 1, 2, [-1, 3]], 2),
+    "D2W_inv": ((4, 6, 8, 10), 3, [0, 1, 2, [-1, 3]], -2),
+    "swap_hw": ((4, 6, 8, 10), -1, [0, 1, 3, 2], 2),
+    "flatten1": ((4, 6, 8, 10), -1, [0, [1, 2, 3]], 2),
+    "perm2031": ((4, 6, 8, 10), -1, [2, 0, 3, 1], 2),
+    "mm_swap": ((3, 40, 24), -1, [0, 2, 1], 2),
+    "promote": ((12, 20), 0, [-1, 0, 1], 1),
+    "heads": ((16, 4, 8), -1, [1, 0, 2], 2),
+}
+CONVS = [  # (x shape, w shape, kwargs)
+    ((2, 8, 12, 10), (6, 4, 3, 3), dict(pad=(1, 1))),
+    ((2, 8, 12, 10), (6, 4, 3, 3), dict(pad=(2, 2), dil=(2, 2))),
+    ((2, 8, 12, 10), (6, 4, 3, 3), dict(pad=(1, 0), stride=(2, 2))),
+    ((1, 6, 9, 11), (4, 6, 1, 1), dict(pad=(0, 0))),
+    ((1, 3, 15, 15), (5, 3, 7, 7), dict(pad=(3, 3), stride=(2, 2))),
+]
+PAD = ([0, 1, 2, 0], [1, 0, 3, 2])
+SLICE = ([0, 1, 2, 0], [1, 0, 3, 2])
+
+
+def words(shape, seed):
+    """Arbitrary 32-bit patterns (copy-type operators must move them untouched)."""
+    return np.random.default_rng(seed).integers(0, 2**32, shape, dtype=np.uint64).astype(np.uint32)
+
+
+def small_ints(shape, seed):
+    """Values in [0, 10000), the range the reference's own dataRand uses (include/tensor.h:171-186)."""
+    return np.random.default_rng(seed).integers(0, 10000, shape, dtype=np.int64).astype(np.uint32)
+
+
+def digits(shape, seed):
+    return np.random.default_rng(seed).integers(0, 10, shape, dtype=np.int64).astype(np.uint32)
+
+
+def batch_gemm_inputs():
+    m, n, k = 8, 8, 4
+    i0 = np.arange(m * k, dtype=np.uint32).reshape(1, m, k)
+    w0 = (np.arange(k * n, dtype=np.uint32) * 3).reshape(1, k, n)
+    w1 = (np.arange(k * n, dtype=np.uint32) * 7).reshape(1, k, n)
+    return i0, w0, w1
+
+
+def pad_slice_inputs():
+    return np.arange(49, dtype=np.uint32).reshape(1, 1, 7, 7), np.arange(25, dtype=np.uint32).reshape(1, 1, 5, 5)
+
+
+def tpm_text(arr):
+    """The text format the reference's transpose test writes: '%u ' per element, newline after every 32."""
+    flat = np.asarray(arr, dtype=np.uint32).ravel()
+    lines = [" ".join(map(str, flat[i:i + 32])) + " \n" for i in range(0, flat.size, 32)]
+    return "".join(lines).encode()

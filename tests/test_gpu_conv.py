@@ -1,0 +1,170 @@
+"""GPU: convolution kernels through the C ABI against the CPU oracle (double-accumulated restatement of the
+reference's ConvOp::compute) and the reference-produced integer vectors; correction windows bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+import golden_cases as gc
+from conftest import rel_err, scale_err
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3        # max relative error the backend has to meet (metric: conftest.rel_err)
+TOL_SCALE = 2e-4  # 3xTF32 accuracy statement: max |err| / max |ref|
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("algo", ["tc_3xtf32", "simt_fp32"])
+@pytest.mark.parametrize("i", range(len(gc.CONVS)))
+def test_conv_on_reference_integer_vectors(ctx, golden, algo, i):
+    # small integers: every product and partial sum is exact in fp32 as long as it stays below 2^24, so the float
+    # kernels must reproduce the reference's integer outputs exactly
+    xs, ws, kw = gc.CONVS[i]
+    x, w = gc.small_ints(xs, 100 + i) % 16, gc.small_ints(ws, 200 + i) % 16
+    from oracle import pet_oracle as po
+    want = po.conv2d_u32(x, w, **kw)
+    pad, st, dl = kw["pad"], kw.get("stride", (1, 1)), kw.get("dil", (1, 1))
+    y = ctx.conv2d(dev(x.astype(np.float32)), dev(w.astype(np.float32)), pad[0], pad[1], st[0], st[1], dl[0], dl[1], algo=algo)
+    ctx.sync_check()
+    assert np.array_equal(y.cpu().numpy().astype(np.uint32), want)
+
+
+CASES = [
+    # name, x shape, w shape, (ph,pw,sh,sw,dh,dw)
+    ("c1", (1, 64, 56, 56), (64, 64, 3, 3), (1, 1, 1, 1, 1, 1)),
+    ("c1_rewrite", (2, 64, 28, 56), (64, 64, 3, 3), (1, 1, 1, 1, 1, 1)),
+    ("dilated_small", (1, 32, 16, 16), (48, 32, 3, 3), (2, 2, 1, 1, 2, 2)),
+    ("stride2", (2, 16, 28, 28), (32, 16, 3, 3), (1, 1, 2, 2, 1, 1)),
+    ("1x1_stride2", (1, 64, 56, 56), (128, 64, 1, 1), (0, 0, 2, 2, 1, 1)),
+    ("stem7x7", (1, 3, 224, 224), (64, 3, 7, 7), (3, 3, 2, 2, 1, 1)),
+    ("odd_width_14", (1, 256, 14, 14), (256, 256, 3, 3), (1, 1, 1, 1, 1, 1)),
+    ("odd_width_7", (3, 64, 7, 7), (96, 64, 3, 3), (1, 1, 1, 1, 1, 1)),
+    ("grouped", (1, 32, 12, 12), (64, 8, 3, 3), (1, 1, 1, 1, 1, 1)),
+    ("depthwise", (1, 16, 10, 12), (16, 1, 3, 3), (1, 1, 1, 1, 1, 1)),
+    ("ragged", (2, 5, 9, 11), (7, 5, 3, 2), (1, 0, 1, 2, 1, 1)),
+    ("wide_row", (1, 8, 3, 300), (16, 8, 3, 3), (1, 1, 1, 1, 1, 1)),
+    ("tiny_image_batch", (9, 24, 4, 4), (40, 24, 3, 3), (1, 1, 1, 1, 1, 1)),
+    ("single_pixel", (1, 8, 1, 4), (8, 8, 1, 1), (0, 0, 1, 1, 1, 1)),
+]
+
+
+@pytest.mark.parametrize("algo", ["auto", "simt_fp32"])
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+def test_conv_vs_oracle(ctx, oracle, case, algo):
+    name, xs, ws, (ph, pw, sh, sw, dh, dw) = case
+    rng = np.random.default_rng(abs(hash(name)) % 2**31)
+    x = rng.uniform(-1, 1, xs).astype(np.float32)
+    w = (rng.standard_normal(ws) * np.sqrt(2.0 / (ws[1] * ws[2] * ws[3]))).astype(np.float32)
+    b = rng.uniform(-1, 1, ws[0]).astype(np.float32)
+    want = oracle.conv2d(x, w, b, pad=(ph, pw), stride=(sh, sw), dil=(dh, dw), act="relu", wide=True)
+    y = ctx.conv2d(dev(x), dev(w), ph, pw, sh, sw, dh, dw, bias=dev(b), act="relu", algo=algo)
+    ctx.sync_check()
+    got = y.cpu().numpy()
+    assert got.shape == want.shape
+    assert rel_err(got, want) <= TOL
+    assert scale_err(got, want) <= TOL_SCALE
+
+
+def test_auto_picks_the_tensor_core_kernel(ctx):
+    plan = ctx.conv2d_plan((1, 64, 56, 56), (64, 64, 3, 3), 1, 1)
+    assert plan.kernel.startswith("tc_3xtf32")
+
+
+def test_dilated_layer_rewrite_equals_direct_conv(ctx, oracle):
+    """Config 2 at full size: space-to-batch -> dense conv -> batch-to-space against the dilated conv itself and the
+    oracle (on a channel subset, the CPU needs seconds for that)."""
+    from test_gpu_layout import S2B, B2S
+    g = torch.Generator().manual_seed(2000)
+    x = torch.randn((1, 512, 64, 64), generator=g)
+    w = torch.randn((512, 512, 3, 3), generator=g) * (2.0 / 4608) ** 0.5
+    xd, wd = x.cuda(), w.cuda()
+    direct = ctx.conv2d(xd, wd, 2, 2, 1, 1, 2, 2)
+    s2b = ctx.transpose_chain(xd, S2B)
+    assert tuple(s2b.shape) == (4, 512, 32, 32)
+    dense = ctx.conv2d(s2b, wd, 1, 1)
+    rewritten = ctx.transpose_chain(dense, B2S)
+    ctx.sync_check()
+    assert tuple(rewritten.shape) == (1, 512, 64, 64)
+    # same kernel, same reduction order per output => the rewrite is bit-identical to the direct dilated conv
+    assert torch.equal(rewritten, direct)
+    want = oracle.conv2d(x.numpy(), w.numpy()[:32], pad=(2, 2), dil=(2, 2), wide=True)
+    got = direct[:, :32].cpu().numpy()
+    assert rel_err(got, want) <= TOL and scale_err(got, want) <= TOL_SCALE
+
+
+@pytest.mark.parametrize("algo", ["auto", "simt_fp32"])
+def test_h2n_rewrite_plus_correction_is_bit_identical(ctx, algo):
+    """Config 1: split H in two halves stacked on the batch dim, conv, merge back: rows 27 and 28 come out wrong;
+    the correction recomputes them from the original input and the result equals the unsplit conv bit for bit."""
+    g = torch.Generator().manual_seed(1000)
+    x = (torch.rand((1, 64, 56, 56), generator=g) * 2 - 1).cuda()
+    w = (torch.rand((64, 64, 3, 3), generator=g) * 2 - 1).cuda()
+    plan = ctx.conv2d_plan(x.shape, w.shape, 1, 1, algo=algo)
+    ctx.conv2d_set_weights(plan, w)
+    whole = ctx.conv2d_run(plan, x)
+    h2n = ctx.transpose(x, 2, [[0, 2], 1, -1, 3], -2)
+    half_plan = ctx.conv2d_plan(h2n.shape, w.shape, 1, 1, algo=algo)
+    ctx.conv2d_set_weights(half_plan, w)
+    merged = ctx.transpose(ctx.conv2d_run(half_plan, h2n), 0, [0, 1, [-1, 2], 3], 2)
+    diff_rows = torch.unique(torch.nonzero(merged != whole)[:, 2]).tolist()
+    assert diff_rows == [27, 28]
+    assert int((merged != whole).sum()) <= 2 * 64 * 56
+    assert torch.equal(merged[:, :, :27], whole[:, :, :27]) and torch.equal(merged[:, :, 29:], whole[:, :, 29:])
+    ctx.conv2d_correct(plan, x, merged, 27, 2)
+    ctx.sync_check()
+    assert torch.equal(merged, whole)
+
+
+def test_correction_window_in_both_axes(ctx):
+    x = torch.randn((2, 32, 24, 24), device="cuda")
+    w = torch.randn((32, 32, 3, 3), device="cuda") * 0.1
+    plan = ctx.conv2d_plan(x.shape, w.shape, 1, 1)
+    ctx.conv2d_set_weights(plan, w)
+    whole = ctx.conv2d_run(plan, x)
+    y = whole.clone()
+    y[:, :, 11:13, :] = 7.0
+    y[:, :, :, 11:13] = -7.0
+    ctx.conv2d_correct(plan, x, y, 11, 2)                 # seam rows
+    ctx.conv2d_correct(plan, x, y, 0, 24, 11, 2)          # seam columns
+    ctx.sync_check()
+    assert torch.equal(y, whole)
+
+
+def test_conv3d_vs_oracle(ctx, oracle):
+    rng = np.random.default_rng(33)
+    for xs, ws, pad, st in [((1, 8, 6, 12, 12), (16, 8, 3, 3, 3), (1, 1, 1), (1, 1, 1)),
+                            ((1, 3, 8, 20, 20), (8, 3, 3, 7, 7), (1, 3, 3), (1, 2, 2)),
+                            ((2, 8, 4, 8, 8), (8, 8, 3, 3, 3), (1, 1, 1), (2, 2, 2)),
+                            ((1, 16, 4, 6, 8), (8, 16, 1, 1, 1), (0, 0, 0), (2, 2, 2))]:
+        x = rng.standard_normal(xs).astype(np.float32)
+        w = (rng.standard_normal(ws) * np.sqrt(2.0 / np.prod(ws[1:]))).astype(np.float32)
+        want = oracle.conv3d(x, w, pad=pad, stride=st, wide=True)
+        for algo in ("auto", "simt_fp32"):
+            got = ctx.conv3d(dev(x), dev(w), pad, st, algo=algo).cpu().numpy()
+            ctx.sync_check()
+            assert got.shape == want.shape
+            assert rel_err(got, want) <= TOL and scale_err(got, want) <= TOL_SCALE
+
+
+def test_invalid_conv_arguments(ctx):
+    from pet_b200 import PetError
+    with pytest.raises(PetError) as e:
+        ctx.conv2d_plan((1, 6, 8, 8), (4, 4, 3, 3), 1, 1)  # 6 channels not divisible by filter channels 4
+    assert e.value.status == 1
+    with pytest.raises(PetError):
+        ctx.conv2d_plan((1, 4, 2, 2), (4, 4, 5, 5), 0, 0)  # empty output
+    with pytest.raises(PetError):
+        ctx.conv2d_plan((1, 8, 8, 8), (6, 4, 3, 3), 1, 1)  # f % groups != 0 (ConvOp::compute returns nullptr)
+    plan = ctx.conv2d_plan((1, 4, 8, 8), (4, 4, 3, 3), 1, 1, bias=True)
+    ctx.conv2d_set_weights(plan, torch.zeros((4, 4, 3, 3), device="cuda"))
+    with pytest.raises(PetError):
+        ctx.conv2d_run(plan, torch.zeros((1, 4, 8, 8), device="cuda"))  # bias promised, none passed
+
+
+def test_device_status_is_clean_and_timing_entry_point_works(ctx):
+    plan = ctx.conv2d_plan((1, 64, 56, 56), (64, 64, 3, 3), 1, 1)
+    ms = plan.time(rounds=20, warmup=5)
+    assert 0 < ms < 5
+    ctx.sync_check()

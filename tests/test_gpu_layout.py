@@ -1,0 +1,99 @@
+"""GPU: layout / index kernels through the C ABI, bit-exact against the reference-produced vectors and the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import golden_cases as gc
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a).view(np.int32)).cuda()
+
+
+def host(t):
+    return t.cpu().numpy().view(np.uint32)
+
+
+@pytest.mark.parametrize("name", sorted(gc.TRANSPOSES))
+def test_transpose_bit_exact_vs_reference_vectors(ctx, golden, name):
+    shape, split, after, factor = gc.TRANSPOSES[name]
+    got = host(ctx.transpose(dev(gc.words(shape, 11)), split, after, factor))
+    want = golden["tr_" + name]
+    assert got.shape == want.shape and np.array_equal(got, want)
+
+
+def test_copy_ops_bit_exact_vs_reference_vectors(ctx, golden):
+    t = gc.words((4, 6, 8, 10), 12)
+    assert np.array_equal(host(ctx.pad(dev(t), *gc.PAD)), golden["pad"])
+    assert np.array_equal(host(ctx.slice(dev(t), *gc.SLICE)), golden["slice"])
+    for d in range(4):
+        assert np.array_equal(host(ctx.extend(dev(t), d, 2)), golden[f"extend_{d}"])
+        assert np.array_equal(host(ctx.concat([dev(t)] * 3, d)), golden[f"concat_{d}"])
+        for j, o in enumerate(ctx.split(dev(t), d, [1, 1])):
+            assert np.array_equal(host(o), golden[f"split_{d}_{j}"])
+    for j, o in enumerate(ctx.split(dev(t), 1, [1, 2])):
+        assert np.array_equal(host(o), golden[f"split_ratio_{j}"])
+
+
+S2B = [(2, [0, 1, [-1, 2], 3], 2), (2, [[0, 2], 1, -1, 3], -2), (3, [0, 1, 2, [-1, 3]], 2), (3, [[0, 3], 1, 2, -1], -2)]
+B2S = [(0, [0, 1, 2, [-1, 3]], 2), (3, [0, 1, 2, [-1, 3]], -2), (0, [0, 1, [-1, 2], 3], 2), (2, [0, 1, [-1, 2], 3], -2)]
+
+
+@pytest.mark.parametrize("shape", [(1, 8, 16, 16), (2, 5, 12, 20), (1, 512, 64, 64)])
+def test_fused_space_to_batch_chain_equals_op_by_op(ctx, oracle, shape):
+    x = gc.words(shape, 3)
+    want = x
+    for op in S2B:
+        want = oracle.transpose(want, *op)
+    fused = ctx.transpose_chain(dev(x), S2B)
+    assert tuple(fused.shape) == want.shape and np.array_equal(host(fused), want)
+    step = dev(x)
+    for op in S2B:
+        step = ctx.transpose(step, *op)
+    assert torch.equal(step, fused)
+    back = ctx.transpose_chain(fused, B2S)  # the inverse chain restores the tensor
+    assert np.array_equal(host(back), x)
+
+
+@pytest.mark.parametrize("shape,split,after,factor", [
+    ((3, 7, 5), -1, [2, 1, 0], 2),           # ragged extents, no 32-multiple anywhere
+    ((1, 33, 65), -1, [0, 2, 1], 2),         # the reference's transpose kernel drops these remainders
+    ((6, 10, 3, 9), 1, [0, [2, -1], 1, 3], 5),
+    ((2, 1, 1, 4), -1, [3, 0, 1, 2], 2),
+    ((1,), -1, [0], 2),
+    ((128, 12, 64), -1, [1, 0, 2], 2),       # BERT head split
+    ((12, 128, 64), -1, [0, 2, 1], 2),       # K^T
+])
+def test_transpose_edge_shapes(ctx, oracle, shape, split, after, factor):
+    x = gc.words(shape, 21)
+    want = oracle.transpose(x, split, after, factor)
+    got = ctx.transpose(dev(x), split, after, factor)
+    assert tuple(got.shape) == want.shape and np.array_equal(host(got), want)
+
+
+def test_large_layout_round_trip_and_checksum(ctx):
+    # size-independent properties at a size far beyond L2: a permutation preserves the multiset (sum) and the
+    # inverse restores the tensor exactly
+    x = torch.randint(-2**31, 2**31 - 1, (64, 64, 128, 128), dtype=torch.int32, device="cuda")  # 256 MiB
+    y = ctx.transpose(x, 2, [[0, 2], 1, -1, 3], -2)   # H2N
+    assert int(y.to(torch.int64).sum()) == int(x.to(torch.int64).sum())
+    z = ctx.transpose(y, 0, [0, 1, [-1, 2], 3], 2)    # N2H
+    assert torch.equal(z, x)
+    t = ctx.transpose(x, -1, [0, 1, 3, 2], 2)
+    assert torch.equal(t, x.transpose(2, 3).contiguous())
+
+
+def test_invalid_layout_requests_are_rejected(ctx):
+    from pet_b200 import PetError
+    x = torch.zeros((3, 5), dtype=torch.int32, device="cuda")
+    with pytest.raises(PetError) as e:
+        ctx.transpose(x, 1, [0, 1, -1], 2)  # 5 % 2 != 0: the reference marks the output invalid
+    assert e.value.status == 1
+    with pytest.raises(PetError):
+        ctx.transpose(x, -1, [0, 0], 2)  # not a permutation
+    with pytest.raises(PetError):
+        ctx.slice(x, [0, 0], [3, 0])  # empty result
+    with pytest.raises(PetError):
+        ctx.split(x, 1, [1, 1])  # 5 not divisible by the ratio sum

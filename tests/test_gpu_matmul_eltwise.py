@@ -1,0 +1,101 @@
+"""GPU: matmul, elementwise, activation, pooling, softmax, LayerNorm, batch-norm through the C ABI vs the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import golden_cases as gc
+from conftest import rel_err, scale_err
+
+pytestmark = pytest.mark.gpu
+TOL, TOL_SCALE = 1e-3, 2e-4
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("algo", ["auto", "simt_fp32"])
+def test_batch_gemm_known_answer(ctx, golden, algo):
+    i0, w0, w1 = gc.batch_gemm_inputs()  # exact in fp32
+    f = lambda a: dev(a.astype(np.float32))
+    o0 = ctx.matmul(f(i0), f(w0), algo=algo).cpu().numpy().astype(np.uint32)
+    o1 = ctx.matmul(f(i0), f(w1), algo=algo).cpu().numpy().astype(np.uint32)
+    assert np.array_equal(o0, golden["bgemm_o0"]) and np.array_equal(o1, golden["bgemm_o1"])
+    a2 = ctx.concat([f(i0), f(i0)], 0)
+    b2 = ctx.concat([f(w0), f(w1)], 0)
+    merged = ctx.matmul(a2, b2, algo=algo)
+    assert np.array_equal(merged.cpu().numpy().astype(np.uint32), golden["bgemm_merged"])
+    parts = ctx.split(merged, 0, [1, 1])
+    assert np.array_equal(parts[0].cpu().numpy().astype(np.uint32), golden["bgemm_o0"])
+    ctx.sync_check()
+
+
+MM = [  # b, m, n, k, transA, transB   (BERT-base shapes and ragged ones)
+    (1, 128, 768, 768, False, False), (12, 128, 128, 64, False, True), (12, 128, 64, 128, False, False),
+    (1, 128, 3072, 768, False, False), (1, 128, 768, 3072, False, False), (1, 1, 1000, 512, False, False),
+    (3, 5, 4, 7, False, False), (2, 36, 20, 50, True, True), (2, 300, 40, 24, True, False), (1, 64, 33, 100, False, True),
+]
+
+
+@pytest.mark.parametrize("algo", ["auto", "simt_fp32"])
+@pytest.mark.parametrize("shape", MM, ids=[str(s) for s in MM])
+def test_matmul_vs_oracle(ctx, oracle, shape, algo):
+    b, m, n, k, ta, tb = shape
+    rng = np.random.default_rng(b * 1000 + m + n + k)
+    a = rng.standard_normal((b, k, m) if ta else (b, m, k)).astype(np.float32)
+    bm = (rng.standard_normal((b, n, k) if tb else (b, k, n)) / np.sqrt(k)).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    want = oracle.matmul(a, bm, bias, ta, tb, act="gelu", wide=True)
+    got = ctx.matmul(dev(a), dev(bm), ta, tb, bias=dev(bias), act="gelu", algo=algo).cpu().numpy()
+    ctx.sync_check()
+    assert got.shape == want.shape
+    assert rel_err(got, want) <= TOL and scale_err(got, want) <= TOL_SCALE
+
+
+def test_matmul_rejects_mismatched_operands(ctx):
+    from pet_b200 import PetError
+    with pytest.raises(PetError):
+        ctx.matmul_plan((2, 4, 5), (3, 5, 6))  # batch mismatch (MatmulOp::checkValid)
+    with pytest.raises(PetError):
+        ctx.matmul_plan((2, 4, 5), (2, 6, 7))  # inner extents differ
+
+
+def test_eltwise_and_activations(ctx, oracle, golden):
+    u, v = gc.small_ints((4, 6, 8, 10), 41), gc.small_ints((8, 10), 42)
+    uf, vf = (u % 64).astype(np.float32), (v % 64).astype(np.float32)
+    for k in ("add", "sub", "mul"):
+        got = ctx.eltwise(k, [dev(uf), dev(vf)]).cpu().numpy()
+        assert np.array_equal(got, oracle.eltwise(k, [uf, vf]))  # exact: small integers
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((3, 7, 5, 9)).astype(np.float32)   # odd sizes: scalar path
+    x4 = rng.standard_normal((4, 8, 16, 16)).astype(np.float32)  # vector path
+    for t in (x, x4):
+        assert np.array_equal(ctx.activation(dev(t), "relu").cpu().numpy(), oracle.activation(t, "relu"))
+        for act in ("sigmoid", "tanh", "gelu"):
+            assert rel_err(ctx.activation(dev(t), act).cpu().numpy(), oracle.activation(t, act)) <= 1e-4
+        r = rng.standard_normal(t.shape).astype(np.float32)
+        got = ctx.eltwise("add", [dev(t), dev(r)], act="relu").cpu().numpy()  # residual add + relu
+        assert np.array_equal(got, np.maximum(t + r, 0))
+    ctx.sync_check()
+
+
+def test_pool_softmax_layernorm_batchnorm(ctx, oracle):
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((2, 64, 112, 112)).astype(np.float32)
+    assert np.array_equal(ctx.maxpool(dev(x), 3, 3, 1, 1, 1, 1, 2, 2).cpu().numpy(), oracle.maxpool(x, (3, 3), (1, 1), (2, 2)))
+    y = rng.standard_normal((2, 512, 7, 7)).astype(np.float32)
+    assert rel_err(ctx.avgpool(dev(y), 7, 7, 0, 0, 1, 1).cpu().numpy(), oracle.avgpool(y, (7, 7), (0, 0), (1, 1))) <= 1e-5
+    assert rel_err(ctx.avgpool(dev(y), 3, 3, 1, 1, 2, 2).cpu().numpy(), oracle.avgpool(y, (3, 3), (1, 1), (2, 2))) <= 1e-5
+    assert rel_err(ctx.rowmean(dev(y), 49).cpu().numpy(), y.reshape(-1, 49).mean(1)) <= 1e-5
+    s = rng.standard_normal((12, 128, 128)).astype(np.float32) * 4
+    assert rel_err(ctx.softmax(dev(s)).cpu().numpy(), oracle.softmax(s)) <= 1e-5
+    s2 = rng.standard_normal((5, 1000)).astype(np.float32)
+    assert rel_err(ctx.softmax(dev(s2)).cpu().numpy(), oracle.softmax(s2)) <= 1e-5
+    h = rng.standard_normal((128, 768)).astype(np.float32)
+    g, b = rng.standard_normal(768).astype(np.float32), rng.standard_normal(768).astype(np.float32)
+    assert rel_err(ctx.layernorm(dev(h), dev(g), dev(b)).cpu().numpy(), oracle.layernorm(h, g, b)) <= 1e-4
+    z = rng.standard_normal((2, 6, 5, 7)).astype(np.float32)
+    sc, bi, me = [rng.standard_normal(6).astype(np.float32) for _ in range(3)]
+    va = (np.abs(rng.standard_normal(6)) + 0.5).astype(np.float32)
+    assert rel_err(ctx.batchnorm(dev(z), dev(sc), dev(bi), dev(me), dev(va)).cpu().numpy(), oracle.batchnorm(z, sc, bi, me, va)) <= 1e-6
+    ctx.sync_check()
