@@ -156,7 +156,7 @@ def test_invalid_conv_arguments(ctx):
     with pytest.raises(PetError):
         ctx.conv2d_plan((1, 4, 2, 2), (4, 4, 5, 5), 0, 0)  # empty output
     with pytest.raises(PetError):
-        ctx.conv2d_plan((1, 8, 8, 8), (6, 4, 3, 3), 1, 1)  # f % groups != 0 (ConvOp::compute returns nullptr)
+        ctx.conv2d_plan((1, 8, 8, 8), (5, 4, 3, 3), 1, 1)  # f % groups != 0 (ConvOp::compute returns nullptr)
     plan = ctx.conv2d_plan((1, 4, 8, 8), (4, 4, 3, 3), 1, 1, bias=True)
     ctx.conv2d_set_weights(plan, torch.zeros((4, 4, 3, 3), device="cuda"))
     with pytest.raises(PetError):
