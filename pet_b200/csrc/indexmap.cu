@@ -29,94 +29,197 @@ struct MapParams {
 // ---------------------------------------------------------------------------------------------------------
 // kernels
 // ---------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) k_rowcopy_v4(const uint4 *__restrict__ in, uint4 *__restrict__ out, MapParams p) {
-    // iteration space counted in uint4 units along the innermost digit; strides of outer digits are word
-    // strides divisible by 4 (checked on the host).
-    long long total4 = p.total >> 2;
-    int inner4 = p.ext[p.nd - 1] >> 2;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total4;
-         i += (long long)gridDim.x * blockDim.x) {
-        long long rem = i / inner4;
-        long long io = p.ibase + (long long)(i - rem * inner4) * 4;
-        long long oo = p.obase + (long long)(i - rem * inner4) * 4;
+// Decomposes a linear index over the digits [0, nd) of `p` (last digit fastest) into input/output word offsets.
+// I is the index type: 32-bit when the iteration space allows it (64-bit division is an order of magnitude slower).
+template <typename I, int FIRST_SKIP>
+__device__ __forceinline__ void decode(const MapParams &p, I rem, long long &io, long long &oo, bool &inside) {
 #pragma unroll
-        for (int d = kMaxDigits - 2; d >= 0; --d) {
-            if (d < p.nd - 1) {
-                long long q = rem / p.ext[d];
-                int idx = (int)(rem - q * p.ext[d]);
-                rem = q;
-                io += idx * p.istr[d];
-                oo += idx * p.ostr[d];
-            }
+    for (int d = kMaxDigits - 1 - FIRST_SKIP; d >= 0; --d) {
+        if (d < p.nd - FIRST_SKIP) {
+            const I q = rem / (I)p.ext[d];
+            const int idx = (int)(rem - q * (I)p.ext[d]);
+            rem = q;
+            io += idx * p.istr[d];
+            oo += idx * p.ostr[d];
+            if (p.guarded && (idx < p.glo[d] || idx >= p.ghi[d]))
+                inside = false;
         }
-        out[oo >> 2] = __ldg(in + (io >> 2));
     }
 }
 
-__global__ void __launch_bounds__(256) k_gather(const uint32_t *__restrict__ in, uint32_t *__restrict__ out, MapParams p) {
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < p.total;
-         i += (long long)gridDim.x * blockDim.x) {
-        long long rem = i, io = p.ibase, oo = p.obase;
-        bool inside = true;
+template <typename I>
+__global__ void __launch_bounds__(256) k_rowcopy_v4(const uint4 *__restrict__ in, uint4 *__restrict__ out, MapParams p) {
+    // iteration space counted in uint4 units along the innermost digit; strides of outer digits are word strides
+    // divisible by 4 (checked on the host).  Four independent 128-bit loads are in flight per thread.
+    const I total4 = (I)(p.total >> 2);
+    const I inner4 = (I)(p.ext[p.nd - 1] >> 2);
+    const I step = (I)gridDim.x * blockDim.x;
+    for (I i0 = (I)blockIdx.x * blockDim.x + threadIdx.x; i0 < total4; i0 += 4 * step) {
+        uint4 v[4];
+        long long oo[4];
 #pragma unroll
-        for (int d = kMaxDigits - 1; d >= 0; --d) {
-            if (d < p.nd) {
-                long long q = rem / p.ext[d];
-                int idx = (int)(rem - q * p.ext[d]);
-                rem = q;
-                io += idx * p.istr[d];
-                oo += idx * p.ostr[d];
-                if (p.guarded && (idx < p.glo[d] || idx >= p.ghi[d]))
-                    inside = false;
+        for (int u = 0; u < 4; ++u) {
+            const I i = i0 + (I)u * step;
+            if (i < total4) {
+                const I row = i / inner4;
+                long long io = p.ibase + (long long)(i - row * inner4) * 4;
+                oo[u] = p.obase + (long long)(i - row * inner4) * 4;
+                bool inside = true;
+                decode<I, 1>(p, row, io, oo[u], inside);
+                v[u] = __ldg(in + (io >> 2));
             }
         }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (i0 + (I)u * step < total4)
+                out[oo[u] >> 2] = v[u];
+    }
+}
+
+template <typename I>
+__global__ void __launch_bounds__(256) k_gather(const uint32_t *__restrict__ in, uint32_t *__restrict__ out, MapParams p) {
+    const I total = (I)p.total;
+    for (I i = (I)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (I)gridDim.x * blockDim.x) {
+        long long io = p.ibase, oo = p.obase;
+        bool inside = true;
+        decode<I, 0>(p, i, io, oo, inside);
         out[oo] = inside ? __ldg(in + io) : 0u;
     }
 }
 
+constexpr int kMaxTileDigits = 4;
+constexpr int kTileElems = 2048;
+constexpr int kTileEPT = kTileElems / 256; // elements per thread
+
+// A tile is the cross product of up to four digits (one of them possibly cut into chunks).  The digits are chosen
+// on the host so that the tile contains both a long run that is contiguous in the INPUT and a long run that is
+// contiguous in the OUTPUT.  Each thread keeps, in registers, the input offset / staging slot of the elements it
+// reads (enumerated in input-stride order) and the output offset of the elements it writes (output order); tiles
+// are then streamed: coalesced reads -> shared memory -> coalesced writes.
 struct TileParams {
-    MapParams m;   // digits with the two tile digits REMOVED (batch digits), in the same order
-    int ext_a, ext_z;           // extents of the input-contiguous digit (a) and the output-contiguous digit (z)
-    long long istr_z, ostr_a;   // a has istr 1, z has ostr 1
-    int ta, tz;                 // tile extents
-    int tiles_a, tiles_z;
+    MapParams m;             // batch digits (everything outside the tile, plus the chunk counter)
+    int nt;                  // tile digits, in output order (0 = outermost)
+    int text[kMaxTileDigits];
+    int tistr[kMaxTileDigits], tostr[kMaxTileDigits];
+    int read_order[kMaxTileDigits]; // tile digit indices, fastest (smallest input stride) first
+    unsigned tmagic[kMaxTileDigits]; // ceil(2^22 / text[k]): e / text[k] == (e * magic) >> 22 for e, text[k] <= 2048
+    int tile_elems;          // prod(text)
+    int ck;                  // tile digit that is chunked (-1: none)
+    int chunk_ext;           // full extent of that digit (text[ck] is the chunk)
+    int chunk_digit;         // index inside m of the batch digit that counts chunks (-1: single chunk)
+    int inner_ck;            // prod(text[ck+1:]) — only used when ck == 0 (ragged last chunk allowed)
 };
 
+__device__ __forceinline__ int fast_div(int e, unsigned magic) { return (int)(((unsigned long long)e * magic) >> 22); }
+
 __global__ void __launch_bounds__(256) k_tile(const uint32_t *__restrict__ in, uint32_t *__restrict__ out, TileParams t) {
-    extern __shared__ uint32_t tile[];
-    const int pitch = t.ta | 1; // odd pitch: conflict-free column reads
-    long long ntiles = (long long)t.tiles_a * t.tiles_z * t.m.total;
-    for (long long blk = blockIdx.x; blk < ntiles; blk += gridDim.x) {
-        long long rem = blk;
-        int tzi = (int)(rem % t.tiles_z);
-        rem /= t.tiles_z;
-        int tai = (int)(rem % t.tiles_a);
-        rem /= t.tiles_a;
-        long long io = t.m.ibase, oo = t.m.obase;
+    __shared__ uint32_t tile[kTileElems + kTileElems / 32]; // one pad word per 32: transposing scatters stay conflict-free
+    int li[kTileEPT], lo[kTileEPT];
+    uint32_t ls[kTileEPT];
+    {
+        int sstride[kMaxTileDigits];
+        int acc = 1;
+#pragma unroll
+        for (int k = kMaxTileDigits - 1; k >= 0; --k)
+            if (k < t.nt) {
+                sstride[k] = acc;
+                acc *= t.text[k];
+            }
+#pragma unroll
+        for (int u = 0; u < kTileEPT; ++u) {
+            const int e = threadIdx.x + u * 256;
+            int rem = e, off_o = 0;
+#pragma unroll
+            for (int k = kMaxTileDigits - 1; k >= 0; --k)
+                if (k < t.nt) {
+                    const int q = fast_div(rem, t.tmagic[k]);
+                    off_o += (rem - q * t.text[k]) * t.tostr[k];
+                    rem = q;
+                }
+            lo[u] = off_o;
+            rem = e;
+            int off_i = 0, sidx = 0, cck = 0;
+#pragma unroll
+            for (int q = 0; q < kMaxTileDigits; ++q)
+                if (q < t.nt) {
+                    const int k = t.read_order[q];
+                    const int d = fast_div(rem, t.tmagic[k]);
+                    const int c = rem - d * t.text[k];
+                    rem = d;
+                    off_i += c * t.tistr[k];
+                    sidx += c * sstride[k];
+                    if (k == t.ck)
+                        cck = c;
+                }
+            li[u] = off_i;
+            ls[u] = (uint32_t)(sidx + (sidx >> 5)) | ((uint32_t)cck << 16);
+        }
+    }
+    // contiguous range of tiles per CTA: one full decode, then an odometer
+    const unsigned ntiles = (unsigned)t.m.total;
+    const unsigned per = (ntiles + gridDim.x - 1) / gridDim.x;
+    const unsigned first = blockIdx.x * per;
+    const unsigned last = min(first + per, ntiles);
+    if (first >= last)
+        return;
+    int idx[kMaxDigits];
+    long long io = t.m.ibase, oo = t.m.obase;
+    {
+        unsigned rem = first;
 #pragma unroll
         for (int d = kMaxDigits - 1; d >= 0; --d) {
+            idx[d] = 0;
             if (d < t.m.nd) {
-                long long q = rem / t.m.ext[d];
-                int idx = (int)(rem - q * t.m.ext[d]);
+                const unsigned q = rem / (unsigned)t.m.ext[d];
+                idx[d] = (int)(rem - q * (unsigned)t.m.ext[d]);
                 rem = q;
-                io += idx * t.m.istr[d];
-                oo += idx * t.m.ostr[d];
+                io += idx[d] * t.m.istr[d];
+                oo += idx[d] * t.m.ostr[d];
             }
         }
-        int a0 = tai * t.ta, z0 = tzi * t.tz;
-        int na = min(t.ta, t.ext_a - a0), nz = min(t.tz, t.ext_z - z0);
-        // read: a fastest (input-contiguous)
-        for (int e = threadIdx.x; e < na * nz; e += blockDim.x) {
-            int zz = e / na, aa = e - zz * na;
-            tile[zz * pitch + aa] = __ldg(in + io + (a0 + aa) + (long long)(z0 + zz) * t.istr_z);
+    }
+    for (unsigned blk = first; blk < last; ++blk) {
+        int chunk_idx = 0;
+#pragma unroll
+        for (int d = 0; d < kMaxDigits; ++d)
+            if (d == t.chunk_digit)
+                chunk_idx = idx[d];
+        const int valid = t.ck >= 0 ? min(t.text[t.ck], t.chunk_ext - chunk_idx * t.text[t.ck]) : 0x7fffffff;
+        const uint32_t *ip = in + io;
+        uint32_t v[kTileEPT];
+#pragma unroll
+        for (int u = 0; u < kTileEPT; ++u)
+            if (threadIdx.x + u * 256 < t.tile_elems && (int)(ls[u] >> 16) < valid)
+                v[u] = __ldg(ip + li[u]);
+#pragma unroll
+        for (int u = 0; u < kTileEPT; ++u)
+            if (threadIdx.x + u * 256 < t.tile_elems && (int)(ls[u] >> 16) < valid)
+                tile[ls[u] & 0xffffu] = v[u];
+        __syncthreads();
+        const int lim = (t.ck == 0) ? valid * t.inner_ck : t.tile_elems;
+        uint32_t *op = out + oo;
+#pragma unroll
+        for (int u = 0; u < kTileEPT; ++u) {
+            const int e = threadIdx.x + u * 256;
+            if (e < lim)
+                op[lo[u]] = tile[e + (e >> 5)];
         }
         __syncthreads();
-        // write: z fastest (output-contiguous)
-        for (int e = threadIdx.x; e < na * nz; e += blockDim.x) {
-            int aa = e / nz, zz = e - aa * nz;
-            out[oo + (long long)(a0 + aa) * t.ostr_a + (z0 + zz)] = tile[zz * pitch + aa];
-        }
-        __syncthreads();
+        // odometer: next tile
+        bool carry = true;
+#pragma unroll
+        for (int d = kMaxDigits - 1; d >= 0; --d)
+            if (d < t.m.nd && carry) {
+                if (++idx[d] < t.m.ext[d]) {
+                    io += t.m.istr[d];
+                    oo += t.m.ostr[d];
+                    carry = false;
+                } else {
+                    io -= (long long)(t.m.ext[d] - 1) * t.m.istr[d];
+                    oo -= (long long)(t.m.ext[d] - 1) * t.m.ostr[d];
+                    idx[d] = 0;
+                }
+            }
     }
 }
 
@@ -137,7 +240,7 @@ struct LayoutPlan : petb200_plan {
     int out_nd = 0;
     int out_dims[kMaxDigits * 2]{};
     long long in_words = 0, out_words = 0;
-    int grid = 1;
+    int grid = 1, grid_gather = 1;
     size_t smem = 0;
     DevBuf bin, bout; // scratch for timing only
     int bench_launch(cudaStream_t s) override;
@@ -212,58 +315,153 @@ static int finalize_plan(petb200_ctx *ctx, LayoutPlan *pl, std::vector<Digit> di
     if (v4) {
         pl->mode = 0;
         pl->kernel = "rowcopy";
-        long long blocks = (m.total / 4 + 255) / 256;
-        pl->grid = (int)std::min<long long>(blocks, (long long)sms * 16);
+        long long blocks = (m.total / 16 + 255) / 256;
+        pl->grid = (int)std::max<long long>(1, std::min<long long>(blocks, (long long)sms * 8));
+        pl->grid_gather = (int)std::max<long long>(1, std::min<long long>((m.total + 255) / 256, (long long)sms * 16));
         return PETB200_OK;
     }
-    // tile: output-contiguous digit z = last (ostr 1); input-contiguous digit a != z with istr 1
-    int a = -1;
-    if (!m.guarded && m.ostr[last] == 1 && m.istr[last] != 1)
-        for (int i = 0; i < last; ++i)
-            if (m.istr[i] == 1)
-                a = i;
-    if (a >= 0) {
-        TileParams &t = pl->tp;
-        t.ext_a = m.ext[a];
-        t.ext_z = m.ext[last];
-        t.istr_z = m.istr[last];
-        t.ostr_a = m.ostr[a];
-        // tile extents: up to 64 x 64 words, favouring whichever digit is short
-        int ta = std::min(64, t.ext_a), tz = std::min(64, t.ext_z);
-        while (ta * tz < 2048 && tz < t.ext_z && tz < 1024)
-            tz = std::min(t.ext_z, tz * 2);
-        while (ta * tz < 2048 && ta < t.ext_a && ta < 1024)
-            ta = std::min(t.ext_a, ta * 2);
-        t.ta = ta;
-        t.tz = tz;
-        t.tiles_a = ceil_div(t.ext_a, ta);
-        t.tiles_z = ceil_div(t.ext_z, tz);
-        t.m = m;
-        int k = 0;
-        t.m.total = 1;
+    // tile: the innermost output digit is not contiguous in the input
+    if (!m.guarded && m.ostr[last] == 1 && m.istr[last] != 1 && m.total < (1ll << 31)) {
+        std::vector<int> chosen; // indices into m, kept sorted at the end
+        auto has = [&](int i) { return std::find(chosen.begin(), chosen.end(), i) != chosen.end(); };
+        auto tile_size = [&]() {
+            long long p = 1;
+            for (int i : chosen)
+                p *= m.ext[i];
+            return p;
+        };
+        // (a) output run: innermost digits while they stay contiguous in the output, until >= 64 words
+        long long run = 1;
+        for (int i = last; i >= 0 && run < 64 && (int)chosen.size() < kMaxTileDigits - 1; --i) {
+            if (m.ostr[i] != run)
+                break;
+            chosen.push_back(i);
+            run *= m.ext[i];
+        }
+        // (b) input run: digits by ascending input stride while they chain contiguously, until >= 64 words
+        std::vector<int> by_istr(m.nd);
         for (int i = 0; i < m.nd; ++i)
-            if (i != a && i != last) {
-                t.m.ext[k] = m.ext[i];
-                t.m.istr[k] = m.istr[i];
-                t.m.ostr[k] = m.ostr[i];
-                t.m.total *= m.ext[i];
+            by_istr[i] = i;
+        std::sort(by_istr.begin(), by_istr.end(), [&](int x, int y) { return m.istr[x] < m.istr[y]; });
+        run = 1;
+        for (int q = 0; q < m.nd && run < 64; ++q) {
+            int i = by_istr[q];
+            if (m.istr[i] != run)
+                break;
+            if (!has(i)) {
+                if ((int)chosen.size() >= kMaxTileDigits)
+                    break;
+                chosen.push_back(i);
+            }
+            run *= m.ext[i];
+        }
+        // (c) grow small tiles with further outer digits
+        for (int i = last; i >= 0 && tile_size() < kTileElems / 2 && (int)chosen.size() < kMaxTileDigits; --i)
+            if (!has(i))
+                chosen.push_back(i);
+        std::sort(chosen.begin(), chosen.end());
+        // If the tile is too large, ONE digit is cut into chunks: the outermost chosen digit when cutting it is enough
+        // (its last chunk may be ragged), otherwise the largest digit, which then needs a chunk that divides it.
+        int ckq = -1, chunk = 0;
+        bool ok = !chosen.empty() && m.total / std::max<long long>(1, tile_size()) < (1ll << 31);
+        for (int i : chosen)
+            ok = ok && (long long)m.ext[i] * std::max(m.istr[i], m.ostr[i]) < (1ll << 31);
+        if (ok && tile_size() > kTileElems) {
+            auto others_of = [&](size_t q) {
+                long long o = 1;
+                for (size_t r = 0; r < chosen.size(); ++r)
+                    if (r != q)
+                        o *= m.ext[chosen[r]];
+                return o;
+            };
+            if (others_of(0) <= kTileElems / 2) {
+                ckq = 0;
+                chunk = (int)std::min<long long>(m.ext[chosen[0]], kTileElems / others_of(0));
+                for (int c = chunk; c >= std::max(1, chunk / 2); --c)
+                    if (m.ext[chosen[0]] % c == 0) {
+                        chunk = c;
+                        break;
+                    }
+            } else {
+                size_t big = 0;
+                for (size_t q = 1; q < chosen.size(); ++q)
+                    if (m.ext[chosen[q]] > m.ext[chosen[big]])
+                        big = q;
+                const long long lim = kTileElems / std::max<long long>(1, others_of(big));
+                for (long long c = std::min<long long>(lim, m.ext[chosen[big]]); c >= 1; --c)
+                    if (m.ext[chosen[big]] % c == 0) {
+                        chunk = (int)c;
+                        break;
+                    }
+                ckq = (int)big;
+                ok = lim >= 1 && chunk >= 1 && (chunk * others_of(big) >= kTileElems / 8 || big == 0);
+            }
+        }
+        if (ok) {
+            TileParams &t = pl->tp;
+            t.nt = (int)chosen.size();
+            t.tile_elems = 1;
+            for (int q = 0; q < t.nt; ++q) {
+                const int i = chosen[q];
+                t.text[q] = q == ckq ? chunk : m.ext[i];
+                t.tistr[q] = (int)m.istr[i];
+                t.tostr[q] = (int)m.ostr[i];
+                t.tile_elems *= t.text[q];
+                t.tmagic[q] = (unsigned)(((1u << 22) + t.text[q] - 1) / t.text[q]);
+            }
+            t.ck = ckq;
+            t.chunk_ext = ckq >= 0 ? m.ext[chosen[ckq]] : 0;
+            t.inner_ck = ckq == 0 ? t.tile_elems / t.text[0] : 1;
+            std::vector<int> ro(t.nt);
+            for (int q = 0; q < t.nt; ++q)
+                ro[q] = q;
+            std::sort(ro.begin(), ro.end(), [&](int x, int y) { return t.tistr[x] < t.tistr[y]; });
+            for (int q = 0; q < t.nt; ++q)
+                t.read_order[q] = ro[q];
+            // batch digits: everything not chosen, plus the chunk counter in place of the chunked digit
+            t.m = m;
+            int k = 0;
+            t.m.total = 1;
+            t.chunk_digit = -1;
+            for (int i = 0; i < m.nd; ++i) {
+                if (ckq >= 0 && i == chosen[ckq]) {
+                    const int nchunks = ceil_div(m.ext[i], chunk);
+                    if (nchunks == 1)
+                        continue;
+                    t.m.ext[k] = nchunks;
+                    t.m.istr[k] = m.istr[i] * chunk;
+                    t.m.ostr[k] = m.ostr[i] * chunk;
+                    t.chunk_digit = k;
+                } else if (has(i)) {
+                    continue;
+                } else {
+                    t.m.ext[k] = m.ext[i];
+                    t.m.istr[k] = m.istr[i];
+                    t.m.ostr[k] = m.ostr[i];
+                }
+                t.m.total *= t.m.ext[k];
                 ++k;
             }
-        t.m.nd = k;
-        pl->mode = 1;
-        pl->kernel = "tile";
-        pl->smem = (size_t)tz * (ta | 1) * 4;
-        long long ntiles = (long long)t.tiles_a * t.tiles_z * t.m.total;
-        pl->grid = (int)std::min<long long>(ntiles, (long long)sms * 8);
-        if (pl->smem > 48 * 1024)
-            return fail(ctx, PETB200_ERR_UNSUPPORTED, "tile too large");
-        return PETB200_OK;
+            t.m.nd = k;
+            pl->mode = 1;
+            pl->kernel = "tile";
+            pl->smem = 0;
+            pl->grid = (int)std::min<long long>(t.m.total, (long long)sms * 4);
+            return PETB200_OK;
+        }
     }
     pl->mode = 2;
     pl->kernel = "gather";
     long long blocks = (m.total + 255) / 256;
-    pl->grid = (int)std::min<long long>(blocks, (long long)sms * 16);
+    pl->grid = pl->grid_gather = (int)std::max<long long>(1, std::min<long long>(blocks, (long long)sms * 16));
     return PETB200_OK;
+}
+
+static void launch_gather(LayoutPlan *pl, const void *in, void *out, cudaStream_t s) {
+    if (pl->mp.total < (1ll << 31))
+        k_gather<unsigned><<<pl->grid_gather, 256, 0, s>>>((const uint32_t *)in, (uint32_t *)out, pl->mp);
+    else
+        k_gather<unsigned long long><<<pl->grid_gather, 256, 0, s>>>((const uint32_t *)in, (uint32_t *)out, pl->mp);
 }
 
 static int layout_launch(LayoutPlan *pl, const void *in, void *out, cudaStream_t s) {
@@ -271,17 +469,20 @@ static int layout_launch(LayoutPlan *pl, const void *in, void *out, cudaStream_t
         return PETB200_OK;
     if (pl->mode == 0) {
         if ((((uintptr_t)in) | ((uintptr_t)out)) & 15) { // unaligned caller buffers: fall back to the word kernel
-            k_gather<<<pl->grid, 256, 0, s>>>((const uint32_t *)in, (uint32_t *)out, pl->mp);
+            launch_gather(pl, in, out, s);
             return launched(pl->ctx, "k_gather");
         }
-        k_rowcopy_v4<<<pl->grid, 256, 0, s>>>((const uint4 *)in, (uint4 *)out, pl->mp);
+        if (pl->mp.total < (1ll << 31))
+            k_rowcopy_v4<unsigned><<<pl->grid, 256, 0, s>>>((const uint4 *)in, (uint4 *)out, pl->mp);
+        else
+            k_rowcopy_v4<unsigned long long><<<pl->grid, 256, 0, s>>>((const uint4 *)in, (uint4 *)out, pl->mp);
         return launched(pl->ctx, "k_rowcopy_v4");
     }
     if (pl->mode == 1) {
         k_tile<<<pl->grid, 256, pl->smem, s>>>((const uint32_t *)in, (uint32_t *)out, pl->tp);
         return launched(pl->ctx, "k_tile");
     }
-    k_gather<<<pl->grid, 256, 0, s>>>((const uint32_t *)in, (uint32_t *)out, pl->mp);
+    launch_gather(pl, in, out, s);
     return launched(pl->ctx, "k_gather");
 }
 
