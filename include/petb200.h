@@ -100,6 +100,9 @@ int petb200_conv3d_run(petb200_plan *plan, const float *x, const float *bias, fl
  * then + bias[n], then activation (bias before activation, unlike the emitted program, which is a reference bug). */
 int petb200_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int n, int k, int has_bias, int act,
                         int algo, petb200_plan **out);
+/* Declares B a weight: it is preprocessed once here (hoisted like the reference's weight-only operators,
+ * ref: src/Graph/code_engine.cc:187-193) and petb200_matmul_run may then be called with b = NULL. */
+int petb200_matmul_set_weights(petb200_plan *plan, const float *b, petb200_stream stream);
 int petb200_matmul_run(petb200_plan *plan, const float *a, const float *b, const float *bias, float *c,
                        petb200_stream stream);
 

@@ -144,6 +144,9 @@ extern "C" int petb200_matmul_plan(petb200_ctx *ctx, int transA, int transB, int
                                    int act, int algo, petb200_plan **out) {
     return make_matmul_plan(ctx, transA, transB, b, m, n, k, has_bias, act, algo, out);
 }
+extern "C" int petb200_matmul_set_weights(petb200_plan *plan, const float *b, petb200_stream s) {
+    return matmul_set_weights(plan, b, (cudaStream_t)s);
+}
 extern "C" int petb200_matmul_run(petb200_plan *plan, const float *a, const float *b, const float *bias, float *c,
                                   petb200_stream s) {
     return matmul_run(plan, a, b, bias, c, (cudaStream_t)s);

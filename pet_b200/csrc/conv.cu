@@ -308,6 +308,7 @@ struct MatmulPlan : petb200_plan {
     int algo = 0;
     void *tc = nullptr;
     DevBuf at; // A re-laid as [b][k][m] when the caller's A is [b][m][k]
+    const float *b_weight = nullptr; // set by matmul_set_weights
     DevBuf ba, bbm, bbias, bc;
     ~MatmulPlan() override {
         if (tc)
@@ -365,12 +366,14 @@ int matmul_run(petb200_plan *plan, const float *a, const float *b, const float *
     if (!pl)
         return PETB200_ERR_INVALID;
     petb200_ctx *ctx = pl->ctx;
+    if (!b)
+        b = pl->b_weight;
     if (!a || !b || !c)
         return fail(ctx, PETB200_ERR_INVALID, "matmul run: null buffer");
     if (pl->has_bias && !bias)
         return fail(ctx, PETB200_ERR_INVALID, "matmul run: plan was made with a bias but none was passed");
     if (pl->algo == PETB200_ALGO_TC_3XTF32) {
-        int rc = tc_matmul_pack_b(pl->tc, b, s);
+        int rc = (b == pl->b_weight) ? PETB200_OK : tc_matmul_pack_b(pl->tc, b, s);
         if (rc)
             return rc;
         const float *at = a;
@@ -388,6 +391,16 @@ int matmul_run(petb200_plan *plan, const float *a, const float *b, const float *
     k_matmul_simt<<<grid_for(ctx, total, 256), 256, 0, s>>>(a, b, pl->has_bias ? bias : nullptr, c, pl->bs, pl->m, pl->n, pl->k,
                                                             pl->transA, pl->transB, pl->act);
     return launched(ctx, "k_matmul_simt");
+}
+
+int matmul_set_weights(petb200_plan *plan, const float *b, cudaStream_t s) {
+    auto *pl = dynamic_cast<MatmulPlan *>(plan);
+    if (!pl || !b)
+        return PETB200_ERR_INVALID;
+    pl->b_weight = b;
+    if (pl->algo == PETB200_ALGO_TC_3XTF32)
+        return tc_matmul_pack_b(pl->tc, b, s);
+    return PETB200_OK;
 }
 
 int MatmulPlan::bench_launch(cudaStream_t s) {

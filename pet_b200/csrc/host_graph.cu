@@ -1,0 +1,1135 @@
+// Host side above the operator C ABI: a graph of tensors and operators built with the reference's builder
+// vocabulary, an executor that plays the role of CodeEngine (order, fuse, plan, replay under a CUDA graph) and a
+// timing table that plays the role of PerfEngine (memoised per-operator milliseconds).  Everything here goes
+// through the functions declared in include/petb200.h; there is no other way into the kernels.
+#include "../../include/petb200_graph.h"
+#include <algorithm>
+#include <cstdarg>
+#include <cstring>
+#include <cuda_runtime.h>
+#include <map>
+#include <memory>
+#include <string>
+#include <tuple>
+#include <vector>
+
+namespace {
+
+using Dim = std::vector<int>;
+
+// OpType values follow the reference's enum names (ref: include/operator.h:19-51) for the operators that exist there.
+enum OpType { Conv, Matmul, Transpose, Pad, Slice, Concat, Split, Extend, Add, Sub, Mul, Activation, MaxPool, AvgPool,
+              Softmax, BatchNorm, Reshape, Conv3d, LayerNorm, Correction };
+
+struct Tensor {
+    Dim dims;
+    bool weight = false;
+    int outputOf = -1;           // operator id, -1 for graph inputs
+    std::vector<int> inputOf;    // consumers
+    int alias = -1;              // tensor whose storage this one shares (reshape, correction)
+    float *dev = nullptr;
+    bool owns = false;
+    bool has_data = false;
+    size_t size() const {
+        size_t n = 1;
+        for (int d : dims)
+            n *= (size_t)d;
+        return n;
+    }
+};
+
+struct Operator {
+    OpType type;
+    std::vector<int> inputs, outputs;
+    // attributes (a flat bag; which are used depends on type)
+    int ph = 0, pw = 0, sh = 1, sw = 1, dh = 1, dw = 1, act = 0, bias = -1;
+    int pad3[3] = {0, 0, 0}, stride3[3] = {1, 1, 1}, dil3[3] = {1, 1, 1};
+    int transA = 0, transB = 0;
+    petb200_transpose_desc tr{};
+    Dim begin, end;
+    int dim = 0, num = 0, axis = 0;
+    Dim sizes;
+    int kh = 0, kw = 0;
+    float eps = 1e-5f;
+    int win[4] = {0, 0, 0, 0};
+    bool fused_away = false; // absorbed into another step
+};
+
+// One executable step after fusion.
+struct Step {
+    std::string name;
+    std::vector<int> ops;      // operator ids it covers
+    petb200_plan *plan = nullptr;
+    const char *kernel = "";
+    OpType type;
+    int launches = 1;
+    bool weight_only = false;  // consumes only weights: hoisted out of the replayed sequence
+};
+
+// PerfEngine's memo tables (ref: include/perf_engine.h:15-21): argument tuple -> milliseconds.
+struct PerfEngine {
+    std::map<std::vector<int>, float> table;
+    bool check(const std::vector<int> &k) const { return table.count(k) != 0; }
+    float get(const std::vector<int> &k) const { return table.at(k); }
+    void save(const std::vector<int> &k, float ms) { table[k] = ms; }
+};
+
+} // namespace
+
+struct petb200_graph {
+    petb200_ctx *ctx = nullptr;
+    std::vector<Tensor> tensors;
+    std::vector<Operator> ops;
+    std::vector<int> outputs;
+    std::vector<Step> steps;
+    std::vector<int> hoisted; // indices of weight-only steps
+    bool compiled = false;
+    cudaGraphExec_t exec = nullptr;
+    cudaStream_t cap_stream = nullptr;
+    bool use_graph = true;
+    bool hoisted_done = false;
+    PerfEngine perf;
+    std::string err;
+
+    int fail(int status, const char *fmt, ...) {
+        char buf[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof buf, fmt, ap);
+        va_end(ap);
+        err = buf;
+        return status;
+    }
+    int pass(int rc) { // propagate an operator-ABI error text
+        if (rc)
+            err = petb200_last_error(ctx);
+        return rc;
+    }
+    bool valid_tensor(int t) const { return t >= 0 && t < (int)tensors.size(); }
+    int root(int t) const {
+        while (tensors[t].alias >= 0)
+            t = tensors[t].alias;
+        return t;
+    }
+    int new_tensor(const Dim &d, bool weight = false) {
+        Tensor t;
+        t.dims = d;
+        t.weight = weight;
+        tensors.push_back(t);
+        return (int)tensors.size() - 1;
+    }
+    int add_op(Operator &&op) {
+        int id = (int)ops.size();
+        for (int t : op.inputs)
+            tensors[t].inputOf.push_back(id);
+        for (int t : op.outputs)
+            tensors[t].outputOf = id;
+        ops.push_back(std::move(op));
+        compiled = false;
+        return id;
+    }
+    ~petb200_graph() {
+        for (auto &s : steps)
+            if (s.plan)
+                petb200_plan_destroy(s.plan);
+        for (auto &t : tensors)
+            if (t.owns && t.dev)
+                cudaFree(t.dev);
+        if (exec)
+            cudaGraphExecDestroy(exec);
+        if (cap_stream)
+            cudaStreamDestroy(cap_stream);
+    }
+
+    int run_step(Step &s, cudaStream_t st);
+    int run_all(cudaStream_t st, bool include_hoisted);
+    int compile(int flags);
+    int capture();
+};
+
+static float *dev_of(petb200_graph *g, int t) { return t < 0 ? nullptr : g->tensors[g->root(t)].dev; }
+
+int petb200_graph::run_step(Step &s, cudaStream_t st) {
+    Operator &op = ops[s.ops.front()];
+    switch (s.type) {
+    case Conv:
+        return pass(petb200_conv2d_run(s.plan, dev_of(this, op.inputs[0]), dev_of(this, op.bias), dev_of(this, ops[s.ops.back()].outputs[0]), st));
+    case Conv3d:
+        return pass(petb200_conv3d_run(s.plan, dev_of(this, op.inputs[0]), dev_of(this, op.bias), dev_of(this, ops[s.ops.back()].outputs[0]), st));
+    case Correction:
+        return pass(petb200_conv2d_correct(s.plan, dev_of(this, op.inputs[0]), dev_of(this, op.bias), dev_of(this, op.outputs[0]),
+                                           op.win[0], op.win[1], op.win[2], op.win[3], st));
+    case Matmul: {
+        const bool wb = tensors[op.inputs[1]].weight;
+        return pass(petb200_matmul_run(s.plan, dev_of(this, op.inputs[0]), wb ? nullptr : dev_of(this, op.inputs[1]), dev_of(this, op.bias),
+                                       dev_of(this, ops[s.ops.back()].outputs[0]), st));
+    }
+    case Transpose:
+    case Pad:
+    case Slice:
+    case Extend:
+        return pass(petb200_layout_run(s.plan, dev_of(this, op.inputs[0]), dev_of(this, ops[s.ops.back()].outputs[0]), st));
+    case Concat: {
+        const Tensor &o = tensors[op.outputs[0]];
+        std::vector<const void *> parts;
+        std::vector<int> ext;
+        for (int t : op.inputs) {
+            parts.push_back(dev_of(this, t));
+            ext.push_back(tensors[t].dims[op.dim]);
+        }
+        return pass(petb200_concat_run(ctx, (int)o.dims.size(), o.dims.data(), op.dim, (int)parts.size(), ext.data(), parts.data(),
+                                       dev_of(this, op.outputs[0]), st));
+    }
+    case Split: {
+        const Tensor &in = tensors[op.inputs[0]];
+        std::vector<void *> parts;
+        std::vector<int> ext;
+        for (int t : op.outputs) {
+            parts.push_back(dev_of(this, t));
+            ext.push_back(tensors[t].dims[op.dim]);
+        }
+        return pass(petb200_split_run(ctx, (int)in.dims.size(), in.dims.data(), op.dim, (int)parts.size(), ext.data(),
+                                      dev_of(this, op.inputs[0]), parts.data(), st));
+    }
+    case Add:
+    case Sub:
+    case Mul: {
+        std::vector<const float *> ins;
+        std::vector<size_t> sz;
+        for (int t : op.inputs) {
+            ins.push_back(dev_of(this, t));
+            sz.push_back(tensors[t].size());
+        }
+        const int out = ops[s.ops.back()].outputs[0];
+        const int act = s.ops.size() > 1 ? ops[s.ops.back()].act : 0;
+        return pass(petb200_eltwise_run(ctx, s.type == Add ? 0 : (s.type == Sub ? 1 : 2), (int)ins.size(), ins.data(), sz.data(),
+                                        dev_of(this, out), tensors[out].size(), act, st));
+    }
+    case Activation:
+        return pass(petb200_activation_run(ctx, dev_of(this, op.inputs[0]), dev_of(this, op.outputs[0]), tensors[op.outputs[0]].size(), op.act, st));
+    case MaxPool:
+    case AvgPool: {
+        const Dim &d = tensors[op.inputs[0]].dims;
+        return pass(petb200_pool2d_run(ctx, s.type == MaxPool ? 0 : 1, dev_of(this, op.inputs[0]), dev_of(this, op.outputs[0]), d[0], d[1], d[2],
+                                       d[3], op.kh, op.kw, op.ph, op.pw, op.sh, op.sw, st));
+    }
+    case Softmax: {
+        const Dim &d = tensors[op.inputs[0]].dims;
+        return pass(petb200_softmax_run(ctx, dev_of(this, op.inputs[0]), dev_of(this, op.outputs[0]), tensors[op.inputs[0]].size() / d.back(),
+                                        d.back(), st));
+    }
+    case LayerNorm: {
+        const Dim &d = tensors[op.inputs[0]].dims;
+        return pass(petb200_layernorm_run(ctx, dev_of(this, op.inputs[0]), dev_of(this, op.inputs.size() > 1 ? op.inputs[1] : -1),
+                                          dev_of(this, op.inputs.size() > 2 ? op.inputs[2] : -1), dev_of(this, op.outputs[0]),
+                                          tensors[op.inputs[0]].size() / d.back(), d.back(), op.eps, st));
+    }
+    case BatchNorm: {
+        const Dim &d = tensors[op.inputs[0]].dims;
+        size_t inner = 1;
+        for (size_t i = 2; i < d.size(); ++i)
+            inner *= (size_t)d[i];
+        return pass(petb200_batchnorm_run(ctx, dev_of(this, op.inputs[0]), dev_of(this, op.inputs[1]), dev_of(this, op.inputs[2]),
+                                          dev_of(this, op.inputs[3]), dev_of(this, op.inputs[4]), dev_of(this, op.outputs[0]), (size_t)d[0], d[1],
+                                          inner, op.eps, st));
+    }
+    case Reshape:
+        return PETB200_OK;
+    }
+    return PETB200_ERR_UNSUPPORTED;
+}
+
+int petb200_graph::run_all(cudaStream_t st, bool include_hoisted) {
+    for (auto &s : steps) {
+        if (s.weight_only && !include_hoisted)
+            continue;
+        int rc = run_step(s, st);
+        if (rc)
+            return rc;
+    }
+    return PETB200_OK;
+}
+
+int petb200_graph::compile(int flags) {
+    const bool fuse = !(flags & 1);
+    use_graph = !(flags & 2);
+    for (auto &s : steps)
+        if (s.plan)
+            petb200_plan_destroy(s.plan);
+    steps.clear();
+    if (exec) {
+        cudaGraphExecDestroy(exec);
+        exec = nullptr;
+    }
+    for (auto &op : ops)
+        op.fused_away = false;
+    hoisted_done = false;
+    // ---- topological order (Kahn, like SubGraph::compute) ----
+    const int n = (int)ops.size();
+    std::vector<int> cnt(n, 0), order;
+    for (int i = 0; i < n; ++i) {
+        std::vector<int> preds;
+        for (int t : ops[i].inputs)
+            if (tensors[t].outputOf >= 0)
+                preds.push_back(tensors[t].outputOf);
+        if (ops[i].bias >= 0 && tensors[ops[i].bias].outputOf >= 0)
+            preds.push_back(tensors[ops[i].bias].outputOf);
+        std::sort(preds.begin(), preds.end());
+        preds.erase(std::unique(preds.begin(), preds.end()), preds.end());
+        cnt[i] = (int)preds.size();
+        if (!cnt[i])
+            order.push_back(i);
+    }
+    for (size_t st = 0; st < order.size(); ++st) {
+        std::vector<int> succ;
+        for (int t : ops[order[st]].outputs)
+            for (int c : tensors[t].inputOf)
+                succ.push_back(c);
+        std::sort(succ.begin(), succ.end());
+        succ.erase(std::unique(succ.begin(), succ.end()), succ.end());
+        for (int c : succ)
+            if (--cnt[c] == 0)
+                order.push_back(c);
+    }
+    if ((int)order.size() != n)
+        return fail(PETB200_ERR_INVALID, "graph has a cycle");
+    if (outputs.empty())
+        for (int t = 0; t < (int)tensors.size(); ++t)
+            if (tensors[t].outputOf >= 0 && tensors[t].inputOf.empty())
+                outputs.push_back(t);
+    auto is_output = [&](int t) { return std::find(outputs.begin(), outputs.end(), t) != outputs.end(); };
+    auto sole_consumer = [&](int t) -> int { return (tensors[t].inputOf.size() == 1 && !is_output(t)) ? tensors[t].inputOf[0] : -1; };
+
+    // ---- build steps with fusion ----
+    for (int id : order) {
+        Operator &op = ops[id];
+        if (op.fused_away)
+            continue;
+        Step s;
+        s.type = op.type;
+        s.ops.push_back(id);
+        s.weight_only = true;
+        for (int t : op.inputs)
+            s.weight_only = s.weight_only && tensors[t].weight;
+        int rc = PETB200_OK;
+        switch (op.type) {
+        case Conv:
+        case Conv3d:
+        case Matmul: {
+            int act = op.act;
+            if (fuse && act == 0) { // fold a sole-consumer activation into the epilogue
+                int c = sole_consumer(op.outputs[0]);
+                if (c >= 0 && ops[c].type == Activation) {
+                    act = ops[c].act;
+                    ops[c].fused_away = true;
+                    s.ops.push_back(c);
+                }
+            }
+            const Dim &x = tensors[op.inputs[0]].dims, &w = tensors[op.inputs[1]].dims;
+            if (op.type == Conv) {
+                int a[16] = {x[0], x[1], x[2], x[3], w[0], w[2], w[3], op.ph, op.pw, op.sh, op.sw, op.dh, op.dw, x[1] / w[1], op.bias >= 0, act};
+                rc = petb200_conv2d_plan(ctx, a, PETB200_ALGO_AUTO, &s.plan);
+                s.name = "conv";
+            } else if (op.type == Conv3d) {
+                int a[21] = {x[0], x[1], x[2], x[3], x[4], w[0], w[2], w[3], w[4], op.pad3[0], op.pad3[1], op.pad3[2], op.stride3[0], op.stride3[1],
+                             op.stride3[2], op.dil3[0], op.dil3[1], op.dil3[2], x[1] / w[1], op.bias >= 0, act};
+                rc = petb200_conv3d_plan(ctx, a, PETB200_ALGO_AUTO, &s.plan);
+                s.name = "conv3d";
+            } else {
+                const Dim &o = tensors[op.outputs[0]].dims;
+                const int k = op.transA ? x[1] : x[2];
+                rc = petb200_matmul_plan(ctx, op.transA, op.transB, o[0], o[1], o[2], k, op.bias >= 0, act, PETB200_ALGO_AUTO, &s.plan);
+                s.name = "matmul";
+                s.launches = 1 + (op.transA ? 0 : 1) + (tensors[op.inputs[1]].weight ? 0 : 1);
+            }
+            s.weight_only = false;
+            break;
+        }
+        case Correction: {
+            const Dim &x = tensors[op.inputs[0]].dims, &w = tensors[op.inputs[1]].dims;
+            int a[16] = {x[0], x[1], x[2], x[3], w[0], w[2], w[3], op.ph, op.pw, op.sh, op.sw, op.dh, op.dw, x[1] / w[1], op.bias >= 0, op.act};
+            rc = petb200_conv2d_plan(ctx, a, PETB200_ALGO_AUTO, &s.plan);
+            s.name = "correction";
+            s.weight_only = false;
+            break;
+        }
+        case Transpose: {
+            std::vector<petb200_transpose_desc> chain = {op.tr};
+            int last = id;
+            while (fuse) { // extend the chain while the intermediate has a single consumer that is a transpose
+                int c = sole_consumer(ops[last].outputs[0]);
+                if (c < 0 || ops[c].type != Transpose)
+                    break;
+                chain.push_back(ops[c].tr);
+                petb200_plan *trial = nullptr;
+                const Dim &d0 = tensors[op.inputs[0]].dims;
+                if (petb200_transpose_plan(ctx, (int)d0.size(), d0.data(), (int)chain.size(), chain.data(), &trial) != PETB200_OK) {
+                    chain.pop_back(); // not expressible as one index map: leave the rest for its own step
+                    break;
+                }
+                petb200_plan_destroy(trial);
+                ops[c].fused_away = true;
+                s.ops.push_back(c);
+                last = c;
+            }
+            const Dim &d0 = tensors[op.inputs[0]].dims;
+            rc = petb200_transpose_plan(ctx, (int)d0.size(), d0.data(), (int)chain.size(), chain.data(), &s.plan);
+            s.name = chain.size() > 1 ? "transpose_chain" : "transpose";
+            break;
+        }
+        case Pad: {
+            const Dim &d = tensors[op.inputs[0]].dims;
+            rc = petb200_pad_plan(ctx, (int)d.size(), d.data(), op.begin.data(), op.end.data(), &s.plan);
+            s.name = "pad";
+            break;
+        }
+        case Slice: {
+            const Dim &d = tensors[op.inputs[0]].dims;
+            rc = petb200_slice_plan(ctx, (int)d.size(), d.data(), op.begin.data(), op.end.data(), &s.plan);
+            s.name = "slice";
+            break;
+        }
+        case Extend: {
+            const Dim &d = tensors[op.inputs[0]].dims;
+            rc = petb200_extend_plan(ctx, (int)d.size(), d.data(), op.dim, op.num, &s.plan);
+            s.name = "extend";
+            break;
+        }
+        case Concat:
+            s.name = "concat";
+            s.launches = (int)op.inputs.size();
+            break;
+        case Split:
+            s.name = "split";
+            s.launches = (int)op.outputs.size();
+            break;
+        case Add:
+        case Sub:
+        case Mul:
+            s.name = op.type == Add ? "add" : (op.type == Sub ? "sub" : "mul");
+            if (fuse) {
+                int c = sole_consumer(op.outputs[0]);
+                if (c >= 0 && ops[c].type == Activation) {
+                    ops[c].fused_away = true;
+                    s.ops.push_back(c);
+                }
+            }
+            break;
+        case Activation:
+            s.name = "activation";
+            break;
+        case MaxPool:
+            s.name = "maxpool";
+            break;
+        case AvgPool:
+            s.name = "avgpool";
+            break;
+        case Softmax:
+            s.name = "softmax";
+            break;
+        case LayerNorm:
+            s.name = "layernorm";
+            break;
+        case BatchNorm:
+            s.name = "batchnorm";
+            break;
+        case Reshape:
+            s.name = "reshape";
+            s.launches = 0;
+            break;
+        }
+        if (rc)
+            return pass(rc);
+        s.kernel = s.plan ? petb200_plan_kernel(s.plan) : (s.launches ? "eltwise" : "alias");
+        steps.push_back(s);
+    }
+    // ---- storage: one buffer per non-aliased tensor (kept across recompiles) ----
+    for (auto &t : tensors) {
+        if (t.alias >= 0 || t.dev)
+            continue;
+        if (cudaMalloc((void **)&t.dev, std::max<size_t>(t.size(), 1) * sizeof(float)) != cudaSuccess)
+            return fail(PETB200_ERR_NOMEM, "tensor allocation of %zu floats failed", t.size());
+        t.owns = true;
+    }
+    compiled = true;
+    return PETB200_OK;
+}
+
+// Work that depends on weights only, done once per set of weights and kept out of the replayed sequence (the
+// reference hoists the same operators, src/Graph/code_engine.cc:187-193): weight-only steps first, then the
+// packing of conv filters and constant matmul operands.
+static int prepare_weights(petb200_graph *g, cudaStream_t st) {
+    for (auto &s : g->steps)
+        if (s.weight_only) {
+            int rc = g->run_step(s, st);
+            if (rc)
+                return rc;
+            for (int o : s.ops)
+                for (int t : g->ops[o].outputs)
+                    g->tensors[t].has_data = true;
+        }
+    for (auto &s : g->steps) {
+        Operator &op = g->ops[s.ops.front()];
+        if (s.weight_only || op.inputs.size() < 2)
+            continue;
+        const Tensor &w = g->tensors[op.inputs[1]];
+        const bool ready = w.has_data || g->tensors[g->root(op.inputs[1])].has_data;
+        int rc = PETB200_OK;
+        if ((s.type == Conv || s.type == Correction) && ready)
+            rc = petb200_conv2d_set_weights(s.plan, dev_of(g, op.inputs[1]), st);
+        else if (s.type == Conv3d && ready)
+            rc = petb200_conv3d_set_weights(s.plan, dev_of(g, op.inputs[1]), st);
+        else if (s.type == Matmul && w.weight && ready)
+            rc = petb200_matmul_set_weights(s.plan, dev_of(g, op.inputs[1]), st);
+        if (rc)
+            return g->pass(rc);
+    }
+    return PETB200_OK;
+}
+
+int petb200_graph::capture() {
+    if (!cap_stream && cudaStreamCreateWithFlags(&cap_stream, cudaStreamNonBlocking) != cudaSuccess)
+        return fail(PETB200_ERR_CUDA, "stream creation failed");
+    // weight-only steps and weight packing run once, eagerly; one eager pass also warms every lazily built plan
+    int rc = prepare_weights(this, cap_stream);
+    if (rc)
+        return rc;
+    rc = run_all(cap_stream, false);
+    if (rc)
+        return rc;
+    if (cudaStreamSynchronize(cap_stream) != cudaSuccess)
+        return fail(PETB200_ERR_CUDA, "warm-up pass failed: %s", cudaGetErrorString(cudaGetLastError()));
+    cudaGraph_t graph = nullptr;
+    if (cudaStreamBeginCapture(cap_stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess)
+        return fail(PETB200_ERR_CUDA, "begin capture failed");
+    rc = run_all(cap_stream, false);
+    cudaError_t e = cudaStreamEndCapture(cap_stream, &graph);
+    if (rc || e != cudaSuccess) {
+        if (graph)
+            cudaGraphDestroy(graph);
+        cudaGetLastError();
+        return rc ? rc : fail(PETB200_ERR_CUDA, "end capture failed: %s", cudaGetErrorString(e));
+    }
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess)
+        return fail(PETB200_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
+    return PETB200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------------------------------------------
+#define G_CHECK_T(g, t)                                                                                      \
+    if (!(g)->valid_tensor(t))                                                                               \
+    return (g)->fail(PETB200_ERR_INVALID, "tensor id %d does not exist", (t))
+
+extern "C" int petb200_graph_create(petb200_ctx *ctx, petb200_graph **out) {
+    if (!ctx || !out)
+        return PETB200_ERR_INVALID;
+    *out = new petb200_graph();
+    (*out)->ctx = ctx;
+    return PETB200_OK;
+}
+extern "C" void petb200_graph_destroy(petb200_graph *g) { delete g; }
+extern "C" const char *petb200_graph_last_error(const petb200_graph *g) { return g ? g->err.c_str() : "null graph"; }
+
+extern "C" int petb200_graph_tensor(petb200_graph *g, int nd, const int *dims, int is_weight, int *tensor) {
+    if (!g || !dims || !tensor || nd < 0 || nd > 8)
+        return PETB200_ERR_INVALID;
+    for (int i = 0; i < nd; ++i)
+        if (dims[i] <= 0)
+            return g->fail(PETB200_ERR_INVALID, "tensor dim %d is %d", i, dims[i]);
+    *tensor = g->new_tensor(Dim(dims, dims + nd), is_weight != 0);
+    return PETB200_OK;
+}
+extern "C" int petb200_graph_tensor_dims(const petb200_graph *g, int tensor, int *dims) {
+    if (!g || !g->valid_tensor(tensor))
+        return -1;
+    const Dim &d = g->tensors[tensor].dims;
+    if (dims)
+        std::copy(d.begin(), d.end(), dims);
+    return (int)d.size();
+}
+
+static int conv_extent(int in, int k, int p, int s, int d) { return (in - (k - s) * d + 2 * p) / s; }
+
+extern "C" int petb200_graph_conv(petb200_graph *g, int x, int w, int bias, int ph, int pw, int sh, int sw, int dh, int dw,
+                                  int act, int *out) {
+    if (!g || !out)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, x);
+    G_CHECK_T(g, w);
+    const Dim &xd = g->tensors[x].dims, &wd = g->tensors[w].dims;
+    // ref: ConvOp::checkValid / compute: 4-D operands, c divisible by filter channels, f divisible by groups
+    if (xd.size() != 4 || wd.size() != 4 || wd[1] <= 0 || xd[1] % wd[1] || wd[0] % (xd[1] / wd[1]) || sh <= 0 || sw <= 0 || dh <= 0 || dw <= 0)
+        return g->fail(PETB200_ERR_INVALID, "conv: operand shapes do not form a valid convolution");
+    if (bias >= 0 && (!g->valid_tensor(bias) || (int)g->tensors[bias].size() != wd[0]))
+        return g->fail(PETB200_ERR_INVALID, "conv: bias must have one value per filter");
+    Dim od = {xd[0], wd[0], conv_extent(xd[2], wd[2], ph, sh, dh), conv_extent(xd[3], wd[3], pw, sw, dw)};
+    if (od[2] <= 0 || od[3] <= 0)
+        return g->fail(PETB200_ERR_INVALID, "conv: empty output");
+    Operator op;
+    op.type = Conv;
+    op.inputs = {x, w};
+    op.bias = bias;
+    op.ph = ph, op.pw = pw, op.sh = sh, op.sw = sw, op.dh = dh, op.dw = dw, op.act = act;
+    // ref: ConvOp::checkAndSetTensorTypeForConstructor marks the filter as a weight
+    g->tensors[w].weight = true;
+    *out = g->new_tensor(od);
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_conv3d(petb200_graph *g, int x, int w, int bias, const int pad[3], const int stride[3],
+                                    const int dil[3], int act, int *out) {
+    if (!g || !out || !pad || !stride || !dil)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, x);
+    G_CHECK_T(g, w);
+    const Dim &xd = g->tensors[x].dims, &wd = g->tensors[w].dims;
+    if (xd.size() != 5 || wd.size() != 5 || wd[1] <= 0 || xd[1] % wd[1] || wd[0] % (xd[1] / wd[1]))
+        return g->fail(PETB200_ERR_INVALID, "conv3d: operand shapes do not form a valid convolution");
+    Dim od = {xd[0], wd[0]};
+    for (int i = 0; i < 3; ++i) {
+        if (stride[i] <= 0 || dil[i] <= 0 || pad[i] < 0)
+            return g->fail(PETB200_ERR_INVALID, "conv3d: bad stride/dilation/pad");
+        od.push_back(conv_extent(xd[2 + i], wd[2 + i], pad[i], stride[i], dil[i]));
+        if (od.back() <= 0)
+            return g->fail(PETB200_ERR_INVALID, "conv3d: empty output");
+    }
+    Operator op;
+    op.type = Conv3d;
+    op.inputs = {x, w};
+    op.bias = bias;
+    op.act = act;
+    for (int i = 0; i < 3; ++i)
+        op.pad3[i] = pad[i], op.stride3[i] = stride[i], op.dil3[i] = dil[i];
+    g->tensors[w].weight = true;
+    *out = g->new_tensor(od);
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_matmul(petb200_graph *g, int a, int b, int bias, int transA, int transB, int act, int *out) {
+    if (!g || !out)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, a);
+    G_CHECK_T(g, b);
+    // ref: MatmulOp::dimExtend promotes 2-D operands to batch 1 (src/Graph/operator.cc:656-662)
+    for (int t : {a, b})
+        if (g->tensors[t].dims.size() == 2)
+            g->tensors[t].dims.insert(g->tensors[t].dims.begin(), 1);
+    const Dim &ad = g->tensors[a].dims, &bd = g->tensors[b].dims;
+    // ref: MatmulOp::checkValid (src/Graph/operator.cc:697-715)
+    if (ad.size() != 3 || bd.size() != 3 || ad[0] != bd[0] || (transA ? ad[1] : ad[2]) != (transB ? bd[2] : bd[1]))
+        return g->fail(PETB200_ERR_INVALID, "matmul: operands must be 3-D with equal batch and inner extents");
+    if (g->tensors[a].weight && g->tensors[b].weight)
+        return g->fail(PETB200_ERR_INVALID, "matmul: both operands are weights");
+    Operator op;
+    op.type = Matmul;
+    op.inputs = {a, b};
+    op.bias = bias;
+    op.transA = transA != 0, op.transB = transB != 0, op.act = act;
+    *out = g->new_tensor({ad[0], transA ? ad[2] : ad[1], transB ? bd[1] : bd[2]});
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_transpose(petb200_graph *g, int x, const petb200_transpose_desc *desc, int *out) {
+    if (!g || !desc || !out)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, x);
+    const Dim &d = g->tensors[x].dims;
+    petb200_plan *trial = nullptr; // shape inference and validation are the lowering's
+    int rc = petb200_transpose_plan(g->ctx, (int)d.size(), d.data(), 1, desc, &trial);
+    if (rc)
+        return g->pass(rc);
+    int od[16];
+    int nd = petb200_layout_out_dims(trial, od);
+    petb200_plan_destroy(trial);
+    Operator op;
+    op.type = Transpose;
+    op.inputs = {x};
+    op.tr = *desc;
+    *out = g->new_tensor(Dim(od, od + nd), g->tensors[x].weight); // ref: Graph::transpose keeps the Weight type
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+static int pad_slice(petb200_graph *g, OpType type, int x, const int *begin, const int *end, int *out) {
+    if (!g || !begin || !end || !out)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, x);
+    const Dim &d = g->tensors[x].dims;
+    Dim od(d.size());
+    for (size_t i = 0; i < d.size(); ++i) {
+        od[i] = type == Pad ? d[i] + begin[i] + end[i] : d[i] - begin[i] - end[i];
+        if (begin[i] < 0 || end[i] < 0 || od[i] <= 0)
+            return g->fail(PETB200_ERR_INVALID, "%s: window outside the tensor", type == Pad ? "pad" : "slice");
+    }
+    Operator op;
+    op.type = type;
+    op.inputs = {x};
+    op.begin.assign(begin, begin + d.size());
+    op.end.assign(end, end + d.size());
+    *out = g->new_tensor(od, g->tensors[x].weight);
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+extern "C" int petb200_graph_pad(petb200_graph *g, int x, const int *begin, const int *end, int *out) { return pad_slice(g, Pad, x, begin, end, out); }
+extern "C" int petb200_graph_slice(petb200_graph *g, int x, const int *begin, const int *end, int *out) { return pad_slice(g, Slice, x, begin, end, out); }
+
+extern "C" int petb200_graph_extend(petb200_graph *g, int x, int dim, int num, int *out) {
+    if (!g || !out)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, x);
+    Dim d = g->tensors[x].dims;
+    if (dim < 0 || dim >= (int)d.size() || num < 0)
+        return g->fail(PETB200_ERR_INVALID, "extend: bad dim/num");
+    d[dim] *= num + 1;
+    Operator op;
+    op.type = Extend;
+    op.inputs = {x};
+    op.dim = dim, op.num = num;
+    *out = g->new_tensor(d, g->tensors[x].weight);
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_concat(petb200_graph *g, int n, const int *xs, int dim, int *out) {
+    if (!g || !xs || !out || n < 1)
+        return PETB200_ERR_INVALID;
+    for (int i = 0; i < n; ++i)
+        G_CHECK_T(g, xs[i]);
+    Dim d = g->tensors[xs[0]].dims;
+    if (dim < 0 || dim >= (int)d.size())
+        return g->fail(PETB200_ERR_INVALID, "concat: bad dim");
+    bool weight = true;
+    d[dim] = 0;
+    for (int i = 0; i < n; ++i) {
+        const Dim &e = g->tensors[xs[i]].dims;
+        if (e.size() != d.size())
+            return g->fail(PETB200_ERR_INVALID, "concat: rank mismatch");
+        for (size_t j = 0; j < e.size(); ++j)
+            if ((int)j != dim && e[j] != g->tensors[xs[0]].dims[j])
+                return g->fail(PETB200_ERR_INVALID, "concat: extents differ outside the concat dim");
+        d[dim] += e[dim];
+        weight = weight && g->tensors[xs[i]].weight;
+    }
+    Operator op;
+    op.type = Concat;
+    op.inputs.assign(xs, xs + n);
+    op.dim = dim;
+    *out = g->new_tensor(d, weight);
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_split(petb200_graph *g, int x, int dim, int n, const int *sizes, int *outs) {
+    if (!g || !sizes || !outs || n < 1)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, x);
+    const Dim d = g->tensors[x].dims;
+    if (dim < 0 || dim >= (int)d.size())
+        return g->fail(PETB200_ERR_INVALID, "split: bad dim");
+    int total = 0;
+    for (int i = 0; i < n; ++i)
+        total += sizes[i];
+    // ref: SplitOp::computeShapeV — sizes are ratios scaled by dim / sum (src/Graph/operator.cc:2074-2101)
+    if (total <= 0 || d[dim] % total)
+        return g->fail(PETB200_ERR_INVALID, "split: ratios do not divide the dimension");
+    Operator op;
+    op.type = Split;
+    op.inputs = {x};
+    op.dim = dim;
+    op.sizes.assign(sizes, sizes + n);
+    for (int i = 0; i < n; ++i) {
+        Dim od = d;
+        od[dim] = d[dim] / total * sizes[i];
+        if (od[dim] <= 0)
+            return g->fail(PETB200_ERR_INVALID, "split: empty part");
+        outs[i] = g->new_tensor(od, g->tensors[x].weight);
+        op.outputs.push_back(outs[i]);
+    }
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_eltwise(petb200_graph *g, int kind, int n, const int *xs, int *out) {
+    if (!g || !xs || !out || kind < 0 || kind > 2 || n < 1 || n > 4 || (kind == 1 && n != 2))
+        return PETB200_ERR_INVALID;
+    for (int i = 0; i < n; ++i)
+        G_CHECK_T(g, xs[i]);
+    Operator op;
+    op.type = kind == 0 ? Add : (kind == 1 ? Sub : Mul);
+    op.inputs.assign(xs, xs + n);
+    *out = g->new_tensor(g->tensors[xs[0]].dims); // ref: the output takes the first operand's shape; others are read modulo their size
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_activation(petb200_graph *g, int x, int act, int *out) {
+    if (!g || !out || act < 1 || act > PETB200_ACT_GELU)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, x);
+    Operator op;
+    op.type = Activation;
+    op.inputs = {x};
+    op.act = act;
+    *out = g->new_tensor(g->tensors[x].dims);
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_pool(petb200_graph *g, int kind, int x, int kh, int kw, int ph, int pw, int sh, int sw, int *out) {
+    if (!g || !out || kind < 0 || kind > 1 || kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0 || ph < 0 || pw < 0)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, x);
+    const Dim &d = g->tensors[x].dims;
+    if (d.size() != 4)
+        return g->fail(PETB200_ERR_INVALID, "pool: input must be 4-D");
+    Dim od = {d[0], d[1], (d[2] - (kh - sh) + 2 * ph) / sh, (d[3] - (kw - sw) + 2 * pw) / sw};
+    if (od[2] <= 0 || od[3] <= 0)
+        return g->fail(PETB200_ERR_INVALID, "pool: empty output");
+    Operator op;
+    op.type = kind == 0 ? MaxPool : AvgPool;
+    op.inputs = {x};
+    op.kh = kh, op.kw = kw, op.ph = ph, op.pw = pw, op.sh = sh, op.sw = sw;
+    *out = g->new_tensor(od);
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_softmax(petb200_graph *g, int x, int axis, int *out) {
+    if (!g || !out)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, x);
+    const int nd = (int)g->tensors[x].dims.size();
+    if (axis < 0)
+        axis += nd;
+    if (axis != nd - 1) // the reference's kernel also only handles the last axis (src/Graph/code_engine.cc:1707-1731)
+        return g->fail(PETB200_ERR_UNSUPPORTED, "softmax over axis %d of %d: only the last axis is built", axis, nd);
+    Operator op;
+    op.type = Softmax;
+    op.inputs = {x};
+    op.axis = axis;
+    *out = g->new_tensor(g->tensors[x].dims);
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_layernorm(petb200_graph *g, int x, int gamma, int beta, float eps, int *out) {
+    if (!g || !out)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, x);
+    const int cols = g->tensors[x].dims.back();
+    for (int t : {gamma, beta})
+        if (t >= 0 && (!g->valid_tensor(t) || (int)g->tensors[t].size() != cols))
+            return g->fail(PETB200_ERR_INVALID, "layernorm: gamma/beta must match the last axis");
+    if ((gamma < 0) != (beta < 0))
+        return g->fail(PETB200_ERR_INVALID, "layernorm: pass both gamma and beta or neither");
+    Operator op;
+    op.type = LayerNorm;
+    op.inputs = {x};
+    if (gamma >= 0) {
+        op.inputs.push_back(gamma);
+        op.inputs.push_back(beta);
+    }
+    op.eps = eps;
+    *out = g->new_tensor(g->tensors[x].dims);
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_batchnorm(petb200_graph *g, int x, int scale, int bias, int mean, int var, float eps, int *out) {
+    if (!g || !out)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, x);
+    if (g->tensors[x].dims.size() < 2)
+        return g->fail(PETB200_ERR_INVALID, "batchnorm: input needs a channel dim");
+    const int c = g->tensors[x].dims[1];
+    for (int t : {scale, bias, mean, var})
+        if (!g->valid_tensor(t) || (int)g->tensors[t].size() != c)
+            return g->fail(PETB200_ERR_INVALID, "batchnorm: parameter tensors must have one value per channel");
+    Operator op;
+    op.type = BatchNorm;
+    op.inputs = {x, scale, bias, mean, var};
+    op.eps = eps;
+    *out = g->new_tensor(g->tensors[x].dims);
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_reshape(petb200_graph *g, int x, int nd, const int *dims, int *out) {
+    if (!g || !dims || !out || nd < 1 || nd > 8)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, x);
+    Dim d(dims, dims + nd);
+    long long known = 1;
+    int infer = -1;
+    for (int i = 0; i < nd; ++i) {
+        if (d[i] == -1) {
+            if (infer >= 0)
+                return g->fail(PETB200_ERR_INVALID, "reshape: more than one inferred dim");
+            infer = i;
+        } else if (d[i] <= 0) {
+            return g->fail(PETB200_ERR_INVALID, "reshape: bad dim");
+        } else {
+            known *= d[i];
+        }
+    }
+    const long long total = (long long)g->tensors[x].size();
+    if (infer >= 0) {
+        if (total % known)
+            return g->fail(PETB200_ERR_INVALID, "reshape: sizes do not match");
+        d[infer] = (int)(total / known);
+    } else if (known != total) {
+        return g->fail(PETB200_ERR_INVALID, "reshape: sizes do not match");
+    }
+    Operator op;
+    op.type = Reshape;
+    op.inputs = {x};
+    *out = g->new_tensor(d, g->tensors[x].weight);
+    g->tensors[*out].alias = x; // ref: reshape is pointer aliasing in the emitted program (code_engine.cc:1681-1690)
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_correction(petb200_graph *g, int x, int w, int bias, int y, int ph, int pw, int sh, int sw, int dh,
+                                        int dw, int act, int oh0, int ohn, int ow0, int own, int *out) {
+    if (!g || !out)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, x);
+    G_CHECK_T(g, w);
+    G_CHECK_T(g, y);
+    const Dim &xd = g->tensors[x].dims, &wd = g->tensors[w].dims, &yd = g->tensors[y].dims;
+    if (xd.size() != 4 || wd.size() != 4 || yd.size() != 4 || wd[1] <= 0 || xd[1] % wd[1])
+        return g->fail(PETB200_ERR_INVALID, "correction: operands must be 4-D conv operands");
+    Dim od = {xd[0], wd[0], conv_extent(xd[2], wd[2], ph, sh, dh), conv_extent(xd[3], wd[3], pw, sw, dw)};
+    if (od != yd)
+        return g->fail(PETB200_ERR_INVALID, "correction: y does not have the shape of the original convolution's output");
+    if (oh0 < 0 || ohn <= 0 || oh0 + ohn > od[2] || ow0 < 0 || own <= 0 || ow0 + own > od[3])
+        return g->fail(PETB200_ERR_INVALID, "correction: window outside the output");
+    Operator op;
+    op.type = Correction;
+    op.inputs = {x, w, y};
+    op.bias = bias;
+    op.ph = ph, op.pw = pw, op.sh = sh, op.sw = sw, op.dh = dh, op.dw = dw, op.act = act;
+    op.win[0] = oh0, op.win[1] = ohn, op.win[2] = ow0, op.win[3] = own;
+    g->tensors[w].weight = true;
+    *out = g->new_tensor(od);
+    g->tensors[*out].alias = y; // corrected in place
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_set_outputs(petb200_graph *g, int n, const int *tensors) {
+    if (!g || (n > 0 && !tensors))
+        return PETB200_ERR_INVALID;
+    for (int i = 0; i < n; ++i)
+        G_CHECK_T(g, tensors[i]);
+    g->outputs.assign(tensors, tensors + n);
+    g->compiled = false;
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_compile(petb200_graph *g, int flags) {
+    if (!g)
+        return PETB200_ERR_INVALID;
+    return g->compile(flags);
+}
+
+extern "C" int petb200_graph_set_data(petb200_graph *g, int tensor, const float *host, size_t n, petb200_stream stream) {
+    if (!g || !host)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, tensor);
+    if (!g->compiled)
+        return g->fail(PETB200_ERR_INVALID, "set_data before compile");
+    Tensor &t = g->tensors[tensor];
+    if (n != t.size())
+        return g->fail(PETB200_ERR_INVALID, "set_data: tensor holds %zu floats, %zu given", t.size(), n);
+    if (cudaMemcpyAsync(dev_of(g, tensor), host, n * sizeof(float), cudaMemcpyHostToDevice, (cudaStream_t)stream) != cudaSuccess)
+        return g->fail(PETB200_ERR_CUDA, "set_data: copy failed");
+    t.has_data = true;
+    if (t.weight) { // packed copies of this weight are stale: redo the hoisted work on next run
+        if (g->exec)
+            cudaGraphExecDestroy(g->exec);
+        g->exec = nullptr;
+        g->hoisted_done = false;
+    }
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_get_data(petb200_graph *g, int tensor, float *host, size_t n, petb200_stream stream) {
+    if (!g || !host)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, tensor);
+    if (!g->compiled || n != g->tensors[tensor].size())
+        return g->fail(PETB200_ERR_INVALID, "get_data: not compiled or size mismatch");
+    if (cudaMemcpyAsync(host, dev_of(g, tensor), n * sizeof(float), cudaMemcpyDeviceToHost, (cudaStream_t)stream) != cudaSuccess ||
+        cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess)
+        return g->fail(PETB200_ERR_CUDA, "get_data: copy failed");
+    return PETB200_OK;
+}
+
+extern "C" void *petb200_graph_device_ptr(petb200_graph *g, int tensor) {
+    return (g && g->valid_tensor(tensor) && g->compiled) ? dev_of(g, tensor) : nullptr;
+}
+
+extern "C" int petb200_graph_run(petb200_graph *g, petb200_stream stream) {
+    if (!g)
+        return PETB200_ERR_INVALID;
+    if (!g->compiled)
+        return g->fail(PETB200_ERR_INVALID, "run before compile");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!g->use_graph) {
+        if (!g->hoisted_done) { // first run after (re)loading weights: hoisted work
+            int rc = prepare_weights(g, st);
+            if (rc)
+                return rc;
+            rc = g->run_all(st, false);
+            g->hoisted_done = true;
+            return rc;
+        }
+        return g->run_all(st, false);
+    }
+    if (!g->exec) {
+        cudaStreamSynchronize(st); // inputs copied on the caller's stream must have landed before the capture pass
+        int rc = g->capture();
+        if (rc)
+            return rc;
+        return PETB200_OK; // the eager pass inside capture() already produced this run's outputs
+    }
+    if (cudaGraphLaunch(g->exec, st) != cudaSuccess)
+        return g->fail(PETB200_ERR_CUDA, "graph launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_num_launches(const petb200_graph *g) {
+    int n = 0;
+    if (g)
+        for (auto &s : g->steps)
+            if (!s.weight_only)
+                n += s.launches;
+    return n;
+}
+extern "C" int petb200_graph_num_steps(const petb200_graph *g) { return g ? (int)g->steps.size() : 0; }
+extern "C" const char *petb200_graph_step_name(const petb200_graph *g, int i) {
+    return (g && i >= 0 && i < (int)g->steps.size()) ? g->steps[i].name.c_str() : "";
+}
+extern "C" const char *petb200_graph_step_kernel(const petb200_graph *g, int i) {
+    return (g && i >= 0 && i < (int)g->steps.size()) ? g->steps[i].kernel : "";
+}
+
+extern "C" int petb200_graph_perf(petb200_graph *g, int rounds, int warmup, float *total_ms, float *per_step_ms) {
+    if (!g || !total_ms || rounds <= 0)
+        return PETB200_ERR_INVALID;
+    if (!g->compiled)
+        return g->fail(PETB200_ERR_INVALID, "perf before compile");
+    float total = 0.f;
+    for (size_t i = 0; i < g->steps.size(); ++i) {
+        Step &s = g->steps[i];
+        float ms = 0.f;
+        if (s.weight_only) {
+            ms = 0.f; // ref: TransposeOp::perf returns 0 for weight inputs (src/Graph/operator.cc:2384-2386)
+        } else if (s.plan) {
+            // memo key: step type + every shape/attribute that determines the plan
+            std::vector<int> key = {(int)s.type, (int)s.ops.size()};
+            for (int o : s.ops) {
+                const Operator &op = g->ops[o];
+                for (int t : op.inputs)
+                    key.insert(key.end(), g->tensors[t].dims.begin(), g->tensors[t].dims.end());
+                int attrs[] = {op.ph, op.pw, op.sh, op.sw, op.dh, op.dw, op.act, op.bias >= 0, op.transA, op.transB, op.dim, op.num,
+                               op.tr.split, op.tr.factor, op.tr.ngroups, op.win[0], op.win[1], op.win[2], op.win[3]};
+                key.insert(key.end(), attrs, attrs + sizeof attrs / sizeof attrs[0]);
+                key.insert(key.end(), op.tr.flat, op.tr.flat + 8);
+                key.insert(key.end(), op.tr.group_sizes, op.tr.group_sizes + 8);
+                key.insert(key.end(), op.pad3, op.pad3 + 3);
+                key.insert(key.end(), op.stride3, op.stride3 + 3);
+                key.insert(key.end(), op.begin.begin(), op.begin.end());
+                key.insert(key.end(), op.end.begin(), op.end.end());
+            }
+            if (g->perf.check(key)) {
+                ms = g->perf.get(key);
+            } else {
+                int rc = petb200_plan_time(s.plan, rounds, warmup, &ms, nullptr);
+                if (rc == PETB200_ERR_UNSUPPORTED)
+                    ms = 1e30f; // ref: unsupported algorithms cost INFINITY (src/Graph/operator.cc:428-433)
+                else if (rc)
+                    return g->pass(rc);
+                g->perf.save(key, ms);
+            }
+        } else if (s.launches > 0) {
+            // plan-less steps (elementwise, pooling, softmax, norms, concat/split) are timed in place on the graph's tensors
+            cudaEvent_t e0, e1;
+            cudaEventCreate(&e0);
+            cudaEventCreate(&e1);
+            for (int r = 0; r < std::max(1, warmup); ++r)
+                g->run_step(s, nullptr);
+            cudaEventRecord(e0, nullptr);
+            for (int r = 0; r < rounds; ++r) {
+                int rc = g->run_step(s, nullptr);
+                if (rc)
+                    return rc;
+            }
+            cudaEventRecord(e1, nullptr);
+            cudaEventSynchronize(e1);
+            cudaEventElapsedTime(&ms, e0, e1);
+            ms /= (float)rounds;
+            cudaEventDestroy(e0);
+            cudaEventDestroy(e1);
+        }
+        if (per_step_ms)
+            per_step_ms[i] = ms;
+        total += ms;
+    }
+    *total_ms = total;
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_time(petb200_graph *g, int rounds, int warmup, float *ms, petb200_stream stream) {
+    if (!g || !ms || rounds <= 0 || warmup < 0)
+        return PETB200_ERR_INVALID;
+    cudaStream_t st = (cudaStream_t)stream;
+    for (int i = 0; i < warmup + 1; ++i) {
+        int rc = petb200_graph_run(g, stream);
+        if (rc)
+            return rc;
+    }
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    cudaEventRecord(e0, st);
+    for (int i = 0; i < rounds; ++i) {
+        int rc = petb200_graph_run(g, stream);
+        if (rc) {
+            cudaEventDestroy(e0);
+            cudaEventDestroy(e1);
+            return rc;
+        }
+    }
+    cudaEventRecord(e1, st);
+    cudaEventSynchronize(e1);
+    float total = 0.f;
+    cudaEventElapsedTime(&total, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    *ms = total / (float)rounds;
+    return petb200_check_device_status(g->ctx, stream);
+}

@@ -799,10 +799,18 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     if (core.koff.alloc(koff.size() * 4) != cudaSuccess)
         return fail(ctx, PETB200_ERR_NOMEM, "koff allocation failed");
     PETB200_CUDA(ctx, cudaMemcpy(core.koff.p, koff.data(), koff.size() * 4, cudaMemcpyHostToDevice));
-    cudaError_t e = core.a_tmem ? cudaFuncSetAttribute(k_igemm<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)core.smem)
-                                : cudaFuncSetAttribute(k_igemm<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)core.smem);
-    if (e != cudaSuccess)
-        return fail(ctx, PETB200_ERR_CUDA, "cudaFuncSetAttribute(%zu bytes) failed: %s", core.smem, cudaGetErrorString(e));
+    // The attribute is per function, not per launch: raise it once to the device limit so that plans with different
+    // shared-memory needs can coexist.
+    static bool attr_set = false;
+    if (!attr_set) {
+        const int lim = (int)std::min<size_t>(ctx->smem_optin, 227 * 1024);
+        cudaError_t e1 = cudaFuncSetAttribute(k_igemm<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        cudaError_t e2 = cudaFuncSetAttribute(k_igemm<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        if (e1 != cudaSuccess || e2 != cudaSuccess)
+            return fail(ctx, PETB200_ERR_CUDA, "cudaFuncSetAttribute(%d bytes) failed: %s", lim,
+                        cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+        attr_set = true;
+    }
     return PETB200_OK;
 }
 

@@ -41,6 +41,7 @@ SYMBOLS = {
     "petb200_conv3d_set_weights": (_i, [_vp, _vp, _vp]),
     "petb200_conv3d_run": (_i, [_vp, _vp, _vp, _vp, _vp]),
     "petb200_matmul_plan": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, C.POINTER(_vp)]),
+    "petb200_matmul_set_weights": (_i, [_vp, _vp, _vp]),
     "petb200_matmul_run": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "petb200_transpose_plan": (_i, [_vp, _i, _ip, _i, C.POINTER(TransposeDesc), C.POINTER(_vp)]),
     "petb200_pad_plan": (_i, [_vp, _i, _ip, _ip, _ip, C.POINTER(_vp)]),

@@ -1,0 +1,122 @@
+"""GPU: the graph layer (builder, fusion, CUDA-graph replay, per-operator timing) on the benchmark configurations,
+checked against the CPU oracle evaluating the same configuration description."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_err, scale_err
+
+pytestmark = pytest.mark.gpu
+TOL, TOL_SCALE = 1e-3, 2e-4
+
+
+def run_config(ctx, build, *args, fuse=True, cuda_graph=True, **kw):
+    from pet_b200 import configs
+    from pet_b200.graph import Graph
+    g = Graph(ctx)
+    b = configs.GraphBuilder(g)
+    out = build(b, *args, **kw)
+    g.setOutputs([out])
+    g.compile(fuse=fuse, cuda_graph=cuda_graph)
+    b.load()
+    g.run()
+    g.run()  # second pass replays the captured CUDA graph
+    torch.cuda.synchronize()
+    ctx.sync_check()
+    return g, out, g.get_data(out)
+
+
+def oracle_config(build, *args, **kw):
+    from oracle_backend import OracleBuilder
+    return build(OracleBuilder(), *args, **kw)
+
+
+def test_c1_rewrite_with_correction_is_bit_identical_to_original(ctx):
+    from pet_b200 import configs
+    x, w = configs.c1_tensors()
+    _, _, y0 = run_config(ctx, configs.c1_original, x, w)
+    g, _, y1 = run_config(ctx, configs.c1_rewrite, x, w, correct=True)
+    assert np.array_equal(y0, y1)
+    _, _, y2 = run_config(ctx, configs.c1_rewrite, x, w, correct=False)
+    bad = np.unique(np.nonzero(y0 != y2)[2])
+    assert list(bad) == [27, 28]
+    names = [n for n, _ in g.steps()]
+    assert names == ["transpose", "conv", "transpose", "correction"]
+    want = oracle_config(configs.c1_original, x, w)
+    assert rel_err(y0, want) <= TOL and scale_err(y0, want) <= TOL_SCALE
+
+
+def test_c2_rewrite_fuses_chains_and_matches_original(ctx):
+    from pet_b200 import configs
+    x, w = configs.c2_tensors(c=64, hw=32, k=96)
+    _, _, y0 = run_config(ctx, configs.c2_original, x, w)
+    g, _, y1 = run_config(ctx, configs.c2_rewrite, x, w)
+    assert [n for n, _ in g.steps()] == ["transpose_chain", "conv", "transpose_chain"]
+    assert g.num_launches() == 3
+    assert np.array_equal(y0, y1)
+    _, _, y2 = run_config(ctx, configs.c2_rewrite, x, w, fuse=False, cuda_graph=False)
+    assert np.array_equal(y1, y2)  # 9 kernels op by op give the same bits as 3 fused ones
+    want = oracle_config(configs.c2_rewrite, x, w)
+    assert rel_err(y1, want) <= TOL and scale_err(y1, want) <= TOL_SCALE
+
+
+def test_resnet18_reduced(ctx):
+    from pet_b200 import configs
+    kw = dict(batch=2, size=64, classes=40, width=16)
+    g, _, y = run_config(ctx, configs.resnet18, **kw)
+    want = oracle_config(configs.resnet18, **kw)
+    assert y.shape == want.shape == (1, 2, 40)
+    assert rel_err(y, want) <= TOL
+    names = [n for n, _ in g.steps()]
+    assert "activation" not in names  # every relu was folded into a conv or an add
+    assert names.count("conv") == 20 and names.count("add") == 8
+
+
+def test_bert_reduced(ctx):
+    from pet_b200 import configs
+    kw = dict(layers=2, seq=32, hidden=64, heads=4, ffn=128)
+    _, _, y = run_config(ctx, configs.bert_encoder, **kw)
+    want = oracle_config(configs.bert_encoder, **kw)
+    assert y.shape == want.shape == (1, 32, 64)
+    assert rel_err(y, want) <= TOL
+
+
+def test_r3d18_reduced(ctx):
+    from pet_b200 import configs
+    kw = dict(batch=1, frames=4, size=32, classes=10, width=8)
+    _, _, y = run_config(ctx, configs.r3d18, **kw)
+    want = oracle_config(configs.r3d18, **kw)
+    assert y.shape == want.shape == (1, 1, 10)
+    assert rel_err(y, want) <= TOL
+
+
+def test_perf_and_time_entry_points(ctx):
+    from pet_b200 import configs
+    x, w = configs.c2_tensors(c=64, hw=32, k=64)
+    g, _, _ = run_config(ctx, configs.c2_rewrite, x, w)
+    total, per = g.perf(rounds=20, warmup=5)
+    assert len(per) == 3 and all(p > 0 for p in per) and abs(total - sum(per)) < 1e-4
+    total2, per2 = g.perf(rounds=20, warmup=5)
+    assert per2 == per  # second call is served from the memo table
+    ms = g.time(rounds=50, warmup=10)
+    assert 0 < ms < 10
+    ctx.sync_check()
+
+
+def test_graph_rejects_invalid_operators(ctx):
+    from pet_b200 import PetError
+    from pet_b200.graph import Graph
+    g = Graph(ctx)
+    x = g.tensor([1, 6, 8, 8])
+    with pytest.raises(PetError):
+        g.conv(x, g.tensor([4, 4, 3, 3]), 1, 1)         # channels not divisible
+    with pytest.raises(PetError):
+        g.matmul(g.tensor([2, 4, 5]), g.tensor([3, 5, 6]))  # batch mismatch
+    with pytest.raises(PetError):
+        g.transpose(x, 1, [0, 1, -1, 2, 3], 4)          # 6 % 4 != 0
+    with pytest.raises(PetError):
+        g.reshape(x, [5, -1])
+    with pytest.raises(PetError):
+        g.softmax(x, 1)                                  # only the last axis is built
+    with pytest.raises(PetError):
+        g.run()                                          # not compiled
