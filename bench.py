@@ -108,6 +108,37 @@ def cpu_reference_sample(filters, threads_note=True):
                              "throughput scaled linearly by channels"}
 
 
+def config_latencies(ctx):
+    """Batch-1 latency (ms) of every benchmark configuration through the graph layer: CUDA-graph replay of the whole
+    graph, 20 warm-up + 200 timed passes between two CUDA events (the reference program's protocol; buffers are reused
+    between passes, so small graphs run L2-warm exactly as they do in the reference's generated program)."""
+    import torch
+    from pet_b200 import configs
+    from pet_b200.graph import Graph
+    out = {}
+
+    def run(name, build, *a, **kw):
+        g = Graph(ctx)
+        b = configs.GraphBuilder(g)
+        g.setOutputs([build(b, *a, **kw)])
+        g.compile()
+        b.load()
+        g.run()
+        torch.cuda.synchronize()
+        out[name] = {"ms": g.time(rounds=200, warmup=20), "kernels": g.num_launches()}
+
+    x, w = configs.c1_tensors()
+    run("c1_conv3x3_original", configs.c1_original, x, w)
+    run("c1_conv3x3_h2n_rewrite_corrected", configs.c1_rewrite, x, w)
+    x, w = configs.c2_tensors()
+    run("c2_dilated_original", configs.c2_original, x, w)
+    run("c2_dilated_space_to_batch_rewrite", configs.c2_rewrite, x, w)
+    run("c3_resnet18", configs.resnet18)
+    run("c4_bert_base_seq128", configs.bert_encoder)
+    run("c5_r3d18", configs.r3d18)
+    return out
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
@@ -132,6 +163,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=40)
     ap.add_argument("--impl", default="petb200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-config-latencies", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -266,6 +298,8 @@ def main():
                              "frac": achieved / peak, "traffic": None, "peak_source": f"{pk_kind} bf16 sustained",
                              "launch_ms": conv_ms, "issued_tf32_tflops": 3 * achieved, "tf32_peak_est": peak / 2,
                              "frac_of_tf32_issue_peak": 3 * achieved / (peak / 2)}}
+        if world == 1 and not args.no_config_latencies:
+            line["batch1_latency_ms"] = config_latencies(ctx)
         if not args.no_cpu_baseline:
             try:
                 _, line["cpu_baseline"] = cpu_reference_sample(8)

@@ -101,10 +101,10 @@ __global__ void __launch_bounds__(256) k_repitch(const float *__restrict__ x, fl
     }
 }
 
-// [b][m][k] -> [b][k][m]
-__global__ void __launch_bounds__(256) k_transpose_a(const float *__restrict__ a, float *__restrict__ at, int bs, int m, int k) {
+// [b][m][k] -> [b][k][mp]  (row pitch mp >= m, padding columns zero)
+__global__ void __launch_bounds__(256) k_transpose_a(const float *__restrict__ a, float *__restrict__ at, int bs, int m, int k, int mp) {
     __shared__ float tile[32][33];
-    const int tiles_k = (k + 31) / 32, tiles_m = (m + 31) / 32;
+    const int tiles_k = (k + 31) / 32, tiles_m = (mp + 31) / 32;
     const long long ntiles = (long long)bs * tiles_k * tiles_m;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
@@ -118,8 +118,8 @@ __global__ void __launch_bounds__(256) k_transpose_a(const float *__restrict__ a
         __syncthreads();
         for (int r = ty; r < 32; r += 8) {
             const int kk = tk * 32 + r, mm = tm * 32 + tx;
-            if (kk < k && mm < m)
-                at[((long long)bb * k + kk) * m + mm] = tile[tx][r];
+            if (kk < k && mm < mp)
+                at[((long long)bb * k + kk) * mp + mm] = tile[tx][r];
         }
         __syncthreads();
     }
@@ -332,14 +332,13 @@ int make_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int
     int rc = PETB200_ERR_UNSUPPORTED;
     if (algo == PETB200_ALGO_AUTO || algo == PETB200_ALGO_TC_3XTF32) {
         size_t bytes = 0;
-        rc = (m % 4 == 0) ? tc_matmul_create(ctx, b, m, n, k, pl->transB, has_bias, act, &pl->tc, &bytes)
-                          : fail(ctx, PETB200_ERR_UNSUPPORTED, "tensor-core matmul needs m %% 4 == 0");
+        rc = tc_matmul_create(ctx, b, m, n, k, pl->transB, has_bias, act, &pl->tc, &bytes);
         if (rc == PETB200_OK) {
             pl->algo = PETB200_ALGO_TC_3XTF32;
-            pl->kernel = "tc_3xtf32_ss";
+            pl->kernel = "tc_3xtf32_ts";
             pl->device_bytes = bytes;
-            if (!pl->transA) {
-                if (pl->at.alloc((size_t)b * m * k * 4) != cudaSuccess) {
+            if (!pl->transA || m % 4 != 0) {
+                if (pl->at.alloc((size_t)b * ((m + 3) / 4 * 4) * k * 4) != cudaSuccess) {
                     delete pl;
                     return fail(ctx, PETB200_ERR_NOMEM, "A re-layout scratch allocation failed");
                 }
@@ -377,10 +376,18 @@ int matmul_run(petb200_plan *plan, const float *a, const float *b, const float *
         if (rc)
             return rc;
         const float *at = a;
+        const int mp = (pl->m + 3) / 4 * 4;
         if (!pl->transA) {
-            long long tiles = (long long)pl->bs * ((pl->k + 31) / 32) * ((pl->m + 31) / 32);
-            k_transpose_a<<<(int)std::min<long long>(tiles, (long long)ctx->sm_count * 8), 256, 0, s>>>(a, (float *)pl->at.p, pl->bs, pl->m, pl->k);
+            long long tiles = (long long)pl->bs * ((pl->k + 31) / 32) * ((mp + 31) / 32);
+            k_transpose_a<<<(int)std::min<long long>(tiles, (long long)ctx->sm_count * 8), 256, 0, s>>>(a, (float *)pl->at.p, pl->bs, pl->m, pl->k, mp);
             rc = launched(ctx, "k_transpose_a");
+            if (rc)
+                return rc;
+            at = (const float *)pl->at.p;
+        } else if (mp != pl->m) {
+            long long rows = (long long)pl->bs * pl->k;
+            k_repitch<<<grid_for(ctx, rows * mp, 256), 256, 0, s>>>(a, (float *)pl->at.p, rows, pl->m, mp);
+            rc = launched(ctx, "k_repitch");
             if (rc)
                 return rc;
             at = (const float *)pl->at.p;

@@ -35,9 +35,9 @@ constexpr int kThreads = 224;
 constexpr int kMaxNB = 6;
 
 struct IgemmParams {
-    int M_total, Pw;        // pixels in the whole problem (per image-batch z when z_is_batch); pixels per image
+    int Pw, units;          // pixels of one output plane (one image, one depth slice); number of such planes
     int OD, OH, OW;         // full output extents (for addressing y)
-    int ohn, own, oh0, ow0; // output window actually computed (ohn*own*OD = Pw)
+    int ohn, own, oh0, ow0; // output window actually computed (ohn*own = Pw)
     int sd, sh, sw, pd, ph, pw;
     int x0;                 // box origin along W (multiple of 4, may be negative)
     int RN, RD, RH, RW, BC; // raw box extents
@@ -45,7 +45,9 @@ struct IgemmParams {
     int cpg, Fg, BN;        // channels per group, filters per group, tile N
     int z_is_batch;         // blockIdx.z: 0 = conv group, 1 = matmul batch
     int wide, row_tiles;    // wide mode: a tile is 128 consecutive pixels of ONE output row (rows wider than a tile)
-    int tpi, ipt, images;   // otherwise: tiles per image (image larger than a tile) or whole images per tile
+    int tpi, ipt;           // otherwise: tiles per plane (plane larger than a tile) or whole planes per tile
+    int ksplit;             // K is split over this many CTAs (partial sums go to scratch, reduced by a second kernel)
+    long long part_stride;  // floats between the partial-sum copies
     int NA, NB;             // ring depths
     int raw_bytes;          // bytes of one raw buffer (128-aligned)
     long long ys_n, ys_f, ys_p;
@@ -53,6 +55,7 @@ struct IgemmParams {
     const int *koff;
     const float *bias;
     float *y;
+    float *partial;
     int *status;
     long long *prof; // optional per-CTA cycle counters (8 per CTA), for tuning only
 };
@@ -76,23 +79,15 @@ __host__ __device__ inline SmemLayout smem_layout(const IgemmParams &P, bool a_t
     return L;
 }
 
-// Which depth slices / rows of an image the pixels [q_lo, q_hi] of that image touch (everything when the tile
-// holds several whole images); shared by the raw producer, the transform threads and the host-side box sizing.
-__host__ __device__ inline void tile_span(const IgemmParams &P, int q_lo, int q_hi, bool whole, int &zl_lo, int &zl_hi,
-                                          int &yl_lo, int &yl_hi) {
-    const int plane = P.ohn * P.own;
-    zl_lo = 0;
-    zl_hi = P.OD - 1;
+// Which rows of an output plane the pixels [q_lo, q_hi] of that plane touch (all of them when a tile holds several
+// whole planes); shared by the raw producer, the transform threads and the host-side box sizing.
+__host__ __device__ inline void tile_rows(const IgemmParams &P, int q_lo, int q_hi, bool whole, int &yl_lo, int &yl_hi) {
     yl_lo = 0;
     yl_hi = P.ohn - 1;
     if (whole)
         return;
-    zl_lo = q_lo / plane;
-    zl_hi = q_hi / plane;
-    if (zl_lo != zl_hi)
-        return;
-    yl_lo = (q_lo - zl_lo * plane) / P.own;
-    yl_hi = (q_hi - zl_hi * plane) / P.own;
+    yl_lo = q_lo / P.own;
+    yl_hi = q_hi / P.own;
 }
 
 template <int ACT> __device__ __forceinline__ float act_fn(float v) {
@@ -168,9 +163,9 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     volatile int *abort_flag = reinterpret_cast<volatile int *>(acc_full + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ntile = blockIdx.y;
+    const int ntile = blockIdx.y / P.ksplit;
+    const int ksp = blockIdx.y - ntile * P.ksplit;
     const int zb = blockIdx.z;
-    const int KS = P.nchunks * P.spc;
     const uint32_t b_half = (uint32_t)P.BN * 128u;
     const uint32_t tmem_cols = A_TMEM ? 512u : (P.BN <= 32 ? 32u : (P.BN <= 64 ? 64u : (P.BN <= 128 ? 128u : 256u)));
 
@@ -206,7 +201,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     const uint32_t tmem_base = *tmem_slot;
 
     // Tile origin in the input: first image, depth slice, row and (16-byte aligned) column of the raw box.
-    int n_lo = 0, q0 = 0, z_start, y_start, x_start, w_zl = 0, w_yl = 0, w_tx = 0;
+    int n_lo = 0, q0 = 0, unit0 = 0, z_start, y_start, x_start, w_zl = 0, w_yl = 0, w_tx = 0;
     if (P.wide) {
         const int row = blockIdx.x / P.row_tiles;
         w_tx = blockIdx.x - row * P.row_tiles;
@@ -218,15 +213,19 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         const int xs = (P.ow0 + w_tx * kTileM) * P.sw - P.pw;
         x_start = (xs >= 0) ? (xs & ~3) : -(((-xs) + 3) & ~3);
     } else {
-        const int tn = blockIdx.x / P.tpi;
-        q0 = (blockIdx.x - tn * P.tpi) * kTileM;
-        n_lo = tn * P.ipt;
-        int zl_lo, zl_hi, yl_lo, yl_hi;
-        tile_span(P, q0, min(q0 + kTileM, P.Pw) - 1, P.ipt > 1, zl_lo, zl_hi, yl_lo, yl_hi);
-        z_start = zl_lo * P.sd - P.pd;
+        const int tu = blockIdx.x / P.tpi;
+        q0 = (blockIdx.x - tu * P.tpi) * kTileM;
+        unit0 = tu * P.ipt;
+        n_lo = unit0 / P.OD;
+        int yl_lo, yl_hi;
+        tile_rows(P, q0, min(q0 + kTileM, P.Pw) - 1, P.ipt > 1, yl_lo, yl_hi);
+        z_start = (unit0 - n_lo * P.OD) * P.sd - P.pd;
         y_start = (P.oh0 + yl_lo) * P.sh - P.ph;
         x_start = P.x0;
     }
+    // split-K: this CTA reduces the channel chunks [c0, c1)
+    const int c0 = (int)((long long)ksp * P.nchunks / P.ksplit), c1 = (int)((long long)(ksp + 1) * P.nchunks / P.ksplit);
+    const int KS = (c1 - c0) * P.spc;
 
     if (warp == 0) {
         // ---------------- packed-weight producer (one thread) ----------------
@@ -239,8 +238,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                     break;
                 uint8_t *dst = sB + (size_t)sb * 2 * b_half;
                 ptx::mbar_expect_tx(b_full + sb, 2u * b_half);
-                ptx::tma_load_2d(dst, &tmap_bhi, b_full + sb, ks * kStageK, row0);
-                ptx::tma_load_2d(dst + b_half, &tmap_blo, b_full + sb, ks * kStageK, row0);
+                ptx::tma_load_2d(dst, &tmap_bhi, b_full + sb, (c0 * P.spc + ks) * kStageK, row0);
+                ptx::tma_load_2d(dst + b_half, &tmap_blo, b_full + sb, (c0 * P.spc + ks) * kStageK, row0);
                 if (++sb == P.NB) {
                     sb = 0;
                     pb ^= 1u;
@@ -253,13 +252,13 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             const int c_base = P.z_is_batch ? 0 : zb * P.cpg;
             const int n_start = P.z_is_batch ? zb : n_lo;
             const uint32_t bytes = (uint32_t)P.RN * P.BC * P.RD * P.RH * P.RW * 4u;
-            for (int ch = 0; ch < P.nchunks; ++ch) {
+            for (int ch = 0; ch < c1 - c0; ++ch) {
                 const int rb = ch & 1;
                 if (!ptx::mbar_wait(raw_empty + rb, (uint32_t)(((ch >> 1) & 1) ^ 1), abort_flag))
                     break;
                 ptx::mbar_expect_tx(raw_full + rb, bytes);
                 ptx::tma_load_5d(sRaw + (size_t)rb * P.raw_bytes, &tmap_x, raw_full + rb, x_start, y_start, z_start,
-                                 c_base + ch * P.BC, n_start);
+                                 c_base + (c0 + ch) * P.BC, n_start);
             }
         }
     } else if (warp == 1) {
@@ -370,17 +369,16 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 y_off = img * P.ys_n + ((long long)(w_zl * P.OH + oh) * P.OW + ow) * P.ys_p;
             }
         } else {
-            int nl = 0, q = q0 + p;
+            int ul = 0, q = q0 + p;
             if (P.ipt > 1) {
-                nl = p / P.Pw;
-                q = p - nl * P.Pw;
+                ul = p / P.Pw;
+                q = p - ul * P.Pw;
             }
-            const int n = n_lo + nl;
-            valid = (nl < P.ipt) && (n < P.images) && (q < P.Pw);
+            const int unit = unit0 + ul;
+            valid = (ul < P.ipt) && (unit < P.units) && (q < P.Pw);
             if (valid) {
-                const int plane = P.ohn * P.own;
-                const int zl = q / plane;
-                q -= zl * plane;
+                const int n = unit / P.OD;
+                const int zl = unit - n * P.OD;
                 const int yl = q / P.own;
                 const int xl = q - yl * P.own;
                 const int oh = P.oh0 + yl, ow = P.ow0 + xl;
@@ -395,7 +393,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         const long long t_begin = P.prof ? clock64() : 0;
         int sa = 0;
         uint32_t pa = 1; // first pass over the ring: every slot is free
-        for (int ch = 0; ch < P.nchunks && alive; ++ch) {
+        for (int ch = 0; ch < c1 - c0 && alive; ++ch) {
             const int rb = ch & 1;
             const long long cr0 = P.prof ? clock64() : 0;
             alive = ptx::mbar_wait(raw_full + rb, (uint32_t)((ch >> 1) & 1), abort_flag);
@@ -476,12 +474,13 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             ptx::tc_fence_after();
             const int f_tile0 = ntile * P.BN;
             const long long f_glob0 = P.z_is_batch ? 0 : (long long)zb * P.Fg;
-            float *yp = P.y + y_off + f_glob0 * P.ys_f;
-            const float *bp = P.has_bias ? P.bias + f_glob0 : nullptr;
+            float *yp = (P.ksplit > 1 ? P.partial + (long long)ksp * P.part_stride : P.y) + y_off + f_glob0 * P.ys_f;
+            const float *bp = (P.has_bias && P.ksplit == 1) ? P.bias + f_glob0 : nullptr;
             const bool vec_ok = (P.ys_f == 1) && ((P.ys_p & 3) == 0) && ((P.ys_n & 3) == 0) && ((P.Fg & 3) == 0) &&
-                                ((reinterpret_cast<uintptr_t>(P.y) & 15) == 0);
+                                ((reinterpret_cast<uintptr_t>(P.y) & 15) == 0) && ((P.part_stride & 3) == 0) &&
+                                ((reinterpret_cast<uintptr_t>(P.partial) & 15) == 0);
             const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16);
-            switch (P.act) {
+            switch (P.ksplit > 1 ? PETB200_ACT_NONE : P.act) {
             case PETB200_ACT_RELU:
                 epilogue_store<PETB200_ACT_RELU>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok);
                 break;
@@ -565,6 +564,45 @@ __global__ void __launch_bounds__(256) k_pack_mm_b(const float *__restrict__ b, 
     }
 }
 
+// Split-K second pass: y = act(sum_s partial[s] + bias) over the output window, in a fixed order (deterministic).
+// Elements are enumerated so that the fastest index is contiguous in y: pixels for conv layouts (ys_p == 1), filters
+// for row-major matmul output (ys_f == 1).
+struct ReduceParams {
+    int images, F, OD, OH, OW, ohn, own, oh0, ow0, ksplit, act, f_fast;
+    long long ys_n, ys_f, ys_p, part_stride;
+};
+__global__ void __launch_bounds__(256) k_splitk_reduce(const float *__restrict__ partial, const float *__restrict__ bias,
+                                                       float *__restrict__ y, ReduceParams r) {
+    const long long pix = (long long)r.OD * r.ohn * r.own;
+    const long long total = (long long)r.images * r.F * pix;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        long long rem = i;
+        int f, n;
+        long long q;
+        if (r.f_fast) {
+            f = (int)(rem % r.F);
+            rem /= r.F;
+            q = rem % pix;
+            n = (int)(rem / pix);
+        } else {
+            q = rem % pix;
+            rem /= pix;
+            f = (int)(rem % r.F);
+            n = (int)(rem / r.F);
+        }
+        const int xl = (int)(q % r.own);
+        const int yl = (int)((q / r.own) % r.ohn);
+        const int zl = (int)(q / ((long long)r.own * r.ohn));
+        const long long off = n * r.ys_n + f * r.ys_f + ((long long)(zl * r.OH + r.oh0 + yl) * r.OW + r.ow0 + xl) * r.ys_p;
+        float acc = 0.f;
+        for (int s = 0; s < r.ksplit; ++s)
+            acc += partial[s * r.part_stride + off];
+        if (bias)
+            acc += __ldg(bias + f);
+        y[off] = apply_act(acc, r.act);
+    }
+}
+
 // -------------------------------------------------------------------------------------------------------------
 // host side
 // -------------------------------------------------------------------------------------------------------------
@@ -595,7 +633,9 @@ struct TcCore {
     int xd[5]{}; // W,H,D,C,N of the activation tensor as the kernel sees it
     long long Ktot = 0;
     int rows_b = 0;
-    DevBuf whi, wlo, koff;
+    DevBuf whi, wlo, koff, partial;
+    ReduceParams red{};
+    long long y_elems = 0;
     CUtensorMap map_x{}, map_bhi{}, map_blo{};
     const void *map_x_ptr = nullptr;
     bool weights_ready = false;
@@ -644,6 +684,7 @@ struct TcCore {
         IgemmParams p = P;
         p.bias = bias;
         p.y = y;
+        p.partial = (float *)partial.p;
         p.koff = (const int *)koff.p;
         p.status = ctx->d_status;
         p.prof = prof;
@@ -652,7 +693,14 @@ struct TcCore {
             k_igemm<true><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
         else
             k_igemm<false><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
-        return launched(ctx, "k_igemm");
+        rc = launched(ctx, "k_igemm");
+        if (rc || P.ksplit == 1)
+            return rc;
+        ReduceParams r = red;
+        const long long total = (long long)r.images * r.F * r.OD * r.ohn * r.own;
+        const int blocks = (int)std::max<long long>(1, std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 8));
+        k_splitk_reduce<<<blocks, 256, 0, s>>>((const float *)partial.p, p.has_bias ? bias : nullptr, y, r);
+        return launched(ctx, "k_splitk_reduce");
     }
 };
 
@@ -671,7 +719,7 @@ static int env_int(const char *name, int dflt) {
 // PETB200_ERR_UNSUPPORTED when the shape does not fit this kernel's constraints.
 static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int oh0, int ohn, int ow0, int own,
                         int z_is_batch, int images, long long ys_n, long long ys_f, long long ys_p, int has_bias, int act,
-                        int force_bc = 0) {
+                        int force_bc = 0, int force_ksplit = 0) {
     IgemmParams &P = core.P;
     const int cpg = g.C / g.groups, Fg = g.F / g.groups;
     if (g.Wst % 4 != 0)
@@ -683,8 +731,8 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     P.ohn = ohn;
     P.ow0 = ow0;
     P.own = own;
-    P.Pw = g.OD * ohn * own;
-    P.M_total = z_is_batch ? P.Pw : images * P.Pw;
+    P.Pw = ohn * own;
+    P.units = (z_is_batch ? 1 : images) * g.OD;
     P.sd = g.stride[0];
     P.sh = g.stride[1];
     P.sw = g.stride[2];
@@ -705,8 +753,21 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     if (BN != 32 && BN != 64 && BN != 128 && BN != 256)
         return fail(ctx, PETB200_ERR_INVALID, "PETB200_TC_BN must be 32, 64, 128 or 256");
     P.BN = BN;
-    P.images = z_is_batch ? 1 : images;
-    P.ipt = (!z_is_batch && 2 * P.Pw <= kTileM) ? kTileM / P.Pw : 1;
+    // Planes smaller than half a tile are packed several to a tile: whole images for 2-D problems, consecutive depth
+    // slices of one image (a divisor of the depth, so that no tile straddles two images) for 3-D problems.
+    P.ipt = 1;
+    if (!z_is_batch && 2 * P.Pw <= kTileM) {
+        const int cap = kTileM / P.Pw;
+        if (g.OD == 1) {
+            P.ipt = cap;
+        } else {
+            for (int d = std::min(cap, g.OD); d >= 1; --d)
+                if (g.OD % d == 0) {
+                    P.ipt = d;
+                    break;
+                }
+        }
+    }
     P.tpi = (P.Pw + kTileM - 1) / kTileM;
     P.wide = (own > kTileM) ? 1 : 0;
     P.row_tiles = (own + kTileM - 1) / kTileM;
@@ -722,16 +783,15 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     } else {
         const int wneed = (own - 1) * P.sw + (g.T3[2] - 1) * g.dil[2] + 1 + (xs - P.x0);
         P.RW = (wneed + 3) / 4 * 4;
-        // raw box along images / depth / rows: maxima over the tiles of one image (in OUTPUT units first)
-        int RN = P.ipt, RDo = 1, RHo = 1;
+        // rows a tile touches: maximum over the tiles of one plane (in OUTPUT rows first)
+        int RHo = 1;
         for (int tq = 0; tq < P.tpi; ++tq) {
-            int zl_lo, zl_hi, yl_lo, yl_hi;
-            tile_span(P, tq * kTileM, std::min((tq + 1) * kTileM, P.Pw) - 1, P.ipt > 1, zl_lo, zl_hi, yl_lo, yl_hi);
-            RDo = std::max(RDo, zl_hi - zl_lo + 1);
+            int yl_lo, yl_hi;
+            tile_rows(P, tq * kTileM, std::min((tq + 1) * kTileM, P.Pw) - 1, P.ipt > 1, yl_lo, yl_hi);
             RHo = std::max(RHo, yl_hi - yl_lo + 1);
         }
-        P.RN = z_is_batch ? 1 : RN;
-        P.RD = (RDo - 1) * P.sd + (g.T3[0] - 1) * g.dil[0] + 1;
+        P.RN = (g.OD == 1) ? P.ipt : 1;
+        P.RD = ((g.OD == 1) ? 0 : (P.ipt - 1) * P.sd) + (g.T3[0] - 1) * g.dil[0] + 1;
         P.RH = (RHo - 1) * P.sh + (g.T3[1] - 1) * g.dil[1] + 1;
     }
     if (P.RW > 256 || P.RH > 256 || P.RD > 256 || P.RN > 256)
@@ -741,7 +801,11 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     core.a_tmem = env_int("PETB200_TC_A_TMEM", 1) != 0;
     if (core.a_tmem && BN > 256)
         return fail(ctx, PETB200_ERR_INVALID, "TS variant supports BN <= 256");
-    int BC = std::min(cpg, 32);
+    // channels per chunk: 32, or more for filters with few taps so that one raw tile still feeds several K stages
+    int bc_cap = 32 * std::max(1, std::min(4, 4 / T));
+    int BC = std::min(cpg, bc_cap);
+    if (BC > 32)
+        BC = BC / 32 * 32;
     const int forced_bc = force_bc > 0 ? force_bc : env_int("PETB200_TC_BC", 0);
     if (forced_bc > 0)
         BC = std::min(forced_bc, cpg);
@@ -779,9 +843,38 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
             return fail(ctx, PETB200_ERR_UNSUPPORTED, "raw activation tile does not fit shared memory");
     }
     core.smem = smem_layout(P, core.a_tmem).total + 1024;
-    const int mtiles = P.wide ? P.images * g.OD * ohn * P.row_tiles : ((P.images + P.ipt - 1) / P.ipt) * P.tpi;
-    core.grid = dim3((unsigned)mtiles, (unsigned)((Fg + BN - 1) / BN),
-                     (unsigned)(z_is_batch ? images : g.groups));
+    const int n_img = z_is_batch ? 1 : images;
+    const int mtiles = P.wide ? n_img * g.OD * ohn * P.row_tiles : ((P.units + P.ipt - 1) / P.ipt) * P.tpi;
+    const int ntiles = (Fg + BN - 1) / BN;
+    const int gz = z_is_batch ? images : g.groups;
+    // split-K when the tile count leaves most SMs idle and K is deep
+    int ksplit = 1;
+    if (force_ksplit > 0) {
+        ksplit = std::min(force_ksplit, P.nchunks);
+    } else {
+        const long long ctas = (long long)mtiles * ntiles * gz;
+        const int want = env_int("PETB200_TC_KSPLIT", 0);
+        if (want > 0)
+            ksplit = std::min(want, P.nchunks);
+        else if (ctas * 2 <= ctx->sm_count && P.nchunks >= 2)
+            ksplit = (int)std::max<long long>(1, std::min<long long>({(long long)P.nchunks, ctx->sm_count / ctas, 32ll}));
+    }
+    P.ksplit = ksplit;
+    core.y_elems = (z_is_batch ? (long long)images : (long long)n_img) * g.F * g.OD * g.OH * g.OW;
+    if (z_is_batch)
+        core.y_elems = (long long)images * ys_n;
+    P.part_stride = (core.y_elems + 3) / 4 * 4;
+    if (ksplit > 1) {
+        if (core.partial.alloc((size_t)ksplit * P.part_stride * 4) != cudaSuccess)
+            return fail(ctx, PETB200_ERR_NOMEM, "split-K scratch allocation failed");
+        ReduceParams &r = core.red;
+        r.images = z_is_batch ? images : n_img;
+        r.F = z_is_batch ? Fg : g.F;
+        r.OD = g.OD, r.OH = g.OH, r.OW = g.OW, r.ohn = ohn, r.own = own, r.oh0 = oh0, r.ow0 = ow0;
+        r.ksplit = ksplit, r.act = act, r.f_fast = (ys_f == 1);
+        r.ys_n = ys_n, r.ys_f = ys_f, r.ys_p = ys_p, r.part_stride = P.part_stride;
+    }
+    core.grid = dim3((unsigned)mtiles, (unsigned)(ntiles * ksplit), (unsigned)gz);
     core.Ktot = (long long)P.nchunks * P.spc * kStageK;
     core.xd[0] = g.Wst;
     core.xd[1] = g.H;
@@ -887,7 +980,7 @@ int tc_conv_create(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const i
         delete t;
         return rc;
     }
-    *dev_bytes = 2 * wbytes + c.koff.bytes;
+    *dev_bytes = 2 * wbytes + c.koff.bytes + c.partial.bytes;
     *out = t;
     return PETB200_OK;
 }
@@ -924,8 +1017,8 @@ int tc_conv_run(void *h, const float *x, const float *bias, float *y, const int 
         // A window must consume K in exactly the order of the full operator (same BC / chunking), otherwise the
         // two would round differently; the raw box only shrinks for a window, so the full plan's BC always fits.
         int rc = tc_configure(wc->ctx, *wc, g, win[0], win[1], win[2], win[3], 0, g.N, (long long)g.F * plane, plane, 1,
-                              t->has_bias, t->act, t->full.P.BC);
-        if (rc == PETB200_OK && (wc->P.BN != t->full.P.BN || wc->P.BC != t->full.P.BC || wc->Ktot != t->full.Ktot))
+                              t->has_bias, t->act, t->full.P.BC, t->full.P.ksplit);
+        if (rc == PETB200_OK && (wc->P.BN != t->full.P.BN || wc->P.BC != t->full.P.BC || wc->Ktot != t->full.Ktot || wc->P.ksplit != t->full.P.ksplit))
             rc = fail(wc->ctx, PETB200_ERR_UNSUPPORTED, "window plan diverged from the full plan");
         if (rc) {
             delete wc;
@@ -961,6 +1054,7 @@ struct TcMatmul {
 
 int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transB, int has_bias, int act, void **out,
                      size_t *dev_bytes) {
+    const int mp = (m + 3) / 4 * 4; // row pitch of A as [b][k][mp]
     if (ctx->cc_major != 10)
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "tcgen05 kernels need compute capability 10.x");
     auto *t = new TcMatmul();
@@ -975,7 +1069,7 @@ int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transB, 
     g.D = 1;
     g.H = 1;
     g.W = m;
-    g.Wst = m;
+    g.Wst = mp;
     g.F = n;
     g.groups = 1;
     for (int i = 0; i < 3; ++i) {
@@ -994,7 +1088,7 @@ int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transB, 
         return rc;
     }
     TcCore &c = t->core;
-    if (c.P.BC != std::min(k, 32)) {
+    if (c.P.nchunks > 1 && c.P.spc * kStageK != c.P.BC) { // the packing below assumes k = chunk * BC + ci
         delete t;
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "matmul K chunking diverged from the packing order");
     }
@@ -1010,7 +1104,7 @@ int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transB, 
         delete t;
         return rc;
     }
-    *dev_bytes = 2 * wbytes + c.koff.bytes;
+    *dev_bytes = 2 * wbytes + c.koff.bytes + c.partial.bytes;
     *out = t;
     return PETB200_OK;
 }
