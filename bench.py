@@ -72,6 +72,21 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def max_over_ranks(values, world, device=None):
+    """Element-wise maximum of `values` over all ranks (the slowest replica defines the job's time)."""
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor(values, device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t.cpu()]
+
+
+def replica_throughput(world, steps, ms_total):
+    """Whole-job images/s of `world` independent replicas that each ran `steps` images in ms_total (max over ranks)."""
+    return world * steps * 1000.0 / ms_total
+
+
 def synthetic(seed=2000):
     """Seeded stand-ins with the configuration's shapes and distributions: X ~ N(0,1), W He-normal (fan-in 4608)."""
     import torch
@@ -278,20 +293,17 @@ def main():
     ctx.sync_check()
 
     # ---- max over ranks ----
-    t = torch.tensor([ms_total, e2e_ms, conv_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms, conv_ms = [float(v) for v in t.cpu()]
+    ms_total, e2e_ms, conv_ms = max_over_ranks([ms_total, e2e_ms, conv_ms], world, dev)
     if rank == 0:
         pk, pk_kind = peaks()
         ms_step = ms_total / args.steps
-        value = world * 1000.0 / ms_step
+        value = replica_throughput(world, args.steps, ms_total)
         achieved = CONV_FLOPS / (conv_ms * 1e-3) / 1e12
         peak = pk["bf16_tflops_sustained"]
         line = {"metric": "images_per_s", "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32x3 (fp32 in/out)",
                 "data": "synthetic", "config": dict(CONFIG, parallelism=f"replicas x{world}"),
-                "e2e": {"value": world * 1000.0 * args.steps / e2e_ms, "unit": "images/s", "h2d_bytes_per_step": int(np.prod(X_SHAPE)) * 4,
+                "e2e": {"value": replica_throughput(world, args.steps, e2e_ms), "unit": "images/s", "h2d_bytes_per_step": int(np.prod(X_SHAPE)) * 4,
                         "d2h_bytes_per_step": int(np.prod(b2s.out_shape)) * 4, "wall_ms_per_step": e2e_wall / args.steps},
                 "gpu_launches": int(launches), "clocks": clocks,
                 "roofline": {"bound": "tensor", "kernel": conv.kernel, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",

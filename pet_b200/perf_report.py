@@ -1,0 +1,82 @@
+"""Per-kernel measurements against the roofline that bounds each kernel (python -m pet_b200.perf_report [group ...]).
+
+Groups: `layout` (index-map kernels at sizes far beyond L2: achieved HBM GB/s), `conv` / `matmul` (tensor-core kernels:
+achieved fp32-equivalent TFLOP/s and the TF32 issue rate), `eltwise`.  Times come from the C ABI's timing entry point
+(CUDA events around repeated launches on plan-owned operands).  Peaks are read from MEASURED_PEAKS.json at the
+repository root when present.
+"""
+import json
+import os
+import sys
+
+import numpy as np
+
+from .configs import BATCH_TO_SPACE, SPACE_TO_BATCH, H2N, N2H, D2W
+from .ops import Context
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return json.load(open(p)), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+LAYOUT = [
+    ("space_to_batch x64", (64, 512, 64, 64), SPACE_TO_BATCH),
+    ("batch_to_space x64", (256, 512, 32, 32), BATCH_TO_SPACE),
+    ("H2N x256", (256, 64, 56, 56), [H2N]),
+    ("N2H x256", (512, 64, 28, 56), [N2H]),
+    ("D2W (de-interleave W)", (64, 512, 64, 64), [D2W]),
+    ("swap H,W", (64, 64, 128, 256), [(-1, [0, 1, 3, 2], 2)]),
+    ("NCHW->NHWC", (64, 256, 56, 56), [(-1, [0, 2, 3, 1], 2)]),
+    ("head split [s,h,d]->[h,s,d]", (4096, 12, 64, 16), [(-1, [1, 0, 2, 3], 2)]),
+    ("matmul transpose", (64, 1024, 2048), [(-1, [0, 2, 1], 2)]),
+]
+CONV = [
+    ("c1 3x3 64->64 56x56", (1, 64, 56, 56), (64, 64, 3, 3), (1, 1, 1, 1, 1, 1)),
+    ("c2 dense 3x3 512->512 [4,32,32]", (4, 512, 32, 32), (512, 512, 3, 3), (1, 1, 1, 1, 1, 1)),
+    ("c2 dilated 3x3 512->512 64x64", (1, 512, 64, 64), (512, 512, 3, 3), (2, 2, 1, 1, 2, 2)),
+    ("c2 dense batch 16", (64, 512, 32, 32), (512, 512, 3, 3), (1, 1, 1, 1, 1, 1)),
+    ("resnet stem 7x7 s2", (1, 3, 224, 224), (64, 3, 7, 7), (3, 3, 2, 2, 1, 1)),
+    ("resnet 3x3 512 7x7", (1, 512, 7, 7), (512, 512, 3, 3), (1, 1, 1, 1, 1, 1)),
+    ("resnet-18 conv batch 64 (128ch 28x28)", (64, 128, 28, 28), (128, 128, 3, 3), (1, 1, 1, 1, 1, 1)),
+]
+MATMUL = [("bert qkv 128x768x768", 1, 128, 768, 768, False, False), ("bert scores 12x128x128x64", 12, 128, 128, 64, False, True),
+          ("bert ffn1 128x3072x768", 1, 128, 3072, 768, False, False), ("bert ffn2 128x768x3072", 1, 128, 768, 3072, False, False),
+          ("square 4096", 1, 4096, 4096, 4096, False, False)]
+
+
+def main(argv):
+    groups = argv or ["layout", "conv", "matmul"]
+    pk, kind = peaks()
+    ctx = Context(0)
+    print(f"peaks ({kind}): HBM {pk['hbm_gbs']:.0f} GB/s, bf16 {pk['bf16_tflops']:.0f} TFLOP/s burst")
+    if "layout" in groups:
+        for name, shape, ops in LAYOUT:
+            plan = ctx.transpose_plan(shape, ops)
+            ms = plan.time(20, 5)
+            gbs = 8.0 * np.prod(shape) / ms / 1e6
+            print(f"layout  {name:30s} {plan.kernel:8s} {ms * 1e3:9.1f} us {gbs:8.0f} GB/s  {gbs / pk['hbm_gbs']:.2f} of {kind} HBM peak")
+    if "conv" in groups:
+        for name, xs, ws, (ph, pw, sh, sw, dh, dw) in CONV:
+            plan = ctx.conv2d_plan(xs, ws, ph, pw, sh, sw, dh, dw)
+            ms = plan.time(50, 10)
+            fl = 2.0 * np.prod(plan.out_shape) * ws[1] * ws[2] * ws[3]
+            tf = fl / ms / 1e9
+            print(f"conv    {name:38s} {plan.kernel:14s} {ms * 1e3:9.1f} us {tf:7.1f} TFLOP/s fp32-equivalent, "
+                  f"{3 * tf:7.1f} TF32 issued = {3 * tf / (pk['bf16_tflops'] / 2):.2f} of bf16/2")
+    if "matmul" in groups:
+        for name, b, m, n, k, ta, tb in MATMUL:
+            plan = ctx.matmul_plan((b, k, m) if ta else (b, m, k), (b, n, k) if tb else (b, k, n), ta, tb)
+            ms = plan.time(50, 10)
+            tf = 2.0 * b * m * n * k / ms / 1e9
+            print(f"matmul  {name:30s} {plan.kernel:14s} {ms * 1e3:9.1f} us {tf:7.1f} TFLOP/s fp32-equivalent")
+    ctx.sync_check()
+    ctx.close()
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])
