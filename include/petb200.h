@@ -161,6 +161,29 @@ int petb200_softmax_run(petb200_ctx *ctx, const float *x, float *y, size_t rows,
 int petb200_layernorm_run(petb200_ctx *ctx, const float *x, const float *gamma, const float *beta, float *y,
                           size_t rows, int cols, float eps, petb200_stream stream);
 
+/* ---- allocation-free entry point ------------------------------------------------------------------------------
+ * Has no counterpart in the reference.  For callers that are not allowed to allocate device memory at the point where
+ * they need a matmul — a thread that must not take the allocator's lock or its implicit device synchronisation, a
+ * plug-in that was handed all of its buffers up front, code that runs after a memory pool has been sealed.  Such a
+ * caller can create neither a context nor a plan (both own device memory), so this function takes neither: it gets
+ * the operands and the result buffer, and the only other memory its two kernels touch is a fixed array of
+ * PETB200_NOALLOC_SCRATCH_FLOATS floats that is part of the library image (every GPU that loads the library holds
+ * those 8 MiB until the process exits).  It calls no cudaMalloc/cudaFree and no routine that allocates.
+ *
+ * C[b,m,n] = act(op(A)·op(B) + bias[n]), operands laid out as for petb200_matmul_run, computed by CUDA-core kernels in
+ * two passes: partial sums of `ksplit` K slices go to the fixed array, a second kernel adds them in a fixed order.
+ * Limit: ksplit * b * m * n <= PETB200_NOALLOC_SCRATCH_FLOATS, otherwise PETB200_ERR_UNSUPPORTED and a message saying so.
+ * Sharing: all calls on a device use the same array and it keeps the last call's contents; nothing needs clearing,
+ * because each call writes every word it later reads.  Calls that overlap on one GPU (two streams, two threads) race
+ * on that array — issue them one after the other.
+ * First call: the first call on each device looks up the array's device address; make that call before starting a
+ * stream capture.
+ * `err` (may be NULL) receives the reason when the status is not PETB200_OK. */
+#define PETB200_NOALLOC_SCRATCH_FLOATS (2u * 1024u * 1024u)
+int petb200_matmul_splitk_noalloc(int transA, int transB, int b, int m, int n, int k, int ksplit, const float *a_dev,
+                                  const float *b_dev, const float *bias_dev, float *c_dev, int act, petb200_stream stream,
+                                  char *err, size_t err_len);
+
 /* ---- timing (the perf_engine side) --------------------------------------------------------------------------
  * Times `rounds` launches of a conv/matmul/layout plan after `warmup` launches on plan-owned scratch operands filled
  * with a fixed pattern, with CUDA events on the given stream; the counterpart of the loops in ConvOp::perf /
