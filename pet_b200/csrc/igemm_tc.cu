@@ -58,6 +58,7 @@ struct IgemmParams {
     float *partial;
     int *status;
     long long *prof; // optional per-CTA cycle counters (8 per CTA), for tuning only
+    int dbg;         // tuning experiments (epilogue only): bit 0 = skip the global stores
 };
 
 struct SmemLayout {
@@ -107,7 +108,7 @@ template <int ACT> __device__ __forceinline__ float act_fn(float v) {
 // the common no-activation case carries none of the transcendental code.
 template <int ACT>
 __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile0, int Fg, bool valid, const float *bias,
-                                               float *yp, long long ys_f, bool vec_ok) {
+                                               float *yp, long long ys_f, bool vec_ok, int dbg, float *stage, int nvalid_warp, float *ybase_warp) {
     uint32_t r[32], nx[32];
     ptx::tmem_ld_32x32(tacc, nx);
     for (int cc = 0; cc < BN; cc += 32) {
@@ -117,7 +118,7 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile
             r[j] = nx[j];
         if (cc + 32 < BN)
             ptx::tmem_ld_32x32(tacc + (uint32_t)(cc + 32), nx); // in flight while this chunk is stored
-        if (!valid)
+        if (dbg || (stage == nullptr && !valid))
             continue;
         const int f0 = f_tile0 + cc;
 #pragma unroll
@@ -127,7 +128,33 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile
                 v += __ldg(bias + f0 + j);
             r[j] = __float_as_uint(act_fn<ACT>(v));
         }
-        if (vec_ok) {
+        if (stage != nullptr) {
+            // NCHW output, the warp's 32 pixels contiguous in memory: transpose the 32x32 block through shared memory so
+            // that every lane stores 16 bytes (4 pixels of one filter) instead of 4 — a quarter of the store instructions.
+            const int lane = threadIdx.x & 31;
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                stage[j * 32 + lane] = __uint_as_float(r[j]);
+            __syncwarp();
+            const int px = (lane & 7) * 4;
+            float *ybase = ybase_warp; // address of the warp's first pixel, filter 0 of the group
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int c = (lane >> 3) + 4 * i;
+                if (f0 + c < Fg) {
+                    const float4 v = *reinterpret_cast<const float4 *>(stage + c * 32 + px);
+                    float *dst = ybase + (long long)(f0 + c) * ys_f + px;
+                    if (px + 3 < nvalid_warp) {
+                        *reinterpret_cast<float4 *>(dst) = v;
+                    } else {
+                        if (px < nvalid_warp) dst[0] = v.x;
+                        if (px + 1 < nvalid_warp) dst[1] = v.y;
+                        if (px + 2 < nvalid_warp) dst[2] = v.z;
+                    }
+                }
+            }
+        } else if (vec_ok) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4)
                 if (f0 + j < Fg)
@@ -262,55 +289,41 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issuer (one thread) ----------------
-        if (lane == 0) {
-            const uint32_t idesc = ptx::idesc_tf32(kTileM, P.BN);
-            const uint64_t bdesc0 = ptx::smem_desc_k128(ptx::smem_u32(sB));
-            const uint64_t adesc0 = A_TMEM ? 0ull : ptx::smem_desc_k128(ptx::smem_u32(sA));
-            const uint32_t b_half16 = b_half >> 4;
-            uint32_t accumulate = 0;
-            int sa = 0, sb = 0;
-            uint32_t pa = 0, pb = 0;
-            long long t_wa = 0, t_wb = 0;
-            const long long t_begin = P.prof ? clock64() : 0;
-            bool ok = true;
-            // Software pipelining of the bookkeeping: the stage-release commits of stage s are issued right after the
-            // first MMA of stage s+1, and the barriers of stage s+1 are polled while the last MMAs of stage s are
-            // still queued, so that the tensor pipe never waits on this thread's housekeeping.
-            int prev_sa = -1, prev_sb = -1;
-            bool ready_next = false;
-            for (int ks = 0; ks < KS; ++ks) {
-                if (!ready_next) {
-                    if (P.prof) {
-                        const long long c0 = clock64();
-                        ok = ptx::mbar_wait(a_full + sa, pa, abort_flag);
-                        const long long c1 = clock64();
-                        ok = ok && ptx::mbar_wait(b_full + sb, pb, abort_flag);
-                        t_wa += c1 - c0;
-                        t_wb += clock64() - c1;
-                    } else {
-                        ok = ptx::mbar_wait(a_full + sa, pa, abort_flag) && ptx::mbar_wait(b_full + sb, pb, abort_flag);
-                    }
-                    if (!ok)
-                        break;
-                }
-                ptx::tc_fence_after();
-                const uint64_t bhi = bdesc0 + (uint64_t)((uint32_t)sb * 2u * b_half16);
-                const uint64_t blo = bhi + b_half16;
-                const uint32_t ahi_t = tmem_base + 256u + (uint32_t)sa * 64u, alo_t = ahi_t + 32u;
-                const uint64_t ahi_s = adesc0 + (uint64_t)((uint32_t)sa * 2u * (kAHalfBytes >> 4));
-                const uint64_t alo_s = ahi_s + (kAHalfBytes >> 4);
-                // next stage's ring positions
-                int nsa = sa + 1, nsb = sb + 1;
-                uint32_t npa = pa, npb = pb;
-                if (nsa == P.NA) {
-                    nsa = 0;
-                    npa ^= 1u;
-                }
-                if (nsb == P.NB) {
-                    nsb = 0;
-                    npb ^= 1u;
-                }
+        // ---------------- MMA issuer ----------------
+        // The whole warp runs this loop with uniform control flow and only the tcgen05 instructions sit under
+        // elect_one: descriptors and TMEM addresses then live in uniform registers.  (With the loop confined to one
+        // lane the same instruction stream was issue-bound: 94 instead of 64 cycles per 128x128x8 MMA.)
+        const uint32_t idesc = ptx::idesc_tf32(kTileM, P.BN);
+        const uint64_t bdesc0 = ptx::smem_desc_k128(ptx::smem_u32(sB));
+        const uint64_t adesc0 = A_TMEM ? 0ull : ptx::smem_desc_k128(ptx::smem_u32(sA));
+        const uint32_t b_half16 = b_half >> 4;
+        uint32_t accumulate = 0;
+        int sa = 0, sb = 0, prev_sa = -1, prev_sb = -1;
+        uint32_t pa = 0, pb = 0;
+        long long t_wa = 0, t_wb = 0;
+        const long long t_begin = P.prof ? clock64() : 0;
+        bool ok = true;
+        for (int ks = 0; ks < KS; ++ks) {
+            if (P.prof) {
+                const long long q0c = clock64();
+                ok = ptx::mbar_wait(a_full + sa, pa, abort_flag);
+                const long long q1c = clock64();
+                ok = ok && ptx::mbar_wait(b_full + sb, pb, abort_flag);
+                t_wa += q1c - q0c;
+                t_wb += clock64() - q1c;
+            } else {
+                ok = ptx::mbar_wait(a_full + sa, pa, abort_flag) && ptx::mbar_wait(b_full + sb, pb, abort_flag);
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok)
+                break;
+            ptx::tc_fence_after();
+            const uint64_t bhi = bdesc0 + (uint64_t)((uint32_t)sb * 2u * b_half16);
+            const uint64_t blo = bhi + b_half16;
+            const uint32_t ahi_t = tmem_base + 256u + (uint32_t)sa * 64u, alo_t = ahi_t + 32u;
+            const uint64_t ahi_s = adesc0 + (uint64_t)((uint32_t)sa * 2u * (kAHalfBytes >> 4));
+            const uint64_t alo_s = ahi_s + (kAHalfBytes >> 4);
+            if (ptx::elect_one()) {
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
                     if (A_TMEM) {
@@ -319,7 +332,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                         ptx::mma_tf32_ss(tmem_base, alo_s + 2 * kk, bhi + 2 * kk, idesc, accumulate);
                     }
                     accumulate = 1u;
-                    if (kk == 0 && prev_sa >= 0) {
+                    if (kk == 0 && prev_sa >= 0) { // release the previous stage once this stage's first MMA is queued
                         ptx::mma_commit(a_empty + prev_sa);
                         ptx::mma_commit(b_empty + prev_sb);
                     }
@@ -331,26 +344,34 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                         ptx::mma_tf32_ss(tmem_base, ahi_s + 2 * kk, bhi + 2 * kk, idesc, 1u);
                     }
                 }
-                ready_next = (ks + 1 < KS) && ptx::mbar_try_wait(a_full + nsa, npa) && ptx::mbar_try_wait(b_full + nsb, npb);
-                prev_sa = sa;
-                prev_sb = sb;
-                sa = nsa;
-                sb = nsb;
-                pa = npa;
-                pb = npb;
             }
+            __syncwarp();
+            accumulate = 1u;
+            prev_sa = sa;
+            prev_sb = sb;
+            if (++sa == P.NA) {
+                sa = 0;
+                pa ^= 1u;
+            }
+            if (++sb == P.NB) {
+                sb = 0;
+                pb ^= 1u;
+            }
+        }
+        if (ptx::elect_one()) {
             if (ok && prev_sa >= 0) {
                 ptx::mma_commit(a_empty + prev_sa);
                 ptx::mma_commit(b_empty + prev_sb);
             }
             if (ok)
                 ptx::mma_commit(acc_full);
-            if (P.prof) {
-                long long *pr = P.prof + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8;
-                pr[0] = t_wa;
-                pr[1] = t_wb;
-                pr[2] = clock64() - t_begin;
-            }
+        }
+        __syncwarp();
+        if (lane == 0 && P.prof) {
+            long long *pr = P.prof + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8;
+            pr[0] = t_wa;
+            pr[1] = t_wb;
+            pr[2] = clock64() - t_begin;
         }
     } else {
         // ---------------- transform + epilogue (warps 3..6) ----------------
@@ -480,21 +501,38 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                                 ((reinterpret_cast<uintptr_t>(P.y) & 15) == 0) && ((P.part_stride & 3) == 0) &&
                                 ((reinterpret_cast<uintptr_t>(P.partial) & 15) == 0);
             const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            // staged 16-byte stores need: pixel-contiguous NCHW output, full-width rows (no column window), one plane per
+            // tile, 16-byte aligned runs
+            float *stage = nullptr;
+            int nvalid_warp = 0;
+            const long long plane_elems = (long long)P.OD * P.OH * P.OW;
+            const long long y_off0 = __shfl_sync(0xffffffffu, y_off, 0);
+            float *ybase_warp = yp - y_off + y_off0;
+            if (P.ys_p == 1 && P.ipt == 1 && P.own == P.OW && P.ow0 == 0 && (plane_elems & 3) == 0 && (P.ys_n & 3) == 0 &&
+                ((P.OH * P.OW) & 3) == 0 && (!P.wide || (P.OW & 3) == 0) &&
+                (P.ys_f & 3) == 0 && ((P.oh0 * P.OW) & 3) == 0 && (P.part_stride & 3) == 0 &&
+                ((reinterpret_cast<uintptr_t>(P.y) | reinterpret_cast<uintptr_t>(P.partial)) & 15) == 0) {
+                nvalid_warp = __popc(__ballot_sync(0xffffffffu, valid));
+                if (nvalid_warp > 0)
+                    stage = reinterpret_cast<float *>(sB) + (warp - 3) * 1024; // B stages are idle once the accumulator is complete
+                else
+                    stage = nullptr;
+            }
             switch (P.ksplit > 1 ? PETB200_ACT_NONE : P.act) {
             case PETB200_ACT_RELU:
-                epilogue_store<PETB200_ACT_RELU>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok);
+                epilogue_store<PETB200_ACT_RELU>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp);
                 break;
             case PETB200_ACT_SIGMOID:
-                epilogue_store<PETB200_ACT_SIGMOID>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok);
+                epilogue_store<PETB200_ACT_SIGMOID>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp);
                 break;
             case PETB200_ACT_TANH:
-                epilogue_store<PETB200_ACT_TANH>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok);
+                epilogue_store<PETB200_ACT_TANH>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp);
                 break;
             case PETB200_ACT_GELU:
-                epilogue_store<PETB200_ACT_GELU>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok);
+                epilogue_store<PETB200_ACT_GELU>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp);
                 break;
             default:
-                epilogue_store<PETB200_ACT_NONE>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok);
+                epilogue_store<PETB200_ACT_NONE>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp);
                 break;
             }
         }
@@ -688,6 +726,7 @@ struct TcCore {
         p.koff = (const int *)koff.p;
         p.status = ctx->d_status;
         p.prof = prof;
+        { static int d = -1; if (d < 0) { const char *e = getenv("PETB200_TC_DBG"); d = e ? atoi(e) : 0; } p.dbg = d; }
         p.has_bias = (P.has_bias && bias) ? 1 : 0;
         if (a_tmem)
             k_igemm<true><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
