@@ -15,8 +15,9 @@ int tc_conv_run(void *h, const float *x, const float *bias, float *y, const int 
 int tc_conv_row_pitch(void *h);
 void tc_conv_set_prof(void *h, long long *p);
 const char *tc_conv_variant(void *h);
-int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transB, int has_bias, int act, void **out,
+int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, int transB, int has_bias, int act, void **out,
                      size_t *dev_bytes);
+int tc_matmul_native_a(void *h);
 void tc_matmul_destroy(void *h);
 int tc_matmul_pack_b(void *h, const float *b, cudaStream_t s);
 int tc_matmul_run(void *h, const float *a_t, const float *bias, float *cmat, cudaStream_t s);
@@ -309,6 +310,7 @@ struct MatmulPlan : petb200_plan {
     void *tc = nullptr;
     DevBuf at; // A re-laid as [b][k][m] when the caller's A is [b][m][k]
     const float *b_weight = nullptr; // set by matmul_set_weights
+    bool native_a = false;           // the kernel reads row-major A directly
     DevBuf ba, bbm, bbias, bc;
     ~MatmulPlan() override {
         if (tc)
@@ -332,12 +334,13 @@ int make_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int
     int rc = PETB200_ERR_UNSUPPORTED;
     if (algo == PETB200_ALGO_AUTO || algo == PETB200_ALGO_TC_3XTF32) {
         size_t bytes = 0;
-        rc = tc_matmul_create(ctx, b, m, n, k, pl->transB, has_bias, act, &pl->tc, &bytes);
+        rc = tc_matmul_create(ctx, b, m, n, k, pl->transA, pl->transB, has_bias, act, &pl->tc, &bytes);
         if (rc == PETB200_OK) {
             pl->algo = PETB200_ALGO_TC_3XTF32;
             pl->kernel = "tc_3xtf32_ts";
             pl->device_bytes = bytes;
-            if (!pl->transA || m % 4 != 0) {
+            pl->native_a = tc_matmul_native_a(pl->tc) != 0;
+            if (!pl->native_a && (!pl->transA || m % 4 != 0)) {
                 if (pl->at.alloc((size_t)b * ((m + 3) / 4 * 4) * k * 4) != cudaSuccess) {
                     delete pl;
                     return fail(ctx, PETB200_ERR_NOMEM, "A re-layout scratch allocation failed");
@@ -377,7 +380,9 @@ int matmul_run(petb200_plan *plan, const float *a, const float *b, const float *
             return rc;
         const float *at = a;
         const int mp = (pl->m + 3) / 4 * 4;
-        if (!pl->transA) {
+        if (pl->native_a) {
+            // nothing to do: the kernel's K-major mode consumes A as it is
+        } else if (!pl->transA) {
             long long tiles = (long long)pl->bs * ((pl->k + 31) / 32) * ((mp + 31) / 32);
             k_transpose_a<<<(int)std::min<long long>(tiles, (long long)ctx->sm_count * 8), 256, 0, s>>>(a, (float *)pl->at.p, pl->bs, pl->m, pl->k, mp);
             rc = launched(ctx, "k_transpose_a");

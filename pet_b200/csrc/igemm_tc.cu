@@ -33,6 +33,7 @@ constexpr int kStageK = 32;               // fp32/TF32 values per K stage = one 
 constexpr int kAHalfBytes = kTileM * 128; // one 128 x 32 operand tile
 constexpr int kThreads = 224;
 constexpr int kMaxNB = 6;
+constexpr int kMaxNR = 6;
 
 struct IgemmParams {
     int Pw, units;          // pixels of one output plane (one image, one depth slice); number of such planes
@@ -48,7 +49,9 @@ struct IgemmParams {
     int tpi, ipt;           // otherwise: tiles per plane (plane larger than a tile) or whole planes per tile
     int ksplit;             // K is split over this many CTAs (partial sums go to scratch, reduced by a second kernel)
     long long part_stride;  // floats between the partial-sum copies
-    int NA, NB;             // ring depths
+    int NA, NB, NR;         // ring depths: A stages, B stages, raw activation buffers
+    int a_kmajor;           // matmul with row-major A: the raw tile is [128 rows][32 k], 128B-swizzled, one per K stage
+    int m_rows;             // a_kmajor: rows of A per batch entry
     int raw_bytes;          // bytes of one raw buffer (128-aligned)
     long long ys_n, ys_f, ys_p;
     int act, has_bias;
@@ -72,11 +75,11 @@ __host__ __device__ inline SmemLayout smem_layout(const IgemmParams &P, bool a_t
     L.b_off = o;
     o += (uint32_t)P.NB * 2 * (uint32_t)P.BN * 128;
     L.raw_off = o;
-    o += 2u * (uint32_t)P.raw_bytes;
+    o += (uint32_t)P.NR * (uint32_t)P.raw_bytes;
     L.koff_off = o;
     o += (uint32_t)P.spc * kStageK * 4;
     L.bar_off = (o + 15) & ~15u;
-    L.total = L.bar_off + 256;
+    L.total = L.bar_off + 320;
     return L;
 }
 
@@ -109,15 +112,18 @@ template <int ACT> __device__ __forceinline__ float act_fn(float v) {
 template <int ACT>
 __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile0, int Fg, bool valid, const float *bias,
                                                float *yp, long long ys_f, bool vec_ok, int dbg, float *stage, int nvalid_warp, float *ybase_warp) {
-    uint32_t r[32], nx[32];
+    uint32_t r[32], nx[32], sm[32];
     ptx::tmem_ld_32x32(tacc, nx);
+    ptx::tmem_ld_32x32(tacc + 128u, sm);
     for (int cc = 0; cc < BN; cc += 32) {
         ptx::tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-            r[j] = nx[j];
-        if (cc + 32 < BN)
-            ptx::tmem_ld_32x32(tacc + (uint32_t)(cc + 32), nx); // in flight while this chunk is stored
+        for (int j = 0; j < 32; ++j) // hi*hi sum + (lo*hi + hi*lo) sum, one rounded fp32 add
+            r[j] = __float_as_uint(__uint_as_float(nx[j]) + __uint_as_float(sm[j]));
+        if (cc + 32 < BN) { // in flight while this chunk is stored
+            ptx::tmem_ld_32x32(tacc + (uint32_t)(cc + 32), nx);
+            ptx::tmem_ld_32x32(tacc + 128u + (uint32_t)(cc + 32), sm);
+        }
         if (dbg || (stage == nullptr && !valid))
             continue;
         const int f0 = f_tile0 + cc;
@@ -168,7 +174,7 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile
     }
 }
 
-template <bool A_TMEM>
+template <bool A_TMEM, bool A_KMAJOR>
 __global__ void __launch_bounds__(kThreads, 1)
 k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_bhi,
         const __grid_constant__ CUtensorMap tmap_blo, const IgemmParams P) {
@@ -182,9 +188,9 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     int *sKoff = reinterpret_cast<int *>(smem + L.koff_off);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L.bar_off);
     // barrier slots
-    uint64_t *raw_full = bars, *raw_empty = bars + 2;
-    uint64_t *b_full = bars + 4, *b_empty = bars + 4 + kMaxNB; // up to kMaxNB stages
-    uint64_t *a_full = bars + 4 + 2 * kMaxNB, *a_empty = a_full + 4; // up to 4 stages
+    uint64_t *raw_full = bars, *raw_empty = bars + kMaxNR;
+    uint64_t *b_full = bars + 2 * kMaxNR, *b_empty = b_full + kMaxNB; // up to kMaxNB stages
+    uint64_t *a_full = b_empty + kMaxNB, *a_empty = a_full + 4;       // up to 4 stages
     uint64_t *acc_full = a_empty + 4;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(acc_full + 2);
@@ -194,10 +200,12 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     const int ksp = blockIdx.y - ntile * P.ksplit;
     const int zb = blockIdx.z;
     const uint32_t b_half = (uint32_t)P.BN * 128u;
-    const uint32_t tmem_cols = A_TMEM ? 512u : (P.BN <= 32 ? 32u : (P.BN <= 64 ? 64u : (P.BN <= 128 ? 128u : 256u)));
+    // TMEM columns: [0,BN) accumulator of the hi*hi products, [128,128+BN) accumulator of the two small cross terms,
+    // [256,512) the A stages of the TS variant
+    const uint32_t tmem_cols = A_TMEM ? 512u : 256u;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kMaxNR; ++i) {
             ptx::mbar_init(raw_full + i, 1);
             ptx::mbar_init(raw_empty + i, 4);
         }
@@ -229,7 +237,9 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
 
     // Tile origin in the input: first image, depth slice, row and (16-byte aligned) column of the raw box.
     int n_lo = 0, q0 = 0, unit0 = 0, z_start, y_start, x_start, w_zl = 0, w_yl = 0, w_tx = 0;
-    if (P.wide) {
+    if (A_KMAJOR) {
+        z_start = y_start = x_start = 0; // the tile is rows [blockIdx.x*128, +128) of A[zb]
+    } else if (P.wide) {
         const int row = blockIdx.x / P.row_tiles;
         w_tx = blockIdx.x - row * P.row_tiles;
         n_lo = row / (P.OD * P.ohn);
@@ -279,13 +289,24 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             const int c_base = P.z_is_batch ? 0 : zb * P.cpg;
             const int n_start = P.z_is_batch ? zb : n_lo;
             const uint32_t bytes = (uint32_t)P.RN * P.BC * P.RD * P.RH * P.RW * 4u;
+            int rb = 0;
+            uint32_t pr = 1; // first pass over the ring: every buffer is free
             for (int ch = 0; ch < c1 - c0; ++ch) {
-                const int rb = ch & 1;
-                if (!ptx::mbar_wait(raw_empty + rb, (uint32_t)(((ch >> 1) & 1) ^ 1), abort_flag))
+                if (!ptx::mbar_wait(raw_empty + rb, pr, abort_flag))
                     break;
-                ptx::mbar_expect_tx(raw_full + rb, bytes);
-                ptx::tma_load_5d(sRaw + (size_t)rb * P.raw_bytes, &tmap_x, raw_full + rb, x_start, y_start, z_start,
-                                 c_base + (c0 + ch) * P.BC, n_start);
+                if (A_KMAJOR) {
+                    ptx::mbar_expect_tx(raw_full + rb, (uint32_t)kAHalfBytes);
+                    ptx::tma_load_3d(sRaw + (size_t)rb * P.raw_bytes, &tmap_x, raw_full + rb, (c0 + ch) * kStageK,
+                                     (int)blockIdx.x * kTileM, zb);
+                } else {
+                    ptx::mbar_expect_tx(raw_full + rb, bytes);
+                    ptx::tma_load_5d(sRaw + (size_t)rb * P.raw_bytes, &tmap_x, raw_full + rb, x_start, y_start, z_start,
+                                     c_base + (c0 + ch) * P.BC, n_start);
+                }
+                if (++rb == P.NR) {
+                    rb = 0;
+                    pr ^= 1u;
+                }
             }
         }
     } else if (warp == 1) {
@@ -297,6 +318,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         const uint64_t bdesc0 = ptx::smem_desc_k128(ptx::smem_u32(sB));
         const uint64_t adesc0 = A_TMEM ? 0ull : ptx::smem_desc_k128(ptx::smem_u32(sA));
         const uint32_t b_half16 = b_half >> 4;
+        const uint32_t tmem_small = tmem_base + 128u;
         uint32_t accumulate = 0;
         int sa = 0, sb = 0, prev_sa = -1, prev_sb = -1;
         uint32_t pa = 0, pb = 0;
@@ -326,23 +348,26 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             if (ptx::elect_one()) {
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
+                    // The two cross terms go to their own accumulator: the tensor core truncates (rounds toward zero) its
+                    // accumulator after every MMA, a bias proportional to the accumulator's magnitude; keeping the small
+                    // terms away from the big sum removes two thirds of those truncations from it.
                     if (A_TMEM) {
-                        ptx::mma_tf32_ts(tmem_base, alo_t + kk * 8, bhi + 2 * kk, idesc, accumulate);
+                        ptx::mma_tf32_ts(tmem_small, alo_t + kk * 8, bhi + 2 * kk, idesc, accumulate);
                     } else {
-                        ptx::mma_tf32_ss(tmem_base, alo_s + 2 * kk, bhi + 2 * kk, idesc, accumulate);
+                        ptx::mma_tf32_ss(tmem_small, alo_s + 2 * kk, bhi + 2 * kk, idesc, accumulate);
                     }
-                    accumulate = 1u;
                     if (kk == 0 && prev_sa >= 0) { // release the previous stage once this stage's first MMA is queued
                         ptx::mma_commit(a_empty + prev_sa);
                         ptx::mma_commit(b_empty + prev_sb);
                     }
                     if (A_TMEM) {
-                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, blo + 2 * kk, idesc, 1u);
-                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, 1u);
+                        ptx::mma_tf32_ts(tmem_small, ahi_t + kk * 8, blo + 2 * kk, idesc, 1u);
+                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, accumulate);
                     } else {
-                        ptx::mma_tf32_ss(tmem_base, ahi_s + 2 * kk, blo + 2 * kk, idesc, 1u);
-                        ptx::mma_tf32_ss(tmem_base, ahi_s + 2 * kk, bhi + 2 * kk, idesc, 1u);
+                        ptx::mma_tf32_ss(tmem_small, ahi_s + 2 * kk, blo + 2 * kk, idesc, 1u);
+                        ptx::mma_tf32_ss(tmem_base, ahi_s + 2 * kk, bhi + 2 * kk, idesc, accumulate);
                     }
+                    accumulate = 1u;
                 }
             }
             __syncwarp();
@@ -380,7 +405,11 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         bool valid;
         int base_p = 0;
         long long y_off = 0;
-        if (P.wide) {
+        if (A_KMAJOR) {
+            const int row = (int)blockIdx.x * kTileM + p;
+            valid = row < P.m_rows;
+            y_off = (long long)zb * P.ys_n + (long long)row * P.ys_p;
+        } else if (P.wide) {
             const int xl = w_tx * kTileM + p;
             valid = xl < P.own;
             if (valid) {
@@ -414,10 +443,11 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         const long long t_begin = P.prof ? clock64() : 0;
         int sa = 0;
         uint32_t pa = 1; // first pass over the ring: every slot is free
+        int rb = 0;
+        uint32_t prw = 0;
         for (int ch = 0; ch < c1 - c0 && alive; ++ch) {
-            const int rb = ch & 1;
             const long long cr0 = P.prof ? clock64() : 0;
-            alive = ptx::mbar_wait(raw_full + rb, (uint32_t)((ch >> 1) & 1), abort_flag);
+            alive = ptx::mbar_wait(raw_full + rb, prw, abort_flag);
             if (P.prof)
                 t_wr += clock64() - cr0;
             const float *raw = reinterpret_cast<const float *>(sRaw + (size_t)rb * P.raw_bytes) + base_p;
@@ -432,11 +462,18 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 if (A_TMEM) {
                     ptx::tc_fence_after();
                     uint32_t hi[32], lo[32];
+                    const uint8_t *krow = sRaw + (size_t)rb * P.raw_bytes + (size_t)p * 128;
 #pragma unroll
                     for (int c4 = 0; c4 < 8; ++c4) {
-                        const int4 o = ko[c4];
-                        float v0 = o.x >= 0 ? raw[o.x] : 0.f, v1 = o.y >= 0 ? raw[o.y] : 0.f;
-                        float v2 = o.z >= 0 ? raw[o.z] : 0.f, v3 = o.w >= 0 ? raw[o.w] : 0.f;
+                        float v0, v1, v2, v3;
+                        if (A_KMAJOR) { // row p of the swizzled [128][32] tile: 16-byte chunk c4 sits at c4 ^ (p & 7)
+                            const float4 t4 = *reinterpret_cast<const float4 *>(krow + ((c4 ^ (p & 7)) << 4));
+                            v0 = t4.x, v1 = t4.y, v2 = t4.z, v3 = t4.w;
+                        } else {
+                            const int4 o = ko[c4];
+                            v0 = o.x >= 0 ? raw[o.x] : 0.f, v1 = o.y >= 0 ? raw[o.y] : 0.f;
+                            v2 = o.z >= 0 ? raw[o.z] : 0.f, v3 = o.w >= 0 ? raw[o.w] : 0.f;
+                        }
                         hi[4 * c4 + 0] = __float_as_uint(v0) & 0xffffe000u;
                         hi[4 * c4 + 1] = __float_as_uint(v1) & 0xffffe000u;
                         hi[4 * c4 + 2] = __float_as_uint(v2) & 0xffffe000u;
@@ -485,6 +522,10 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             __syncwarp();
             if (lane == 0 && alive)
                 ptx::mbar_arrive(raw_empty + rb);
+            if (++rb == P.NR) {
+                rb = 0;
+                prw ^= 1u;
+            }
         }
         // ---------------- epilogue ----------------
         const long long t_loop = P.prof ? clock64() - t_begin : 0;
@@ -685,6 +726,19 @@ struct TcCore {
         EncodeTiledFn enc = encode_fn();
         if (!enc)
             return fail(ctx, PETB200_ERR_CUDA, "cuTensorMapEncodeTiled entry point unavailable");
+        if (P.a_kmajor) { // A[b][m][k] row-major: dims (k, m, b), one 128B-swizzled [128 rows][32 k] box per K stage
+            cuuint64_t d3[3] = {(cuuint64_t)xd[0], (cuuint64_t)xd[1], (cuuint64_t)xd[2]};
+            cuuint64_t s3[2] = {(cuuint64_t)xd[0] * 4, (cuuint64_t)xd[0] * xd[1] * 4};
+            cuuint32_t b3[3] = {(cuuint32_t)kStageK, (cuuint32_t)kTileM, 1};
+            cuuint32_t e3[3] = {1, 1, 1};
+            CUresult r3 = enc(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(x), d3, s3, b3, e3,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r3 != CUDA_SUCCESS)
+                return fail(ctx, PETB200_ERR_CUDA, "cuTensorMapEncodeTiled(row-major A) failed with %d", (int)r3);
+            map_x_ptr = x;
+            return PETB200_OK;
+        }
         cuuint64_t dims[5] = {(cuuint64_t)xd[0], (cuuint64_t)xd[1], (cuuint64_t)xd[2], (cuuint64_t)xd[3], (cuuint64_t)xd[4]};
         cuuint64_t str[4] = {(cuuint64_t)xd[0] * 4, (cuuint64_t)xd[0] * xd[1] * 4, (cuuint64_t)xd[0] * xd[1] * xd[2] * 4,
                              (cuuint64_t)xd[0] * xd[1] * xd[2] * xd[3] * 4};
@@ -728,10 +782,12 @@ struct TcCore {
         p.prof = prof;
         { static int d = -1; if (d < 0) { const char *e = getenv("PETB200_TC_DBG"); d = e ? atoi(e) : 0; } p.dbg = d; }
         p.has_bias = (P.has_bias && bias) ? 1 : 0;
-        if (a_tmem)
-            k_igemm<true><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
+        if (P.a_kmajor)
+            k_igemm<true, true><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
+        else if (a_tmem)
+            k_igemm<true, false><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
         else
-            k_igemm<false><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
+            k_igemm<false, false><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
         rc = launched(ctx, "k_igemm");
         if (rc || P.ksplit == 1)
             return rc;
@@ -789,8 +845,8 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     // tile N
     int BN = Fg <= 32 ? 32 : (Fg <= 64 ? 64 : 128);
     BN = env_int("PETB200_TC_BN", BN);
-    if (BN != 32 && BN != 64 && BN != 128 && BN != 256)
-        return fail(ctx, PETB200_ERR_INVALID, "PETB200_TC_BN must be 32, 64, 128 or 256");
+    if (BN != 32 && BN != 64 && BN != 128)
+        return fail(ctx, PETB200_ERR_INVALID, "PETB200_TC_BN must be 32, 64 or 128");
     P.BN = BN;
     // Planes smaller than half a tile are packed several to a tile: whole images for 2-D problems, consecutive depth
     // slices of one image (a divisor of the depth, so that no tile straddles two images) for 3-D problems.
@@ -856,6 +912,9 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
         P.raw_bytes = (int)((raw + 127) / 128 * 128);
         P.NA = core.a_tmem ? 4 : 2;
         P.NB = 2;
+        P.NR = 2;
+        P.a_kmajor = 0;
+        P.m_rows = 0;
         bool fits = smem_layout(P, core.a_tmem).total <= budget;
         if (fits) {
             // deepen the rings while there is room: B first (it hides TMA latency), then A
@@ -936,8 +995,10 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     static bool attr_set = false;
     if (!attr_set) {
         const int lim = (int)std::min<size_t>(ctx->smem_optin, 227 * 1024);
-        cudaError_t e1 = cudaFuncSetAttribute(k_igemm<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
-        cudaError_t e2 = cudaFuncSetAttribute(k_igemm<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        cudaError_t e1 = cudaFuncSetAttribute(k_igemm<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        cudaError_t e2 = cudaFuncSetAttribute(k_igemm<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        if (e1 == cudaSuccess)
+            e1 = cudaFuncSetAttribute(k_igemm<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
         if (e1 != cudaSuccess || e2 != cudaSuccess)
             return fail(ctx, PETB200_ERR_CUDA, "cudaFuncSetAttribute(%d bytes) failed: %s", lim,
                         cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
@@ -1089,9 +1150,87 @@ const char *tc_conv_variant(void *h) { return ((TcConv *)h)->full.a_tmem ? "tc_3
 struct TcMatmul {
     TcCore core;
     int bs, m, n, k, transB;
+    bool native_a = false; // A is consumed row-major as passed (no re-layout)
 };
 
-int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transB, int has_bias, int act, void **out,
+// Shared tail of the two matmul configurations: split-K decision, scratch, reduce parameters, grid.
+static int matmul_finish(petb200_ctx *ctx, TcCore &c, int bs, int m, int n, int mtiles, int act) {
+    IgemmParams &P = c.P;
+    const int ntiles = (n + P.BN - 1) / P.BN;
+    const long long ctas = (long long)mtiles * ntiles * bs;
+    int ksplit = 1;
+    const int want = env_int("PETB200_TC_KSPLIT", 0);
+    if (want > 0)
+        ksplit = std::min(want, P.nchunks);
+    else if (ctas * 2 <= ctx->sm_count && P.nchunks >= 2)
+        ksplit = (int)std::max<long long>(1, std::min<long long>({(long long)P.nchunks, ctx->sm_count / ctas, 32ll}));
+    P.ksplit = ksplit;
+    c.y_elems = (long long)bs * m * n;
+    P.part_stride = (c.y_elems + 3) / 4 * 4;
+    if (ksplit > 1) {
+        if (c.partial.alloc((size_t)ksplit * P.part_stride * 4) != cudaSuccess)
+            return fail(ctx, PETB200_ERR_NOMEM, "split-K scratch allocation failed");
+        ReduceParams &r = c.red;
+        r.images = bs, r.F = n, r.OD = 1, r.OH = 1, r.OW = m, r.ohn = 1, r.own = m, r.oh0 = 0, r.ow0 = 0;
+        r.ksplit = ksplit, r.act = act, r.f_fast = 1;
+        r.ys_n = (long long)m * n, r.ys_f = 1, r.ys_p = n, r.part_stride = P.part_stride;
+    }
+    c.grid = dim3((unsigned)mtiles, (unsigned)(ntiles * ksplit), (unsigned)bs);
+    return PETB200_OK;
+}
+
+// Row-major A ([b][m][k], k % 4 == 0): the kernel's K-major mode, no re-layout of A.
+static int tc_configure_kmajor(petb200_ctx *ctx, TcCore &core, int bs, int m, int n, int k, int has_bias, int act) {
+    IgemmParams &P = core.P;
+    memset(&P, 0, sizeof P);
+    core.a_tmem = true;
+    P.a_kmajor = 1;
+    P.m_rows = m;
+    P.z_is_batch = 1;
+    P.OD = P.OH = 1, P.OW = m, P.ohn = 1, P.own = m, P.Pw = m, P.units = 1, P.ipt = 1, P.tpi = (m + kTileM - 1) / kTileM;
+    P.sd = P.sh = P.sw = 1;
+    P.cpg = k, P.Fg = n;
+    int BN = n <= 32 ? 32 : (n <= 64 ? 64 : 128);
+    BN = env_int("PETB200_TC_BN", BN);
+    P.BN = BN;
+    P.BC = kStageK, P.spc = 1, P.nchunks = (k + kStageK - 1) / kStageK;
+    P.RN = P.RD = 1, P.RH = kTileM, P.RW = kStageK;
+    P.raw_bytes = kAHalfBytes;
+    P.ys_n = (long long)m * n, P.ys_f = 1, P.ys_p = n;
+    P.has_bias = has_bias, P.act = act;
+    P.NA = 4;
+    const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 1024;
+    P.NB = 2, P.NR = 2;
+    if (smem_layout(P, true).total > budget)
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "matmul tile does not fit shared memory");
+    for (bool grew = true; grew;) { // deepen both rings alternately: every K stage needs one B tile and one raw tile
+        grew = false;
+        if (P.NB < kMaxNB) {
+            P.NB++;
+            if (smem_layout(P, true).total <= budget)
+                grew = true;
+            else
+                P.NB--;
+        }
+        if (P.NR < kMaxNR) {
+            P.NR++;
+            if (smem_layout(P, true).total <= budget)
+                grew = true;
+            else
+                P.NR--;
+        }
+    }
+    core.smem = smem_layout(P, true).total + 1024;
+    core.Ktot = (long long)P.nchunks * kStageK;
+    core.xd[0] = k, core.xd[1] = m, core.xd[2] = bs;
+    std::vector<int> koff(kStageK, -1); // unused in this mode; the kernel still copies one stage worth of table
+    if (core.koff.alloc(koff.size() * 4) != cudaSuccess)
+        return fail(ctx, PETB200_ERR_NOMEM, "koff allocation failed");
+    PETB200_CUDA(ctx, cudaMemcpy(core.koff.p, koff.data(), koff.size() * 4, cudaMemcpyHostToDevice));
+    return matmul_finish(ctx, core, bs, m, n, P.tpi, act);
+}
+
+int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, int transB, int has_bias, int act, void **out,
                      size_t *dev_bytes) {
     const int mp = (m + 3) / 4 * 4; // row pitch of A as [b][k][mp]
     if (ctx->cc_major != 10)
@@ -1102,26 +1241,41 @@ int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transB, 
     t->n = n;
     t->k = k;
     t->transB = transB;
-    ConvGeom g{};
-    g.N = bs;
-    g.C = k;
-    g.D = 1;
-    g.H = 1;
-    g.W = m;
-    g.Wst = mp;
-    g.F = n;
-    g.groups = 1;
-    for (int i = 0; i < 3; ++i) {
-        g.T3[i] = 1;
-        g.pad[i] = 0;
-        g.stride[i] = 1;
-        g.dil[i] = 1;
-    }
-    g.OD = 1;
-    g.OH = 1;
-    g.OW = m;
     t->core.ctx = ctx;
-    int rc = tc_configure(ctx, t->core, g, 0, 1, 0, m, 1, bs, (long long)m * n, 1, n, has_bias, act);
+    int rc;
+    if (!transA && k % 4 == 0 && env_int("PETB200_TC_KMAJOR", 1)) {
+        // make sure the shared-memory attribute of every instantiation is raised (done inside tc_configure)
+        ConvGeom g0{};
+        g0.N = 1, g0.C = 4, g0.D = 1, g0.H = 1, g0.W = 4, g0.Wst = 4, g0.F = 32, g0.groups = 1, g0.OD = 1, g0.OH = 1, g0.OW = 4;
+        for (int i = 0; i < 3; ++i)
+            g0.T3[i] = 1, g0.pad[i] = 0, g0.stride[i] = 1, g0.dil[i] = 1;
+        TcCore dummy;
+        dummy.ctx = ctx;
+        rc = tc_configure(ctx, dummy, g0, 0, 1, 0, 4, 1, 1, 128, 1, 32, 0, 0);
+        if (rc == PETB200_OK)
+            rc = tc_configure_kmajor(ctx, t->core, bs, m, n, k, has_bias, act);
+        t->native_a = true;
+    } else {
+        ConvGeom g{};
+        g.N = bs;
+        g.C = k;
+        g.D = 1;
+        g.H = 1;
+        g.W = m;
+        g.Wst = mp;
+        g.F = n;
+        g.groups = 1;
+        for (int i = 0; i < 3; ++i) {
+            g.T3[i] = 1;
+            g.pad[i] = 0;
+            g.stride[i] = 1;
+            g.dil[i] = 1;
+        }
+        g.OD = 1;
+        g.OH = 1;
+        g.OW = m;
+        rc = tc_configure(ctx, t->core, g, 0, 1, 0, m, 1, bs, (long long)m * n, 1, n, has_bias, act);
+    }
     if (rc) {
         delete t;
         return rc;
@@ -1147,6 +1301,7 @@ int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transB, 
     *out = t;
     return PETB200_OK;
 }
+int tc_matmul_native_a(void *h) { return ((TcMatmul *)h)->native_a ? 1 : 0; }
 void tc_matmul_destroy(void *h) { delete (TcMatmul *)h; }
 int tc_matmul_pack_b(void *h, const float *b, cudaStream_t s) {
     auto *t = (TcMatmul *)h;

@@ -7,7 +7,7 @@ import golden_cases as gc
 from conftest import rel_err, scale_err
 
 pytestmark = pytest.mark.gpu
-TOL, TOL_SCALE = 1e-3, 2e-4
+TOL, TOL_SCALE = 1e-3, 5e-5
 
 
 def dev(a):
