@@ -8,15 +8,15 @@ namespace petb200 {
 
 // implemented in igemm_tc.cu
 int tc_conv_create(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const int *k, const int *pad, const int *stride,
-                   const int *dil, int groups, int has_bias, int act, void **out, size_t *dev_bytes);
+                   const int *dil, int groups, int has_bias, int act, int passes, void **out, size_t *dev_bytes);
 void tc_conv_destroy(void *h);
 int tc_conv_set_weights(void *h, const float *w, cudaStream_t s);
 int tc_conv_run(void *h, const float *x, const float *bias, float *y, const int *win, cudaStream_t s);
 int tc_conv_row_pitch(void *h);
 void tc_conv_set_prof(void *h, long long *p);
 const char *tc_conv_variant(void *h);
-int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, int transB, int has_bias, int act, void **out,
-                     size_t *dev_bytes);
+int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, int transB, int has_bias, int act, int passes,
+                     void **out, size_t *dev_bytes);
 int tc_matmul_native_a(void *h);
 void tc_matmul_destroy(void *h);
 int tc_matmul_pack_b(void *h, const float *b, cudaStream_t s);
@@ -197,14 +197,11 @@ int make_conv_plan(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const i
         return fail(ctx, PETB200_ERR_INVALID, "conv plan: empty output");
     }
     c.oh0 = 0, c.ohn = c.OH, c.ow0 = 0, c.own = c.OW;
-    if (algo == PETB200_ALGO_TC_1XTF32) {
-        delete pl;
-        return fail(ctx, PETB200_ERR_UNSUPPORTED, "single-pass TF32 is not built");
-    }
     int rc = PETB200_ERR_UNSUPPORTED;
-    if (algo == PETB200_ALGO_AUTO || algo == PETB200_ALGO_TC_3XTF32) {
+    if (algo == PETB200_ALGO_AUTO || algo == PETB200_ALGO_TC_3XTF32 || algo == PETB200_ALGO_TC_1XTF32) {
         size_t bytes = 0;
-        rc = tc_conv_create(ctx, nsp, in_dims, f, k, pad, stride, dil, groups, has_bias, act, &pl->tc, &bytes);
+        rc = tc_conv_create(ctx, nsp, in_dims, f, k, pad, stride, dil, groups, has_bias, act, algo == PETB200_ALGO_TC_1XTF32 ? 1 : 3,
+                            &pl->tc, &bytes);
         if (rc == PETB200_OK) {
             pl->algo = PETB200_ALGO_TC_3XTF32;
             pl->kernel = tc_conv_variant(pl->tc);
@@ -218,7 +215,7 @@ int make_conv_plan(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const i
                 }
                 pl->device_bytes += n;
             }
-        } else if (algo == PETB200_ALGO_TC_3XTF32 || rc != PETB200_ERR_UNSUPPORTED) {
+        } else if (algo != PETB200_ALGO_AUTO || rc != PETB200_ERR_UNSUPPORTED) {
             delete pl;
             return rc;
         }
@@ -332,12 +329,13 @@ int make_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int
     pl->transA = transA != 0, pl->transB = transB != 0, pl->bs = b, pl->m = m, pl->n = n, pl->k = k;
     pl->has_bias = has_bias, pl->act = act;
     int rc = PETB200_ERR_UNSUPPORTED;
-    if (algo == PETB200_ALGO_AUTO || algo == PETB200_ALGO_TC_3XTF32) {
+    if (algo == PETB200_ALGO_AUTO || algo == PETB200_ALGO_TC_3XTF32 || algo == PETB200_ALGO_TC_1XTF32) {
         size_t bytes = 0;
-        rc = tc_matmul_create(ctx, b, m, n, k, pl->transA, pl->transB, has_bias, act, &pl->tc, &bytes);
+        rc = tc_matmul_create(ctx, b, m, n, k, pl->transA, pl->transB, has_bias, act, algo == PETB200_ALGO_TC_1XTF32 ? 1 : 3, &pl->tc,
+                              &bytes);
         if (rc == PETB200_OK) {
             pl->algo = PETB200_ALGO_TC_3XTF32;
-            pl->kernel = "tc_3xtf32_ts";
+            pl->kernel = algo == PETB200_ALGO_TC_1XTF32 ? "tc_1xtf32_ts" : "tc_3xtf32_ts";
             pl->device_bytes = bytes;
             pl->native_a = tc_matmul_native_a(pl->tc) != 0;
             if (!pl->native_a && (!pl->transA || m % 4 != 0)) {
@@ -347,7 +345,7 @@ int make_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int
                 }
                 pl->device_bytes += pl->at.bytes;
             }
-        } else if (algo == PETB200_ALGO_TC_3XTF32 || rc != PETB200_ERR_UNSUPPORTED) {
+        } else if (algo != PETB200_ALGO_AUTO || rc != PETB200_ERR_UNSUPPORTED) {
             delete pl;
             return rc;
         }

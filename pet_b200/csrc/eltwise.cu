@@ -173,6 +173,79 @@ __global__ void __launch_bounds__(256) k_layernorm(const float *__restrict__ x, 
     }
 }
 
+// Block-wide sum / max of one value per thread (blockDim.x = 256), result broadcast to every thread.
+__device__ __forceinline__ float block_sum(float v, float *red) {
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0)
+        red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        t += red[i];
+    return t;
+}
+__device__ __forceinline__ float block_max(float v, float *red) {
+    v = warp_max(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0)
+        red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i)
+        t = fmaxf(t, red[i]);
+    return t;
+}
+
+// One 256-thread block per row: used when there are too few rows to fill the GPU with one warp per row.
+__global__ void __launch_bounds__(256) k_softmax_block(const float *__restrict__ x, float *__restrict__ y, size_t rows, int cols) {
+    __shared__ float red[8];
+    for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const float *xp = x + r * (size_t)cols;
+        float *yp = y + r * (size_t)cols;
+        float mx = -INFINITY;
+        for (int i = threadIdx.x; i < cols; i += 256)
+            mx = fmaxf(mx, __ldg(xp + i));
+        mx = block_max(mx, red);
+        float den = 0.f;
+        for (int i = threadIdx.x; i < cols; i += 256)
+            den += expf(__ldg(xp + i) - mx);
+        const float inv = 1.f / block_sum(den, red);
+        for (int i = threadIdx.x; i < cols; i += 256)
+            yp[i] = expf(__ldg(xp + i) - mx) * inv;
+    }
+}
+
+__global__ void __launch_bounds__(256) k_layernorm_block(const float *__restrict__ x, const float *__restrict__ gamma,
+                                                         const float *__restrict__ beta, float *__restrict__ y, size_t rows,
+                                                         int cols, float eps) {
+    __shared__ float red[8];
+    for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const float *xp = x + r * (size_t)cols;
+        float *yp = y + r * (size_t)cols;
+        float s = 0.f;
+        for (int i = threadIdx.x; i < cols; i += 256)
+            s += __ldg(xp + i);
+        const float mean = block_sum(s, red) / (float)cols;
+        float v = 0.f;
+        for (int i = threadIdx.x; i < cols; i += 256) {
+            const float d = __ldg(xp + i) - mean;
+            v += d * d;
+        }
+        const float inv = rsqrtf(block_sum(v, red) / (float)cols + eps);
+        for (int i = threadIdx.x; i < cols; i += 256) {
+            float o = (__ldg(xp + i) - mean) * inv;
+            if (gamma)
+                o *= __ldg(gamma + i);
+            if (beta)
+                o += __ldg(beta + i);
+            yp[i] = o;
+        }
+    }
+}
+
 static int grid_for(petb200_ctx *ctx, size_t work_items, int per_block) {
     size_t blocks = (work_items + per_block - 1) / per_block;
     size_t cap = (size_t)ctx->sm_count * 16;
@@ -264,6 +337,10 @@ extern "C" int petb200_softmax_run(petb200_ctx *ctx, const float *x, float *y, s
         return fail(ctx, PETB200_ERR_INVALID, "softmax_run: bad arguments");
     if (!rows)
         return PETB200_OK;
+    if (cols >= 256 && rows <= (size_t)ctx->sm_count * 64) {
+        k_softmax_block<<<(int)std::min<size_t>(rows, (size_t)ctx->sm_count * 8), 256, 0, (cudaStream_t)stream>>>(x, y, rows, cols);
+        return launched(ctx, "k_softmax_block");
+    }
     k_softmax<<<grid_for(ctx, rows, 8), 256, 0, (cudaStream_t)stream>>>(x, y, rows, cols);
     return launched(ctx, "k_softmax");
 }
@@ -274,6 +351,11 @@ extern "C" int petb200_layernorm_run(petb200_ctx *ctx, const float *x, const flo
         return fail(ctx, PETB200_ERR_INVALID, "layernorm_run: bad arguments");
     if (!rows)
         return PETB200_OK;
+    if (cols >= 256 && rows <= (size_t)ctx->sm_count * 64) {
+        k_layernorm_block<<<(int)std::min<size_t>(rows, (size_t)ctx->sm_count * 8), 256, 0, (cudaStream_t)stream>>>(x, gamma, beta, y, rows,
+                                                                                                           cols, eps);
+        return launched(ctx, "k_layernorm_block");
+    }
     k_layernorm<<<grid_for(ctx, rows, 8), 256, 0, (cudaStream_t)stream>>>(x, gamma, beta, y, rows, cols, eps);
     return launched(ctx, "k_layernorm");
 }

@@ -31,7 +31,7 @@ namespace petb200 {
 constexpr int kTileM = 128;
 constexpr int kStageK = 32;               // fp32/TF32 values per K stage = one 128-byte swizzle row
 constexpr int kAHalfBytes = kTileM * 128; // one 128 x 32 operand tile
-constexpr int kThreads = 224;
+constexpr int kThreads = 352;   // warps: 0 B producer, 1 MMA, 2 raw producer, 3-6 and 7-10 two transform/epilogue sets
 constexpr int kMaxNB = 6;
 constexpr int kMaxNR = 6;
 
@@ -109,20 +109,25 @@ template <int ACT> __device__ __forceinline__ float act_fn(float v) {
 // TMEM accumulator rows -> (+bias, activation) -> global.  `yp` already points at this thread's pixel and the first
 // filter of the group; column j of the tile is filter f_tile0 + j.  The activation is a template parameter so that
 // the common no-activation case carries none of the transcendental code.
-template <int ACT>
+template <int ACT, int PASSES>
 __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile0, int Fg, bool valid, const float *bias,
-                                               float *yp, long long ys_f, bool vec_ok, int dbg, float *stage, int nvalid_warp, float *ybase_warp) {
+                                               float *yp, long long ys_f, bool vec_ok, int dbg, float *stage, int nvalid_warp, float *ybase_warp,
+                                               int col0, int col1) {
     uint32_t r[32], nx[32], sm[32];
-    ptx::tmem_ld_32x32(tacc, nx);
-    ptx::tmem_ld_32x32(tacc + 128u, sm);
-    for (int cc = 0; cc < BN; cc += 32) {
+    if (col0 >= col1)
+        return;
+    ptx::tmem_ld_32x32(tacc + (uint32_t)col0, nx);
+    if (PASSES == 3)
+        ptx::tmem_ld_32x32(tacc + 128u + (uint32_t)col0, sm);
+    for (int cc = col0; cc < col1; cc += 32) {
         ptx::tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) // hi*hi sum + (lo*hi + hi*lo) sum, one rounded fp32 add
-            r[j] = __float_as_uint(__uint_as_float(nx[j]) + __uint_as_float(sm[j]));
-        if (cc + 32 < BN) { // in flight while this chunk is stored
+            r[j] = PASSES == 3 ? __float_as_uint(__uint_as_float(nx[j]) + __uint_as_float(sm[j])) : nx[j];
+        if (cc + 32 < col1) { // in flight while this chunk is stored
             ptx::tmem_ld_32x32(tacc + (uint32_t)(cc + 32), nx);
-            ptx::tmem_ld_32x32(tacc + 128u + (uint32_t)(cc + 32), sm);
+            if (PASSES == 3)
+                ptx::tmem_ld_32x32(tacc + 128u + (uint32_t)(cc + 32), sm);
         }
         if (dbg || (stage == nullptr && !valid))
             continue;
@@ -174,7 +179,7 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile
     }
 }
 
-template <bool A_TMEM, bool A_KMAJOR>
+template <bool A_TMEM, bool A_KMAJOR, int PASSES>
 __global__ void __launch_bounds__(kThreads, 1)
 k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_bhi,
         const __grid_constant__ CUtensorMap tmap_blo, const IgemmParams P) {
@@ -207,7 +212,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     if (threadIdx.x == 0) {
         for (int i = 0; i < kMaxNR; ++i) {
             ptx::mbar_init(raw_full + i, 1);
-            ptx::mbar_init(raw_empty + i, 4);
+            ptx::mbar_init(raw_empty + i, 8);
         }
         for (int i = 0; i < kMaxNB; ++i) {
             ptx::mbar_init(b_full + i, 1);
@@ -274,9 +279,10 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 if (!ptx::mbar_wait(b_empty + sb, pb, abort_flag))
                     break;
                 uint8_t *dst = sB + (size_t)sb * 2 * b_half;
-                ptx::mbar_expect_tx(b_full + sb, 2u * b_half);
+                ptx::mbar_expect_tx(b_full + sb, (PASSES == 3 ? 2u : 1u) * b_half);
                 ptx::tma_load_2d(dst, &tmap_bhi, b_full + sb, (c0 * P.spc + ks) * kStageK, row0);
-                ptx::tma_load_2d(dst + b_half, &tmap_blo, b_full + sb, (c0 * P.spc + ks) * kStageK, row0);
+                if (PASSES == 3)
+                    ptx::tma_load_2d(dst + b_half, &tmap_blo, b_full + sb, (c0 * P.spc + ks) * kStageK, row0);
                 if (++sb == P.NB) {
                     sb = 0;
                     pb ^= 1u;
@@ -324,19 +330,21 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         uint32_t pa = 0, pb = 0;
         long long t_wa = 0, t_wb = 0;
         const long long t_begin = P.prof ? clock64() : 0;
-        bool ok = true;
+        bool ok = true, ready_next = false;
         for (int ks = 0; ks < KS; ++ks) {
-            if (P.prof) {
-                const long long q0c = clock64();
-                ok = ptx::mbar_wait(a_full + sa, pa, abort_flag);
-                const long long q1c = clock64();
-                ok = ok && ptx::mbar_wait(b_full + sb, pb, abort_flag);
-                t_wa += q1c - q0c;
-                t_wb += clock64() - q1c;
-            } else {
-                ok = ptx::mbar_wait(a_full + sa, pa, abort_flag) && ptx::mbar_wait(b_full + sb, pb, abort_flag);
+            if (!ready_next) { // not already seen complete by the poll issued in the shadow of the previous stage's MMAs
+                if (P.prof) {
+                    const long long q0c = clock64();
+                    ok = ptx::mbar_wait(a_full + sa, pa, abort_flag);
+                    const long long q1c = clock64();
+                    ok = ok && ptx::mbar_wait(b_full + sb, pb, abort_flag);
+                    t_wa += q1c - q0c;
+                    t_wb += clock64() - q1c;
+                } else {
+                    ok = ptx::mbar_wait(a_full + sa, pa, abort_flag) && ptx::mbar_wait(b_full + sb, pb, abort_flag);
+                }
+                ok = __all_sync(0xffffffffu, ok);
             }
-            ok = __all_sync(0xffffffffu, ok);
             if (!ok)
                 break;
             ptx::tc_fence_after();
@@ -345,43 +353,90 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             const uint32_t ahi_t = tmem_base + 256u + (uint32_t)sa * 64u, alo_t = ahi_t + 32u;
             const uint64_t ahi_s = adesc0 + (uint64_t)((uint32_t)sa * 2u * (kAHalfBytes >> 4));
             const uint64_t alo_s = ahi_s + (kAHalfBytes >> 4);
+            // next stage's ring positions, polled (non-blocking) while this stage's last MMAs are still queued
+            int nsa = sa + 1, nsb = sb + 1;
+            uint32_t npa = pa, npb = pb;
+            if (nsa == P.NA) {
+                nsa = 0;
+                npa ^= 1u;
+            }
+            if (nsb == P.NB) {
+                nsb = 0;
+                npb ^= 1u;
+            }
             if (ptx::elect_one()) {
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
+                for (int kk = 0; kk < 3; ++kk) {
+                    const uint32_t acc_kk = kk == 0 ? accumulate : 1u;
                     // The two cross terms go to their own accumulator: the tensor core truncates (rounds toward zero) its
                     // accumulator after every MMA, a bias proportional to the accumulator's magnitude; keeping the small
                     // terms away from the big sum removes two thirds of those truncations from it.
-                    if (A_TMEM) {
-                        ptx::mma_tf32_ts(tmem_small, alo_t + kk * 8, bhi + 2 * kk, idesc, accumulate);
+                    if (PASSES == 3) {
+                        if (A_TMEM) {
+                            ptx::mma_tf32_ts(tmem_small, alo_t + kk * 8, bhi + 2 * kk, idesc, acc_kk);
+                        } else {
+                            ptx::mma_tf32_ss(tmem_small, alo_s + 2 * kk, bhi + 2 * kk, idesc, acc_kk);
+                        }
                     } else {
-                        ptx::mma_tf32_ss(tmem_small, alo_s + 2 * kk, bhi + 2 * kk, idesc, accumulate);
+                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, acc_kk); // single TF32 pass
                     }
                     if (kk == 0 && prev_sa >= 0) { // release the previous stage once this stage's first MMA is queued
                         ptx::mma_commit(a_empty + prev_sa);
                         ptx::mma_commit(b_empty + prev_sb);
                     }
-                    if (A_TMEM) {
+                    if (PASSES != 3) {
+                        // nothing more for a single pass
+                    } else if (A_TMEM) {
                         ptx::mma_tf32_ts(tmem_small, ahi_t + kk * 8, blo + 2 * kk, idesc, 1u);
-                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, accumulate);
+                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, acc_kk);
                     } else {
                         ptx::mma_tf32_ss(tmem_small, ahi_s + 2 * kk, blo + 2 * kk, idesc, 1u);
-                        ptx::mma_tf32_ss(tmem_base, ahi_s + 2 * kk, bhi + 2 * kk, idesc, accumulate);
+                        ptx::mma_tf32_ss(tmem_base, ahi_s + 2 * kk, bhi + 2 * kk, idesc, acc_kk);
                     }
-                    accumulate = 1u;
+                }
+            }
+            __syncwarp();
+            ready_next = (ks + 1 < KS) && ptx::mbar_try_wait(a_full + nsa, npa) && ptx::mbar_try_wait(b_full + nsb, npb);
+            ready_next = __all_sync(0xffffffffu, ready_next);
+            if (ptx::elect_one()) {
+                {
+                    const int kk = 3;
+                    const uint32_t acc_kk = 1u;
+                    // The two cross terms go to their own accumulator: the tensor core truncates (rounds toward zero) its
+                    // accumulator after every MMA, a bias proportional to the accumulator's magnitude; keeping the small
+                    // terms away from the big sum removes two thirds of those truncations from it.
+                    if (PASSES == 3) {
+                        if (A_TMEM) {
+                            ptx::mma_tf32_ts(tmem_small, alo_t + kk * 8, bhi + 2 * kk, idesc, acc_kk);
+                        } else {
+                            ptx::mma_tf32_ss(tmem_small, alo_s + 2 * kk, bhi + 2 * kk, idesc, acc_kk);
+                        }
+                    } else {
+                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, acc_kk); // single TF32 pass
+                    }
+                    if (kk == 0 && prev_sa >= 0) { // release the previous stage once this stage's first MMA is queued
+                        ptx::mma_commit(a_empty + prev_sa);
+                        ptx::mma_commit(b_empty + prev_sb);
+                    }
+                    if (PASSES != 3) {
+                        // nothing more for a single pass
+                    } else if (A_TMEM) {
+                        ptx::mma_tf32_ts(tmem_small, ahi_t + kk * 8, blo + 2 * kk, idesc, 1u);
+                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, acc_kk);
+                    } else {
+                        ptx::mma_tf32_ss(tmem_small, ahi_s + 2 * kk, blo + 2 * kk, idesc, 1u);
+                        ptx::mma_tf32_ss(tmem_base, ahi_s + 2 * kk, bhi + 2 * kk, idesc, acc_kk);
+                    }
                 }
             }
             __syncwarp();
             accumulate = 1u;
             prev_sa = sa;
             prev_sb = sb;
-            if (++sa == P.NA) {
-                sa = 0;
-                pa ^= 1u;
-            }
-            if (++sb == P.NB) {
-                sb = 0;
-                pb ^= 1u;
-            }
+            sa = nsa;
+            sb = nsb;
+            pa = npa;
+            pb = npb;
         }
         if (ptx::elect_one()) {
             if (ok && prev_sa >= 0) {
@@ -399,7 +454,10 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             pr[2] = clock64() - t_begin;
         }
     } else {
-        // ---------------- transform + epilogue (warps 3..6) ----------------
+        // ---------------- transform + epilogue: two sets of four warps (3..6 and 7..10) ----------------
+        // The per-stage chain  wait -> gather -> tcgen05.st -> wait::st -> arrive  is latency bound (~600 cycles);
+        // two sets taking alternate K stages double the rate at which A stages are produced.
+        const int tset = (warp - 3) >> 2;     // 0 or 1
         const int quarter = warp & 3;         // TMEM lane quarter this warp may access
         const int p = quarter * 32 + lane;    // pixel row inside the tile
         bool valid;
@@ -441,8 +499,6 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         bool alive = true;
         long long t_we = 0, t_wr = 0;
         const long long t_begin = P.prof ? clock64() : 0;
-        int sa = 0;
-        uint32_t pa = 1; // first pass over the ring: every slot is free
         int rb = 0;
         uint32_t prw = 0;
         for (int ch = 0; ch < c1 - c0 && alive; ++ch) {
@@ -452,6 +508,11 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 t_wr += clock64() - cr0;
             const float *raw = reinterpret_cast<const float *>(sRaw + (size_t)rb * P.raw_bytes) + base_p;
             for (int st = 0; st < P.spc && alive; ++st) {
+                const int ks = ch * P.spc + st;
+                if ((ks & 1) != tset)
+                    continue; // the other set's stage
+                const int sa = ks % P.NA;
+                const uint32_t pa = (uint32_t)(((ks / P.NA) & 1) ^ 1); // first pass over the ring: every slot is free
                 const long long ce0 = P.prof ? clock64() : 0;
                 alive = ptx::mbar_wait(a_empty + sa, pa, abort_flag);
                 if (P.prof)
@@ -474,18 +535,26 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                             v0 = o.x >= 0 ? raw[o.x] : 0.f, v1 = o.y >= 0 ? raw[o.y] : 0.f;
                             v2 = o.z >= 0 ? raw[o.z] : 0.f, v3 = o.w >= 0 ? raw[o.w] : 0.f;
                         }
-                        hi[4 * c4 + 0] = __float_as_uint(v0) & 0xffffe000u;
-                        hi[4 * c4 + 1] = __float_as_uint(v1) & 0xffffe000u;
-                        hi[4 * c4 + 2] = __float_as_uint(v2) & 0xffffe000u;
-                        hi[4 * c4 + 3] = __float_as_uint(v3) & 0xffffe000u;
-                        lo[4 * c4 + 0] = __float_as_uint(v0 - __uint_as_float(hi[4 * c4 + 0]));
-                        lo[4 * c4 + 1] = __float_as_uint(v1 - __uint_as_float(hi[4 * c4 + 1]));
-                        lo[4 * c4 + 2] = __float_as_uint(v2 - __uint_as_float(hi[4 * c4 + 2]));
-                        lo[4 * c4 + 3] = __float_as_uint(v3 - __uint_as_float(hi[4 * c4 + 3]));
+                        if (PASSES == 3) {
+                            hi[4 * c4 + 0] = __float_as_uint(v0) & 0xffffe000u;
+                            hi[4 * c4 + 1] = __float_as_uint(v1) & 0xffffe000u;
+                            hi[4 * c4 + 2] = __float_as_uint(v2) & 0xffffe000u;
+                            hi[4 * c4 + 3] = __float_as_uint(v3) & 0xffffe000u;
+                            lo[4 * c4 + 0] = __float_as_uint(v0 - __uint_as_float(hi[4 * c4 + 0]));
+                            lo[4 * c4 + 1] = __float_as_uint(v1 - __uint_as_float(hi[4 * c4 + 1]));
+                            lo[4 * c4 + 2] = __float_as_uint(v2 - __uint_as_float(hi[4 * c4 + 2]));
+                            lo[4 * c4 + 3] = __float_as_uint(v3 - __uint_as_float(hi[4 * c4 + 3]));
+                        } else { // single pass: round to nearest TF32 instead of letting the tensor core truncate
+                            hi[4 * c4 + 0] = ptx::cvt_rna_tf32(v0);
+                            hi[4 * c4 + 1] = ptx::cvt_rna_tf32(v1);
+                            hi[4 * c4 + 2] = ptx::cvt_rna_tf32(v2);
+                            hi[4 * c4 + 3] = ptx::cvt_rna_tf32(v3);
+                        }
                     }
                     const uint32_t t = tmem_base + ((uint32_t)(quarter * 32) << 16) + 256u + (uint32_t)sa * 64u;
                     ptx::tmem_st_32x32(t, hi);
-                    ptx::tmem_st_32x32(t + 32u, lo);
+                    if (PASSES == 3)
+                        ptx::tmem_st_32x32(t + 32u, lo);
                     ptx::tmem_st_wait();
                     ptx::tc_fence_before();
                 } else {
@@ -514,10 +583,6 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 __syncwarp();
                 if (lane == 0)
                     ptx::mbar_arrive(a_full + sa);
-                if (++sa == P.NA) {
-                    sa = 0;
-                    pa ^= 1u;
-                }
             }
             __syncwarp();
             if (lane == 0 && alive)
@@ -556,28 +621,33 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 nvalid_warp = __popc(__ballot_sync(0xffffffffu, valid));
                 if (nvalid_warp > 0)
                     stage = reinterpret_cast<float *>(sB) + (warp - 3) * 1024; // B stages are idle once the accumulator is complete
+                if ((uint32_t)(warp - 3 + 1) * 4096u > (uint32_t)P.NB * (PASSES == 3 ? 2u : 1u) * b_half)
+                    stage = nullptr; // not enough idle shared memory for this warp's block
                 else
                     stage = nullptr;
             }
+            // the two sets split the tile's columns (whole 32-column blocks)
+            const int nblk = P.BN / 32, half_blk = (nblk + 1) / 2;
+            const int col0 = tset == 0 ? 0 : half_blk * 32, col1 = tset == 0 ? half_blk * 32 : P.BN;
             switch (P.ksplit > 1 ? PETB200_ACT_NONE : P.act) {
             case PETB200_ACT_RELU:
-                epilogue_store<PETB200_ACT_RELU>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp);
+                epilogue_store<PETB200_ACT_RELU, PASSES>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp, col0, col1);
                 break;
             case PETB200_ACT_SIGMOID:
-                epilogue_store<PETB200_ACT_SIGMOID>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp);
+                epilogue_store<PETB200_ACT_SIGMOID, PASSES>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp, col0, col1);
                 break;
             case PETB200_ACT_TANH:
-                epilogue_store<PETB200_ACT_TANH>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp);
+                epilogue_store<PETB200_ACT_TANH, PASSES>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp, col0, col1);
                 break;
             case PETB200_ACT_GELU:
-                epilogue_store<PETB200_ACT_GELU>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp);
+                epilogue_store<PETB200_ACT_GELU, PASSES>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp, col0, col1);
                 break;
             default:
-                epilogue_store<PETB200_ACT_NONE>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp);
+                epilogue_store<PETB200_ACT_NONE, PASSES>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp, col0, col1);
                 break;
             }
         }
-        if (P.prof && threadIdx.x == 96) {
+        if (P.prof && threadIdx.x == 96) { // lane 0 of warp 3 (transform set 0)
             long long *pr = P.prof + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8;
             pr[3] = t_we;
             pr[4] = t_wr;
@@ -608,7 +678,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
 // -------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k_pack_conv_w(const float *__restrict__ w, float *__restrict__ hi,
                                                      float *__restrict__ lo, int F, int cpg, int T, int BC, int Kc_pad,
-                                                     int nchunks) {
+                                                     int nchunks, int rna) {
     const long long Ktot = (long long)Kc_pad * nchunks;
     const long long total = (long long)F * Ktot;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -620,14 +690,14 @@ __global__ void __launch_bounds__(256) k_pack_conv_w(const float *__restrict__ w
         float v = 0.f;
         if (tap < T && c < cpg)
             v = __ldg(w + ((long long)f * cpg + c) * T + tap);
-        const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+        const float h = rna ? __uint_as_float(ptx::cvt_rna_tf32(v)) : __uint_as_float(__float_as_uint(v) & 0xffffe000u);
         hi[i] = h;
         lo[i] = v - h;
     }
 }
 
 __global__ void __launch_bounds__(256) k_pack_mm_b(const float *__restrict__ b, float *__restrict__ hi,
-                                                   float *__restrict__ lo, int bs, int n, int k, int Kpad, int transB) {
+                                                   float *__restrict__ lo, int bs, int n, int k, int Kpad, int transB, int rna) {
     const long long total = (long long)bs * n * Kpad;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int kk = (int)(i % Kpad);
@@ -637,7 +707,7 @@ __global__ void __launch_bounds__(256) k_pack_mm_b(const float *__restrict__ b, 
         float v = 0.f;
         if (kk < k)
             v = transB ? __ldg(b + ((long long)bb * n + nn) * k + kk) : __ldg(b + ((long long)bb * k + kk) * n + nn);
-        const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+        const float h = rna ? __uint_as_float(ptx::cvt_rna_tf32(v)) : __uint_as_float(__float_as_uint(v) & 0xffffe000u);
         hi[i] = h;
         lo[i] = v - h;
     }
@@ -782,12 +852,16 @@ struct TcCore {
         p.prof = prof;
         { static int d = -1; if (d < 0) { const char *e = getenv("PETB200_TC_DBG"); d = e ? atoi(e) : 0; } p.dbg = d; }
         p.has_bias = (P.has_bias && bias) ? 1 : 0;
-        if (P.a_kmajor)
-            k_igemm<true, true><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
+        if (single_pass && P.a_kmajor)
+            k_igemm<true, true, 1><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
+        else if (single_pass)
+            k_igemm<true, false, 1><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
+        else if (P.a_kmajor)
+            k_igemm<true, true, 3><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
         else if (a_tmem)
-            k_igemm<true, false><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
+            k_igemm<true, false, 3><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
         else
-            k_igemm<false, false><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
+            k_igemm<false, false, 3><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
         rc = launched(ctx, "k_igemm");
         if (rc || P.ksplit == 1)
             return rc;
@@ -893,7 +967,7 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "raw activation box %dx%dx%dx%d exceeds the TMA box limit", P.RN, P.RD, P.RH, P.RW);
     const int T = g.T3[0] * g.T3[1] * g.T3[2];
     const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 1024; // alignment slack
-    core.a_tmem = env_int("PETB200_TC_A_TMEM", 1) != 0;
+    core.a_tmem = core.single_pass || env_int("PETB200_TC_A_TMEM", 1) != 0; // the single-pass variant exists for TS only
     if (core.a_tmem && BN > 256)
         return fail(ctx, PETB200_ERR_INVALID, "TS variant supports BN <= 256");
     // channels per chunk: 32, or more for filters with few taps so that one raw tile still feeds several K stages
@@ -995,10 +1069,14 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     static bool attr_set = false;
     if (!attr_set) {
         const int lim = (int)std::min<size_t>(ctx->smem_optin, 227 * 1024);
-        cudaError_t e1 = cudaFuncSetAttribute(k_igemm<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
-        cudaError_t e2 = cudaFuncSetAttribute(k_igemm<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        cudaError_t e1 = cudaFuncSetAttribute(k_igemm<true, false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        cudaError_t e2 = cudaFuncSetAttribute(k_igemm<false, false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
         if (e1 == cudaSuccess)
-            e1 = cudaFuncSetAttribute(k_igemm<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+            e1 = cudaFuncSetAttribute(k_igemm<true, true, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        if (e1 == cudaSuccess)
+            e1 = cudaFuncSetAttribute(k_igemm<true, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        if (e1 == cudaSuccess)
+            e1 = cudaFuncSetAttribute(k_igemm<true, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
         if (e1 != cudaSuccess || e2 != cudaSuccess)
             return fail(ctx, PETB200_ERR_CUDA, "cudaFuncSetAttribute(%d bytes) failed: %s", lim,
                         cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
@@ -1020,7 +1098,7 @@ struct TcConv {
 };
 
 int tc_conv_create(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const int *k, const int *pad, const int *stride,
-                   const int *dil, int groups, int has_bias, int act, void **out, size_t *dev_bytes) {
+                   const int *dil, int groups, int has_bias, int act, int passes, void **out, size_t *dev_bytes) {
     if (ctx->cc_major != 10)
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "tcgen05 kernels need compute capability 10.x, device has %d.%d", ctx->cc_major, ctx->cc_minor);
     auto *t = new TcConv();
@@ -1062,6 +1140,7 @@ int tc_conv_create(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const i
     t->has_bias = has_bias;
     t->act = act;
     t->full.ctx = ctx;
+    t->full.single_pass = passes == 1;
     const long long plane = (long long)g.OD * g.OH * g.OW;
     int rc = tc_configure(ctx, t->full, g, 0, g.OH, 0, g.OW, 0, g.N, (long long)g.F * plane, plane, 1, has_bias, act);
     if (rc) {
@@ -1094,7 +1173,7 @@ int tc_conv_set_weights(void *h, const float *w, cudaStream_t s) {
     long long total = (long long)t->g.F * c.Ktot;
     int blocks = (int)std::min<long long>((total + 255) / 256, (long long)c.ctx->sm_count * 16);
     k_pack_conv_w<<<blocks, 256, 0, s>>>(w, (float *)c.whi.p, (float *)c.wlo.p, t->g.F, cpg, T, c.P.BC, c.P.spc * kStageK,
-                                         c.P.nchunks);
+                                         c.P.nchunks, c.single_pass);
     c.weights_ready = true;
     return launched(c.ctx, "k_pack_conv_w");
 }
@@ -1113,6 +1192,7 @@ int tc_conv_run(void *h, const float *x, const float *bias, float *y, const int 
     if (!wc) {
         wc = new TcCore();
         wc->ctx = t->full.ctx;
+        wc->single_pass = t->full.single_pass;
         const long long plane = (long long)g.OD * g.OH * g.OW;
         // A window must consume K in exactly the order of the full operator (same BC / chunking), otherwise the
         // two would round differently; the raw box only shrinks for a window, so the full plan's BC always fits.
@@ -1142,7 +1222,10 @@ void tc_conv_out_dims(void *h, int *d5) {
 }
 void tc_conv_set_prof(void *h, long long *p) { ((TcConv *)h)->full.prof = p; }
 int tc_conv_row_pitch(void *h) { return ((TcConv *)h)->g.Wst; }
-const char *tc_conv_variant(void *h) { return ((TcConv *)h)->full.a_tmem ? "tc_3xtf32_ts" : "tc_3xtf32_ss"; }
+const char *tc_conv_variant(void *h) {
+    const TcCore &c = ((TcConv *)h)->full;
+    return c.single_pass ? "tc_1xtf32_ts" : (c.a_tmem ? "tc_3xtf32_ts" : "tc_3xtf32_ss");
+}
 
 // ---- matmul on the same kernel ------------------------------------------------------------------------------
 // C[b,m,n] = A·B with A supplied as [b,k,m] (i.e. transA): a 1x1 "convolution" whose image is one batch entry,
@@ -1230,8 +1313,8 @@ static int tc_configure_kmajor(petb200_ctx *ctx, TcCore &core, int bs, int m, in
     return matmul_finish(ctx, core, bs, m, n, P.tpi, act);
 }
 
-int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, int transB, int has_bias, int act, void **out,
-                     size_t *dev_bytes) {
+int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, int transB, int has_bias, int act, int passes,
+                     void **out, size_t *dev_bytes) {
     const int mp = (m + 3) / 4 * 4; // row pitch of A as [b][k][mp]
     if (ctx->cc_major != 10)
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "tcgen05 kernels need compute capability 10.x");
@@ -1242,6 +1325,7 @@ int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, 
     t->k = k;
     t->transB = transB;
     t->core.ctx = ctx;
+    t->core.single_pass = passes == 1;
     int rc;
     if (!transA && k % 4 == 0 && env_int("PETB200_TC_KMAJOR", 1)) {
         // make sure the shared-memory attribute of every instantiation is raised (done inside tc_configure)
@@ -1308,7 +1392,7 @@ int tc_matmul_pack_b(void *h, const float *b, cudaStream_t s) {
     TcCore &c = t->core;
     long long total = (long long)t->bs * t->n * c.Ktot;
     int blocks = (int)std::min<long long>((total + 255) / 256, (long long)c.ctx->sm_count * 16);
-    k_pack_mm_b<<<blocks, 256, 0, s>>>(b, (float *)c.whi.p, (float *)c.wlo.p, t->bs, t->n, t->k, (int)c.Ktot, t->transB);
+    k_pack_mm_b<<<blocks, 256, 0, s>>>(b, (float *)c.whi.p, (float *)c.wlo.p, t->bs, t->n, t->k, (int)c.Ktot, t->transB, c.single_pass);
     c.weights_ready = true;
     return launched(c.ctx, "k_pack_mm_b");
 }

@@ -142,6 +142,12 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+__device__ __forceinline__ uint32_t cvt_rna_tf32(float v) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
+    return u;
+}
+
 // ---- descriptors ------------------------------------------------------------------------------------------
 // K-major operand tile in the 128-byte-swizzled canonical layout: rows of 128 bytes (32 TF32 values along K),
 // groups of 8 rows form a 1024-byte swizzle atom, 16-byte chunk c of row r is stored at chunk c ^ (r & 7).

@@ -168,3 +168,22 @@ def test_device_status_is_clean_and_timing_entry_point_works(ctx):
     ms = plan.time(rounds=20, warmup=5)
     assert 0 < ms < 5
     ctx.sync_check()
+
+
+def test_single_pass_tf32_option(ctx, oracle):
+    """PETB200_ALGO_TC_1XTF32: one TF32 pass with round-to-nearest operands, the accuracy class of cuDNN's default
+    math mode (what the reference's cudnnConvolutionForward gets on this GPU).  Looser bound, stated here: 5e-3."""
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((2, 64, 28, 28)).astype(np.float32)
+    w = (rng.standard_normal((96, 64, 3, 3)) * np.sqrt(2.0 / 576)).astype(np.float32)
+    want = oracle.conv2d(x, w, pad=(1, 1), wide=True)
+    plan = ctx.conv2d_plan(x.shape, w.shape, 1, 1, algo="tc_1xtf32")
+    assert plan.kernel == "tc_1xtf32_ts"
+    ctx.conv2d_set_weights(plan, dev(w))
+    got = ctx.conv2d_run(plan, dev(x)).cpu().numpy()
+    ctx.sync_check()
+    assert rel_err(got, want) <= 5e-3 and scale_err(got, want) <= 1e-3
+    a = rng.standard_normal((1, 128, 768)).astype(np.float32)
+    b = (rng.standard_normal((1, 768, 256)) / 27.7).astype(np.float32)
+    got = ctx.matmul(dev(a), dev(b), algo="tc_1xtf32").cpu().numpy()
+    assert rel_err(got, oracle.matmul(a, b)) <= 5e-3
