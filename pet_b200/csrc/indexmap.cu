@@ -178,19 +178,26 @@ __global__ void __launch_bounds__(256) k_tile(const uint32_t *__restrict__ in, u
             }
         }
     }
-    for (unsigned blk = first; blk < last; ++blk) {
+    // Software pipeline: the loads of tile t+1 are issued before tile t is written out, so that reads stay in flight
+    // during the store phase.
+    auto valid_of = [&]() {
         int chunk_idx = 0;
 #pragma unroll
         for (int d = 0; d < kMaxDigits; ++d)
             if (d == t.chunk_digit)
                 chunk_idx = idx[d];
-        const int valid = t.ck >= 0 ? min(t.text[t.ck], t.chunk_ext - chunk_idx * t.text[t.ck]) : 0x7fffffff;
+        return t.ck >= 0 ? min(t.text[t.ck], t.chunk_ext - chunk_idx * t.text[t.ck]) : 0x7fffffff;
+    };
+    uint32_t v[kTileEPT];
+    int valid = valid_of();
+    {
         const uint32_t *ip = in + io;
-        uint32_t v[kTileEPT];
 #pragma unroll
         for (int u = 0; u < kTileEPT; ++u)
             if (threadIdx.x + u * 256 < t.tile_elems && (int)(ls[u] >> 16) < valid)
                 v[u] = __ldg(ip + li[u]);
+    }
+    for (unsigned blk = first; blk < last; ++blk) {
 #pragma unroll
         for (int u = 0; u < kTileEPT; ++u)
             if (threadIdx.x + u * 256 < t.tile_elems && (int)(ls[u] >> 16) < valid)
@@ -198,13 +205,6 @@ __global__ void __launch_bounds__(256) k_tile(const uint32_t *__restrict__ in, u
         __syncthreads();
         const int lim = (t.ck == 0) ? valid * t.inner_ck : t.tile_elems;
         uint32_t *op = out + oo;
-#pragma unroll
-        for (int u = 0; u < kTileEPT; ++u) {
-            const int e = threadIdx.x + u * 256;
-            if (e < lim)
-                op[lo[u]] = tile[e + (e >> 5)];
-        }
-        __syncthreads();
         // odometer: next tile
         bool carry = true;
 #pragma unroll
@@ -220,6 +220,21 @@ __global__ void __launch_bounds__(256) k_tile(const uint32_t *__restrict__ in, u
                     idx[d] = 0;
                 }
             }
+        if (blk + 1 < last) { // prefetch the next tile into registers
+            valid = valid_of();
+            const uint32_t *ip = in + io;
+#pragma unroll
+            for (int u = 0; u < kTileEPT; ++u)
+                if (threadIdx.x + u * 256 < t.tile_elems && (int)(ls[u] >> 16) < valid)
+                    v[u] = __ldg(ip + li[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < kTileEPT; ++u) {
+            const int e = threadIdx.x + u * 256;
+            if (e < lim)
+                op[lo[u]] = tile[e + (e >> 5)];
+        }
+        __syncthreads();
     }
 }
 
@@ -322,6 +337,47 @@ static int finalize_plan(petb200_ctx *ctx, LayoutPlan *pl, std::vector<Digit> di
     }
     // tile: the innermost output digit is not contiguous in the input
     if (!m.guarded && m.ostr[last] == 1 && m.istr[last] != 1 && m.total < (1ll << 31)) {
+        // Long contiguous digits are first split (exactly, by a divisor) into an outer and a 32..64-wide inner digit, so
+        // that a tile can take a moderate run on BOTH sides instead of one very long run on one side only.
+        auto split_digit = [&](int i) {
+            if (m.nd >= kMaxDigits || m.ext[i] <= 128)
+                return false;
+            int c = 0;
+            for (int cand = 64; cand >= 32; --cand)
+                if (m.ext[i] % cand == 0) {
+                    c = cand;
+                    break;
+                }
+            if (!c)
+                return false;
+            for (int j = m.nd; j > i + 1; --j) {
+                m.ext[j] = m.ext[j - 1];
+                m.istr[j] = m.istr[j - 1];
+                m.ostr[j] = m.ostr[j - 1];
+                m.glo[j] = m.glo[j - 1];
+                m.ghi[j] = m.ghi[j - 1];
+            }
+            m.ext[i + 1] = c;
+            m.istr[i + 1] = m.istr[i];
+            m.ostr[i + 1] = m.ostr[i];
+            m.glo[i + 1] = 0;
+            m.ghi[i + 1] = c;
+            m.ext[i] /= c;
+            m.istr[i] *= c;
+            m.ostr[i] *= c;
+            m.ghi[i] = m.ext[i];
+            m.nd++;
+            return true;
+        };
+        int a_in = -1;
+        for (int i = 0; i < m.nd - 1; ++i)
+            if (m.istr[i] == 1)
+                a_in = i;
+        if (a_in >= 0 && m.ext[a_in] > 128 && m.ext[m.nd - 1] > 128) {
+            split_digit(m.nd - 1);
+            split_digit(a_in);
+        }
+        const int last = m.nd - 1; // shadows the outer `last`: the digit count may have grown
         std::vector<int> chosen; // indices into m, kept sorted at the end
         auto has = [&](int i) { return std::find(chosen.begin(), chosen.end(), i) != chosen.end(); };
         auto tile_size = [&]() {
