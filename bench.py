@@ -28,6 +28,7 @@ W_SHAPE = (512, 512, 3, 3)
 S2B = [(2, [0, 1, [-1, 2], 3], 2), (2, [[0, 2], 1, -1, 3], -2), (3, [0, 1, 2, [-1, 3]], 2), (3, [[0, 3], 1, 2, -1], -2)]
 B2S = [(0, [0, 1, 2, [-1, 3]], 2), (3, [0, 1, 2, [-1, 3]], -2), (0, [0, 1, [-1, 2], 3], 2), (2, [0, 1, [-1, 2], 3], -2)]
 CONV_FLOPS = 2.0 * 4 * 512 * 32 * 32 * 512 * 9          # algorithmic flops of the dense conv per step
+CONV_DRAM_TRAFFIC = 27.36e6   # bytes per launch, dram__bytes_read+write of the conv kernel (profiles/conv_tc3xtf32_dilated_layer.md)
 RING = 20                                               # distinct buffer sets cycled through: 20 x 8 MiB inputs > 126 MB L2
 CONFIG = {"workload": "dilated conv layer 512->512 64x64 d2 p2 fp32 batch 1, PET rewrite: space-to-batch -> dense 3x3 conv -> batch-to-space",
           "kernels_per_step": 3, "l2": f"ring of {RING} input/intermediate/output buffer sets (168 MB of inputs) cycled, larger than L2"}
@@ -307,7 +308,7 @@ def main():
                         "d2h_bytes_per_step": int(np.prod(b2s.out_shape)) * 4, "wall_ms_per_step": e2e_wall / args.steps},
                 "gpu_launches": int(launches), "clocks": clocks,
                 "roofline": {"bound": "tensor", "kernel": conv.kernel, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                             "frac": achieved / peak, "traffic": None, "peak_source": f"{pk_kind} bf16 sustained",
+                             "frac": achieved / peak, "traffic": CONV_DRAM_TRAFFIC, "peak_source": f"{pk_kind} bf16 sustained",
                              "launch_ms": conv_ms, "issued_tf32_tflops": 3 * achieved, "tf32_peak_est": peak / 2,
                              "frac_of_tf32_issue_peak": 3 * achieved / (peak / 2)}}
         if world == 1 and not args.no_config_latencies:
