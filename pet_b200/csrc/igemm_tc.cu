@@ -32,6 +32,7 @@ constexpr int kTileM = 128;
 constexpr int kStageK = 32;               // fp32/TF32 values per K stage = one 128-byte swizzle row
 constexpr int kAHalfBytes = kTileM * 128; // one 128 x 32 operand tile
 constexpr int kThreads = 352;   // warps: 0 B producer, 1 MMA, 2 raw producer, 3-6 and 7-10 two transform/epilogue sets
+constexpr int kProfSlots = 16; // tuning counters per CTA (see IgemmParams::prof)
 constexpr int kMaxNB = 6;
 constexpr int kMaxNR = 6;
 
@@ -60,7 +61,7 @@ struct IgemmParams {
     float *y;
     float *partial;
     int *status;
-    long long *prof; // optional per-CTA cycle counters (8 per CTA), for tuning only
+    long long *prof; // optional per-CTA counters (kProfSlots per CTA), for tuning only
     int dbg;         // tuning experiments (epilogue only): bit 0 = skip the global stores
 };
 
@@ -129,7 +130,7 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile
             if (PASSES == 3)
                 ptx::tmem_ld_32x32(tacc + 128u + (uint32_t)(cc + 32), sm);
         }
-        if (dbg || (stage == nullptr && !valid))
+        if ((dbg & 1) || (stage == nullptr && !valid))
             continue;
         const int f0 = f_tile0 + cc;
 #pragma unroll
@@ -201,6 +202,11 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     volatile int *abort_flag = reinterpret_cast<volatile int *>(acc_full + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    long long *prof_cta = nullptr; // wall-clock marks of this CTA (entry, prologue done, epilogue done, exit), tuning only
+    if (P.prof && threadIdx.x == 96) {
+        prof_cta = P.prof + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * kProfSlots;
+        prof_cta[8] = (long long)ptx::globaltimer_ns();
+    }
     const int ntile = blockIdx.y / P.ksplit;
     const int ksp = blockIdx.y - ntile * P.ksplit;
     const int zb = blockIdx.z;
@@ -239,6 +245,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (prof_cta)
+        prof_cta[9] = (long long)ptx::globaltimer_ns();
 
     // Tile origin in the input: first image, depth slice, row and (16-byte aligned) column of the raw box.
     int n_lo = 0, q0 = 0, unit0 = 0, z_start, y_start, x_start, w_zl = 0, w_yl = 0, w_tx = 0;
@@ -448,7 +456,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         }
         __syncwarp();
         if (lane == 0 && P.prof) {
-            long long *pr = P.prof + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8;
+            long long *pr = P.prof + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * kProfSlots;
             pr[0] = t_wa;
             pr[1] = t_wb;
             pr[2] = clock64() - t_begin;
@@ -621,10 +629,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 nvalid_warp = __popc(__ballot_sync(0xffffffffu, valid));
                 if (nvalid_warp > 0)
                     stage = reinterpret_cast<float *>(sB) + (warp - 3) * 1024; // B stages are idle once the accumulator is complete
-                if ((uint32_t)(warp - 3 + 1) * 4096u > (uint32_t)P.NB * (PASSES == 3 ? 2u : 1u) * b_half)
+                if ((uint32_t)(warp - 3 + 1) * 4096u > (uint32_t)P.NB * (PASSES == 3 ? 2u : 1u) * b_half || !(P.dbg & 2))
                     stage = nullptr; // not enough idle shared memory for this warp's block
-                else
-                    stage = nullptr;
             }
             // the two sets split the tile's columns (whole 32-column blocks)
             const int nblk = P.BN / 32, half_blk = (nblk + 1) / 2;
@@ -648,12 +654,13 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             }
         }
         if (P.prof && threadIdx.x == 96) { // lane 0 of warp 3 (transform set 0)
-            long long *pr = P.prof + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 8;
+            long long *pr = P.prof + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * kProfSlots;
             pr[3] = t_we;
             pr[4] = t_wr;
             pr[5] = t_loop;
             pr[6] = clock64() - t_epi0;
             pr[7] = t_epi0 - t_begin;
+            pr[10] = (long long)ptx::globaltimer_ns();
         }
     }
 
@@ -670,6 +677,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     __syncthreads();
     if (warp == 2)
         ptx::tmem_dealloc(tmem_base, tmem_cols);
+    if (prof_cta)
+        prof_cta[11] = (long long)ptx::globaltimer_ns();
 }
 
 // -------------------------------------------------------------------------------------------------------------
