@@ -48,7 +48,8 @@ struct IgemmParams {
     int z_is_batch;         // blockIdx.z: 0 = conv group, 1 = matmul batch
     int wide, row_tiles;    // wide mode: a tile is 128 consecutive pixels of ONE output row (rows wider than a tile)
     int tpi, ipt;           // otherwise: tiles per plane (plane larger than a tile) or whole planes per tile
-    int ksplit;             // K is split over this many CTAs (partial sums go to scratch, reduced by a second kernel)
+    int ksplit;             // K is split over this many CTAs: partial sums go to scratch, the CTA of a tile that
+                            // finishes last adds them up (in split order, so the result does not depend on which)
     long long part_stride;  // floats between the partial-sum copies
     int NA, NB, NR;         // ring depths: A stages, B stages, raw activation buffers
     int a_kmajor;           // matmul with row-major A: the raw tile is [128 rows][32 k], 128B-swizzled, one per K stage
@@ -60,6 +61,7 @@ struct IgemmParams {
     const float *bias;
     float *y;
     float *partial;
+    int *tickets;    // split-K: one arrival counter per output tile, zero between launches
     int *status;
     long long *prof; // optional per-CTA counters (kProfSlots per CTA), for tuning only
     int dbg;         // tuning experiments (epilogue only): bit 0 = skip the global stores
@@ -180,6 +182,64 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile
     }
 }
 
+// Split-K fix-up, run by the last CTA to arrive at an output tile: every epilogue thread re-reads the elements it stored
+// (its pixel row, half of the tile's columns) from all the partial copies, adds them in split order, and writes
+// act(sum + bias).  Partial sums were written by other SMs: they are read through L2 (ld.global.cg).
+template <int ACT>
+__device__ __forceinline__ void splitk_fixup(const float *part /*copy 0, at this thread's pixel, filter 0 of the group*/,
+                                             long long part_stride, int ksplit, int f_tile0, int Fg, bool valid,
+                                             const float *bias, float *yp, long long ys_f, bool vec_ok, int col0, int col1) {
+    if (!valid)
+        return;
+    for (int cc = col0; cc < col1; cc += 16) {
+        const int f0 = f_tile0 + cc;
+        if (f0 >= Fg)
+            break;
+        float acc[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            acc[j] = 0.f;
+        if (vec_ok) { // filters contiguous: 16-byte loads (Fg is a multiple of 4 here)
+#pragma unroll 4
+            for (int ks = 0; ks < ksplit; ++ks) {
+                const float4 *src = reinterpret_cast<const float4 *>(part + (long long)ks * part_stride + f0);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (f0 + 4 * j < Fg) {
+                        const float4 v = __ldcg(src + j);
+                        acc[4 * j] += v.x, acc[4 * j + 1] += v.y, acc[4 * j + 2] += v.z, acc[4 * j + 3] += v.w;
+                    }
+            }
+        } else {
+#pragma unroll 4
+            for (int ks = 0; ks < ksplit; ++ks) {
+                const float *src = part + (long long)ks * part_stride + (long long)f0 * ys_f;
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (f0 + j < Fg)
+                        acc[j] += __ldcg(src + (long long)j * ys_f);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            if (bias != nullptr && f0 + j < Fg)
+                acc[j] += __ldg(bias + f0 + j);
+            acc[j] = act_fn<ACT>(acc[j]);
+        }
+        if (vec_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4)
+                if (f0 + j < Fg)
+                    *reinterpret_cast<float4 *>(yp + f0 + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (f0 + j < Fg)
+                    yp[(long long)(f0 + j) * ys_f] = acc[j];
+        }
+    }
+}
+
 template <bool A_TMEM, bool A_KMAJOR, int PASSES>
 __global__ void __launch_bounds__(kThreads, 1)
 k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_bhi,
@@ -200,6 +260,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     uint64_t *acc_full = a_empty + 4;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(acc_full + 2);
+    volatile int *last_flag = reinterpret_cast<volatile int *>(acc_full + 3); // split-K: this CTA adds the partial sums up
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     long long *prof_cta = nullptr; // wall-clock marks of this CTA (entry, prologue done, epilogue done, exit), tuning only
@@ -605,15 +666,16 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         if (alive)
             alive = ptx::mbar_wait(acc_full, 0u, abort_flag);
         const long long t_epi0 = P.prof ? clock64() : 0;
+        const bool vec_ok = (P.ys_f == 1) && ((P.ys_p & 3) == 0) && ((P.ys_n & 3) == 0) && ((P.Fg & 3) == 0) &&
+                            ((reinterpret_cast<uintptr_t>(P.y) & 15) == 0) && ((P.part_stride & 3) == 0) &&
+                            ((reinterpret_cast<uintptr_t>(P.partial) & 15) == 0);
+        int col0 = 0, col1 = 0;
         if (alive) {
             ptx::tc_fence_after();
             const int f_tile0 = ntile * P.BN;
             const long long f_glob0 = P.z_is_batch ? 0 : (long long)zb * P.Fg;
             float *yp = (P.ksplit > 1 ? P.partial + (long long)ksp * P.part_stride : P.y) + y_off + f_glob0 * P.ys_f;
             const float *bp = (P.has_bias && P.ksplit == 1) ? P.bias + f_glob0 : nullptr;
-            const bool vec_ok = (P.ys_f == 1) && ((P.ys_p & 3) == 0) && ((P.ys_n & 3) == 0) && ((P.Fg & 3) == 0) &&
-                                ((reinterpret_cast<uintptr_t>(P.y) & 15) == 0) && ((P.part_stride & 3) == 0) &&
-                                ((reinterpret_cast<uintptr_t>(P.partial) & 15) == 0);
             const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16);
             // staged 16-byte stores need: pixel-contiguous NCHW output, full-width rows (no column window), one plane per
             // tile, 16-byte aligned runs
@@ -634,23 +696,59 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             }
             // the two sets split the tile's columns (whole 32-column blocks)
             const int nblk = P.BN / 32, half_blk = (nblk + 1) / 2;
-            const int col0 = tset == 0 ? 0 : half_blk * 32, col1 = tset == 0 ? half_blk * 32 : P.BN;
+            col0 = tset == 0 ? 0 : half_blk * 32;
+            col1 = tset == 0 ? half_blk * 32 : P.BN;
+#define PETB200_EPI(ACT_)                                                                                              \
+    epilogue_store<ACT_, PASSES>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, \
+                                 ybase_warp, col0, col1)
             switch (P.ksplit > 1 ? PETB200_ACT_NONE : P.act) {
-            case PETB200_ACT_RELU:
-                epilogue_store<PETB200_ACT_RELU, PASSES>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp, col0, col1);
-                break;
-            case PETB200_ACT_SIGMOID:
-                epilogue_store<PETB200_ACT_SIGMOID, PASSES>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp, col0, col1);
-                break;
-            case PETB200_ACT_TANH:
-                epilogue_store<PETB200_ACT_TANH, PASSES>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp, col0, col1);
-                break;
-            case PETB200_ACT_GELU:
-                epilogue_store<PETB200_ACT_GELU, PASSES>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp, col0, col1);
-                break;
-            default:
-                epilogue_store<PETB200_ACT_NONE, PASSES>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, ybase_warp, col0, col1);
-                break;
+            case PETB200_ACT_RELU: PETB200_EPI(PETB200_ACT_RELU); break;
+            case PETB200_ACT_SIGMOID: PETB200_EPI(PETB200_ACT_SIGMOID); break;
+            case PETB200_ACT_TANH: PETB200_EPI(PETB200_ACT_TANH); break;
+            case PETB200_ACT_GELU: PETB200_EPI(PETB200_ACT_GELU); break;
+            default: PETB200_EPI(PETB200_ACT_NONE); break;
+            }
+#undef PETB200_EPI
+        }
+        if (P.ksplit > 1) {
+            // Split-K: count this CTA in at its output tile; the last one to arrive adds the partial sums up.  Nothing
+            // waits for another CTA.  Both barriers are reached by all eight epilogue warps whatever happened before.
+            if (P.prof && threadIdx.x == 96)
+                P.prof[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * kProfSlots + 12] = (long long)ptx::globaltimer_ns();
+            __threadfence(); // this thread's partial sums are visible device-wide before the arrival is counted
+            ptx::named_bar_sync(1, 8 * 32);
+            if (P.prof && threadIdx.x == 96)
+                P.prof[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * kProfSlots + 13] = (long long)ptx::globaltimer_ns();
+            if (threadIdx.x == 96) {
+                int last = 0;
+                if (*abort_flag == 0) {
+                    int *ticket = P.tickets + ((size_t)zb * (gridDim.y / P.ksplit) + ntile) * gridDim.x + blockIdx.x;
+                    last = (atomicAdd(ticket, 1) == P.ksplit - 1) ? 1 : 0;
+                    if (last)
+                        *ticket = 0; // every split has arrived: ready for the next launch
+                }
+                *last_flag = last;
+            }
+            ptx::named_bar_sync(1, 8 * 32);
+            if (P.prof && threadIdx.x == 96)
+                P.prof[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * kProfSlots + 14] = (long long)ptx::globaltimer_ns();
+            if (*last_flag) {
+                __threadfence();
+                const long long f_glob0 = P.z_is_batch ? 0 : (long long)zb * P.Fg;
+                const float *part = P.partial + y_off + f_glob0 * P.ys_f;
+                float *yf = P.y + y_off + f_glob0 * P.ys_f;
+                const float *bp = P.has_bias ? P.bias + f_glob0 : nullptr;
+#define PETB200_FIX(ACT_) \
+    splitk_fixup<ACT_>(part, P.part_stride, P.ksplit, ntile * P.BN, P.Fg, valid, bp, yf, P.ys_f, vec_ok, tset * (P.BN / 2), \
+                       (tset + 1) * (P.BN / 2))
+                switch (P.act) {
+                case PETB200_ACT_RELU: PETB200_FIX(PETB200_ACT_RELU); break;
+                case PETB200_ACT_SIGMOID: PETB200_FIX(PETB200_ACT_SIGMOID); break;
+                case PETB200_ACT_TANH: PETB200_FIX(PETB200_ACT_TANH); break;
+                case PETB200_ACT_GELU: PETB200_FIX(PETB200_ACT_GELU); break;
+                default: PETB200_FIX(PETB200_ACT_NONE); break;
+                }
+#undef PETB200_FIX
             }
         }
         if (P.prof && threadIdx.x == 96) { // lane 0 of warp 3 (transform set 0)
@@ -722,45 +820,6 @@ __global__ void __launch_bounds__(256) k_pack_mm_b(const float *__restrict__ b, 
     }
 }
 
-// Split-K second pass: y = act(sum_s partial[s] + bias) over the output window, in a fixed order (deterministic).
-// Elements are enumerated so that the fastest index is contiguous in y: pixels for conv layouts (ys_p == 1), filters
-// for row-major matmul output (ys_f == 1).
-struct ReduceParams {
-    int images, F, OD, OH, OW, ohn, own, oh0, ow0, ksplit, act, f_fast;
-    long long ys_n, ys_f, ys_p, part_stride;
-};
-__global__ void __launch_bounds__(256) k_splitk_reduce(const float *__restrict__ partial, const float *__restrict__ bias,
-                                                       float *__restrict__ y, ReduceParams r) {
-    const long long pix = (long long)r.OD * r.ohn * r.own;
-    const long long total = (long long)r.images * r.F * pix;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        long long rem = i;
-        int f, n;
-        long long q;
-        if (r.f_fast) {
-            f = (int)(rem % r.F);
-            rem /= r.F;
-            q = rem % pix;
-            n = (int)(rem / pix);
-        } else {
-            q = rem % pix;
-            rem /= pix;
-            f = (int)(rem % r.F);
-            n = (int)(rem / r.F);
-        }
-        const int xl = (int)(q % r.own);
-        const int yl = (int)((q / r.own) % r.ohn);
-        const int zl = (int)(q / ((long long)r.own * r.ohn));
-        const long long off = n * r.ys_n + f * r.ys_f + ((long long)(zl * r.OH + r.oh0 + yl) * r.OW + r.ow0 + xl) * r.ys_p;
-        float acc = 0.f;
-        for (int s = 0; s < r.ksplit; ++s)
-            acc += partial[s * r.part_stride + off];
-        if (bias)
-            acc += __ldg(bias + f);
-        y[off] = apply_act(acc, r.act);
-    }
-}
-
 // -------------------------------------------------------------------------------------------------------------
 // host side
 // -------------------------------------------------------------------------------------------------------------
@@ -791,8 +850,7 @@ struct TcCore {
     int xd[5]{}; // W,H,D,C,N of the activation tensor as the kernel sees it
     long long Ktot = 0;
     int rows_b = 0;
-    DevBuf whi, wlo, koff, partial;
-    ReduceParams red{};
+    DevBuf whi, wlo, koff, partial, tickets;
     long long y_elems = 0;
     CUtensorMap map_x{}, map_bhi{}, map_blo{};
     const void *map_x_ptr = nullptr;
@@ -856,6 +914,7 @@ struct TcCore {
         p.bias = bias;
         p.y = y;
         p.partial = (float *)partial.p;
+        p.tickets = (int *)tickets.p;
         p.koff = (const int *)koff.p;
         p.status = ctx->d_status;
         p.prof = prof;
@@ -871,14 +930,7 @@ struct TcCore {
             k_igemm<true, false, 3><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
         else
             k_igemm<false, false, 3><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
-        rc = launched(ctx, "k_igemm");
-        if (rc || P.ksplit == 1)
-            return rc;
-        ReduceParams r = red;
-        const long long total = (long long)r.images * r.F * r.OD * r.ohn * r.own;
-        const int blocks = (int)std::max<long long>(1, std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 8));
-        k_splitk_reduce<<<blocks, 256, 0, s>>>((const float *)partial.p, p.has_bias ? bias : nullptr, y, r);
-        return launched(ctx, "k_splitk_reduce");
+        return launched(ctx, "k_igemm");
     }
 };
 
@@ -895,9 +947,69 @@ static int env_int(const char *name, int dflt) {
 
 // Fills core.P (tiling, raw box, stage counts) for a window [oh0,ohn) x [ow0,own) of the output; returns
 // PETB200_ERR_UNSUPPORTED when the shape does not fit this kernel's constraints.
+// Rough cycle model of one launch, used to pick the tile width and the K split for problems that cannot fill the GPU
+// with 128-wide tiles.  Constants are measured on B200: a K stage costs its MMAs (N/2 cycles each, 12 per stage for
+// 3xTF32, 4 for one pass) or, if larger, the transform chain of the stage (~330 cycles with two warp sets); a CTA pays
+// ~3000 cycles before its first MMA and 1700 + 44*BN cycles of epilogue; the split-K fix-up re-reads every partial copy
+// through L2, four copies per round trip.
+static double est_cycles(int sm_count, long long base_ctas, int nchunks, int spc, int BN, int passes, int ks) {
+    const double stage = std::max<double>((passes == 3 ? 12.0 : 4.0) * (BN / 2), 330.0);
+    const long long stages = (long long)((nchunks + ks - 1) / ks) * spc;
+    const double per_cta = 3000.0 + (double)stages * stage + 1700.0 + 44.0 * BN;
+    const long long waves = (base_ctas * ks + sm_count - 1) / sm_count;
+    const double fix = ks > 1 ? 1200.0 + (double)((ks + 3) / 4) * (BN / 32) * 700.0 : 0.0;
+    return (double)waves * per_cta + fix;
+}
+static int choose_ksplit(int sm_count, long long base_ctas, int nchunks, int spc, int BN, int passes, double *cycles) {
+    int best = 1;
+    double best_c = est_cycles(sm_count, base_ctas, nchunks, spc, BN, passes, 1);
+    for (int ks = 2; ks <= std::min(nchunks, 32); ++ks) {
+        if ((nchunks + ks - 1) / ks == (nchunks + ks - 2) / (ks - 1))
+            continue; // no shorter than the previous split
+        const double c = est_cycles(sm_count, base_ctas, nchunks, spc, BN, passes, ks);
+        if (c < best_c * 0.97) // a deeper split has to pay for its extra traffic
+            best = ks, best_c = c;
+    }
+    if (cycles)
+        *cycles = best_c;
+    return best;
+}
+
+// Scratch of a split-K plan: the partial copies and one arrival counter per output tile (zero between launches).
+static int alloc_split_scratch(petb200_ctx *ctx, TcCore &c, long long tiles) {
+    if (c.P.ksplit <= 1)
+        return PETB200_OK;
+    if (c.partial.alloc((size_t)c.P.ksplit * c.P.part_stride * 4) != cudaSuccess || c.tickets.alloc((size_t)tiles * 4) != cudaSuccess)
+        return fail(ctx, PETB200_ERR_NOMEM, "split-K scratch allocation failed");
+    PETB200_CUDA(ctx, cudaMemset(c.tickets.p, 0, (size_t)tiles * 4));
+    return PETB200_OK;
+}
+
+// The dynamic shared-memory attribute is per function, not per launch: raise it once to the device limit so that plans
+// with different needs can coexist.
+static int raise_smem_limit(petb200_ctx *ctx) {
+    static bool attr_set = false;
+    if (attr_set)
+        return PETB200_OK;
+    const int lim = (int)std::min<size_t>(ctx->smem_optin, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(k_igemm<true, false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(k_igemm<false, false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(k_igemm<true, true, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(k_igemm<true, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(k_igemm<true, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    if (e != cudaSuccess)
+        return fail(ctx, PETB200_ERR_CUDA, "cudaFuncSetAttribute(%d bytes) failed: %s", lim, cudaGetErrorString(e));
+    attr_set = true;
+    return PETB200_OK;
+}
+
 static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int oh0, int ohn, int ow0, int own,
                         int z_is_batch, int images, long long ys_n, long long ys_f, long long ys_p, int has_bias, int act,
-                        int force_bc = 0, int force_ksplit = 0) {
+                        int force_bc = 0, int force_ksplit = 0, int force_bn = 0) {
     IgemmParams &P = core.P;
     const int cpg = g.C / g.groups, Fg = g.F / g.groups;
     if (g.Wst % 4 != 0)
@@ -925,12 +1037,6 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     P.ys_p = ys_p;
     P.has_bias = has_bias;
     P.act = act;
-    // tile N
-    int BN = Fg <= 32 ? 32 : (Fg <= 64 ? 64 : 128);
-    BN = env_int("PETB200_TC_BN", BN);
-    if (BN != 32 && BN != 64 && BN != 128)
-        return fail(ctx, PETB200_ERR_INVALID, "PETB200_TC_BN must be 32, 64 or 128");
-    P.BN = BN;
     // Planes smaller than half a tile are packed several to a tile: whole images for 2-D problems, consecutive depth
     // slices of one image (a divisor of the depth, so that no tile straddles two images) for 3-D problems.
     P.ipt = 1;
@@ -977,85 +1083,104 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     const int T = g.T3[0] * g.T3[1] * g.T3[2];
     const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 1024; // alignment slack
     core.a_tmem = core.single_pass || env_int("PETB200_TC_A_TMEM", 1) != 0; // the single-pass variant exists for TS only
-    if (core.a_tmem && BN > 256)
-        return fail(ctx, PETB200_ERR_INVALID, "TS variant supports BN <= 256");
-    // channels per chunk: 32, or more for filters with few taps so that one raw tile still feeds several K stages
-    int bc_cap = 32 * std::max(1, std::min(4, 4 / T));
-    int BC = std::min(cpg, bc_cap);
-    if (BC > 32)
-        BC = BC / 32 * 32;
     const int forced_bc = force_bc > 0 ? force_bc : env_int("PETB200_TC_BC", 0);
-    if (forced_bc > 0)
-        BC = std::min(forced_bc, cpg);
-    for (;; BC = std::max(1, BC / 2)) {
-        P.BC = BC;
-        P.spc = (T * BC + kStageK - 1) / kStageK;
-        P.nchunks = (cpg + BC - 1) / BC;
-        size_t raw = (size_t)P.RN * BC * P.RD * P.RH * P.RW * 4;
-        P.raw_bytes = (int)((raw + 127) / 128 * 128);
-        P.NA = core.a_tmem ? 4 : 2;
-        P.NB = 2;
-        P.NR = 2;
-        P.a_kmajor = 0;
-        P.m_rows = 0;
-        bool fits = smem_layout(P, core.a_tmem).total <= budget;
-        if (fits) {
-            // deepen the rings while there is room: B first (it hides TMA latency), then A
-            for (bool grew = true; grew;) {
-                grew = false;
-                if (P.NB < kMaxNB) {
-                    P.NB++;
-                    if (smem_layout(P, core.a_tmem).total <= budget)
-                        grew = true;
-                    else
-                        P.NB--;
+    // Channels per chunk (32, or more for filters with few taps so that one raw tile still feeds several K stages) and
+    // ring depths for a given tile width; false if not even one channel's raw tile fits.
+    auto fit = [&](int BN) -> bool {
+        P.BN = BN;
+        int bc_cap = 32 * std::max(1, std::min(4, 4 / T));
+        int BC = std::min(cpg, bc_cap);
+        if (BC > 32)
+            BC = BC / 32 * 32;
+        if (forced_bc > 0)
+            BC = std::min(forced_bc, cpg);
+        for (;; BC = std::max(1, BC / 2)) {
+            P.BC = BC;
+            P.spc = (T * BC + kStageK - 1) / kStageK;
+            P.nchunks = (cpg + BC - 1) / BC;
+            size_t raw = (size_t)P.RN * BC * P.RD * P.RH * P.RW * 4;
+            P.raw_bytes = (int)((raw + 127) / 128 * 128);
+            P.NA = core.a_tmem ? 4 : 2;
+            P.NB = 2;
+            P.NR = 2;
+            P.a_kmajor = 0;
+            P.m_rows = 0;
+            if (smem_layout(P, core.a_tmem).total <= budget) {
+                // deepen the rings while there is room: B first (it hides TMA latency), then A
+                for (bool grew = true; grew;) {
+                    grew = false;
+                    if (P.NB < kMaxNB) {
+                        P.NB++;
+                        if (smem_layout(P, core.a_tmem).total <= budget)
+                            grew = true;
+                        else
+                            P.NB--;
+                    }
+                    if (!core.a_tmem && P.NA < 3 && P.NB >= 3) {
+                        P.NA++;
+                        if (smem_layout(P, core.a_tmem).total <= budget)
+                            grew = true;
+                        else
+                            P.NA--;
+                    }
                 }
-                if (!core.a_tmem && P.NA < 3 && P.NB >= 3) {
-                    P.NA++;
-                    if (smem_layout(P, core.a_tmem).total <= budget)
-                        grew = true;
-                    else
-                        P.NA--;
-                }
+                return true;
             }
-            break;
+            if (BC == 1 || forced_bc > 0)
+                return false;
         }
-        if (BC == 1 || forced_bc > 0)
-            return fail(ctx, PETB200_ERR_UNSUPPORTED, "raw activation tile does not fit shared memory");
-    }
-    core.smem = smem_layout(P, core.a_tmem).total + 1024;
+    };
     const int n_img = z_is_batch ? 1 : images;
     const int mtiles = P.wide ? n_img * g.OD * ohn * P.row_tiles : ((P.units + P.ipt - 1) / P.ipt) * P.tpi;
-    const int ntiles = (Fg + BN - 1) / BN;
     const int gz = z_is_batch ? images : g.groups;
-    // split-K when the tile count leaves most SMs idle and K is deep
-    int ksplit = 1;
-    if (force_ksplit > 0) {
-        ksplit = std::min(force_ksplit, P.nchunks);
-    } else {
-        const long long ctas = (long long)mtiles * ntiles * gz;
-        const int want = env_int("PETB200_TC_KSPLIT", 0);
-        if (want > 0)
-            ksplit = std::min(want, P.nchunks);
-        else if (ctas * 2 <= ctx->sm_count && P.nchunks >= 2)
-            ksplit = (int)std::max<long long>(1, std::min<long long>({(long long)P.nchunks, ctx->sm_count / ctas, 32ll}));
+    // Tile width and K split: 128-wide tiles unless the problem has too few of them for the GPU, in which case narrower
+    // tiles and/or a split of K spread the same MMA work over more SMs (see est_cycles).
+    const int bn_max = Fg <= 32 ? 32 : (Fg <= 64 ? 64 : 128);
+    const int forced_bn = force_bn > 0 ? force_bn : env_int("PETB200_TC_BN", 0);
+    if (forced_bn != 0 && forced_bn != 32 && forced_bn != 64 && forced_bn != 128)
+        return fail(ctx, PETB200_ERR_INVALID, "PETB200_TC_BN must be 32, 64 or 128");
+    const int want_ks = force_ksplit > 0 ? force_ksplit : env_int("PETB200_TC_KSPLIT", 0);
+    double best_cycles = 0;
+    IgemmParams bestP{};
+    bool have = false;
+    for (int bn = 128; bn >= 32; bn /= 2) {
+        if (forced_bn ? bn != forced_bn : bn > bn_max)
+            continue;
+        if (!fit(bn))
+            continue;
+        const long long base_ctas = (long long)mtiles * ((Fg + bn - 1) / bn) * gz;
+        const int passes = core.single_pass ? 1 : 3;
+        double cyc;
+        if (want_ks > 0) {
+            P.ksplit = std::min(want_ks, P.nchunks);
+            cyc = est_cycles(ctx->sm_count, base_ctas, P.nchunks, P.spc, bn, passes, P.ksplit);
+        } else {
+            P.ksplit = choose_ksplit(ctx->sm_count, base_ctas, P.nchunks, P.spc, bn, passes, &cyc);
+        }
+        if (!have || cyc < best_cycles * 0.97) { // prefer the wider tile unless the narrower one clearly wins
+            have = true;
+            best_cycles = cyc;
+            bestP = P;
+        }
     }
-    P.ksplit = ksplit;
+    if (!have)
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "raw activation tile does not fit shared memory");
+    P = bestP;
+    const int BN = P.BN;
+    if (core.a_tmem && BN > 256)
+        return fail(ctx, PETB200_ERR_INVALID, "TS variant supports BN <= 256");
+    core.smem = smem_layout(P, core.a_tmem).total + 1024;
+    const int ntiles = (Fg + BN - 1) / BN;
     core.y_elems = (z_is_batch ? (long long)images : (long long)n_img) * g.F * g.OD * g.OH * g.OW;
     if (z_is_batch)
         core.y_elems = (long long)images * ys_n;
     P.part_stride = (core.y_elems + 3) / 4 * 4;
-    if (ksplit > 1) {
-        if (core.partial.alloc((size_t)ksplit * P.part_stride * 4) != cudaSuccess)
-            return fail(ctx, PETB200_ERR_NOMEM, "split-K scratch allocation failed");
-        ReduceParams &r = core.red;
-        r.images = z_is_batch ? images : n_img;
-        r.F = z_is_batch ? Fg : g.F;
-        r.OD = g.OD, r.OH = g.OH, r.OW = g.OW, r.ohn = ohn, r.own = own, r.oh0 = oh0, r.ow0 = ow0;
-        r.ksplit = ksplit, r.act = act, r.f_fast = (ys_f == 1);
-        r.ys_n = ys_n, r.ys_f = ys_f, r.ys_p = ys_p, r.part_stride = P.part_stride;
+    {
+        int rc = alloc_split_scratch(ctx, core, (long long)mtiles * ntiles * gz);
+        if (rc)
+            return rc;
     }
-    core.grid = dim3((unsigned)mtiles, (unsigned)(ntiles * ksplit), (unsigned)gz);
+    core.grid = dim3((unsigned)mtiles, (unsigned)(ntiles * P.ksplit), (unsigned)gz);
     core.Ktot = (long long)P.nchunks * P.spc * kStageK;
     core.xd[0] = g.Wst;
     core.xd[1] = g.H;
@@ -1067,31 +1192,13 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     const int plane_w = P.RW, plane_h = P.RH * P.RW, plane_d = P.RD * plane_h;
     for (int tap = 0; tap < T; ++tap) {
         int t = tap / (g.T3[1] * g.T3[2]), r = (tap / g.T3[2]) % g.T3[1], s = tap % g.T3[2];
-        for (int ci = 0; ci < BC; ++ci)
-            koff[(size_t)tap * BC + ci] = ci * plane_d + t * g.dil[0] * plane_h + r * g.dil[1] * plane_w + s * g.dil[2];
+        for (int ci = 0; ci < P.BC; ++ci)
+            koff[(size_t)tap * P.BC + ci] = ci * plane_d + t * g.dil[0] * plane_h + r * g.dil[1] * plane_w + s * g.dil[2];
     }
     if (core.koff.alloc(koff.size() * 4) != cudaSuccess)
         return fail(ctx, PETB200_ERR_NOMEM, "koff allocation failed");
     PETB200_CUDA(ctx, cudaMemcpy(core.koff.p, koff.data(), koff.size() * 4, cudaMemcpyHostToDevice));
-    // The attribute is per function, not per launch: raise it once to the device limit so that plans with different
-    // shared-memory needs can coexist.
-    static bool attr_set = false;
-    if (!attr_set) {
-        const int lim = (int)std::min<size_t>(ctx->smem_optin, 227 * 1024);
-        cudaError_t e1 = cudaFuncSetAttribute(k_igemm<true, false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
-        cudaError_t e2 = cudaFuncSetAttribute(k_igemm<false, false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
-        if (e1 == cudaSuccess)
-            e1 = cudaFuncSetAttribute(k_igemm<true, true, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
-        if (e1 == cudaSuccess)
-            e1 = cudaFuncSetAttribute(k_igemm<true, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
-        if (e1 == cudaSuccess)
-            e1 = cudaFuncSetAttribute(k_igemm<true, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
-        if (e1 != cudaSuccess || e2 != cudaSuccess)
-            return fail(ctx, PETB200_ERR_CUDA, "cudaFuncSetAttribute(%d bytes) failed: %s", lim,
-                        cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
-        attr_set = true;
-    }
-    return PETB200_OK;
+    return raise_smem_limit(ctx);
 }
 
 // ---- exported to conv.cu -------------------------------------------------------------------------------------
@@ -1206,7 +1313,7 @@ int tc_conv_run(void *h, const float *x, const float *bias, float *y, const int 
         // A window must consume K in exactly the order of the full operator (same BC / chunking), otherwise the
         // two would round differently; the raw box only shrinks for a window, so the full plan's BC always fits.
         int rc = tc_configure(wc->ctx, *wc, g, win[0], win[1], win[2], win[3], 0, g.N, (long long)g.F * plane, plane, 1,
-                              t->has_bias, t->act, t->full.P.BC, t->full.P.ksplit);
+                              t->has_bias, t->act, t->full.P.BC, t->full.P.ksplit, t->full.P.BN);
         if (rc == PETB200_OK && (wc->P.BN != t->full.P.BN || wc->P.BC != t->full.P.BC || wc->Ktot != t->full.Ktot || wc->P.ksplit != t->full.P.ksplit))
             rc = fail(wc->ctx, PETB200_ERR_UNSUPPORTED, "window plan diverged from the full plan");
         if (rc) {
@@ -1245,30 +1352,21 @@ struct TcMatmul {
     bool native_a = false; // A is consumed row-major as passed (no re-layout)
 };
 
-// Shared tail of the two matmul configurations: split-K decision, scratch, reduce parameters, grid.
-static int matmul_finish(petb200_ctx *ctx, TcCore &c, int bs, int m, int n, int mtiles, int act) {
+// Shared tail of the row-major-A matmul configuration: split-K decision, scratch, grid.
+static int matmul_finish(petb200_ctx *ctx, TcCore &c, int bs, int m, int n, int mtiles) {
     IgemmParams &P = c.P;
     const int ntiles = (n + P.BN - 1) / P.BN;
     const long long ctas = (long long)mtiles * ntiles * bs;
-    int ksplit = 1;
     const int want = env_int("PETB200_TC_KSPLIT", 0);
-    if (want > 0)
-        ksplit = std::min(want, P.nchunks);
-    else if (ctas * 2 <= ctx->sm_count && P.nchunks >= 2)
-        ksplit = (int)std::max<long long>(1, std::min<long long>({(long long)P.nchunks, ctx->sm_count / ctas, 32ll}));
-    P.ksplit = ksplit;
+    P.ksplit = want > 0 ? std::min(want, P.nchunks)
+                        : choose_ksplit(ctx->sm_count, ctas, P.nchunks, P.spc, P.BN, c.single_pass ? 1 : 3, nullptr);
     c.y_elems = (long long)bs * m * n;
     P.part_stride = (c.y_elems + 3) / 4 * 4;
-    if (ksplit > 1) {
-        if (c.partial.alloc((size_t)ksplit * P.part_stride * 4) != cudaSuccess)
-            return fail(ctx, PETB200_ERR_NOMEM, "split-K scratch allocation failed");
-        ReduceParams &r = c.red;
-        r.images = bs, r.F = n, r.OD = 1, r.OH = 1, r.OW = m, r.ohn = 1, r.own = m, r.oh0 = 0, r.ow0 = 0;
-        r.ksplit = ksplit, r.act = act, r.f_fast = 1;
-        r.ys_n = (long long)m * n, r.ys_f = 1, r.ys_p = n, r.part_stride = P.part_stride;
-    }
-    c.grid = dim3((unsigned)mtiles, (unsigned)(ntiles * ksplit), (unsigned)bs);
-    return PETB200_OK;
+    int rc = alloc_split_scratch(ctx, c, ctas);
+    if (rc)
+        return rc;
+    c.grid = dim3((unsigned)mtiles, (unsigned)(ntiles * P.ksplit), (unsigned)bs);
+    return raise_smem_limit(ctx);
 }
 
 // Row-major A ([b][m][k], k % 4 == 0): the kernel's K-major mode, no re-layout of A.
@@ -1319,7 +1417,7 @@ static int tc_configure_kmajor(petb200_ctx *ctx, TcCore &core, int bs, int m, in
     if (core.koff.alloc(koff.size() * 4) != cudaSuccess)
         return fail(ctx, PETB200_ERR_NOMEM, "koff allocation failed");
     PETB200_CUDA(ctx, cudaMemcpy(core.koff.p, koff.data(), koff.size() * 4, cudaMemcpyHostToDevice));
-    return matmul_finish(ctx, core, bs, m, n, P.tpi, act);
+    return matmul_finish(ctx, core, bs, m, n, P.tpi);
 }
 
 int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, int transB, int has_bias, int act, int passes,
@@ -1337,16 +1435,7 @@ int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, 
     t->core.single_pass = passes == 1;
     int rc;
     if (!transA && k % 4 == 0 && env_int("PETB200_TC_KMAJOR", 1)) {
-        // make sure the shared-memory attribute of every instantiation is raised (done inside tc_configure)
-        ConvGeom g0{};
-        g0.N = 1, g0.C = 4, g0.D = 1, g0.H = 1, g0.W = 4, g0.Wst = 4, g0.F = 32, g0.groups = 1, g0.OD = 1, g0.OH = 1, g0.OW = 4;
-        for (int i = 0; i < 3; ++i)
-            g0.T3[i] = 1, g0.pad[i] = 0, g0.stride[i] = 1, g0.dil[i] = 1;
-        TcCore dummy;
-        dummy.ctx = ctx;
-        rc = tc_configure(ctx, dummy, g0, 0, 1, 0, 4, 1, 1, 128, 1, 32, 0, 0);
-        if (rc == PETB200_OK)
-            rc = tc_configure_kmajor(ctx, t->core, bs, m, n, k, has_bias, act);
+        rc = tc_configure_kmajor(ctx, t->core, bs, m, n, k, has_bias, act);
         t->native_a = true;
     } else {
         ConvGeom g{};
