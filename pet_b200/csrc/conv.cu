@@ -92,6 +92,84 @@ __global__ void __launch_bounds__(256) k_matmul_simt(const float *__restrict__ a
     }
 }
 
+// Matrix-vector shapes (m <= 8 rows of A, e.g. a classifier head at batch 1): the 128-row tensor-core tile would be
+// almost empty, and the work is one pass over B.  A block owns 32 columns of C for all rows; exact fp32 FMA.
+//   B as [k][n]: lanes = columns (coalesced rows of B), the 8 warps split K and are added up through shared memory.
+//   B as [n][k]: a warp owns 4 columns, lanes split K (coalesced rows of B), lanes are added up by shuffles.
+constexpr int kGemvRows = 8, kGemvWarps = 16;
+__global__ void __launch_bounds__(kGemvWarps * 32) k_gemv_small_m(const float *__restrict__ a, const float *__restrict__ b,
+                                                                 const float *__restrict__ bias, float *__restrict__ c, int m,
+                                                                 int n, int k, int transA, int transB, int act) {
+    __shared__ float red[kGemvWarps][kGemvRows][33];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, bb = blockIdx.y;
+    const float *ab = a + (long long)bb * m * k, *bm = b + (long long)bb * k * n;
+    const long long a_sk = transA ? m : 1, a_sr = transA ? 1 : k; // A(r, kk) = ab[r * a_sr + kk * a_sk]
+    float acc[kGemvRows];
+#pragma unroll
+    for (int r = 0; r < kGemvRows; ++r)
+        acc[r] = 0.f;
+    if (!transB) {
+        const int col = blockIdx.x * 32 + lane;
+        const int kbeg = (int)((long long)k * warp / kGemvWarps), kend = (int)((long long)k * (warp + 1) / kGemvWarps);
+        for (int k0 = kbeg; k0 < kend; k0 += 8) {
+            float bv[8]; // eight rows of B in flight per lane
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                bv[u] = (k0 + u < kend && col < n) ? __ldg(bm + (long long)(k0 + u) * n + col) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+#pragma unroll
+                for (int r = 0; r < kGemvRows; ++r)
+                    if (r < m && k0 + u < kend)
+                        acc[r] = fmaf(__ldg(ab + r * a_sr + (k0 + u) * a_sk), bv[u], acc[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < kGemvRows; ++r)
+            red[warp][r][lane] = acc[r];
+        __syncthreads();
+        // warp r adds up row r over the K slices, in slice order
+        if (warp < m && col < n) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < kGemvWarps; ++w)
+                v += red[w][warp][lane];
+            if (bias)
+                v += __ldg(bias + col);
+            c[((long long)bb * m + warp) * n + col] = apply_act(v, act);
+        }
+    } else {
+        for (int col = blockIdx.x * 32 + warp; col < min(n, (int)blockIdx.x * 32 + 32); col += kGemvWarps) {
+#pragma unroll
+            for (int r = 0; r < kGemvRows; ++r)
+                acc[r] = 0.f;
+            for (int k0 = lane; k0 < k; k0 += 8 * 32) {
+                float bv[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    bv[u] = k0 + 32 * u < k ? __ldg(bm + (long long)col * k + k0 + 32 * u) : 0.f;
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+#pragma unroll
+                    for (int r = 0; r < kGemvRows; ++r)
+                        if (r < m && k0 + 32 * u < k)
+                            acc[r] = fmaf(__ldg(ab + r * a_sr + (k0 + 32 * u) * a_sk), bv[u], acc[r]);
+            }
+#pragma unroll
+            for (int r = 0; r < kGemvRows; ++r) {
+                float v = acc[r];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1)
+                    v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0 && r < m) {
+                    if (bias)
+                        v += __ldg(bias + col);
+                    c[((long long)bb * m + r) * n + col] = apply_act(v, act);
+                }
+            }
+        }
+    }
+}
+
 // Re-pitches [planes, H, W] rows to a pitch divisible by 4 (zero fill), so TMA's 16-byte stride rule holds.
 __global__ void __launch_bounds__(256) k_repitch(const float *__restrict__ x, float *__restrict__ y, long long rows, int w, int wp) {
     const long long total = rows * wp;
@@ -133,13 +211,13 @@ static int grid_for(petb200_ctx *ctx, long long work, int per_block) {
 
 // -------------------------------------------------------------------------------------------------------------
 struct ConvPlan : petb200_plan {
+    DevBuf xpad; // re-pitched input, for the shapes whose rows TMA cannot address (see tc_conv_row_pitch)
+    int wp = 0;
     int nsp = 2;
     SimtConv sc{};
     int algo = 0; // resolved: PETB200_ALGO_TC_3XTF32 or PETB200_ALGO_SIMT_FP32
     void *tc = nullptr;
     const float *w_simt = nullptr; // SIMT path keeps the caller's weight pointer
-    DevBuf xpad;                   // re-pitched input when W % 4 != 0 (tensor-core path only)
-    int wp = 0;
     DevBuf bx, bw, bb, by; // timing operands
     ~ConvPlan() override {
         if (tc)
@@ -308,6 +386,7 @@ struct MatmulPlan : petb200_plan {
     DevBuf at; // A re-laid as [b][k][m] when the caller's A is [b][m][k]
     const float *b_weight = nullptr; // set by matmul_set_weights
     bool native_a = false;           // the kernel reads row-major A directly
+    bool gemv = false;               // m <= 8: matrix-vector kernel
     DevBuf ba, bbm, bbias, bc;
     ~MatmulPlan() override {
         if (tc)
@@ -329,6 +408,13 @@ int make_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int
     pl->transA = transA != 0, pl->transB = transB != 0, pl->bs = b, pl->m = m, pl->n = n, pl->k = k;
     pl->has_bias = has_bias, pl->act = act;
     int rc = PETB200_ERR_UNSUPPORTED;
+    if (algo == PETB200_ALGO_AUTO && m <= kGemvRows) {
+        pl->algo = PETB200_ALGO_SIMT_FP32;
+        pl->gemv = true;
+        pl->kernel = "gemv_fp32";
+        *out = pl;
+        return PETB200_OK;
+    }
     if (algo == PETB200_ALGO_AUTO || algo == PETB200_ALGO_TC_3XTF32 || algo == PETB200_ALGO_TC_1XTF32) {
         size_t bytes = 0;
         rc = tc_matmul_create(ctx, b, m, n, k, pl->transA, pl->transB, has_bias, act, algo == PETB200_ALGO_TC_1XTF32 ? 1 : 3, &pl->tc,
@@ -396,6 +482,11 @@ int matmul_run(petb200_plan *plan, const float *a, const float *b, const float *
             at = (const float *)pl->at.p;
         }
         return tc_matmul_run(pl->tc, at, pl->has_bias ? bias : nullptr, c, s);
+    }
+    if (pl->gemv) {
+        k_gemv_small_m<<<dim3((unsigned)((pl->n + 31) / 32), (unsigned)pl->bs), kGemvWarps * 32, 0, s>>>(
+            a, b, pl->has_bias ? bias : nullptr, c, pl->m, pl->n, pl->k, pl->transA, pl->transB, pl->act);
+        return launched(ctx, "k_gemv_small_m");
     }
     long long total = (long long)pl->bs * pl->m * pl->n;
     k_matmul_simt<<<grid_for(ctx, total, 256), 256, 0, s>>>(a, b, pl->has_bias ? bias : nullptr, c, pl->bs, pl->m, pl->n, pl->k,

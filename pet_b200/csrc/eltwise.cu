@@ -106,6 +106,40 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// Large windows (global pooling): one warp per output, the window spread over the lanes.  One thread per output would
+// walk the window serially, one dependent L2 access after another.
+__global__ void __launch_bounds__(256) k_pool2d_warp(int kind, const float *__restrict__ x, float *__restrict__ y, int nc,
+                                                     int h, int w, int oh, int ow, int kh, int kw, int ph, int pw, int sh,
+                                                     int sw) {
+    const size_t total = (size_t)nc * oh * ow;
+    const int lane = threadIdx.x & 31;
+    for (size_t i = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5; i < total; i += ((size_t)gridDim.x * blockDim.x) >> 5) {
+        const int j = (int)(i % ow);
+        const size_t r = i / ow;
+        const int ii = (int)(r % oh);
+        const float *xp = x + (r / oh) * (size_t)h * w;
+        float best = -INFINITY, acc = 0.f;
+        int cnt = 0;
+        for (int e = lane; e < kh * kw; e += 32) {
+            const int a = e / kw, b = e - a * kw;
+            const int yy = ii * sh + a - ph, xx = j * sw + b - pw;
+            if (yy < 0 || yy >= h || xx < 0 || xx >= w)
+                continue;
+            const float v = __ldg(xp + (size_t)yy * w + xx);
+            best = fmaxf(best, v);
+            acc += v;
+            cnt++;
+        }
+        best = warp_max(best);
+        acc = warp_sum(acc);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+            cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+        if (lane == 0)
+            y[i] = kind == 0 ? best : (cnt ? acc / (float)cnt : 0.f);
+    }
+}
+
 // One warp per row; rows are short (<= a few thousand) in every PET workload, so the row stays in registers/L1.
 __global__ void __launch_bounds__(256) k_rowmean(const float *__restrict__ x, float *__restrict__ y, size_t rows, int cols) {
     size_t warp = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
@@ -316,6 +350,11 @@ extern "C" int petb200_pool2d_run(petb200_ctx *ctx, int kind, const float *x, fl
     if (oh <= 0 || ow <= 0)
         return fail(ctx, PETB200_ERR_INVALID, "pool2d_run: empty output");
     size_t total = (size_t)n * c * oh * ow;
+    if (kh * kw >= 32) {
+        k_pool2d_warp<<<grid_for(ctx, total, 8), 256, 0, (cudaStream_t)stream>>>(kind, x, y, n * c, h, w, oh, ow, kh, kw, ph,
+                                                                                  pw, sh, sw);
+        return launched(ctx, "k_pool2d_warp");
+    }
     k_pool2d<<<grid_for(ctx, total, 256), 256, 0, (cudaStream_t)stream>>>(kind, x, y, n * c, h, w, oh, ow, kh, kw, ph,
                                                                           pw, sh, sw);
     return launched(ctx, "k_pool2d");

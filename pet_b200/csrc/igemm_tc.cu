@@ -48,20 +48,23 @@ struct IgemmParams {
     int z_is_batch;         // blockIdx.z: 0 = conv group, 1 = matmul batch
     int wide, row_tiles;    // wide mode: a tile is 128 consecutive pixels of ONE output row (rows wider than a tile)
     int tpi, ipt;           // otherwise: tiles per plane (plane larger than a tile) or whole planes per tile
-    int ksplit;             // K is split over this many CTAs: partial sums go to scratch, the CTA of a tile that
-                            // finishes last adds them up (in split order, so the result does not depend on which)
-    long long part_stride;  // floats between the partial-sum copies
+    int ksplit;             // K is split over this many CTAs, launched as one thread-block cluster (2, 4 or 8); partial
+                            // tiles are added up through distributed shared memory
     int NA, NB, NR;         // ring depths: A stages, B stages, raw activation buffers
     int a_kmajor;           // matmul with row-major A: the raw tile is [128 rows][32 k], 128B-swizzled, one per K stage
     int m_rows;             // a_kmajor: rows of A per batch entry
     int raw_bytes;          // bytes of one raw buffer (128-aligned)
+    int flat;               // rows of the input are not 16-byte multiples: the raw tile is BC whole channels of RN images,
+                            // dense and unpadded, fetched as a 2-D box [flat_rows][flat_w] of the contiguous run; padding
+                            // becomes a per-pixel mask over the filter taps (<= 32 taps)
+    int flat_w, flat_rows;
+    int T3[3], dil[3];      // filter extents and dilations (flat only: for the tap mask)
+    int xD, xH, xW;         // input extents (flat only)
     long long ys_n, ys_f, ys_p;
     int act, has_bias;
     const int *koff;
     const float *bias;
     float *y;
-    float *partial;
-    int *tickets;    // split-K: one arrival counter per output tile, zero between launches
     int *status;
     long long *prof; // optional per-CTA counters (kProfSlots per CTA), for tuning only
     int dbg;         // tuning experiments (epilogue only): bit 0 = skip the global stores
@@ -115,7 +118,7 @@ template <int ACT> __device__ __forceinline__ float act_fn(float v) {
 template <int ACT, int PASSES>
 __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile0, int Fg, bool valid, const float *bias,
                                                float *yp, long long ys_f, bool vec_ok, int dbg, float *stage, int nvalid_warp, float *ybase_warp,
-                                               int col0, int col1) {
+                                               int col0, int col1, float *split_row /*split-K: this row of the staged tile*/) {
     uint32_t r[32], nx[32], sm[32];
     if (col0 >= col1)
         return;
@@ -131,6 +134,12 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile
             ptx::tmem_ld_32x32(tacc + (uint32_t)(cc + 32), nx);
             if (PASSES == 3)
                 ptx::tmem_ld_32x32(tacc + 128u + (uint32_t)(cc + 32), sm);
+        }
+        if (split_row != nullptr) { // partial sums stay on chip: [column][pixel], consecutive lanes = consecutive words
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                split_row[(cc + j) * kTileM] = __uint_as_float(r[j]);
+            continue;
         }
         if ((dbg & 1) || (stage == nullptr && !valid))
             continue;
@@ -182,61 +191,62 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile
     }
 }
 
-// Split-K fix-up, run by the last CTA to arrive at an output tile: every epilogue thread re-reads the elements it stored
-// (its pixel row, half of the tile's columns) from all the partial copies, adds them in split order, and writes
-// act(sum + bias).  Partial sums were written by other SMs: they are read through L2 (ld.global.cg).
+// One K stage of one tile row: fetch the 32 operands (gathered through the offset table, or straight from the
+// swizzled row in K-major mode) and split them into the TF32 hi/lo parts (or round them, for a single pass).
+// FLAT: the table entries carry the filter tap in bits 24..30 and `tmask` tells which taps fall inside the input for
+// this pixel (the raw tile has no padding of its own).
+template <bool A_KMAJOR, bool FLAT, int PASSES>
+__device__ __forceinline__ void gather_split(const int4 *ko, const float *raw, const uint8_t *krow, int p, uint32_t tmask,
+                                             uint32_t (&hi)[32], uint32_t (&lo)[32]) {
+#pragma unroll
+    for (int c4 = 0; c4 < 8; ++c4) {
+        float v[4];
+        if (A_KMAJOR) { // row p of the swizzled [128][32] tile: 16-byte chunk c4 sits at c4 ^ (p & 7)
+            const float4 t4 = *reinterpret_cast<const float4 *>(krow + ((c4 ^ (p & 7)) << 4));
+            v[0] = t4.x, v[1] = t4.y, v[2] = t4.z, v[3] = t4.w;
+        } else {
+            const int4 o4 = ko[c4];
+            const int o[4] = {o4.x, o4.y, o4.z, o4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (FLAT)
+                    v[i] = (o[i] >= 0 && ((tmask >> (o[i] >> 24)) & 1u)) ? raw[o[i] & 0xffffff] : 0.f;
+                else
+                    v[i] = o[i] >= 0 ? raw[o[i]] : 0.f;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (PASSES == 3) {
+                hi[4 * c4 + i] = __float_as_uint(v[i]) & 0xffffe000u;
+                lo[4 * c4 + i] = __float_as_uint(v[i] - __uint_as_float(hi[4 * c4 + i]));
+            } else { // single pass: round to nearest TF32 instead of letting the tensor core truncate
+                hi[4 * c4 + i] = ptx::cvt_rna_tf32(v[i]);
+            }
+        }
+    }
+}
+
+// Split-K reduction inside a thread-block cluster.  The ksplit CTAs of one output tile form a cluster; each has staged
+// its 128 x BN partial tile in its own shared memory as [column][pixel].  CTA `rank` owns BN/ksplit columns: a thread adds
+// the ksplit copies of an element in rank order (so the sum does not depend on timing), reading the peers' copies
+// through distributed shared memory, and stores act(sum + bias).
 template <int ACT>
-__device__ __forceinline__ void splitk_fixup(const float *part /*copy 0, at this thread's pixel, filter 0 of the group*/,
-                                             long long part_stride, int ksplit, int f_tile0, int Fg, bool valid,
-                                             const float *bias, float *yp, long long ys_f, bool vec_ok, int col0, int col1) {
-    if (!valid)
-        return;
-    for (int cc = col0; cc < col1; cc += 16) {
-        const int f0 = f_tile0 + cc;
-        if (f0 >= Fg)
+__device__ __forceinline__ void cluster_reduce_store(uint32_t stage_addr, int ksplit, int rank, int BN, int et /*0..255*/,
+                                                     int f_tile0, int Fg, const float *bias, float *yp /*this pixel, filter 0*/,
+                                                     long long ys_f) {
+    const int cols = BN / ksplit, px = et & (kTileM - 1);
+    for (int cl = et >> 7; cl < cols; cl += 2) {
+        const int col = rank * cols + cl, f = f_tile0 + col;
+        if (f >= Fg)
             break;
-        float acc[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j)
-            acc[j] = 0.f;
-        if (vec_ok) { // filters contiguous: 16-byte loads (Fg is a multiple of 4 here)
-#pragma unroll 4
-            for (int ks = 0; ks < ksplit; ++ks) {
-                const float4 *src = reinterpret_cast<const float4 *>(part + (long long)ks * part_stride + f0);
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (f0 + 4 * j < Fg) {
-                        const float4 v = __ldcg(src + j);
-                        acc[4 * j] += v.x, acc[4 * j + 1] += v.y, acc[4 * j + 2] += v.z, acc[4 * j + 3] += v.w;
-                    }
-            }
-        } else {
-#pragma unroll 4
-            for (int ks = 0; ks < ksplit; ++ks) {
-                const float *src = part + (long long)ks * part_stride + (long long)f0 * ys_f;
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    if (f0 + j < Fg)
-                        acc[j] += __ldcg(src + (long long)j * ys_f);
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            if (bias != nullptr && f0 + j < Fg)
-                acc[j] += __ldg(bias + f0 + j);
-            acc[j] = act_fn<ACT>(acc[j]);
-        }
-        if (vec_ok) {
-#pragma unroll
-            for (int j = 0; j < 16; j += 4)
-                if (f0 + j < Fg)
-                    *reinterpret_cast<float4 *>(yp + f0 + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-        } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-                if (f0 + j < Fg)
-                    yp[(long long)(f0 + j) * ys_f] = acc[j];
-        }
+        const uint32_t a = stage_addr + (uint32_t)(col * kTileM + px) * 4u;
+        float acc = 0.f;
+        for (int r = 0; r < ksplit; ++r)
+            acc += ptx::ld_dsmem_f32(ptx::map_to_cta(a, (uint32_t)r));
+        if (bias != nullptr)
+            acc += __ldg(bias + f);
+        yp[(long long)f * ys_f] = act_fn<ACT>(acc);
     }
 }
 
@@ -260,7 +270,6 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     uint64_t *acc_full = a_empty + 4;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(acc_full + 2);
-    volatile int *last_flag = reinterpret_cast<volatile int *>(acc_full + 3); // split-K: this CTA adds the partial sums up
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     long long *prof_cta = nullptr; // wall-clock marks of this CTA (entry, prologue done, epilogue done, exit), tuning only
@@ -334,6 +343,47 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         y_start = (P.oh0 + yl_lo) * P.sh - P.ph;
         x_start = P.x0;
     }
+    if (!A_KMAJOR && P.flat)
+        z_start = y_start = x_start = 0; // the raw tile holds whole planes
+    // Row p of this CTA's tile: is it an output pixel, where does its receptive field start in the raw tile, where does
+    // it go in y.
+    auto pixel_geom = [&](int p, bool &valid, int &base_p, long long &y_off) {
+        base_p = 0;
+        y_off = 0;
+        if (A_KMAJOR) {
+            const int row = (int)blockIdx.x * kTileM + p;
+            valid = row < P.m_rows;
+            y_off = (long long)zb * P.ys_n + (long long)row * P.ys_p;
+        } else if (P.wide) {
+            const int xl = w_tx * kTileM + p;
+            valid = xl < P.own;
+            if (valid) {
+                const int oh = P.oh0 + w_yl, ow = P.ow0 + xl;
+                base_p = ow * P.sw - P.pw - x_start;
+                const long long img = P.z_is_batch ? (long long)zb : (long long)n_lo;
+                y_off = img * P.ys_n + ((long long)(w_zl * P.OH + oh) * P.OW + ow) * P.ys_p;
+            }
+        } else {
+            int ul = 0, q = q0 + p;
+            if (P.ipt > 1) {
+                ul = p / P.Pw;
+                q = p - ul * P.Pw;
+            }
+            const int unit = unit0 + ul;
+            valid = (ul < P.ipt) && (unit < P.units) && (q < P.Pw);
+            if (valid) {
+                const int n = unit / P.OD;
+                const int zl = unit - n * P.OD;
+                const int yl = q / P.own;
+                const int xl = q - yl * P.own;
+                const int oh = P.oh0 + yl, ow = P.ow0 + xl;
+                base_p = (((n - n_lo) * P.BC * P.RD + (zl * P.sd - P.pd - z_start)) * P.RH + (oh * P.sh - P.ph - y_start)) * P.RW +
+                         (ow * P.sw - P.pw - x_start);
+                const long long img = P.z_is_batch ? (long long)zb : (long long)n;
+                y_off = img * P.ys_n + ((long long)(zl * P.OH + oh) * P.OW + ow) * P.ys_p;
+            }
+        }
+    };
     // split-K: this CTA reduces the channel chunks [c0, c1)
     const int c0 = (int)((long long)ksp * P.nchunks / P.ksplit), c1 = (int)((long long)(ksp + 1) * P.nchunks / P.ksplit);
     const int KS = (c1 - c0) * P.spc;
@@ -359,10 +409,10 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             }
         }
     } else if (warp == 2) {
-        // ---------------- raw activation producer (one thread) ----------------
+        // ---------------- raw activation producer ----------------
+        const int c_base = P.z_is_batch ? 0 : zb * P.cpg;
+        const int n_start = P.z_is_batch ? zb : n_lo;
         if (lane == 0) {
-            const int c_base = P.z_is_batch ? 0 : zb * P.cpg;
-            const int n_start = P.z_is_batch ? zb : n_lo;
             const uint32_t bytes = (uint32_t)P.RN * P.BC * P.RD * P.RH * P.RW * 4u;
             int rb = 0;
             uint32_t pr = 1; // first pass over the ring: every buffer is free
@@ -373,6 +423,10 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                     ptx::mbar_expect_tx(raw_full + rb, (uint32_t)kAHalfBytes);
                     ptx::tma_load_3d(sRaw + (size_t)rb * P.raw_bytes, &tmap_x, raw_full + rb, (c0 + ch) * kStageK,
                                      (int)blockIdx.x * kTileM, zb);
+                } else if (P.flat) {
+                    ptx::mbar_expect_tx(raw_full + rb, bytes);
+                    ptx::tma_load_3d(sRaw + (size_t)rb * P.raw_bytes, &tmap_x, raw_full + rb, 0,
+                                     ((c_base + (c0 + ch) * P.BC) / P.BC) * P.flat_rows, n_start);
                 } else {
                     ptx::mbar_expect_tx(raw_full + rb, bytes);
                     ptx::tma_load_5d(sRaw + (size_t)rb * P.raw_bytes, &tmap_x, raw_full + rb, x_start, y_start, z_start,
@@ -530,40 +584,26 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         const int quarter = warp & 3;         // TMEM lane quarter this warp may access
         const int p = quarter * 32 + lane;    // pixel row inside the tile
         bool valid;
-        int base_p = 0;
-        long long y_off = 0;
-        if (A_KMAJOR) {
-            const int row = (int)blockIdx.x * kTileM + p;
-            valid = row < P.m_rows;
-            y_off = (long long)zb * P.ys_n + (long long)row * P.ys_p;
-        } else if (P.wide) {
-            const int xl = w_tx * kTileM + p;
-            valid = xl < P.own;
-            if (valid) {
-                const int oh = P.oh0 + w_yl, ow = P.ow0 + xl;
-                base_p = ow * P.sw - P.pw - x_start;
-                const long long img = P.z_is_batch ? (long long)zb : (long long)n_lo;
-                y_off = img * P.ys_n + ((long long)(w_zl * P.OH + oh) * P.OW + ow) * P.ys_p;
-            }
-        } else {
+        int base_p;
+        long long y_off;
+        pixel_geom(p, valid, base_p, y_off);
+        uint32_t tmask = 0;
+        if (!A_KMAJOR && P.flat && valid) { // which filter taps of this pixel lie inside the (unpadded) input
             int ul = 0, q = q0 + p;
             if (P.ipt > 1) {
                 ul = p / P.Pw;
                 q = p - ul * P.Pw;
             }
-            const int unit = unit0 + ul;
-            valid = (ul < P.ipt) && (unit < P.units) && (q < P.Pw);
-            if (valid) {
-                const int n = unit / P.OD;
-                const int zl = unit - n * P.OD;
-                const int yl = q / P.own;
-                const int xl = q - yl * P.own;
-                const int oh = P.oh0 + yl, ow = P.ow0 + xl;
-                base_p = (((n - n_lo) * P.BC * P.RD + (zl * P.sd - P.pd - z_start)) * P.RH + (oh * P.sh - P.ph - y_start)) * P.RW +
-                         (ow * P.sw - P.pw - x_start);
-                const long long img = P.z_is_batch ? (long long)zb : (long long)n;
-                y_off = img * P.ys_n + ((long long)(zl * P.OH + oh) * P.OW + ow) * P.ys_p;
-            }
+            const int zl = (unit0 + ul) % P.OD, yl = q / P.own, xl = q - yl * P.own;
+            const int z0 = zl * P.sd - P.pd, y0 = (P.oh0 + yl) * P.sh - P.ph, x0 = (P.ow0 + xl) * P.sw - P.pw;
+            int tap = 0;
+            for (int t = 0; t < P.T3[0]; ++t)
+                for (int r = 0; r < P.T3[1]; ++r)
+                    for (int sx = 0; sx < P.T3[2]; ++sx, ++tap) {
+                        const int z = z0 + t * P.dil[0], y = y0 + r * P.dil[1], x = x0 + sx * P.dil[2];
+                        if (z >= 0 && z < P.xD && y >= 0 && y < P.xH && x >= 0 && x < P.xW)
+                            tmask |= 1u << tap;
+                    }
         }
         bool alive = true;
         long long t_we = 0, t_wr = 0;
@@ -593,33 +633,10 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                     ptx::tc_fence_after();
                     uint32_t hi[32], lo[32];
                     const uint8_t *krow = sRaw + (size_t)rb * P.raw_bytes + (size_t)p * 128;
-#pragma unroll
-                    for (int c4 = 0; c4 < 8; ++c4) {
-                        float v0, v1, v2, v3;
-                        if (A_KMAJOR) { // row p of the swizzled [128][32] tile: 16-byte chunk c4 sits at c4 ^ (p & 7)
-                            const float4 t4 = *reinterpret_cast<const float4 *>(krow + ((c4 ^ (p & 7)) << 4));
-                            v0 = t4.x, v1 = t4.y, v2 = t4.z, v3 = t4.w;
-                        } else {
-                            const int4 o = ko[c4];
-                            v0 = o.x >= 0 ? raw[o.x] : 0.f, v1 = o.y >= 0 ? raw[o.y] : 0.f;
-                            v2 = o.z >= 0 ? raw[o.z] : 0.f, v3 = o.w >= 0 ? raw[o.w] : 0.f;
-                        }
-                        if (PASSES == 3) {
-                            hi[4 * c4 + 0] = __float_as_uint(v0) & 0xffffe000u;
-                            hi[4 * c4 + 1] = __float_as_uint(v1) & 0xffffe000u;
-                            hi[4 * c4 + 2] = __float_as_uint(v2) & 0xffffe000u;
-                            hi[4 * c4 + 3] = __float_as_uint(v3) & 0xffffe000u;
-                            lo[4 * c4 + 0] = __float_as_uint(v0 - __uint_as_float(hi[4 * c4 + 0]));
-                            lo[4 * c4 + 1] = __float_as_uint(v1 - __uint_as_float(hi[4 * c4 + 1]));
-                            lo[4 * c4 + 2] = __float_as_uint(v2 - __uint_as_float(hi[4 * c4 + 2]));
-                            lo[4 * c4 + 3] = __float_as_uint(v3 - __uint_as_float(hi[4 * c4 + 3]));
-                        } else { // single pass: round to nearest TF32 instead of letting the tensor core truncate
-                            hi[4 * c4 + 0] = ptx::cvt_rna_tf32(v0);
-                            hi[4 * c4 + 1] = ptx::cvt_rna_tf32(v1);
-                            hi[4 * c4 + 2] = ptx::cvt_rna_tf32(v2);
-                            hi[4 * c4 + 3] = ptx::cvt_rna_tf32(v3);
-                        }
-                    }
+                    if (!A_KMAJOR && P.flat)
+                        gather_split<false, true, PASSES>(ko, raw, krow, p, tmask, hi, lo);
+                    else
+                        gather_split<A_KMAJOR, false, PASSES>(ko, raw, krow, p, tmask, hi, lo);
                     const uint32_t t = tmem_base + ((uint32_t)(quarter * 32) << 16) + 256u + (uint32_t)sa * 64u;
                     ptx::tmem_st_32x32(t, hi);
                     if (PASSES == 3)
@@ -667,15 +684,15 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             alive = ptx::mbar_wait(acc_full, 0u, abort_flag);
         const long long t_epi0 = P.prof ? clock64() : 0;
         const bool vec_ok = (P.ys_f == 1) && ((P.ys_p & 3) == 0) && ((P.ys_n & 3) == 0) && ((P.Fg & 3) == 0) &&
-                            ((reinterpret_cast<uintptr_t>(P.y) & 15) == 0) && ((P.part_stride & 3) == 0) &&
-                            ((reinterpret_cast<uintptr_t>(P.partial) & 15) == 0);
-        int col0 = 0, col1 = 0;
+                            ((reinterpret_cast<uintptr_t>(P.y) & 15) == 0);
         if (alive) {
             ptx::tc_fence_after();
             const int f_tile0 = ntile * P.BN;
             const long long f_glob0 = P.z_is_batch ? 0 : (long long)zb * P.Fg;
-            float *yp = (P.ksplit > 1 ? P.partial + (long long)ksp * P.part_stride : P.y) + y_off + f_glob0 * P.ys_f;
+            float *yp = P.y + y_off + f_glob0 * P.ys_f;
             const float *bp = (P.has_bias && P.ksplit == 1) ? P.bias + f_glob0 : nullptr;
+            // split-K: the partial tile is staged in the (now idle) B ring for the cluster reduction after the role branches
+            float *split_row = P.ksplit > 1 ? reinterpret_cast<float *>(sB) + p : nullptr;
             const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16);
             // staged 16-byte stores need: pixel-contiguous NCHW output, full-width rows (no column window), one plane per
             // tile, 16-byte aligned runs
@@ -686,8 +703,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             float *ybase_warp = yp - y_off + y_off0;
             if (P.ys_p == 1 && P.ipt == 1 && P.own == P.OW && P.ow0 == 0 && (plane_elems & 3) == 0 && (P.ys_n & 3) == 0 &&
                 ((P.OH * P.OW) & 3) == 0 && (!P.wide || (P.OW & 3) == 0) &&
-                (P.ys_f & 3) == 0 && ((P.oh0 * P.OW) & 3) == 0 && (P.part_stride & 3) == 0 &&
-                ((reinterpret_cast<uintptr_t>(P.y) | reinterpret_cast<uintptr_t>(P.partial)) & 15) == 0) {
+                (P.ys_f & 3) == 0 && ((P.oh0 * P.OW) & 3) == 0 && P.ksplit == 1 &&
+                (reinterpret_cast<uintptr_t>(P.y) & 15) == 0) {
                 nvalid_warp = __popc(__ballot_sync(0xffffffffu, valid));
                 if (nvalid_warp > 0)
                     stage = reinterpret_cast<float *>(sB) + (warp - 3) * 1024; // B stages are idle once the accumulator is complete
@@ -696,11 +713,10 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             }
             // the two sets split the tile's columns (whole 32-column blocks)
             const int nblk = P.BN / 32, half_blk = (nblk + 1) / 2;
-            col0 = tset == 0 ? 0 : half_blk * 32;
-            col1 = tset == 0 ? half_blk * 32 : P.BN;
+            const int col0 = tset == 0 ? 0 : half_blk * 32, col1 = tset == 0 ? half_blk * 32 : P.BN;
 #define PETB200_EPI(ACT_)                                                                                              \
     epilogue_store<ACT_, PASSES>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, \
-                                 ybase_warp, col0, col1)
+                                 ybase_warp, col0, col1, split_row)
             switch (P.ksplit > 1 ? PETB200_ACT_NONE : P.act) {
             case PETB200_ACT_RELU: PETB200_EPI(PETB200_ACT_RELU); break;
             case PETB200_ACT_SIGMOID: PETB200_EPI(PETB200_ACT_SIGMOID); break;
@@ -709,47 +725,6 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             default: PETB200_EPI(PETB200_ACT_NONE); break;
             }
 #undef PETB200_EPI
-        }
-        if (P.ksplit > 1) {
-            // Split-K: count this CTA in at its output tile; the last one to arrive adds the partial sums up.  Nothing
-            // waits for another CTA.  Both barriers are reached by all eight epilogue warps whatever happened before.
-            if (P.prof && threadIdx.x == 96)
-                P.prof[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * kProfSlots + 12] = (long long)ptx::globaltimer_ns();
-            __threadfence(); // this thread's partial sums are visible device-wide before the arrival is counted
-            ptx::named_bar_sync(1, 8 * 32);
-            if (P.prof && threadIdx.x == 96)
-                P.prof[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * kProfSlots + 13] = (long long)ptx::globaltimer_ns();
-            if (threadIdx.x == 96) {
-                int last = 0;
-                if (*abort_flag == 0) {
-                    int *ticket = P.tickets + ((size_t)zb * (gridDim.y / P.ksplit) + ntile) * gridDim.x + blockIdx.x;
-                    last = (atomicAdd(ticket, 1) == P.ksplit - 1) ? 1 : 0;
-                    if (last)
-                        *ticket = 0; // every split has arrived: ready for the next launch
-                }
-                *last_flag = last;
-            }
-            ptx::named_bar_sync(1, 8 * 32);
-            if (P.prof && threadIdx.x == 96)
-                P.prof[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * kProfSlots + 14] = (long long)ptx::globaltimer_ns();
-            if (*last_flag) {
-                __threadfence();
-                const long long f_glob0 = P.z_is_batch ? 0 : (long long)zb * P.Fg;
-                const float *part = P.partial + y_off + f_glob0 * P.ys_f;
-                float *yf = P.y + y_off + f_glob0 * P.ys_f;
-                const float *bp = P.has_bias ? P.bias + f_glob0 : nullptr;
-#define PETB200_FIX(ACT_) \
-    splitk_fixup<ACT_>(part, P.part_stride, P.ksplit, ntile * P.BN, P.Fg, valid, bp, yf, P.ys_f, vec_ok, tset * (P.BN / 2), \
-                       (tset + 1) * (P.BN / 2))
-                switch (P.act) {
-                case PETB200_ACT_RELU: PETB200_FIX(PETB200_ACT_RELU); break;
-                case PETB200_ACT_SIGMOID: PETB200_FIX(PETB200_ACT_SIGMOID); break;
-                case PETB200_ACT_TANH: PETB200_FIX(PETB200_ACT_TANH); break;
-                case PETB200_ACT_GELU: PETB200_FIX(PETB200_ACT_GELU); break;
-                default: PETB200_FIX(PETB200_ACT_NONE); break;
-                }
-#undef PETB200_FIX
-            }
         }
         if (P.prof && threadIdx.x == 96) { // lane 0 of warp 3 (transform set 0)
             long long *pr = P.prof + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * kProfSlots;
@@ -760,6 +735,36 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             pr[7] = t_epi0 - t_begin;
             pr[10] = (long long)ptx::globaltimer_ns();
         }
+    }
+
+    // ---------------- split-K: reduction across the cluster ----------------
+    // Every thread of every CTA of the cluster reaches both barriers (all waits above are bounded).
+    if (P.ksplit > 1) {
+        ptx::cluster_sync_all(); // all partial tiles are staged
+        if (warp >= 3) {
+            const int et = threadIdx.x - 96;
+            bool valid;
+            int base_p;
+            long long y_off;
+            pixel_geom(et & (kTileM - 1), valid, base_p, y_off);
+            if (valid && *abort_flag == 0) {
+                const long long f_glob0 = P.z_is_batch ? 0 : (long long)zb * P.Fg;
+                float *yp = P.y + y_off + f_glob0 * P.ys_f;
+                const float *bp = P.has_bias ? P.bias + f_glob0 : nullptr;
+                const uint32_t stage_addr = ptx::smem_u32(sB);
+                const int rank = (int)ptx::cluster_ctarank();
+#define PETB200_RED(ACT_) cluster_reduce_store<ACT_>(stage_addr, P.ksplit, rank, P.BN, et, ntile * P.BN, P.Fg, bp, yp, P.ys_f)
+                switch (P.act) {
+                case PETB200_ACT_RELU: PETB200_RED(PETB200_ACT_RELU); break;
+                case PETB200_ACT_SIGMOID: PETB200_RED(PETB200_ACT_SIGMOID); break;
+                case PETB200_ACT_TANH: PETB200_RED(PETB200_ACT_TANH); break;
+                case PETB200_ACT_GELU: PETB200_RED(PETB200_ACT_GELU); break;
+                default: PETB200_RED(PETB200_ACT_NONE); break;
+                }
+#undef PETB200_RED
+            }
+        }
+        ptx::cluster_sync_all(); // peers have finished reading this CTA's tile
     }
 
     // ---------------- teardown ----------------
@@ -850,13 +855,20 @@ struct TcCore {
     int xd[5]{}; // W,H,D,C,N of the activation tensor as the kernel sees it
     long long Ktot = 0;
     int rows_b = 0;
-    DevBuf whi, wlo, koff, partial, tickets;
+    DevBuf whi, wlo, koff;
     long long y_elems = 0;
     CUtensorMap map_x{}, map_bhi{}, map_blo{};
     const void *map_x_ptr = nullptr;
     bool weights_ready = false;
     long long *prof = nullptr;
 
+    void (*kernel() const)(CUtensorMap, CUtensorMap, CUtensorMap, IgemmParams) {
+        if (single_pass)
+            return P.a_kmajor ? k_igemm<true, true, 1> : k_igemm<true, false, 1>;
+        if (P.a_kmajor)
+            return k_igemm<true, true, 3>;
+        return a_tmem ? k_igemm<true, false, 3> : k_igemm<false, false, 3>;
+    }
     int encode_x(const float *x) {
         if (x == map_x_ptr)
             return PETB200_OK;
@@ -873,6 +885,20 @@ struct TcCore {
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r3 != CUDA_SUCCESS)
                 return fail(ctx, PETB200_ERR_CUDA, "cuTensorMapEncodeTiled(row-major A) failed with %d", (int)r3);
+            map_x_ptr = x;
+            return PETB200_OK;
+        }
+        if (P.flat) { // each image is one run of C*D*H*W floats, viewed as rows of flat_w
+            const cuuint64_t run = (cuuint64_t)xd[0] * xd[1] * xd[2] * xd[3];
+            cuuint64_t d3[3] = {(cuuint64_t)P.flat_w, run / P.flat_w, (cuuint64_t)xd[4]};
+            cuuint64_t s3[2] = {(cuuint64_t)P.flat_w * 4, run * 4};
+            cuuint32_t b3[3] = {(cuuint32_t)P.flat_w, (cuuint32_t)P.flat_rows, (cuuint32_t)P.RN};
+            cuuint32_t e3[3] = {1, 1, 1};
+            CUresult r3 = enc(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(x), d3, s3, b3, e3,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r3 != CUDA_SUCCESS)
+                return fail(ctx, PETB200_ERR_CUDA, "cuTensorMapEncodeTiled(flat activations) failed with %d", (int)r3);
             map_x_ptr = x;
             return PETB200_OK;
         }
@@ -913,23 +939,31 @@ struct TcCore {
         IgemmParams p = P;
         p.bias = bias;
         p.y = y;
-        p.partial = (float *)partial.p;
-        p.tickets = (int *)tickets.p;
         p.koff = (const int *)koff.p;
         p.status = ctx->d_status;
         p.prof = prof;
         { static int d = -1; if (d < 0) { const char *e = getenv("PETB200_TC_DBG"); d = e ? atoi(e) : 0; } p.dbg = d; }
         p.has_bias = (P.has_bias && bias) ? 1 : 0;
-        if (single_pass && P.a_kmajor)
-            k_igemm<true, true, 1><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
-        else if (single_pass)
-            k_igemm<true, false, 1><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
-        else if (P.a_kmajor)
-            k_igemm<true, true, 3><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
-        else if (a_tmem)
-            k_igemm<true, false, 3><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
-        else
-            k_igemm<false, false, 3><<<grid, kThreads, smem, s>>>(map_x, map_bhi, map_blo, p);
+        void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, IgemmParams) = kernel();
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = s;
+        cudaLaunchAttribute attr{};
+        if (P.ksplit > 1) { // the splits of one output tile are consecutive in blockIdx.y: one cluster
+            attr.id = cudaLaunchAttributeClusterDimension;
+            attr.val.clusterDim.x = 1;
+            attr.val.clusterDim.y = (unsigned)P.ksplit;
+            attr.val.clusterDim.z = 1;
+            cfg.attrs = &attr;
+            cfg.numAttrs = 1;
+        }
+        cudaError_t le = cudaLaunchKernelEx(&cfg, kern, map_x, map_bhi, map_blo, p);
+        if (le != cudaSuccess) {
+            (void)cudaGetLastError();
+            return fail(ctx, PETB200_ERR_CUDA, "launch of k_igemm failed: %s", cudaGetErrorString(le));
+        }
         return launched(ctx, "k_igemm");
     }
 };
@@ -953,36 +987,37 @@ static int env_int(const char *name, int dflt) {
 // ~3000 cycles before its first MMA and 1700 + 44*BN cycles of epilogue; the split-K fix-up re-reads every partial copy
 // through L2, four copies per round trip.
 static double est_cycles(int sm_count, long long base_ctas, int nchunks, int spc, int BN, int passes, int ks) {
-    const double stage = std::max<double>((passes == 3 ? 12.0 : 4.0) * (BN / 2), 330.0);
+    const double stage = std::max<double>((passes == 3 ? 12.0 : 4.0) * (BN / 2), 520.0);
     const long long stages = (long long)((nchunks + ks - 1) / ks) * spc;
-    const double per_cta = 3000.0 + (double)stages * stage + 1700.0 + 44.0 * BN;
-    const long long waves = (base_ctas * ks + sm_count - 1) / sm_count;
-    const double fix = ks > 1 ? 1200.0 + (double)((ks + 3) / 4) * (BN / 32) * 700.0 : 0.0;
-    return (double)waves * per_cta + fix;
+    const double per_cta = 3000.0 + (double)stages * stage + 1700.0 + (ks > 1 ? 12.0 * BN + 1500.0 : 44.0 * BN);
+    // clusters are placed inside one GPC, which leaves a few SMs of each GPC unused
+    const long long slots = ks == 1 ? sm_count : std::max(1, (sm_count * (ks <= 2 ? 96 : 86) / 100) / ks);
+    const long long waves = (base_ctas + slots - 1) / slots;
+    return (double)waves * per_cta;
 }
-static int choose_ksplit(int sm_count, long long base_ctas, int nchunks, int spc, int BN, int passes, double *cycles) {
+// Split K over 1, 2, 4 or 8 CTAs (a cluster): the split must divide the tile width, leave every CTA a chunk, and the
+// staged tile (512*BN bytes) must fit the B ring.
+static int choose_ksplit(int sm_count, long long base_ctas, const IgemmParams &P, int passes, int want, double *cycles) {
+    const size_t ring = (size_t)P.NB * (passes == 3 ? 2 : 1) * P.BN * 128;
+    auto ok = [&](int ks) { return ks == 1 || (ks <= P.nchunks && P.BN % ks == 0 && (size_t)512 * P.BN <= ring); };
     int best = 1;
-    double best_c = est_cycles(sm_count, base_ctas, nchunks, spc, BN, passes, 1);
-    for (int ks = 2; ks <= std::min(nchunks, 32); ++ks) {
-        if ((nchunks + ks - 1) / ks == (nchunks + ks - 2) / (ks - 1))
-            continue; // no shorter than the previous split
-        const double c = est_cycles(sm_count, base_ctas, nchunks, spc, BN, passes, ks);
-        if (c < best_c * 0.97) // a deeper split has to pay for its extra traffic
-            best = ks, best_c = c;
+    double best_c = est_cycles(sm_count, base_ctas, P.nchunks, P.spc, P.BN, passes, 1);
+    if (want > 0) {
+        for (best = 8; best > 1 && !(best <= want && ok(best)); best /= 2) {
+        }
+        best_c = est_cycles(sm_count, base_ctas, P.nchunks, P.spc, P.BN, passes, best);
+    } else {
+        for (int ks = 2; ks <= 8; ks *= 2) {
+            if (!ok(ks))
+                continue;
+            const double c = est_cycles(sm_count, base_ctas, P.nchunks, P.spc, P.BN, passes, ks);
+            if (c < best_c * 0.97) // a deeper split has to pay for itself
+                best = ks, best_c = c;
+        }
     }
     if (cycles)
         *cycles = best_c;
     return best;
-}
-
-// Scratch of a split-K plan: the partial copies and one arrival counter per output tile (zero between launches).
-static int alloc_split_scratch(petb200_ctx *ctx, TcCore &c, long long tiles) {
-    if (c.P.ksplit <= 1)
-        return PETB200_OK;
-    if (c.partial.alloc((size_t)c.P.ksplit * c.P.part_stride * 4) != cudaSuccess || c.tickets.alloc((size_t)tiles * 4) != cudaSuccess)
-        return fail(ctx, PETB200_ERR_NOMEM, "split-K scratch allocation failed");
-    PETB200_CUDA(ctx, cudaMemset(c.tickets.p, 0, (size_t)tiles * 4));
-    return PETB200_OK;
 }
 
 // The dynamic shared-memory attribute is per function, not per launch: raise it once to the device limit so that plans
@@ -1009,11 +1044,15 @@ static int raise_smem_limit(petb200_ctx *ctx) {
 
 static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int oh0, int ohn, int ow0, int own,
                         int z_is_batch, int images, long long ys_n, long long ys_f, long long ys_p, int has_bias, int act,
-                        int force_bc = 0, int force_ksplit = 0, int force_bn = 0) {
+                        int force_bc = 0, int force_ksplit = 0, int force_bn = 0, int flat = 0) {
     IgemmParams &P = core.P;
     const int cpg = g.C / g.groups, Fg = g.F / g.groups;
-    if (g.Wst % 4 != 0)
-        return fail(ctx, PETB200_ERR_UNSUPPORTED, "tensor-core path needs a row pitch divisible by 4 (TMA stride rule), got %d", g.Wst);
+    if (!flat && g.Wst % 4 != 0)
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "the TMA box needs a row pitch divisible by 4, got %d", g.Wst);
+    P.flat = flat ? 1 : 0;
+    P.xD = g.D, P.xH = g.H, P.xW = g.W;
+    for (int i = 0; i < 3; ++i)
+        P.T3[i] = g.T3[i], P.dil[i] = g.dil[i];
     P.OD = g.OD;
     P.OH = g.OH;
     P.OW = g.OW;
@@ -1078,9 +1117,17 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
         P.RD = ((g.OD == 1) ? 0 : (P.ipt - 1) * P.sd) + (g.T3[0] - 1) * g.dil[0] + 1;
         P.RH = (RHo - 1) * P.sh + (g.T3[1] - 1) * g.dil[1] + 1;
     }
-    if (P.RW > 256 || P.RH > 256 || P.RD > 256 || P.RN > 256)
-        return fail(ctx, PETB200_ERR_UNSUPPORTED, "raw activation box %dx%dx%dx%d exceeds the TMA box limit", P.RN, P.RD, P.RH, P.RW);
     const int T = g.T3[0] * g.T3[1] * g.T3[2];
+    if (flat) {
+        // whole, unpadded planes: BC channels x all depth slices of RN images; padding is a mask over the taps
+        if (P.wide || T > 32 || g.Wst != g.W)
+            return fail(ctx, PETB200_ERR_UNSUPPORTED, "flat raw tiles need rows of at most 128 pixels and at most 32 taps");
+        P.x0 = 0;
+        P.RW = g.W, P.RH = g.H, P.RD = g.D;
+        P.RN = (g.OD == 1) ? P.ipt : 1;
+    } else if (P.RW > 256 || P.RH > 256 || P.RD > 256 || P.RN > 256) {
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "raw activation box %dx%dx%dx%d exceeds the TMA box limit", P.RN, P.RD, P.RH, P.RW);
+    }
     const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 1024; // alignment slack
     core.a_tmem = core.single_pass || env_int("PETB200_TC_A_TMEM", 1) != 0; // the single-pass variant exists for TS only
     const int forced_bc = force_bc > 0 ? force_bc : env_int("PETB200_TC_BC", 0);
@@ -1105,7 +1152,18 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
             P.NR = 2;
             P.a_kmajor = 0;
             P.m_rows = 0;
-            if (smem_layout(P, core.a_tmem).total <= budget) {
+            bool shape_ok = true;
+            if (flat) {
+                // The BC*D*H*W floats of a chunk are one contiguous run: fetch it as a 2-D box [rows][w] with w a multiple
+                // of 4 (16-byte rule), both extents within the TMA box limit; chunks must start on a box boundary.
+                const long long L = (long long)BC * g.D * g.H * g.W;
+                P.flat_w = 0;
+                for (int w = 256; w >= 4 && !P.flat_w; w -= 4)
+                    if (L % w == 0 && L / w <= 256)
+                        P.flat_w = w, P.flat_rows = (int)(L / w);
+                shape_ok = P.flat_w != 0 && cpg % BC == 0 && P.RN <= 256;
+            }
+            if (shape_ok && smem_layout(P, core.a_tmem).total <= budget) {
                 // deepen the rings while there is room: B first (it hides TMA latency), then A
                 for (bool grew = true; grew;) {
                     grew = false;
@@ -1151,12 +1209,7 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
         const long long base_ctas = (long long)mtiles * ((Fg + bn - 1) / bn) * gz;
         const int passes = core.single_pass ? 1 : 3;
         double cyc;
-        if (want_ks > 0) {
-            P.ksplit = std::min(want_ks, P.nchunks);
-            cyc = est_cycles(ctx->sm_count, base_ctas, P.nchunks, P.spc, bn, passes, P.ksplit);
-        } else {
-            P.ksplit = choose_ksplit(ctx->sm_count, base_ctas, P.nchunks, P.spc, bn, passes, &cyc);
-        }
+        P.ksplit = choose_ksplit(ctx->sm_count, base_ctas, P, passes, want_ks, &cyc);
         if (!have || cyc < best_cycles * 0.97) { // prefer the wider tile unless the narrower one clearly wins
             have = true;
             best_cycles = cyc;
@@ -1166,6 +1219,8 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     if (!have)
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "raw activation tile does not fit shared memory");
     P = bestP;
+    if (flat && (!core.a_tmem || (long long)P.RN * P.BC * P.RD * P.RH * P.RW >= (1 << 24)))
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "flat raw tiles need the TS kernel variant");
     const int BN = P.BN;
     if (core.a_tmem && BN > 256)
         return fail(ctx, PETB200_ERR_INVALID, "TS variant supports BN <= 256");
@@ -1174,12 +1229,6 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     core.y_elems = (z_is_batch ? (long long)images : (long long)n_img) * g.F * g.OD * g.OH * g.OW;
     if (z_is_batch)
         core.y_elems = (long long)images * ys_n;
-    P.part_stride = (core.y_elems + 3) / 4 * 4;
-    {
-        int rc = alloc_split_scratch(ctx, core, (long long)mtiles * ntiles * gz);
-        if (rc)
-            return rc;
-    }
     core.grid = dim3((unsigned)mtiles, (unsigned)(ntiles * P.ksplit), (unsigned)gz);
     core.Ktot = (long long)P.nchunks * P.spc * kStageK;
     core.xd[0] = g.Wst;
@@ -1193,7 +1242,8 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     for (int tap = 0; tap < T; ++tap) {
         int t = tap / (g.T3[1] * g.T3[2]), r = (tap / g.T3[2]) % g.T3[1], s = tap % g.T3[2];
         for (int ci = 0; ci < P.BC; ++ci)
-            koff[(size_t)tap * P.BC + ci] = ci * plane_d + t * g.dil[0] * plane_h + r * g.dil[1] * plane_w + s * g.dil[2];
+            koff[(size_t)tap * P.BC + ci] =
+                (ci * plane_d + t * g.dil[0] * plane_h + r * g.dil[1] * plane_w + s * g.dil[2]) | (flat ? tap << 24 : 0);
     }
     if (core.koff.alloc(koff.size() * 4) != cudaSuccess)
         return fail(ctx, PETB200_ERR_NOMEM, "koff allocation failed");
@@ -1252,13 +1302,24 @@ int tc_conv_create(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const i
     g.OD = nsp == 3 ? oext(g.D, g.T3[0], g.pad[0], g.stride[0], g.dil[0]) : 1;
     g.OH = oext(g.H, g.T3[1], g.pad[1], g.stride[1], g.dil[1]);
     g.OW = oext(g.W, g.T3[2], g.pad[2], g.stride[2], g.dil[2]);
-    g.Wst = (g.W + 3) / 4 * 4; // the caller re-pitches the input when this differs from W
+    g.Wst = g.W;
     t->has_bias = has_bias;
     t->act = act;
     t->full.ctx = ctx;
     t->full.single_pass = passes == 1;
     const long long plane = (long long)g.OD * g.OH * g.OW;
-    int rc = tc_configure(ctx, t->full, g, 0, g.OH, 0, g.OW, 0, g.N, (long long)g.F * plane, plane, 1, has_bias, act);
+    // Rows that are not multiples of 16 bytes cannot be a TMA stride: small planes are fetched whole ("flat"), anything
+    // else is re-pitched by the caller first (tc_conv_row_pitch tells it to what).
+    int rc = PETB200_ERR_UNSUPPORTED;
+    if (g.W % 4 != 0) {
+        rc = tc_configure(ctx, t->full, g, 0, g.OH, 0, g.OW, 0, g.N, (long long)g.F * plane, plane, 1, has_bias, act, 0, 0, 0, 1);
+        if (rc == PETB200_ERR_UNSUPPORTED) {
+            g.Wst = (g.W + 3) / 4 * 4;
+            memset(&t->full.P, 0, sizeof t->full.P);
+        }
+    }
+    if (rc == PETB200_ERR_UNSUPPORTED)
+        rc = tc_configure(ctx, t->full, g, 0, g.OH, 0, g.OW, 0, g.N, (long long)g.F * plane, plane, 1, has_bias, act);
     if (rc) {
         delete t;
         return rc;
@@ -1275,7 +1336,7 @@ int tc_conv_create(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const i
         delete t;
         return rc;
     }
-    *dev_bytes = 2 * wbytes + c.koff.bytes + c.partial.bytes;
+    *dev_bytes = 2 * wbytes + c.koff.bytes;
     *out = t;
     return PETB200_OK;
 }
@@ -1313,7 +1374,7 @@ int tc_conv_run(void *h, const float *x, const float *bias, float *y, const int 
         // A window must consume K in exactly the order of the full operator (same BC / chunking), otherwise the
         // two would round differently; the raw box only shrinks for a window, so the full plan's BC always fits.
         int rc = tc_configure(wc->ctx, *wc, g, win[0], win[1], win[2], win[3], 0, g.N, (long long)g.F * plane, plane, 1,
-                              t->has_bias, t->act, t->full.P.BC, t->full.P.ksplit, t->full.P.BN);
+                              t->has_bias, t->act, t->full.P.BC, t->full.P.ksplit, t->full.P.BN, t->full.P.flat);
         if (rc == PETB200_OK && (wc->P.BN != t->full.P.BN || wc->P.BC != t->full.P.BC || wc->Ktot != t->full.Ktot || wc->P.ksplit != t->full.P.ksplit))
             rc = fail(wc->ctx, PETB200_ERR_UNSUPPORTED, "window plan diverged from the full plan");
         if (rc) {
@@ -1352,19 +1413,14 @@ struct TcMatmul {
     bool native_a = false; // A is consumed row-major as passed (no re-layout)
 };
 
-// Shared tail of the row-major-A matmul configuration: split-K decision, scratch, grid.
+// Shared tail of the row-major-A matmul configuration: split-K decision, grid.
 static int matmul_finish(petb200_ctx *ctx, TcCore &c, int bs, int m, int n, int mtiles) {
     IgemmParams &P = c.P;
     const int ntiles = (n + P.BN - 1) / P.BN;
     const long long ctas = (long long)mtiles * ntiles * bs;
     const int want = env_int("PETB200_TC_KSPLIT", 0);
-    P.ksplit = want > 0 ? std::min(want, P.nchunks)
-                        : choose_ksplit(ctx->sm_count, ctas, P.nchunks, P.spc, P.BN, c.single_pass ? 1 : 3, nullptr);
+    P.ksplit = choose_ksplit(ctx->sm_count, ctas, P, c.single_pass ? 1 : 3, want, nullptr);
     c.y_elems = (long long)bs * m * n;
-    P.part_stride = (c.y_elems + 3) / 4 * 4;
-    int rc = alloc_split_scratch(ctx, c, ctas);
-    if (rc)
-        return rc;
     c.grid = dim3((unsigned)mtiles, (unsigned)(ntiles * P.ksplit), (unsigned)bs);
     return raise_smem_limit(ctx);
 }
@@ -1479,7 +1535,7 @@ int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, 
         delete t;
         return rc;
     }
-    *dev_bytes = 2 * wbytes + c.koff.bytes + c.partial.bytes;
+    *dev_bytes = 2 * wbytes + c.koff.bytes;
     *out = t;
     return PETB200_OK;
 }

@@ -65,6 +65,43 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// ---- thread-block clusters: hardware barrier and distributed shared memory ------------------------------------------
+// The barrier counts every thread of every CTA of the cluster that has not exited; the non-aligned forms may be
+// executed by diverged warps.  release/acquire make shared-memory writes before the arrive visible to peers after
+// their wait.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of the same shared-memory location in the CTA with the given rank of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t cluster_addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+    return v;
+}
+
+// ---- 4-byte asynchronous copies (for sources TMA cannot address) ---------------------------------------------------
+// Copies 4 bytes, or writes 4 zero bytes without reading the source when `valid` is false (the zeros are then tracked
+// by the same completion mechanism as the copies).
+__device__ __forceinline__ void cp_async_4_zfill(void *smem_dst, const void *gmem_src, bool valid) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(valid ? 4 : 0)
+                 : "memory");
+}
+// The executing thread arrives on the barrier once all its earlier cp.async copies have completed; the arrival counts
+// against the barrier's expected count (noinc).
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t *bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 // ---- proxy fences -----------------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 

@@ -33,7 +33,8 @@ def test_batch_gemm_known_answer(ctx, golden, algo):
 MM = [  # b, m, n, k, transA, transB   (BERT-base shapes and ragged ones)
     (1, 128, 768, 768, False, False), (12, 128, 128, 64, False, True), (12, 128, 64, 128, False, False),
     (1, 128, 3072, 768, False, False), (1, 128, 768, 3072, False, False), (1, 1, 1000, 512, False, False),
-    (3, 5, 4, 7, False, False), (2, 36, 20, 50, True, True), (2, 300, 40, 24, True, False), (1, 64, 33, 100, False, True),
+    (3, 5, 4, 7, False, False), (2, 8, 70, 130, True, True), (1, 3, 100, 257, False, True), (2, 2, 65, 40, True, False),
+    (2, 36, 20, 50, True, True), (2, 300, 40, 24, True, False), (1, 64, 33, 100, False, True),
 ]
 
 
@@ -86,6 +87,9 @@ def test_pool_softmax_layernorm_batchnorm(ctx, oracle):
     y = rng.standard_normal((2, 512, 7, 7)).astype(np.float32)
     assert rel_err(ctx.avgpool(dev(y), 7, 7, 0, 0, 1, 1).cpu().numpy(), oracle.avgpool(y, (7, 7), (0, 0), (1, 1))) <= 1e-5
     assert rel_err(ctx.avgpool(dev(y), 3, 3, 1, 1, 2, 2).cpu().numpy(), oracle.avgpool(y, (3, 3), (1, 1), (2, 2))) <= 1e-5
+    # large windows (one warp per output), with padding and stride
+    assert np.array_equal(ctx.maxpool(dev(y), 6, 7, 1, 1, 2, 3, 3, 2).cpu().numpy(), oracle.maxpool(y, (6, 7), (2, 3), (3, 2)))
+    assert rel_err(ctx.avgpool(dev(y), 6, 7, 2, 3, 3, 2).cpu().numpy(), oracle.avgpool(y, (6, 7), (2, 3), (3, 2))) <= 1e-5
     assert rel_err(ctx.rowmean(dev(y), 49).cpu().numpy(), y.reshape(-1, 49).mean(1)) <= 1e-5
     s = rng.standard_normal((12, 128, 128)).astype(np.float32) * 4
     assert rel_err(ctx.softmax(dev(s)).cpu().numpy(), oracle.softmax(s)) <= 1e-5
