@@ -92,6 +92,12 @@ int petb200_conv2d_correct(petb200_plan *plan, const float *x, const float *bias
 int petb200_conv3d_plan(petb200_ctx *ctx, const int args[21], int algo, petb200_plan **out);
 int petb200_conv3d_set_weights(petb200_plan *plan, const float *w, petb200_stream stream);
 int petb200_conv3d_run(petb200_plan *plan, const float *x, const float *bias, float *y, petb200_stream stream);
+/* y = act(conv(x) + bias + residual) for a 2-D or 3-D convolution plan; residual has the shape of y (NULL: none).  The
+ * reference runs the residual Add of a ResNet block as its own operator (ref: src/Graph/operator.cc, AddOp); this entry
+ * lets an executor fold that Add (and the activation after it) into the convolution's epilogue.  Same arithmetic, in
+ * the same order, as petb200_conv2d_run followed by petb200_eltwise_run(add, act). */
+int petb200_conv_run_residual(petb200_plan *plan, const float *x, const float *bias, const float *residual, float *y,
+                              petb200_stream stream);
 
 /* ---- matmul ---------------------------------------------------------------------------------------------------
  * Replaces cublasGemmStridedBatchedEx / cublasGemmEx as issued by MatmulOp::perf (ref: src/Graph/operator.cc:728-832)
@@ -105,6 +111,9 @@ int petb200_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, 
 int petb200_matmul_set_weights(petb200_plan *plan, const float *b, petb200_stream stream);
 int petb200_matmul_run(petb200_plan *plan, const float *a, const float *b, const float *bias, float *c,
                        petb200_stream stream);
+/* c = act(op(A)·op(B) + bias + residual); residual has the shape of c (NULL: none).  See petb200_conv_run_residual. */
+int petb200_matmul_run_residual(petb200_plan *plan, const float *a, const float *b, const float *bias,
+                                const float *residual, float *c, petb200_stream stream);
 
 /* ---- layout / index operators (bit-exact copies of 32-bit words) ------------------------------------------
  * One TransposeOp (ref: include/operator.h:1100-1202; host definition src/Graph/operator.cc:2172-2210): input dim

@@ -140,6 +140,11 @@ extern "C" int petb200_conv3d_run(petb200_plan *plan, const float *x, const floa
     return conv_run(plan, x, bias, y, nullptr, (cudaStream_t)s);
 }
 
+extern "C" int petb200_conv_run_residual(petb200_plan *plan, const float *x, const float *bias, const float *residual, float *y,
+                                         petb200_stream s) {
+    return conv_run(plan, x, bias, y, nullptr, (cudaStream_t)s, residual);
+}
+
 extern "C" int petb200_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int n, int k, int has_bias,
                                    int act, int algo, petb200_plan **out) {
     return make_matmul_plan(ctx, transA, transB, b, m, n, k, has_bias, act, algo, out);
@@ -150,6 +155,11 @@ extern "C" int petb200_matmul_set_weights(petb200_plan *plan, const float *b, pe
 extern "C" int petb200_matmul_run(petb200_plan *plan, const float *a, const float *b, const float *bias, float *c,
                                   petb200_stream s) {
     return matmul_run(plan, a, b, bias, c, (cudaStream_t)s);
+}
+
+extern "C" int petb200_matmul_run_residual(petb200_plan *plan, const float *a, const float *b, const float *bias,
+                                           const float *residual, float *c, petb200_stream s) {
+    return matmul_run(plan, a, b, bias, c, (cudaStream_t)s, residual);
 }
 
 extern "C" int petb200_plan_time(petb200_plan *plan, int rounds, int warmup, float *ms, petb200_stream stream) {

@@ -98,12 +98,13 @@ int make_conv_plan(petb200_ctx *ctx, int nsp, const int *in_dims /*n,c,[d],h,w*/
                    petb200_plan **out);
 int conv_set_weights(petb200_plan *plan, const float *w, cudaStream_t s);
 int conv_run(petb200_plan *plan, const float *x, const float *bias, float *y, const int *win /*oh0,ohn,ow0,own or null*/,
-             cudaStream_t s);
+             cudaStream_t s, const float *res = nullptr /*optional residual, shaped like y*/);
 int conv_out_dims(const petb200_plan *plan, int *dims5);
 
 int make_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int n, int k, int has_bias, int act,
                      int algo, petb200_plan **out);
 int matmul_set_weights(petb200_plan *plan, const float *b, cudaStream_t s);
-int matmul_run(petb200_plan *plan, const float *a, const float *b, const float *bias, float *c, cudaStream_t s);
+int matmul_run(petb200_plan *plan, const float *a, const float *b, const float *bias, float *c, cudaStream_t s,
+               const float *res = nullptr /*optional residual, shaped like c*/);
 
 } // namespace petb200

@@ -11,7 +11,7 @@ int tc_conv_create(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const i
                    const int *dil, int groups, int has_bias, int act, int passes, void **out, size_t *dev_bytes);
 void tc_conv_destroy(void *h);
 int tc_conv_set_weights(void *h, const float *w, cudaStream_t s);
-int tc_conv_run(void *h, const float *x, const float *bias, float *y, const int *win, cudaStream_t s);
+int tc_conv_run(void *h, const float *x, const float *bias, const float *res, float *y, const int *win, cudaStream_t s);
 int tc_conv_row_pitch(void *h);
 void tc_conv_set_prof(void *h, long long *p);
 const char *tc_conv_variant(void *h);
@@ -20,7 +20,7 @@ int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, 
 int tc_matmul_native_a(void *h);
 void tc_matmul_destroy(void *h);
 int tc_matmul_pack_b(void *h, const float *b, cudaStream_t s);
-int tc_matmul_run(void *h, const float *a_t, const float *bias, float *cmat, cudaStream_t s);
+int tc_matmul_run(void *h, const float *a_t, const float *bias, const float *res, float *cmat, cudaStream_t s);
 
 // -------------------------------------------------------------------------------------------------------------
 // CUDA-core kernels (exact fp32 products, sequential accumulation in the reference's loop order cc,tt,rr,ss)
@@ -32,7 +32,8 @@ struct SimtConv {
 };
 
 __global__ void __launch_bounds__(256) k_conv_simt(const float *__restrict__ x, const float *__restrict__ w,
-                                                   const float *__restrict__ bias, float *__restrict__ y, SimtConv c) {
+                                                   const float *__restrict__ bias, const float *__restrict__ res,
+                                                   float *__restrict__ y, SimtConv c) {
     const int cpg = c.C / c.groups, fpg = c.F / c.groups;
     const long long total = (long long)c.N * c.F * c.OD * c.ohn * c.own;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -68,13 +69,17 @@ __global__ void __launch_bounds__(256) k_conv_simt(const float *__restrict__ x, 
             }
         if (c.has_bias)
             acc += __ldg(bias + ff);
-        y[ww + (long long)c.OW * (hh + (long long)c.OH * (zz + (long long)c.OD * (ff + (long long)c.F * nn)))] = apply_act(acc, c.act);
+        const long long yo = ww + (long long)c.OW * (hh + (long long)c.OH * (zz + (long long)c.OD * (ff + (long long)c.F * nn)));
+        if (res)
+            acc += __ldg(res + yo);
+        y[yo] = apply_act(acc, c.act);
     }
 }
 
 __global__ void __launch_bounds__(256) k_matmul_simt(const float *__restrict__ a, const float *__restrict__ b,
-                                                     const float *__restrict__ bias, float *__restrict__ c, int bs, int m,
-                                                     int n, int k, int transA, int transB, int act) {
+                                                     const float *__restrict__ bias, const float *__restrict__ res,
+                                                     float *__restrict__ c, int bs, int m, int n, int k, int transA, int transB,
+                                                     int act) {
     const long long total = (long long)bs * m * n;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int nn = (int)(i % n);
@@ -88,6 +93,8 @@ __global__ void __launch_bounds__(256) k_matmul_simt(const float *__restrict__ a
         }
         if (bias)
             acc += __ldg(bias + nn);
+        if (res)
+            acc += __ldg(res + i);
         c[i] = apply_act(acc, act);
     }
 }
@@ -98,8 +105,9 @@ __global__ void __launch_bounds__(256) k_matmul_simt(const float *__restrict__ a
 //   B as [n][k]: a warp owns 4 columns, lanes split K (coalesced rows of B), lanes are added up by shuffles.
 constexpr int kGemvRows = 8, kGemvWarps = 16;
 __global__ void __launch_bounds__(kGemvWarps * 32) k_gemv_small_m(const float *__restrict__ a, const float *__restrict__ b,
-                                                                 const float *__restrict__ bias, float *__restrict__ c, int m,
-                                                                 int n, int k, int transA, int transB, int act) {
+                                                                 const float *__restrict__ bias, const float *__restrict__ res,
+                                                                 float *__restrict__ c, int m, int n, int k, int transA, int transB,
+                                                                 int act) {
     __shared__ float red[kGemvWarps][kGemvRows][33];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, bb = blockIdx.y;
     const float *ab = a + (long long)bb * m * k, *bm = b + (long long)bb * k * n;
@@ -135,7 +143,10 @@ __global__ void __launch_bounds__(kGemvWarps * 32) k_gemv_small_m(const float *_
                 v += red[w][warp][lane];
             if (bias)
                 v += __ldg(bias + col);
-            c[((long long)bb * m + warp) * n + col] = apply_act(v, act);
+            const long long co = ((long long)bb * m + warp) * n + col;
+            if (res)
+                v += __ldg(res + co);
+            c[co] = apply_act(v, act);
         }
     } else {
         for (int col = blockIdx.x * 32 + warp; col < min(n, (int)blockIdx.x * 32 + 32); col += kGemvWarps) {
@@ -163,7 +174,10 @@ __global__ void __launch_bounds__(kGemvWarps * 32) k_gemv_small_m(const float *_
                 if (lane == 0 && r < m) {
                     if (bias)
                         v += __ldg(bias + col);
-                    c[((long long)bb * m + r) * n + col] = apply_act(v, act);
+                    const long long co = ((long long)bb * m + r) * n + col;
+                    if (res)
+                        v += __ldg(res + co);
+                    c[co] = apply_act(v, act);
                 }
             }
         }
@@ -316,7 +330,7 @@ int conv_set_weights(petb200_plan *plan, const float *w, cudaStream_t s) {
     return PETB200_OK;
 }
 
-int conv_run(petb200_plan *plan, const float *x, const float *bias, float *y, const int *win, cudaStream_t s) {
+int conv_run(petb200_plan *plan, const float *x, const float *bias, float *y, const int *win, cudaStream_t s, const float *res) {
     auto *pl = dynamic_cast<ConvPlan *>(plan);
     if (!pl)
         return PETB200_ERR_INVALID;
@@ -336,7 +350,7 @@ int conv_run(petb200_plan *plan, const float *x, const float *bias, float *y, co
                 return rc;
             xin = (const float *)pl->xpad.p;
         }
-        return tc_conv_run(pl->tc, xin, bias, y, win, s);
+        return tc_conv_run(pl->tc, xin, bias, res, y, win, s);
     }
     if (!pl->w_simt)
         return fail(ctx, PETB200_ERR_INVALID, "conv run before set_weights");
@@ -347,7 +361,7 @@ int conv_run(petb200_plan *plan, const float *x, const float *bias, float *y, co
         c.oh0 = win[0], c.ohn = win[1], c.ow0 = win[2], c.own = win[3];
     }
     long long total = (long long)c.N * c.F * c.OD * c.ohn * c.own;
-    k_conv_simt<<<grid_for(ctx, total, 256), 256, 0, s>>>(x, pl->w_simt, bias, y, c);
+    k_conv_simt<<<grid_for(ctx, total, 256), 256, 0, s>>>(x, pl->w_simt, bias, res, y, c);
     return launched(ctx, "k_conv_simt");
 }
 
@@ -447,7 +461,7 @@ int make_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int
     return PETB200_OK;
 }
 
-int matmul_run(petb200_plan *plan, const float *a, const float *b, const float *bias, float *c, cudaStream_t s) {
+int matmul_run(petb200_plan *plan, const float *a, const float *b, const float *bias, float *c, cudaStream_t s, const float *res) {
     auto *pl = dynamic_cast<MatmulPlan *>(plan);
     if (!pl)
         return PETB200_ERR_INVALID;
@@ -481,15 +495,15 @@ int matmul_run(petb200_plan *plan, const float *a, const float *b, const float *
                 return rc;
             at = (const float *)pl->at.p;
         }
-        return tc_matmul_run(pl->tc, at, pl->has_bias ? bias : nullptr, c, s);
+        return tc_matmul_run(pl->tc, at, pl->has_bias ? bias : nullptr, res, c, s);
     }
     if (pl->gemv) {
         k_gemv_small_m<<<dim3((unsigned)((pl->n + 31) / 32), (unsigned)pl->bs), kGemvWarps * 32, 0, s>>>(
-            a, b, pl->has_bias ? bias : nullptr, c, pl->m, pl->n, pl->k, pl->transA, pl->transB, pl->act);
+            a, b, pl->has_bias ? bias : nullptr, res, c, pl->m, pl->n, pl->k, pl->transA, pl->transB, pl->act);
         return launched(ctx, "k_gemv_small_m");
     }
     long long total = (long long)pl->bs * pl->m * pl->n;
-    k_matmul_simt<<<grid_for(ctx, total, 256), 256, 0, s>>>(a, b, pl->has_bias ? bias : nullptr, c, pl->bs, pl->m, pl->n, pl->k,
+    k_matmul_simt<<<grid_for(ctx, total, 256), 256, 0, s>>>(a, b, pl->has_bias ? bias : nullptr, res, c, pl->bs, pl->m, pl->n, pl->k,
                                                             pl->transA, pl->transB, pl->act);
     return launched(ctx, "k_matmul_simt");
 }

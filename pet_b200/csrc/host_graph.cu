@@ -64,6 +64,7 @@ struct Step {
     OpType type;
     int launches = 1;
     bool weight_only = false;  // consumes only weights: hoisted out of the replayed sequence
+    int residual = -1;         // conv/matmul: tensor added in the epilogue (a folded residual Add), or -1
 };
 
 // PerfEngine's memo tables (ref: include/perf_engine.h:15-21): argument tuple -> milliseconds.
@@ -153,16 +154,16 @@ int petb200_graph::run_step(Step &s, cudaStream_t st) {
     Operator &op = ops[s.ops.front()];
     switch (s.type) {
     case Conv:
-        return pass(petb200_conv2d_run(s.plan, dev_of(this, op.inputs[0]), dev_of(this, op.bias), dev_of(this, ops[s.ops.back()].outputs[0]), st));
     case Conv3d:
-        return pass(petb200_conv3d_run(s.plan, dev_of(this, op.inputs[0]), dev_of(this, op.bias), dev_of(this, ops[s.ops.back()].outputs[0]), st));
+        return pass(petb200_conv_run_residual(s.plan, dev_of(this, op.inputs[0]), dev_of(this, op.bias), dev_of(this, s.residual),
+                                              dev_of(this, ops[s.ops.back()].outputs[0]), st));
     case Correction:
         return pass(petb200_conv2d_correct(s.plan, dev_of(this, op.inputs[0]), dev_of(this, op.bias), dev_of(this, op.outputs[0]),
                                            op.win[0], op.win[1], op.win[2], op.win[3], st));
     case Matmul: {
         const bool wb = tensors[op.inputs[1]].weight;
-        return pass(petb200_matmul_run(s.plan, dev_of(this, op.inputs[0]), wb ? nullptr : dev_of(this, op.inputs[1]), dev_of(this, op.bias),
-                                       dev_of(this, ops[s.ops.back()].outputs[0]), st));
+        return pass(petb200_matmul_run_residual(s.plan, dev_of(this, op.inputs[0]), wb ? nullptr : dev_of(this, op.inputs[1]),
+                                                dev_of(this, op.bias), dev_of(this, s.residual), dev_of(this, ops[s.ops.back()].outputs[0]), st));
     }
     case Transpose:
     case Pad:
@@ -301,6 +302,7 @@ int petb200_graph::compile(int flags) {
     auto sole_consumer = [&](int t) -> int { return (tensors[t].inputOf.size() == 1 && !is_output(t)) ? tensors[t].inputOf[0] : -1; };
 
     // ---- build steps with fusion ----
+    std::vector<char> emitted(n, 0); // operators already covered by a step
     for (int id : order) {
         Operator &op = ops[id];
         if (op.fused_away)
@@ -323,6 +325,22 @@ int petb200_graph::compile(int flags) {
                     act = ops[c].act;
                     ops[c].fused_away = true;
                     s.ops.push_back(c);
+                } else if (c >= 0 && ops[c].type == Add && ops[c].inputs.size() == 2 && !ops[c].fused_away) {
+                    // ... or a residual Add (and the activation after it), when the other summand already exists at
+                    // this point of the order: y = act(conv + bias + residual), the Add's own arithmetic in its own order
+                    const int other = ops[c].inputs[0] == op.outputs[0] ? ops[c].inputs[1] : ops[c].inputs[0];
+                    const int prod = tensors[other].outputOf;
+                    if (other != op.outputs[0] && tensors[other].dims == tensors[op.outputs[0]].dims && (prod < 0 || emitted[prod])) {
+                        s.residual = other;
+                        ops[c].fused_away = true;
+                        s.ops.push_back(c);
+                        const int c2 = sole_consumer(ops[c].outputs[0]);
+                        if (c2 >= 0 && ops[c2].type == Activation) {
+                            act = ops[c2].act;
+                            ops[c2].fused_away = true;
+                            s.ops.push_back(c2);
+                        }
+                    }
                 }
             }
             const Dim &x = tensors[op.inputs[0]].dims, &w = tensors[op.inputs[1]].dims;
@@ -441,6 +459,8 @@ int petb200_graph::compile(int flags) {
         if (rc)
             return pass(rc);
         s.kernel = s.plan ? petb200_plan_kernel(s.plan) : (s.launches ? "eltwise" : "alias");
+        for (int o : s.ops)
+            emitted[o] = 1;
         steps.push_back(s);
     }
     // ---- storage: one buffer per non-aliased tensor (kept across recompiles) ----

@@ -58,12 +58,14 @@ struct IgemmParams {
                             // dense and unpadded, fetched as a 2-D box [flat_rows][flat_w] of the contiguous run; padding
                             // becomes a per-pixel mask over the filter taps (<= 32 taps)
     int flat_w, flat_rows;
+    int cstride;            // BC % 32 == 0: floats between consecutive channels of the raw tile (else 0: use the table)
     int T3[3], dil[3];      // filter extents and dilations (flat only: for the tap mask)
     int xD, xH, xW;         // input extents (flat only)
     long long ys_n, ys_f, ys_p;
     int act, has_bias;
     const int *koff;
     const float *bias;
+    const float *res; // optional residual, laid out like y: y = act(sum + bias + res)
     float *y;
     int *status;
     long long *prof; // optional per-CTA counters (kProfSlots per CTA), for tuning only
@@ -71,7 +73,7 @@ struct IgemmParams {
 };
 
 struct SmemLayout {
-    uint32_t a_off, b_off, raw_off, koff_off, bar_off, total;
+    uint32_t a_off, b_off, raw_off, koff_off, split_off, bar_off, total;
 };
 __host__ __device__ inline SmemLayout smem_layout(const IgemmParams &P, bool a_tmem) {
     SmemLayout L;
@@ -84,6 +86,10 @@ __host__ __device__ inline SmemLayout smem_layout(const IgemmParams &P, bool a_t
     o += (uint32_t)P.NR * (uint32_t)P.raw_bytes;
     L.koff_off = o;
     o += (uint32_t)P.spc * kStageK * 4;
+    // split-K: landing area for the cluster's partial sums of this CTA's columns, [rank][BN/ksplit][128] floats.  Its
+    // own region: peers push into it while this CTA may still be in its main loop.
+    L.split_off = (o + 127) & ~127u;
+    o = L.split_off + (P.ksplit > 1 ? 512u * (uint32_t)P.BN + 1024u : 0u); // + each tile row's offset in y (-1: none)
     L.bar_off = (o + 15) & ~15u;
     L.total = L.bar_off + 320;
     return L;
@@ -117,8 +123,9 @@ template <int ACT> __device__ __forceinline__ float act_fn(float v) {
 // the common no-activation case carries none of the transcendental code.
 template <int ACT, int PASSES>
 __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile0, int Fg, bool valid, const float *bias,
-                                               float *yp, long long ys_f, bool vec_ok, int dbg, float *stage, int nvalid_warp, float *ybase_warp,
-                                               int col0, int col1, float *split_row /*split-K: this row of the staged tile*/) {
+                                               const float *rp /*residual at this pixel, or null*/, float *yp, long long ys_f, bool vec_ok, int dbg, float *stage, int nvalid_warp, float *ybase_warp,
+                                               int col0, int col1, uint32_t split_addr /*split-K: shared address of [this rank][0][this pixel]*/,
+                                               int split_shift /*log2(columns per CTA)*/) {
     uint32_t r[32], nx[32], sm[32];
     if (col0 >= col1)
         return;
@@ -135,10 +142,14 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile
             if (PASSES == 3)
                 ptx::tmem_ld_32x32(tacc + 128u + (uint32_t)(cc + 32), sm);
         }
-        if (split_row != nullptr) { // partial sums stay on chip: [column][pixel], consecutive lanes = consecutive words
+        if (split_addr != 0u) {
+            // Split-K: column c of the tile is summed by CTA c / cols of the cluster.  Push this CTA's partial sum into
+            // that CTA's shared memory, slot [this rank][c % cols][pixel] (consecutive lanes = consecutive words).
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-                split_row[(cc + j) * kTileM] = __uint_as_float(r[j]);
+            for (int j = 0; j < 32; ++j) {
+                const int col = cc + j, owner = col >> split_shift, lc = col & ((1 << split_shift) - 1);
+                ptx::st_dsmem_f32(ptx::map_to_cta(split_addr + (uint32_t)(lc * kTileM) * 4u, (uint32_t)owner), __uint_as_float(r[j]));
+            }
             continue;
         }
         if ((dbg & 1) || (stage == nullptr && !valid))
@@ -149,6 +160,8 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile
             float v = __uint_as_float(r[j]);
             if (bias != nullptr && f0 + j < Fg)
                 v += __ldg(bias + f0 + j);
+            if (rp != nullptr && f0 + j < Fg) // only reached by valid rows (no staging with a residual)
+                v += __ldg(rp + (long long)(f0 + j) * ys_f);
             r[j] = __float_as_uint(act_fn<ACT>(v));
         }
         if (stage != nullptr) {
@@ -191,25 +204,42 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile
     }
 }
 
-// One K stage of one tile row: fetch the 32 operands (gathered through the offset table, or straight from the
-// swizzled row in K-major mode) and split them into the TF32 hi/lo parts (or round them, for a single pass).
-// FLAT: the table entries carry the filter tap in bits 24..30 and `tmask` tells which taps fall inside the input for
-// this pixel (the raw tile has no padding of its own).
-template <bool A_KMAJOR, bool FLAT, int PASSES>
+// One K stage of one tile row: fetch the 32 operands and split them into the TF32 hi/lo parts (or round them, for a
+// single pass).  Where the operands come from:
+//   kGatherTable   im2col through the offset table of the stage (entry < 0: no such element);
+//   kGatherFlat    the same for unpadded whole-plane raw tiles: entries carry the filter tap in bits 24..30 and `tmask`
+//                  tells which taps fall inside the input for this pixel;
+//   kGatherStride  chunks of a multiple of 32 channels: a stage is 32 consecutive channels of ONE tap, so the operands
+//                  sit `cstride` floats apart from the stage's first table entry - no table reads, no per-element tests;
+//   kGatherKMajor  matmul with row-major A: row p of the 128B-swizzled [128][32] tile.
+enum { kGatherTable = 0, kGatherFlat = 1, kGatherStride = 2, kGatherKMajor = 3 };
+template <int MODE, int PASSES>
 __device__ __forceinline__ void gather_split(const int4 *ko, const float *raw, const uint8_t *krow, int p, uint32_t tmask,
-                                             uint32_t (&hi)[32], uint32_t (&lo)[32]) {
+                                             int cstride, bool flat, const float *zero_word, uint32_t (&hi)[32],
+                                             uint32_t (&lo)[32]) {
+    const float *q = raw;
+    if (MODE == kGatherStride) {
+        const int o0 = ko[0].x;
+        q = raw + (flat ? (o0 & 0xffffff) : o0);
+        if (flat && !((tmask >> (o0 >> 24)) & 1u)) // this tap is outside the input for this pixel: read zeros
+            q = zero_word, cstride = 0;
+    }
 #pragma unroll
     for (int c4 = 0; c4 < 8; ++c4) {
         float v[4];
-        if (A_KMAJOR) { // row p of the swizzled [128][32] tile: 16-byte chunk c4 sits at c4 ^ (p & 7)
+        if (MODE == kGatherKMajor) { // 16-byte chunk c4 of row p sits at c4 ^ (p & 7)
             const float4 t4 = *reinterpret_cast<const float4 *>(krow + ((c4 ^ (p & 7)) << 4));
             v[0] = t4.x, v[1] = t4.y, v[2] = t4.z, v[3] = t4.w;
+        } else if (MODE == kGatherStride) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                v[i] = q[(4 * c4 + i) * cstride];
         } else {
             const int4 o4 = ko[c4];
             const int o[4] = {o4.x, o4.y, o4.z, o4.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                if (FLAT)
+                if (MODE == kGatherFlat)
                     v[i] = (o[i] >= 0 && ((tmask >> (o[i] >> 24)) & 1u)) ? raw[o[i] & 0xffffff] : 0.f;
                 else
                     v[i] = o[i] >= 0 ? raw[o[i]] : 0.f;
@@ -227,25 +257,32 @@ __device__ __forceinline__ void gather_split(const int4 *ko, const float *raw, c
     }
 }
 
-// Split-K reduction inside a thread-block cluster.  The ksplit CTAs of one output tile form a cluster; each has staged
-// its 128 x BN partial tile in its own shared memory as [column][pixel].  CTA `rank` owns BN/ksplit columns: a thread adds
-// the ksplit copies of an element in rank order (so the sum does not depend on timing), reading the peers' copies
-// through distributed shared memory, and stores act(sum + bias).
+// Split-K reduction inside a thread-block cluster.  The ksplit CTAs of one output tile form a cluster; CTA `rank` owns
+// BN/ksplit columns of the tile, and every CTA has pushed its partial sums of those columns into this CTA's shared memory
+// as [source rank][column][pixel].  A thread adds the ksplit copies of an element in rank order (the sum does not depend
+// on timing) and stores act(sum + bias).
 template <int ACT>
-__device__ __forceinline__ void cluster_reduce_store(uint32_t stage_addr, int ksplit, int rank, int BN, int et /*0..255*/,
-                                                     int f_tile0, int Fg, const float *bias, float *yp /*this pixel, filter 0*/,
+__device__ __forceinline__ void cluster_reduce_store(const float *stage, int ksplit, int rank, int BN, int et /*0..255*/,
+                                                     int f_tile0, int Fg, const float *bias, const float *rp, float *yp /*this pixel, filter 0*/,
                                                      long long ys_f) {
     const int cols = BN / ksplit, px = et & (kTileM - 1);
+#pragma unroll 2
     for (int cl = et >> 7; cl < cols; cl += 2) {
-        const int col = rank * cols + cl, f = f_tile0 + col;
+        const int f = f_tile0 + rank * cols + cl;
         if (f >= Fg)
             break;
-        const uint32_t a = stage_addr + (uint32_t)(col * kTileM + px) * 4u;
-        float acc = 0.f;
-        for (int r = 0; r < ksplit; ++r)
-            acc += ptx::ld_dsmem_f32(ptx::map_to_cta(a, (uint32_t)r));
+        float v[8]; // all copies fetched before the first add
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            v[r] = r < ksplit ? stage[(r * cols + cl) * kTileM + px] : 0.f;
+        float acc = v[0];
+#pragma unroll
+        for (int r = 1; r < 8; ++r)
+            acc += v[r];
         if (bias != nullptr)
             acc += __ldg(bias + f);
+        if (rp != nullptr)
+            acc += __ldg(rp + (long long)f * ys_f);
         yp[(long long)f * ys_f] = act_fn<ACT>(acc);
     }
 }
@@ -262,6 +299,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     uint8_t *sB = smem + L.b_off;
     uint8_t *sRaw = smem + L.raw_off;
     int *sKoff = reinterpret_cast<int *>(smem + L.koff_off);
+    float *sSplit = reinterpret_cast<float *>(smem + L.split_off);
+    long long *sYoff = reinterpret_cast<long long *>(smem + L.split_off + 512u * (uint32_t)P.BN); // split-K only
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L.bar_off);
     // barrier slots
     uint64_t *raw_full = bars, *raw_empty = bars + kMaxNR;
@@ -270,6 +309,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     uint64_t *acc_full = a_empty + 4;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(acc_full + 2);
+    float *zero_word = reinterpret_cast<float *>(acc_full + 3); // holds 0.0f: what a masked-off filter tap reads
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     long long *prof_cta = nullptr; // wall-clock marks of this CTA (entry, prologue done, epilogue done, exit), tuning only
@@ -300,6 +340,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         }
         ptx::mbar_init(acc_full, 1);
         *abort_flag = 0;
+        *zero_word = 0.f;
         ptx::fence_mbar_init();
         ptx::prefetch_tmap(&tmap_x);
         ptx::prefetch_tmap(&tmap_bhi);
@@ -554,8 +595,19 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             }
             __syncwarp();
             accumulate = 1u;
-            prev_sa = sa;
-            prev_sb = sb;
+            if (ready_next) {
+                // MMA-bound: the release of this stage rides behind the next stage's first MMA (nothing to wait for)
+                prev_sa = sa;
+                prev_sb = sb;
+            } else {
+                // transform-bound: the next stage is not there yet, and its producers may be waiting for this slot
+                if (ptx::elect_one()) {
+                    ptx::mma_commit(a_empty + sa);
+                    ptx::mma_commit(b_empty + sb);
+                }
+                __syncwarp();
+                prev_sa = -1;
+            }
             sa = nsa;
             sb = nsb;
             pa = npa;
@@ -587,6 +639,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         int base_p;
         long long y_off;
         pixel_geom(p, valid, base_p, y_off);
+        if (P.ksplit > 1 && tset == 0)
+            sYoff[p] = valid ? y_off : -1; // read by the split-K reduction, after the cluster barrier
         uint32_t tmask = 0;
         if (!A_KMAJOR && P.flat && valid) { // which filter taps of this pixel lie inside the (unpadded) input
             int ul = 0, q = q0 + p;
@@ -606,22 +660,21 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                     }
         }
         bool alive = true;
-        long long t_we = 0, t_wr = 0;
+        long long t_we = 0, t_wr = 0, t_g = 0, t_st = 0;
         const long long t_begin = P.prof ? clock64() : 0;
         int rb = 0;
         uint32_t prw = 0;
-        for (int ch = 0; ch < c1 - c0 && alive; ++ch) {
+        // This set owns every second K stage (tset, tset + 2, ...): `st` is the next one's index inside the current chunk,
+        // `sa`/`pa` its slot of the A ring and the parity to wait for (first pass over the ring: every slot is free).
+        int st = tset, sa = tset;
+        uint32_t pa = 1;
+        for (int ch = 0; ch < c1 - c0 && alive; ++ch, st -= P.spc) {
             const long long cr0 = P.prof ? clock64() : 0;
-            alive = ptx::mbar_wait(raw_full + rb, prw, abort_flag);
+            alive = ptx::mbar_wait(raw_full + rb, prw, abort_flag); // also by a set without a stage in this chunk
             if (P.prof)
                 t_wr += clock64() - cr0;
             const float *raw = reinterpret_cast<const float *>(sRaw + (size_t)rb * P.raw_bytes) + base_p;
-            for (int st = 0; st < P.spc && alive; ++st) {
-                const int ks = ch * P.spc + st;
-                if ((ks & 1) != tset)
-                    continue; // the other set's stage
-                const int sa = ks % P.NA;
-                const uint32_t pa = (uint32_t)(((ks / P.NA) & 1) ^ 1); // first pass over the ring: every slot is free
+            for (; st < P.spc && alive; st += 2) {
                 const long long ce0 = P.prof ? clock64() : 0;
                 alive = ptx::mbar_wait(a_empty + sa, pa, abort_flag);
                 if (P.prof)
@@ -633,16 +686,26 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                     ptx::tc_fence_after();
                     uint32_t hi[32], lo[32];
                     const uint8_t *krow = sRaw + (size_t)rb * P.raw_bytes + (size_t)p * 128;
-                    if (!A_KMAJOR && P.flat)
-                        gather_split<false, true, PASSES>(ko, raw, krow, p, tmask, hi, lo);
+                    const long long cg0 = P.prof ? clock64() : 0;
+                    if (A_KMAJOR)
+                        gather_split<kGatherKMajor, PASSES>(ko, raw, krow, p, tmask, 0, false, zero_word, hi, lo);
+                    else if (P.cstride)
+                        gather_split<kGatherStride, PASSES>(ko, raw, krow, p, tmask, P.cstride, P.flat != 0, zero_word, hi, lo);
+                    else if (P.flat)
+                        gather_split<kGatherFlat, PASSES>(ko, raw, krow, p, tmask, 0, true, zero_word, hi, lo);
                     else
-                        gather_split<A_KMAJOR, false, PASSES>(ko, raw, krow, p, tmask, hi, lo);
+                        gather_split<kGatherTable, PASSES>(ko, raw, krow, p, tmask, 0, false, zero_word, hi, lo);
                     const uint32_t t = tmem_base + ((uint32_t)(quarter * 32) << 16) + 256u + (uint32_t)sa * 64u;
                     ptx::tmem_st_32x32(t, hi);
+                    const long long cg1 = P.prof ? clock64() : 0;
                     if (PASSES == 3)
                         ptx::tmem_st_32x32(t + 32u, lo);
                     ptx::tmem_st_wait();
                     ptx::tc_fence_before();
+                    if (P.prof) {
+                        t_g += cg1 - cg0;
+                        t_st += clock64() - cg1;
+                    }
                 } else {
                     uint8_t *rowh = sA + (size_t)sa * 2 * kAHalfBytes + (size_t)p * 128;
                     uint8_t *rowl = rowh + kAHalfBytes;
@@ -669,6 +732,11 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 __syncwarp();
                 if (lane == 0)
                     ptx::mbar_arrive(a_full + sa);
+                sa += 2;
+                if (sa >= P.NA) {
+                    sa -= P.NA;
+                    pa ^= 1u;
+                }
             }
             __syncwarp();
             if (lane == 0 && alive)
@@ -691,8 +759,11 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             const long long f_glob0 = P.z_is_batch ? 0 : (long long)zb * P.Fg;
             float *yp = P.y + y_off + f_glob0 * P.ys_f;
             const float *bp = (P.has_bias && P.ksplit == 1) ? P.bias + f_glob0 : nullptr;
-            // split-K: the partial tile is staged in the (now idle) B ring for the cluster reduction after the role branches
-            float *split_row = P.ksplit > 1 ? reinterpret_cast<float *>(sB) + p : nullptr;
+            const float *rp = (P.res != nullptr && P.ksplit == 1) ? P.res + y_off + f_glob0 * P.ys_f : nullptr;
+            // split-K: partial sums go to the landing areas of the cluster's CTAs, summed after the role branches
+            const int split_cols = P.BN / P.ksplit, split_shift = 31 - __clz(split_cols);
+            const uint32_t split_addr =
+                P.ksplit > 1 ? ptx::smem_u32(sSplit) + (uint32_t)(((int)ptx::cluster_ctarank() * split_cols) * kTileM + p) * 4u : 0u;
             const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16);
             // staged 16-byte stores need: pixel-contiguous NCHW output, full-width rows (no column window), one plane per
             // tile, 16-byte aligned runs
@@ -703,20 +774,20 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             float *ybase_warp = yp - y_off + y_off0;
             if (P.ys_p == 1 && P.ipt == 1 && P.own == P.OW && P.ow0 == 0 && (plane_elems & 3) == 0 && (P.ys_n & 3) == 0 &&
                 ((P.OH * P.OW) & 3) == 0 && (!P.wide || (P.OW & 3) == 0) &&
-                (P.ys_f & 3) == 0 && ((P.oh0 * P.OW) & 3) == 0 && P.ksplit == 1 &&
+                (P.ys_f & 3) == 0 && ((P.oh0 * P.OW) & 3) == 0 && P.ksplit == 1 && P.res == nullptr &&
                 (reinterpret_cast<uintptr_t>(P.y) & 15) == 0) {
                 nvalid_warp = __popc(__ballot_sync(0xffffffffu, valid));
                 if (nvalid_warp > 0)
                     stage = reinterpret_cast<float *>(sB) + (warp - 3) * 1024; // B stages are idle once the accumulator is complete
-                if ((uint32_t)(warp - 3 + 1) * 4096u > (uint32_t)P.NB * (PASSES == 3 ? 2u : 1u) * b_half || !(P.dbg & 2))
+                if ((uint32_t)(warp - 3 + 1) * 4096u > (uint32_t)P.NB * (PASSES == 3 ? 2u : 1u) * b_half)
                     stage = nullptr; // not enough idle shared memory for this warp's block
             }
             // the two sets split the tile's columns (whole 32-column blocks)
             const int nblk = P.BN / 32, half_blk = (nblk + 1) / 2;
             const int col0 = tset == 0 ? 0 : half_blk * 32, col1 = tset == 0 ? half_blk * 32 : P.BN;
 #define PETB200_EPI(ACT_)                                                                                              \
-    epilogue_store<ACT_, PASSES>(tacc, P.BN, f_tile0, P.Fg, valid, bp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, \
-                                 ybase_warp, col0, col1, split_row)
+    epilogue_store<ACT_, PASSES>(tacc, P.BN, f_tile0, P.Fg, valid, bp, rp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, \
+                                 ybase_warp, col0, col1, split_addr, split_shift)
             switch (P.ksplit > 1 ? PETB200_ACT_NONE : P.act) {
             case PETB200_ACT_RELU: PETB200_EPI(PETB200_ACT_RELU); break;
             case PETB200_ACT_SIGMOID: PETB200_EPI(PETB200_ACT_SIGMOID); break;
@@ -734,26 +805,27 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             pr[6] = clock64() - t_epi0;
             pr[7] = t_epi0 - t_begin;
             pr[10] = (long long)ptx::globaltimer_ns();
+            pr[12] = t_g;
+            pr[13] = t_st;
         }
     }
 
     // ---------------- split-K: reduction across the cluster ----------------
-    // Every thread of every CTA of the cluster reaches both barriers (all waits above are bounded).
+    // Every thread of every CTA of the cluster reaches the barrier (all waits above are bounded).
     if (P.ksplit > 1) {
-        ptx::cluster_sync_all(); // all partial tiles are staged
+        ptx::cluster_sync_all(); // every CTA's pushes have landed; nothing touches a peer's memory after this
+        if (prof_cta)
+            prof_cta[14] = (long long)ptx::globaltimer_ns();
         if (warp >= 3) {
             const int et = threadIdx.x - 96;
-            bool valid;
-            int base_p;
-            long long y_off;
-            pixel_geom(et & (kTileM - 1), valid, base_p, y_off);
-            if (valid && *abort_flag == 0) {
+            const long long y_off = sYoff[et & (kTileM - 1)];
+            if (y_off >= 0 && *abort_flag == 0) {
                 const long long f_glob0 = P.z_is_batch ? 0 : (long long)zb * P.Fg;
                 float *yp = P.y + y_off + f_glob0 * P.ys_f;
                 const float *bp = P.has_bias ? P.bias + f_glob0 : nullptr;
-                const uint32_t stage_addr = ptx::smem_u32(sB);
+                const float *rp = P.res != nullptr ? P.res + y_off + f_glob0 * P.ys_f : nullptr;
                 const int rank = (int)ptx::cluster_ctarank();
-#define PETB200_RED(ACT_) cluster_reduce_store<ACT_>(stage_addr, P.ksplit, rank, P.BN, et, ntile * P.BN, P.Fg, bp, yp, P.ys_f)
+#define PETB200_RED(ACT_) cluster_reduce_store<ACT_>(sSplit, P.ksplit, rank, P.BN, et, ntile * P.BN, P.Fg, bp, rp, yp, P.ys_f)
                 switch (P.act) {
                 case PETB200_ACT_RELU: PETB200_RED(PETB200_ACT_RELU); break;
                 case PETB200_ACT_SIGMOID: PETB200_RED(PETB200_ACT_SIGMOID); break;
@@ -764,7 +836,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
 #undef PETB200_RED
             }
         }
-        ptx::cluster_sync_all(); // peers have finished reading this CTA's tile
+        if (prof_cta)
+            prof_cta[15] = (long long)ptx::globaltimer_ns();
     }
 
     // ---------------- teardown ----------------
@@ -932,12 +1005,13 @@ struct TcCore {
         }
         return PETB200_OK;
     }
-    int launch(const float *x, const float *bias, float *y, cudaStream_t s) {
+    int launch(const float *x, const float *bias, const float *res, float *y, cudaStream_t s) {
         int rc = encode_x(x);
         if (rc)
             return rc;
         IgemmParams p = P;
         p.bias = bias;
+        p.res = res;
         p.y = y;
         p.koff = (const int *)koff.p;
         p.status = ctx->d_status;
@@ -995,11 +1069,9 @@ static double est_cycles(int sm_count, long long base_ctas, int nchunks, int spc
     const long long waves = (base_ctas + slots - 1) / slots;
     return (double)waves * per_cta;
 }
-// Split K over 1, 2, 4 or 8 CTAs (a cluster): the split must divide the tile width, leave every CTA a chunk, and the
-// staged tile (512*BN bytes) must fit the B ring.
+// Split K over 1, 2, 4 or 8 CTAs (a cluster): the split must divide the tile width and leave every CTA a chunk.
 static int choose_ksplit(int sm_count, long long base_ctas, const IgemmParams &P, int passes, int want, double *cycles) {
-    const size_t ring = (size_t)P.NB * (passes == 3 ? 2 : 1) * P.BN * 128;
-    auto ok = [&](int ks) { return ks == 1 || (ks <= P.nchunks && P.BN % ks == 0 && (size_t)512 * P.BN <= ring); };
+    auto ok = [&](int ks) { return ks == 1 || (ks <= P.nchunks && P.BN % ks == 0); };
     int best = 1;
     double best_c = est_cycles(sm_count, base_ctas, P.nchunks, P.spc, P.BN, passes, 1);
     if (want > 0) {
@@ -1204,12 +1276,24 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     for (int bn = 128; bn >= 32; bn /= 2) {
         if (forced_bn ? bn != forced_bn : bn > bn_max)
             continue;
+        P.ksplit = 1;
         if (!fit(bn))
             continue;
         const long long base_ctas = (long long)mtiles * ((Fg + bn - 1) / bn) * gz;
         const int passes = core.single_pass ? 1 : 3;
         double cyc;
-        P.ksplit = choose_ksplit(ctx->sm_count, base_ctas, P, passes, want_ks, &cyc);
+        const int ks = choose_ksplit(ctx->sm_count, base_ctas, P, passes, want_ks, &cyc);
+        if (ks > 1) { // the landing area takes shared memory from the rings (or even from the chunk size): fit again
+            P.ksplit = ks;
+            if (!fit(bn))
+                continue;
+            if (P.nchunks < ks) {
+                P.ksplit = 1;
+                if (!fit(bn))
+                    continue;
+                cyc = est_cycles(ctx->sm_count, base_ctas, P.nchunks, P.spc, bn, passes, 1);
+            }
+        }
         if (!have || cyc < best_cycles * 0.97) { // prefer the wider tile unless the narrower one clearly wins
             have = true;
             best_cycles = cyc;
@@ -1219,6 +1303,7 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     if (!have)
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "raw activation tile does not fit shared memory");
     P = bestP;
+    P.cstride = (P.BC % kStageK == 0 && env_int("PETB200_TC_TABLE", 0) == 0) ? P.RD * P.RH * P.RW : 0;
     if (flat && (!core.a_tmem || (long long)P.RN * P.BC * P.RD * P.RH * P.RW >= (1 << 24)))
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "flat raw tiles need the TS kernel variant");
     const int BN = P.BN;
@@ -1355,12 +1440,12 @@ int tc_conv_set_weights(void *h, const float *w, cudaStream_t s) {
     return launched(c.ctx, "k_pack_conv_w");
 }
 
-int tc_conv_run(void *h, const float *x, const float *bias, float *y, const int *win, cudaStream_t s) {
+int tc_conv_run(void *h, const float *x, const float *bias, const float *res, float *y, const int *win, cudaStream_t s) {
     auto *t = (TcConv *)h;
     if (!t->full.weights_ready)
         return fail(t->full.ctx, PETB200_ERR_INVALID, "conv run before set_weights");
     if (!win)
-        return t->full.launch(x, bias, y, s);
+        return t->full.launch(x, bias, res, y, s);
     const ConvGeom &g = t->g;
     if (win[0] < 0 || win[1] <= 0 || win[0] + win[1] > g.OH || win[2] < 0 || win[3] <= 0 || win[2] + win[3] > g.OW)
         return fail(t->full.ctx, PETB200_ERR_INVALID, "correction window outside the output");
@@ -1386,7 +1471,7 @@ int tc_conv_run(void *h, const float *x, const float *bias, float *y, const int 
         wc->map_blo = t->full.map_blo;
         wc->weights_ready = true;
     }
-    return wc->launch(x, bias, y, s);
+    return wc->launch(x, bias, res, y, s);
 }
 
 void tc_conv_out_dims(void *h, int *d5) {
@@ -1413,18 +1498,6 @@ struct TcMatmul {
     bool native_a = false; // A is consumed row-major as passed (no re-layout)
 };
 
-// Shared tail of the row-major-A matmul configuration: split-K decision, grid.
-static int matmul_finish(petb200_ctx *ctx, TcCore &c, int bs, int m, int n, int mtiles) {
-    IgemmParams &P = c.P;
-    const int ntiles = (n + P.BN - 1) / P.BN;
-    const long long ctas = (long long)mtiles * ntiles * bs;
-    const int want = env_int("PETB200_TC_KSPLIT", 0);
-    P.ksplit = choose_ksplit(ctx->sm_count, ctas, P, c.single_pass ? 1 : 3, want, nullptr);
-    c.y_elems = (long long)bs * m * n;
-    c.grid = dim3((unsigned)mtiles, (unsigned)(ntiles * P.ksplit), (unsigned)bs);
-    return raise_smem_limit(ctx);
-}
-
 // Row-major A ([b][m][k], k % 4 == 0): the kernel's K-major mode, no re-layout of A.
 static int tc_configure_kmajor(petb200_ctx *ctx, TcCore &core, int bs, int m, int n, int k, int has_bias, int act) {
     IgemmParams &P = core.P;
@@ -1447,6 +1520,8 @@ static int tc_configure_kmajor(petb200_ctx *ctx, TcCore &core, int bs, int m, in
     P.NA = 4;
     const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 1024;
     P.NB = 2, P.NR = 2;
+    P.ksplit = choose_ksplit(ctx->sm_count, (long long)P.tpi * ((n + P.BN - 1) / P.BN) * bs, P, core.single_pass ? 1 : 3,
+                             env_int("PETB200_TC_KSPLIT", 0), nullptr); // before the rings: the split takes shared memory
     if (smem_layout(P, true).total > budget)
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "matmul tile does not fit shared memory");
     for (bool grew = true; grew;) { // deepen both rings alternately: every K stage needs one B tile and one raw tile
@@ -1473,7 +1548,9 @@ static int tc_configure_kmajor(petb200_ctx *ctx, TcCore &core, int bs, int m, in
     if (core.koff.alloc(koff.size() * 4) != cudaSuccess)
         return fail(ctx, PETB200_ERR_NOMEM, "koff allocation failed");
     PETB200_CUDA(ctx, cudaMemcpy(core.koff.p, koff.data(), koff.size() * 4, cudaMemcpyHostToDevice));
-    return matmul_finish(ctx, core, bs, m, n, P.tpi);
+    core.y_elems = (long long)bs * m * n;
+    core.grid = dim3((unsigned)P.tpi, (unsigned)(((n + P.BN - 1) / P.BN) * P.ksplit), (unsigned)bs);
+    return raise_smem_limit(ctx);
 }
 
 int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, int transB, int has_bias, int act, int passes,
@@ -1550,9 +1627,9 @@ int tc_matmul_pack_b(void *h, const float *b, cudaStream_t s) {
     c.weights_ready = true;
     return launched(c.ctx, "k_pack_mm_b");
 }
-int tc_matmul_run(void *h, const float *a_t, const float *bias, float *cmat, cudaStream_t s) {
+int tc_matmul_run(void *h, const float *a_t, const float *bias, const float *res, float *cmat, cudaStream_t s) {
     auto *t = (TcMatmul *)h;
-    return t->core.launch(a_t, bias, cmat, s);
+    return t->core.launch(a_t, bias, res, cmat, s);
 }
 
 } // namespace petb200

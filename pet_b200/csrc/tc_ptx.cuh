@@ -80,13 +80,11 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
 // Address of the same shared-memory location in the CTA with the given rank of this cluster.
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
     uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
     return r;
 }
-__device__ __forceinline__ float ld_dsmem_f32(uint32_t cluster_addr) {
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
-    return v;
+__device__ __forceinline__ void st_dsmem_f32(uint32_t cluster_addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
 }
 
 // ---- 4-byte asynchronous copies (for sources TMA cannot address) ---------------------------------------------------

@@ -40,9 +40,11 @@ SYMBOLS = {
     "petb200_conv3d_plan": (_i, [_vp, _ip, _i, C.POINTER(_vp)]),
     "petb200_conv3d_set_weights": (_i, [_vp, _vp, _vp]),
     "petb200_conv3d_run": (_i, [_vp, _vp, _vp, _vp, _vp]),
+    "petb200_conv_run_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "petb200_matmul_plan": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, C.POINTER(_vp)]),
     "petb200_matmul_set_weights": (_i, [_vp, _vp, _vp]),
     "petb200_matmul_run": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    "petb200_matmul_run_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "petb200_transpose_plan": (_i, [_vp, _i, _ip, _i, C.POINTER(TransposeDesc), C.POINTER(_vp)]),
     "petb200_pad_plan": (_i, [_vp, _i, _ip, _ip, _ip, C.POINTER(_vp)]),
     "petb200_slice_plan": (_i, [_vp, _i, _ip, _ip, _ip, C.POINTER(_vp)]),

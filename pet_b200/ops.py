@@ -100,11 +100,17 @@ class Context:
         plan._w = _f32(w)  # keep alive: the CUDA-core path reads the caller's tensor
         self.check(self.lib.petb200_conv2d_set_weights(plan.h, _ptr(plan._w), _stream()))
 
-    def conv2d_run(self, plan, x, bias=None, out=None):
+    def conv2d_run(self, plan, x, bias=None, out=None, residual=None):
+        """y = act(conv(x) + bias [+ residual]); residual (shaped like y) folds a following Add into the epilogue."""
         x = _f32(x)
         y = out if out is not None else torch.empty(plan.out_shape, device=x.device, dtype=torch.float32)
-        self.check(self.lib.petb200_conv2d_run(plan.h, _ptr(x), _ptr(_f32(bias) if bias is not None else None), _ptr(y),
-                                               _stream()))
+        b = _ptr(_f32(bias) if bias is not None else None)
+        if residual is not None:
+            if tuple(residual.shape) != tuple(plan.out_shape):
+                raise L.PetError(L.ERR_INVALID, "residual must have the shape of the output")
+            self.check(self.lib.petb200_conv_run_residual(plan.h, _ptr(x), b, _ptr(_f32(residual)), _ptr(y), _stream()))
+        else:
+            self.check(self.lib.petb200_conv2d_run(plan.h, _ptr(x), b, _ptr(y), _stream()))
         return y
 
     def conv2d_correct(self, plan, x, y, oh0, ohn, ow0=0, own=None, bias=None):
@@ -114,13 +120,13 @@ class Context:
                                                    _stream()))
         return y
 
-    def conv2d(self, x, w, ph, pw, sh=1, sw=1, dh=1, dw=1, bias=None, act="none", algo="auto"):
+    def conv2d(self, x, w, ph, pw, sh=1, sw=1, dh=1, dw=1, bias=None, act="none", algo="auto", residual=None):
         key = ("conv2d", tuple(x.shape), tuple(w.shape), ph, pw, sh, sw, dh, dw, bias is not None, act, algo)
         plan = self._plans.get(key)
         if plan is None:
             plan = self._plans[key] = self.conv2d_plan(x.shape, w.shape, ph, pw, sh, sw, dh, dw, bias is not None, act, algo)
         self.conv2d_set_weights(plan, w)
-        return self.conv2d_run(plan, x, bias)
+        return self.conv2d_run(plan, x, bias, residual=residual)
 
     def conv3d_plan(self, xshape, wshape, pad, stride=(1, 1, 1), dil=(1, 1, 1), bias=False, act="none", algo="auto"):
         n, c, d, h, w = xshape
@@ -136,7 +142,7 @@ class Context:
                        o(w, s, pad[2], stride[2], dil[2]))
         return p
 
-    def conv3d(self, x, w, pad, stride=(1, 1, 1), dil=(1, 1, 1), bias=None, act="none", algo="auto"):
+    def conv3d(self, x, w, pad, stride=(1, 1, 1), dil=(1, 1, 1), bias=None, act="none", algo="auto", residual=None):
         key = ("conv3d", tuple(x.shape), tuple(w.shape), tuple(pad), tuple(stride), tuple(dil), bias is not None, act, algo)
         plan = self._plans.get(key)
         if plan is None:
@@ -144,7 +150,10 @@ class Context:
         plan._w = _f32(w)
         self.check(self.lib.petb200_conv3d_set_weights(plan.h, _ptr(plan._w), _stream()))
         y = torch.empty(plan.out_shape, device=x.device, dtype=torch.float32)
-        self.check(self.lib.petb200_conv3d_run(plan.h, _ptr(_f32(x)), _ptr(bias), _ptr(y), _stream()))
+        if residual is not None:
+            self.check(self.lib.petb200_conv_run_residual(plan.h, _ptr(_f32(x)), _ptr(bias), _ptr(_f32(residual)), _ptr(y), _stream()))
+        else:
+            self.check(self.lib.petb200_conv3d_run(plan.h, _ptr(_f32(x)), _ptr(bias), _ptr(y), _stream()))
         return y
 
     # ---- matmul --------------------------------------------------------------------------------------------
@@ -163,17 +172,23 @@ class Context:
         p.out_shape = (b, m, n)
         return p
 
-    def matmul_run(self, plan, a, b, bias=None, out=None):
+    def matmul_run(self, plan, a, b, bias=None, out=None, residual=None):
         c = out if out is not None else torch.empty(plan.out_shape, device=a.device, dtype=torch.float32)
-        self.check(self.lib.petb200_matmul_run(plan.h, _ptr(_f32(a)), _ptr(_f32(b)), _ptr(bias), _ptr(c), _stream()))
+        if residual is not None:
+            if tuple(residual.shape) != tuple(plan.out_shape):
+                raise L.PetError(L.ERR_INVALID, "residual must have the shape of the output")
+            self.check(self.lib.petb200_matmul_run_residual(plan.h, _ptr(_f32(a)), _ptr(_f32(b)), _ptr(bias), _ptr(_f32(residual)),
+                                                            _ptr(c), _stream()))
+        else:
+            self.check(self.lib.petb200_matmul_run(plan.h, _ptr(_f32(a)), _ptr(_f32(b)), _ptr(bias), _ptr(c), _stream()))
         return c
 
-    def matmul(self, a, b, transA=False, transB=False, bias=None, act="none", algo="auto"):
+    def matmul(self, a, b, transA=False, transB=False, bias=None, act="none", algo="auto", residual=None):
         key = ("matmul", tuple(a.shape), tuple(b.shape), transA, transB, bias is not None, act, algo)
         plan = self._plans.get(key)
         if plan is None:
             plan = self._plans[key] = self.matmul_plan(a.shape, b.shape, transA, transB, bias is not None, act, algo)
-        return self.matmul_run(plan, a, b, bias)
+        return self.matmul_run(plan, a, b, bias, residual=residual)
 
     # ---- layout --------------------------------------------------------------------------------------------
     def transpose_plan(self, shape, ops):

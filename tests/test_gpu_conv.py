@@ -67,6 +67,27 @@ def test_conv_vs_oracle(ctx, oracle, case, algo):
     assert scale_err(got, want) <= TOL_SCALE
 
 
+RES_CASES = [  # tile kinds: split K over a cluster, unsplit, flat whole-plane tiles, CUDA-core fallback
+    ("split_k", (1, 128, 28, 28), (128, 128, 3, 3), 1, "auto"), ("unsplit", (8, 64, 56, 56), (64, 64, 3, 3), 1, "auto"),
+    ("flat_7", (2, 64, 7, 7), (96, 64, 3, 3), 1, "auto"), ("simt", (1, 8, 9, 11), (12, 8, 3, 3), 1, "simt_fp32"),
+]
+
+
+@pytest.mark.parametrize("case", RES_CASES, ids=[c[0] for c in RES_CASES])
+def test_conv_with_residual_equals_conv_then_add(ctx, case):
+    _, xs, ws, pad, algo = case
+    rng = np.random.default_rng(len(xs) + xs[1])
+    x = dev(rng.uniform(-1, 1, xs).astype(np.float32))
+    w = dev((rng.standard_normal(ws) / np.sqrt(ws[1] * 9)).astype(np.float32))
+    b = dev(rng.uniform(-1, 1, ws[0]).astype(np.float32))
+    plain = ctx.conv2d(x, w, pad, pad, bias=b, algo=algo)
+    res = dev(rng.uniform(-1, 1, tuple(plain.shape)).astype(np.float32))
+    want = ctx.eltwise("add", [plain, res], act="relu")
+    got = ctx.conv2d(x, w, pad, pad, bias=b, act="relu", algo=algo, residual=res)
+    ctx.sync_check()
+    assert torch.equal(got, want)  # same sums in the same order as the two-operator form
+
+
 def test_auto_picks_the_tensor_core_kernel(ctx):
     plan = ctx.conv2d_plan((1, 64, 56, 56), (64, 64, 3, 3), 1, 1)
     assert plan.kernel.startswith("tc_3xtf32")

@@ -53,6 +53,18 @@ def test_matmul_vs_oracle(ctx, oracle, shape, algo):
     assert rel_err(got, want) <= TOL and scale_err(got, want) <= TOL_SCALE
 
 
+@pytest.mark.parametrize("shape", [(1, 128, 768, 768), (1, 2, 100, 64), (2, 36, 20, 52)], ids=str)
+def test_matmul_with_residual_equals_matmul_then_add(ctx, shape):
+    b, m, n, k = shape
+    rng = np.random.default_rng(m + n)
+    a, bm = dev(rng.standard_normal((b, m, k)).astype(np.float32)), dev((rng.standard_normal((b, k, n)) / np.sqrt(k)).astype(np.float32))
+    bias, res = dev(rng.standard_normal(n).astype(np.float32)), dev(rng.standard_normal((b, m, n)).astype(np.float32))
+    want = ctx.eltwise("add", [ctx.matmul(a, bm, bias=bias), res])
+    got = ctx.matmul(a, bm, bias=bias, residual=res)
+    ctx.sync_check()
+    assert torch.equal(got, want)
+
+
 def test_matmul_rejects_mismatched_operands(ctx):
     from pet_b200 import PetError
     with pytest.raises(PetError):
