@@ -103,83 +103,113 @@ __global__ void __launch_bounds__(256) k_matmul_simt(const float *__restrict__ a
 // almost empty, and the work is one pass over B.  A block owns 32 columns of C for all rows; exact fp32 FMA.
 //   B as [k][n]: lanes = columns (coalesced rows of B), the 8 warps split K and are added up through shared memory.
 //   B as [n][k]: a warp owns 4 columns, lanes split K (coalesced rows of B), lanes are added up by shuffles.
-constexpr int kGemvRows = 8, kGemvWarps = 16;
+constexpr int kGemvRows = 8, kGemvWarps = 16, kGemvKTile = 768;
 __global__ void __launch_bounds__(kGemvWarps * 32) k_gemv_small_m(const float *__restrict__ a, const float *__restrict__ b,
                                                                  const float *__restrict__ bias, const float *__restrict__ res,
                                                                  float *__restrict__ c, int m, int n, int k, int transA, int transB,
                                                                  int act) {
+    __shared__ float sa[kGemvRows][kGemvKTile];        // a K tile of A, row r at sa[r]
     __shared__ float red[kGemvWarps][kGemvRows][33];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, bb = blockIdx.y;
     const float *ab = a + (long long)bb * m * k, *bm = b + (long long)bb * k * n;
-    const long long a_sk = transA ? m : 1, a_sr = transA ? 1 : k; // A(r, kk) = ab[r * a_sr + kk * a_sk]
     float acc[kGemvRows];
 #pragma unroll
     for (int r = 0; r < kGemvRows; ++r)
         acc[r] = 0.f;
-    if (!transB) {
-        const int col = blockIdx.x * 32 + lane;
-        const int kbeg = (int)((long long)k * warp / kGemvWarps), kend = (int)((long long)k * (warp + 1) / kGemvWarps);
-        for (int k0 = kbeg; k0 < kend; k0 += 8) {
-            float bv[8]; // eight rows of B in flight per lane
+    const int col0 = blockIdx.x * 32;
+    for (int kt = 0; kt < k; kt += kGemvKTile) {
+        const int kn = min(kGemvKTile, k - kt);
+        __syncthreads(); // the previous tile has been consumed
+        for (int i = threadIdx.x; i < m * kn; i += kGemvWarps * 32) {
+            int r, kk;
+            if (transA) // A is [k][m]: consecutive threads read consecutive addresses
+                kk = i / m, r = i - kk * m;
+            else
+                r = i / kn, kk = i - r * kn;
+            sa[r][kk] = __ldg(transA ? ab + (long long)(kt + kk) * m + r : ab + (long long)r * k + kt + kk);
+        }
+        __syncthreads();
+        if (!transB) {
+            // B as [k][n]: lanes = columns (coalesced rows of B), the warps split the tile's K range
+            const int col = col0 + lane;
+            const int kbeg = kn * warp / kGemvWarps, kend = kn * (warp + 1) / kGemvWarps;
+            for (int k0 = kbeg; k0 < kend; k0 += 16) {
+                float bv[16]; // sixteen rows of B in flight per lane
 #pragma unroll
-            for (int u = 0; u < 8; ++u)
-                bv[u] = (k0 + u < kend && col < n) ? __ldg(bm + (long long)(k0 + u) * n + col) : 0.f;
+                for (int u = 0; u < 16; ++u)
+                    bv[u] = (k0 + u < kend && col < n) ? __ldg(bm + (long long)(kt + k0 + u) * n + col) : 0.f;
 #pragma unroll
-            for (int u = 0; u < 8; ++u)
+                for (int u = 0; u < 16; ++u) {
+                    const int kk = min(k0 + u, kend - 1); // rows past the end carry bv = 0
+#pragma unroll
+                    for (int r = 0; r < kGemvRows; ++r)
+                        acc[r] = fmaf(sa[r][kk], bv[u], acc[r]);
+                }
+            }
+        } else {
+            // B as [n][k]: a warp owns columns warp and warp + 16 of the block, lanes split K (coalesced rows of B);
+            // two accumulator sets would be needed to keep both: process the tile column by column instead
+            for (int cc = 0; cc < 2; ++cc) {
+                const int col = col0 + warp + cc * kGemvWarps;
+                if (col >= n)
+                    break;
+                float part[kGemvRows];
 #pragma unroll
                 for (int r = 0; r < kGemvRows; ++r)
-                    if (r < m && k0 + u < kend)
-                        acc[r] = fmaf(__ldg(ab + r * a_sr + (k0 + u) * a_sk), bv[u], acc[r]);
+                    part[r] = 0.f;
+                for (int k0 = lane; k0 < kn; k0 += 8 * 32) {
+                    float bv[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        bv[u] = k0 + 32 * u < kn ? __ldg(bm + (long long)col * k + kt + k0 + 32 * u) : 0.f;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int kk = min(k0 + 32 * u, kn - 1);
+#pragma unroll
+                        for (int r = 0; r < kGemvRows; ++r)
+                            part[r] = fmaf(sa[r][kk], bv[u], part[r]);
+                    }
+                }
+                // per-column partial sums of this K tile go through shared memory, slot [cc*16 + warp... ] is this column
+#pragma unroll
+                for (int r = 0; r < kGemvRows; ++r) {
+                    float v = part[r];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1)
+                        v += __shfl_xor_sync(0xffffffffu, v, o);
+                    if (lane == 0)
+                        red[cc][r][warp] = (kt == 0 ? 0.f : red[cc][r][warp]) + v;
+                }
+            }
         }
+    }
+    if (!transB) {
 #pragma unroll
         for (int r = 0; r < kGemvRows; ++r)
             red[warp][r][lane] = acc[r];
-        __syncthreads();
-        // warp r adds up row r over the K slices, in slice order
-        if (warp < m && col < n) {
-            float v = 0.f;
+    }
+    __syncthreads();
+    // thread (warp = row, lane = column) finishes one output
+    if (warp < m) {
+        const int r = warp;
+        float v = 0.f;
+        int col;
+        if (!transB) {
+            col = col0 + lane;
 #pragma unroll
-            for (int w = 0; w < kGemvWarps; ++w)
-                v += red[w][warp][lane];
+            for (int w = 0; w < kGemvWarps; ++w) // K slices in order
+                v += red[w][r][lane];
+        } else {
+            col = col0 + (lane & 15) + (lane >> 4) * kGemvWarps;
+            v = red[lane >> 4][r][lane & 15];
+        }
+        if (col < n) {
             if (bias)
                 v += __ldg(bias + col);
-            const long long co = ((long long)bb * m + warp) * n + col;
+            const long long co = ((long long)bb * m + r) * n + col;
             if (res)
                 v += __ldg(res + co);
             c[co] = apply_act(v, act);
-        }
-    } else {
-        for (int col = blockIdx.x * 32 + warp; col < min(n, (int)blockIdx.x * 32 + 32); col += kGemvWarps) {
-#pragma unroll
-            for (int r = 0; r < kGemvRows; ++r)
-                acc[r] = 0.f;
-            for (int k0 = lane; k0 < k; k0 += 8 * 32) {
-                float bv[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    bv[u] = k0 + 32 * u < k ? __ldg(bm + (long long)col * k + k0 + 32 * u) : 0.f;
-#pragma unroll
-                for (int u = 0; u < 8; ++u)
-#pragma unroll
-                    for (int r = 0; r < kGemvRows; ++r)
-                        if (r < m && k0 + 32 * u < k)
-                            acc[r] = fmaf(__ldg(ab + r * a_sr + (k0 + 32 * u) * a_sk), bv[u], acc[r]);
-            }
-#pragma unroll
-            for (int r = 0; r < kGemvRows; ++r) {
-                float v = acc[r];
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1)
-                    v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == 0 && r < m) {
-                    if (bias)
-                        v += __ldg(bias + col);
-                    const long long co = ((long long)bb * m + r) * n + col;
-                    if (res)
-                        v += __ldg(res + co);
-                    c[co] = apply_act(v, act);
-                }
-            }
         }
     }
 }
