@@ -14,6 +14,7 @@ int tc_conv_set_weights(void *h, const float *w, cudaStream_t s);
 int tc_conv_run(void *h, const float *x, const float *bias, const float *res, float *y, const int *win, cudaStream_t s);
 int tc_conv_row_pitch(void *h);
 void tc_conv_set_prof(void *h, long long *p);
+void tc_matmul_set_prof(void *h, long long *p);
 const char *tc_conv_variant(void *h);
 int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, int transB, int has_bias, int act, int passes,
                      void **out, size_t *dev_bytes);
@@ -565,6 +566,12 @@ int MatmulPlan::bench_launch(cudaStream_t s) {
 
 // Tuning aid (not part of the public header): per-CTA cycle counters of the tensor-core conv kernel, 8 per CTA.
 extern "C" int petb200_debug_conv_prof(petb200_plan *plan, long long *dev_counters) {
+    if (auto *mp = dynamic_cast<petb200::MatmulPlan *>(plan)) {
+        if (!mp->tc)
+            return PETB200_ERR_INVALID;
+        petb200::tc_matmul_set_prof(mp->tc, dev_counters);
+        return PETB200_OK;
+    }
     auto *pl = dynamic_cast<petb200::ConvPlan *>(plan);
     if (!pl || !pl->tc)
         return PETB200_ERR_INVALID;

@@ -264,10 +264,43 @@ __device__ __forceinline__ void gather_split(const int4 *ko, const float *raw, c
 template <int ACT>
 __device__ __forceinline__ void cluster_reduce_store(const float *stage, int ksplit, int rank, int BN, int et /*0..255*/,
                                                      int f_tile0, int Fg, const float *bias, const float *rp, float *yp /*this pixel, filter 0*/,
-                                                     long long ys_f) {
-    const int cols = BN / ksplit, px = et & (kTileM - 1);
+                                                     long long ys_f, bool vec_ok) {
+    const int cols = BN / ksplit, px = et & (kTileM - 1), half = et >> 7;
+    if (vec_ok) {
+        // Filters are contiguous in y (row-major matmul output): a thread owns a run of cols/2 consecutive columns of its
+        // pixel and stores them 16 bytes at a time; with the interleaved assignment below every 4-byte store would
+        // touch its own 32-byte sector.
+        const int run = cols >> 1; // 2, 4, 8, ... 32
+        for (int c0 = half * run; c0 < (half + 1) * run; c0 += 4) {
+            const int f = f_tile0 + rank * cols + c0, nv = min(4, run);
+            if (f >= Fg)
+                break;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (r < ksplit && j < nv)
+                        acc[j] += stage[(r * cols + c0 + j) * kTileM + px]; // rank order for every element
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (j < nv && f + j < Fg) {
+                    if (bias != nullptr)
+                        acc[j] += __ldg(bias + f + j);
+                    if (rp != nullptr)
+                        acc[j] += __ldg(rp + f + j);
+                    acc[j] = act_fn<ACT>(acc[j]);
+                }
+            }
+            if (nv == 4) // Fg % 4 == 0 and f % 4 == 0 here: the whole quad is inside the row
+                *reinterpret_cast<float4 *>(yp + f) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            else
+                *reinterpret_cast<float2 *>(yp + f) = make_float2(acc[0], acc[1]);
+        }
+        return;
+    }
 #pragma unroll 2
-    for (int cl = et >> 7; cl < cols; cl += 2) {
+    for (int cl = half; cl < cols; cl += 2) {
         const int f = f_tile0 + rank * cols + cl;
         if (f >= Fg)
             break;
@@ -825,7 +858,12 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 const float *bp = P.has_bias ? P.bias + f_glob0 : nullptr;
                 const float *rp = P.res != nullptr ? P.res + y_off + f_glob0 * P.ys_f : nullptr;
                 const int rank = (int)ptx::cluster_ctarank();
-#define PETB200_RED(ACT_) cluster_reduce_store<ACT_>(sSplit, P.ksplit, rank, P.BN, et, ntile * P.BN, P.Fg, bp, rp, yp, P.ys_f)
+                // 16-byte stores need filters contiguous in y, 16-byte aligned rows, and column runs of at least 2
+                const bool red_vec = (P.ys_f == 1) && ((P.ys_p & 3) == 0) && ((P.ys_n & 3) == 0) && ((P.Fg & 3) == 0) &&
+                                     ((reinterpret_cast<uintptr_t>(P.y) & 15) == 0) && (P.BN / P.ksplit >= 4) &&
+                                     (P.res == nullptr || (reinterpret_cast<uintptr_t>(P.res) & 15) == 0);
+#define PETB200_RED(ACT_) \
+    cluster_reduce_store<ACT_>(sSplit, P.ksplit, rank, P.BN, et, ntile * P.BN, P.Fg, bp, rp, yp, P.ys_f, red_vec)
                 switch (P.act) {
                 case PETB200_ACT_RELU: PETB200_RED(PETB200_ACT_RELU); break;
                 case PETB200_ACT_SIGMOID: PETB200_RED(PETB200_ACT_SIGMOID); break;
@@ -1058,12 +1096,12 @@ static int env_int(const char *name, int dflt) {
 // Rough cycle model of one launch, used to pick the tile width and the K split for problems that cannot fill the GPU
 // with 128-wide tiles.  Constants are measured on B200: a K stage costs its MMAs (N/2 cycles each, 12 per stage for
 // 3xTF32, 4 for one pass) or, if larger, the transform chain of the stage (~330 cycles with two warp sets); a CTA pays
-// ~3000 cycles before its first MMA and 1700 + 44*BN cycles of epilogue; the split-K fix-up re-reads every partial copy
-// through L2, four copies per round trip.
+// ~3000 cycles before its first MMA and 1700 + 44*BN cycles of epilogue (split-K: the exchange through the cluster instead).
 static double est_cycles(int sm_count, long long base_ctas, int nchunks, int spc, int BN, int passes, int ks) {
     const double stage = std::max<double>((passes == 3 ? 12.0 : 4.0) * (BN / 2), 520.0);
     const long long stages = (long long)((nchunks + ks - 1) / ks) * spc;
-    const double per_cta = 3000.0 + (double)stages * stage + 1700.0 + (ks > 1 ? 12.0 * BN + 1500.0 : 44.0 * BN);
+    // split-K: (ks-1)/ks of the 512*BN-byte tile crosses to other SMs at ~10 bytes per cycle, then barrier + local sums
+    const double per_cta = 3000.0 + (double)stages * stage + 1700.0 + (ks > 1 ? 1500.0 + 50.0 * BN * (ks - 1) / ks : 44.0 * BN);
     // clusters are placed inside one GPC, which leaves a few SMs of each GPC unused
     const long long slots = ks == 1 ? sm_count : std::max(1, (sm_count * (ks <= 2 ? 96 : 86) / 100) / ks);
     const long long waves = (base_ctas + slots - 1) / slots;
@@ -1509,9 +1547,6 @@ static int tc_configure_kmajor(petb200_ctx *ctx, TcCore &core, int bs, int m, in
     P.OD = P.OH = 1, P.OW = m, P.ohn = 1, P.own = m, P.Pw = m, P.units = 1, P.ipt = 1, P.tpi = (m + kTileM - 1) / kTileM;
     P.sd = P.sh = P.sw = 1;
     P.cpg = k, P.Fg = n;
-    int BN = n <= 32 ? 32 : (n <= 64 ? 64 : 128);
-    BN = env_int("PETB200_TC_BN", BN);
-    P.BN = BN;
     P.BC = kStageK, P.spc = 1, P.nchunks = (k + kStageK - 1) / kStageK;
     P.RN = P.RD = 1, P.RH = kTileM, P.RW = kStageK;
     P.raw_bytes = kAHalfBytes;
@@ -1520,8 +1555,26 @@ static int tc_configure_kmajor(petb200_ctx *ctx, TcCore &core, int bs, int m, in
     P.NA = 4;
     const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 1024;
     P.NB = 2, P.NR = 2;
-    P.ksplit = choose_ksplit(ctx->sm_count, (long long)P.tpi * ((n + P.BN - 1) / P.BN) * bs, P, core.single_pass ? 1 : 3,
-                             env_int("PETB200_TC_KSPLIT", 0), nullptr); // before the rings: the split takes shared memory
+    // tile width and K split by the cycle model (before the rings are sized: a split takes shared memory)
+    {
+        const int bn_max = n <= 32 ? 32 : (n <= 64 ? 64 : 128), forced_bn = env_int("PETB200_TC_BN", 0);
+        double best = 0;
+        int best_bn = 0, best_ks = 1;
+        for (int bn = 128; bn >= 32; bn /= 2) {
+            if (forced_bn ? bn != forced_bn : bn > bn_max)
+                continue;
+            P.BN = bn;
+            double cyc;
+            const int ks = choose_ksplit(ctx->sm_count, (long long)P.tpi * ((n + bn - 1) / bn) * bs, P, core.single_pass ? 1 : 3,
+                                         env_int("PETB200_TC_KSPLIT", 0), &cyc);
+            if (!best_bn || cyc < best * 0.97)
+                best = cyc, best_bn = bn, best_ks = ks;
+        }
+        if (!best_bn)
+            return fail(ctx, PETB200_ERR_INVALID, "PETB200_TC_BN must be 32, 64 or 128");
+        P.BN = best_bn;
+        P.ksplit = best_ks;
+    }
     if (smem_layout(P, true).total > budget)
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "matmul tile does not fit shared memory");
     for (bool grew = true; grew;) { // deepen both rings alternately: every K stage needs one B tile and one raw tile
@@ -1616,6 +1669,7 @@ int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, 
     *out = t;
     return PETB200_OK;
 }
+void tc_matmul_set_prof(void *h, long long *p) { ((TcMatmul *)h)->core.prof = p; }
 int tc_matmul_native_a(void *h) { return ((TcMatmul *)h)->native_a ? 1 : 0; }
 void tc_matmul_destroy(void *h) { delete (TcMatmul *)h; }
 int tc_matmul_pack_b(void *h, const float *b, cudaStream_t s) {
