@@ -389,6 +389,10 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above touched only this CTA's own state and the plan's constant table, so under programmatic dependent
+    // launch it overlaps the tail of the preceding kernel; from here on the kernel reads what that kernel wrote.
+    ptx::grid_dep_launch_dependents();
+    ptx::grid_dep_wait();
     if (prof_cta)
         prof_cta[9] = (long long)ptx::globaltimer_ns();
 
@@ -955,6 +959,15 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
+static bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("PETB200_PDL");
+        v = e ? atoi(e) : 1;
+    }
+    return v != 0;
+}
+
 struct TcCore {
     petb200_ctx *ctx = nullptr;
     IgemmParams P{};
@@ -1062,15 +1075,22 @@ struct TcCore {
         cfg.blockDim = dim3(kThreads);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = s;
-        cudaLaunchAttribute attr{};
+        cudaLaunchAttribute attr[2] = {};
+        int nattr = 0;
         if (P.ksplit > 1) { // the splits of one output tile are consecutive in blockIdx.y: one cluster
-            attr.id = cudaLaunchAttributeClusterDimension;
-            attr.val.clusterDim.x = 1;
-            attr.val.clusterDim.y = (unsigned)P.ksplit;
-            attr.val.clusterDim.z = 1;
-            cfg.attrs = &attr;
-            cfg.numAttrs = 1;
+            attr[nattr].id = cudaLaunchAttributeClusterDimension;
+            attr[nattr].val.clusterDim.x = 1;
+            attr[nattr].val.clusterDim.y = (unsigned)P.ksplit;
+            attr[nattr].val.clusterDim.z = 1;
+            ++nattr;
         }
+        if (pdl_enabled()) { // this kernel's set-up may overlap the end of the kernel before it in the stream
+            attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+            ++nattr;
+        }
+        cfg.attrs = nattr ? attr : nullptr;
+        cfg.numAttrs = (unsigned)nattr;
         cudaError_t le = cudaLaunchKernelEx(&cfg, kern, map_x, map_bhi, map_blo, p);
         if (le != cudaSuccess) {
             (void)cudaGetLastError();

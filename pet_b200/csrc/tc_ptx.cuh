@@ -100,6 +100,13 @@ __device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t *bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------------------------
+// launch_dependents: once every CTA of this grid has executed it (or exited), a following kernel launched with the
+// programmatic-serialization attribute may start its CTAs on free SMs.  wait: blocks until the preceding grid has
+// completed and its memory is visible; a no-op for kernels launched without the attribute.
+__device__ __forceinline__ void grid_dep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- proxy fences -----------------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
