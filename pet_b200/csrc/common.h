@@ -1,5 +1,6 @@
 // Internal definitions shared by the kernels and the C-ABI glue of libpetb200.
 #pragma once
+#include <cstdlib>
 #include "../../include/petb200.h"
 #include <cuda_runtime.h>
 #include <cstdarg>
@@ -55,6 +56,42 @@ inline int launched(petb200_ctx *ctx, const char *what) {
     if (e != cudaSuccess)
         return fail(ctx, PETB200_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
     return PETB200_OK;
+}
+
+// ---- programmatic dependent launch ---------------------------------------------------------------------------------
+// Every kernel of the library starts with pdl_prologue() and is launched through launch_pdl(): a kernel's CTAs may then
+// be placed on free SMs while the kernel before it in the stream is still finishing, and wait (griddepcontrol.wait)
+// until that kernel has completed and its writes are visible before they touch global memory.  PETB200_PDL=0 in the
+// environment launches without the attribute (both instructions are then no-ops).
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_prologue() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+#endif
+inline bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("PETB200_PDL");
+        v = e ? atoi(e) : 1;
+    }
+    return v != 0;
+}
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    if (pdl_enabled()) {
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+    }
+    (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...); // errors surface through launched()
 }
 
 struct DevBuf {

@@ -35,6 +35,7 @@ struct SimtConv {
 __global__ void __launch_bounds__(256) k_conv_simt(const float *__restrict__ x, const float *__restrict__ w,
                                                    const float *__restrict__ bias, const float *__restrict__ res,
                                                    float *__restrict__ y, SimtConv c) {
+    pdl_prologue();
     const int cpg = c.C / c.groups, fpg = c.F / c.groups;
     const long long total = (long long)c.N * c.F * c.OD * c.ohn * c.own;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -81,6 +82,7 @@ __global__ void __launch_bounds__(256) k_matmul_simt(const float *__restrict__ a
                                                      const float *__restrict__ bias, const float *__restrict__ res,
                                                      float *__restrict__ c, int bs, int m, int n, int k, int transA, int transB,
                                                      int act) {
+    pdl_prologue();
     const long long total = (long long)bs * m * n;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int nn = (int)(i % n);
@@ -109,6 +111,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) k_gemv_small_m(const float *_
                                                                  const float *__restrict__ bias, const float *__restrict__ res,
                                                                  float *__restrict__ c, int m, int n, int k, int transA, int transB,
                                                                  int act) {
+    pdl_prologue();
     __shared__ float sa[kGemvRows][kGemvKTile];        // a K tile of A, row r at sa[r]
     __shared__ float red[kGemvWarps][kGemvRows][33];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, bb = blockIdx.y;
@@ -217,6 +220,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32) k_gemv_small_m(const float *_
 
 // Re-pitches [planes, H, W] rows to a pitch divisible by 4 (zero fill), so TMA's 16-byte stride rule holds.
 __global__ void __launch_bounds__(256) k_repitch(const float *__restrict__ x, float *__restrict__ y, long long rows, int w, int wp) {
+    pdl_prologue();
     const long long total = rows * wp;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int col = (int)(i % wp);
@@ -227,6 +231,7 @@ __global__ void __launch_bounds__(256) k_repitch(const float *__restrict__ x, fl
 
 // [b][m][k] -> [b][k][mp]  (row pitch mp >= m, padding columns zero)
 __global__ void __launch_bounds__(256) k_transpose_a(const float *__restrict__ a, float *__restrict__ at, int bs, int m, int k, int mp) {
+    pdl_prologue();
     __shared__ float tile[32][33];
     const int tiles_k = (k + 31) / 32, tiles_m = (mp + 31) / 32;
     const long long ntiles = (long long)bs * tiles_k * tiles_m;
@@ -375,7 +380,7 @@ int conv_run(petb200_plan *plan, const float *x, const float *bias, float *y, co
         if (pl->xpad.p) {
             const SimtConv &c = pl->sc;
             long long rows = (long long)c.N * c.C * c.D * c.H;
-            k_repitch<<<grid_for(ctx, rows * pl->wp, 256), 256, 0, s>>>(x, (float *)pl->xpad.p, rows, c.W, pl->wp);
+            launch_pdl(k_repitch, grid_for(ctx, rows * pl->wp, 256), 256, 0, s, x, (float *)pl->xpad.p, rows, c.W, pl->wp);
             int rc = launched(ctx, "k_repitch");
             if (rc)
                 return rc;
@@ -392,7 +397,7 @@ int conv_run(petb200_plan *plan, const float *x, const float *bias, float *y, co
         c.oh0 = win[0], c.ohn = win[1], c.ow0 = win[2], c.own = win[3];
     }
     long long total = (long long)c.N * c.F * c.OD * c.ohn * c.own;
-    k_conv_simt<<<grid_for(ctx, total, 256), 256, 0, s>>>(x, pl->w_simt, bias, res, y, c);
+    launch_pdl(k_conv_simt, grid_for(ctx, total, 256), 256, 0, s, x, pl->w_simt, bias, res, y, c);
     return launched(ctx, "k_conv_simt");
 }
 
@@ -513,14 +518,14 @@ int matmul_run(petb200_plan *plan, const float *a, const float *b, const float *
             // nothing to do: the kernel's K-major mode consumes A as it is
         } else if (!pl->transA) {
             long long tiles = (long long)pl->bs * ((pl->k + 31) / 32) * ((mp + 31) / 32);
-            k_transpose_a<<<(int)std::min<long long>(tiles, (long long)ctx->sm_count * 8), 256, 0, s>>>(a, (float *)pl->at.p, pl->bs, pl->m, pl->k, mp);
+            launch_pdl(k_transpose_a, (int)std::min<long long>(tiles, (long long)ctx->sm_count * 8), 256, 0, s, a, (float *)pl->at.p, pl->bs, pl->m, pl->k, mp);
             rc = launched(ctx, "k_transpose_a");
             if (rc)
                 return rc;
             at = (const float *)pl->at.p;
         } else if (mp != pl->m) {
             long long rows = (long long)pl->bs * pl->k;
-            k_repitch<<<grid_for(ctx, rows * mp, 256), 256, 0, s>>>(a, (float *)pl->at.p, rows, pl->m, mp);
+            launch_pdl(k_repitch, grid_for(ctx, rows * mp, 256), 256, 0, s, a, (float *)pl->at.p, rows, pl->m, mp);
             rc = launched(ctx, "k_repitch");
             if (rc)
                 return rc;
@@ -529,12 +534,12 @@ int matmul_run(petb200_plan *plan, const float *a, const float *b, const float *
         return tc_matmul_run(pl->tc, at, pl->has_bias ? bias : nullptr, res, c, s);
     }
     if (pl->gemv) {
-        k_gemv_small_m<<<dim3((unsigned)((pl->n + 31) / 32), (unsigned)pl->bs), kGemvWarps * 32, 0, s>>>(
+        launch_pdl(k_gemv_small_m, dim3((unsigned)((pl->n + 31) / 32), (unsigned)pl->bs), kGemvWarps * 32, 0, s, 
             a, b, pl->has_bias ? bias : nullptr, res, c, pl->m, pl->n, pl->k, pl->transA, pl->transB, pl->act);
         return launched(ctx, "k_gemv_small_m");
     }
     long long total = (long long)pl->bs * pl->m * pl->n;
-    k_matmul_simt<<<grid_for(ctx, total, 256), 256, 0, s>>>(a, b, pl->has_bias ? bias : nullptr, res, c, pl->bs, pl->m, pl->n, pl->k,
+    launch_pdl(k_matmul_simt, grid_for(ctx, total, 256), 256, 0, s, a, b, pl->has_bias ? bias : nullptr, res, c, pl->bs, pl->m, pl->n, pl->k,
                                                             pl->transA, pl->transB, pl->act);
     return launched(ctx, "k_matmul_simt");
 }

@@ -20,6 +20,7 @@ __device__ __forceinline__ float combine(int kind, float a, float b) {
 // Operand j is read at i % size_j (the reference's broadcast rule).  vec4 path: every operand either spans the whole
 // output or has a size divisible by 4 that divides into aligned groups.
 __global__ void __launch_bounds__(256) k_eltwise_v4(EltArgs a, float4 *__restrict__ out, size_t n4) {
+    pdl_prologue();
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
         size_t e = i * 4;
         float4 v = __ldg(reinterpret_cast<const float4 *>(a.in[0] + e % a.size[0]));
@@ -41,6 +42,7 @@ __global__ void __launch_bounds__(256) k_eltwise_v4(EltArgs a, float4 *__restric
 }
 
 __global__ void __launch_bounds__(256) k_eltwise(EltArgs a, float *__restrict__ out, size_t n) {
+    pdl_prologue();
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         float v = __ldg(a.in[0] + i % a.size[0]);
 #pragma unroll
@@ -55,6 +57,7 @@ __global__ void __launch_bounds__(256) k_batchnorm(const float *__restrict__ x, 
                                                    const float *__restrict__ bias, const float *__restrict__ mean,
                                                    const float *__restrict__ var, float *__restrict__ y, size_t total,
                                                    int c, size_t inner, float eps) {
+    pdl_prologue();
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         int cc = (int)((i / inner) % c);
         // the reference forms scale/sqrt(var+eps) in double (src/Graph/operator.cc:2669-2671)
@@ -66,6 +69,7 @@ __global__ void __launch_bounds__(256) k_batchnorm(const float *__restrict__ x, 
 __global__ void __launch_bounds__(256) k_pool2d(int kind, const float *__restrict__ x, float *__restrict__ y, int nc,
                                                 int h, int w, int oh, int ow, int kh, int kw, int ph, int pw, int sh,
                                                 int sw) {
+    pdl_prologue();
     size_t total = (size_t)nc * oh * ow;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         int j = (int)(i % ow);
@@ -111,6 +115,7 @@ __device__ __forceinline__ float warp_max(float v) {
 __global__ void __launch_bounds__(256) k_pool2d_warp(int kind, const float *__restrict__ x, float *__restrict__ y, int nc,
                                                      int h, int w, int oh, int ow, int kh, int kw, int ph, int pw, int sh,
                                                      int sw) {
+    pdl_prologue();
     const size_t total = (size_t)nc * oh * ow;
     const int lane = threadIdx.x & 31;
     for (size_t i = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5; i < total; i += ((size_t)gridDim.x * blockDim.x) >> 5) {
@@ -142,6 +147,7 @@ __global__ void __launch_bounds__(256) k_pool2d_warp(int kind, const float *__re
 
 // One warp per row; rows are short (<= a few thousand) in every PET workload, so the row stays in registers/L1.
 __global__ void __launch_bounds__(256) k_rowmean(const float *__restrict__ x, float *__restrict__ y, size_t rows, int cols) {
+    pdl_prologue();
     size_t warp = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
     int lane = threadIdx.x & 31;
     size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
@@ -157,6 +163,7 @@ __global__ void __launch_bounds__(256) k_rowmean(const float *__restrict__ x, fl
 }
 
 __global__ void __launch_bounds__(256) k_softmax(const float *__restrict__ x, float *__restrict__ y, size_t rows, int cols) {
+    pdl_prologue();
     size_t warp = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
     int lane = threadIdx.x & 31;
     size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
@@ -180,6 +187,7 @@ __global__ void __launch_bounds__(256) k_softmax(const float *__restrict__ x, fl
 __global__ void __launch_bounds__(256) k_layernorm(const float *__restrict__ x, const float *__restrict__ gamma,
                                                    const float *__restrict__ beta, float *__restrict__ y, size_t rows,
                                                    int cols, float eps) {
+    pdl_prologue();
     size_t warp = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5;
     int lane = threadIdx.x & 31;
     size_t nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
@@ -235,6 +243,7 @@ __device__ __forceinline__ float block_max(float v, float *red) {
 
 // One 256-thread block per row: used when there are too few rows to fill the GPU with one warp per row.
 __global__ void __launch_bounds__(256) k_softmax_block(const float *__restrict__ x, float *__restrict__ y, size_t rows, int cols) {
+    pdl_prologue();
     __shared__ float red[8];
     for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
         const float *xp = x + r * (size_t)cols;
@@ -255,6 +264,7 @@ __global__ void __launch_bounds__(256) k_softmax_block(const float *__restrict__
 __global__ void __launch_bounds__(256) k_layernorm_block(const float *__restrict__ x, const float *__restrict__ gamma,
                                                          const float *__restrict__ beta, float *__restrict__ y, size_t rows,
                                                          int cols, float eps) {
+    pdl_prologue();
     __shared__ float red[8];
     for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
         const float *xp = x + r * (size_t)cols;
@@ -310,10 +320,10 @@ extern "C" int petb200_eltwise_run(petb200_ctx *ctx, int kind, int n_in, const f
     }
     cudaStream_t s = (cudaStream_t)stream;
     if (v4) {
-        k_eltwise_v4<<<grid_for(ctx, out_size / 4, 256), 256, 0, s>>>(a, (float4 *)out, out_size / 4);
+        launch_pdl(k_eltwise_v4, grid_for(ctx, out_size / 4, 256), 256, 0, s, a, (float4 *)out, out_size / 4);
         return launched(ctx, "k_eltwise_v4");
     }
-    k_eltwise<<<grid_for(ctx, out_size, 256), 256, 0, s>>>(a, out, out_size);
+    launch_pdl(k_eltwise, grid_for(ctx, out_size, 256), 256, 0, s, a, out, out_size);
     return launched(ctx, "k_eltwise");
 }
 
@@ -336,7 +346,7 @@ extern "C" int petb200_batchnorm_run(petb200_ctx *ctx, const float *x, const flo
     size_t total = outer * (size_t)c * inner;
     if (!total)
         return PETB200_OK;
-    k_batchnorm<<<grid_for(ctx, total, 256), 256, 0, (cudaStream_t)stream>>>(x, scale, bias, mean, var, y, total, c,
+    launch_pdl(k_batchnorm, grid_for(ctx, total, 256), 256, 0, (cudaStream_t)stream, x, scale, bias, mean, var, y, total, c,
                                                                              inner, eps);
     return launched(ctx, "k_batchnorm");
 }
@@ -351,11 +361,11 @@ extern "C" int petb200_pool2d_run(petb200_ctx *ctx, int kind, const float *x, fl
         return fail(ctx, PETB200_ERR_INVALID, "pool2d_run: empty output");
     size_t total = (size_t)n * c * oh * ow;
     if (kh * kw >= 32) {
-        k_pool2d_warp<<<grid_for(ctx, total, 8), 256, 0, (cudaStream_t)stream>>>(kind, x, y, n * c, h, w, oh, ow, kh, kw, ph,
+        launch_pdl(k_pool2d_warp, grid_for(ctx, total, 8), 256, 0, (cudaStream_t)stream, kind, x, y, n * c, h, w, oh, ow, kh, kw, ph,
                                                                                   pw, sh, sw);
         return launched(ctx, "k_pool2d_warp");
     }
-    k_pool2d<<<grid_for(ctx, total, 256), 256, 0, (cudaStream_t)stream>>>(kind, x, y, n * c, h, w, oh, ow, kh, kw, ph,
+    launch_pdl(k_pool2d, grid_for(ctx, total, 256), 256, 0, (cudaStream_t)stream, kind, x, y, n * c, h, w, oh, ow, kh, kw, ph,
                                                                           pw, sh, sw);
     return launched(ctx, "k_pool2d");
 }
@@ -366,7 +376,7 @@ extern "C" int petb200_rowmean_run(petb200_ctx *ctx, const float *x, float *y, s
         return fail(ctx, PETB200_ERR_INVALID, "rowmean_run: bad arguments");
     if (!rows)
         return PETB200_OK;
-    k_rowmean<<<grid_for(ctx, rows, 8), 256, 0, (cudaStream_t)stream>>>(x, y, rows, cols);
+    launch_pdl(k_rowmean, grid_for(ctx, rows, 8), 256, 0, (cudaStream_t)stream, x, y, rows, cols);
     return launched(ctx, "k_rowmean");
 }
 
@@ -377,10 +387,10 @@ extern "C" int petb200_softmax_run(petb200_ctx *ctx, const float *x, float *y, s
     if (!rows)
         return PETB200_OK;
     if (cols >= 256 && rows <= (size_t)ctx->sm_count * 64) {
-        k_softmax_block<<<(int)std::min<size_t>(rows, (size_t)ctx->sm_count * 8), 256, 0, (cudaStream_t)stream>>>(x, y, rows, cols);
+        launch_pdl(k_softmax_block, (int)std::min<size_t>(rows, (size_t)ctx->sm_count * 8), 256, 0, (cudaStream_t)stream, x, y, rows, cols);
         return launched(ctx, "k_softmax_block");
     }
-    k_softmax<<<grid_for(ctx, rows, 8), 256, 0, (cudaStream_t)stream>>>(x, y, rows, cols);
+    launch_pdl(k_softmax, grid_for(ctx, rows, 8), 256, 0, (cudaStream_t)stream, x, y, rows, cols);
     return launched(ctx, "k_softmax");
 }
 
@@ -391,10 +401,10 @@ extern "C" int petb200_layernorm_run(petb200_ctx *ctx, const float *x, const flo
     if (!rows)
         return PETB200_OK;
     if (cols >= 256 && rows <= (size_t)ctx->sm_count * 64) {
-        k_layernorm_block<<<(int)std::min<size_t>(rows, (size_t)ctx->sm_count * 8), 256, 0, (cudaStream_t)stream>>>(x, gamma, beta, y, rows,
+        launch_pdl(k_layernorm_block, (int)std::min<size_t>(rows, (size_t)ctx->sm_count * 8), 256, 0, (cudaStream_t)stream, x, gamma, beta, y, rows,
                                                                                                            cols, eps);
         return launched(ctx, "k_layernorm_block");
     }
-    k_layernorm<<<grid_for(ctx, rows, 8), 256, 0, (cudaStream_t)stream>>>(x, gamma, beta, y, rows, cols, eps);
+    launch_pdl(k_layernorm, grid_for(ctx, rows, 8), 256, 0, (cudaStream_t)stream, x, gamma, beta, y, rows, cols, eps);
     return launched(ctx, "k_layernorm");
 }

@@ -925,6 +925,7 @@ __global__ void __launch_bounds__(256) k_pack_conv_w(const float *__restrict__ w
 
 __global__ void __launch_bounds__(256) k_pack_mm_b(const float *__restrict__ b, float *__restrict__ hi,
                                                    float *__restrict__ lo, int bs, int n, int k, int Kpad, int transB, int rna) {
+    pdl_prologue();
     const long long total = (long long)bs * n * Kpad;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int kk = (int)(i % Kpad);
@@ -957,15 +958,6 @@ static EncodeTiledFn encode_fn() {
             fn = (EncodeTiledFn)p;
     }
     return fn;
-}
-
-static bool pdl_enabled() {
-    static int v = -1;
-    if (v < 0) {
-        const char *e = getenv("PETB200_PDL");
-        v = e ? atoi(e) : 1;
-    }
-    return v != 0;
 }
 
 struct TcCore {
@@ -1697,7 +1689,7 @@ int tc_matmul_pack_b(void *h, const float *b, cudaStream_t s) {
     TcCore &c = t->core;
     long long total = (long long)t->bs * t->n * c.Ktot;
     int blocks = (int)std::min<long long>((total + 255) / 256, (long long)c.ctx->sm_count * 16);
-    k_pack_mm_b<<<blocks, 256, 0, s>>>(b, (float *)c.whi.p, (float *)c.wlo.p, t->bs, t->n, t->k, (int)c.Ktot, t->transB, c.single_pass);
+    launch_pdl(k_pack_mm_b, blocks, 256, 0, s, b, (float *)c.whi.p, (float *)c.wlo.p, t->bs, t->n, t->k, (int)c.Ktot, t->transB, c.single_pass);
     c.weights_ready = true;
     return launched(c.ctx, "k_pack_mm_b");
 }

@@ -49,6 +49,7 @@ __device__ __forceinline__ void decode(const MapParams &p, I rem, long long &io,
 
 template <typename I>
 __global__ void __launch_bounds__(256) k_rowcopy_v4(const uint4 *__restrict__ in, uint4 *__restrict__ out, MapParams p) {
+    pdl_prologue();
     // iteration space counted in uint4 units along the innermost digit; strides of outer digits are word strides
     // divisible by 4 (checked on the host).  Four independent 128-bit loads are in flight per thread.
     const I total4 = (I)(p.total >> 2);
@@ -78,6 +79,7 @@ __global__ void __launch_bounds__(256) k_rowcopy_v4(const uint4 *__restrict__ in
 
 template <typename I>
 __global__ void __launch_bounds__(256) k_gather(const uint32_t *__restrict__ in, uint32_t *__restrict__ out, MapParams p) {
+    pdl_prologue();
     const I total = (I)p.total;
     for (I i = (I)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (I)gridDim.x * blockDim.x) {
         long long io = p.ibase, oo = p.obase;
@@ -113,6 +115,7 @@ struct TileParams {
 __device__ __forceinline__ int fast_div(int e, unsigned magic) { return (int)(((unsigned long long)e * magic) >> 22); }
 
 __global__ void __launch_bounds__(256) k_tile(const uint32_t *__restrict__ in, uint32_t *__restrict__ out, TileParams t) {
+    pdl_prologue();
     __shared__ uint32_t tile[kTileElems + kTileElems / 32]; // one pad word per 32: transposing scatters stay conflict-free
     int li[kTileEPT], lo[kTileEPT];
     uint32_t ls[kTileEPT];
@@ -515,9 +518,9 @@ static int finalize_plan(petb200_ctx *ctx, LayoutPlan *pl, std::vector<Digit> di
 
 static void launch_gather(LayoutPlan *pl, const void *in, void *out, cudaStream_t s) {
     if (pl->mp.total < (1ll << 31))
-        k_gather<unsigned><<<pl->grid_gather, 256, 0, s>>>((const uint32_t *)in, (uint32_t *)out, pl->mp);
+        launch_pdl(k_gather<unsigned>, pl->grid_gather, 256, 0, s, (const uint32_t *)in, (uint32_t *)out, pl->mp);
     else
-        k_gather<unsigned long long><<<pl->grid_gather, 256, 0, s>>>((const uint32_t *)in, (uint32_t *)out, pl->mp);
+        launch_pdl(k_gather<unsigned long long>, pl->grid_gather, 256, 0, s, (const uint32_t *)in, (uint32_t *)out, pl->mp);
 }
 
 static int layout_launch(LayoutPlan *pl, const void *in, void *out, cudaStream_t s) {
@@ -529,13 +532,13 @@ static int layout_launch(LayoutPlan *pl, const void *in, void *out, cudaStream_t
             return launched(pl->ctx, "k_gather");
         }
         if (pl->mp.total < (1ll << 31))
-            k_rowcopy_v4<unsigned><<<pl->grid, 256, 0, s>>>((const uint4 *)in, (uint4 *)out, pl->mp);
+            launch_pdl(k_rowcopy_v4<unsigned>, pl->grid, 256, 0, s, (const uint4 *)in, (uint4 *)out, pl->mp);
         else
-            k_rowcopy_v4<unsigned long long><<<pl->grid, 256, 0, s>>>((const uint4 *)in, (uint4 *)out, pl->mp);
+            launch_pdl(k_rowcopy_v4<unsigned long long>, pl->grid, 256, 0, s, (const uint4 *)in, (uint4 *)out, pl->mp);
         return launched(pl->ctx, "k_rowcopy_v4");
     }
     if (pl->mode == 1) {
-        k_tile<<<pl->grid, 256, pl->smem, s>>>((const uint32_t *)in, (uint32_t *)out, pl->tp);
+        launch_pdl(k_tile, pl->grid, 256, pl->smem, s, (const uint32_t *)in, (uint32_t *)out, pl->tp);
         return launched(pl->ctx, "k_tile");
     }
     launch_gather(pl, in, out, s);
