@@ -106,6 +106,15 @@ int petb200_conv_run_residual(petb200_plan *plan, const float *x, const float *b
  * then + bias[n], then activation (bias before activation, unlike the emitted program, which is a reference bug). */
 int petb200_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int n, int k, int has_bias, int act,
                         int algo, petb200_plan **out);
+/* The same with operands that are strided views: strides = {A batch, A row, B batch, B row, C batch, C row} in elements,
+ * the innermost dimension of each matrix contiguous ("B row" is the row stride of B as stored, [k][n] or [n][k]).  This
+ * is how an executor folds the head split/merge transposes around attention matmuls (a [seq, heads, d] tensor read as
+ * [heads, seq, d] is A batch = d, A row = heads*d) instead of running TransposeOp (ref: include/operator.h:1100-1202) as a
+ * copy.  Served by the tensor-core kernel only: PETB200_ERR_UNSUPPORTED for transposed A, k % 4 != 0 or A strides that
+ * are not multiples of 4 (the caller then keeps the copy).  A residual passed to petb200_matmul_run_residual uses the
+ * C strides. */
+int petb200_matmul_plan_strided(petb200_ctx *ctx, int transA, int transB, int b, int m, int n, int k, int has_bias, int act,
+                                int algo, const long long strides[6], petb200_plan **out);
 /* Declares B a weight: it is preprocessed once here (hoisted like the reference's weight-only operators,
  * ref: src/Graph/code_engine.cc:187-193) and petb200_matmul_run may then be called with b = NULL. */
 int petb200_matmul_set_weights(petb200_plan *plan, const float *b, petb200_stream stream);

@@ -149,6 +149,12 @@ extern "C" int petb200_matmul_plan(petb200_ctx *ctx, int transA, int transB, int
                                    int act, int algo, petb200_plan **out) {
     return make_matmul_plan(ctx, transA, transB, b, m, n, k, has_bias, act, algo, out);
 }
+extern "C" int petb200_matmul_plan_strided(petb200_ctx *ctx, int transA, int transB, int b, int m, int n, int k, int has_bias,
+                                           int act, int algo, const long long strides[6], petb200_plan **out) {
+    if (!strides)
+        return fail(ctx, PETB200_ERR_INVALID, "matmul_plan_strided: null strides");
+    return make_matmul_plan(ctx, transA, transB, b, m, n, k, has_bias, act, algo, out, strides);
+}
 extern "C" int petb200_matmul_set_weights(petb200_plan *plan, const float *b, petb200_stream s) {
     return matmul_set_weights(plan, b, (cudaStream_t)s);
 }

@@ -139,7 +139,8 @@ int conv_run(petb200_plan *plan, const float *x, const float *bias, float *y, co
 int conv_out_dims(const petb200_plan *plan, int *dims5);
 
 int make_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int n, int k, int has_bias, int act,
-                     int algo, petb200_plan **out);
+                     int algo, petb200_plan **out,
+                     const long long *strides = nullptr /*{A batch, A row, B batch, B row, C batch, C row} in elements*/);
 int matmul_set_weights(petb200_plan *plan, const float *b, cudaStream_t s);
 int matmul_run(petb200_plan *plan, const float *a, const float *b, const float *bias, float *c, cudaStream_t s,
                const float *res = nullptr /*optional residual, shaped like c*/);

@@ -17,7 +17,7 @@ void tc_conv_set_prof(void *h, long long *p);
 void tc_matmul_set_prof(void *h, long long *p);
 const char *tc_conv_variant(void *h);
 int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, int transB, int has_bias, int act, int passes,
-                     void **out, size_t *dev_bytes);
+                     const long long *strides, void **out, size_t *dev_bytes);
 int tc_matmul_native_a(void *h);
 void tc_matmul_destroy(void *h);
 int tc_matmul_pack_b(void *h, const float *b, cudaStream_t s);
@@ -437,6 +437,8 @@ struct MatmulPlan : petb200_plan {
     const float *b_weight = nullptr; // set by matmul_set_weights
     bool native_a = false;           // the kernel reads row-major A directly
     bool gemv = false;               // m <= 8: matrix-vector kernel
+    bool strided = false;            // operands/result addressed through st[] (tensor-core kernel only)
+    long long st[6] = {0, 0, 0, 0, 0, 0};
     DevBuf ba, bbm, bbias, bc;
     ~MatmulPlan() override {
         if (tc)
@@ -446,7 +448,7 @@ struct MatmulPlan : petb200_plan {
 };
 
 int make_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int n, int k, int has_bias, int act, int algo,
-                     petb200_plan **out) {
+                     petb200_plan **out, const long long *strides) {
     if (!ctx || !out)
         return PETB200_ERR_INVALID;
     if (b <= 0 || m <= 0 || n <= 0 || k <= 0)
@@ -458,7 +460,17 @@ int make_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int
     pl->transA = transA != 0, pl->transB = transB != 0, pl->bs = b, pl->m = m, pl->n = n, pl->k = k;
     pl->has_bias = has_bias, pl->act = act;
     int rc = PETB200_ERR_UNSUPPORTED;
-    if (algo == PETB200_ALGO_AUTO && m <= kGemvRows) {
+    if (strides) {
+        for (int i = 0; i < 6; ++i) {
+            if (strides[i] <= 0) {
+                delete pl;
+                return fail(ctx, PETB200_ERR_INVALID, "matmul plan: strides must be positive");
+            }
+            pl->st[i] = strides[i];
+        }
+        pl->strided = true;
+    }
+    if (algo == PETB200_ALGO_AUTO && m <= kGemvRows && !strides) {
         pl->algo = PETB200_ALGO_SIMT_FP32;
         pl->gemv = true;
         pl->kernel = "gemv_fp32";
@@ -467,8 +479,8 @@ int make_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int
     }
     if (algo == PETB200_ALGO_AUTO || algo == PETB200_ALGO_TC_3XTF32 || algo == PETB200_ALGO_TC_1XTF32) {
         size_t bytes = 0;
-        rc = tc_matmul_create(ctx, b, m, n, k, pl->transA, pl->transB, has_bias, act, algo == PETB200_ALGO_TC_1XTF32 ? 1 : 3, &pl->tc,
-                              &bytes);
+        rc = tc_matmul_create(ctx, b, m, n, k, pl->transA, pl->transB, has_bias, act, algo == PETB200_ALGO_TC_1XTF32 ? 1 : 3, strides,
+                              &pl->tc, &bytes);
         if (rc == PETB200_OK) {
             pl->algo = PETB200_ALGO_TC_3XTF32;
             pl->kernel = algo == PETB200_ALGO_TC_1XTF32 ? "tc_1xtf32_ts" : "tc_3xtf32_ts";
@@ -490,6 +502,10 @@ int make_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "matmul plan: algo %d is not built", algo);
     }
     if (rc != PETB200_OK) {
+        if (strides) {
+            delete pl;
+            return fail(ctx, PETB200_ERR_UNSUPPORTED, "strided matmul operands are served by the tensor-core kernel only");
+        }
         pl->algo = PETB200_ALGO_SIMT_FP32;
         pl->kernel = "simt_fp32";
     }
@@ -557,6 +573,11 @@ int matmul_set_weights(petb200_plan *plan, const float *b, cudaStream_t s) {
 int MatmulPlan::bench_launch(cudaStream_t s) {
     if (!ba.p) {
         size_t na = (size_t)bs * m * k, nb = (size_t)bs * k * n, nc = (size_t)bs * m * n;
+        if (strided) { // extents that cover the last addressed element
+            na = (size_t)((bs - 1) * st[0] + (m - 1) * st[1] + k);
+            nb = (size_t)((bs - 1) * st[2] + ((transB ? n : k) - 1) * st[3] + (transB ? k : n));
+            nc = (size_t)((bs - 1) * st[4] + (m - 1) * st[5] + n);
+        }
         if (ba.alloc(na * 4) != cudaSuccess || bbm.alloc(nb * 4) != cudaSuccess || bc.alloc(nc * 4) != cudaSuccess ||
             bbias.alloc((size_t)n * 4) != cudaSuccess)
             return fail(ctx, PETB200_ERR_NOMEM, "scratch allocation for timing failed");

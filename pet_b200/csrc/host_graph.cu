@@ -53,6 +53,11 @@ struct Operator {
     float eps = 1e-5f;
     int win[4] = {0, 0, 0, 0};
     bool fused_away = false; // absorbed into another step
+    // Matmul whose operands/result are strided views of other tensors (folded batch-swap transposes):
+    bool mm_strided = false;
+    long long mm_strides[6] = {0, 0, 0, 0, 0, 0};
+    int mm_in[2] = {-1, -1}; // tensor read in place of inputs[i], or -1
+    int mm_out_op = -1;      // transpose after the matmul whose output the matmul writes directly, or -1
 };
 
 // One executable step after fusion.
@@ -162,7 +167,8 @@ int petb200_graph::run_step(Step &s, cudaStream_t st) {
                                            op.win[0], op.win[1], op.win[2], op.win[3], st));
     case Matmul: {
         const bool wb = tensors[op.inputs[1]].weight;
-        return pass(petb200_matmul_run_residual(s.plan, dev_of(this, op.inputs[0]), wb ? nullptr : dev_of(this, op.inputs[1]),
+        const int ta = op.mm_in[0] >= 0 ? op.mm_in[0] : op.inputs[0], tb = op.mm_in[1] >= 0 ? op.mm_in[1] : op.inputs[1];
+        return pass(petb200_matmul_run_residual(s.plan, dev_of(this, ta), wb ? nullptr : dev_of(this, tb),
                                                 dev_of(this, op.bias), dev_of(this, s.residual), dev_of(this, ops[s.ops.back()].outputs[0]), st));
     }
     case Transpose:
@@ -301,6 +307,59 @@ int petb200_graph::compile(int flags) {
     auto is_output = [&](int t) { return std::find(outputs.begin(), outputs.end(), t) != outputs.end(); };
     auto sole_consumer = [&](int t) -> int { return (tensors[t].inputOf.size() == 1 && !is_output(t)) ? tensors[t].inputOf[0] : -1; };
 
+    // ---- fold [X,Y,Z] -> [Y,X,Z] transposes around matmuls into operand strides (BERT's head split / merge) ----
+    auto batch_swap = [&](const Operator &t) {
+        const petb200_transpose_desc &d = t.tr;
+        return t.type == Transpose && !t.fused_away && d.split < 0 && d.ngroups == 3 && d.group_sizes[0] == 1 &&
+               d.group_sizes[1] == 1 && d.group_sizes[2] == 1 && d.flat[0] == 1 && d.flat[1] == 0 && d.flat[2] == 2 &&
+               tensors[t.inputs[0]].dims.size() == 3;
+    };
+    for (int id = 0; id < n && fuse; ++id) {
+        Operator &op = ops[id];
+        op.mm_strided = false;
+        op.mm_in[0] = op.mm_in[1] = op.mm_out_op = -1;
+        if (op.type != Matmul)
+            continue;
+        const Dim &o = tensors[op.outputs[0]].dims, &x = tensors[op.inputs[0]].dims;
+        const int bsz = o[0], m = o[1], nn = o[2], k = op.transA ? x[1] : x[2];
+        long long st[6] = {(long long)m * k, op.transA ? m : k, (long long)k * nn, op.transB ? k : nn, (long long)m * nn, nn};
+        int in_t[2] = {-1, -1}, out_op = -1;
+        for (int i = 0; i < 2; ++i) {
+            const int t = op.inputs[i], prod = tensors[t].outputOf;
+            if (tensors[t].weight || prod < 0 || !batch_swap(ops[prod]) || sole_consumer(t) != id)
+                continue;
+            const Dim &src = tensors[ops[prod].inputs[0]].dims; // stored [X, Y, Z], read as [Y, X, Z]
+            st[2 * i] = src[2];
+            st[2 * i + 1] = (long long)src[1] * src[2];
+            in_t[i] = ops[prod].inputs[0];
+        }
+        const int c = sole_consumer(op.outputs[0]);
+        if (c >= 0 && batch_swap(ops[c])) { // written as [m, b, n]
+            st[4] = nn;
+            st[5] = (long long)bsz * nn;
+            out_op = c;
+        }
+        if (in_t[0] < 0 && in_t[1] < 0 && out_op < 0)
+            continue;
+        petb200_plan *trial = nullptr; // does the tensor-core kernel take these strides?
+        if (petb200_matmul_plan_strided(ctx, op.transA, op.transB, bsz, m, nn, k, op.bias >= 0, 0, PETB200_ALGO_AUTO, st, &trial) !=
+            PETB200_OK)
+            continue;
+        petb200_plan_destroy(trial);
+        op.mm_strided = true;
+        for (int i = 0; i < 6; ++i)
+            op.mm_strides[i] = st[i];
+        for (int i = 0; i < 2; ++i)
+            if (in_t[i] >= 0) {
+                op.mm_in[i] = in_t[i];
+                ops[tensors[op.inputs[i]].outputOf].fused_away = true;
+            }
+        if (out_op >= 0) {
+            op.mm_out_op = out_op;
+            ops[out_op].fused_away = true;
+        }
+    }
+
     // ---- build steps with fusion ----
     std::vector<char> emitted(n, 0); // operators already covered by a step
     for (int id : order) {
@@ -356,7 +415,14 @@ int petb200_graph::compile(int flags) {
             } else {
                 const Dim &o = tensors[op.outputs[0]].dims;
                 const int k = op.transA ? x[1] : x[2];
-                rc = petb200_matmul_plan(ctx, op.transA, op.transB, o[0], o[1], o[2], k, op.bias >= 0, act, PETB200_ALGO_AUTO, &s.plan);
+                if (op.mm_strided) {
+                    rc = petb200_matmul_plan_strided(ctx, op.transA, op.transB, o[0], o[1], o[2], k, op.bias >= 0, act, PETB200_ALGO_AUTO,
+                                                     op.mm_strides, &s.plan);
+                    if (op.mm_out_op >= 0)
+                        s.ops.push_back(op.mm_out_op); // the step's result is the transposed tensor
+                } else {
+                    rc = petb200_matmul_plan(ctx, op.transA, op.transB, o[0], o[1], o[2], k, op.bias >= 0, act, PETB200_ALGO_AUTO, &s.plan);
+                }
                 s.name = "matmul";
                 s.launches = 1 + (op.transA ? 0 : 1) + (tensors[op.inputs[1]].weight ? 0 : 1);
             }

@@ -924,7 +924,8 @@ __global__ void __launch_bounds__(256) k_pack_conv_w(const float *__restrict__ w
 }
 
 __global__ void __launch_bounds__(256) k_pack_mm_b(const float *__restrict__ b, float *__restrict__ hi,
-                                                   float *__restrict__ lo, int bs, int n, int k, int Kpad, int transB, int rna) {
+                                                   float *__restrict__ lo, int bs, int n, int k, int Kpad, int transB, int rna,
+                                                   long long sb_batch, long long sb_row) {
     pdl_prologue();
     const long long total = (long long)bs * n * Kpad;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -934,7 +935,7 @@ __global__ void __launch_bounds__(256) k_pack_mm_b(const float *__restrict__ b, 
         const int bb = (int)(row / n);
         float v = 0.f;
         if (kk < k)
-            v = transB ? __ldg(b + ((long long)bb * n + nn) * k + kk) : __ldg(b + ((long long)bb * k + kk) * n + nn);
+            v = transB ? __ldg(b + bb * sb_batch + nn * sb_row + kk) : __ldg(b + bb * sb_batch + kk * sb_row + nn);
         const float h = rna ? __uint_as_float(ptx::cvt_rna_tf32(v)) : __uint_as_float(__float_as_uint(v) & 0xffffe000u);
         hi[i] = h;
         lo[i] = v - h;
@@ -969,6 +970,7 @@ struct TcCore {
     size_t smem = 0;
     // geometry needed to (re)encode the activation map
     int xd[5]{}; // W,H,D,C,N of the activation tensor as the kernel sees it
+    long long a_row = 0, a_batch = 0; // row-major matmul A: element strides of a row and of a batch entry
     long long Ktot = 0;
     int rows_b = 0;
     DevBuf whi, wlo, koff;
@@ -993,7 +995,7 @@ struct TcCore {
             return fail(ctx, PETB200_ERR_CUDA, "cuTensorMapEncodeTiled entry point unavailable");
         if (P.a_kmajor) { // A[b][m][k] row-major: dims (k, m, b), one 128B-swizzled [128 rows][32 k] box per K stage
             cuuint64_t d3[3] = {(cuuint64_t)xd[0], (cuuint64_t)xd[1], (cuuint64_t)xd[2]};
-            cuuint64_t s3[2] = {(cuuint64_t)xd[0] * 4, (cuuint64_t)xd[0] * xd[1] * 4};
+            cuuint64_t s3[2] = {(cuuint64_t)a_row * 4, (cuuint64_t)a_batch * 4};
             cuuint32_t b3[3] = {(cuuint32_t)kStageK, (cuuint32_t)kTileM, 1};
             cuuint32_t e3[3] = {1, 1, 1};
             CUresult r3 = enc(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(x), d3, s3, b3, e3,
@@ -1543,13 +1545,16 @@ const char *tc_conv_variant(void *h) {
 // C[b,m,n] = A·B with A supplied as [b,k,m] (i.e. transA): a 1x1 "convolution" whose image is one batch entry,
 // channels = k, width = m; B is packed per call (or once, for weights) into hi/lo [b*n][Kpad].
 struct TcMatmul {
+    // element strides {A batch, A row, B batch, B row (of the stored matrix), C batch, C row}; innermost dims contiguous
+    long long st[6] = {0, 0, 0, 0, 0, 0};
     TcCore core;
     int bs, m, n, k, transB;
     bool native_a = false; // A is consumed row-major as passed (no re-layout)
 };
 
 // Row-major A ([b][m][k], k % 4 == 0): the kernel's K-major mode, no re-layout of A.
-static int tc_configure_kmajor(petb200_ctx *ctx, TcCore &core, int bs, int m, int n, int k, int has_bias, int act) {
+static int tc_configure_kmajor(petb200_ctx *ctx, TcCore &core, int bs, int m, int n, int k, int has_bias, int act,
+                               const long long *st) {
     IgemmParams &P = core.P;
     memset(&P, 0, sizeof P);
     core.a_tmem = true;
@@ -1562,7 +1567,8 @@ static int tc_configure_kmajor(petb200_ctx *ctx, TcCore &core, int bs, int m, in
     P.BC = kStageK, P.spc = 1, P.nchunks = (k + kStageK - 1) / kStageK;
     P.RN = P.RD = 1, P.RH = kTileM, P.RW = kStageK;
     P.raw_bytes = kAHalfBytes;
-    P.ys_n = (long long)m * n, P.ys_f = 1, P.ys_p = n;
+    P.ys_n = st[4], P.ys_f = 1, P.ys_p = st[5];
+    core.a_batch = st[0], core.a_row = st[1];
     P.has_bias = has_bias, P.act = act;
     P.NA = 4;
     const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 1024;
@@ -1619,7 +1625,7 @@ static int tc_configure_kmajor(petb200_ctx *ctx, TcCore &core, int bs, int m, in
 }
 
 int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, int transB, int has_bias, int act, int passes,
-                     void **out, size_t *dev_bytes) {
+                     const long long *strides, void **out, size_t *dev_bytes) {
     const int mp = (m + 3) / 4 * 4; // row pitch of A as [b][k][mp]
     if (ctx->cc_major != 10)
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "tcgen05 kernels need compute capability 10.x");
@@ -1631,10 +1637,16 @@ int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, 
     t->transB = transB;
     t->core.ctx = ctx;
     t->core.single_pass = passes == 1;
+    const long long dense[6] = {(long long)m * k, transA ? m : k, (long long)k * n, transB ? k : n, (long long)m * n, n};
+    for (int i = 0; i < 6; ++i)
+        t->st[i] = strides ? strides[i] : dense[i];
     int rc;
-    if (!transA && k % 4 == 0 && env_int("PETB200_TC_KMAJOR", 1)) {
-        rc = tc_configure_kmajor(ctx, t->core, bs, m, n, k, has_bias, act);
+    if (!transA && k % 4 == 0 && t->st[0] % 4 == 0 && t->st[1] % 4 == 0 && env_int("PETB200_TC_KMAJOR", 1)) {
+        rc = tc_configure_kmajor(ctx, t->core, bs, m, n, k, has_bias, act, t->st);
         t->native_a = true;
+    } else if (strides) {
+        delete t;
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "strided matmul operands need row-major A with k and the A strides multiples of 4");
     } else {
         ConvGeom g{};
         g.N = bs;
@@ -1689,7 +1701,8 @@ int tc_matmul_pack_b(void *h, const float *b, cudaStream_t s) {
     TcCore &c = t->core;
     long long total = (long long)t->bs * t->n * c.Ktot;
     int blocks = (int)std::min<long long>((total + 255) / 256, (long long)c.ctx->sm_count * 16);
-    launch_pdl(k_pack_mm_b, blocks, 256, 0, s, b, (float *)c.whi.p, (float *)c.wlo.p, t->bs, t->n, t->k, (int)c.Ktot, t->transB, c.single_pass);
+    launch_pdl(k_pack_mm_b, blocks, 256, 0, s, b, (float *)c.whi.p, (float *)c.wlo.p, t->bs, t->n, t->k, (int)c.Ktot, t->transB, c.single_pass,
+               t->st[2], t->st[3]);
     c.weights_ready = true;
     return launched(c.ctx, "k_pack_mm_b");
 }

@@ -42,6 +42,7 @@ SYMBOLS = {
     "petb200_conv3d_run": (_i, [_vp, _vp, _vp, _vp, _vp]),
     "petb200_conv_run_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "petb200_matmul_plan": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, C.POINTER(_vp)]),
+    "petb200_matmul_plan_strided": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, C.POINTER(C.c_longlong), C.POINTER(_vp)]),
     "petb200_matmul_set_weights": (_i, [_vp, _vp, _vp]),
     "petb200_matmul_run": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "petb200_matmul_run_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp]),

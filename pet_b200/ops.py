@@ -157,7 +157,9 @@ class Context:
         return y
 
     # ---- matmul --------------------------------------------------------------------------------------------
-    def matmul_plan(self, ashape, bshape, transA=False, transB=False, bias=False, act="none", algo="auto"):
+    def matmul_plan(self, ashape, bshape, transA=False, transB=False, bias=False, act="none", algo="auto", strides=None):
+        """strides: optional (A batch, A row, B batch, B row, C batch, C row) in elements for operands that are strided
+        views (the logical shapes stay ashape/bshape); the result then has to be passed in through `out`."""
         if len(ashape) != 3 or len(bshape) != 3 or ashape[0] != bshape[0]:
             raise L.PetError(L.ERR_INVALID, "matmul operands must be 3-D with equal batch")  # MatmulOp::checkValid
         b = ashape[0]
@@ -166,8 +168,13 @@ class Context:
         if k != k2:
             raise L.PetError(L.ERR_INVALID, "matmul inner extents differ")
         h_ = C.c_void_p()
-        self.check(self.lib.petb200_matmul_plan(self.h, int(transA), int(transB), b, m, n, k, int(bool(bias)), L.ACT[act],
-                                                L.ALGO[algo], C.byref(h_)))
+        if strides is not None:
+            st = (C.c_longlong * 6)(*[int(v) for v in strides])
+            self.check(self.lib.petb200_matmul_plan_strided(self.h, int(transA), int(transB), b, m, n, k, int(bool(bias)),
+                                                            L.ACT[act], L.ALGO[algo], st, C.byref(h_)))
+        else:
+            self.check(self.lib.petb200_matmul_plan(self.h, int(transA), int(transB), b, m, n, k, int(bool(bias)), L.ACT[act],
+                                                    L.ALGO[algo], C.byref(h_)))
         p = Plan(self, h_)
         p.out_shape = (b, m, n)
         return p

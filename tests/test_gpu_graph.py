@@ -80,10 +80,16 @@ def test_resnet18_reduced(ctx):
 def test_bert_reduced(ctx):
     from pet_b200 import configs
     kw = dict(layers=2, seq=32, hidden=64, heads=4, ffn=128)
-    _, _, y = run_config(ctx, configs.bert_encoder, **kw)
+    g, _, y = run_config(ctx, configs.bert_encoder, **kw)
     want = oracle_config(configs.bert_encoder, **kw)
     assert y.shape == want.shape == (1, 32, 64)
     assert rel_err(y, want) <= TOL
+    names = [n for n, _ in g.steps()]
+    # head split / merge transposes became operand strides of the attention matmuls, residual adds went into epilogues
+    assert "transpose" not in names and "add" not in names
+    g2, _, y2 = run_config(ctx, configs.bert_encoder, fuse=False, cuda_graph=False, **kw)
+    assert [n for n, _ in g2.steps()].count("transpose") == 8
+    assert np.array_equal(y, y2)
 
 
 def test_r3d18_reduced(ctx):

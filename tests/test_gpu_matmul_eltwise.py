@@ -65,6 +65,29 @@ def test_matmul_with_residual_equals_matmul_then_add(ctx, shape):
     assert torch.equal(got, want)
 
 
+def test_strided_matmul_equals_matmul_on_transposed_copies(ctx):
+    """Attention with the head split/merge folded into operand strides: q, k, v stored as [seq, heads, d]."""
+    seq, heads, d = 128, 12, 64
+    rng = np.random.default_rng(7)
+    q, k, v = (dev(rng.standard_normal((seq, heads, d)).astype(np.float32)) for _ in range(3))
+    qh, kh, vh = (t.permute(1, 0, 2).contiguous() for t in (q, k, v))                      # [heads, seq, d] copies
+    hd = heads * d
+    # scores[h] = q[h] . k[h]^T : A and B (stored [n][k]) are strided views, C dense [heads, seq, seq]
+    p1 = ctx.matmul_plan((heads, seq, d), (heads, seq, d), transB=True, strides=(d, hd, d, hd, seq * seq, seq))
+    s = torch.empty((heads, seq, seq), device="cuda")
+    ctx.matmul_run(p1, q, k, out=s)
+    assert torch.equal(s, ctx.matmul(qh, kh, transB=True))
+    # ctx[h] = s[h] . v[h], written straight into [seq, heads, d]
+    p2 = ctx.matmul_plan((heads, seq, seq), (heads, seq, d), strides=(seq * seq, seq, d, hd, d, hd))
+    c = torch.empty((seq, heads, d), device="cuda")
+    ctx.matmul_run(p2, s, v, out=c)
+    assert torch.equal(c, ctx.matmul(s, vh).permute(1, 0, 2).contiguous())
+    ctx.sync_check()
+    from pet_b200 import PetError
+    with pytest.raises(PetError):  # A strides that TMA cannot express: the caller keeps the copy
+        ctx.matmul_plan((2, 16, 8), (2, 8, 8), strides=(130, 10, 64, 8, 128, 8))
+
+
 def test_matmul_rejects_mismatched_operands(ctx):
     from pet_b200 import PetError
     with pytest.raises(PetError):
