@@ -158,6 +158,9 @@ def config_latencies(ctx):
 def run_reference(args, rank, world):
     if rank != 0:
         return
+    # rank 0 alone runs the host arm, with all host threads: torchrun presets OMP_NUM_THREADS=1 for its workers
+    if world > 1:
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     vals, info = [], None
     for i in range(args.warmup + args.steps):
         v, info = cpu_reference_sample(8)
