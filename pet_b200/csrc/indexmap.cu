@@ -241,6 +241,142 @@ __global__ void __launch_bounds__(256) k_tile(const uint32_t *__restrict__ in, u
     }
 }
 
+// The same tile kernel with 16-byte global accesses on the side(s) whose contiguous run allows it (VI: four consecutive
+// input words per load, VO: four consecutive output words per store; host-checked: run lengths and every other stride
+// multiples of 4, no ragged chunk).  Shared memory stays word-addressed (one pad word per 32), so the in-tile permutation
+// is unchanged; a quarter of the global-memory instructions remain.
+template <bool VI, bool VO>
+__global__ void __launch_bounds__(256) k_tile_v4(const uint32_t *__restrict__ in, uint32_t *__restrict__ out, TileParams t) {
+    pdl_prologue();
+    __shared__ uint32_t tile[kTileElems + kTileElems / 32];
+    constexpr int NI = VI ? kTileEPT / 4 : kTileEPT, NO = VO ? kTileEPT / 4 : kTileEPT;
+    constexpr int WI = VI ? 4 : 1, WO = VO ? 4 : 1;
+    int li[NI], lo[NO], ls[NI];
+    int svin = 0; // shared-memory stride of the input-contiguous digit
+    {
+        int sstride[kMaxTileDigits];
+        int acc = 1;
+#pragma unroll
+        for (int k = kMaxTileDigits - 1; k >= 0; --k)
+            if (k < t.nt) {
+                sstride[k] = acc;
+                acc *= t.text[k];
+            }
+#pragma unroll
+        for (int k = 0; k < kMaxTileDigits; ++k)
+            if (k == t.read_order[0])
+                svin = sstride[k];
+#pragma unroll
+        for (int u = 0; u < NO; ++u) {
+            int rem = (threadIdx.x + u * 256) * WO, off_o = 0;
+#pragma unroll
+            for (int k = kMaxTileDigits - 1; k >= 0; --k)
+                if (k < t.nt) {
+                    const int q = fast_div(rem, t.tmagic[k]);
+                    off_o += (rem - q * t.text[k]) * t.tostr[k];
+                    rem = q;
+                }
+            lo[u] = off_o;
+        }
+#pragma unroll
+        for (int u = 0; u < NI; ++u) {
+            int rem = (threadIdx.x + u * 256) * WI, off_i = 0, sidx = 0;
+#pragma unroll
+            for (int q = 0; q < kMaxTileDigits; ++q)
+                if (q < t.nt) {
+                    const int k = t.read_order[q];
+                    const int d = fast_div(rem, t.tmagic[k]);
+                    const int c = rem - d * t.text[k];
+                    rem = d;
+                    off_i += c * t.tistr[k];
+                    sidx += c * sstride[k];
+                }
+            li[u] = off_i;
+            ls[u] = sidx;
+        }
+    }
+    const unsigned ntiles = (unsigned)t.m.total;
+    const unsigned per = (ntiles + gridDim.x - 1) / gridDim.x;
+    const unsigned first = blockIdx.x * per;
+    const unsigned last = min(first + per, ntiles);
+    if (first >= last)
+        return;
+    int idx[kMaxDigits];
+    long long io = t.m.ibase, oo = t.m.obase;
+    {
+        unsigned rem = first;
+#pragma unroll
+        for (int d = kMaxDigits - 1; d >= 0; --d) {
+            idx[d] = 0;
+            if (d < t.m.nd) {
+                const unsigned q = rem / (unsigned)t.m.ext[d];
+                idx[d] = (int)(rem - q * (unsigned)t.m.ext[d]);
+                rem = q;
+                io += idx[d] * t.m.istr[d];
+                oo += idx[d] * t.m.ostr[d];
+            }
+        }
+    }
+    uint32_t v[kTileEPT];
+    auto load_tile = [&](const uint32_t *ip) {
+#pragma unroll
+        for (int u = 0; u < NI; ++u)
+            if ((threadIdx.x + u * 256) * WI < t.tile_elems) {
+                if (VI) {
+                    const uint4 q = __ldg(reinterpret_cast<const uint4 *>(ip + li[u]));
+                    v[4 * u] = q.x, v[4 * u + 1] = q.y, v[4 * u + 2] = q.z, v[4 * u + 3] = q.w;
+                } else {
+                    v[u] = __ldg(ip + li[u]);
+                }
+            }
+    };
+    load_tile(in + io);
+    for (unsigned blk = first; blk < last; ++blk) {
+#pragma unroll
+        for (int u = 0; u < NI; ++u)
+            if ((threadIdx.x + u * 256) * WI < t.tile_elems) {
+#pragma unroll
+                for (int j = 0; j < WI; ++j) {
+                    const int sdx = ls[u] + j * svin;
+                    tile[sdx + (sdx >> 5)] = v[WI * u + j];
+                }
+            }
+        __syncthreads();
+        uint32_t *op = out + oo;
+        bool carry = true; // odometer: next tile
+#pragma unroll
+        for (int d = kMaxDigits - 1; d >= 0; --d)
+            if (d < t.m.nd && carry) {
+                if (++idx[d] < t.m.ext[d]) {
+                    io += t.m.istr[d];
+                    oo += t.m.ostr[d];
+                    carry = false;
+                } else {
+                    io -= (long long)(t.m.ext[d] - 1) * t.m.istr[d];
+                    oo -= (long long)(t.m.ext[d] - 1) * t.m.ostr[d];
+                    idx[d] = 0;
+                }
+            }
+        if (blk + 1 < last) // the next tile's loads stay in flight during the store phase
+            load_tile(in + io);
+#pragma unroll
+        for (int u = 0; u < NO; ++u) {
+            const int e = (threadIdx.x + u * 256) * WO;
+            if (e < t.tile_elems) {
+                if (VO) {
+                    uint4 q;
+                    q.x = tile[e + (e >> 5)], q.y = tile[e + 1 + ((e + 1) >> 5)];
+                    q.z = tile[e + 2 + ((e + 2) >> 5)], q.w = tile[e + 3 + ((e + 3) >> 5)];
+                    *reinterpret_cast<uint4 *>(op + lo[u]) = q;
+                } else {
+                    op[lo[u]] = tile[e + (e >> 5)];
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // host-side lowering
 // ---------------------------------------------------------------------------------------------------------
@@ -253,6 +389,7 @@ using DigitList = std::vector<Digit>;
 
 struct LayoutPlan : petb200_plan {
     int mode = 0; // 0 rowcopy, 1 tile, 2 gather
+    bool tile_vi = false, tile_vo = false; // tile mode: 16-byte global loads / stores are possible
     MapParams mp{};
     TileParams tp{};
     int out_nd = 0;
@@ -502,6 +639,23 @@ static int finalize_plan(petb200_ctx *ctx, LayoutPlan *pl, std::vector<Digit> di
                 ++k;
             }
             t.m.nd = k;
+            // 16-byte global accesses where the contiguous run and every other stride allow them
+            {
+                const bool whole_chunks = t.ck < 0 || t.chunk_ext % t.text[t.ck] == 0;
+                const int kin = t.read_order[0], kout = t.nt - 1;
+                bool vi = whole_chunks && t.tile_elems % 4 == 0 && t.tistr[kin] == 1 && t.text[kin] % 4 == 0 && t.m.ibase % 4 == 0;
+                bool vo = whole_chunks && t.tile_elems % 4 == 0 && t.tostr[kout] == 1 && t.text[kout] % 4 == 0 && t.m.obase % 4 == 0;
+                for (int q = 0; q < t.nt; ++q) {
+                    vi = vi && (q == kin || t.tistr[q] % 4 == 0);
+                    vo = vo && (q == kout || t.tostr[q] % 4 == 0);
+                }
+                for (int d = 0; d < t.m.nd; ++d) {
+                    vi = vi && t.m.istr[d] % 4 == 0;
+                    vo = vo && t.m.ostr[d] % 4 == 0;
+                }
+                pl->tile_vi = vi;
+                pl->tile_vo = vo;
+            }
             pl->mode = 1;
             pl->kernel = "tile";
             pl->smem = 0;
@@ -538,7 +692,17 @@ static int layout_launch(LayoutPlan *pl, const void *in, void *out, cudaStream_t
         return launched(pl->ctx, "k_rowcopy_v4");
     }
     if (pl->mode == 1) {
-        launch_pdl(k_tile, pl->grid, 256, pl->smem, s, (const uint32_t *)in, (uint32_t *)out, pl->tp);
+        const bool vi = pl->tile_vi && (((uintptr_t)in) & 15) == 0, vo = pl->tile_vo && (((uintptr_t)out) & 15) == 0;
+        const uint32_t *ip = (const uint32_t *)in;
+        uint32_t *op = (uint32_t *)out;
+        if (vi && vo)
+            launch_pdl(k_tile_v4<true, true>, pl->grid, 256, pl->smem, s, ip, op, pl->tp);
+        else if (vi)
+            launch_pdl(k_tile_v4<true, false>, pl->grid, 256, pl->smem, s, ip, op, pl->tp);
+        else if (vo)
+            launch_pdl(k_tile_v4<false, true>, pl->grid, 256, pl->smem, s, ip, op, pl->tp);
+        else
+            launch_pdl(k_tile, pl->grid, 256, pl->smem, s, ip, op, pl->tp);
         return launched(pl->ctx, "k_tile");
     }
     launch_gather(pl, in, out, s);
