@@ -47,19 +47,20 @@ __device__ __forceinline__ void decode(const MapParams &p, I rem, long long &io,
     }
 }
 
+constexpr int kRowU = 4;
 template <typename I>
 __global__ void __launch_bounds__(256) k_rowcopy_v4(const uint4 *__restrict__ in, uint4 *__restrict__ out, MapParams p) {
     pdl_prologue();
     // iteration space counted in uint4 units along the innermost digit; strides of outer digits are word strides
-    // divisible by 4 (checked on the host).  Four independent 128-bit loads are in flight per thread.
+    // divisible by 4 (checked on the host).  kRowU independent 128-bit loads are in flight per thread.
     const I total4 = (I)(p.total >> 2);
     const I inner4 = (I)(p.ext[p.nd - 1] >> 2);
     const I step = (I)gridDim.x * blockDim.x;
-    for (I i0 = (I)blockIdx.x * blockDim.x + threadIdx.x; i0 < total4; i0 += 4 * step) {
-        uint4 v[4];
-        long long oo[4];
+    for (I i0 = (I)blockIdx.x * blockDim.x + threadIdx.x; i0 < total4; i0 += kRowU * step) {
+        uint4 v[kRowU];
+        long long oo[kRowU];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kRowU; ++u) {
             const I i = i0 + (I)u * step;
             if (i < total4) {
                 const I row = i / inner4;
@@ -71,7 +72,7 @@ __global__ void __launch_bounds__(256) k_rowcopy_v4(const uint4 *__restrict__ in
             }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < kRowU; ++u)
             if (i0 + (I)u * step < total4)
                 out[oo[u] >> 2] = v[u];
     }
