@@ -1206,7 +1206,7 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     if (!z_is_batch && 2 * P.Pw <= kTileM) {
         const int cap = kTileM / P.Pw;
         if (g.OD == 1) {
-            P.ipt = cap;
+            P.ipt = std::min(cap, P.units); // no more images per tile than there are
         } else {
             for (int d = std::min(cap, g.OD); d >= 1; --d)
                 if (g.OD % d == 0) {

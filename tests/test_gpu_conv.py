@@ -169,6 +169,63 @@ def test_conv3d_vs_oracle(ctx, oracle):
             assert rel_err(got, want) <= TOL and scale_err(got, want) <= TOL_SCALE
 
 
+MODE_CASES = [
+    # raw-tile and reduction modes of the tensor-core kernel: (name, x, w, pad, stride, dil, act)
+    ("flat_grouped_7", (2, 64, 7, 7), (64, 32, 3, 3), (1, 1), (1, 1), (1, 1), "tanh"),          # whole-plane tiles, 2 groups
+    ("flat_dilated_14", (1, 128, 14, 14), (128, 128, 3, 3), (2, 2), (1, 1), (2, 2), "sigmoid"), # tap mask with dilation
+    ("flat_stride2_14", (1, 64, 14, 14), (128, 64, 3, 3), (1, 1), (2, 2), (1, 1), "gelu"),
+    ("flat_1x1_7", (4, 256, 7, 7), (512, 256, 1, 1), (0, 0), (1, 1), (1, 1), "relu"),           # chunks of 128 channels
+    ("flat_small_chunk", (1, 20, 6, 6), (24, 20, 3, 3), (1, 1), (1, 1), (1, 1), "none"),         # table gather (BC < 32)
+    ("cluster_8", (1, 512, 7, 7), (512, 512, 3, 3), (1, 1), (1, 1), (1, 1), "relu"),            # K split over 8 CTAs
+    ("cluster_bias_act", (1, 256, 28, 28), (96, 256, 3, 3), (1, 1), (1, 1), (1, 1), "sigmoid"),  # ragged filter count
+    ("odd_width_repitch", (1, 8, 30, 150), (16, 8, 3, 3), (1, 1), (1, 1), (1, 1), "none"),       # rows too wide for flat tiles
+]
+
+
+@pytest.mark.parametrize("case", MODE_CASES, ids=[c[0] for c in MODE_CASES])
+def test_conv_kernel_modes_vs_oracle(ctx, oracle, case):
+    name, xs, ws, pad, st, dil, act = case
+    rng = np.random.default_rng(len(name) * 131 + xs[1])
+    x = rng.uniform(-1, 1, xs).astype(np.float32)
+    w = (rng.standard_normal(ws) * np.sqrt(2.0 / (ws[1] * ws[2] * ws[3]))).astype(np.float32)
+    b = rng.uniform(-1, 1, ws[0]).astype(np.float32)
+    want = oracle.conv2d(x, w, b, pad=pad, stride=st, dil=dil, act=act, wide=True)
+    got = ctx.conv2d(dev(x), dev(w), pad[0], pad[1], st[0], st[1], dil[0], dil[1], bias=dev(b), act=act).cpu().numpy()
+    ctx.sync_check()
+    assert got.shape == want.shape
+    assert rel_err(got, want) <= TOL and scale_err(got, want) <= TOL_SCALE
+    exact = ctx.conv2d(dev(x), dev(w), pad[0], pad[1], st[0], st[1], dil[0], dil[1], bias=dev(b), act=act, algo="simt_fp32")
+    assert rel_err(got, exact.cpu().numpy()) <= TOL  # and against the CUDA-core fp32 kernel
+
+
+def test_conv3d_small_planes_vs_oracle(ctx, oracle):
+    """3-D layers whose rows are not 16-byte multiples (the last stages of ResNet3D): flat raw tiles over all depth slices."""
+    rng = np.random.default_rng(35)
+    for xs, ws, pad, st in [((1, 64, 2, 7, 7), (64, 64, 3, 3, 3), (1, 1, 1), (1, 1, 1)),
+                            ((1, 32, 4, 14, 14), (48, 32, 3, 3, 3), (1, 1, 1), (1, 1, 1)),
+                            ((2, 32, 4, 14, 14), (64, 32, 1, 1, 1), (0, 0, 0), (2, 2, 2))]:
+        x = rng.standard_normal(xs).astype(np.float32)
+        w = (rng.standard_normal(ws) * np.sqrt(2.0 / np.prod(ws[1:]))).astype(np.float32)
+        want = oracle.conv3d(x, w, pad=pad, stride=st, wide=True)
+        got = ctx.conv3d(dev(x), dev(w), pad, st).cpu().numpy()
+        ctx.sync_check()
+        assert got.shape == want.shape
+        assert rel_err(got, want) <= TOL and scale_err(got, want) <= TOL_SCALE
+
+
+def test_correction_window_on_a_flat_plan_is_bit_identical(ctx):
+    x = torch.randn((1, 64, 14, 14), device="cuda")
+    w = torch.randn((64, 64, 3, 3), device="cuda") * 0.05
+    plan = ctx.conv2d_plan(x.shape, w.shape, 1, 1)
+    ctx.conv2d_set_weights(plan, w)
+    whole = ctx.conv2d_run(plan, x)
+    y = whole.clone()
+    y[:, :, 6:8, :] = 3.0
+    ctx.conv2d_correct(plan, x, y, 6, 2)
+    ctx.sync_check()
+    assert torch.equal(y, whole)
+
+
 def test_invalid_conv_arguments(ctx):
     from pet_b200 import PetError
     with pytest.raises(PetError) as e:
