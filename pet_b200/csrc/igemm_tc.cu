@@ -131,7 +131,7 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile
         return;
     ptx::tmem_ld_32x32(tacc + (uint32_t)col0, nx);
     if (PASSES == 3)
-        ptx::tmem_ld_32x32(tacc + 128u + (uint32_t)col0, sm);
+        ptx::tmem_ld_32x32(tacc + (uint32_t)BN + (uint32_t)col0, sm);
     for (int cc = col0; cc < col1; cc += 32) {
         ptx::tmem_ld_wait();
 #pragma unroll
@@ -140,7 +140,7 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile
         if (cc + 32 < col1) { // in flight while this chunk is stored
             ptx::tmem_ld_32x32(tacc + (uint32_t)(cc + 32), nx);
             if (PASSES == 3)
-                ptx::tmem_ld_32x32(tacc + 128u + (uint32_t)(cc + 32), sm);
+                ptx::tmem_ld_32x32(tacc + (uint32_t)BN + (uint32_t)(cc + 32), sm);
         }
         if (split_addr != 0u) {
             // Split-K: column c of the tile is summed by CTA c / cols of the cluster.  Push this CTA's partial sum into
@@ -521,11 +521,16 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         // The whole warp runs this loop with uniform control flow and only the tcgen05 instructions sit under
         // elect_one: descriptors and TMEM addresses then live in uniform registers.  (With the loop confined to one
         // lane the same instruction stream was issue-bound: 94 instead of 64 cycles per 128x128x8 MMA.)
+        // 3xTF32 with two MMAs per K=8 step instead of three: the hi and lo filter tiles of a stage are adjacent in shared
+        // memory, i.e. one K-major tile of 2*BN rows, so  A_hi x [B_hi ; B_lo]  is ONE MMA of width 2*BN whose result columns
+        // [0,BN) are the main accumulator and [BN,2BN) the accumulator of the cross terms; A_lo x B_hi then adds to the
+        // latter.  Same tensor-pipe work, a third fewer instructions from the warp that every stage waits for.
         const uint32_t idesc = ptx::idesc_tf32(kTileM, P.BN);
+        const uint32_t idesc_wide = ptx::idesc_tf32(kTileM, 2 * P.BN);
         const uint64_t bdesc0 = ptx::smem_desc_k128(ptx::smem_u32(sB));
         const uint64_t adesc0 = A_TMEM ? 0ull : ptx::smem_desc_k128(ptx::smem_u32(sA));
         const uint32_t b_half16 = b_half >> 4;
-        const uint32_t tmem_small = tmem_base + 128u;
+        const uint32_t tmem_small = tmem_base + (uint32_t)P.BN;
         uint32_t accumulate = 0;
         int sa = 0, sb = 0, prev_sa = -1, prev_sb = -1;
         uint32_t pa = 0, pb = 0;
@@ -550,7 +555,6 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 break;
             ptx::tc_fence_after();
             const uint64_t bhi = bdesc0 + (uint64_t)((uint32_t)sb * 2u * b_half16);
-            const uint64_t blo = bhi + b_half16;
             const uint32_t ahi_t = tmem_base + 256u + (uint32_t)sa * 64u, alo_t = ahi_t + 32u;
             const uint64_t ahi_s = adesc0 + (uint64_t)((uint32_t)sa * 2u * (kAHalfBytes >> 4));
             const uint64_t alo_s = ahi_s + (kAHalfBytes >> 4);
@@ -565,71 +569,40 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 nsb = 0;
                 npb ^= 1u;
             }
+            // one K=8 step.  The cross terms have their own accumulator: the tensor core truncates (rounds toward zero) its
+            // accumulator after every MMA, a bias proportional to the accumulator's magnitude; keeping the small terms
+            // away from the big sum removes most of those truncations from it.
+            auto issue_step = [&](int kk) {
+                const uint32_t acc_kk = kk == 0 ? accumulate : 1u;
+                if (PASSES == 3) {
+                    if (A_TMEM)
+                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc_wide, acc_kk);
+                    else
+                        ptx::mma_tf32_ss(tmem_base, ahi_s + 2 * kk, bhi + 2 * kk, idesc_wide, acc_kk);
+                } else {
+                    ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, acc_kk); // single TF32 pass
+                }
+                if (kk == 0 && prev_sa >= 0) { // release the previous stage once this stage's first MMA is queued
+                    ptx::mma_commit(a_empty + prev_sa);
+                    ptx::mma_commit(b_empty + prev_sb);
+                }
+                if (PASSES == 3) {
+                    if (A_TMEM)
+                        ptx::mma_tf32_ts(tmem_small, alo_t + kk * 8, bhi + 2 * kk, idesc, 1u);
+                    else
+                        ptx::mma_tf32_ss(tmem_small, alo_s + 2 * kk, bhi + 2 * kk, idesc, 1u);
+                }
+            };
             if (ptx::elect_one()) {
 #pragma unroll
-                for (int kk = 0; kk < 3; ++kk) {
-                    const uint32_t acc_kk = kk == 0 ? accumulate : 1u;
-                    // The two cross terms go to their own accumulator: the tensor core truncates (rounds toward zero) its
-                    // accumulator after every MMA, a bias proportional to the accumulator's magnitude; keeping the small
-                    // terms away from the big sum removes two thirds of those truncations from it.
-                    if (PASSES == 3) {
-                        if (A_TMEM) {
-                            ptx::mma_tf32_ts(tmem_small, alo_t + kk * 8, bhi + 2 * kk, idesc, acc_kk);
-                        } else {
-                            ptx::mma_tf32_ss(tmem_small, alo_s + 2 * kk, bhi + 2 * kk, idesc, acc_kk);
-                        }
-                    } else {
-                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, acc_kk); // single TF32 pass
-                    }
-                    if (kk == 0 && prev_sa >= 0) { // release the previous stage once this stage's first MMA is queued
-                        ptx::mma_commit(a_empty + prev_sa);
-                        ptx::mma_commit(b_empty + prev_sb);
-                    }
-                    if (PASSES != 3) {
-                        // nothing more for a single pass
-                    } else if (A_TMEM) {
-                        ptx::mma_tf32_ts(tmem_small, ahi_t + kk * 8, blo + 2 * kk, idesc, 1u);
-                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, acc_kk);
-                    } else {
-                        ptx::mma_tf32_ss(tmem_small, ahi_s + 2 * kk, blo + 2 * kk, idesc, 1u);
-                        ptx::mma_tf32_ss(tmem_base, ahi_s + 2 * kk, bhi + 2 * kk, idesc, acc_kk);
-                    }
-                }
+                for (int kk = 0; kk < 3; ++kk)
+                    issue_step(kk);
             }
             __syncwarp();
             ready_next = (ks + 1 < KS) && ptx::mbar_try_wait(a_full + nsa, npa) && ptx::mbar_try_wait(b_full + nsb, npb);
             ready_next = __all_sync(0xffffffffu, ready_next);
-            if (ptx::elect_one()) {
-                {
-                    const int kk = 3;
-                    const uint32_t acc_kk = 1u;
-                    // The two cross terms go to their own accumulator: the tensor core truncates (rounds toward zero) its
-                    // accumulator after every MMA, a bias proportional to the accumulator's magnitude; keeping the small
-                    // terms away from the big sum removes two thirds of those truncations from it.
-                    if (PASSES == 3) {
-                        if (A_TMEM) {
-                            ptx::mma_tf32_ts(tmem_small, alo_t + kk * 8, bhi + 2 * kk, idesc, acc_kk);
-                        } else {
-                            ptx::mma_tf32_ss(tmem_small, alo_s + 2 * kk, bhi + 2 * kk, idesc, acc_kk);
-                        }
-                    } else {
-                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, acc_kk); // single TF32 pass
-                    }
-                    if (kk == 0 && prev_sa >= 0) { // release the previous stage once this stage's first MMA is queued
-                        ptx::mma_commit(a_empty + prev_sa);
-                        ptx::mma_commit(b_empty + prev_sb);
-                    }
-                    if (PASSES != 3) {
-                        // nothing more for a single pass
-                    } else if (A_TMEM) {
-                        ptx::mma_tf32_ts(tmem_small, ahi_t + kk * 8, blo + 2 * kk, idesc, 1u);
-                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, acc_kk);
-                    } else {
-                        ptx::mma_tf32_ss(tmem_small, ahi_s + 2 * kk, blo + 2 * kk, idesc, 1u);
-                        ptx::mma_tf32_ss(tmem_base, ahi_s + 2 * kk, bhi + 2 * kk, idesc, acc_kk);
-                    }
-                }
-            }
+            if (ptx::elect_one())
+                issue_step(3);
             __syncwarp();
             accumulate = 1u;
             if (ready_next) {
