@@ -599,7 +599,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                     issue_step(kk);
             }
             __syncwarp();
-            ready_next = (ks + 1 < KS) && ptx::mbar_try_wait(a_full + nsa, npa) && ptx::mbar_try_wait(b_full + nsb, npb);
+            ready_next = (ks + 1 < KS) && ptx::mbar_test_wait(a_full + nsa, npa) && ptx::mbar_test_wait(b_full + nsb, npb);
             ready_next = __all_sync(0xffffffffu, ready_next);
             if (ptx::elect_one())
                 issue_step(3);
