@@ -155,6 +155,31 @@ def config_latencies(ctx):
     return out
 
 
+def model_throughput(ctx, world, dev):
+    """Images/s of ResNet-18 (global batch 64) and ResNet3D-18 (global batch 32) with the batch sharded into independent
+    replicas, one per GPU, no collective: every rank runs global_batch / world images through its own captured graph;
+    the job's time is the slowest rank's (device events, max over ranks)."""
+    import torch
+    from pet_b200 import configs
+    from pet_b200.graph import Graph
+    out = {}
+    for name, build, gb in (("c3_resnet18", configs.resnet18, 64), ("c5_r3d18", configs.r3d18, 32)):
+        per = max(1, gb // world)
+        g = Graph(ctx)
+        b = configs.GraphBuilder(g)
+        g.setOutputs([build(b, batch=per)])
+        g.compile()
+        b.load()
+        g.run()
+        torch.cuda.synchronize()
+        ms = g.time(rounds=20, warmup=3)
+        (ms,) = max_over_ranks([ms], world, dev)
+        out[name] = {"global_batch": per * world, "per_gpu_batch": per, "ms": ms, "images_per_s": per * world * 1000.0 / ms,
+                     "kernels": g.num_launches(), "scaling": "strong"}
+        del g, b
+    return out
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
@@ -298,6 +323,7 @@ def main():
 
     # ---- max over ranks ----
     ms_total, e2e_ms, conv_ms = max_over_ranks([ms_total, e2e_ms, conv_ms], world, dev)
+    models = None if args.no_config_latencies else model_throughput(ctx, world, dev)
     if rank == 0:
         pk, pk_kind = peaks()
         ms_step = ms_total / args.steps
@@ -314,6 +340,8 @@ def main():
                              "frac": achieved / peak, "traffic": CONV_DRAM_TRAFFIC, "peak_source": f"{pk_kind} bf16 sustained",
                              "launch_ms": conv_ms, "issued_tf32_tflops": 3 * achieved, "tf32_peak_est": peak / 2,
                              "frac_of_tf32_issue_peak": 3 * achieved / (peak / 2)}}
+        if models is not None:
+            line["model_throughput"] = models
         if world == 1 and not args.no_config_latencies:
             line["batch1_latency_ms"] = config_latencies(ctx)
         if not args.no_cpu_baseline:
