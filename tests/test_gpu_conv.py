@@ -179,6 +179,9 @@ MODE_CASES = [
     ("cluster_8", (1, 512, 7, 7), (512, 512, 3, 3), (1, 1), (1, 1), (1, 1), "relu"),            # K split over 8 CTAs
     ("cluster_bias_act", (1, 256, 28, 28), (96, 256, 3, 3), (1, 1), (1, 1), (1, 1), "sigmoid"),  # ragged filter count
     ("odd_width_repitch", (1, 8, 30, 150), (16, 8, 3, 3), (1, 1), (1, 1), (1, 1), "none"),       # rows too wide for flat tiles
+    ("many_tiles", (6, 32, 56, 56), (96, 32, 3, 3), (1, 1), (1, 1), (1, 1), "relu"),       # 294 tiles on 148 SMs
+    ("many_tiles_flat", (40, 64, 14, 14), (64, 64, 3, 3), (1, 1), (1, 1), (1, 1), "none"),        # 80 planes x 2 tiles, flat
+    ("many_tiles_odd_k", (5, 24, 40, 40), (32, 24, 3, 3), (1, 1), (1, 1), (1, 1), "tanh"),        # 7 stages per tile (odd)
 ]
 
 
