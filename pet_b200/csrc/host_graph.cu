@@ -250,9 +250,11 @@ int petb200_graph::run_all(cudaStream_t st, bool include_hoisted) {
     for (auto &s : steps) {
         if (s.weight_only && !include_hoisted)
             continue;
+        const unsigned long long before = petb200_launch_count(ctx);
         int rc = run_step(s, st);
         if (rc)
             return rc;
+        s.launches = (int)(petb200_launch_count(ctx) - before); // what the step really launches (plans decide, e.g. a per-call operand pack)
     }
     return PETB200_OK;
 }

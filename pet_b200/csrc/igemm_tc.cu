@@ -69,7 +69,6 @@ struct IgemmParams {
     float *y;
     int *status;
     long long *prof; // optional per-CTA counters (kProfSlots per CTA), for tuning only
-    int dbg;         // tuning experiments (epilogue only): bit 0 = skip the global stores
 };
 
 struct SmemLayout {
@@ -123,7 +122,7 @@ template <int ACT> __device__ __forceinline__ float act_fn(float v) {
 // the common no-activation case carries none of the transcendental code.
 template <int ACT, int PASSES>
 __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile0, int Fg, bool valid, const float *bias,
-                                               const float *rp /*residual at this pixel, or null*/, float *yp, long long ys_f, bool vec_ok, int dbg, float *stage, int nvalid_warp, float *ybase_warp,
+                                               const float *rp /*residual at this pixel, or null*/, float *yp, long long ys_f, bool vec_ok, float *stage, int nvalid_warp, float *ybase_warp,
                                                int col0, int col1, uint32_t split_addr /*split-K: shared address of [this rank][0][this pixel]*/,
                                                int split_shift /*log2(columns per CTA)*/) {
     uint32_t r[32], nx[32], sm[32];
@@ -152,7 +151,7 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile
             }
             continue;
         }
-        if ((dbg & 1) || (stage == nullptr && !valid))
+        if (stage == nullptr && !valid)
             continue;
         const int f0 = f_tile0 + cc;
 #pragma unroll
@@ -354,7 +353,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     const int ksp = blockIdx.y - ntile * P.ksplit;
     const int zb = blockIdx.z;
     const uint32_t b_half = (uint32_t)P.BN * 128u;
-    // TMEM columns: [0,BN) accumulator of the hi*hi products, [128,128+BN) accumulator of the two small cross terms,
+    // TMEM columns: [0,BN) accumulator of the hi*hi products, [BN,2*BN) accumulator of the two small cross terms,
     // [256,512) the A stages of the TS variant
     const uint32_t tmem_cols = A_TMEM ? 512u : 256u;
 
@@ -796,7 +795,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             const int nblk = P.BN / 32, half_blk = (nblk + 1) / 2;
             const int col0 = tset == 0 ? 0 : half_blk * 32, col1 = tset == 0 ? half_blk * 32 : P.BN;
 #define PETB200_EPI(ACT_)                                                                                              \
-    epilogue_store<ACT_, PASSES>(tacc, P.BN, f_tile0, P.Fg, valid, bp, rp, yp, P.ys_f, vec_ok, P.dbg, stage, nvalid_warp, \
+    epilogue_store<ACT_, PASSES>(tacc, P.BN, f_tile0, P.Fg, valid, bp, rp, yp, P.ys_f, vec_ok, stage, nvalid_warp, \
                                  ybase_warp, col0, col1, split_addr, split_shift)
             switch (P.ksplit > 1 ? PETB200_ACT_NONE : P.act) {
             case PETB200_ACT_RELU: PETB200_EPI(PETB200_ACT_RELU); break;
@@ -1034,7 +1033,6 @@ struct TcCore {
         p.koff = (const int *)koff.p;
         p.status = ctx->d_status;
         p.prof = prof;
-        { static int d = -1; if (d < 0) { const char *e = getenv("PETB200_TC_DBG"); d = e ? atoi(e) : 0; } p.dbg = d; }
         p.has_bias = (P.has_bias && bias) ? 1 : 0;
         void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, IgemmParams) = kernel();
         cudaLaunchConfig_t cfg{};
