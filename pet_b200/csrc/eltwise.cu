@@ -66,34 +66,35 @@ __global__ void __launch_bounds__(256) k_batchnorm(const float *__restrict__ x, 
     }
 }
 
+// One thread per output; blockIdx.z walks the (image, channel) planes and a 32x8 thread block covers a patch of one
+// plane's outputs, so there is no division anywhere and neighbouring threads read neighbouring inputs.
 __global__ void __launch_bounds__(256) k_pool2d(int kind, const float *__restrict__ x, float *__restrict__ y, int nc,
                                                 int h, int w, int oh, int ow, int kh, int kw, int ph, int pw, int sh,
                                                 int sw) {
     pdl_prologue();
-    size_t total = (size_t)nc * oh * ow;
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        int j = (int)(i % ow);
-        size_t r = i / ow;
-        int ii = (int)(r % oh);
-        size_t plane = r / oh;
-        const float *xp = x + plane * (size_t)h * w;
+    const int j = blockIdx.x * 32 + threadIdx.x, ii = blockIdx.y * 8 + threadIdx.y;
+    if (j >= ow || ii >= oh)
+        return;
+    for (int plane = blockIdx.z; plane < nc; plane += gridDim.z) {
+        const float *xp = x + (size_t)plane * h * w;
         float best = -INFINITY, acc = 0.f;
         int cnt = 0;
         for (int a = 0; a < kh; ++a) {
-            int yy = ii * sh + a - ph;
+            const int yy = ii * sh + a - ph;
             if (yy < 0 || yy >= h)
                 continue;
+            const float *row = xp + (size_t)yy * w;
             for (int b = 0; b < kw; ++b) {
-                int xx = j * sw + b - pw;
+                const int xx = j * sw + b - pw;
                 if (xx < 0 || xx >= w)
                     continue;
-                float v = __ldg(xp + (size_t)yy * w + xx);
+                const float v = __ldg(row + xx);
                 best = fmaxf(best, v);
                 acc += v;
                 cnt++;
             }
         }
-        y[i] = kind == 0 ? best : (cnt ? acc / (float)cnt : 0.f);
+        y[((size_t)plane * oh + ii) * ow + j] = kind == 0 ? best : (cnt ? acc / (float)cnt : 0.f);
     }
 }
 
@@ -365,8 +366,8 @@ extern "C" int petb200_pool2d_run(petb200_ctx *ctx, int kind, const float *x, fl
                                                                                   pw, sh, sw);
         return launched(ctx, "k_pool2d_warp");
     }
-    launch_pdl(k_pool2d, grid_for(ctx, total, 256), 256, 0, (cudaStream_t)stream, kind, x, y, n * c, h, w, oh, ow, kh, kw, ph,
-                                                                          pw, sh, sw);
+    launch_pdl(k_pool2d, dim3((unsigned)((ow + 31) / 32), (unsigned)((oh + 7) / 8), (unsigned)std::min(n * c, 65535)), dim3(32, 8), 0,
+               (cudaStream_t)stream, kind, x, y, n * c, h, w, oh, ow, kh, kw, ph, pw, sh, sw);
     return launched(ctx, "k_pool2d");
 }
 
