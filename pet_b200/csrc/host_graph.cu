@@ -26,7 +26,10 @@ struct Tensor {
     bool weight = false;
     int outputOf = -1;           // operator id, -1 for graph inputs
     std::vector<int> inputOf;    // consumers
-    int alias = -1;              // tensor whose storage this one shares (reshape, correction)
+    int alias = -1;              // tensor whose storage this one shares (reshape, correction, merged matmul outputs)
+    long long view_off = 0;      // element offset inside the aliased tensor
+    int pitch = 0;               // > 0: rows of `inner` contiguous elements, `pitch` elements apart (a column slice of a
+    int inner = 0;               //      wider matrix); only operand-stride folding understands such tensors
     float *dev = nullptr;
     bool owns = false;
     bool has_data = false;
@@ -58,6 +61,9 @@ struct Operator {
     long long mm_strides[6] = {0, 0, 0, 0, 0, 0};
     int mm_in[2] = {-1, -1}; // tensor read in place of inputs[i], or -1
     int mm_out_op = -1;      // transpose after the matmul whose output the matmul writes directly, or -1
+    // Leader of a group of matmuls that share their A operand and were merged into one (weights side by side along N):
+    std::vector<int> merged_w, merged_b; // the members' weight / bias tensors, in column order
+    int merged_out = -1, merged_wt = -1, merged_bias = -1; // the wide result, weight and bias tensors of the merged matmul
 };
 
 // One executable step after fusion.
@@ -153,7 +159,16 @@ struct petb200_graph {
     int capture();
 };
 
-static float *dev_of(petb200_graph *g, int t) { return t < 0 ? nullptr : g->tensors[g->root(t)].dev; }
+static float *dev_of(petb200_graph *g, int t) {
+    if (t < 0)
+        return nullptr;
+    long long off = 0;
+    while (g->tensors[t].alias >= 0) {
+        off += g->tensors[t].view_off;
+        t = g->tensors[t].alias;
+    }
+    return g->tensors[t].dev ? g->tensors[t].dev + off : nullptr;
+}
 
 int petb200_graph::run_step(Step &s, cudaStream_t st) {
     Operator &op = ops[s.ops.front()];
@@ -168,6 +183,9 @@ int petb200_graph::run_step(Step &s, cudaStream_t st) {
     case Matmul: {
         const bool wb = tensors[op.inputs[1]].weight;
         const int ta = op.mm_in[0] >= 0 ? op.mm_in[0] : op.inputs[0], tb = op.mm_in[1] >= 0 ? op.mm_in[1] : op.inputs[1];
+        if (op.merged_out >= 0) // merged siblings: one wide matmul on the side-by-side weights
+            return pass(petb200_matmul_run_residual(s.plan, dev_of(this, ta), nullptr, dev_of(this, op.merged_bias), nullptr,
+                                                    dev_of(this, op.merged_out), st));
         return pass(petb200_matmul_run_residual(s.plan, dev_of(this, ta), wb ? nullptr : dev_of(this, tb),
                                                 dev_of(this, op.bias), dev_of(this, s.residual), dev_of(this, ops[s.ops.back()].outputs[0]), st));
     }
@@ -270,8 +288,16 @@ int petb200_graph::compile(int flags) {
         cudaGraphExecDestroy(exec);
         exec = nullptr;
     }
-    for (auto &op : ops)
+    for (auto &op : ops) {
         op.fused_away = false;
+        if (op.merged_out >= 0) // views created by an earlier compile
+            for (int t = 0; t < (int)tensors.size(); ++t)
+                if (tensors[t].alias == op.merged_out && tensors[t].pitch > 0)
+                    tensors[t].alias = -1, tensors[t].view_off = 0, tensors[t].pitch = tensors[t].inner = 0;
+        op.merged_w.clear();
+        op.merged_b.clear();
+        op.merged_out = op.merged_wt = op.merged_bias = -1;
+    }
     hoisted_done = false;
     // ---- topological order (Kahn, like SubGraph::compute) ----
     const int n = (int)ops.size();
@@ -362,6 +388,70 @@ int petb200_graph::compile(int flags) {
         }
     }
 
+    // ---- merge matmuls that share their A operand (BERT's Q/K/V projections) into one wide matmul ----
+    // PET's own optimiser rewrites such siblings into one operator (ref: src/Mutant/generator.cc:1495-1552); here the
+    // weights are laid side by side along N and every member's result becomes a column slice of the wide result.  Only done
+    // when all readers of those results are operands already folded into strides above (nothing else understands a
+    // pitched tensor).
+    for (int xt = 0; xt < (int)tensors.size() && fuse; ++xt) {
+        std::vector<int> grp;
+        for (int c : tensors[xt].inputOf) {
+            const Operator &o = ops[c];
+            if (o.type != Matmul || o.fused_away || o.mm_strided || o.inputs[0] != xt || o.transA || o.transB || o.act != 0 ||
+                !tensors[o.inputs[1]].weight || (o.bias >= 0 && !tensors[o.bias].weight) || is_output(o.outputs[0]))
+                continue;
+            bool ok_out = !tensors[o.outputs[0]].inputOf.empty();
+            for (int rc_ : tensors[o.outputs[0]].inputOf) { // every reader: Reshape -> folded transpose -> strided matmul operand
+                const Operator &r = ops[rc_];
+                if (r.type != Reshape) {
+                    ok_out = false;
+                    break;
+                }
+                const int R = r.outputs[0];
+                ok_out = ok_out && !is_output(R) && !tensors[R].inputOf.empty();
+                for (int tc : tensors[R].inputOf) {
+                    const Operator &tr = ops[tc];
+                    const int user = tr.type == Transpose && tr.fused_away ? sole_consumer(tr.outputs[0]) : -1;
+                    ok_out = ok_out && user >= 0 && ops[user].mm_strided && (ops[user].mm_in[0] == R || ops[user].mm_in[1] == R);
+                }
+            }
+            if (ok_out && (grp.empty() || ((ops[grp[0]].bias >= 0) == (o.bias >= 0) &&
+                                           tensors[ops[grp[0]].inputs[1]].dims[1] == tensors[o.inputs[1]].dims[1])))
+                grp.push_back(c);
+        }
+        if (grp.size() < 2)
+            continue;
+        std::sort(grp.begin(), grp.end());
+        const Dim o0 = tensors[ops[grp[0]].outputs[0]].dims;
+        const int kdim = tensors[ops[grp[0]].inputs[1]].dims[1];
+        int ntot = 0;
+        for (int c : grp)
+            ntot += tensors[ops[c].outputs[0]].dims[2];
+        const int M = new_tensor({o0[0], o0[1], ntot}), Wm = new_tensor({1, kdim, ntot}, true);
+        const int Bm = ops[grp[0]].bias >= 0 ? new_tensor({ntot}, true) : -1;
+        Operator &lead = ops[grp[0]];
+        lead.merged_out = M, lead.merged_wt = Wm, lead.merged_bias = Bm;
+        int off = 0;
+        for (int c : grp) {
+            Operator &o = ops[c];
+            const int O = o.outputs[0], ni = tensors[O].dims[2];
+            lead.merged_w.push_back(o.inputs[1]);
+            if (Bm >= 0)
+                lead.merged_b.push_back(o.bias);
+            tensors[O].alias = M, tensors[O].view_off = off, tensors[O].pitch = ntot, tensors[O].inner = ni;
+            for (int rc_ : tensors[O].inputOf) // readers address rows `ntot` apart instead of `ni`
+                for (int tc : tensors[ops[rc_].outputs[0]].inputOf) {
+                    Operator &user = ops[sole_consumer(ops[tc].outputs[0])];
+                    for (int j = 0; j < 2; ++j)
+                        if (user.mm_in[j] == ops[rc_].outputs[0])
+                            user.mm_strides[2 * j + 1] = ntot;
+                }
+            if (c != grp[0])
+                o.fused_away = true;
+            off += ni;
+        }
+    }
+
     // ---- build steps with fusion ----
     std::vector<char> emitted(n, 0); // operators already covered by a step
     for (int id : order) {
@@ -415,9 +505,11 @@ int petb200_graph::compile(int flags) {
                 rc = petb200_conv3d_plan(ctx, a, PETB200_ALGO_AUTO, &s.plan);
                 s.name = "conv3d";
             } else {
-                const Dim &o = tensors[op.outputs[0]].dims;
+                const Dim &o = tensors[op.merged_out >= 0 ? op.merged_out : op.outputs[0]].dims;
                 const int k = op.transA ? x[1] : x[2];
-                if (op.mm_strided) {
+                if (op.merged_out >= 0) {
+                    rc = petb200_matmul_plan(ctx, 0, 0, o[0], o[1], o[2], k, op.merged_bias >= 0, act, PETB200_ALGO_AUTO, &s.plan);
+                } else if (op.mm_strided) {
                     rc = petb200_matmul_plan_strided(ctx, op.transA, op.transB, o[0], o[1], o[2], k, op.bias >= 0, act, PETB200_ALGO_AUTO,
                                                      op.mm_strides, &s.plan);
                     if (op.mm_out_op >= 0)
@@ -563,6 +655,34 @@ static int prepare_weights(petb200_graph *g, cudaStream_t st) {
         const Tensor &w = g->tensors[op.inputs[1]];
         const bool ready = w.has_data || g->tensors[g->root(op.inputs[1])].has_data;
         int rc = PETB200_OK;
+        if (s.type == Matmul && op.merged_out >= 0) {
+            // lay the members' weights (and biases) side by side, then preprocess the wide matrix once
+            bool all = true;
+            for (int wt : op.merged_w)
+                all = all && g->tensors[wt].has_data;
+            for (int bt : op.merged_b)
+                all = all && g->tensors[bt].has_data;
+            if (!all)
+                continue;
+            const Dim &wd = g->tensors[op.merged_wt].dims; // [1, k, ntot]
+            size_t off = 0;
+            for (size_t i = 0; i < op.merged_w.size(); ++i) {
+                const int ni = g->tensors[op.merged_w[i]].dims[2];
+                if (cudaMemcpy2DAsync(dev_of(g, op.merged_wt) + off, (size_t)wd[2] * 4, dev_of(g, op.merged_w[i]), (size_t)ni * 4,
+                                      (size_t)ni * 4, (size_t)wd[1], cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+                    return g->fail(PETB200_ERR_CUDA, "merged weight copy failed");
+                if (!op.merged_b.empty() &&
+                    cudaMemcpyAsync(dev_of(g, op.merged_bias) + off, dev_of(g, op.merged_b[i]), (size_t)ni * 4, cudaMemcpyDeviceToDevice, st) !=
+                        cudaSuccess)
+                    return g->fail(PETB200_ERR_CUDA, "merged bias copy failed");
+                off += (size_t)ni;
+            }
+            g->tensors[op.merged_wt].has_data = true;
+            rc = petb200_matmul_set_weights(s.plan, dev_of(g, op.merged_wt), st);
+            if (rc)
+                return g->pass(rc);
+            continue;
+        }
         if ((s.type == Conv || s.type == Correction) && ready)
             rc = petb200_conv2d_set_weights(s.plan, dev_of(g, op.inputs[1]), st);
         else if (s.type == Conv3d && ready)

@@ -89,7 +89,10 @@ def test_bert_reduced(ctx):
     assert "transpose" not in names and "add" not in names
     g2, _, y2 = run_config(ctx, configs.bert_encoder, fuse=False, cuda_graph=False, **kw)
     assert [n for n, _ in g2.steps()].count("transpose") == 8
-    assert np.array_equal(y, y2)
+    # the Q/K/V projections of a layer were merged into one wide matmul (2 layers x (8 - 2) matmuls)
+    assert names.count("matmul") == 12 and [n for n, _ in g2.steps()].count("matmul") == 16
+    # same products; the wide matmul may split K differently from the three narrow ones, so sums can round differently
+    assert rel_err(y, y2) <= 1e-5
 
 
 def test_r3d18_reduced(ctx):
