@@ -76,6 +76,11 @@ struct Step {
     int launches = 1;
     bool weight_only = false;  // consumes only weights: hoisted out of the replayed sequence
     int residual = -1;         // conv/matmul: tensor added in the epilogue (a folded residual Add), or -1
+    // A step whose result is read only as another step's residual (the shortcut convolution of a ResNet block) runs on a
+    // second stream beside the steps between it and that reader:
+    bool side = false;
+    int join_from = -1;        // index of the side step this step has to wait for, or -1
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 };
 
 // PerfEngine's memo tables (ref: include/perf_engine.h:15-21): argument tuple -> milliseconds.
@@ -98,6 +103,7 @@ struct petb200_graph {
     bool compiled = false;
     cudaGraphExec_t exec = nullptr;
     cudaStream_t cap_stream = nullptr;
+    cudaStream_t side_stream = nullptr; // side-branch steps (see Step::side)
     bool use_graph = true;
     bool hoisted_done = false;
     PerfEngine perf;
@@ -151,6 +157,14 @@ struct petb200_graph {
             cudaGraphExecDestroy(exec);
         if (cap_stream)
             cudaStreamDestroy(cap_stream);
+        if (side_stream)
+            cudaStreamDestroy(side_stream);
+        for (auto &s : steps) {
+            if (s.ev_fork)
+                cudaEventDestroy(s.ev_fork);
+            if (s.ev_join)
+                cudaEventDestroy(s.ev_join);
+        }
     }
 
     int run_step(Step &s, cudaStream_t st);
@@ -269,9 +283,19 @@ int petb200_graph::run_all(cudaStream_t st, bool include_hoisted) {
         if (s.weight_only && !include_hoisted)
             continue;
         const unsigned long long before = petb200_launch_count(ctx);
-        int rc = run_step(s, st);
+        cudaStream_t where = st;
+        if (s.side && side_stream) { // fork: everything issued so far precedes the side step
+            if (cudaEventRecord(s.ev_fork, st) != cudaSuccess || cudaStreamWaitEvent(side_stream, s.ev_fork, 0) != cudaSuccess)
+                return fail(PETB200_ERR_CUDA, "side-branch fork failed");
+            where = side_stream;
+        }
+        if (s.join_from >= 0 && side_stream && cudaStreamWaitEvent(st, steps[s.join_from].ev_join, 0) != cudaSuccess)
+            return fail(PETB200_ERR_CUDA, "side-branch join failed");
+        int rc = run_step(s, where);
         if (rc)
             return rc;
+        if (where != st && cudaEventRecord(s.ev_join, side_stream) != cudaSuccess)
+            return fail(PETB200_ERR_CUDA, "side-branch join record failed");
         s.launches = (int)(petb200_launch_count(ctx) - before); // what the step really launches (plans decide, e.g. a per-call operand pack)
     }
     return PETB200_OK;
@@ -280,9 +304,14 @@ int petb200_graph::run_all(cudaStream_t st, bool include_hoisted) {
 int petb200_graph::compile(int flags) {
     const bool fuse = !(flags & 1);
     use_graph = !(flags & 2);
-    for (auto &s : steps)
+    for (auto &s : steps) {
         if (s.plan)
             petb200_plan_destroy(s.plan);
+        if (s.ev_fork)
+            cudaEventDestroy(s.ev_fork);
+        if (s.ev_join)
+            cudaEventDestroy(s.ev_join);
+    }
     steps.clear();
     if (exec) {
         cudaGraphExecDestroy(exec);
@@ -622,6 +651,59 @@ int petb200_graph::compile(int flags) {
         for (int o : s.ops)
             emitted[o] = 1;
         steps.push_back(s);
+    }
+    // ---- side branches: a conv/matmul step read only as a later step's residual runs beside the main chain ----
+    // (the shortcut convolution of a ResNet block: it is moved up to right after the step that produces its input and put on
+    // a second stream, so that it overlaps the block's first convolution)
+    if (fuse && !(flags & 4)) {
+        auto residual_reader = [&](size_t i) -> int { // the one later step that reads step i's result, as its residual only
+            const int out = ops[steps[i].ops.back()].outputs[0];
+            if (is_output(out) || tensors[out].inputOf.empty())
+                return -1;
+            int reader = -1;
+            for (int c : tensors[out].inputOf) {
+                int owner = -1;
+                for (size_t j = i + 1; j < steps.size() && owner < 0; ++j)
+                    if (steps[j].residual == out && std::find(steps[j].ops.begin(), steps[j].ops.end(), c) != steps[j].ops.end())
+                        owner = (int)j;
+                if (owner < 0 || (reader >= 0 && reader != owner))
+                    return -1;
+                reader = owner;
+            }
+            return reader;
+        };
+        for (size_t i = 0; i < steps.size(); ++i) {
+            if (steps[i].weight_only || steps[i].side || (steps[i].type != Conv && steps[i].type != Conv3d && steps[i].type != Matmul))
+                continue;
+            if (residual_reader(i) < 0)
+                continue;
+            // earliest slot: right after the last step that produces one of its (non-weight) inputs
+            const Operator &op = ops[steps[i].ops.front()];
+            size_t earliest = 0;
+            for (int t : op.inputs) {
+                if (tensors[t].weight)
+                    continue;
+                const int prod = tensors[root(t)].outputOf;
+                for (size_t j = 0; j < i; ++j)
+                    if (prod >= 0 && std::find(steps[j].ops.begin(), steps[j].ops.end(), prod) != steps[j].ops.end())
+                        earliest = std::max(earliest, j + 1);
+            }
+            if (earliest < i)
+                std::rotate(steps.begin() + earliest, steps.begin() + i, steps.begin() + i + 1);
+            const size_t at = std::min(earliest, i);
+            const int reader = residual_reader(at);
+            if (reader < 0 || reader == (int)at + 1 || steps[reader].join_from >= 0)
+                continue; // nothing to overlap with
+            if (!side_stream && cudaStreamCreateWithFlags(&side_stream, cudaStreamNonBlocking) != cudaSuccess)
+                return fail(PETB200_ERR_CUDA, "side stream creation failed");
+            if (cudaEventCreateWithFlags(&steps[at].ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&steps[at].ev_join, cudaEventDisableTiming) != cudaSuccess)
+                return fail(PETB200_ERR_CUDA, "event creation failed");
+            steps[at].side = true;
+        }
+        for (size_t i = 0; i < steps.size(); ++i) // (indices are final only now)
+            if (steps[i].side)
+                steps[residual_reader(i)].join_from = (int)i;
     }
     // ---- storage: one buffer per non-aliased tensor (kept across recompiles) ----
     for (auto &t : tensors) {
