@@ -58,7 +58,8 @@ struct IgemmParams {
                             // dense and unpadded, fetched as a 2-D box [flat_rows][flat_w] of the contiguous run; padding
                             // becomes a per-pixel mask over the filter taps (<= 32 taps)
     int flat_w, flat_rows;
-    int cstride;            // BC % 32 == 0: floats between consecutive channels of the raw tile (else 0: use the table)
+    int cstride;            // BC % 32 == 0, or BC 16 / 8: floats between consecutive channels of the raw tile (else 0: table)
+    int gruns;              // runs (filter taps) per 32-wide K stage in that mode: 1, 2 (BC 16) or 4 (BC 8)
     int T3[3], dil[3];      // filter extents and dilations (flat only: for the tap mask)
     int xD, xH, xW;         // input extents (flat only)
     long long ys_n, ys_f, ys_p;
@@ -210,18 +211,27 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile
 //                  tells which taps fall inside the input for this pixel;
 //   kGatherStride  chunks of a multiple of 32 channels: a stage is 32 consecutive channels of ONE tap, so the operands
 //                  sit `cstride` floats apart from the stage's first table entry - no table reads, no per-element tests;
+//                  chunks of 16 or 8 channels: the same with RUNS = 2 or 4 taps per stage (one table entry per run);
 //   kGatherKMajor  matmul with row-major A: row p of the 128B-swizzled [128][32] tile.
 enum { kGatherTable = 0, kGatherFlat = 1, kGatherStride = 2, kGatherKMajor = 3 };
-template <int MODE, int PASSES>
+template <int MODE, int PASSES, int RUNS = 1>
 __device__ __forceinline__ void gather_split(const int4 *ko, const float *raw, const uint8_t *krow, int p, uint32_t tmask,
                                              int cstride, bool flat, const float *zero_word, uint32_t (&hi)[32],
                                              uint32_t (&lo)[32]) {
-    const float *q = raw;
-    if (MODE == kGatherStride) {
-        const int o0 = ko[0].x;
-        q = raw + (flat ? (o0 & 0xffffff) : o0);
-        if (flat && !((tmask >> (o0 >> 24)) & 1u)) // this tap is outside the input for this pixel: read zeros
-            q = zero_word, cstride = 0;
+    constexpr int kRun = 32 / RUNS; // channels per run
+    const float *q[RUNS];
+    int cs[RUNS];
+#pragma unroll
+    for (int r = 0; r < RUNS; ++r) {
+        q[r] = raw;
+        cs[r] = cstride;
+        if (MODE == kGatherStride) {
+            const int o0 = ko[r * (kRun / 4)].x; // first table entry of the run
+            // past the end of the chunk's K range, or a tap outside the input for this pixel: read zeros
+            const bool off = o0 < 0 || (flat && !((tmask >> (o0 >> 24)) & 1u));
+            q[r] = off ? zero_word : raw + (flat ? (o0 & 0xffffff) : o0);
+            cs[r] = off ? 0 : cstride;
+        }
     }
 #pragma unroll
     for (int c4 = 0; c4 < 8; ++c4) {
@@ -232,7 +242,7 @@ __device__ __forceinline__ void gather_split(const int4 *ko, const float *raw, c
         } else if (MODE == kGatherStride) {
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-                v[i] = q[(4 * c4 + i) * cstride];
+                v[i] = q[(4 * c4 + i) / kRun][((4 * c4 + i) % kRun) * cs[(4 * c4 + i) / kRun]];
         } else {
             const int4 o4 = ko[c4];
             const int o[4] = {o4.x, o4.y, o4.z, o4.w};
@@ -699,7 +709,12 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                     if (A_KMAJOR)
                         gather_split<kGatherKMajor, PASSES>(ko, raw, krow, p, tmask, 0, false, zero_word, hi, lo);
                     else if (P.cstride)
-                        gather_split<kGatherStride, PASSES>(ko, raw, krow, p, tmask, P.cstride, P.flat != 0, zero_word, hi, lo);
+                        if (P.gruns == 1)
+                            gather_split<kGatherStride, PASSES, 1>(ko, raw, krow, p, tmask, P.cstride, P.flat != 0, zero_word, hi, lo);
+                        else if (P.gruns == 2)
+                            gather_split<kGatherStride, PASSES, 2>(ko, raw, krow, p, tmask, P.cstride, P.flat != 0, zero_word, hi, lo);
+                        else
+                            gather_split<kGatherStride, PASSES, 4>(ko, raw, krow, p, tmask, P.cstride, P.flat != 0, zero_word, hi, lo);
                     else if (P.flat)
                         gather_split<kGatherFlat, PASSES>(ko, raw, krow, p, tmask, 0, true, zero_word, hi, lo);
                     else
@@ -1326,7 +1341,8 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     if (!have)
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "raw activation tile does not fit shared memory");
     P = bestP;
-    P.cstride = (P.BC % kStageK == 0 && env_int("PETB200_TC_TABLE", 0) == 0) ? P.RD * P.RH * P.RW : 0;
+    P.gruns = P.BC % kStageK == 0 ? 1 : (P.BC == 16 ? 2 : (P.BC == 8 ? 4 : 0));
+    P.cstride = (P.gruns && env_int("PETB200_TC_TABLE", 0) == 0) ? P.RD * P.RH * P.RW : 0;
     if (flat && (!core.a_tmem || (long long)P.RN * P.BC * P.RD * P.RH * P.RW >= (1 << 24)))
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "flat raw tiles need the TS kernel variant");
     const int BN = P.BN;
