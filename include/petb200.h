@@ -179,6 +179,33 @@ int petb200_softmax_run(petb200_ctx *ctx, const float *x, float *y, size_t rows,
 int petb200_layernorm_run(petb200_ctx *ctx, const float *x, const float *gamma, const float *beta, float *y,
                           size_t rows, int cols, float eps, petb200_stream stream);
 
+/* ---- transposed convolution and banded attention products ------------------------------------------------------ */
+/* ConvTransOp (ref: include/operator.h:466-614; host definition src/Graph/operator.cc:931-983; timing through
+ * cudnnConvolutionBackwardData :1113-1287).  Channels-last tensors as the reference defines the operator:
+ * x {n,h,w,f}, weight {r,s,f,c}, y {n,oh,ow,c}, oh = (h-1)*sh - 2*ph + (r-1) + oph + 1 (ref: operator.cc:1058-1059).
+ * args = ConvTransOp::getArgs order (ref: include/operator.h:583-598) followed by the output padding, which the
+ * reference leaves out of its tuple: {n,c,h,w,f,r,s,ph,pw,sh,sw,dh,dw,g,bias,act,oph,opw}.  Dilation other than 1 and
+ * groups other than 1 return PETB200_ERR_UNSUPPORTED, as the reference refuses them (ref: operator.cc:1104,1134). */
+int petb200_convtrans_plan(petb200_ctx *ctx, const int args[18], int algo, petb200_plan **out);
+/* Weight-only work (filter flip, split for the tensor cores); once per weight tensor before *_run. */
+int petb200_convtrans_set_weights(petb200_plan *plan, const float *w, petb200_stream stream);
+int petb200_convtrans_run(petb200_plan *plan, const float *x, const float *bias, float *y, petb200_stream stream);
+int petb200_convtrans_out_dims(const petb200_plan *plan, int out_nhwc[4]);
+
+/* G2BMMOp / GBMMLOp (ref: include/operator.h:617-778), argument order of the reference's launchers
+ * _sg2bmm / _sgbmml(a, b, y, bs, n, m, w, d) (ref: src/custom_ops.cu:6-14), any shape:
+ *   g2bmm  y[b,i,j] = sum_k q[b,i,k] * k[b, i + d*(j-w), k]   q,k [bs,n,m] -> y [bs,n,2w+1]
+ *   gbmml  y[b,i,k] = sum_j p[b,i,j] * v[b, i + d*(j-w), k]   p [bs,n,2w+1], v [bs,n,m] -> y [bs,n,m]
+ * (ref: src/nnet/iterator_table.cc:597-633); rows outside [0,n) count as zero. */
+int petb200_g2bmm_run(petb200_ctx *ctx, const float *q, const float *k, float *y, int bs, int n, int m, int w, int d,
+                      petb200_stream stream);
+int petb200_gbmml_run(petb200_ctx *ctx, const float *p, const float *v, float *y, int bs, int n, int m, int w, int d,
+                      petb200_stream stream);
+/* Milliseconds per launch on library-owned operands, as G2BMMOp::perf / GBMMLOp::perf time the reference's kernels
+ * (ref: src/Graph/operator.cc:1424-1465,1562-1598).  kind 0 = g2bmm, 1 = gbmml. */
+int petb200_banded_time(petb200_ctx *ctx, int kind, int bs, int n, int m, int w, int d, int rounds, int warmup, float *ms,
+                        petb200_stream stream);
+
 /* ---- allocation-free entry point ------------------------------------------------------------------------------
  * Has no counterpart in the reference.  For callers that are not allowed to allocate device memory at the point where
  * they need a matmul — a thread that must not take the allocator's lock or its implicit device synchronisation, a

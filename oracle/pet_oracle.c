@@ -437,3 +437,96 @@ void oracle_layernorm_f32(const float *x, const float *gamma, const float *beta,
             yp[i] = (float)(((double)xp[i] - mean) * inv * (gamma ? (double)gamma[i] : 1.0) + (beta ? (double)beta[i] : 0.0));
     }
 }
+
+/* ---- ConvTransOp ------------------------------------------------------------------------------------------------ */
+int oracle_convtrans_out(int in, int k, int pad, int stride, int dil, int out_pad) {
+    /* src/Graph/operator.cc:1058-1059 */
+    return (in - 1) * stride - 2 * pad + dil * (k - 1) + out_pad + 1;
+}
+
+#define CONVTRANS_BODY(TYPE, ACC)                                                                                    \
+    int oh = oracle_convtrans_out(h, r, ph, sh, dh, oph), ow = oracle_convtrans_out(w, s, pw, sw, dw, opw);           \
+    int ah = (h + 2 * ph - r) % sh, aw = (w + 2 * pw - s) % sw;                                                       \
+    for (int nn = 0; nn < n; nn++) {                                                                                  \
+        _Pragma("omp parallel for") for (int cc = 0; cc < c; cc++) {                                                  \
+            for (int hh = 0; hh < oh; hh++)                                                                           \
+                for (int ww = 0; ww < ow; ww++) {                                                                     \
+                    ACC val = 0;                                                                                      \
+                    for (int ff = 0; ff < f; ff++)                                                                    \
+                        for (int rr = 0; rr < r; rr++)                                                                \
+                            for (int ss = 0; ss < s; ss++) {                                                          \
+                                if (r - ah < rr || s - aw < ss)                                                       \
+                                    continue;                                                                         \
+                                int posH = hh + rr * dh - (r - ph - 1), posW = ww + ss * dw - (s - pw - 1);           \
+                                if (posH % sh != 0 || posW % sw != 0)                                                 \
+                                    continue;                                                                         \
+                                posH /= sh;                                                                           \
+                                posW /= sw;                                                                           \
+                                if (posH < 0 || posH >= h || posW < 0 || posW >= w)                                   \
+                                    continue;                                                                         \
+                                TYPE xv = x[ff + (size_t)f * (posW + (size_t)w * (posH + (size_t)h * nn))];           \
+                                TYPE wv = wt[cc + (size_t)c * (ff + (size_t)f * ((s - 1 - ss) + (size_t)s * (r - 1 - rr)))]; \
+                                val += (ACC)wv * (ACC)xv;                                                             \
+                            }                                                                                         \
+                    y[cc + (size_t)c * (ww + (size_t)ow * (hh + (size_t)oh * nn))] = (TYPE)val;                       \
+                }                                                                                                     \
+        }                                                                                                             \
+    }
+
+void oracle_convtrans_u32(const uint32_t *x, const uint32_t *wt, uint32_t *y, int n, int h, int w, int f, int r, int s,
+                          int c, int ph, int pw, int sh, int sw, int dh, int dw, int oph, int opw) {
+    CONVTRANS_BODY(uint32_t, uint32_t)
+}
+
+void oracle_convtrans_f32(const float *x, const float *wt, float *y, int n, int h, int w, int f, int r, int s, int c,
+                          int ph, int pw, int sh, int sw, int dh, int dw, int oph, int opw, int wide) {
+    if (wide) {
+        CONVTRANS_BODY(float, double)
+    } else {
+        CONVTRANS_BODY(float, float)
+    }
+}
+
+/* ---- banded attention products ---------------------------------------------------------------------------------- */
+void oracle_g2bmm_f32(const float *q, const float *kk, float *y, int bs, int n, int m, int w, int d, int wide) {
+    const int bw = 2 * w + 1;
+#pragma omp parallel for collapse(2)
+    for (int b = 0; b < bs; b++)
+        for (int i = 0; i < n; i++)
+            for (int j = 0; j < bw; j++) {
+                long row = (long)i + (long)d * (j - w);
+                double accd = 0;
+                float accf = 0.f;
+                if (row >= 0 && row < n)
+                    for (int k = 0; k < m; k++) {
+                        float a = q[((size_t)b * n + i) * m + k], c = kk[((size_t)b * n + row) * m + k];
+                        if (wide)
+                            accd += (double)a * (double)c;
+                        else
+                            accf += a * c;
+                    }
+                y[((size_t)b * n + i) * bw + j] = wide ? (float)accd : accf;
+            }
+}
+
+void oracle_gbmml_f32(const float *p, const float *v, float *y, int bs, int n, int m, int w, int d, int wide) {
+    const int bw = 2 * w + 1;
+#pragma omp parallel for collapse(2)
+    for (int b = 0; b < bs; b++)
+        for (int i = 0; i < n; i++)
+            for (int k = 0; k < m; k++) {
+                double accd = 0;
+                float accf = 0.f;
+                for (int j = 0; j < bw; j++) {
+                    long row = (long)i + (long)d * (j - w);
+                    if (row < 0 || row >= n)
+                        continue;
+                    float a = p[((size_t)b * n + i) * bw + j], c = v[((size_t)b * n + row) * m + k];
+                    if (wide)
+                        accd += (double)a * (double)c;
+                    else
+                        accf += a * c;
+                }
+                y[((size_t)b * n + i) * m + k] = wide ? (float)accd : accf;
+            }
+}

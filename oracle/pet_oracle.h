@@ -80,6 +80,26 @@ void oracle_softmax_f32(const float *x, float *y, size_t rows, int cols);
 void oracle_layernorm_f32(const float *x, const float *gamma, const float *beta, float *y, size_t rows, int cols,
                           float eps);
 
+/* ConvTransOp, src/Graph/operator.cc:931-983 (whole tensor) and :1006-1040 (one position): x [n,h,w,f] (channels
+ * last), wt [r,s,f,c], y [n,oh,ow,c] with oh = (h-1)*sh - 2*ph + dh*(r-1) + oph + 1 (:1058-1059).  Output (hh,ww)
+ * gathers tap (rr,ss) from input row (hh + rr*dh - (r-ph-1)) / sh when that is a whole in-range number, times
+ * wt[r-1-rr][s-1-ss]; taps with r - ((h+2ph-r) % sh) < rr (same for columns) are skipped, as the reference does.
+ * The whole-tensor body of the reference reads its loop bounds from output dims 2 and 3 (ow and c); this
+ * restatement uses oh and ow, which is what the one-position body computes. */
+int oracle_convtrans_out(int in, int k, int pad, int stride, int dil, int out_pad);
+void oracle_convtrans_u32(const uint32_t *x, const uint32_t *wt, uint32_t *y, int n, int h, int w, int f, int r, int s,
+                          int c, int ph, int pw, int sh, int sw, int dh, int dw, int oph, int opw);
+void oracle_convtrans_f32(const float *x, const float *wt, float *y, int n, int h, int w, int f, int r, int s, int c,
+                          int ph, int pw, int sh, int sw, int dh, int dw, int oph, int opw, int wide);
+
+/* Banded attention products.  The reference only has generated GPU kernels for one shape (include/custom_ops.cuh);
+ * the definitions are the expressions its own rewriter uses for these operators (src/nnet/iterator_table.cc:597-633):
+ *   G2BMM  y[b,i,j] = sum_k q[b,i,k] * kk[b, i + d*(j-w), k],  j in [0, 2w], rows outside [0,n) count as zero;
+ *   GBMML  y[b,i,k] = sum_j p[b,i,j] * v[b, i + d*(j-w), k].
+ * q, kk, v are [b,n,m]; the band tensors are [b,n,2w+1] (shapes: src/Graph/operator.cc:1415-1422). */
+void oracle_g2bmm_f32(const float *q, const float *kk, float *y, int bs, int n, int m, int w, int d, int wide);
+void oracle_gbmml_f32(const float *p, const float *v, float *y, int bs, int n, int m, int w, int d, int wide);
+
 #ifdef __cplusplus
 }
 #endif

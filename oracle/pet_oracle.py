@@ -29,6 +29,7 @@ def lib():
         _LIB = C.CDLL(path)
         _LIB.oracle_transpose_u32.restype = C.c_int
         _LIB.oracle_conv_out.restype = C.c_int
+        _LIB.oracle_convtrans_out.restype = C.c_int
         _LIB.oracle_num_threads.restype = C.c_int
     return _LIB
 
@@ -264,6 +265,58 @@ def layernorm(x, gamma, beta, eps=1e-5):
     y = np.empty_like(x)
     lib().oracle_layernorm_f32(_p(x), _p(_f32(gamma)), _p(_f32(beta)), _p(y), C.c_size_t(x.size // x.shape[-1]),
                                x.shape[-1], C.c_float(eps))
+    return y
+
+
+def convtrans_out(size, k, pad, stride, dil, out_pad):
+    return lib().oracle_convtrans_out(size, k, pad, stride, dil, out_pad)
+
+
+def _convtrans_shapes(x, w, pad, stride, dil, out_pad):
+    n, h, ww, f = x.shape
+    r, s, f2, c = w.shape
+    assert f == f2, (x.shape, w.shape)
+    oh = (h - 1) * stride[0] - 2 * pad[0] + dil[0] * (r - 1) + out_pad[0] + 1
+    ow = (ww - 1) * stride[1] - 2 * pad[1] + dil[1] * (s - 1) + out_pad[1] + 1
+    return n, h, ww, f, r, s, c, oh, ow
+
+
+def convtrans(x, w, pad=(0, 0), stride=(1, 1), dil=(1, 1), out_pad=(0, 0), wide=True):
+    """ConvTransOp in float: x [n,h,w,f], w [r,s,f,c] -> [n,oh,ow,c]."""
+    x, w = _f32(x), _f32(w)
+    n, h, ww, f, r, s, c, oh, ow = _convtrans_shapes(x, w, pad, stride, dil, out_pad)
+    y = np.zeros((n, oh, ow, c), np.float32)
+    lib().oracle_convtrans_f32(_p(x), _p(w), _p(y), n, h, ww, f, r, s, c, pad[0], pad[1], stride[0], stride[1], dil[0],
+                               dil[1], out_pad[0], out_pad[1], int(wide))
+    return y
+
+
+def convtrans_u32(x, w, pad=(0, 0), stride=(1, 1), dil=(1, 1), out_pad=(0, 0)):
+    """ConvTransOp on the reference's own value type (uint32, wrap-around)."""
+    x, w = _u32(x), _u32(w)
+    n, h, ww, f, r, s, c, oh, ow = _convtrans_shapes(x, w, pad, stride, dil, out_pad)
+    y = np.zeros((n, oh, ow, c), np.uint32)
+    lib().oracle_convtrans_u32(_p(x), _p(w), _p(y), n, h, ww, f, r, s, c, pad[0], pad[1], stride[0], stride[1], dil[0],
+                               dil[1], out_pad[0], out_pad[1])
+    return y
+
+
+def g2bmm(q, k, width, dilation=1, wide=True):
+    """Banded Q.K^T: q, k [b,n,m] -> [b,n,2*width+1]."""
+    q, k = _f32(q), _f32(k)
+    b, n, m = q.shape
+    y = np.zeros((b, n, 2 * width + 1), np.float32)
+    lib().oracle_g2bmm_f32(_p(q), _p(k), _p(y), b, n, m, width, dilation, int(wide))
+    return y
+
+
+def gbmml(p, v, dilation=1, wide=True):
+    """Banded P.V: p [b,n,2w+1], v [b,n,m] -> [b,n,m]."""
+    p, v = _f32(p), _f32(v)
+    b, n, bw = p.shape
+    m = v.shape[2]
+    y = np.zeros((b, n, m), np.float32)
+    lib().oracle_gbmml_f32(_p(p), _p(v), _p(y), b, n, m, (bw - 1) // 2, dilation, int(wide))
     return y
 
 

@@ -75,6 +75,22 @@ def conv2d_u32(x, w, pad=(0, 0), stride=(1, 1), dil=(1, 1), return_secs=False):
     return (y, secs.value) if return_secs else y
 
 
+def convtrans_u32(x, w, pad=(0, 0), stride=(1, 1), dil=(1, 1), out_pad=(0, 0), whole=False):
+    """ConvTransOp of the reference: whole=True runs its whole-tensor body (only complete when oh == ow == c),
+    whole=False its one-position body at every output position."""
+    x, w = _u32(x), _u32(w)
+    n, h, ww, f = x.shape
+    r, s, _, c = w.shape
+    oh = (h - 1) * stride[0] - 2 * pad[0] + dil[0] * (r - 1) + out_pad[0] + 1
+    ow = (ww - 1) * stride[1] - 2 * pad[1] + dil[1] * (s - 1) + out_pad[1] + 1
+    y = np.empty((n, oh, ow, c), np.uint32)
+    yd = (C.c_int * 4)()
+    _ok(lib().petref_convtrans(_p(x), _ia(x.shape), _p(w), _ia(w.shape), pad[0], pad[1], stride[0], stride[1], dil[0],
+                               dil[1], out_pad[0], out_pad[1], int(whole), _p(y), yd), "convtrans")
+    assert tuple(yd) == y.shape, (tuple(yd), y.shape)
+    return y
+
+
 def matmul_u32(a, b, transA=False, transB=False):
     a, b = _u32(a), _u32(b)
     bs = a.shape[0]

@@ -258,4 +258,33 @@ int petref_dilated_rewrite(const uint32_t *x, const int *xd, const uint32_t *w, 
     return fetch(t, y, &nd, yd);
 }
 
+// ConvTransOp — include/operator.h:466-614.  x {n,h,w,f}, w {r,s,f,c}, y {n,oh,ow,c}.  whole = 1 runs the reference's
+// whole-tensor body (operator.cc:931-983; it takes its row/column loop bounds from output dims 2 and 3, so it only
+// fills the tensor when oh == ow == c); whole = 0 runs the reference's one-position body (operator.cc:1006-1040)
+// at every output position.
+int petref_convtrans(const uint32_t *x, const int *xd, const uint32_t *w, const int *wd, int ph, int pw, int sh, int sw,
+                     int dh, int dw, int oph, int opw, int whole, uint32_t *y, int *yd) {
+    Graph g;
+    Tensor *tx = feed(g, x, xd, 4);
+    Tensor *tw = feed(g, w, wd, 4, true);
+    auto *op = new ConvTransOp(tx, tw, ph, pw, sh, sw, dh, dw, oph, opw);
+    Tensor *out = op->getOutputs()[0];
+    if (whole) {
+        if (op->compute() == nullptr)
+            return -1;
+    } else {
+        const Dim od = out->getDims();
+        for (int a = 0; a < od[0]; ++a)
+            for (int b = 0; b < od[1]; ++b)
+                for (int c = 0; c < od[2]; ++c)
+                    for (int d = 0; d < od[3]; ++d) {
+                        auto pr = op->compute(DimRange(Dim{a, b, c, d}));
+                        if (!pr.second || !pr.second())
+                            return -1;
+                    }
+    }
+    int nd;
+    return fetch(out, y, &nd, yd);
+}
+
 } // extern "C"

@@ -132,7 +132,7 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 // ---- plan factories implemented in the kernel files ----
 int make_conv_plan(petb200_ctx *ctx, int nsp, const int *in_dims /*n,c,[d],h,w*/, int f, const int *k /*[t],r,s*/,
                    const int *pad, const int *stride, const int *dil, int groups, int has_bias, int act, int algo,
-                   petb200_plan **out);
+                   petb200_plan **out, int channels_last_out = 0 /*y as [n,(od,)oh,ow,f]*/);
 int conv_set_weights(petb200_plan *plan, const float *w, cudaStream_t s);
 int conv_run(petb200_plan *plan, const float *x, const float *bias, float *y, const int *win /*oh0,ohn,ow0,own or null*/,
              cudaStream_t s, const float *res = nullptr /*optional residual, shaped like y*/);

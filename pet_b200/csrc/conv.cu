@@ -8,7 +8,7 @@ namespace petb200 {
 
 // implemented in igemm_tc.cu
 int tc_conv_create(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const int *k, const int *pad, const int *stride,
-                   const int *dil, int groups, int has_bias, int act, int passes, void **out, size_t *dev_bytes);
+                   const int *dil, int groups, int has_bias, int act, int passes, void **out, size_t *dev_bytes, int channels_last_out);
 void tc_conv_destroy(void *h);
 int tc_conv_set_weights(void *h, const float *w, cudaStream_t s);
 int tc_conv_run(void *h, const float *x, const float *bias, const float *res, float *y, const int *win, cudaStream_t s);
@@ -30,6 +30,7 @@ struct SimtConv {
     int N, C, D, H, W, F, T, R, S, pd, ph, pw, sd, sh, sw, dd, dh, dw, groups, OD, OH, OW;
     int oh0, ohn, ow0, own;
     int act, has_bias;
+    int cl_out; // output [n,(od,)oh,ow,f] instead of [n,f,(od,)oh,ow]
 };
 
 __global__ void __launch_bounds__(256) k_conv_simt(const float *__restrict__ x, const float *__restrict__ w,
@@ -71,7 +72,8 @@ __global__ void __launch_bounds__(256) k_conv_simt(const float *__restrict__ x, 
             }
         if (c.has_bias)
             acc += __ldg(bias + ff);
-        const long long yo = ww + (long long)c.OW * (hh + (long long)c.OH * (zz + (long long)c.OD * (ff + (long long)c.F * nn)));
+        const long long yo = c.cl_out ? ff + (long long)c.F * (ww + (long long)c.OW * (hh + (long long)c.OH * (zz + (long long)c.OD * nn)))
+                                      : ww + (long long)c.OW * (hh + (long long)c.OH * (zz + (long long)c.OD * (ff + (long long)c.F * nn)));
         if (res)
             acc += __ldg(res + yo);
         y[yo] = apply_act(acc, c.act);
@@ -277,7 +279,7 @@ struct ConvPlan : petb200_plan {
 };
 
 int make_conv_plan(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const int *k, const int *pad, const int *stride,
-                   const int *dil, int groups, int has_bias, int act, int algo, petb200_plan **out) {
+                   const int *dil, int groups, int has_bias, int act, int algo, petb200_plan **out, int channels_last_out) {
     if (!ctx || !out)
         return PETB200_ERR_INVALID;
     const int nd = nsp + 2;
@@ -303,6 +305,7 @@ int make_conv_plan(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const i
     c.groups = groups;
     c.act = act;
     c.has_bias = has_bias;
+    c.cl_out = channels_last_out ? 1 : 0;
     if (nsp == 3) {
         c.D = in_dims[2], c.H = in_dims[3], c.W = in_dims[4];
         c.T = k[0], c.R = k[1], c.S = k[2];
@@ -329,7 +332,7 @@ int make_conv_plan(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const i
     if (algo == PETB200_ALGO_AUTO || algo == PETB200_ALGO_TC_3XTF32 || algo == PETB200_ALGO_TC_1XTF32) {
         size_t bytes = 0;
         rc = tc_conv_create(ctx, nsp, in_dims, f, k, pad, stride, dil, groups, has_bias, act, algo == PETB200_ALGO_TC_1XTF32 ? 1 : 3,
-                            &pl->tc, &bytes);
+                            &pl->tc, &bytes, c.cl_out);
         if (rc == PETB200_OK) {
             pl->algo = PETB200_ALGO_TC_3XTF32;
             pl->kernel = tc_conv_variant(pl->tc);

@@ -1,0 +1,197 @@
+// Transposed convolution (the reference's ConvTransOp, include/operator.h:466-614) on the convolution kernels.
+//
+// The reference defines the operator on channels-last tensors: x {n,h,w,f}, weight {r,s,f,c}, y {n,oh,ow,c} with
+// oh = (h-1)*sh - 2*ph + (r-1) + oph + 1 (src/Graph/operator.cc:1058-1059); output (hh,ww) gathers tap (rr,ss) from input
+// row (hh + rr - (r-ph-1)) / sh when that is a whole in-range number, times weight[r-1-rr][s-1-ss]
+// (src/Graph/operator.cc:931-983).  Dilation other than 1 is refused, as the reference does (operator.cc:1104).
+//
+// That is an ordinary stride-1 cross-correlation of the zero-inserted input with the flipped filter, so it runs as
+//   1. k_convtrans_expand: x {n,h,w,f} -> xe [n,f,oh+r-1,ow+s-1], zero-inserted and shifted so that no padding is left
+//      (one pass: a 32x32 transpose through shared memory, channel-contiguous reads, row-contiguous writes);
+//   2. the implicit-GEMM convolution over xe with the flipped filter, its epilogue writing y channels-last directly.
+// The filter flip (and the reference's skipped taps) is weight-only work done once in set_weights.
+#include "common.h"
+#include <algorithm>
+
+namespace petb200 {
+
+namespace {
+
+struct ExpandGeom {
+    int n, h, w, f, Hb, Wb, lead_h, lead_w, sh, sw;
+};
+
+// grid (ceil(Wb/32), Hb, n * ceil(f/32)), block (32, 8)
+__global__ void __launch_bounds__(256) k_convtrans_expand(const float *__restrict__ x, float *__restrict__ xe, ExpandGeom g) {
+    pdl_prologue();
+    __shared__ float tile[32][33]; // [position][channel]
+    const int ftiles = (g.f + 31) / 32;
+    const int nn = blockIdx.z / ftiles, f0 = (blockIdx.z % ftiles) * 32;
+    const int y = blockIdx.y, bx0 = blockIdx.x * 32;
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    const int ry = y - g.lead_h;
+    const bool row_live = ry >= 0 && ry % g.sh == 0 && ry / g.sh < g.h;
+    if (row_live) {
+        const int iy = ry / g.sh;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int pos = ty + 8 * i, rx = bx0 + pos - g.lead_w;
+            float v = 0.f;
+            if (bx0 + pos < g.Wb && rx >= 0 && rx % g.sw == 0 && rx / g.sw < g.w && f0 + tx < g.f)
+                v = __ldg(x + ((size_t)(nn * g.h + iy) * g.w + rx / g.sw) * g.f + f0 + tx);
+            tile[pos][tx] = v;
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int ch = ty + 8 * i;
+        if (f0 + ch < g.f && bx0 + tx < g.Wb)
+            xe[((size_t)(nn * g.f + f0 + ch) * g.Hb + y) * g.Wb + bx0 + tx] = row_live ? tile[tx][ch] : 0.f;
+    }
+}
+
+// weight {r,s,f,c} -> [c][f][r][s], flipped in r and s; taps the reference skips (operator.cc:954-957) become zeros.
+__global__ void __launch_bounds__(256) k_convtrans_flip_w(const float *__restrict__ w, float *__restrict__ wf, int r, int s, int f,
+                                                          int c, int ah, int aw) {
+    pdl_prologue();
+    const long long total = (long long)c * f * r * s;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        long long rem = i;
+        const int ss = (int)(rem % s);
+        rem /= s;
+        const int rr = (int)(rem % r);
+        rem /= r;
+        const int ff = (int)(rem % f);
+        const int cc = (int)(rem / f);
+        float v = 0.f;
+        if (!(r - ah < rr || s - aw < ss))
+            v = __ldg(w + cc + (size_t)c * (ff + (size_t)f * ((s - 1 - ss) + (size_t)s * (r - 1 - rr))));
+        wf[i] = v;
+    }
+}
+
+struct ConvTransPlan : petb200_plan {
+    ExpandGeom g{};
+    int r = 0, s = 0, c = 0, oh = 0, ow = 0, ah = 0, aw = 0, has_bias = 0;
+    petb200_plan *conv = nullptr;
+    DevBuf xe, wflip;
+    DevBuf bx, bw, bb, by; // timing operands
+    bool weights_ready = false;
+    ~ConvTransPlan() override { delete conv; }
+    int bench_launch(cudaStream_t s) override;
+};
+
+} // namespace
+
+int make_convtrans_plan(petb200_ctx *ctx, const int *a /*n,c,h,w,f,r,s,ph,pw,sh,sw,dh,dw,g,bias,act,oph,opw*/, int algo,
+                        petb200_plan **out) {
+    if (!ctx || !a || !out)
+        return fail(ctx, PETB200_ERR_INVALID, "convtrans plan: null argument");
+    const int n = a[0], c = a[1], h = a[2], w = a[3], f = a[4], r = a[5], s = a[6], ph = a[7], pw = a[8], sh = a[9], sw = a[10];
+    const int dh = a[11], dw = a[12], groups = a[13], has_bias = a[14], act = a[15], oph = a[16], opw = a[17];
+    if (n <= 0 || c <= 0 || h <= 0 || w <= 0 || f <= 0 || r <= 0 || s <= 0 || sh <= 0 || sw <= 0 || ph < 0 || pw < 0 || oph < 0 || opw < 0)
+        return fail(ctx, PETB200_ERR_INVALID, "convtrans plan: bad extent");
+    if (dh != 1 || dw != 1) // ref: ConvTransOp::checkValid, src/Graph/operator.cc:1103-1104
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "convtrans plan: dilation must be 1 (the reference refuses dilated transposed convolutions)");
+    if (groups != 1) // ref: ConvTransOp::perf, src/Graph/operator.cc:1132-1134
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "convtrans plan: groups must be 1");
+    const int oh = (h - 1) * sh - 2 * ph + (r - 1) + oph + 1, ow = (w - 1) * sw - 2 * pw + (s - 1) + opw + 1;
+    if (oh <= 0 || ow <= 0)
+        return fail(ctx, PETB200_ERR_INVALID, "convtrans plan: empty output");
+    auto *pl = new ConvTransPlan();
+    pl->ctx = ctx;
+    pl->g = ExpandGeom{n, h, w, f, oh + r - 1, ow + s - 1, r - ph - 1, s - pw - 1, sh, sw};
+    pl->r = r, pl->s = s, pl->c = c, pl->oh = oh, pl->ow = ow, pl->has_bias = has_bias;
+    pl->ah = (h + 2 * ph - r) % sh, pl->aw = (w + 2 * pw - s) % sw;
+    const int in_dims[4] = {n, f, pl->g.Hb, pl->g.Wb}, k[2] = {r, s}, zero[2] = {0, 0}, one[2] = {1, 1};
+    int rc = make_conv_plan(ctx, 2, in_dims, c, k, zero, one, one, 1, has_bias, act, algo, &pl->conv, 1);
+    if (rc) {
+        delete pl;
+        return rc;
+    }
+    const size_t xe_bytes = (size_t)n * f * pl->g.Hb * pl->g.Wb * 4, w_bytes = (size_t)c * f * r * s * 4;
+    if (pl->xe.alloc(xe_bytes) != cudaSuccess || pl->wflip.alloc(w_bytes) != cudaSuccess) {
+        delete pl;
+        return fail(ctx, PETB200_ERR_NOMEM, "convtrans plan: scratch allocation (%zu bytes) failed", xe_bytes + w_bytes);
+    }
+    pl->kernel = pl->conv->kernel;
+    pl->device_bytes = pl->conv->device_bytes + xe_bytes + w_bytes;
+    *out = pl;
+    return PETB200_OK;
+}
+
+int convtrans_set_weights(petb200_plan *plan, const float *w, cudaStream_t s) {
+    auto *pl = dynamic_cast<ConvTransPlan *>(plan);
+    if (!pl || !w)
+        return PETB200_ERR_INVALID;
+    petb200_ctx *ctx = pl->ctx;
+    const long long total = (long long)pl->c * pl->g.f * pl->r * pl->s;
+    const int blocks = (int)std::max<long long>(1, std::min<long long>((total + 255) / 256, (long long)ctx->sm_count * 16));
+    launch_pdl(k_convtrans_flip_w, blocks, 256, 0, s, w, (float *)pl->wflip.p, pl->r, pl->s, pl->g.f, pl->c, pl->ah, pl->aw);
+    int rc = launched(ctx, "k_convtrans_flip_w");
+    if (rc)
+        return rc;
+    rc = conv_set_weights(pl->conv, (const float *)pl->wflip.p, s);
+    pl->weights_ready = rc == PETB200_OK;
+    return rc;
+}
+
+int convtrans_run(petb200_plan *plan, const float *x, const float *bias, float *y, cudaStream_t s) {
+    auto *pl = dynamic_cast<ConvTransPlan *>(plan);
+    if (!pl)
+        return PETB200_ERR_INVALID;
+    petb200_ctx *ctx = pl->ctx;
+    if (!x || !y)
+        return fail(ctx, PETB200_ERR_INVALID, "convtrans run: null buffer");
+    if (!pl->weights_ready)
+        return fail(ctx, PETB200_ERR_INVALID, "convtrans run before set_weights");
+    const ExpandGeom &g = pl->g;
+    const dim3 grid((unsigned)((g.Wb + 31) / 32), (unsigned)g.Hb, (unsigned)(g.n * ((g.f + 31) / 32)));
+    if (grid.y > 65535u || grid.z > 65535u)
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "convtrans run: expanded image too tall or too many channel tiles for one launch");
+    launch_pdl(k_convtrans_expand, grid, dim3(32, 8), 0, s, x, (float *)pl->xe.p, g);
+    int rc = launched(ctx, "k_convtrans_expand");
+    if (rc)
+        return rc;
+    return conv_run(pl->conv, (const float *)pl->xe.p, bias, y, nullptr, s);
+}
+
+int convtrans_out_dims(const petb200_plan *plan, int *nhwc) {
+    auto *pl = dynamic_cast<const ConvTransPlan *>(plan);
+    if (!pl || !nhwc)
+        return PETB200_ERR_INVALID;
+    nhwc[0] = pl->g.n, nhwc[1] = pl->oh, nhwc[2] = pl->ow, nhwc[3] = pl->c;
+    return PETB200_OK;
+}
+
+int ConvTransPlan::bench_launch(cudaStream_t st) {
+    if (!bx.p) {
+        const size_t nx = (size_t)g.n * g.h * g.w * g.f, nw = (size_t)r * s * g.f * c, ny = (size_t)g.n * oh * ow * c;
+        if (bx.alloc(nx * 4) != cudaSuccess || bw.alloc(nw * 4) != cudaSuccess || by.alloc(ny * 4) != cudaSuccess ||
+            bb.alloc((size_t)c * 4) != cudaSuccess)
+            return fail(ctx, PETB200_ERR_NOMEM, "scratch allocation for timing failed");
+        cudaMemsetAsync(bx.p, 0x3c, nx * 4, st); // 0x3c3c3c3c is 0.0115 as fp32
+        cudaMemsetAsync(bw.p, 0x3c, nw * 4, st);
+        cudaMemsetAsync(bb.p, 0, (size_t)c * 4, st);
+        int rc = convtrans_set_weights(this, (const float *)bw.p, st);
+        if (rc)
+            return rc;
+    }
+    return convtrans_run(this, (const float *)bx.p, has_bias ? (const float *)bb.p : nullptr, (float *)by.p, st);
+}
+
+} // namespace petb200
+
+using namespace petb200;
+
+extern "C" int petb200_convtrans_plan(petb200_ctx *ctx, const int args[18], int algo, petb200_plan **out) {
+    return make_convtrans_plan(ctx, args, algo, out);
+}
+extern "C" int petb200_convtrans_set_weights(petb200_plan *plan, const float *w, petb200_stream s) {
+    return convtrans_set_weights(plan, w, (cudaStream_t)s);
+}
+extern "C" int petb200_convtrans_run(petb200_plan *plan, const float *x, const float *bias, float *y, petb200_stream s) {
+    return convtrans_run(plan, x, bias, y, (cudaStream_t)s);
+}
+extern "C" int petb200_convtrans_out_dims(const petb200_plan *plan, int out_nhwc[4]) { return convtrans_out_dims(plan, out_nhwc); }

@@ -1380,6 +1380,7 @@ struct TcConv {
     TcCore full;                 // the whole output
     ConvGeom g{};
     int has_bias = 0, act = 0;
+    long long ys[3] = {0, 0, 0}; // output strides {image, filter, pixel}: {F*plane, plane, 1} (NCHW) or {F*plane, 1, F} (channels last)
     std::map<long long, TcCore *> windows; // correction windows, keyed by (oh0,ohn,ow0,own)
     ~TcConv() {
         for (auto &kv : windows)
@@ -1388,7 +1389,7 @@ struct TcConv {
 };
 
 int tc_conv_create(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const int *k, const int *pad, const int *stride,
-                   const int *dil, int groups, int has_bias, int act, int passes, void **out, size_t *dev_bytes) {
+                   const int *dil, int groups, int has_bias, int act, int passes, void **out, size_t *dev_bytes, int channels_last_out) {
     if (ctx->cc_major != 10)
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "tcgen05 kernels need compute capability 10.x, device has %d.%d", ctx->cc_major, ctx->cc_minor);
     auto *t = new TcConv();
@@ -1432,18 +1433,21 @@ int tc_conv_create(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const i
     t->full.ctx = ctx;
     t->full.single_pass = passes == 1;
     const long long plane = (long long)g.OD * g.OH * g.OW;
+    t->ys[0] = (long long)g.F * plane;
+    t->ys[1] = channels_last_out ? 1 : plane;
+    t->ys[2] = channels_last_out ? g.F : 1;
     // Rows that are not multiples of 16 bytes cannot be a TMA stride: small planes are fetched whole ("flat"), anything
     // else is re-pitched by the caller first (tc_conv_row_pitch tells it to what).
     int rc = PETB200_ERR_UNSUPPORTED;
     if (g.W % 4 != 0) {
-        rc = tc_configure(ctx, t->full, g, 0, g.OH, 0, g.OW, 0, g.N, (long long)g.F * plane, plane, 1, has_bias, act, 0, 0, 0, 1);
+        rc = tc_configure(ctx, t->full, g, 0, g.OH, 0, g.OW, 0, g.N, t->ys[0], t->ys[1], t->ys[2], has_bias, act, 0, 0, 0, 1);
         if (rc == PETB200_ERR_UNSUPPORTED) {
             g.Wst = (g.W + 3) / 4 * 4;
             memset(&t->full.P, 0, sizeof t->full.P);
         }
     }
     if (rc == PETB200_ERR_UNSUPPORTED)
-        rc = tc_configure(ctx, t->full, g, 0, g.OH, 0, g.OW, 0, g.N, (long long)g.F * plane, plane, 1, has_bias, act);
+        rc = tc_configure(ctx, t->full, g, 0, g.OH, 0, g.OW, 0, g.N, t->ys[0], t->ys[1], t->ys[2], has_bias, act);
     if (rc) {
         delete t;
         return rc;
@@ -1494,10 +1498,9 @@ int tc_conv_run(void *h, const float *x, const float *bias, const float *res, fl
         wc = new TcCore();
         wc->ctx = t->full.ctx;
         wc->single_pass = t->full.single_pass;
-        const long long plane = (long long)g.OD * g.OH * g.OW;
         // A window must consume K in exactly the order of the full operator (same BC / chunking), otherwise the
         // two would round differently; the raw box only shrinks for a window, so the full plan's BC always fits.
-        int rc = tc_configure(wc->ctx, *wc, g, win[0], win[1], win[2], win[3], 0, g.N, (long long)g.F * plane, plane, 1,
+        int rc = tc_configure(wc->ctx, *wc, g, win[0], win[1], win[2], win[3], 0, g.N, t->ys[0], t->ys[1], t->ys[2],
                               t->has_bias, t->act, t->full.P.BC, t->full.P.ksplit, t->full.P.BN, t->full.P.flat);
         if (rc == PETB200_OK && (wc->P.BN != t->full.P.BN || wc->P.BC != t->full.P.BC || wc->Ktot != t->full.Ktot || wc->P.ksplit != t->full.P.ksplit))
             rc = fail(wc->ctx, PETB200_ERR_UNSUPPORTED, "window plan diverged from the full plan");

@@ -40,6 +40,13 @@ SYMBOLS = {
     "petb200_conv3d_plan": (_i, [_vp, _ip, _i, C.POINTER(_vp)]),
     "petb200_conv3d_set_weights": (_i, [_vp, _vp, _vp]),
     "petb200_conv3d_run": (_i, [_vp, _vp, _vp, _vp, _vp]),
+    "petb200_convtrans_plan": (_i, [_vp, _ip, _i, C.POINTER(_vp)]),
+    "petb200_convtrans_set_weights": (_i, [_vp, _vp, _vp]),
+    "petb200_convtrans_run": (_i, [_vp, _vp, _vp, _vp, _vp]),
+    "petb200_convtrans_out_dims": (_i, [_vp, _ip]),
+    "petb200_g2bmm_run": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "petb200_gbmml_run": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "petb200_banded_time": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, C.POINTER(_fp), _vp]),
     "petb200_conv_run_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "petb200_matmul_plan": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, C.POINTER(_vp)]),
     "petb200_matmul_plan_strided": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, C.POINTER(C.c_longlong), C.POINTER(_vp)]),

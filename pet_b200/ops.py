@@ -156,6 +156,63 @@ class Context:
             self.check(self.lib.petb200_conv3d_run(plan.h, _ptr(_f32(x)), _ptr(bias), _ptr(y), _stream()))
         return y
 
+    # ---- transposed convolution, banded attention products -------------------------------------------------
+    def convtrans_plan(self, xshape, wshape, ph, pw, sh=1, sw=1, dh=1, dw=1, oph=0, opw=0, bias=False, act="none",
+                       algo="auto"):
+        """ConvTransOp: x {n,h,w,f}, weight {r,s,f,c} -> {n,oh,ow,c} (channels last, as the reference defines it)."""
+        n, h, w, f = xshape
+        r, s, f2, c = wshape
+        if f != f2:
+            raise L.PetError(L.ERR_INVALID, "input channels differ from the filter's")
+        args = [n, c, h, w, f, r, s, ph, pw, sh, sw, dh, dw, 1, int(bool(bias)), L.ACT[act], oph, opw]
+        h_ = C.c_void_p()
+        self.check(self.lib.petb200_convtrans_plan(self.h, L.ints(args), L.ALGO[algo], C.byref(h_)))
+        p = Plan(self, h_)
+        od = (C.c_int * 4)()
+        self.check(self.lib.petb200_convtrans_out_dims(h_, od))
+        p.out_shape = tuple(od)
+        return p
+
+    def convtrans(self, x, w, ph, pw, sh=1, sw=1, dh=1, dw=1, oph=0, opw=0, bias=None, act="none", algo="auto"):
+        key = ("convtrans", tuple(x.shape), tuple(w.shape), ph, pw, sh, sw, dh, dw, oph, opw, bias is not None, act, algo)
+        plan = self._plans.get(key)
+        if plan is None:
+            plan = self._plans[key] = self.convtrans_plan(x.shape, w.shape, ph, pw, sh, sw, dh, dw, oph, opw,
+                                                          bias is not None, act, algo)
+        plan._w = _f32(w)
+        self.check(self.lib.petb200_convtrans_set_weights(plan.h, _ptr(plan._w), _stream()))
+        y = torch.empty(plan.out_shape, device=x.device, dtype=torch.float32)
+        self.check(self.lib.petb200_convtrans_run(plan.h, _ptr(_f32(x)), _ptr(_f32(bias) if bias is not None else None),
+                                                  _ptr(y), _stream()))
+        return y
+
+    def g2bmm(self, q, k, width, dilation=1):
+        """Banded Q.K^T: q, k [b,n,m] -> [b,n,2*width+1]; key row i + dilation*(j-width), zero outside [0,n)."""
+        q, k = _f32(q), _f32(k)
+        if q.dim() != 3 or tuple(q.shape) != tuple(k.shape):
+            raise L.PetError(L.ERR_INVALID, "g2bmm operands must be 3-D and of equal shape")
+        b, n, m = q.shape
+        y = torch.empty((b, n, 2 * width + 1), device=q.device, dtype=torch.float32)
+        self.check(self.lib.petb200_g2bmm_run(self.h, _ptr(q), _ptr(k), _ptr(y), b, n, m, width, dilation, _stream()))
+        return y
+
+    def gbmml(self, p, v, dilation=1):
+        """Banded P.V: p [b,n,2w+1], v [b,n,m] -> [b,n,m]."""
+        p, v = _f32(p), _f32(v)
+        if p.dim() != 3 or v.dim() != 3 or p.shape[:2] != v.shape[:2] or p.shape[2] % 2 != 1:
+            raise L.PetError(L.ERR_INVALID, "gbmml operands must be [b,n,2w+1] and [b,n,m]")
+        b, n, bw = p.shape
+        m = v.shape[2]
+        y = torch.empty((b, n, m), device=p.device, dtype=torch.float32)
+        self.check(self.lib.petb200_gbmml_run(self.h, _ptr(p), _ptr(v), _ptr(y), b, n, m, (bw - 1) // 2, dilation, _stream()))
+        return y
+
+    def banded_time(self, kind, b, n, m, width, dilation=1, rounds=100, warmup=10):
+        ms = C.c_float()
+        self.check(self.lib.petb200_banded_time(self.h, {"g2bmm": 0, "gbmml": 1}[kind], b, n, m, width, dilation, rounds,
+                                                warmup, C.byref(ms), _stream()))
+        return ms.value
+
     # ---- matmul --------------------------------------------------------------------------------------------
     def matmul_plan(self, ashape, bshape, transA=False, transB=False, bias=False, act="none", algo="auto", strides=None):
         """strides: optional (A batch, A row, B batch, B row, C batch, C row) in elements for operands that are strided

@@ -26,6 +26,14 @@ CONVS = [  # (x shape, w shape, kwargs)
     ((1, 6, 9, 11), (4, 6, 1, 1), dict(pad=(0, 0))),
     ((1, 3, 15, 15), (5, 3, 7, 7), dict(pad=(3, 3), stride=(2, 2))),
 ]
+CONVTRANS = [  # (x shape {n,h,w,f}, w shape {r,s,f,c}, kwargs, whole) — ConvTransOp; `whole` picks the reference's
+    # whole-tensor body (complete only when oh == ow == c), otherwise its one-position body fills the tensor
+    ((1, 4, 4, 3), (4, 4, 3, 8), dict(pad=(1, 1), stride=(2, 2)), True),
+    ((2, 5, 4, 3), (3, 3, 3, 5), dict(pad=(1, 0), stride=(2, 1), out_pad=(1, 0)), False),
+    ((1, 4, 5, 2), (3, 2, 2, 3), dict(pad=(0, 1), stride=(3, 2), out_pad=(2, 1)), False),
+    ((1, 6, 5, 2), (4, 3, 2, 3), dict(stride=(3, 3)), False),  # (h+2ph-r) % sh = 2: the reference skips tap rr = 3
+    ((1, 3, 3, 2), (2, 2, 2, 2), dict(pad=(3, 3), stride=(2, 2), out_pad=(1, 1)), False),  # padding >= kernel
+]
 PAD = ([0, 1, 2, 0], [1, 0, 3, 2])
 SLICE = ([0, 1, 2, 0], [1, 0, 3, 2])
 

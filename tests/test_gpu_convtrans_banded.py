@@ -1,0 +1,166 @@
+"""GPU: transposed convolution and the banded attention products through the C ABI against the CPU oracle
+(restatements of ConvTransOp::compute and of the reference's G2BMM / GBMML definitions) and the reference-produced
+integer vectors."""
+import numpy as np
+import pytest
+import torch
+
+import golden_cases as gc
+from conftest import rel_err, scale_err
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3        # max relative error the backend has to meet (metric: conftest.rel_err)
+TOL_SCALE = 5e-5  # 3xTF32 accuracy statement: max |err| / max |ref|
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _ct(ctx, x, w, kw, algo, bias=None, act="none"):
+    pad, st, op = kw.get("pad", (0, 0)), kw.get("stride", (1, 1)), kw.get("out_pad", (0, 0))
+    return ctx.convtrans(dev(x), dev(w), pad[0], pad[1], st[0], st[1], 1, 1, op[0], op[1],
+                         bias=None if bias is None else dev(bias), act=act, algo=algo)
+
+
+@pytest.mark.parametrize("algo", ["tc_3xtf32", "simt_fp32"])
+@pytest.mark.parametrize("i", range(len(gc.CONVTRANS)))
+def test_convtrans_on_reference_integer_vectors(ctx, golden, algo, i):
+    # small integers: products and partial sums are exact in fp32, so the float kernels must reproduce the integer
+    # results of the reference's own host operator
+    xs, ws, kw, _ = gc.CONVTRANS[i]
+    x, w = gc.small_ints(xs, 300 + i) % 16, gc.small_ints(ws, 400 + i) % 16
+    from oracle import pet_oracle as po
+    want = po.convtrans_u32(x, w, **kw)
+    y = _ct(ctx, x.astype(np.float32), w.astype(np.float32), kw, algo)
+    ctx.sync_check()
+    assert tuple(y.shape) == want.shape
+    assert np.array_equal(y.cpu().numpy().astype(np.uint32), want)
+
+
+CT_CASES = [
+    # name, x {n,h,w,f}, w {r,s,f,c}, kwargs
+    ("upsample2x_k4", (1, 16, 16, 64), (4, 4, 64, 32), dict(pad=(1, 1), stride=(2, 2))),
+    ("upsample2x_k3_outpad", (2, 14, 14, 48), (3, 3, 48, 24), dict(pad=(1, 1), stride=(2, 2), out_pad=(1, 1))),
+    ("stride1_same", (1, 12, 20, 32), (3, 3, 32, 40), dict(pad=(1, 1))),
+    ("stride3_skipped_tap", (1, 6, 5, 16), (4, 3, 16, 12), dict(stride=(3, 3))),
+    ("ragged_channels", (2, 5, 7, 5), (3, 2, 5, 7), dict(pad=(0, 1), stride=(2, 1), out_pad=(1, 0))),
+    ("dcgan_layer", (4, 8, 8, 256), (4, 4, 256, 128), dict(pad=(1, 1), stride=(2, 2))),
+    ("padding_ge_kernel", (1, 6, 6, 8), (2, 2, 8, 8), dict(pad=(3, 3), stride=(2, 2), out_pad=(1, 1))),
+]
+
+
+@pytest.mark.parametrize("algo", ["auto", "simt_fp32"])
+@pytest.mark.parametrize("case", CT_CASES, ids=[c[0] for c in CT_CASES])
+def test_convtrans_vs_oracle(ctx, oracle, case, algo):
+    name, xs, ws, kw = case
+    rng = np.random.default_rng(abs(hash(name)) % 2**31)
+    x = rng.uniform(-1, 1, xs).astype(np.float32)
+    w = (rng.standard_normal(ws) * np.sqrt(2.0 / (ws[0] * ws[1] * ws[2]))).astype(np.float32)
+    want = oracle.convtrans(x, w, wide=True, **kw)
+    y = _ct(ctx, x, w, kw, algo).cpu().numpy()
+    ctx.sync_check()
+    assert y.shape == want.shape
+    assert rel_err(y, want) <= TOL
+    assert scale_err(y, want) <= TOL_SCALE
+
+
+def test_convtrans_bias_activation_and_torch(ctx, oracle):
+    rng = np.random.default_rng(3)
+    x = rng.uniform(-1, 1, (2, 9, 9, 32)).astype(np.float32)
+    w = (rng.standard_normal((3, 3, 32, 16)) * 0.1).astype(np.float32)
+    b = rng.uniform(-1, 1, 16).astype(np.float32)
+    kw = dict(pad=(1, 1), stride=(2, 2), out_pad=(1, 1))
+    want = np.maximum(oracle.convtrans(x, w, wide=True, **kw) + b, 0)
+    y = _ct(ctx, x, w, kw, "auto", bias=b, act="relu").cpu().numpy()
+    assert rel_err(y, want) <= TOL
+    # the same operator as torch states it: weight [f_in, c_out, r, s], NCHW
+    tx = torch.from_numpy(x).permute(0, 3, 1, 2).double()
+    tw = torch.from_numpy(w).permute(2, 3, 0, 1).double()
+    ty = torch.nn.functional.conv_transpose2d(tx, tw, torch.from_numpy(b).double(), stride=2, padding=1, output_padding=1)
+    assert rel_err(y, torch.relu(ty).permute(0, 2, 3, 1).numpy()) <= TOL
+
+
+def test_convtrans_rejects_what_the_reference_rejects(ctx):
+    import pet_b200.lib as L
+    with pytest.raises(L.PetError):
+        ctx.convtrans_plan((1, 4, 4, 8), (3, 3, 8, 8), 1, 1, 1, 1, 2, 2)  # dilation
+    with pytest.raises(L.PetError):
+        ctx.convtrans_plan((1, 4, 4, 8), (3, 3, 6, 8), 1, 1)  # channel mismatch
+
+
+def test_convtrans_plan_time(ctx):
+    p = ctx.convtrans_plan((1, 16, 16, 64), (4, 4, 64, 64), 1, 1, 2, 2)
+    assert p.out_shape == (1, 32, 32, 64)
+    assert 0 < p.time(rounds=20, warmup=5) < 5.0
+
+
+BAND_CASES = [
+    # b, n, m, w, d
+    (2, 37, 8, 3, 1),
+    (1, 300, 64, 40, 1),
+    (2, 257, 64, 17, 2),
+    (1, 100, 20, 150, 1),   # band wider than the sequence
+    (3, 64, 6, 0, 1),       # zero width: the diagonal
+    (1, 130, 33, 9, 4),     # m not a multiple of 4
+    (1, 50, 16, 7, 64),     # dilation beyond the sequence length
+]
+
+
+@pytest.mark.parametrize("case", BAND_CASES, ids=["b%d_n%d_m%d_w%d_d%d" % c for c in BAND_CASES])
+def test_banded_products_vs_oracle(ctx, oracle, case):
+    b, n, m, w, d = case
+    rng = np.random.default_rng(1000 * n + w)
+    q = rng.standard_normal((b, n, m)).astype(np.float32)
+    k = rng.standard_normal((b, n, m)).astype(np.float32)
+    p = rng.standard_normal((b, n, 2 * w + 1)).astype(np.float32)
+    s = ctx.g2bmm(dev(q), dev(k), w, d).cpu().numpy()
+    o = ctx.gbmml(dev(p), dev(k), d).cpu().numpy()
+    ctx.sync_check()
+    want_s, want_o = oracle.g2bmm(q, k, w, d, wide=True), oracle.gbmml(p, k, d, wide=True)
+    assert s.shape == want_s.shape and o.shape == want_o.shape
+    assert scale_err(s, want_s) <= 1e-5 and scale_err(o, want_o) <= 1e-5
+    # positions whose key row is outside the sequence are exact zeros, whatever p holds there
+    i = np.arange(n)[:, None] + d * (np.arange(2 * w + 1)[None, :] - w)
+    assert np.all(s[:, (i < 0) | (i >= n)] == 0)
+    p_bad = p.copy()
+    p_bad[:, (i < 0) | (i >= n)] = np.inf
+    assert np.array_equal(ctx.gbmml(dev(p_bad), dev(k), d).cpu().numpy(), o)
+
+
+def test_banded_products_small_integers_exact(ctx, oracle):
+    rng = np.random.default_rng(8)
+    q = rng.integers(0, 16, (2, 90, 24)).astype(np.float32)
+    k = rng.integers(0, 16, (2, 90, 24)).astype(np.float32)
+    p = rng.integers(0, 16, (2, 90, 23)).astype(np.float32)
+    assert np.array_equal(ctx.g2bmm(dev(q), dev(k), 11, 2).cpu().numpy(), oracle.g2bmm(q, k, 11, 2, wide=False))
+    assert np.array_equal(ctx.gbmml(dev(p), dev(k), 3).cpu().numpy(), oracle.gbmml(p, k, 3, wide=False))
+
+
+def test_banded_reference_shape_properties(ctx):
+    """The one shape the reference ships kernels for (n=10000, m=64, w=1000, d in {1,4}), checked through properties:
+    a sample of entries against a dot product, and GBMML of a one-hot band against a row gather."""
+    n, m, w = 10000, 64, 1000
+    g = torch.Generator(device="cuda").manual_seed(4)
+    q = torch.randn((1, n, m), device="cuda", generator=g)
+    k = torch.randn((1, n, m), device="cuda", generator=g)
+    for d in (1, 4):
+        s = ctx.g2bmm(q, k, w, d)
+        ctx.sync_check()
+        assert tuple(s.shape) == (1, n, 2 * w + 1)
+        ii = torch.randint(0, n, (4096,), device="cuda", generator=g)
+        jj = torch.randint(0, 2 * w + 1, (4096,), device="cuda", generator=g)
+        rows = ii + d * (jj - w)
+        ok = (rows >= 0) & (rows < n)
+        want = (q[0, ii].double() * k[0, rows.clamp(0, n - 1)].double()).sum(-1) * ok
+        assert float((s[0, ii, jj].double() - want).abs().max()) <= 1e-4
+        # one-hot band: column j0 set to 1 selects key row i + d*(j0-w)
+        j0 = w + 3
+        p = torch.zeros((1, n, 2 * w + 1), device="cuda")
+        p[:, :, j0] = 1.0
+        o = ctx.gbmml(p, k, d)
+        shift = d * (j0 - w)
+        assert torch.equal(o[0, : n - shift], k[0, shift:])
+        assert float(o[0, n - shift:].abs().max()) == 0.0
+    assert 0 < ctx.banded_time("g2bmm", 1, n, m, w, 1, rounds=5, warmup=2) < 50.0
+    assert 0 < ctx.banded_time("gbmml", 1, n, m, w, 1, rounds=5, warmup=2) < 50.0
