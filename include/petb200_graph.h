@@ -43,6 +43,12 @@ int petb200_graph_conv(petb200_graph *g, int x, int w, int bias, int ph, int pw,
 int petb200_graph_conv3d(petb200_graph *g, int x, int w, int bias, const int pad[3], const int stride[3], const int dil[3],
                          int act, int *out);
 int petb200_graph_matmul(petb200_graph *g, int a, int b, int bias, int transA, int transB, int act, int *out);
+/* ref: Graph::convTrans (src/Graph/graph.cc:120-131): x {n,h,w,f}, w {r,s,f,c} -> {n,oh,ow,c}; dilation must be 1. */
+int petb200_graph_convtrans(petb200_graph *g, int x, int w, int bias, int ph, int pw, int sh, int sw, int dh, int dw, int oph,
+                            int opw, int act, int *out);
+/* ref: Graph::g2bmm / Graph::gbmml (include/graph.h:80-90): banded Q.K^T -> [b,n,2*width+1]; banded P.V -> [b,n,m]. */
+int petb200_graph_g2bmm(petb200_graph *g, int a, int b, int width, int dilation, int *out);
+int petb200_graph_gbmml(petb200_graph *g, int a, int b, int dilation, int *out);
 int petb200_graph_transpose(petb200_graph *g, int x, const petb200_transpose_desc *desc, int *out);
 int petb200_graph_pad(petb200_graph *g, int x, const int *begin, const int *end, int *out);
 int petb200_graph_slice(petb200_graph *g, int x, const int *begin, const int *end, int *out);

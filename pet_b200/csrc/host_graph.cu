@@ -19,7 +19,7 @@ using Dim = std::vector<int>;
 
 // OpType values follow the reference's enum names (ref: include/operator.h:19-51) for the operators that exist there.
 enum OpType { Conv, Matmul, Transpose, Pad, Slice, Concat, Split, Extend, Add, Sub, Mul, Activation, MaxPool, AvgPool,
-              Softmax, BatchNorm, Reshape, Conv3d, LayerNorm, Correction };
+              Softmax, BatchNorm, Reshape, Conv3d, LayerNorm, Correction, ConvTrans, G2BMM, GBMML };
 
 struct Tensor {
     Dim dims;
@@ -55,6 +55,8 @@ struct Operator {
     int kh = 0, kw = 0;
     float eps = 1e-5f;
     int win[4] = {0, 0, 0, 0};
+    int oph = 0, opw = 0;         // ConvTrans output padding
+    int width = 0, dilation = 1;  // G2BMM / GBMML band half-width and key step
     bool fused_away = false; // absorbed into another step
     // Matmul whose operands/result are strided views of other tensors (folded batch-swap transposes):
     bool mm_strided = false;
@@ -191,6 +193,15 @@ int petb200_graph::run_step(Step &s, cudaStream_t st) {
     case Conv3d:
         return pass(petb200_conv_run_residual(s.plan, dev_of(this, op.inputs[0]), dev_of(this, op.bias), dev_of(this, s.residual),
                                               dev_of(this, ops[s.ops.back()].outputs[0]), st));
+    case ConvTrans:
+        return pass(petb200_convtrans_run(s.plan, dev_of(this, op.inputs[0]), dev_of(this, op.bias), dev_of(this, op.outputs[0]), st));
+    case G2BMM:
+    case GBMML: {
+        const Dim &b = tensors[op.inputs[1]].dims; // [bs, n, m]
+        auto fn = s.type == G2BMM ? petb200_g2bmm_run : petb200_gbmml_run;
+        return pass(fn(ctx, dev_of(this, op.inputs[0]), dev_of(this, op.inputs[1]), dev_of(this, op.outputs[0]), b[0], b[1], b[2], op.width,
+                       op.dilation, st));
+    }
     case Correction:
         return pass(petb200_conv2d_correct(s.plan, dev_of(this, op.inputs[0]), dev_of(this, op.bias), dev_of(this, op.outputs[0]),
                                            op.win[0], op.win[1], op.win[2], op.win[3], st));
@@ -622,6 +633,21 @@ int petb200_graph::compile(int flags) {
                 }
             }
             break;
+        case ConvTrans: {
+            const Dim &x = tensors[op.inputs[0]].dims, &w = tensors[op.inputs[1]].dims; // {n,h,w,f}, {r,s,f,c}
+            int a[18] = {x[0], w[3], x[1], x[2], x[3], w[0], w[1], op.ph, op.pw, op.sh, op.sw, op.dh, op.dw, 1, op.bias >= 0, op.act, op.oph, op.opw};
+            rc = petb200_convtrans_plan(ctx, a, PETB200_ALGO_AUTO, &s.plan);
+            s.name = "convtrans";
+            s.launches = 2;
+            s.weight_only = false;
+            break;
+        }
+        case G2BMM:
+            s.name = "g2bmm";
+            break;
+        case GBMML:
+            s.name = "gbmml";
+            break;
         case Activation:
             s.name = "activation";
             break;
@@ -647,7 +673,7 @@ int petb200_graph::compile(int flags) {
         }
         if (rc)
             return pass(rc);
-        s.kernel = s.plan ? petb200_plan_kernel(s.plan) : (s.launches ? "eltwise" : "alias");
+        s.kernel = s.plan ? petb200_plan_kernel(s.plan) : (s.type == G2BMM ? "k_g2bmm" : (s.type == GBMML ? "k_gbmml" : (s.launches ? "eltwise" : "alias")));
         for (int o : s.ops)
             emitted[o] = 1;
         steps.push_back(s);
@@ -769,6 +795,8 @@ static int prepare_weights(petb200_graph *g, cudaStream_t st) {
             rc = petb200_conv2d_set_weights(s.plan, dev_of(g, op.inputs[1]), st);
         else if (s.type == Conv3d && ready)
             rc = petb200_conv3d_set_weights(s.plan, dev_of(g, op.inputs[1]), st);
+        else if (s.type == ConvTrans && ready)
+            rc = petb200_convtrans_set_weights(s.plan, dev_of(g, op.inputs[1]), st);
         else if (s.type == Matmul && w.weight && ready)
             rc = petb200_matmul_set_weights(s.plan, dev_of(g, op.inputs[1]), st);
         if (rc)
@@ -898,6 +926,74 @@ extern "C" int petb200_graph_conv3d(petb200_graph *g, int x, int w, int bias, co
         op.pad3[i] = pad[i], op.stride3[i] = stride[i], op.dil3[i] = dil[i];
     g->tensors[w].weight = true;
     *out = g->new_tensor(od);
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+// ref: Graph::convTrans, src/Graph/graph.cc:120-131; shape ConvTransOp::computeShape, src/Graph/operator.cc:1043-1063.
+extern "C" int petb200_graph_convtrans(petb200_graph *g, int x, int w, int bias, int ph, int pw, int sh, int sw, int dh, int dw, int oph,
+                                       int opw, int act, int *out) {
+    if (!g || !out)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, x);
+    G_CHECK_T(g, w);
+    const Dim &xd = g->tensors[x].dims, &wd = g->tensors[w].dims; // {n,h,w,f}, {r,s,f,c}
+    if (xd.size() != 4 || wd.size() != 4 || xd[3] != wd[2])
+        return g->fail(PETB200_ERR_INVALID, "convTrans: operands must be {n,h,w,f} and {r,s,f,c}");
+    if (dh != 1 || dw != 1) // ref: ConvTransOp::checkValid, src/Graph/operator.cc:1103-1104
+        return g->fail(PETB200_ERR_UNSUPPORTED, "convTrans: dilation must be 1");
+    if (sh <= 0 || sw <= 0 || ph < 0 || pw < 0 || oph < 0 || opw < 0)
+        return g->fail(PETB200_ERR_INVALID, "convTrans: bad stride/pad");
+    const int oh = (xd[1] - 1) * sh - 2 * ph + (wd[0] - 1) + oph + 1, ow = (xd[2] - 1) * sw - 2 * pw + (wd[1] - 1) + opw + 1;
+    if (oh <= 0 || ow <= 0)
+        return g->fail(PETB200_ERR_INVALID, "convTrans: empty output");
+    Operator op;
+    op.type = ConvTrans;
+    op.inputs = {x, w};
+    op.bias = bias;
+    op.act = act;
+    op.ph = ph, op.pw = pw, op.sh = sh, op.sw = sw, op.dh = dh, op.dw = dw, op.oph = oph, op.opw = opw;
+    g->tensors[w].weight = true;
+    *out = g->new_tensor(Dim{xd[0], oh, ow, wd[3]});
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+// ref: Graph::g2bmm / Graph::gbmml, include/graph.h:80-90; shapes G2BMMOp::computeShape / GBMMLOp::computeShape,
+// src/Graph/operator.cc:1414-1422,1552-1560; validity :1390-1412,1528-1550.
+extern "C" int petb200_graph_g2bmm(petb200_graph *g, int a, int b, int width, int dilation, int *out) {
+    if (!g || !out)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, a);
+    G_CHECK_T(g, b);
+    const Dim &ad = g->tensors[a].dims, &bd = g->tensors[b].dims;
+    if (ad.size() != 3 || ad != bd || width < 0 || dilation <= 0)
+        return g->fail(PETB200_ERR_INVALID, "g2bmm: operands must be 3-D and of equal shape, width >= 0, dilation > 0");
+    Operator op;
+    op.type = G2BMM;
+    op.inputs = {a, b};
+    op.width = width, op.dilation = dilation;
+    *out = g->new_tensor(Dim{ad[0], ad[1], 2 * width + 1});
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_gbmml(petb200_graph *g, int a, int b, int dilation, int *out) {
+    if (!g || !out)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, a);
+    G_CHECK_T(g, b);
+    const Dim &ad = g->tensors[a].dims, &bd = g->tensors[b].dims;
+    if (ad.size() != 3 || bd.size() != 3 || ad[0] != bd[0] || ad[1] != bd[1] || ad[2] % 2 != 1 || dilation <= 0)
+        return g->fail(PETB200_ERR_INVALID, "gbmml: operands must be [b,n,2w+1] and [b,n,m], dilation > 0");
+    Operator op;
+    op.type = GBMML;
+    op.inputs = {a, b};
+    op.width = (ad[2] - 1) / 2, op.dilation = dilation;
+    *out = g->new_tensor(Dim{ad[0], ad[1], bd[2]});
     op.outputs = {*out};
     g->add_op(std::move(op));
     return PETB200_OK;
@@ -1346,7 +1442,7 @@ extern "C" int petb200_graph_perf(petb200_graph *g, int rounds, int warmup, floa
                 for (int t : op.inputs)
                     key.insert(key.end(), g->tensors[t].dims.begin(), g->tensors[t].dims.end());
                 int attrs[] = {op.ph, op.pw, op.sh, op.sw, op.dh, op.dw, op.act, op.bias >= 0, op.transA, op.transB, op.dim, op.num,
-                               op.tr.split, op.tr.factor, op.tr.ngroups, op.win[0], op.win[1], op.win[2], op.win[3]};
+                               op.tr.split, op.tr.factor, op.tr.ngroups, op.win[0], op.win[1], op.win[2], op.win[3], op.oph, op.opw, op.width, op.dilation};
                 key.insert(key.end(), attrs, attrs + sizeof attrs / sizeof attrs[0]);
                 key.insert(key.end(), op.tr.flat, op.tr.flat + 8);
                 key.insert(key.end(), op.tr.group_sizes, op.tr.group_sizes + 8);

@@ -24,6 +24,9 @@ GRAPH_SYMBOLS = {
     "petb200_graph_tensor_dims": (_i, [_vp, _i, _ip]),
     "petb200_graph_conv": (_i, [_vp] + [_i] * 10 + [_ip]),
     "petb200_graph_conv3d": (_i, [_vp, _i, _i, _i, _ip, _ip, _ip, _i, _ip]),
+    "petb200_graph_convtrans": (_i, [_vp] + [_i] * 12 + [_ip]),
+    "petb200_graph_g2bmm": (_i, [_vp, _i, _i, _i, _i, _ip]),
+    "petb200_graph_gbmml": (_i, [_vp, _i, _i, _i, _ip]),
     "petb200_graph_matmul": (_i, [_vp, _i, _i, _i, _i, _i, _i, _ip]),
     "petb200_graph_transpose": (_i, [_vp, _i, C.POINTER(L.TransposeDesc), _ip]),
     "petb200_graph_pad": (_i, [_vp, _i, _ip, _ip, _ip]),
@@ -123,6 +126,17 @@ class Graph:
 
     def conv3d(self, input, weight, pad, stride=(1, 1, 1), dil=(1, 1, 1), bias=None, act="none"):
         return self._out(self.lib.petb200_graph_conv3d, input.id, weight.id, _tid(bias), L.ints(pad), L.ints(stride), L.ints(dil), L.ACT[act])
+
+    def convTrans(self, input, weight, ph, pw, sh=1, sw=1, dh=1, dw=1, oph=0, opw=0, bias=None, act="none"):
+        """ConvTransOp: input {n,h,w,f}, weight {r,s,f,c} -> {n,oh,ow,c} (ref: Graph::convTrans, src/ffi/ffi_pet.cc:45-48)."""
+        return self._out(self.lib.petb200_graph_convtrans, input.id, weight.id, _tid(bias), ph, pw, sh, sw, dh, dw, oph, opw,
+                         L.ACT[act])
+
+    def g2bmm(self, A, B, width, dilation=1):
+        return self._out(self.lib.petb200_graph_g2bmm, A.id, B.id, width, dilation)
+
+    def gbmml(self, A, B, dilation=1):
+        return self._out(self.lib.petb200_graph_gbmml, A.id, B.id, dilation)
 
     def matmul(self, A, B, transA=False, transB=False, bias=None, act="none"):
         return self._out(self.lib.petb200_graph_matmul, A.id, B.id, _tid(bias), int(transA), int(transB), L.ACT[act])

@@ -104,6 +104,38 @@ def test_r3d18_reduced(ctx):
     assert rel_err(y, want) <= TOL
 
 
+def test_convtrans_and_banded_attention_in_a_graph(ctx, oracle):
+    """convTrans -> relu, and g2bmm -> softmax -> gbmml (sliding-window attention) built with the reference's method
+    names, executed as a captured graph, against the oracle."""
+    from pet_b200.graph import Graph
+    rng = np.random.default_rng(12)
+    g = Graph(ctx)
+    x = g.tensor([2, 8, 8, 32])
+    w = g.tensor([4, 4, 32, 16], weight=True)
+    up = g.relu(g.convTrans(x, w, 1, 1, 2, 2))
+    q, k, v = g.tensor([2, 96, 32]), g.tensor([2, 96, 32]), g.tensor([2, 96, 32])
+    att = g.gbmml(g.softmax(g.g2bmm(q, k, 8, 2), -1), v, 2)
+    g.setOutputs([up, att])
+    g.compile()
+    assert tuple(up.dims) == (2, 16, 16, 16) and tuple(att.dims) == (2, 96, 32)
+    data = {t: rng.standard_normal(t.dims).astype(np.float32) * 0.5 for t in (x, w, q, k, v)}
+    for t, a in data.items():
+        g.set_data(t, a)
+    g.run()
+    g.run()
+    torch.cuda.synchronize()
+    ctx.sync_check()
+    names = [n for n, _ in g.steps()]
+    assert names.count("convtrans") == 1 and "g2bmm" in names and "gbmml" in names
+    want_up = np.maximum(oracle.convtrans(data[x], data[w], pad=(1, 1), stride=(2, 2), wide=True), 0)
+    assert rel_err(g.get_data(up), want_up) <= TOL
+    sc = oracle.g2bmm(data[q], data[k], 8, 2, wide=True)
+    want_att = oracle.gbmml(oracle.softmax(sc), data[v], 2, wide=True)
+    assert rel_err(g.get_data(att), want_att) <= TOL
+    total, per = g.perf(rounds=10, warmup=3)
+    assert len(per) == len(names) and total > 0
+
+
 def test_perf_and_time_entry_points(ctx):
     from pet_b200 import configs
     x, w = configs.c2_tensors(c=64, hw=32, k=64)
@@ -132,5 +164,11 @@ def test_graph_rejects_invalid_operators(ctx):
         g.reshape(x, [5, -1])
     with pytest.raises(PetError):
         g.softmax(x, 1)                                  # only the last axis is built
+    with pytest.raises(PetError):
+        g.convTrans(x, g.tensor([3, 3, 8, 4]), 1, 1, 1, 1, 2, 2)  # dilated transposed convolution
+    with pytest.raises(PetError):
+        g.g2bmm(g.tensor([1, 8, 4]), g.tensor([1, 9, 4]), 2)       # operand shapes differ
+    with pytest.raises(PetError):
+        g.gbmml(g.tensor([1, 8, 4]), g.tensor([1, 8, 4]))          # band extent must be odd
     with pytest.raises(PetError):
         g.run()                                          # not compiled
