@@ -16,88 +16,105 @@ namespace {
 
 constexpr int kTI = 32;   // rows of one class per block
 constexpr int kKC = 32;   // reduction chunk held in shared memory (G2BMM)
-constexpr int kTJ = 128;  // band columns per block (G2BMM)
+constexpr int kTJ = 224;  // band columns per block (G2BMM)
+constexpr int kKeys = 256; // keys per block (G2BMM): kTI + kTJ
 constexpr int kGJ = 64;   // band columns per reduction chunk (GBMML)
 constexpr int kGKR = 96;  // key rows per chunk: kTI + kGJ - 1, rounded up
 constexpr int kGM = 64;   // output columns per block (GBMML)
 
 struct BandGeom {
     int n, m, w, d, tiles_per_class;
+    int mtiles, chunks_per_split; // GBMML: column tiles of y; band-column chunks summed by one block
 };
 
-// grid (ceil((2w+1)/kTJ), d * tiles_per_class, b), 256 threads.  Thread (ti = tid/32, tj = tid%32) owns rows 4ti..4ti+3 and
-// band columns 4tj..4tj+3 of the tile: out(R, J) = sum_k Qs[k][R] * Ks[k][R + J], key rows 4(ti+tj) .. +6 per step.
-__global__ void __launch_bounds__(256) k_g2bmm(const float *__restrict__ q, const float *__restrict__ kk, float *__restrict__ y, BandGeom g) {
+// grid (ceil((2w+1)/kTJ), d * tiles_per_class, b), 128 threads.  In (row, key) coordinates the band is an ordinary product
+// P[R][key] = q[R] . kk[key]: a block forms the kTI x kKeys rectangle of it that holds band columns [J0, J0 + kTJ) of its
+// rows (the parallelogram key - R in [0, kTJ)) with an 8 x 8 register tile per thread — rows 8ti..8ti+7, keys
+// 4tj..4tj+3 and 128+4tj..128+4tj+3, so that a warp's 16-byte reads of the key tile are consecutive — and writes the
+// parallelogram out through shared memory, a warp storing 32 consecutive band columns of one row.
+__global__ void __launch_bounds__(128) k_g2bmm(const float *__restrict__ q, const float *__restrict__ kk, float *__restrict__ y, BandGeom g) {
     pdl_prologue();
     __shared__ __align__(16) float Qs[kKC][kTI];
-    __shared__ __align__(16) float Ks[kKC][kTI + kTJ]; // reused as the [kTI][kTJ + 1] output stage
+    __shared__ __align__(16) float Ks[kKC][kKeys]; // reused as the [kTI][kKeys] output stage
     const int tid = threadIdx.x, ti = tid >> 5, tj = tid & 31;
     const int rho = blockIdx.y / g.tiles_per_class, R0 = (blockIdx.y % g.tiles_per_class) * kTI, J0 = blockIdx.x * kTJ;
     const int bw = 2 * g.w + 1;
     const size_t bb = (size_t)blockIdx.z * g.n;
-    float acc[4][4];
+    float acc[8][8];
 #pragma unroll
-    for (int a = 0; a < 4; ++a)
+    for (int a = 0; a < 8; ++a)
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 8; ++c)
             acc[a][c] = 0.f;
     const bool vec = (g.m & 3) == 0 && ((reinterpret_cast<size_t>(q) | reinterpret_cast<size_t>(kk)) & 15) == 0;
     for (int k0 = 0; k0 < g.m; k0 += kKC) {
-        // rows of the class: one 16-byte piece of a row per thread and step; consecutive lanes take consecutive rows, so
-        // the transposing stores into [k][row] are conflict-free
-        for (int e = tid; e < (kTI + (kTI + kTJ)) * (kKC / 4); e += 256) {
-            const bool is_q = e < kTI * (kKC / 4);
-            const int e2 = is_q ? e : e - kTI * (kKC / 4);
-            const int rows = is_q ? kTI : kTI + kTJ;
-            const int row = e2 % rows, kq = (e2 / rows) * 4;
-            const long long cls = is_q ? (long long)R0 + row : (long long)R0 + row + J0 - g.w; // index inside the class
-            const long long i = (long long)rho + (long long)g.d * cls;
-            float v[4] = {0.f, 0.f, 0.f, 0.f};
-            if (cls >= 0 && i < g.n) {
-                const float *src = (is_q ? q : kk) + (bb + (size_t)i) * g.m + k0 + kq;
-                if (vec && k0 + kq + 3 < g.m) {
-                    const float4 t = __ldg(reinterpret_cast<const float4 *>(src));
-                    v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
-                } else {
+        // One 16-byte piece of a row per thread and step: eight lanes read the 128 contiguous bytes of a row, a warp four
+        // consecutive rows.  The tiles are stored transposed ([k][row]) with the 4-row groups of a k row XOR-swizzled by
+        // k / 4, which makes both these scattered stores and the 16-byte reads of the product loop conflict-free.  Loads
+        // are issued in batches so that their latencies overlap.
+        constexpr int kPieces = (kTI + kKeys) * (kKC / 4) / 128, kBatch = 6;
+        static_assert(kPieces % kBatch == 0 && (kTI + kKeys) * (kKC / 4) % 128 == 0, "load loop of k_g2bmm");
+#pragma unroll 1
+        for (int it0 = 0; it0 < kPieces; it0 += kBatch) {
+            float4 buf[kBatch];
 #pragma unroll
-                    for (int x = 0; x < 4; ++x)
-                        if (k0 + kq + x < g.m)
-                            v[x] = __ldg(src + x);
+            for (int b = 0; b < kBatch; ++b) {
+                const int e = tid + 128 * (it0 + b), kq = (e & 7) * 4, rall = e >> 3; // rall < kTI: a row of q
+                const bool is_q = rall < kTI;
+                const int row = is_q ? rall : rall - kTI;
+                const long long cls = is_q ? (long long)R0 + row : (long long)R0 + row + J0 - g.w; // index inside the class
+                const long long i = (long long)rho + (long long)g.d * cls;
+                float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (cls >= 0 && i < g.n) {
+                    const float *src = (is_q ? q : kk) + (bb + (size_t)i) * g.m + k0 + kq;
+                    if (vec && k0 + kq + 3 < g.m) {
+                        t = __ldg(reinterpret_cast<const float4 *>(src));
+                    } else {
+                        if (k0 + kq < g.m) t.x = __ldg(src);
+                        if (k0 + kq + 1 < g.m) t.y = __ldg(src + 1);
+                        if (k0 + kq + 2 < g.m) t.z = __ldg(src + 2);
+                        if (k0 + kq + 3 < g.m) t.w = __ldg(src + 3);
+                    }
                 }
+                buf[b] = t;
             }
 #pragma unroll
-            for (int x = 0; x < 4; ++x) {
-                if (is_q)
-                    Qs[kq + x][row] = v[x];
-                else
-                    Ks[kq + x][row] = v[x];
+            for (int b = 0; b < kBatch; ++b) {
+                const int e = tid + 128 * (it0 + b), kq = (e & 7) * 4, rall = e >> 3;
+                const bool is_q = rall < kTI;
+                const int row = is_q ? rall : rall - kTI;
+                const int col = ((((row >> 2) ^ (kq >> 2)) << 2) | (row & 3)); // swizzled inside each aligned run of 8 groups
+                float *dstp = is_q ? &Qs[kq][col] : &Ks[kq][col];
+                const int pitch = is_q ? kTI : kKeys;
+                dstp[0] = buf[b].x, dstp[pitch] = buf[b].y, dstp[2 * pitch] = buf[b].z, dstp[3 * pitch] = buf[b].w;
             }
         }
         __syncthreads();
-#pragma unroll 8
+#pragma unroll 4
         for (int k = 0; k < kKC; ++k) {
-            const float4 qa = *reinterpret_cast<const float4 *>(&Qs[k][4 * ti]);
-            const float4 ka = *reinterpret_cast<const float4 *>(&Ks[k][4 * (ti + tj)]);
-            const float4 kb = *reinterpret_cast<const float4 *>(&Ks[k][4 * (ti + tj) + 4]);
-            const float qv[4] = {qa.x, qa.y, qa.z, qa.w};
+            const int h = k >> 2; // the swizzle of this k row
+            const float4 qa = *reinterpret_cast<const float4 *>(&Qs[k][((2 * ti) ^ h) << 2]);
+            const float4 qb = *reinterpret_cast<const float4 *>(&Qs[k][((2 * ti + 1) ^ h) << 2]);
+            const float4 ka = *reinterpret_cast<const float4 *>(&Ks[k][(tj ^ h) << 2]);
+            const float4 kb = *reinterpret_cast<const float4 *>(&Ks[k][kKeys / 2 + ((tj ^ h) << 2)]);
+            const float qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
             const float kv[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
 #pragma unroll
-            for (int a = 0; a < 4; ++a)
+            for (int a = 0; a < 8; ++a)
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    acc[a][c] = fmaf(qv[a], kv[a + c], acc[a][c]);
+                for (int c = 0; c < 8; ++c)
+                    acc[a][c] = fmaf(qv[a], kv[c], acc[a][c]);
         }
         __syncthreads();
     }
-    // through shared memory so that a warp writes 32 consecutive band columns of one row
-    float(*stage)[kTJ + 1] = reinterpret_cast<float(*)[kTJ + 1]>(&Ks[0][0]);
+    float(*stage)[kKeys] = Ks;
 #pragma unroll
-    for (int a = 0; a < 4; ++a)
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-            stage[4 * ti + a][4 * tj + c] = acc[a][c];
+    for (int a = 0; a < 8; ++a) {
+        *reinterpret_cast<float4 *>(&stage[8 * ti + a][4 * tj]) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+        *reinterpret_cast<float4 *>(&stage[8 * ti + a][kKeys / 2 + 4 * tj]) = make_float4(acc[a][4], acc[a][5], acc[a][6], acc[a][7]);
+    }
     __syncthreads();
-    for (int r = ti; r < kTI; r += 8) {
+    for (int r = ti; r < kTI; r += 4) {
         const long long i = (long long)rho + (long long)g.d * (R0 + r);
         if (i >= g.n)
             continue;
@@ -106,13 +123,15 @@ __global__ void __launch_bounds__(256) k_g2bmm(const float *__restrict__ q, cons
         for (int c = 0; c < kTJ / 32; ++c) {
             const int j = tj + 32 * c;
             if (J0 + j < bw)
-                dst[j] = stage[r][j];
+                dst[j] = stage[r][r + j]; // band column j of row r is key r + j of the tile
         }
     }
 }
-static_assert(sizeof(float) * kKC * (kTI + kTJ) >= sizeof(float) * kTI * (kTJ + 1), "output stage must fit the key tile");
+static_assert(kKeys == kTI + kTJ && kTJ % 32 == 0 && kKeys == 256 && kKC == kTI, "tile geometry of k_g2bmm");
 
-// grid (ceil(m/kGM), d * tiles_per_class, b), 128 threads.  Thread (ti = tid/16, tk = tid%16) owns rows 4ti..4ti+3 and
+// grid (ceil(m/kGM) * splits, d * tiles_per_class, b), 128 threads.  The band columns are split over `splits` blocks so that
+// a long band still fills the GPU; split s writes its partial sums to y + s * (b*n*m) (the caller passes scratch there and
+// k_band_reduce adds the parts in split order).  Thread (ti = tid/16, tk = tid%16) owns rows 4ti..4ti+3 and
 // output columns 4tk..4tk+3.  A chunk of kGJ band columns is re-indexed by key: Ps[key][R] = p[R][key - R] (zero outside
 // the chunk), which turns the chunk into a plain [kTI x kGKR] x [kGKR x kGM] product.
 __global__ void __launch_bounds__(128) k_gbmml(const float *__restrict__ p, const float *__restrict__ v, float *__restrict__ y, BandGeom g) {
@@ -120,9 +139,12 @@ __global__ void __launch_bounds__(128) k_gbmml(const float *__restrict__ p, cons
     __shared__ __align__(16) float Ps[kGKR][kTI + 4];
     __shared__ __align__(16) float Vs[kGKR][kGM];
     const int tid = threadIdx.x, ti = tid >> 4, tk = tid & 15;
-    const int rho = blockIdx.y / g.tiles_per_class, R0 = (blockIdx.y % g.tiles_per_class) * kTI, M0 = blockIdx.x * kGM;
+    const int rho = blockIdx.y / g.tiles_per_class, R0 = (blockIdx.y % g.tiles_per_class) * kTI;
+    const int M0 = ((int)blockIdx.x % g.mtiles) * kGM, split = (int)blockIdx.x / g.mtiles;
     const int bw = 2 * g.w + 1;
     const size_t bb = (size_t)blockIdx.z * g.n;
+    y += (size_t)split * gridDim.z * g.n * g.m;
+    const int J_begin = split * g.chunks_per_split * kGJ, J_end = min(bw, J_begin + g.chunks_per_split * kGJ);
     const bool vec = (g.m & 3) == 0 && ((reinterpret_cast<size_t>(v) | reinterpret_cast<size_t>(y)) & 15) == 0;
     float acc[4][4];
 #pragma unroll
@@ -130,34 +152,58 @@ __global__ void __launch_bounds__(128) k_gbmml(const float *__restrict__ p, cons
 #pragma unroll
         for (int c = 0; c < 4; ++c)
             acc[a][c] = 0.f;
-    for (int J0 = 0; J0 < bw; J0 += kGJ) {
-        // key row `kr` of the chunk is class index R0 + kr + J0 - w
-        for (int e = tid; e < kGKR * kTI; e += 128) {
-            const int r = e / kGKR, kr = e % kGKR, jj = kr - r; // consecutive threads: consecutive band columns of one row
-            const long long i = (long long)rho + (long long)g.d * (R0 + r);
-            const long long kcls = (long long)R0 + kr + J0 - g.w, ki = (long long)rho + (long long)g.d * kcls;
-            float val = 0.f;
-            if (jj >= 0 && jj < kGJ && J0 + jj < bw && i < g.n && kcls >= 0 && ki < g.n)
-                val = __ldg(p + (bb + (size_t)i) * bw + J0 + jj);
-            Ps[kr][r] = val;
-        }
-        for (int e = tid; e < kGKR * (kGM / 4); e += 128) {
-            const int kr = e / (kGM / 4), c4 = (e % (kGM / 4)) * 4;
-            const long long kcls = (long long)R0 + kr + J0 - g.w, ki = (long long)rho + (long long)g.d * kcls;
-            float t[4] = {0.f, 0.f, 0.f, 0.f};
-            if (kcls >= 0 && ki < g.n) {
-                const float *src = v + (bb + (size_t)ki) * g.m + M0 + c4;
-                if (vec && M0 + c4 + 3 < g.m) {
-                    const float4 t4 = __ldg(reinterpret_cast<const float4 *>(src));
-                    t[0] = t4.x, t[1] = t4.y, t[2] = t4.z, t[3] = t4.w;
-                } else {
+    for (int J0 = J_begin; J0 < J_end; J0 += kGJ) {
+        // key row `kr` of the chunk is class index R0 + kr + J0 - w.  Loads are issued in batches so that their latencies
+        // overlap.
+        constexpr int kPIters = kGKR * kTI / 128, kVIters = kGKR * (kGM / 4) / 128, kPB = 8, kVB = 4;
+        static_assert(kPIters % kPB == 0 && kVIters % kVB == 0 && kGKR * kTI % 128 == 0 && kGKR * (kGM / 4) % 128 == 0, "fill loops of k_gbmml");
+#pragma unroll 1
+        for (int it0 = 0; it0 < kPIters; it0 += kPB) {
+            float buf[kPB];
 #pragma unroll
-                    for (int x = 0; x < 4; ++x)
-                        if (M0 + c4 + x < g.m)
-                            t[x] = __ldg(src + x);
-                }
+            for (int b = 0; b < kPB; ++b) {
+                const int e = tid + 128 * (it0 + b);
+                const int r = e / kGKR, kr = e % kGKR, jj = kr - r; // consecutive threads: consecutive band columns of one row
+                const long long i = (long long)rho + (long long)g.d * (R0 + r);
+                const long long kcls = (long long)R0 + kr + J0 - g.w, ki = (long long)rho + (long long)g.d * kcls;
+                float val = 0.f;
+                if (jj >= 0 && jj < kGJ && J0 + jj < J_end && i < g.n && kcls >= 0 && ki < g.n)
+                    val = __ldg(p + (bb + (size_t)i) * bw + J0 + jj);
+                buf[b] = val;
             }
-            *reinterpret_cast<float4 *>(&Vs[kr][c4]) = make_float4(t[0], t[1], t[2], t[3]);
+#pragma unroll
+            for (int b = 0; b < kPB; ++b) {
+                const int e = tid + 128 * (it0 + b);
+                Ps[e % kGKR][e / kGKR] = buf[b];
+            }
+        }
+#pragma unroll 1
+        for (int it0 = 0; it0 < kVIters; it0 += kVB) {
+            float4 buf[kVB];
+#pragma unroll
+            for (int b = 0; b < kVB; ++b) {
+                const int e = tid + 128 * (it0 + b);
+                const int kr = e / (kGM / 4), c4 = (e % (kGM / 4)) * 4;
+                const long long kcls = (long long)R0 + kr + J0 - g.w, ki = (long long)rho + (long long)g.d * kcls;
+                float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (kcls >= 0 && ki < g.n) {
+                    const float *src = v + (bb + (size_t)ki) * g.m + M0 + c4;
+                    if (vec && M0 + c4 + 3 < g.m) {
+                        t = __ldg(reinterpret_cast<const float4 *>(src));
+                    } else {
+                        if (M0 + c4 < g.m) t.x = __ldg(src);
+                        if (M0 + c4 + 1 < g.m) t.y = __ldg(src + 1);
+                        if (M0 + c4 + 2 < g.m) t.z = __ldg(src + 2);
+                        if (M0 + c4 + 3 < g.m) t.w = __ldg(src + 3);
+                    }
+                }
+                buf[b] = t;
+            }
+#pragma unroll
+            for (int b = 0; b < kVB; ++b) {
+                const int e = tid + 128 * (it0 + b);
+                *reinterpret_cast<float4 *>(&Vs[e / (kGM / 4)][(e % (kGM / 4)) * 4]) = buf[b];
+            }
         }
         __syncthreads();
 #pragma unroll 8
@@ -192,6 +238,17 @@ __global__ void __launch_bounds__(128) k_gbmml(const float *__restrict__ p, cons
 }
 static_assert(kGKR >= kTI + kGJ - 1 && kGKR % 8 == 0, "key rows of a chunk");
 
+// y[i] = parts[0][i] + parts[1][i] + ... in split order (the sum does not depend on timing).
+__global__ void __launch_bounds__(256) k_band_reduce(const float *__restrict__ parts, float *__restrict__ y, size_t total, int splits) {
+    pdl_prologue();
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float acc = parts[i];
+        for (int s = 1; s < splits; ++s)
+            acc += parts[(size_t)s * total + i];
+        y[i] = acc;
+    }
+}
+
 int check_band(petb200_ctx *ctx, const void *a, const void *b, const void *y, int bs, int n, int m, int w, int d, BandGeom *g, int *ytiles) {
     if (!ctx)
         return PETB200_ERR_INVALID;
@@ -223,7 +280,7 @@ extern "C" int petb200_g2bmm_run(petb200_ctx *ctx, const float *q, const float *
     if (rc)
         return rc;
     const dim3 grid((unsigned)((2 * w + 1 + kTJ - 1) / kTJ), (unsigned)ytiles, (unsigned)bs);
-    launch_pdl(k_g2bmm, grid, dim3(256), 0, (cudaStream_t)stream, q, k, y, g);
+    launch_pdl(k_g2bmm, grid, dim3(128), 0, (cudaStream_t)stream, q, k, y, g);
     return launched(ctx, "k_g2bmm");
 }
 
@@ -235,9 +292,28 @@ extern "C" int petb200_gbmml_run(petb200_ctx *ctx, const float *p, const float *
     int rc = check_band(ctx, p, v, y, bs, n, m, w, d, &g, &ytiles);
     if (rc)
         return rc;
-    const dim3 grid((unsigned)((m + kGM - 1) / kGM), (unsigned)ytiles, (unsigned)bs);
-    launch_pdl(k_gbmml, grid, dim3(128), 0, (cudaStream_t)stream, p, v, y, g);
-    return launched(ctx, "k_gbmml");
+    // split the band columns until there are about four blocks per SM
+    const int chunks = (2 * w + 1 + kGJ - 1) / kGJ;
+    g.mtiles = (m + kGM - 1) / kGM;
+    const long long base = (long long)g.mtiles * ytiles * bs;
+    int splits = (int)std::min<long long>(std::min(chunks, 8), std::max<long long>(1, (4LL * ctx->sm_count + base - 1) / base));
+    g.chunks_per_split = (chunks + splits - 1) / splits;
+    splits = (chunks + g.chunks_per_split - 1) / g.chunks_per_split;
+    const size_t total = (size_t)bs * n * m;
+    float *dst = y;
+    if (splits > 1) {
+        if (ctx->band_scratch.bytes < total * splits * 4 && ctx->band_scratch.alloc(total * splits * 4) != cudaSuccess)
+            return fail(ctx, PETB200_ERR_NOMEM, "gbmml: scratch for %d partial sums failed", splits);
+        dst = (float *)ctx->band_scratch.p;
+    }
+    const dim3 grid((unsigned)(g.mtiles * splits), (unsigned)ytiles, (unsigned)bs);
+    launch_pdl(k_gbmml, grid, dim3(128), 0, (cudaStream_t)stream, p, v, dst, g);
+    rc = launched(ctx, "k_gbmml");
+    if (rc || splits == 1)
+        return rc;
+    const int blocks = (int)std::min<size_t>((total + 255) / 256, (size_t)ctx->sm_count * 8);
+    launch_pdl(k_band_reduce, blocks, 256, 0, (cudaStream_t)stream, (const float *)dst, y, total, splits);
+    return launched(ctx, "k_band_reduce");
 }
 
 // Milliseconds per launch on library-owned operands, the way G2BMMOp::perf / GBMMLOp::perf time the reference's kernels

@@ -9,6 +9,25 @@
 #include <string>
 #include <vector>
 
+namespace petb200 {
+struct DevBuf {
+    void *p = nullptr;
+    size_t bytes = 0;
+    ~DevBuf() {
+        if (p)
+            cudaFree(p);
+    }
+    cudaError_t alloc(size_t n) {
+        if (p) {
+            cudaFree(p);
+            p = nullptr;
+        }
+        bytes = n;
+        return n ? cudaMalloc(&p, n) : cudaSuccess;
+    }
+};
+} // namespace petb200
+
 struct petb200_ctx {
     int device = 0;
     int sm_count = 148;
@@ -17,6 +36,7 @@ struct petb200_ctx {
     uint64_t launches = 0;
     std::string err;
     int *d_status = nullptr; // device word kernels write when a bounded wait expires
+    petb200::DevBuf band_scratch; // partial sums of a banded product split over its band columns (grown on demand)
 };
 
 struct petb200_plan {
@@ -93,23 +113,6 @@ inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     }
     (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...); // errors surface through launched()
 }
-
-struct DevBuf {
-    void *p = nullptr;
-    size_t bytes = 0;
-    ~DevBuf() {
-        if (p)
-            cudaFree(p);
-    }
-    cudaError_t alloc(size_t n) {
-        if (p) {
-            cudaFree(p);
-            p = nullptr;
-        }
-        bytes = n;
-        return n ? cudaMalloc(&p, n) : cudaSuccess;
-    }
-};
 
 __host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
