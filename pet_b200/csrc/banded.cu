@@ -18,8 +18,8 @@ constexpr int kTI = 32;   // rows of one class per block
 constexpr int kKC = 32;   // reduction chunk held in shared memory (G2BMM)
 constexpr int kTJ = 224;  // band columns per block (G2BMM)
 constexpr int kKeys = 256; // keys per block (G2BMM): kTI + kTJ
-constexpr int kGJ = 64;   // band columns per reduction chunk (GBMML)
-constexpr int kGKR = 96;  // key rows per chunk: kTI + kGJ - 1, rounded up
+constexpr int kGJ = 96;   // band columns per reduction chunk (GBMML)
+constexpr int kGKR = 128; // key rows per chunk: kTI + kGJ - 1, rounded up
 constexpr int kGM = 64;   // output columns per block (GBMML)
 
 struct BandGeom {
@@ -47,27 +47,20 @@ __global__ void __launch_bounds__(128) k_g2bmm(const float *__restrict__ q, cons
         for (int c = 0; c < 8; ++c)
             acc[a][c] = 0.f;
     const bool vec = (g.m & 3) == 0 && ((reinterpret_cast<size_t>(q) | reinterpret_cast<size_t>(kk)) & 15) == 0;
+    const int cls_lim = (g.n - rho + g.d - 1) / g.d; // class indices 0 .. cls_lim-1 are rows of the sequence
     for (int k0 = 0; k0 < g.m; k0 += kKC) {
         // One 16-byte piece of a row per thread and step: eight lanes read the 128 contiguous bytes of a row, a warp four
         // consecutive rows.  The tiles are stored transposed ([k][row]) with the 4-row groups of a k row XOR-swizzled by
         // k / 4, which makes both these scattered stores and the 16-byte reads of the product loop conflict-free.  Loads
         // are issued in batches so that their latencies overlap.
-        constexpr int kPieces = (kTI + kKeys) * (kKC / 4) / 128, kBatch = 6;
-        static_assert(kPieces % kBatch == 0 && (kTI + kKeys) * (kKC / 4) % 128 == 0, "load loop of k_g2bmm");
-#pragma unroll 1
-        for (int it0 = 0; it0 < kPieces; it0 += kBatch) {
-            float4 buf[kBatch];
-#pragma unroll
-            for (int b = 0; b < kBatch; ++b) {
-                const int e = tid + 128 * (it0 + b), kq = (e & 7) * 4, rall = e >> 3; // rall < kTI: a row of q
-                const bool is_q = rall < kTI;
-                const int row = is_q ? rall : rall - kTI;
-                const long long cls = is_q ? (long long)R0 + row : (long long)R0 + row + J0 - g.w; // index inside the class
-                const long long i = (long long)rho + (long long)g.d * cls;
+        {
+            const int kq = (tid & 7) * 4, r_lo = tid >> 3; // this thread's piece of a row, and its first row (then every 16th)
+            const bool full = vec && k0 + kq + 3 < g.m;
+            auto fetch = [&](const float *base, int cls) {
                 float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (cls >= 0 && i < g.n) {
-                    const float *src = (is_q ? q : kk) + (bb + (size_t)i) * g.m + k0 + kq;
-                    if (vec && k0 + kq + 3 < g.m) {
+                if (cls >= 0 && cls < cls_lim) {
+                    const float *src = base + (bb + (size_t)rho + (size_t)g.d * cls) * g.m + k0 + kq;
+                    if (full) {
                         t = __ldg(reinterpret_cast<const float4 *>(src));
                     } else {
                         if (k0 + kq < g.m) t.x = __ldg(src);
@@ -76,17 +69,25 @@ __global__ void __launch_bounds__(128) k_g2bmm(const float *__restrict__ q, cons
                         if (k0 + kq + 3 < g.m) t.w = __ldg(src + 3);
                     }
                 }
-                buf[b] = t;
-            }
+                return t;
+            };
+            auto put = [&](float *tile, int pitch, int row, const float4 &t) {
+                float *dstp = tile + kq * pitch + ((((row >> 2) ^ (kq >> 2)) << 2) | (row & 3)); // swizzled inside each aligned run of 8 groups
+                dstp[0] = t.x, dstp[pitch] = t.y, dstp[2 * pitch] = t.z, dstp[3 * pitch] = t.w;
+            };
+            const float4 q0 = fetch(q, R0 + r_lo), q1 = fetch(q, R0 + r_lo + 16);
+            put(&Qs[0][0], kTI, r_lo, q0);
+            put(&Qs[0][0], kTI, r_lo + 16, q1);
+            const int kcls0 = R0 + r_lo + J0 - g.w;
+#pragma unroll 1
+            for (int it0 = 0; it0 < kKeys / 16; it0 += 8) {
+                float4 buf[8];
 #pragma unroll
-            for (int b = 0; b < kBatch; ++b) {
-                const int e = tid + 128 * (it0 + b), kq = (e & 7) * 4, rall = e >> 3;
-                const bool is_q = rall < kTI;
-                const int row = is_q ? rall : rall - kTI;
-                const int col = ((((row >> 2) ^ (kq >> 2)) << 2) | (row & 3)); // swizzled inside each aligned run of 8 groups
-                float *dstp = is_q ? &Qs[kq][col] : &Ks[kq][col];
-                const int pitch = is_q ? kTI : kKeys;
-                dstp[0] = buf[b].x, dstp[pitch] = buf[b].y, dstp[2 * pitch] = buf[b].z, dstp[3 * pitch] = buf[b].w;
+                for (int b = 0; b < 8; ++b)
+                    buf[b] = fetch(kk, kcls0 + 16 * (it0 + b));
+#pragma unroll
+                for (int b = 0; b < 8; ++b)
+                    put(&Ks[0][0], kKeys, r_lo + 16 * (it0 + b), buf[b]);
             }
         }
         __syncthreads();
@@ -136,8 +137,9 @@ static_assert(kKeys == kTI + kTJ && kTJ % 32 == 0 && kKeys == 256 && kKC == kTI,
 // the chunk), which turns the chunk into a plain [kTI x kGKR] x [kGKR x kGM] product.
 __global__ void __launch_bounds__(128) k_gbmml(const float *__restrict__ p, const float *__restrict__ v, float *__restrict__ y, BandGeom g) {
     pdl_prologue();
-    __shared__ __align__(16) float Ps[kGKR][kTI + 4];
-    __shared__ __align__(16) float Vs[kGKR][kGM];
+    extern __shared__ __align__(16) float band_smem[];
+    float(*Ps)[kTI + 4] = reinterpret_cast<float(*)[kTI + 4]>(band_smem);                     // [kGKR][kTI + 4]
+    float(*Vs)[kGM] = reinterpret_cast<float(*)[kGM]>(band_smem + kGKR * (kTI + 4));          // [kGKR][kGM]
     const int tid = threadIdx.x, ti = tid >> 4, tk = tid & 15;
     const int rho = blockIdx.y / g.tiles_per_class, R0 = (blockIdx.y % g.tiles_per_class) * kTI;
     const int M0 = ((int)blockIdx.x % g.mtiles) * kGM, split = (int)blockIdx.x / g.mtiles;
@@ -146,6 +148,9 @@ __global__ void __launch_bounds__(128) k_gbmml(const float *__restrict__ p, cons
     y += (size_t)split * gridDim.z * g.n * g.m;
     const int J_begin = split * g.chunks_per_split * kGJ, J_end = min(bw, J_begin + g.chunks_per_split * kGJ);
     const bool vec = (g.m & 3) == 0 && ((reinterpret_cast<size_t>(v) | reinterpret_cast<size_t>(y)) & 15) == 0;
+    const int cls_lim = (g.n - rho + g.d - 1) / g.d;    // class indices 0 .. cls_lim-1 are rows of the sequence
+    const int rows_valid = min(kTI, cls_lim - R0);      // rows of this tile inside the sequence
+    const size_t p_step = (size_t)g.d * bw - 1;         // next row of the class, one band column to the left
     float acc[4][4];
 #pragma unroll
     for (int a = 0; a < 4; ++a)
@@ -153,56 +158,53 @@ __global__ void __launch_bounds__(128) k_gbmml(const float *__restrict__ p, cons
         for (int c = 0; c < 4; ++c)
             acc[a][c] = 0.f;
     for (int J0 = J_begin; J0 < J_end; J0 += kGJ) {
-        // key row `kr` of the chunk is class index R0 + kr + J0 - w.  Loads are issued in batches so that their latencies
-        // overlap.
-        constexpr int kPIters = kGKR * kTI / 128, kVIters = kGKR * (kGM / 4) / 128, kPB = 8, kVB = 4;
-        static_assert(kPIters % kPB == 0 && kVIters % kVB == 0 && kGKR * kTI % 128 == 0 && kGKR * (kGM / 4) % 128 == 0, "fill loops of k_gbmml");
+        // Key row kr of the chunk is class index R0 + kr + J0 - w.  Thread `tid` fills key row tid of Ps: for row r that
+        // is band column tid - r of the chunk — consecutive threads read consecutive band columns.  Loads are issued in
+        // batches so that their latencies overlap.
+        {
+            const int kcls = R0 + tid + J0 - g.w;
+            const bool key_ok = kcls >= 0 && kcls < cls_lim;
+            const float *src = p + (bb + (size_t)rho + (size_t)g.d * R0) * bw + J0 + tid;
 #pragma unroll 1
-        for (int it0 = 0; it0 < kPIters; it0 += kPB) {
-            float buf[kPB];
+            for (int r0 = 0; r0 < kTI; r0 += 8) {
+                float buf[8];
 #pragma unroll
-            for (int b = 0; b < kPB; ++b) {
-                const int e = tid + 128 * (it0 + b);
-                const int r = e / kGKR, kr = e % kGKR, jj = kr - r; // consecutive threads: consecutive band columns of one row
-                const long long i = (long long)rho + (long long)g.d * (R0 + r);
-                const long long kcls = (long long)R0 + kr + J0 - g.w, ki = (long long)rho + (long long)g.d * kcls;
-                float val = 0.f;
-                if (jj >= 0 && jj < kGJ && J0 + jj < J_end && i < g.n && kcls >= 0 && ki < g.n)
-                    val = __ldg(p + (bb + (size_t)i) * bw + J0 + jj);
-                buf[b] = val;
-            }
+                for (int b = 0; b < 8; ++b) {
+                    const int r = r0 + b, jj = tid - r;
+                    buf[b] = (key_ok && r < rows_valid && jj >= 0 && jj < kGJ && J0 + jj < J_end) ? __ldg(src + r * p_step) : 0.f;
+                }
 #pragma unroll
-            for (int b = 0; b < kPB; ++b) {
-                const int e = tid + 128 * (it0 + b);
-                Ps[e % kGKR][e / kGKR] = buf[b];
+                for (int b = 0; b < 8; ++b)
+                    Ps[tid][r0 + b] = buf[b];
             }
         }
+        {
+            const int c4 = (tid & 15) * 4;
+            const int kcls0 = R0 + (tid >> 4) + J0 - g.w; // this thread's key rows: kcls0 + 8 * it
+            const bool full = vec && M0 + c4 + 3 < g.m;
 #pragma unroll 1
-        for (int it0 = 0; it0 < kVIters; it0 += kVB) {
-            float4 buf[kVB];
+            for (int it0 = 0; it0 < kGKR / 8; it0 += 4) {
+                float4 buf[4];
 #pragma unroll
-            for (int b = 0; b < kVB; ++b) {
-                const int e = tid + 128 * (it0 + b);
-                const int kr = e / (kGM / 4), c4 = (e % (kGM / 4)) * 4;
-                const long long kcls = (long long)R0 + kr + J0 - g.w, ki = (long long)rho + (long long)g.d * kcls;
-                float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (kcls >= 0 && ki < g.n) {
-                    const float *src = v + (bb + (size_t)ki) * g.m + M0 + c4;
-                    if (vec && M0 + c4 + 3 < g.m) {
-                        t = __ldg(reinterpret_cast<const float4 *>(src));
-                    } else {
-                        if (M0 + c4 < g.m) t.x = __ldg(src);
-                        if (M0 + c4 + 1 < g.m) t.y = __ldg(src + 1);
-                        if (M0 + c4 + 2 < g.m) t.z = __ldg(src + 2);
-                        if (M0 + c4 + 3 < g.m) t.w = __ldg(src + 3);
+                for (int b = 0; b < 4; ++b) {
+                    const int kcls = kcls0 + 8 * (it0 + b);
+                    float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (kcls >= 0 && kcls < cls_lim) {
+                        const float *src = v + (bb + (size_t)rho + (size_t)g.d * kcls) * g.m + M0 + c4;
+                        if (full) {
+                            t = __ldg(reinterpret_cast<const float4 *>(src));
+                        } else {
+                            if (M0 + c4 < g.m) t.x = __ldg(src);
+                            if (M0 + c4 + 1 < g.m) t.y = __ldg(src + 1);
+                            if (M0 + c4 + 2 < g.m) t.z = __ldg(src + 2);
+                            if (M0 + c4 + 3 < g.m) t.w = __ldg(src + 3);
+                        }
                     }
+                    buf[b] = t;
                 }
-                buf[b] = t;
-            }
 #pragma unroll
-            for (int b = 0; b < kVB; ++b) {
-                const int e = tid + 128 * (it0 + b);
-                *reinterpret_cast<float4 *>(&Vs[e / (kGM / 4)][(e % (kGM / 4)) * 4]) = buf[b];
+                for (int b = 0; b < 4; ++b)
+                    *reinterpret_cast<float4 *>(&Vs[(tid >> 4) + 8 * (it0 + b)][c4]) = buf[b];
             }
         }
         __syncthreads();
@@ -236,7 +238,8 @@ __global__ void __launch_bounds__(128) k_gbmml(const float *__restrict__ p, cons
         }
     }
 }
-static_assert(kGKR >= kTI + kGJ - 1 && kGKR % 8 == 0, "key rows of a chunk");
+constexpr size_t kGbmmlSmem = sizeof(float) * kGKR * (kTI + 4 + kGM);
+static_assert(kGKR >= kTI + kGJ - 1 && kGKR == 128 && kTI % 8 == 0, "key rows of a chunk: one per thread of k_gbmml");
 
 // y[i] = parts[0][i] + parts[1][i] + ... in split order (the sum does not depend on timing).
 __global__ void __launch_bounds__(256) k_band_reduce(const float *__restrict__ parts, float *__restrict__ y, size_t total, int splits) {
@@ -292,13 +295,19 @@ extern "C" int petb200_gbmml_run(petb200_ctx *ctx, const float *p, const float *
     int rc = check_band(ctx, p, v, y, bs, n, m, w, d, &g, &ytiles);
     if (rc)
         return rc;
-    // split the band columns until there are about four blocks per SM
+    // Split the band columns over blocks so that the last wave of blocks is not nearly empty: cost of a choice = waves of
+    // resident blocks (four per SM) x chunks per block, plus a little per split for the reduction pass.
     const int chunks = (2 * w + 1 + kGJ - 1) / kGJ;
     g.mtiles = (m + kGM - 1) / kGM;
-    const long long base = (long long)g.mtiles * ytiles * bs;
-    int splits = (int)std::min<long long>(std::min(chunks, 8), std::max<long long>(1, (4LL * ctx->sm_count + base - 1) / base));
-    g.chunks_per_split = (chunks + splits - 1) / splits;
-    splits = (chunks + g.chunks_per_split - 1) / g.chunks_per_split;
+    const long long base = (long long)g.mtiles * ytiles * bs, slots = 4LL * ctx->sm_count;
+    int splits = 1;
+    double best = 0;
+    for (int sp = 1; sp <= std::min(chunks, 16); ++sp) {
+        const int cps = (chunks + sp - 1) / sp, real = (chunks + cps - 1) / cps;
+        const double cost = (double)((base * real + slots - 1) / slots) * cps + 0.3 * (real - 1);
+        if (sp == 1 || cost < best * 0.98)
+            best = cost, splits = real, g.chunks_per_split = cps;
+    }
     const size_t total = (size_t)bs * n * m;
     float *dst = y;
     if (splits > 1) {
@@ -307,7 +316,11 @@ extern "C" int petb200_gbmml_run(petb200_ctx *ctx, const float *p, const float *
         dst = (float *)ctx->band_scratch.p;
     }
     const dim3 grid((unsigned)(g.mtiles * splits), (unsigned)ytiles, (unsigned)bs);
-    launch_pdl(k_gbmml, grid, dim3(128), 0, (cudaStream_t)stream, p, v, dst, g);
+    if (!ctx->band_attr_set) {
+        PETB200_CUDA(ctx, cudaFuncSetAttribute(k_gbmml, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGbmmlSmem));
+        ctx->band_attr_set = true;
+    }
+    launch_pdl(k_gbmml, grid, dim3(128), kGbmmlSmem, (cudaStream_t)stream, p, v, dst, g);
     rc = launched(ctx, "k_gbmml");
     if (rc || splits == 1)
         return rc;

@@ -22,8 +22,11 @@ struct DevBuf {
             cudaFree(p);
             p = nullptr;
         }
-        bytes = n;
-        return n ? cudaMalloc(&p, n) : cudaSuccess;
+        const cudaError_t e = n ? cudaMalloc(&p, n) : cudaSuccess;
+        if (e != cudaSuccess)
+            p = nullptr;
+        bytes = e == cudaSuccess ? n : 0; // a failed allocation leaves an empty buffer, not a size without memory
+        return e;
     }
 };
 } // namespace petb200
@@ -36,6 +39,7 @@ struct petb200_ctx {
     uint64_t launches = 0;
     std::string err;
     int *d_status = nullptr; // device word kernels write when a bounded wait expires
+    bool band_attr_set = false;   // the banded-product kernel's shared-memory limit was raised on this device
     petb200::DevBuf band_scratch; // partial sums of a banded product split over its band columns (grown on demand)
 };
 

@@ -399,6 +399,8 @@ struct LayoutPlan : petb200_plan {
     int grid = 1, grid_gather = 1;
     size_t smem = 0;
     DevBuf bin, bout; // scratch for timing only
+    LayoutPlan *zero_fill = nullptr; // second map of the same output that writes zeros where the first writes nothing
+    ~LayoutPlan() override { delete zero_fill; }
     int bench_launch(cudaStream_t s) override;
 };
 
@@ -679,6 +681,11 @@ static void launch_gather(LayoutPlan *pl, const void *in, void *out, cudaStream_
 }
 
 static int layout_launch(LayoutPlan *pl, const void *in, void *out, cudaStream_t s) {
+    if (pl->zero_fill) {
+        int rc = layout_launch(pl->zero_fill, in, out, s);
+        if (rc)
+            return rc;
+    }
     if (pl->mp.total == 0)
         return PETB200_OK;
     if (pl->mode == 0) {
@@ -866,6 +873,167 @@ extern "C" int petb200_transpose_plan(petb200_ctx *ctx, int nd, const int *dims,
     }
     pl->in_words = pl->out_words = prod(d0);
     int rc = finalize_plan(ctx, pl, digits, contiguous_ostr(digits), 0, 0);
+    if (rc) {
+        delete pl;
+        return rc;
+    }
+    *out = pl;
+    return PETB200_OK;
+}
+
+// One TransposeOp whose split or merge carries the reference's padding / halo parameters (ref: TransposeOp::getTTParam,
+// src/Graph/operator.cc:2403-2441; index expressions TransSplit::putTranspose / TransFuse::putTranspose,
+// src/Transpose/transpose.cc:22-42,70-106).  With in = extent of the inner part of the split or merged pair:
+//   extr  (split)  out[a][b] = in[a*(in+extr) + b]         a < (D-1)/(in+extr)+1: skips the gaps a padded merge left
+//   copys (split)  out[a][b] = in[a*in + b - a*copys]      D == 2*in, b < in+copys: two halves that overlap by the halo
+//   pad   (merge)  out[x] = x % (in+pad) < in ? in[x/(in+pad)][x%(in+pad)] : 0     extent A*(in+pad) - pad: zero gaps
+//   dels  (merge)  out[x] = in[x/(in-dels)][x%(in-dels) + (x/(in-dels))*dels]      A == 2: drops the overlap again
+extern "C" int petb200_transpose_halo_plan(petb200_ctx *ctx, int nd, const int *dims, const petb200_transpose_desc *op, int pad,
+                                           int extr, int copys, int dels, petb200_plan **out) {
+    if (!ctx || !dims || !op || !out || nd < 1 || nd > 7)
+        return fail(ctx, PETB200_ERR_INVALID, "transpose_halo_plan: bad arguments");
+    if (pad < 0 || extr < 0 || copys < 0 || dels < 0 || (extr && copys) || (pad && dels)) // ref: transpose.cc:25,74-76
+        return fail(ctx, PETB200_ERR_INVALID, "transpose_halo_plan: extr/copys and pad/dels exclude each other");
+    std::vector<long long> d0(dims, dims + nd);
+    for (auto v : d0)
+        if (v <= 0)
+            return fail(ctx, PETB200_ERR_INVALID, "transpose_halo_plan: non-positive dim");
+    auto str = row_major_strides(d0);
+    if (op->split >= nd || op->ngroups < 1 || op->ngroups > 8)
+        return fail(ctx, PETB200_ERR_INVALID, "transpose_halo_plan: bad split/groups");
+    if ((extr || copys) && op->split < 0)
+        return fail(ctx, PETB200_ERR_INVALID, "transpose_halo_plan: extr/copys need a split");
+    std::vector<Digit> flat; // one digit per dim after the split
+    for (int i = 0; i < nd; ++i) {
+        if (i != op->split) {
+            flat.push_back(Digit{d0[i], str[i]});
+            continue;
+        }
+        const long long D = d0[i], af = op->factor > 0 ? op->factor : -(long long)op->factor;
+        if (af == 0 || D < af || (!extr && D % af != 0))
+            return fail(ctx, PETB200_ERR_INVALID, "transpose_halo_plan: factor %d does not divide dim %lld", op->factor, D);
+        const long long in = op->factor > 0 ? af : D / af; // ref: splitFactor, operator.cc:2425
+        if (copys) {
+            if (D != 2 * in || copys > in) // ref: transpose.cc:34
+                return fail(ctx, PETB200_ERR_INVALID, "transpose_halo_plan: a halo split needs a dim of exactly 2 x %lld", in);
+            flat.push_back(Digit{2, (in - copys) * str[i]});
+            flat.push_back(Digit{in + copys, str[i]});
+        } else {
+            if (in + extr > D && extr)
+                return fail(ctx, PETB200_ERR_INVALID, "transpose_halo_plan: gap larger than the dim");
+            const long long parts = extr ? (D - 1) / (in + extr) + 1 : D / in;
+            if (extr && (parts - 1) * (in + extr) + in > D)
+                return fail(ctx, PETB200_ERR_INVALID, "transpose_halo_plan: dim %lld is not parts*(%lld+%d)-%d", D, in, extr, extr);
+            flat.push_back(Digit{parts, (in + extr) * str[i]});
+            flat.push_back(Digit{in, str[i]});
+        }
+    }
+    const int nflat = (int)flat.size();
+    std::vector<std::vector<int>> groups;
+    std::vector<int> used(nflat, 0);
+    int p = 0, merged = -1;
+    for (int g = 0; g < op->ngroups; ++g) {
+        if (op->group_sizes[g] < 1 || p + op->group_sizes[g] > 8)
+            return fail(ctx, PETB200_ERR_INVALID, "transpose_halo_plan: bad group size");
+        std::vector<int> items;
+        for (int j = 0; j < op->group_sizes[g]; ++j, ++p) {
+            int item = op->flat[p];
+            if (op->split >= 0) { // ref: TransposeOp::setParam, include/operator.h:1133-1143
+                if (item > op->split)
+                    item += 1;
+                if (item == -1)
+                    item = op->split + 1;
+            }
+            if (item < 0 || item >= nflat || used[item])
+                return fail(ctx, PETB200_ERR_INVALID, "transpose_halo_plan: permutation entry %d invalid", op->flat[p]);
+            used[item] = 1;
+            items.push_back(item);
+        }
+        if (items.size() > 1) {
+            if (merged >= 0) // ref: TransposeOp::checkValid, src/Graph/operator.cc:2324-2336
+                return fail(ctx, PETB200_ERR_INVALID, "transpose_halo_plan: more than one merged group");
+            merged = g;
+        }
+        groups.push_back(items);
+    }
+    for (int i = 0; i < nflat; ++i)
+        if (!used[i])
+            return fail(ctx, PETB200_ERR_INVALID, "transpose_halo_plan: permutation does not cover dim %d", i);
+    if ((pad || dels) && (merged < 0 || groups[merged].size() != 2))
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "transpose_halo_plan: pad/dels need one merged pair of dims");
+    // output dims, digits in output order, and the zero gaps of a padded merge
+    auto *pl = new LayoutPlan();
+    pl->ctx = ctx;
+    pl->out_nd = op->ngroups;
+    std::vector<Digit> digits, zdigits;
+    std::vector<long long> oext; // extent of every output dim
+    for (int g = 0; g < op->ngroups; ++g) {
+        if (g != merged || !(pad || dels)) {
+            long long e = 1;
+            for (int it : groups[g])
+                e *= flat[it].ext;
+            oext.push_back(e);
+            continue;
+        }
+        const Digit &a = flat[groups[g][0]], &b = flat[groups[g][1]];
+        if (dels && (a.ext != 2 || dels >= b.ext)) { // ref: transpose.cc:76
+            delete pl;
+            return fail(ctx, PETB200_ERR_INVALID, "transpose_halo_plan: dels needs a merged pair [2][in] with in > dels");
+        }
+        oext.push_back(pad ? a.ext * (b.ext + pad) - pad : a.ext * (b.ext - dels));
+    }
+    std::vector<long long> ostride(op->ngroups, 1);
+    for (int g = op->ngroups - 2; g >= 0; --g)
+        ostride[g] = ostride[g + 1] * oext[g + 1];
+    std::vector<long long> ostr, zostr;
+    for (int g = 0; g < op->ngroups; ++g) {
+        pl->out_dims[g] = (int)oext[g];
+        if (g == merged && (pad || dels)) {
+            Digit a = flat[groups[g][0]], b = flat[groups[g][1]];
+            if (dels) {
+                a.istr += dels * b.istr;
+                b.ext -= dels;
+            }
+            digits.push_back(a);
+            ostr.push_back((b.ext + pad) * ostride[g]);
+            digits.push_back(b);
+            ostr.push_back(ostride[g]);
+            if (pad && a.ext > 1) { // the gaps: (a.ext - 1) runs of `pad` zeros, read through an always-closed guard
+                Digit za{a.ext - 1, 0}, zb{pad, 0};
+                zb.guard = true, zb.glo = 0, zb.ghi = 0;
+                zdigits.push_back(za);
+                zostr.push_back((b.ext + pad) * ostride[g]);
+                zdigits.push_back(zb);
+                zostr.push_back(ostride[g]);
+            }
+            continue;
+        }
+        long long inner = 1; // out stride inside the group: later members are inner
+        std::vector<long long> os(groups[g].size());
+        for (int j = (int)groups[g].size() - 1; j >= 0; --j) {
+            os[j] = inner * ostride[g];
+            inner *= flat[groups[g][j]].ext;
+        }
+        for (size_t j = 0; j < groups[g].size(); ++j) {
+            digits.push_back(flat[groups[g][j]]);
+            ostr.push_back(os[j]);
+            Digit z = flat[groups[g][j]];
+            z.istr = 0;
+            zdigits.push_back(z);
+            zostr.push_back(os[j]);
+        }
+    }
+    pl->in_words = prod(d0);
+    pl->out_words = prod(oext);
+    int rc = finalize_plan(ctx, pl, digits, ostr, 0, 0);
+    if (rc == PETB200_OK && pad && merged >= 0 && flat[groups[merged][0]].ext > 1) {
+        const long long gap0 = flat[groups[merged][1]].ext * ostride[merged]; // first gap starts after the first block
+        pl->zero_fill = new LayoutPlan();
+        pl->zero_fill->ctx = ctx;
+        pl->zero_fill->in_words = pl->in_words;
+        pl->zero_fill->out_words = pl->out_words;
+        rc = finalize_plan(ctx, pl->zero_fill, zdigits, zostr, 0, gap0);
+    }
     if (rc) {
         delete pl;
         return rc;

@@ -1,7 +1,8 @@
 """Per-kernel measurements against the roofline that bounds each kernel (python -m pet_b200.perf_report [group ...]).
 
 Groups: `layout` (index-map kernels at sizes far beyond L2: achieved HBM GB/s), `conv` / `matmul` (tensor-core kernels:
-achieved fp32-equivalent TFLOP/s and the TF32 issue rate), `eltwise`.  Times come from the C ABI's timing entry point
+achieved fp32-equivalent TFLOP/s and the TF32 issue rate), `convtrans` (transposed convolution), `banded` (G2BMM / GBMML
+at the one shape the reference ships kernels for, and a short-sequence one).  Times come from the C ABI's timing entry point
 (CUDA events around repeated launches on plan-owned operands).  Peaks are read from MEASURED_PEAKS.json at the
 repository root when present.
 """
@@ -49,9 +50,18 @@ MATMUL = [("bert qkv 128x768x768", 1, 128, 768, 768, False, False), ("bert score
           ("square 4096", 1, 4096, 4096, 4096, False, False)]
 
 
+CONVTRANS = [  # x {n,h,w,f}, w {r,s,f,c}, (ph, pw, sh, sw, oph, opw)
+    ("2x upsample 4x4 256->128 8x8 b4", (4, 8, 8, 256), (4, 4, 256, 128), (1, 1, 2, 2, 0, 0)),
+    ("2x upsample 4x4 128->64 32x32 b8", (8, 32, 32, 128), (4, 4, 128, 64), (1, 1, 2, 2, 0, 0)),
+    ("stride 1 3x3 128->128 32x32 b8", (8, 32, 32, 128), (3, 3, 128, 128), (1, 1, 1, 1, 0, 0)),
+]
+BANDED = [(1, 10000, 64, 1000, 1), (1, 10000, 64, 1000, 4), (8, 10000, 64, 1000, 1), (12, 4096, 64, 256, 1)]  # b, n, m, w, d
+
+
 def main(argv):
     groups = argv or ["layout", "conv", "matmul"]
     pk, kind = peaks()
+    pk_kind = kind
     ctx = Context(0)
     print(f"peaks ({kind}): HBM {pk['hbm_gbs']:.0f} GB/s, bf16 {pk['bf16_tflops']:.0f} TFLOP/s burst")
     if "layout" in groups:
@@ -74,6 +84,22 @@ def main(argv):
             ms = plan.time(50, 10)
             tf = 2.0 * b * m * n * k / ms / 1e9
             print(f"matmul  {name:30s} {plan.kernel:14s} {ms * 1e3:9.1f} us {tf:7.1f} TFLOP/s fp32-equivalent")
+    if "convtrans" in groups:
+        for name, xs, ws, (ph, pw, sh, sw, oph, opw) in CONVTRANS:
+            plan = ctx.convtrans_plan(xs, ws, ph, pw, sh, sw, 1, 1, oph, opw)
+            ms = plan.time(50, 10)
+            useful = 2.0 * np.prod(xs) * ws[0] * ws[1] * ws[3]  # every input element meets every tap of every output channel
+            issued = 2.0 * np.prod(plan.out_shape) * ws[0] * ws[1] * ws[2]
+            print(f"convtr  {name:34s} {plan.kernel:14s} {ms * 1e3:9.1f} us {useful / ms / 1e9:7.1f} TFLOP/s useful, "
+                  f"{issued / ms / 1e9:7.1f} issued (zero-inserted)")
+    if "banded" in groups:
+        for b, n, m, w, d in BANDED:
+            fl = 2.0 * b * n * (2 * w + 1) * m
+            by = 4.0 * b * n * (2 * m + 2 * w + 1)
+            for kind in ("g2bmm", "gbmml"):
+                ms = ctx.banded_time(kind, b, n, m, w, d, rounds=20, warmup=3)
+                print(f"banded  {kind} b{b} n{n} m{m} w{w} d{d}: {ms * 1e3:9.1f} us {fl / ms / 1e9:6.1f} TFLOP/s fp32, "
+                      f"{by / ms / 1e6:6.0f} GB/s = {by / ms / 1e6 / pk['hbm_gbs']:.2f} of {pk_kind} HBM peak")
     ctx.sync_check()
     ctx.close()
 
