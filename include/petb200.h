@@ -140,6 +140,17 @@ typedef struct {
  * consecutive transposes (ref: src/Graph/code_engine.cc:1428-1459).  n_ops = 1 is a single TransposeOp. */
 int petb200_transpose_plan(petb200_ctx *ctx, int nd, const int *dims, int n_ops, const petb200_transpose_desc *ops,
                            petb200_plan **out);
+/* One TransposeOp carrying the reference's padding / halo parameters: what TransposeOp::getTTParam hands to the split
+ * and merge micro-operations once TransposeOp::setPaddingSize is used (ref: include/operator.h:1184-1190,
+ * src/Graph/operator.cc:2403-2441; index expressions src/Transpose/transpose.cc:22-42,70-106).  With n the inner extent
+ * of the split or merged pair, at most one of extr/copys and one of pad/dels non-zero:
+ *   extr  (split)  out[a][b] = in[a*(n+extr) + b]        skips the gaps a padded merge left       (Post of N2H/D2H/N2W/D2W)
+ *   copys (split)  out[a][b] = in[a*n + b - a*copys]     dim == 2n, b < n+copys: halves overlapping by the halo (Pre of H2N/W2N)
+ *   pad   (merge)  out[i] = i % (n+pad) < n ? in[i/(n+pad)][i%(n+pad)] : 0   extent A*(n+pad)-pad  (Pre of N2H/...)
+ *   dels  (merge)  out[i] = in[i/(n-dels)][i%(n-dels) + (i/(n-dels))*dels]   A == 2               (Post of H2N/W2N)
+ * pad/dels need the merged group to be a pair.  Run with petb200_layout_run; bit-exact. */
+int petb200_transpose_halo_plan(petb200_ctx *ctx, int nd, const int *dims, const petb200_transpose_desc *op, int pad,
+                                int extr, int copys, int dels, petb200_plan **out);
 /* PadOp (ref: src/Graph/operator.cc:1640-1662), SliceOp (:1741-1773), ExtendOp (:2577-2597). */
 int petb200_pad_plan(petb200_ctx *ctx, int nd, const int *dims, const int *begin, const int *end, petb200_plan **out);
 int petb200_slice_plan(petb200_ctx *ctx, int nd, const int *dims, const int *begin, const int *end,

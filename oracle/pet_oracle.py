@@ -138,6 +138,67 @@ def transpose(x, split, after, factor=2):
     return out.view(x.dtype) if x.dtype.itemsize == 4 else out
 
 
+def transpose_halo(x, split, after, factor, mode, amount):
+    """A TransposeOp whose split or merge carries one of the reference's padding / halo parameters
+    (TransposeOp::getTTParam, src/Graph/operator.cc:2403-2441; TransSplit / TransFuse::putTranspose,
+    src/Transpose/transpose.cc:22-42,70-106).  With `n` the inner extent of the split or merged pair:
+      extr   split   out[a][b] = in[a*(n+extr) + b]
+      copys  split   out[a][b] = in[a*n + b - a*copys], b < n + copys   (dim == 2n)
+      pad    merge   out[i] = in[i // (n+pad)][i % (n+pad)] if i % (n+pad) < n else 0, extent A*(n+pad) - pad
+      dels   merge   out[i] = in[i // (n-dels)][i % (n-dels) + (i // (n-dels)) * dels]   (A == 2)
+    Word-exact (numpy indexing only)."""
+    x = np.ascontiguousarray(x)
+    groups = [list(g) if isinstance(g, (list, tuple)) else [g] for g in after]
+    extr = amount if mode == "extr" else 0
+    copys = amount if mode == "copys" else 0
+    pad_ = amount if mode == "pad" else 0
+    dels = amount if mode == "dels" else 0
+    t = x
+    if split >= 0:
+        d = x.shape[split]
+        n = factor if factor > 0 else d // (-factor)
+        if copys:
+            assert d == 2 * n
+            idx = np.array([[a * n + b - a * copys for b in range(n + copys)] for a in range(2)])
+        else:
+            parts = (d - 1) // (n + extr) + 1 if extr else d // n
+            idx = np.array([[a * (n + extr) + b for b in range(n)] for a in range(parts)])
+        t = np.take(x, idx.reshape(-1), axis=split)
+        t = t.reshape(x.shape[:split] + idx.shape + x.shape[split + 1:])
+
+    def item(i):  # constructor numbering -> axis after the split (include/operator.h:1133-1143)
+        if split < 0:
+            return i
+        return split + 1 if i == -1 else (i + 1 if i > split else i)
+
+    order = [item(i) for g in groups for i in g]
+    t = np.transpose(t, order)
+    out_shape, pos, merged_axis = [], 0, None
+    for gi, g in enumerate(groups):
+        if len(g) > 1 and (pad_ or dels):
+            assert len(g) == 2
+            merged_axis = gi
+            out_shape += [t.shape[pos], t.shape[pos + 1]]
+        else:
+            out_shape.append(int(np.prod(t.shape[pos:pos + len(g)])))
+        pos += len(g)
+    t = np.ascontiguousarray(t).reshape(out_shape)
+    if merged_axis is None:
+        return t
+    a_ext, n = t.shape[merged_axis], t.shape[merged_axis + 1]
+    lead = t.shape[:merged_axis]
+    tail = t.shape[merged_axis + 2:]
+    if pad_:
+        out = np.zeros(lead + (a_ext * (n + pad_) - pad_,) + tail, x.dtype)
+        for a in range(a_ext):
+            sl = [slice(None)] * merged_axis
+            out[tuple(sl + [slice(a * (n + pad_), a * (n + pad_) + n)])] = t[tuple(sl + [a])]
+        return out
+    assert a_ext == 2 and dels < n
+    sl = [slice(None)] * merged_axis
+    return np.concatenate([t[tuple(sl + [0, slice(0, n - dels)])], t[tuple(sl + [1, slice(dels, n)])]], axis=merged_axis)
+
+
 def pad(x, begin, end):
     """PadOp::compute (src/Graph/operator.cc:1640-1662)."""
     xin = _u32(x)

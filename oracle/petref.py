@@ -60,6 +60,59 @@ def transpose(x, split, after, factor=2):
     return out.reshape([od[i] for i in range(nd.value)]).view(x.dtype)
 
 
+_TT = {"N2H": 1, "N2W": 2, "H2N": 3, "W2N": 4, "D2H": 7, "D2W": 8}
+# which (type, position) makes TransposeOp::getTTParam hand out each parameter (src/Graph/operator.cc:2406-2438)
+HALO_MODES = {"pad": ("N2H", 1), "extr": ("N2H", 2), "copys": ("H2N", 1), "dels": ("H2N", 2)}
+
+
+def transpose_lambda(shape, split, after, factor, mode, amount):
+    """(lambda source, output dims) the reference generates for a TransposeOp carrying `amount` of pad/extr/copys/dels."""
+    sizes, flat = perm_spec(after)
+    ttype, pos = HALO_MODES[mode]
+    buf = C.create_string_buffer(4096)
+    nd = C.c_int()
+    od = (C.c_int * 16)()
+    _ok(lib().petref_transpose_lambda(len(shape), _ia(shape), split, len(sizes), _ia(sizes), _ia(flat), factor, _TT[ttype],
+                                      pos, amount, amount, buf, 4096, C.byref(nd), od), "transpose lambda")
+    return buf.value.decode(), tuple(od[i] for i in range(nd.value))
+
+
+class _Lenient:
+    """I[0][a,b,...] of the generated lambda: reads outside the tensor give 0 (TVM evaluates only the taken branch)."""
+
+    def __init__(self, a):
+        self.a = a
+
+    def __getitem__(self, idx):
+        if any(i < 0 or i >= n for i, n in zip(idx, self.a.shape)):
+            return 0
+        return self.a[idx]
+
+
+class _Tir:
+    @staticmethod
+    def if_then_else(c, x, y):
+        return x if c else y
+
+    @staticmethod
+    def const(v, t):
+        return 0
+
+
+class _Tvm:
+    tir = _Tir
+
+
+def transpose_halo(x, split, after, factor, mode, amount):
+    """Evaluates the reference's own generated index expression at every output position (small tensors only)."""
+    src, od = transpose_lambda(x.shape, split, after, factor, mode, amount)
+    fn = eval(src, {"tvm": _Tvm, "I": [_Lenient(np.ascontiguousarray(x))]})
+    out = np.zeros(od, x.dtype)
+    for idx in np.ndindex(*od):
+        out[idx] = fn(*idx)
+    return out
+
+
 def conv2d_u32(x, w, pad=(0, 0), stride=(1, 1), dil=(1, 1), return_secs=False):
     x, w = _u32(x), _u32(w)
     n, c, h, ww = x.shape

@@ -10,6 +10,7 @@
 #include "graph.h"
 #include "operator.h"
 #include "tensor.h"
+#include "transpose.h"
 #include <chrono>
 #include <cstring>
 #include <omp.h>
@@ -285,6 +286,44 @@ int petref_convtrans(const uint32_t *x, const int *xd, const uint32_t *w, const 
     }
     int nd;
     return fetch(out, y, &nd, yd);
+}
+
+// The index expression the reference generates for a TransposeOp with padding / halo parameters: builds the operator,
+// marks it the way markTransType would (type, Pre/Post position, padding sizes — include/operator.h:1180-1190), takes
+// its micro-operations from TransposeOp::getTTParam (src/Graph/operator.cc:2403-2441) and asks TransposeEngine::getLambda
+// (src/Transpose/transpose.cc:185-214) for the Python lambda that CodeEngine hands to TVM (src/Graph/code_engine.cc:27-84).
+// Also returns the output dims the micro-operations produce.  type: 1 N2H, 2 N2W, 3 H2N, 4 W2N, 7 D2H, 8 D2W; pos: 1 Pre, 2 Post.
+int petref_transpose_lambda(int nd, const int *dims, int split, int ngroups, const int *group_sizes, const int *flat,
+                            int factor, int type, int pos, int pad_h, int pad_w, char *buf, int buflen, int *out_nd,
+                            int *out_dims) {
+    Graph g;
+    Tensor *x = g.tensor(mkdim(dims, nd));
+    auto *op = dynamic_cast<TransposeOp *>(g.transpose(x, split, mkperm(ngroups, group_sizes, flat), factor));
+    if (op == nullptr)
+        return -1;
+    op->setType((TransposeOp::TransType)type);
+    op->setPos((TransposeOp::TransPos)pos);
+    op->setPaddingSize(pad_h, pad_w);
+    auto micro = op->getTTParam();
+    std::vector<TransBasic *> raw;
+    for (auto &m : micro)
+        raw.push_back(m.get());
+    std::vector<int> in(dims, dims + nd);
+    std::string lam = TransposeEngine::getInstance().getLambda(raw, in);
+    if ((int)lam.size() + 1 > buflen)
+        return -3;
+    std::memcpy(buf, lam.c_str(), lam.size() + 1);
+    std::vector<std::string> vars;
+    for (int i = 0; i < nd; ++i)
+        vars.push_back(std::string(1, (char)('a' + i)));
+    DecisionTree *tree = new DecisionTree(vars);
+    std::vector<int> od = in;
+    for (auto *m : raw)
+        tree = m->putTranspose(tree, od);
+    *out_nd = (int)od.size();
+    for (size_t i = 0; i < od.size(); ++i)
+        out_dims[i] = od[i];
+    return 0;
 }
 
 } // extern "C"

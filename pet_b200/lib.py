@@ -54,6 +54,7 @@ SYMBOLS = {
     "petb200_matmul_run": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "petb200_matmul_run_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "petb200_transpose_plan": (_i, [_vp, _i, _ip, _i, C.POINTER(TransposeDesc), C.POINTER(_vp)]),
+    "petb200_transpose_halo_plan": (_i, [_vp, _i, _ip, C.POINTER(TransposeDesc), _i, _i, _i, _i, C.POINTER(_vp)]),
     "petb200_pad_plan": (_i, [_vp, _i, _ip, _ip, _ip, C.POINTER(_vp)]),
     "petb200_slice_plan": (_i, [_vp, _i, _ip, _ip, _ip, C.POINTER(_vp)]),
     "petb200_extend_plan": (_i, [_vp, _i, _ip, _i, _i, C.POINTER(_vp)]),

@@ -269,6 +269,27 @@ class Context:
         self.check(self.lib.petb200_transpose_plan(self.h, len(shape), L.ints(shape), len(ops), descs, C.byref(h_)))
         return self._layout_plan(h_)
 
+    def transpose_halo_plan(self, shape, split, after, factor, mode, amount):
+        """One TransposeOp with `amount` of the reference's pad / extr / copys / dels (TransposeOp::getTTParam)."""
+        d = L.TransposeDesc()
+        sizes, flat = perm_spec(after)
+        d.split, d.factor, d.ngroups = split, factor, len(sizes)
+        for i, v in enumerate(sizes):
+            d.group_sizes[i] = v
+        for i, v in enumerate(flat):
+            d.flat[i] = v
+        amt = {m: (amount if m == mode else 0) for m in ("pad", "extr", "copys", "dels")}
+        if mode not in amt:
+            raise L.PetError(L.ERR_INVALID, "mode must be pad, extr, copys or dels")
+        h_ = C.c_void_p()
+        self.check(self.lib.petb200_transpose_halo_plan(self.h, len(shape), L.ints(shape), C.byref(d), amt["pad"], amt["extr"],
+                                                        amt["copys"], amt["dels"], C.byref(h_)))
+        return self._layout_plan(h_)
+
+    def transpose_halo(self, x, split, after, factor, mode, amount):
+        key = ("halo", tuple(x.shape), split, repr(after), factor, mode, amount)
+        return self.layout_run(self._cached_layout(key, lambda: self.transpose_halo_plan(x.shape, split, after, factor, mode, amount)), x)
+
     def _layout_plan(self, h_):
         p = Plan(self, h_)
         od = (C.c_int * 16)()

@@ -2,7 +2,8 @@
 
 Groups: `layout` (index-map kernels at sizes far beyond L2: achieved HBM GB/s), `conv` / `matmul` (tensor-core kernels:
 achieved fp32-equivalent TFLOP/s and the TF32 issue rate), `convtrans` (transposed convolution), `banded` (G2BMM / GBMML
-at the one shape the reference ships kernels for, and a short-sequence one).  Times come from the C ABI's timing entry point
+at the one shape the reference ships kernels for, and a short-sequence one), `rewrite` (config 1's H->N rewrite restored by
+the correction kernel and by halo transposes, each route replayed as a CUDA graph).  Times come from the C ABI's timing entry point
 (CUDA events around repeated launches on plan-owned operands).  Peaks are read from MEASURED_PEAKS.json at the
 repository root when present.
 """
@@ -58,6 +59,58 @@ CONVTRANS = [  # x {n,h,w,f}, w {r,s,f,c}, (ph, pw, sh, sw, oph, opw)
 BANDED = [(1, 10000, 64, 1000, 1), (1, 10000, 64, 1000, 4), (8, 10000, 64, 1000, 1), (12, 4096, 64, 256, 1)]  # b, n, m, w, d
 
 
+def _graph_time(fn, iters=200):
+    """Microseconds per replay of `fn` captured as one CUDA graph (launch overheads of the Python layer excluded)."""
+    import torch
+    fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    for _ in range(10):
+        g.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e3
+
+
+def rewrite_routes(ctx):
+    import torch
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.rand((1, 64, 56, 56), device="cuda", generator=gen) * 2 - 1
+    w = torch.rand((64, 64, 3, 3), device="cuda", generator=gen) * 2 - 1
+    H2N, N2H_ = (2, [[0, 2], 1, -1, 3], -2), (0, [0, 1, [-1, 2], 3], 2)
+    plans = {}
+    for shape in ((1, 64, 56, 56), (2, 64, 28, 56), (2, 64, 29, 56)):  # weights are packed once, outside the replayed part
+        plans[shape] = ctx.conv2d_plan(shape, w.shape, 1, 1)
+        ctx.conv2d_set_weights(plans[shape], w)
+    plan = plans[(1, 64, 56, 56)]
+
+    def conv(t):
+        return ctx.conv2d_run(plans[tuple(t.shape)], t)
+
+    def original():
+        return conv(x)
+
+    def corrected():
+        y = ctx.transpose(conv(ctx.transpose(x, *H2N)), *N2H_)
+        return ctx.conv2d_correct(plan, x, y, 27, 2)
+
+    def halo():
+        return ctx.transpose_halo(conv(ctx.transpose_halo(x, *H2N, "copys", 1)), *N2H_, "dels", 1)
+
+    y0 = original()
+    print(f"rewrite max |corrected - original| = {float((corrected() - y0).abs().max()):.3g}, "
+          f"max |halo - original| = {float((halo() - y0).abs().max()):.3g}")
+    for name, fn in (("original conv", original), ("H2N + conv + N2H + correction of rows 27,28", corrected),
+                     ("halo H2N + conv + dropping N2H", halo)):
+        print(f"rewrite {name:46s} {_graph_time(fn):8.1f} us per replay")
+
+
 def main(argv):
     groups = argv or ["layout", "conv", "matmul"]
     pk, kind = peaks()
@@ -100,6 +153,8 @@ def main(argv):
                 ms = ctx.banded_time(kind, b, n, m, w, d, rounds=20, warmup=3)
                 print(f"banded  {kind} b{b} n{n} m{m} w{w} d{d}: {ms * 1e3:9.1f} us {fl / ms / 1e9:6.1f} TFLOP/s fp32, "
                       f"{by / ms / 1e6:6.0f} GB/s = {by / ms / 1e6 / pk['hbm_gbs']:.2f} of {pk_kind} HBM peak")
+    if "rewrite" in groups:
+        rewrite_routes(ctx)
     ctx.sync_check()
     ctx.close()
 

@@ -19,6 +19,19 @@ TRANSPOSES = {  # name: (input shape, split, after, factor) — constructor argu
     "promote": ((12, 20), 0, [-1, 0, 1], 1),
     "heads": ((16, 4, 8), -1, [1, 0, 2], 2),
 }
+HALO_TRANSPOSES = [  # (input shape, split, after, factor, mode, amount): TransposeOp with pad / extr / copys / dels
+    ((2, 3, 8, 4), 2, [[0, 2], 1, -1, 3], -2, "copys", 1),    # H2N before a 3x3 conv: two halves with one halo row
+    ((2, 3, 8, 4), 2, [[0, 2], 1, -1, 3], -2, "copys", 2),
+    ((2, 2, 4, 12), 3, [[0, 3], 1, 2, -1], -2, "copys", 1),   # W2N
+    ((4, 3, 5, 4), 0, [0, 1, [-1, 2], 3], 2, "dels", 1),      # N2H after it: drops the rows computed from the halo
+    ((4, 3, 6, 4), 0, [0, 1, [-1, 2], 3], 2, "dels", 2),
+    ((4, 2, 3, 7), 0, [0, 1, 2, [-1, 3]], 2, "dels", 1),      # N2W
+    ((4, 3, 5, 4), 0, [0, 1, [-1, 2], 3], 2, "pad", 1),       # N2H before a conv: zero rows between the images
+    ((4, 2, 3, 5), 0, [0, 1, 2, [-1, 3]], 2, "pad", 2),
+    ((6, 2, 3, 4), 0, [0, 1, [-1, 2], 3], 3, "pad", 1),       # three images stacked
+    ((2, 3, 11, 4), 2, [[0, 2], 1, -1, 3], -2, "extr", 1),    # H2N after it: skips the gap rows
+    ((2, 2, 4, 12), 3, [[0, 3], 1, 2, -1], 5, "extr", 2),
+]
 CONVS = [  # (x shape, w shape, kwargs)
     ((2, 8, 12, 10), (6, 4, 3, 3), dict(pad=(1, 1))),
     ((2, 8, 12, 10), (6, 4, 3, 3), dict(pad=(2, 2), dil=(2, 2))),

@@ -28,6 +28,9 @@ def main():
         out[f"conv_{i}"] = pr.conv2d_u32(gc.small_ints(xs, 100 + i), gc.small_ints(ws, 200 + i), **kw)
     for i, (xs, ws, kw, whole) in enumerate(gc.CONVTRANS):
         out[f"convtrans_{i}"] = pr.convtrans_u32(gc.small_ints(xs, 300 + i), gc.small_ints(ws, 400 + i), whole=whole, **kw)
+    # the reference's own generated index expression (TransposeEngine::getLambda), evaluated at every output position
+    for i, (shape, split, after, factor, mode, amount) in enumerate(gc.HALO_TRANSPOSES):
+        out[f"halo_{i}"] = pr.transpose_halo(gc.words(shape, 500 + i), split, after, factor, mode, amount)
     # src/Test/batch_gemm_test.cc: inputs i, 3i, 7i; two matmuls and the merged batch matmul
     i0, w0, w1 = gc.batch_gemm_inputs()
     out["bgemm_o0"] = pr.matmul_u32(i0, w0)

@@ -97,3 +97,66 @@ def test_invalid_layout_requests_are_rejected(ctx):
         ctx.slice(x, [0, 0], [3, 0])  # empty result
     with pytest.raises(PetError):
         ctx.split(x, 1, [1, 1])  # 5 not divisible by the ratio sum
+
+
+@pytest.mark.parametrize("i", range(len(gc.HALO_TRANSPOSES)))
+def test_halo_transpose_bit_exact_vs_reference_vectors(ctx, golden, i):
+    shape, split, after, factor, mode, amount = gc.HALO_TRANSPOSES[i]
+    x = gc.words(shape, 500 + i)
+    y = ctx.transpose_halo(dev(x.view(np.int32)), split, after, factor, mode, amount)
+    ctx.sync_check()
+    want = golden[f"halo_{i}"]
+    assert tuple(y.shape) == want.shape
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), want)
+
+
+HALO_BIG = [
+    # config-1 sized: H split with a one-row halo and its inverse merge; stacked images with a zero row and its inverse split
+    ((1, 64, 56, 56), 2, [[0, 2], 1, -1, 3], -2, "copys", 1),
+    ((2, 64, 29, 56), 0, [0, 1, [-1, 2], 3], 2, "dels", 1),
+    ((2, 64, 28, 56), 0, [0, 1, [-1, 2], 3], 2, "pad", 1),
+    ((1, 64, 57, 56), 2, [[0, 2], 1, -1, 3], 28, "extr", 1),
+    ((8, 32, 30, 33), 0, [0, 1, 2, [-1, 3]], 2, "pad", 3),    # odd row length: word kernels
+    ((4, 16, 9, 130), 3, [[0, 3], 1, 2, -1], -2, "copys", 2),
+]
+
+
+@pytest.mark.parametrize("case", HALO_BIG, ids=[f"{c[4]}{c[5]}_{'x'.join(map(str, c[0]))}" for c in HALO_BIG])
+def test_halo_transpose_vs_oracle(ctx, oracle, case):
+    shape, split, after, factor, mode, amount = case
+    x = gc.words(shape, 77)
+    want = oracle.transpose_halo(x, split, after, factor, mode, amount)
+    y = ctx.transpose_halo(dev(x.view(np.int32)), split, after, factor, mode, amount)
+    ctx.sync_check()
+    assert tuple(y.shape) == want.shape
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), want)
+
+
+def test_halo_rewrite_equals_unsplit_conv_and_correction_route(ctx):
+    """Config 1 (3x3, 64 channels, 56x56): the H->N rewrite restored three ways — halo split + dropping merge, the
+    correction kernel on the seam rows, and the unsplit conv — agree (small integers: every route is exact)."""
+    x = torch.from_numpy((gc.small_ints((1, 64, 56, 56), 91) % 8).astype(np.float32)).cuda()
+    w = torch.from_numpy((gc.small_ints((64, 64, 3, 3), 92) % 8).astype(np.float32)).cuda()
+    y0 = ctx.conv2d(x, w, 1, 1)
+    xs = ctx.transpose_halo(x, 2, [[0, 2], 1, -1, 3], -2, "copys", 1)
+    assert tuple(xs.shape) == (2, 64, 29, 56)
+    y1 = ctx.transpose_halo(ctx.conv2d(xs, w, 1, 1), 0, [0, 1, [-1, 2], 3], 2, "dels", 1)
+    assert torch.equal(y1, y0)
+    xm = ctx.transpose(x, 2, [[0, 2], 1, -1, 3], -2)                    # plain H2N: seam rows 27/28 come out wrong ...
+    y2 = ctx.transpose(ctx.conv2d(xm, w, 1, 1), 0, [0, 1, [-1, 2], 3], 2)
+    assert not torch.equal(y2, y0)
+    plan = ctx.conv2d_plan(x.shape, w.shape, 1, 1)
+    ctx.conv2d_set_weights(plan, w)
+    ctx.conv2d_correct(plan, x, y2, 27, 2)                              # ... until the correction recomputes them
+    ctx.sync_check()
+    assert torch.equal(y2, y0)
+
+
+def test_halo_transpose_rejects_bad_requests(ctx):
+    from pet_b200 import PetError
+    with pytest.raises(PetError):
+        ctx.transpose_halo_plan((1, 4, 9, 8), 2, [[0, 2], 1, -1, 3], -2, "copys", 1)       # 9 is not 2 x n
+    with pytest.raises(PetError):
+        ctx.transpose_halo_plan((6, 4, 8, 8), 0, [0, 1, [-1, 2], 3], 3, "dels", 1)         # dels needs a pair [2][n]
+    with pytest.raises(PetError):
+        ctx.transpose_halo_plan((2, 4, 8, 8), -1, [0, 1, 3, 2], 2, "pad", 1)               # no merged pair
