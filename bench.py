@@ -146,6 +146,7 @@ def config_latencies(ctx):
     x, w = configs.c1_tensors()
     run("c1_conv3x3_original", configs.c1_original, x, w)
     run("c1_conv3x3_h2n_rewrite_corrected", configs.c1_rewrite, x, w)
+    run("c1_conv3x3_h2n_rewrite_halo", configs.c1_rewrite_halo, x, w)
     x, w = configs.c2_tensors()
     run("c2_dilated_original", configs.c2_original, x, w)
     run("c2_dilated_space_to_batch_rewrite", configs.c2_rewrite, x, w)

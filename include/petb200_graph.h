@@ -50,6 +50,10 @@ int petb200_graph_convtrans(petb200_graph *g, int x, int w, int bias, int ph, in
 int petb200_graph_g2bmm(petb200_graph *g, int a, int b, int width, int dilation, int *out);
 int petb200_graph_gbmml(petb200_graph *g, int a, int b, int dilation, int *out);
 int petb200_graph_transpose(petb200_graph *g, int x, const petb200_transpose_desc *desc, int *out);
+/* TransposeOp with padding / halo parameters (ref: TransposeOp::setPaddingSize, include/operator.h:1187-1190); at most one of
+ * extr/copys and one of pad/dels non-zero, see petb200_transpose_halo_plan. */
+int petb200_graph_transpose_halo(petb200_graph *g, int x, const petb200_transpose_desc *desc, int pad, int extr, int copys,
+                                 int dels, int *out);
 int petb200_graph_pad(petb200_graph *g, int x, const int *begin, const int *end, int *out);
 int petb200_graph_slice(petb200_graph *g, int x, const int *begin, const int *end, int *out);
 int petb200_graph_extend(petb200_graph *g, int x, int dim, int num, int *out);

@@ -80,6 +80,13 @@ def c1_rewrite(b, x, w, correct=True):
     return y
 
 
+def c1_rewrite_halo(b, x, w):
+    """The same H->N rewrite made exact without a correction: the halves overlap by one halo row (copys = 1) and the merge
+    drops the row each half computed from the other's territory (dels = 1)."""
+    xi, wi = b.input(x), b.const(w)
+    return b.transpose_halo(b.conv(b.transpose_halo(xi, *H2N, "copys", 1), wi, 1, 1), *N2H, "dels", 1)
+
+
 # ---- config 2: dilated conv, original and the space-to-batch rewrite -------------------------------------------
 def c2_tensors(c=512, hw=64, k=512):
     return (rng_for(2, 0).standard_normal((1, c, hw, hw)).astype(np.float32), he_normal(rng_for(2, 1), (k, c, 3, 3)))

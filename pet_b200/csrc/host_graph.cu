@@ -56,6 +56,7 @@ struct Operator {
     float eps = 1e-5f;
     int win[4] = {0, 0, 0, 0};
     int oph = 0, opw = 0;         // ConvTrans output padding
+    int halo[4] = {0, 0, 0, 0};   // Transpose: pad, extr, copys, dels (TransposeOp::getTTParam), all 0 for a plain transpose
     int width = 0, dilation = 1;  // G2BMM / GBMML band half-width and key step
     bool fused_away = false; // absorbed into another step
     // Matmul whose operands/result are strided views of other tensors (folded batch-swap transposes):
@@ -572,11 +573,19 @@ int petb200_graph::compile(int flags) {
             break;
         }
         case Transpose: {
+            auto has_halo = [](const Operator &o) { return o.halo[0] || o.halo[1] || o.halo[2] || o.halo[3]; };
+            if (has_halo(op)) { // carries padding / halo parameters: its own index map, not part of a fused chain
+                const Dim &d0 = tensors[op.inputs[0]].dims;
+                rc = petb200_transpose_halo_plan(ctx, (int)d0.size(), d0.data(), &op.tr, op.halo[0], op.halo[1], op.halo[2], op.halo[3], &s.plan);
+                s.name = "transpose_halo";
+                s.launches = op.halo[0] ? 2 : 1;
+                break;
+            }
             std::vector<petb200_transpose_desc> chain = {op.tr};
             int last = id;
             while (fuse) { // extend the chain while the intermediate has a single consumer that is a transpose
                 int c = sole_consumer(ops[last].outputs[0]);
-                if (c < 0 || ops[c].type != Transpose)
+                if (c < 0 || ops[c].type != Transpose || has_halo(ops[c]))
                     break;
                 chain.push_back(ops[c].tr);
                 petb200_plan *trial = nullptr;
@@ -1047,6 +1056,32 @@ extern "C" int petb200_graph_transpose(petb200_graph *g, int x, const petb200_tr
     return PETB200_OK;
 }
 
+// A TransposeOp with the reference's padding / halo parameters (ref: TransposeOp::setPaddingSize + getTTParam,
+// include/operator.h:1187-1190, src/Graph/operator.cc:2403-2441); see petb200_transpose_halo_plan.
+extern "C" int petb200_graph_transpose_halo(petb200_graph *g, int x, const petb200_transpose_desc *desc, int pad, int extr, int copys,
+                                            int dels, int *out) {
+    if (!g || !desc || !out)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, x);
+    const Dim &d = g->tensors[x].dims;
+    petb200_plan *trial = nullptr; // shape inference and validation are the lowering's
+    int rc = petb200_transpose_halo_plan(g->ctx, (int)d.size(), d.data(), desc, pad, extr, copys, dels, &trial);
+    if (rc)
+        return g->pass(rc);
+    int od[16];
+    int nd = petb200_layout_out_dims(trial, od);
+    petb200_plan_destroy(trial);
+    Operator op;
+    op.type = Transpose;
+    op.inputs = {x};
+    op.tr = *desc;
+    op.halo[0] = pad, op.halo[1] = extr, op.halo[2] = copys, op.halo[3] = dels;
+    *out = g->new_tensor(Dim(od, od + nd), g->tensors[x].weight);
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
 static int pad_slice(petb200_graph *g, OpType type, int x, const int *begin, const int *end, int *out) {
     if (!g || !begin || !end || !out)
         return PETB200_ERR_INVALID;
@@ -1442,7 +1477,7 @@ extern "C" int petb200_graph_perf(petb200_graph *g, int rounds, int warmup, floa
                 for (int t : op.inputs)
                     key.insert(key.end(), g->tensors[t].dims.begin(), g->tensors[t].dims.end());
                 int attrs[] = {op.ph, op.pw, op.sh, op.sw, op.dh, op.dw, op.act, op.bias >= 0, op.transA, op.transB, op.dim, op.num,
-                               op.tr.split, op.tr.factor, op.tr.ngroups, op.win[0], op.win[1], op.win[2], op.win[3], op.oph, op.opw, op.width, op.dilation};
+                               op.tr.split, op.tr.factor, op.tr.ngroups, op.win[0], op.win[1], op.win[2], op.win[3], op.oph, op.opw, op.width, op.dilation, op.halo[0], op.halo[1], op.halo[2], op.halo[3]};
                 key.insert(key.end(), attrs, attrs + sizeof attrs / sizeof attrs[0]);
                 key.insert(key.end(), op.tr.flat, op.tr.flat + 8);
                 key.insert(key.end(), op.tr.group_sizes, op.tr.group_sizes + 8);

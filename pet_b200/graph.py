@@ -29,6 +29,7 @@ GRAPH_SYMBOLS = {
     "petb200_graph_gbmml": (_i, [_vp, _i, _i, _i, _ip]),
     "petb200_graph_matmul": (_i, [_vp, _i, _i, _i, _i, _i, _i, _ip]),
     "petb200_graph_transpose": (_i, [_vp, _i, C.POINTER(L.TransposeDesc), _ip]),
+    "petb200_graph_transpose_halo": (_i, [_vp, _i, C.POINTER(L.TransposeDesc), _i, _i, _i, _i, _ip]),
     "petb200_graph_pad": (_i, [_vp, _i, _ip, _ip, _ip]),
     "petb200_graph_slice": (_i, [_vp, _i, _ip, _ip, _ip]),
     "petb200_graph_extend": (_i, [_vp, _i, _i, _i, _ip]),
@@ -141,7 +142,8 @@ class Graph:
     def matmul(self, A, B, transA=False, transB=False, bias=None, act="none"):
         return self._out(self.lib.petb200_graph_matmul, A.id, B.id, _tid(bias), int(transA), int(transB), L.ACT[act])
 
-    def transpose(self, input, split, after, factor=2):
+    @staticmethod
+    def _desc(split, after, factor):
         groups = [list(g) if isinstance(g, (list, tuple)) else [g] for g in after]
         d = L.TransposeDesc()
         d.split, d.factor, d.ngroups = split, factor, len(groups)
@@ -150,7 +152,17 @@ class Graph:
             d.group_sizes[i] = len(g)
         for i, v in enumerate(flat):
             d.flat[i] = v
-        return self._out(self.lib.petb200_graph_transpose, input.id, C.byref(d))
+        return d
+
+    def transpose(self, input, split, after, factor=2):
+        return self._out(self.lib.petb200_graph_transpose, input.id, C.byref(self._desc(split, after, factor)))
+
+    def transpose_halo(self, input, split, after, factor, mode, amount):
+        """TransposeOp with `amount` of pad / extr / copys / dels (what setPaddingSize + Pre/Post select in the reference)."""
+        if mode not in ("pad", "extr", "copys", "dels"):
+            raise L.PetError(L.ERR_INVALID, "mode must be pad, extr, copys or dels")
+        a = [amount if m == mode else 0 for m in ("pad", "extr", "copys", "dels")]
+        return self._out(self.lib.petb200_graph_transpose_halo, input.id, C.byref(self._desc(split, after, factor)), *a)
 
     def flatten(self, input, axis):
         nd = len(input.dims)  # Graph::flatten, src/Graph/graph.cc:342-358

@@ -24,6 +24,9 @@ class OracleBuilder:
     def transpose(self, x, split, after, factor=2):
         return po.transpose(x, split, after, factor)
 
+    def transpose_halo(self, x, split, after, factor, mode, amount):
+        return po.transpose_halo(x, split, after, factor, mode, amount)
+
     def pad(self, x, begin, end):
         return po.pad(x, begin, end)
 

@@ -46,6 +46,16 @@ def test_c1_rewrite_with_correction_is_bit_identical_to_original(ctx):
     assert rel_err(y0, want) <= TOL and scale_err(y0, want) <= TOL_SCALE
 
 
+def test_c1_rewrite_with_halo_transposes_is_bit_identical_to_original(ctx):
+    from pet_b200 import configs
+    x, w = configs.c1_tensors()
+    _, _, y0 = run_config(ctx, configs.c1_original, x, w)
+    g, _, y1 = run_config(ctx, configs.c1_rewrite_halo, x, w)
+    assert [n for n, _ in g.steps()] == ["transpose_halo", "conv", "transpose_halo"]
+    assert np.array_equal(y0, y1)  # same K order per output: the halo route needs no correction
+    assert rel_err(y1, oracle_config(configs.c1_rewrite_halo, x, w)) <= TOL
+
+
 def test_c2_rewrite_fuses_chains_and_matches_original(ctx):
     from pet_b200 import configs
     x, w = configs.c2_tensors(c=64, hw=32, k=96)
