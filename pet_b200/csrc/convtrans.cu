@@ -10,10 +10,24 @@
 //      (one pass: a 32x32 transpose through shared memory, channel-contiguous reads, row-contiguous writes);
 //   2. the implicit-GEMM convolution over xe with the flipped filter, its epilogue writing y channels-last directly.
 // The filter flip (and the reference's skipped taps) is weight-only work done once in set_weights.
+//
+// For strides above 1 on problems large enough to pay for the extra launches the zeros are not multiplied at all: output
+// rows hh = a (mod sh) only meet the filter taps rr = rr0(a) (mod sh), so each of the sh*sw phases (a,b) is a stride-1
+// convolution of the ORIGINAL input (brought to NCHW once) with a sub-filter of ceil-ish(r/sh) x (s/sw) taps, writing every
+// sh-th row and sw-th column of y (tc_conv_create_view: signed padding, explicit window, free output strides).
 #include "common.h"
 #include <algorithm>
+#include <vector>
 
 namespace petb200 {
+
+int tc_conv_create_view(petb200_ctx *ctx, int n, int c, int h, int w, int f, int r, int s, int pad_h, int pad_w, int ohn, int own,
+                        int ow_nominal, long long ys_n, long long ys_f, long long ys_p, int has_bias, int act, int passes, void **out,
+                        size_t *dev_bytes);
+void tc_conv_destroy(void *h);
+int tc_conv_set_weights(void *h, const float *w, cudaStream_t s);
+int tc_conv_run(void *h, const float *x, const float *bias, const float *res, float *y, const int *win, cudaStream_t s);
+const char *tc_conv_variant(void *h);
 
 namespace {
 
@@ -71,14 +85,52 @@ __global__ void __launch_bounds__(256) k_convtrans_flip_w(const float *__restric
     }
 }
 
+// Sub-filter of one phase: [c][f][Ta][Tb], tap (t,t') = flipped tap (rr0 + sh*t, ss0 + sw*t') of the full filter.
+__global__ void __launch_bounds__(256) k_convtrans_phase_w(const float *__restrict__ w, float *__restrict__ wf, int r, int s, int f,
+                                                           int c, int ah, int aw, int rr0, int sh, int Ta, int ss0, int sw, int Tb) {
+    pdl_prologue();
+    const long long total = (long long)c * f * Ta * Tb;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        long long rem = i;
+        const int tb = (int)(rem % Tb);
+        rem /= Tb;
+        const int ta = (int)(rem % Ta);
+        rem /= Ta;
+        const int ff = (int)(rem % f);
+        const int cc = (int)(rem / f);
+        const int rr = rr0 + sh * ta, ss = ss0 + sw * tb;
+        float v = 0.f;
+        if (!(r - ah < rr || s - aw < ss))
+            v = __ldg(w + cc + (size_t)c * (ff + (size_t)f * ((s - 1 - ss) + (size_t)s * (r - 1 - rr))));
+        wf[i] = v;
+    }
+}
+
+struct Phase {
+    void *tc = nullptr;
+    DevBuf wsub;
+    int a = 0, b = 0, rr0 = 0, ss0 = 0, Ta = 0, Tb = 0;
+    ~Phase() {
+        if (tc)
+            tc_conv_destroy(tc);
+    }
+};
+
 struct ConvTransPlan : petb200_plan {
+    std::vector<Phase *> phases; // non-empty: the phase decomposition is used instead of `conv`
+    DevBuf xn;                   // x as NCHW for the phase convolutions
+    int sh = 1, sw = 1;
     ExpandGeom g{};
     int r = 0, s = 0, c = 0, oh = 0, ow = 0, ah = 0, aw = 0, has_bias = 0;
     petb200_plan *conv = nullptr;
     DevBuf xe, wflip;
     DevBuf bx, bw, bb, by; // timing operands
     bool weights_ready = false;
-    ~ConvTransPlan() override { delete conv; }
+    ~ConvTransPlan() override {
+        delete conv;
+        for (Phase *p : phases)
+            delete p;
+    }
     int bench_launch(cudaStream_t s) override;
 };
 
@@ -117,6 +169,52 @@ int make_convtrans_plan(petb200_ctx *ctx, const int *a /*n,c,h,w,f,r,s,ph,pw,sh,
     }
     pl->kernel = pl->conv->kernel;
     pl->device_bytes = pl->conv->device_bytes + xe_bytes + w_bytes;
+    pl->sh = sh, pl->sw = sw;
+    // Phase decomposition: worth its sh*sw + 1 launches once the zero-inserted product is large (rough model from
+    // measurements on B200: the zero-inserted conv sustains ~100 TFLOP/s of issued work, a phase conv ~170 with a floor
+    // of ~8 us per launch).  Needs taps in every phase and a row stride of y that is a whole number of phase pixels.
+    const double issued = 2.0 * n * c * (double)oh * ow * f * r * s;
+    const double us_inserted = issued / 100e6, us_phased = sh * sw * std::max(8.0, issued / (sh * sw) / 170e6);
+    const bool tc_algo = algo == PETB200_ALGO_AUTO || algo == PETB200_ALGO_TC_3XTF32 || algo == PETB200_ALGO_TC_1XTF32;
+    const char *env = getenv("PETB200_CONVTRANS_PHASES");
+    const int want = env ? atoi(env) : -1; // 0 never, 1 whenever possible, unset: by size
+    if (tc_algo && sh * sw > 1 && r >= sh && s >= sw && ((long long)sh * ow) % sw == 0 && want != 0 && (want == 1 || us_phased < us_inserted) &&
+        ctx->cc_major == 10) {
+        const int lead_h = r - ph - 1, lead_w = s - pw - 1;
+        auto mod = [](int v, int m) { return ((v % m) + m) % m; };
+        bool ok = true;
+        size_t extra = 0;
+        for (int a = 0; a < sh && ok; ++a)
+            for (int b = 0; b < sw && ok; ++b) {
+                if (a >= oh || b >= ow)
+                    continue; // no output row / column in this phase
+                auto *ps = new Phase();
+                pl->phases.push_back(ps);
+                ps->a = a, ps->b = b;
+                ps->rr0 = mod(lead_h - a, sh), ps->ss0 = mod(lead_w - b, sw);
+                ps->Ta = (r - ps->rr0 + sh - 1) / sh, ps->Tb = (s - ps->ss0 + sw - 1) / sw;
+                const int off_a = (a + ps->rr0 - lead_h) / sh, off_b = (b + ps->ss0 - lead_w) / sw; // exact divisions
+                const int Ua = (oh - a + sh - 1) / sh, Vb = (ow - b + sw - 1) / sw;
+                size_t bytes = 0;
+                int prc = tc_conv_create_view(ctx, n, f, h, w, c, ps->Ta, ps->Tb, -off_a, -off_b, Ua, Vb, (int)(((long long)sh * ow) / sw),
+                                              (long long)oh * ow * c, 1, (long long)sw * c, has_bias, act,
+                                              algo == PETB200_ALGO_TC_1XTF32 ? 1 : 3, &ps->tc, &bytes);
+                if (prc != PETB200_OK || ps->wsub.alloc((size_t)c * f * ps->Ta * ps->Tb * 4) != cudaSuccess)
+                    ok = false;
+                extra += bytes + ps->wsub.bytes;
+            }
+        if (ok && pl->xn.alloc((size_t)n * f * h * w * 4) != cudaSuccess)
+            ok = false;
+        if (!ok) { // keep the zero-insertion path
+            for (Phase *p : pl->phases)
+                delete p;
+            pl->phases.clear();
+            pl->xn.alloc(0);
+        } else {
+            pl->device_bytes += extra + pl->xn.bytes;
+            pl->kernel = tc_conv_variant(pl->phases.front()->tc);
+        }
+    }
     *out = pl;
     return PETB200_OK;
 }
@@ -133,6 +231,17 @@ int convtrans_set_weights(petb200_plan *plan, const float *w, cudaStream_t s) {
     if (rc)
         return rc;
     rc = conv_set_weights(pl->conv, (const float *)pl->wflip.p, s);
+    for (Phase *ps : pl->phases) {
+        if (rc)
+            break;
+        const long long tot = (long long)pl->c * pl->g.f * ps->Ta * ps->Tb;
+        const int nb = (int)std::max<long long>(1, std::min<long long>((tot + 255) / 256, (long long)ctx->sm_count * 16));
+        launch_pdl(k_convtrans_phase_w, nb, 256, 0, s, w, (float *)ps->wsub.p, pl->r, pl->s, pl->g.f, pl->c, pl->ah, pl->aw, ps->rr0, pl->sh,
+                   ps->Ta, ps->ss0, pl->sw, ps->Tb);
+        rc = launched(ctx, "k_convtrans_phase_w");
+        if (rc == PETB200_OK)
+            rc = tc_conv_set_weights(ps->tc, (const float *)ps->wsub.p, s);
+    }
     pl->weights_ready = rc == PETB200_OK;
     return rc;
 }
@@ -146,6 +255,23 @@ int convtrans_run(petb200_plan *plan, const float *x, const float *bias, float *
         return fail(ctx, PETB200_ERR_INVALID, "convtrans run: null buffer");
     if (!pl->weights_ready)
         return fail(ctx, PETB200_ERR_INVALID, "convtrans run before set_weights");
+    if (!pl->phases.empty()) {
+        if (pl->has_bias && !bias)
+            return fail(ctx, PETB200_ERR_INVALID, "convtrans run: plan was made with a bias but none was passed");
+        // x {n,h,w,f} -> NCHW once (the expansion kernel without insertion), then one convolution per phase
+        const ExpandGeom t{pl->g.n, pl->g.h, pl->g.w, pl->g.f, pl->g.h, pl->g.w, 0, 0, 1, 1};
+        const dim3 tg((unsigned)((t.Wb + 31) / 32), (unsigned)t.Hb, (unsigned)(t.n * ((t.f + 31) / 32)));
+        if (tg.y > 65535u || tg.z > 65535u)
+            return fail(ctx, PETB200_ERR_UNSUPPORTED, "convtrans run: image too tall or too many channel tiles for one launch");
+        launch_pdl(k_convtrans_expand, tg, dim3(32, 8), 0, s, x, (float *)pl->xn.p, t);
+        int rc = launched(ctx, "k_convtrans_expand");
+        for (Phase *ps : pl->phases) {
+            if (rc)
+                return rc;
+            rc = tc_conv_run(ps->tc, (const float *)pl->xn.p, bias, nullptr, y + ((size_t)ps->a * pl->ow + ps->b) * pl->c, nullptr, s);
+        }
+        return rc;
+    }
     const ExpandGeom &g = pl->g;
     const dim3 grid((unsigned)((g.Wb + 31) / 32), (unsigned)g.Hb, (unsigned)(g.n * ((g.f + 31) / 32)));
     if (grid.y > 65535u || grid.z > 65535u)

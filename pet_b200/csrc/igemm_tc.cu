@@ -1469,6 +1469,57 @@ int tc_conv_create(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const i
     return PETB200_OK;
 }
 
+// A stride-1, dilation-1 2-D convolution whose geometry is given explicitly instead of derived: signed padding (a negative
+// value crops; whatever falls outside the input reads as zero on every side, so bottom/right padding is whatever the
+// output extent asks for), an output window of ohn x own pixels, and free output strides {image, filter, row, pixel}
+// with row = ow_nominal * pixel.  Used by the transposed convolution, whose sh*sw phases are such convolutions writing
+// every sh-th row and sw-th column of a channels-last tensor.
+int tc_conv_create_view(petb200_ctx *ctx, int n, int c, int h, int w, int f, int r, int s, int pad_h, int pad_w, int ohn, int own,
+                        int ow_nominal, long long ys_n, long long ys_f, long long ys_p, int has_bias, int act, int passes, void **out,
+                        size_t *dev_bytes) {
+    if (ctx->cc_major != 10)
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "tcgen05 kernels need compute capability 10.x, device has %d.%d", ctx->cc_major, ctx->cc_minor);
+    if (ohn <= 0 || own <= 0 || own > ow_nominal)
+        return fail(ctx, PETB200_ERR_INVALID, "conv view: empty or oversized window");
+    auto *t = new TcConv();
+    ConvGeom &g = t->g;
+    g.N = n, g.C = c, g.D = 1, g.H = h, g.W = w, g.Wst = w, g.F = f, g.groups = 1;
+    g.T3[0] = 1, g.T3[1] = r, g.T3[2] = s;
+    g.pad[0] = 0, g.pad[1] = pad_h, g.pad[2] = pad_w;
+    for (int i = 0; i < 3; ++i)
+        g.stride[i] = 1, g.dil[i] = 1;
+    g.OD = 1, g.OH = ohn, g.OW = ow_nominal;
+    t->has_bias = has_bias;
+    t->act = act;
+    t->full.ctx = ctx;
+    t->full.single_pass = passes == 1;
+    t->ys[0] = ys_n, t->ys[1] = ys_f, t->ys[2] = ys_p;
+    int rc = PETB200_ERR_UNSUPPORTED;
+    if (w % 4 != 0)
+        rc = tc_configure(ctx, t->full, g, 0, ohn, 0, own, 0, n, ys_n, ys_f, ys_p, has_bias, act, 0, 0, 0, 1);
+    else
+        rc = tc_configure(ctx, t->full, g, 0, ohn, 0, own, 0, n, ys_n, ys_f, ys_p, has_bias, act);
+    if (rc) {
+        delete t;
+        return rc;
+    }
+    TcCore &core = t->full;
+    core.rows_b = f;
+    const size_t wbytes = (size_t)f * core.Ktot * 4;
+    if (core.whi.alloc(wbytes) != cudaSuccess || core.wlo.alloc(wbytes) != cudaSuccess) {
+        delete t;
+        return fail(ctx, PETB200_ERR_NOMEM, "packed weight allocation (%zu bytes) failed", 2 * wbytes);
+    }
+    rc = core.encode_b();
+    if (rc) {
+        delete t;
+        return rc;
+    }
+    *dev_bytes = 2 * wbytes + core.koff.bytes;
+    *out = t;
+    return PETB200_OK;
+}
+
 void tc_conv_destroy(void *h) { delete (TcConv *)h; }
 
 int tc_conv_set_weights(void *h, const float *w, cudaStream_t s) {

@@ -173,18 +173,21 @@ class Context:
         p.out_shape = tuple(od)
         return p
 
-    def convtrans(self, x, w, ph, pw, sh=1, sw=1, dh=1, dw=1, oph=0, opw=0, bias=None, act="none", algo="auto"):
-        key = ("convtrans", tuple(x.shape), tuple(w.shape), ph, pw, sh, sw, dh, dw, oph, opw, bias is not None, act, algo)
-        plan = self._plans.get(key)
-        if plan is None:
-            plan = self._plans[key] = self.convtrans_plan(x.shape, w.shape, ph, pw, sh, sw, dh, dw, oph, opw,
-                                                          bias is not None, act, algo)
+    def convtrans_run(self, plan, x, w, bias=None):
         plan._w = _f32(w)
         self.check(self.lib.petb200_convtrans_set_weights(plan.h, _ptr(plan._w), _stream()))
         y = torch.empty(plan.out_shape, device=x.device, dtype=torch.float32)
         self.check(self.lib.petb200_convtrans_run(plan.h, _ptr(_f32(x)), _ptr(_f32(bias) if bias is not None else None),
                                                   _ptr(y), _stream()))
         return y
+
+    def convtrans(self, x, w, ph, pw, sh=1, sw=1, dh=1, dw=1, oph=0, opw=0, bias=None, act="none", algo="auto"):
+        key = ("convtrans", tuple(x.shape), tuple(w.shape), ph, pw, sh, sw, dh, dw, oph, opw, bias is not None, act, algo)
+        plan = self._plans.get(key)
+        if plan is None:
+            plan = self._plans[key] = self.convtrans_plan(x.shape, w.shape, ph, pw, sh, sw, dh, dw, oph, opw,
+                                                          bias is not None, act, algo)
+        return self.convtrans_run(plan, x, w, bias)
 
     def g2bmm(self, q, k, width, dilation=1):
         """Banded Q.K^T: q, k [b,n,m] -> [b,n,2*width+1]; key row i + dilation*(j-width), zero outside [0,n)."""

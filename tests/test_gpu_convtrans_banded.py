@@ -65,6 +65,42 @@ def test_convtrans_vs_oracle(ctx, oracle, case, algo):
     assert scale_err(y, want) <= TOL_SCALE
 
 
+PHASE_CASES = CT_CASES + [
+    ("stride3_k5", (2, 7, 6, 16), (5, 5, 16, 8), dict(pad=(1, 2), stride=(3, 3), out_pad=(2, 1))),
+    ("stride2x1", (1, 9, 10, 8), (3, 3, 8, 8), dict(pad=(1, 1), stride=(2, 1))),
+    ("odd_width_phases", (1, 7, 7, 24), (4, 4, 24, 20), dict(pad=(1, 1), stride=(2, 2))),
+    ("large_batch", (8, 32, 32, 128), (4, 4, 128, 64), dict(pad=(1, 1), stride=(2, 2))),
+]
+
+
+@pytest.mark.parametrize("case", PHASE_CASES, ids=[c[0] for c in PHASE_CASES])
+def test_convtrans_phase_decomposition_vs_oracle(ctx, oracle, case, monkeypatch):
+    """The sh*sw phase convolutions (forced on, whatever the problem size) against the oracle, with bias and ReLU; where
+    the shape does not allow them the plan keeps the zero-insertion path and must agree all the same."""
+    name, xs, ws, kw = case
+    monkeypatch.setenv("PETB200_CONVTRANS_PHASES", "1")
+    rng = np.random.default_rng(len(name) * 7919 + xs[1])
+    x = rng.uniform(-1, 1, xs).astype(np.float32)
+    w = (rng.standard_normal(ws) * np.sqrt(2.0 / (ws[0] * ws[1] * ws[2]))).astype(np.float32)
+    b = rng.uniform(-1, 1, ws[3]).astype(np.float32)
+    pad, st, op = kw.get("pad", (0, 0)), kw.get("stride", (1, 1)), kw.get("out_pad", (0, 0))
+    plan = ctx.convtrans_plan(xs, ws, pad[0], pad[1], st[0], st[1], 1, 1, op[0], op[1], bias=True, act="relu")
+    y = ctx.convtrans_run(plan, dev(x), dev(w), dev(b)).cpu().numpy()
+    ctx.sync_check()
+    want = np.maximum(oracle.convtrans(x, w, wide=True, **kw) + b, 0)
+    assert y.shape == want.shape
+    assert rel_err(y, want) <= TOL and scale_err(y, want) <= TOL_SCALE
+    # small integers: exact, also against the zero-insertion path
+    xi = rng.integers(0, 8, xs).astype(np.float32)
+    wi = rng.integers(0, 8, ws).astype(np.float32)
+    yi = ctx.convtrans_run(plan, dev(xi), dev(wi), dev(np.zeros(ws[3], np.float32))).cpu().numpy()
+    monkeypatch.setenv("PETB200_CONVTRANS_PHASES", "0")
+    plan0 = ctx.convtrans_plan(xs, ws, pad[0], pad[1], st[0], st[1], 1, 1, op[0], op[1], bias=True, act="relu")
+    y0 = ctx.convtrans_run(plan0, dev(xi), dev(wi), dev(np.zeros(ws[3], np.float32))).cpu().numpy()
+    assert np.array_equal(yi, y0)
+    assert np.array_equal(yi, oracle.convtrans(xi, wi, wide=False, **kw))
+
+
 def test_convtrans_bias_activation_and_torch(ctx, oracle):
     rng = np.random.default_rng(3)
     x = rng.uniform(-1, 1, (2, 9, 9, 32)).astype(np.float32)
