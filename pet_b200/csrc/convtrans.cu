@@ -118,6 +118,11 @@ struct Phase {
 
 struct ConvTransPlan : petb200_plan {
     std::vector<Phase *> phases; // non-empty: the phase decomposition is used instead of `conv`
+    // The phases write disjoint pixels of y and each fills only part of the GPU, so they run side by side: phase i goes to
+    // stream i % 4 (0 = the caller's), forked after the layout pass and joined before the call returns to the stream.
+    static constexpr int kSide = 3;
+    cudaStream_t side[kSide] = {nullptr, nullptr, nullptr};
+    cudaEvent_t ev_fork = nullptr, ev_join[kSide] = {nullptr, nullptr, nullptr};
     DevBuf xn;                   // x as NCHW for the phase convolutions
     int sh = 1, sw = 1;
     ExpandGeom g{};
@@ -130,6 +135,14 @@ struct ConvTransPlan : petb200_plan {
         delete conv;
         for (Phase *p : phases)
             delete p;
+        for (int i = 0; i < kSide; ++i) {
+            if (side[i])
+                cudaStreamDestroy(side[i]);
+            if (ev_join[i])
+                cudaEventDestroy(ev_join[i]);
+        }
+        if (ev_fork)
+            cudaEventDestroy(ev_fork);
     }
     int bench_launch(cudaStream_t s) override;
 };
@@ -265,10 +278,30 @@ int convtrans_run(petb200_plan *plan, const float *x, const float *bias, float *
             return fail(ctx, PETB200_ERR_UNSUPPORTED, "convtrans run: image too tall or too many channel tiles for one launch");
         launch_pdl(k_convtrans_expand, tg, dim3(32, 8), 0, s, x, (float *)pl->xn.p, t);
         int rc = launched(ctx, "k_convtrans_expand");
-        for (Phase *ps : pl->phases) {
-            if (rc)
-                return rc;
-            rc = tc_conv_run(ps->tc, (const float *)pl->xn.p, bias, nullptr, y + ((size_t)ps->a * pl->ow + ps->b) * pl->c, nullptr, s);
+        if (rc)
+            return rc;
+        const int nside = std::min<int>(ConvTransPlan::kSide, (int)pl->phases.size() - 1);
+        if (nside > 0 && !pl->ev_fork) {
+            PETB200_CUDA(ctx, cudaEventCreateWithFlags(&pl->ev_fork, cudaEventDisableTiming));
+            for (int i = 0; i < nside; ++i) {
+                PETB200_CUDA(ctx, cudaStreamCreateWithFlags(&pl->side[i], cudaStreamNonBlocking));
+                PETB200_CUDA(ctx, cudaEventCreateWithFlags(&pl->ev_join[i], cudaEventDisableTiming));
+            }
+        }
+        if (nside > 0) {
+            PETB200_CUDA(ctx, cudaEventRecord(pl->ev_fork, s));
+            for (int i = 0; i < nside; ++i)
+                PETB200_CUDA(ctx, cudaStreamWaitEvent(pl->side[i], pl->ev_fork, 0));
+        }
+        for (size_t i = 0; i < pl->phases.size() && rc == PETB200_OK; ++i) {
+            Phase *ps = pl->phases[i];
+            const int lane = (int)(i % (size_t)(nside + 1));
+            rc = tc_conv_run(ps->tc, (const float *)pl->xn.p, bias, nullptr, y + ((size_t)ps->a * pl->ow + ps->b) * pl->c, nullptr,
+                             lane == 0 ? s : pl->side[lane - 1]);
+        }
+        for (int i = 0; i < nside; ++i) { // join even after a failed launch, so that a capture in progress stays well-formed
+            cudaEventRecord(pl->ev_join[i], pl->side[i]);
+            cudaStreamWaitEvent(s, pl->ev_join[i], 0);
         }
         return rc;
     }

@@ -173,9 +173,11 @@ class Context:
         p.out_shape = tuple(od)
         return p
 
-    def convtrans_run(self, plan, x, w, bias=None):
-        plan._w = _f32(w)
-        self.check(self.lib.petb200_convtrans_set_weights(plan.h, _ptr(plan._w), _stream()))
+    def convtrans_run(self, plan, x, w=None, bias=None):
+        """w given: (re)do the weight-only work first; w None: reuse the weights of the previous call."""
+        if w is not None:
+            plan._w = _f32(w)
+            self.check(self.lib.petb200_convtrans_set_weights(plan.h, _ptr(plan._w), _stream()))
         y = torch.empty(plan.out_shape, device=x.device, dtype=torch.float32)
         self.check(self.lib.petb200_convtrans_run(plan.h, _ptr(_f32(x)), _ptr(_f32(bias) if bias is not None else None),
                                                   _ptr(y), _stream()))
