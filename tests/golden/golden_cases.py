@@ -82,3 +82,17 @@ def tpm_text(arr):
     flat = np.asarray(arr, dtype=np.uint32).ravel()
     lines = [" ".join(map(str, flat[i:i + 32])) + " \n" for i in range(0, flat.size, 32)]
     return "".join(lines).encode()
+
+
+def convtrans_kat():
+    """Inputs and expected output of the reference's own ConvTransOp test (src/Test/convtrans_test_1.cc:14-76): x = its own
+    offset, weight[r,s,f,c] = ((f*R + r)*S + s)*C + c, 4x4 filter, stride 2, padding 1; the expected values are the ones
+    that test lists (as [c][oh][ow])."""
+    n, c, h, w, f, r, s = 1, 2, 2, 2, 3, 4, 4
+    x = np.arange(n * h * w * f, dtype=np.uint32).reshape(n, h, w, f)
+    rr, ss, ff, cc = np.meshgrid(np.arange(r), np.arange(s), np.arange(f), np.arange(c), indexing="ij")
+    wt = (((ff * r + rr) * s + ss) * c + cc).astype(np.uint32)
+    want = np.array([[[190, 740, 770, 592], [992, 2704, 2836, 1832], [1184, 3232, 3364, 2168], [1114, 2660, 2762, 1624]],
+                     [[193, 755, 785, 604], [1016, 2770, 2902, 1874], [1208, 3298, 3430, 2210], [1135, 2711, 2813, 1654]]],
+                    np.uint32)
+    return x, wt, dict(pad=(1, 1), stride=(2, 2)), np.ascontiguousarray(want.transpose(1, 2, 0))[None]

@@ -38,6 +38,17 @@ def test_convtrans_on_reference_integer_vectors(ctx, golden, algo, i):
     assert np.array_equal(y.cpu().numpy().astype(np.uint32), want)
 
 
+@pytest.mark.parametrize("algo", ["tc_3xtf32", "simt_fp32"])
+@pytest.mark.parametrize("phases", ["0", "1"])
+def test_convtrans_known_answer_of_the_reference_test(ctx, algo, phases, monkeypatch):
+    monkeypatch.setenv("PETB200_CONVTRANS_PHASES", phases)
+    x, wt, kw, want = gc.convtrans_kat()
+    plan = ctx.convtrans_plan(x.shape, wt.shape, 1, 1, 2, 2, algo=algo)
+    y = ctx.convtrans_run(plan, dev(x.astype(np.float32)), dev(wt.astype(np.float32)))
+    ctx.sync_check()
+    assert np.array_equal(y.cpu().numpy().astype(np.uint32), want)
+
+
 CT_CASES = [
     # name, x {n,h,w,f}, w {r,s,f,c}, kwargs
     ("upsample2x_k4", (1, 16, 16, 64), (4, 4, 64, 32), dict(pad=(1, 1), stride=(2, 2))),
