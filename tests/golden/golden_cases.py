@@ -96,3 +96,18 @@ def convtrans_kat():
                      [[193, 755, 785, 604], [1016, 2770, 2902, 1874], [1208, 3298, 3430, 2210], [1135, 2711, 2813, 1654]]],
                     np.uint32)
     return x, wt, dict(pad=(1, 1), stride=(2, 2)), np.ascontiguousarray(want.transpose(1, 2, 0))[None]
+
+
+def reshape_transpose_definitions():
+    """The reshape/transpose statements of D2H, its inverse, N2H and H2N that the reference's transpose_test_2.py gives
+    (src/Test/transpose_test_2.py:4-33), as (name, input, TransposeOp arguments, expected) on that file's shapes."""
+    i0 = np.arange(64, dtype=np.uint32).reshape(1, 1, 8, 8)
+    d2h = i0.reshape(1, 1, 4, 2, 8).transpose(0, 1, 3, 2, 4).reshape(1, 1, 8, 8)           # h_d2_d1
+    d2h_inv = d2h.reshape(1, 1, 2, 4, 8).transpose(0, 1, 3, 2, 4).reshape(1, 1, 8, 8)      # h_d1_d2
+    j0 = np.arange(32, dtype=np.uint32).reshape(2, 1, 4, 4)
+    n2h = j0.reshape(1, 2, 1, 4, 4).transpose(0, 2, 1, 3, 4).reshape(1, 1, 8, 4)           # nd2_hm2
+    h2n = n2h.reshape(1, 1, 2, 4, 4).transpose(0, 2, 1, 3, 4).reshape(2, 1, 4, 4)          # nm2_hd2
+    return [("D2H", i0, TRANSPOSES["D2H"][1:], np.ascontiguousarray(d2h)),
+            ("D2H_inv", np.ascontiguousarray(d2h), TRANSPOSES["D2H_inv"][1:], np.ascontiguousarray(d2h_inv)),
+            ("N2H", j0, TRANSPOSES["N2H"][1:], np.ascontiguousarray(n2h)),
+            ("H2N", np.ascontiguousarray(n2h), TRANSPOSES["H2N"][1:], np.ascontiguousarray(h2n))]

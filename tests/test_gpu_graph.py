@@ -114,6 +114,32 @@ def test_r3d18_reduced(ctx):
     assert rel_err(y, want) <= TOL
 
 
+def test_group_conv_merge_property_of_the_reference_test(ctx):
+    """src/Test/group_conv_test_1.cc as a graph: extend + concat + grouped conv + ratio split equals the two separate convs
+    (small integers: exact)."""
+    import golden_cases as gc
+    from pet_b200.graph import Graph
+    g = Graph(ctx)
+    i0, i1 = g.tensor([1, 2, 4, 4]), g.tensor([1, 2, 4, 4])
+    w0, w1 = g.tensor([4, 2, 3, 3], weight=True), g.tensor([6, 2, 3, 3], weight=True)
+    merged = g.conv(g.concat([g.extend(i0, 1, 1), g.extend(i1, 1, 2)], 1), g.concat([w0, w1], 0), 1, 1)
+    o0, o1 = g.split(merged, 1, [2, 3])
+    t0, t1 = g.conv(i0, w0, 1, 1), g.conv(i1, w1, 1, 1)
+    g.setOutputs([o0, o1, t0, t1])
+    g.compile()
+    data = {i0: gc.small_ints((1, 2, 4, 4), 61) % 16, i1: gc.small_ints((1, 2, 4, 4), 62) % 16,
+            w0: gc.small_ints((4, 2, 3, 3), 63) % 16, w1: gc.small_ints((6, 2, 3, 3), 64) % 16}
+    for t, a in data.items():
+        g.set_data(t, a.astype(np.float32))
+    g.run()
+    torch.cuda.synchronize()
+    ctx.sync_check()
+    assert tuple(o0.dims) == (1, 4, 4, 4) and tuple(o1.dims) == (1, 6, 4, 4)
+    assert np.array_equal(g.get_data(o0), g.get_data(t0)) and np.array_equal(g.get_data(o1), g.get_data(t1))
+    from oracle import pet_oracle as po
+    assert np.array_equal(g.get_data(t0).astype(np.uint32), po.conv2d_u32(data[i0], data[w0], pad=(1, 1)))
+
+
 def test_convtrans_and_banded_attention_in_a_graph(ctx, oracle):
     """convTrans -> relu, and g2bmm -> softmax -> gbmml (sliding-window attention) built with the reference's method
     names, executed as a captured graph, against the oracle."""

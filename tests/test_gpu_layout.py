@@ -160,3 +160,9 @@ def test_halo_transpose_rejects_bad_requests(ctx):
         ctx.transpose_halo_plan((6, 4, 8, 8), 0, [0, 1, [-1, 2], 3], 3, "dels", 1)         # dels needs a pair [2][n]
     with pytest.raises(PetError):
         ctx.transpose_halo_plan((2, 4, 8, 8), -1, [0, 1, 3, 2], 2, "pad", 1)               # no merged pair
+
+
+def test_transposes_match_the_reference_tests_reshape_definitions(ctx):
+    for name, x, (split, after, factor), want in gc.reshape_transpose_definitions():
+        got = host(ctx.transpose(dev(x), split, after, factor))
+        assert got.shape == want.shape and np.array_equal(got, want), name
