@@ -56,6 +56,37 @@ def test_c1_rewrite_with_halo_transposes_is_bit_identical_to_original(ctx):
     assert rel_err(y1, oracle_config(configs.c1_rewrite_halo, x, w)) <= TOL
 
 
+def test_n2h_rewrite_with_zero_gap_transposes_is_bit_identical_to_original(ctx):
+    """The other direction: two images stacked along H with one zero row between them (pad = 1), one convolution over the
+    taller image, and a split that skips the gap row (extr = 1) — as a captured graph, equal to the batched conv."""
+    from pet_b200.graph import Graph
+    rng = np.random.default_rng(31)
+    x = rng.uniform(-1, 1, (2, 32, 28, 28)).astype(np.float32)
+    w = (rng.standard_normal((48, 32, 3, 3)) * 0.06).astype(np.float32)
+    outs = []
+    for rewrite in (False, True):
+        g = Graph(ctx)
+        xi, wi = g.tensor(list(x.shape)), g.tensor(list(w.shape), weight=True)
+        if rewrite:
+            t = g.transpose_halo(xi, 0, [0, 1, [-1, 2], 3], 2, "pad", 1)           # [1,32,57,28]
+            y = g.transpose_halo(g.conv(t, wi, 1, 1), 2, [[0, 2], 1, -1, 3], 28, "extr", 1)
+        else:
+            y = g.conv(xi, wi, 1, 1)
+        g.setOutputs([y])
+        g.compile()
+        g.set_data(xi, x)
+        g.set_data(wi, w)
+        g.run()
+        g.run()
+        torch.cuda.synchronize()
+        ctx.sync_check()
+        assert tuple(y.dims) == (2, 48, 28, 28)
+        outs.append(g.get_data(y))
+        if rewrite:
+            assert [n for n, _ in g.steps()] == ["transpose_halo", "conv", "transpose_halo"]
+    assert np.array_equal(outs[0], outs[1])
+
+
 def test_c2_rewrite_fuses_chains_and_matches_original(ctx):
     from pet_b200 import configs
     x, w = configs.c2_tensors(c=64, hw=32, k=96)
