@@ -142,6 +142,16 @@ def config_latencies(ctx):
         g.run()
         torch.cuda.synchronize()
         out[name] = {"ms": g.time(rounds=200, warmup=20), "kernels": g.num_launches()}
+        # spread of single replays: one event pair per replay (includes the launch gap of a lone replay, so the median sits
+        # a few microseconds above the back-to-back mean)
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(200)]
+        for e0, e1 in evs:
+            e0.record()
+            g.run()
+            e1.record()
+        torch.cuda.synchronize()
+        lat = sorted(e0.elapsed_time(e1) for e0, e1 in evs)
+        out[name].update({"median_ms": lat[len(lat) // 2], "p99_ms": lat[int(len(lat) * 0.99) - 1]})
 
     x, w = configs.c1_tensors()
     run("c1_conv3x3_original", configs.c1_original, x, w)
