@@ -171,10 +171,13 @@ def test_group_conv_merge_property_of_the_reference_test(ctx):
     assert np.array_equal(g.get_data(t0).astype(np.uint32), po.conv2d_u32(data[i0], data[w0], pad=(1, 1)))
 
 
-def test_convtrans_and_banded_attention_in_a_graph(ctx, oracle):
+@pytest.mark.parametrize("phases", ["0", "1"])
+def test_convtrans_and_banded_attention_in_a_graph(ctx, oracle, phases, monkeypatch):
     """convTrans -> relu, and g2bmm -> softmax -> gbmml (sliding-window attention) built with the reference's method
-    names, executed as a captured graph, against the oracle."""
+    names, executed as a captured graph, against the oracle; the transposed convolution through the zero-insertion path
+    and through the phase path (whose convolutions run on forked streams inside the capture)."""
     from pet_b200.graph import Graph
+    monkeypatch.setenv("PETB200_CONVTRANS_PHASES", phases)
     rng = np.random.default_rng(12)
     g = Graph(ctx)
     x = g.tensor([2, 8, 8, 32])
