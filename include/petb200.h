@@ -190,6 +190,22 @@ int petb200_softmax_run(petb200_ctx *ctx, const float *x, float *y, size_t rows,
 int petb200_layernorm_run(petb200_ctx *ctx, const float *x, const float *gamma, const float *beta, float *y,
                           size_t rows, int cols, float eps, petb200_stream stream);
 
+/* ---- the remaining small operators of the graph API ------------------------------------------------------------- */
+/* DivOp (ref: include/operator.h:1580-1628): out[i] = a[i % size_a] / b[i % size_b].  The reference's host body subtracts
+ * (ref: src/Graph/operator.cc:3258-3259) and its code generator has no case for the operator; this divides. */
+int petb200_div_run(petb200_ctx *ctx, const float *a, size_t size_a, const float *b, size_t size_b, float *out,
+                    size_t out_size, petb200_stream stream);
+/* PowOp with its integer exponent (ref: include/operator.h:1630-1679; src/Graph/operator.cc:3330-3343). */
+int petb200_pow_run(petb200_ctx *ctx, const float *x, float *y, size_t n, int p, petb200_stream stream);
+/* ReduceMeanOp (ref: include/operator.h:1727-1782; shape src/Graph/operator.cc:3454-3458): x [outer, len, inner] -> y [outer, inner]. */
+int petb200_reducemean_run(petb200_ctx *ctx, const float *x, float *y, size_t outer, int len, size_t inner,
+                           petb200_stream stream);
+/* GatherOp (ref: include/operator.h:1681-1725; shape src/Graph/operator.cc:3420-3428; index expression
+ * src/Graph/code_engine.cc:1465-1487): data [outer, len, inner], n_idx int32 indices -> out [n_idx, outer, inner];
+ * an index outside [0, len) yields 0.  Moves 32-bit words untouched. */
+int petb200_gather_run(petb200_ctx *ctx, const void *data, const int *indices, void *out, size_t n_idx, size_t outer, int len,
+                       size_t inner, petb200_stream stream);
+
 /* ---- transposed convolution and banded attention products ------------------------------------------------------ */
 /* ConvTransOp (ref: include/operator.h:466-614; host definition src/Graph/operator.cc:931-983; timing through
  * cudnnConvolutionBackwardData :1113-1287).  Channels-last tensors as the reference defines the operator:

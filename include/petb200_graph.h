@@ -64,6 +64,12 @@ int petb200_graph_activation(petb200_graph *g, int x, int act, int *out);
 int petb200_graph_pool(petb200_graph *g, int kind /*0 max,1 avg*/, int x, int kh, int kw, int ph, int pw, int sh, int sw,
                        int *out);
 int petb200_graph_softmax(petb200_graph *g, int x, int axis, int *out);
+/* ref: Graph::div / pow / reduceMean / gather (src/ffi/ffi_pet.cc:110-125).  `indices` of gather is a tensor whose 32-bit
+ * words are int32 values. */
+int petb200_graph_div(petb200_graph *g, int a, int b, int *out);
+int petb200_graph_pow(petb200_graph *g, int x, int p, int *out);
+int petb200_graph_reducemean(petb200_graph *g, int x, int axis, int *out);
+int petb200_graph_gather(petb200_graph *g, int data, int indices, int axis, int *out);
 int petb200_graph_layernorm(petb200_graph *g, int x, int gamma, int beta, float eps, int *out);
 int petb200_graph_batchnorm(petb200_graph *g, int x, int scale, int bias, int mean, int var, float eps, int *out);
 int petb200_graph_reshape(petb200_graph *g, int x, int nd, const int *dims, int *out); /* alias; -1 infers one dim */

@@ -381,6 +381,36 @@ def gbmml(p, v, dilation=1, wide=True):
     return y
 
 
+def div(a, b):
+    """DivOp as a division with the element-wise operators' modulo broadcast (operand j read at i % size_j,
+    src/Graph/operator.cc:2996-2998).  The reference's own host body subtracts (operator.cc:3258-3259)."""
+    a, b = _f32(a), _f32(b)
+    i = np.arange(a.size)
+    return (a.reshape(-1)[i % a.size] / b.reshape(-1)[i % b.size]).reshape(a.shape)
+
+
+def pow_(x, p):
+    """PowOp::compute: repeated multiplication starting from 1 (powVType, include/common.h:157-162)."""
+    x = _f32(x)
+    r = np.ones_like(x)
+    for _ in range(abs(int(p))):
+        r = r * x
+    return (np.float32(1) / r) if p < 0 else r
+
+
+def reduce_mean(x, axis):
+    """ReduceMeanOp: the axis stays with extent 1 (src/Graph/operator.cc:3454-3458)."""
+    return _f32(x).astype(np.float64).mean(axis, keepdims=True).astype(np.float32)
+
+
+def gather(data, indices, axis):
+    """GatherOp: output dims = indices dims + data dims without the axis (src/Graph/operator.cc:3420-3428; index
+    expression src/Graph/code_engine.cc:1465-1487)."""
+    t = np.take(np.ascontiguousarray(data), np.asarray(indices), axis=axis)
+    k = np.asarray(indices).ndim
+    return np.ascontiguousarray(np.moveaxis(t, list(range(axis, axis + k)), list(range(k))))
+
+
 def rel_err(a, b):
     """The parity metric for floating-point operators: max |a-b| / max(|b|, 1e-3*max|b|)."""
     a = np.asarray(a, np.float64)

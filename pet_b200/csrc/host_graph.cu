@@ -19,7 +19,7 @@ using Dim = std::vector<int>;
 
 // OpType values follow the reference's enum names (ref: include/operator.h:19-51) for the operators that exist there.
 enum OpType { Conv, Matmul, Transpose, Pad, Slice, Concat, Split, Extend, Add, Sub, Mul, Activation, MaxPool, AvgPool,
-              Softmax, BatchNorm, Reshape, Conv3d, LayerNorm, Correction, ConvTrans, G2BMM, GBMML };
+              Softmax, BatchNorm, Reshape, Conv3d, LayerNorm, Correction, ConvTrans, G2BMM, GBMML, Div, Pow, ReduceMean, Gather };
 
 struct Tensor {
     Dim dims;
@@ -202,6 +202,24 @@ int petb200_graph::run_step(Step &s, cudaStream_t st) {
         auto fn = s.type == G2BMM ? petb200_g2bmm_run : petb200_gbmml_run;
         return pass(fn(ctx, dev_of(this, op.inputs[0]), dev_of(this, op.inputs[1]), dev_of(this, op.outputs[0]), b[0], b[1], b[2], op.width,
                        op.dilation, st));
+    }
+    case Div:
+        return pass(petb200_div_run(ctx, dev_of(this, op.inputs[0]), tensors[op.inputs[0]].size(), dev_of(this, op.inputs[1]),
+                                    tensors[op.inputs[1]].size(), dev_of(this, op.outputs[0]), tensors[op.outputs[0]].size(), st));
+    case Pow:
+        return pass(petb200_pow_run(ctx, dev_of(this, op.inputs[0]), dev_of(this, op.outputs[0]), tensors[op.outputs[0]].size(), op.num, st));
+    case ReduceMean:
+    case Gather: {
+        const Dim &d = tensors[op.inputs[0]].dims;
+        size_t outer = 1, inner = 1;
+        for (int i = 0; i < op.axis; ++i)
+            outer *= (size_t)d[i];
+        for (size_t i = op.axis + 1; i < d.size(); ++i)
+            inner *= (size_t)d[i];
+        if (s.type == ReduceMean)
+            return pass(petb200_reducemean_run(ctx, dev_of(this, op.inputs[0]), dev_of(this, op.outputs[0]), outer, d[op.axis], inner, st));
+        return pass(petb200_gather_run(ctx, dev_of(this, op.inputs[0]), reinterpret_cast<const int *>(dev_of(this, op.inputs[1])),
+                                       dev_of(this, op.outputs[0]), tensors[op.inputs[1]].size(), outer, d[op.axis], inner, st));
     }
     case Correction:
         return pass(petb200_conv2d_correct(s.plan, dev_of(this, op.inputs[0]), dev_of(this, op.bias), dev_of(this, op.outputs[0]),
@@ -653,6 +671,18 @@ int petb200_graph::compile(int flags) {
         }
         case G2BMM:
             s.name = "g2bmm";
+            break;
+        case Div:
+            s.name = "div";
+            break;
+        case Pow:
+            s.name = "pow";
+            break;
+        case ReduceMean:
+            s.name = "reduce_mean";
+            break;
+        case Gather:
+            s.name = "gather";
             break;
         case GBMML:
             s.name = "gbmml";
@@ -1246,6 +1276,82 @@ extern "C" int petb200_graph_softmax(petb200_graph *g, int x, int axis, int *out
     op.inputs = {x};
     op.axis = axis;
     *out = g->new_tensor(g->tensors[x].dims);
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+// ref: Graph::div / pow / reduceMean / gather (include/graph.h; src/ffi/ffi_pet.cc:110-125).
+extern "C" int petb200_graph_div(petb200_graph *g, int a, int b, int *out) {
+    if (!g || !out)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, a);
+    G_CHECK_T(g, b);
+    Operator op;
+    op.type = Div;
+    op.inputs = {a, b};
+    // ref: the element-wise operators take the first input's shape; the second is read modulo its size (operator.cc:2983-3002)
+    *out = g->new_tensor(g->tensors[a].dims);
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_pow(petb200_graph *g, int x, int p, int *out) {
+    if (!g || !out)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, x);
+    Operator op;
+    op.type = Pow;
+    op.inputs = {x};
+    op.num = p;
+    *out = g->new_tensor(g->tensors[x].dims);
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_reducemean(petb200_graph *g, int x, int axis, int *out) {
+    if (!g || !out)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, x);
+    Dim d = g->tensors[x].dims;
+    if (axis < 0)
+        axis += (int)d.size();
+    if (axis < 0 || axis >= (int)d.size())
+        return g->fail(PETB200_ERR_INVALID, "reduceMean: axis out of range");
+    Operator op;
+    op.type = ReduceMean;
+    op.inputs = {x};
+    op.axis = axis;
+    d[axis] = 1; // ref: ReduceMeanOp::computeShape, src/Graph/operator.cc:3454-3458
+    *out = g->new_tensor(d);
+    op.outputs = {*out};
+    g->add_op(std::move(op));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_gather(petb200_graph *g, int data, int indices, int axis, int *out) {
+    if (!g || !out)
+        return PETB200_ERR_INVALID;
+    G_CHECK_T(g, data);
+    G_CHECK_T(g, indices);
+    const Dim &a = g->tensors[data].dims;
+    if (axis < 0)
+        axis += (int)a.size();
+    if (axis < 0 || axis >= (int)a.size())
+        return g->fail(PETB200_ERR_INVALID, "gather: axis out of range");
+    Dim d = g->tensors[indices].dims; // ref: GatherOp::computeShape, src/Graph/operator.cc:3420-3428
+    for (int i = 0; i < (int)a.size(); ++i)
+        if (i != axis)
+            d.push_back(a[i]);
+    if (d.size() > 8)
+        return g->fail(PETB200_ERR_UNSUPPORTED, "gather: result has more than 8 dims");
+    Operator op;
+    op.type = Gather;
+    op.inputs = {data, indices};
+    op.axis = axis;
+    *out = g->new_tensor(d);
     op.outputs = {*out};
     g->add_op(std::move(op));
     return PETB200_OK;

@@ -39,6 +39,10 @@ GRAPH_SYMBOLS = {
     "petb200_graph_activation": (_i, [_vp, _i, _i, _ip]),
     "petb200_graph_pool": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _i, _ip]),
     "petb200_graph_softmax": (_i, [_vp, _i, _i, _ip]),
+    "petb200_graph_div": (_i, [_vp, _i, _i, _ip]),
+    "petb200_graph_pow": (_i, [_vp, _i, _i, _ip]),
+    "petb200_graph_reducemean": (_i, [_vp, _i, _i, _ip]),
+    "petb200_graph_gather": (_i, [_vp, _i, _i, _i, _ip]),
     "petb200_graph_layernorm": (_i, [_vp, _i, _i, _i, _fp, _ip]),
     "petb200_graph_batchnorm": (_i, [_vp, _i, _i, _i, _i, _i, _fp, _ip]),
     "petb200_graph_reshape": (_i, [_vp, _i, _i, _ip, _ip]),
@@ -116,8 +120,9 @@ class Graph:
 
     # ---- builders (reference names) ----
     def tensor(self, dims, dtype="FLOAT", weight=False):
-        if dtype not in ("FLOAT", "Float32", "float32"):
-            raise L.PetError(L.ERR_UNSUPPORTED, "only fp32 tensors take part in execution")
+        # ref: Tensor::Float32, and Tensor::Int32 for gather indices only (include/tensor.h:11-14)
+        if dtype not in ("FLOAT", "Float32", "float32", "INT32", "Int32", "int32"):
+            raise L.PetError(L.ERR_UNSUPPORTED, "tensors are fp32, or int32 for gather indices")
         out = C.c_int()
         self._check(self.lib.petb200_graph_tensor(self.h, len(dims), L.ints(dims), int(weight), C.byref(out)))
         return Tensor(self, out.value)
@@ -239,6 +244,35 @@ class Graph:
     def identity(self, input):
         return self.reshape(input, input.dims)
 
+    def div(self, input0, input1):
+        return self._out(self.lib.petb200_graph_div, input0.id, input1.id)
+
+    def pow(self, input, pow):
+        return self._out(self.lib.petb200_graph_pow, input.id, int(pow))
+
+    def reduceMean(self, input, axis):
+        return self._out(self.lib.petb200_graph_reducemean, input.id, axis)
+
+    def gather(self, data, indices, axis):
+        """indices: a tensor whose 32-bit words are int32 values (set_data with an int32 array)."""
+        return self._out(self.lib.petb200_graph_gather, data.id, indices.id, axis)
+
+    def resize(self, input, sizes=None):
+        # ref: ResizeOp has neither a host body nor generated code (src/Graph/operator.cc:3696-3699 asserts)
+        raise L.PetError(L.ERR_UNSUPPORTED, "resize: the reference defines only its shape; nothing to execute")
+
+    def setInputs(self, inputs):
+        """Kept for the reference's call sequence (Graph::setInputs): inputs are the tensors no operator produces."""
+        self._declared_inputs = list(inputs)
+
+    def getOperators(self):
+        """(name, kernel) of every executable step after compile(), the closest counterpart of Graph::getOperators."""
+        return self.steps()
+
+    def updateConnection(self):
+        """Connections are maintained as operators are added; kept for the reference's call sequence."""
+        return True
+
     def correction(self, input, weight, y, ph, pw, sh=1, sw=1, dh=1, dw=1, rows=None, cols=None, bias=None, act="none"):
         """Recompute rows=(first, count) and cols=(first, count) of y — the rewritten sub-graph's output in the original
         layout — from the original conv operands."""
@@ -257,7 +291,10 @@ class Graph:
         return self
 
     def set_data(self, tensor, array, stream=None):
-        a = np.ascontiguousarray(array, dtype=np.float32)
+        if np.issubdtype(np.asarray(array).dtype, np.integer):  # index tensors: the int32 words go in untouched
+            a = np.ascontiguousarray(array, dtype=np.int32).view(np.float32)
+        else:
+            a = np.ascontiguousarray(array, dtype=np.float32)
         self._check(self.lib.petb200_graph_set_data(self.h, tensor.id, a.ctypes.data_as(C.c_void_p), a.size, stream))
         if stream is None:
             import torch

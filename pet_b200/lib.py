@@ -66,6 +66,10 @@ SYMBOLS = {
     "petb200_activation_run": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
     "petb200_batchnorm_run": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _sz, _fp, _vp]),
     "petb200_pool2d_run": (_i, [_vp, _i, _vp, _vp] + [_i] * 10 + [_vp]),
+    "petb200_div_run": (_i, [_vp, _vp, _sz, _vp, _sz, _vp, _sz, _vp]),
+    "petb200_pow_run": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
+    "petb200_reducemean_run": (_i, [_vp, _vp, _vp, _sz, _i, _sz, _vp]),
+    "petb200_gather_run": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _i, _sz, _vp]),
     "petb200_rowmean_run": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
     "petb200_softmax_run": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
     "petb200_layernorm_run": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _i, _fp, _vp]),

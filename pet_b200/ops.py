@@ -7,6 +7,7 @@ Unsupported or invalid operators raise PetError carrying the C-ABI status.
 """
 import ctypes as C
 
+import numpy as np
 import torch
 
 from . import lib as L
@@ -410,6 +411,43 @@ class Context:
 
     def avgpool(self, x, kh, kw, ph, pw, sh, sw):
         return self._pool(1, x, kh, kw, ph, pw, sh, sw)
+
+    def div(self, a, b):
+        a, b = _f32(a), _f32(b)
+        out = torch.empty(a.shape if a.numel() >= b.numel() else b.shape, device=a.device, dtype=torch.float32)
+        self.check(self.lib.petb200_div_run(self.h, _ptr(a), a.numel(), _ptr(b), b.numel(), _ptr(out), out.numel(), _stream()))
+        return out
+
+    def pow(self, x, p):
+        x = _f32(x)
+        y = torch.empty_like(x)
+        self.check(self.lib.petb200_pow_run(self.h, _ptr(x), _ptr(y), x.numel(), int(p), _stream()))
+        return y
+
+    @staticmethod
+    def _around(shape, axis):
+        outer = int(np.prod(shape[:axis], dtype=np.int64))
+        inner = int(np.prod(shape[axis + 1:], dtype=np.int64))
+        return outer, int(shape[axis]), inner
+
+    def reduce_mean(self, x, axis):
+        x = _f32(x)
+        outer, ln, inner = self._around(x.shape, axis)
+        shape = list(x.shape)
+        shape[axis] = 1
+        y = torch.empty(shape, device=x.device, dtype=torch.float32)
+        self.check(self.lib.petb200_reducemean_run(self.h, _ptr(x), _ptr(y), outer, ln, inner, _stream()))
+        return y
+
+    def gather(self, data, indices, axis):
+        """GatherOp: output dims = indices dims + data dims without `axis`."""
+        data = data.contiguous()
+        idx = indices.to(torch.int32).contiguous()
+        outer, ln, inner = self._around(data.shape, axis)
+        shape = list(idx.shape) + [d for i, d in enumerate(data.shape) if i != axis]
+        out = torch.empty(shape, device=data.device, dtype=data.dtype)
+        self.check(self.lib.petb200_gather_run(self.h, _ptr(data), _ptr(idx), _ptr(out), idx.numel(), outer, ln, inner, _stream()))
+        return out
 
     def rowmean(self, x, cols):
         x = _f32(x)

@@ -138,3 +138,67 @@ def test_pool_softmax_layernorm_batchnorm(ctx, oracle):
     va = (np.abs(rng.standard_normal(6)) + 0.5).astype(np.float32)
     assert rel_err(ctx.batchnorm(dev(z), dev(sc), dev(bi), dev(me), dev(va)).cpu().numpy(), oracle.batchnorm(z, sc, bi, me, va)) <= 1e-6
     ctx.sync_check()
+
+
+def test_div_pow_reducemean_gather(ctx):
+    rng = np.random.default_rng(17)
+    a = rng.uniform(1, 2, (3, 5, 7, 6)).astype(np.float32)
+    b = rng.uniform(1, 2, (7, 6)).astype(np.float32)
+    ta, tb = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    # division with the reference's modulo broadcast (operand j read at i % size_j)
+    want = (a.reshape(-1) / b.reshape(-1)[np.arange(a.size) % b.size]).reshape(a.shape)
+    assert np.array_equal(ctx.div(ta, tb).cpu().numpy(), want)
+    # integer power by repeated multiplication, in the order the reference multiplies
+    p3 = ctx.pow(ta, 3).cpu().numpy()
+    assert np.array_equal(p3, (np.float32(1) * a) * a * a)
+    assert np.allclose(ctx.pow(ta, -2).cpu().numpy(), 1.0 / (a * a), rtol=1e-6)
+    assert np.array_equal(ctx.pow(ta, 0).cpu().numpy(), np.ones_like(a))
+    for axis in range(4):
+        y = ctx.reduce_mean(ta, axis).cpu().numpy()
+        assert y.shape == tuple(1 if i == axis else d for i, d in enumerate(a.shape))
+        assert np.allclose(y, a.astype(np.float64).mean(axis, keepdims=True), rtol=1e-6, atol=1e-7)
+    idx = rng.integers(0, 5, (4, 2)).astype(np.int32)
+    words = rng.integers(0, 2**32, a.shape, dtype=np.uint64).astype(np.uint32).view(np.float32)  # arbitrary bit patterns
+    tw = torch.from_numpy(words).cuda()
+    for axis in range(4):
+        ii = rng.integers(0, a.shape[axis], (4, 2)).astype(np.int32)
+        got = ctx.gather(tw, torch.from_numpy(ii).cuda(), axis).cpu().numpy()
+        want = np.moveaxis(np.take(words, ii, axis=axis), [axis, axis + 1], [0, 1])  # index dims first, then the rest
+        assert got.shape == want.shape and np.array_equal(got.view(np.uint32), np.ascontiguousarray(want).view(np.uint32))
+    bad = torch.tensor([[0, 9], [-1, 2]], dtype=torch.int32).cuda()  # outside [0,5): zeros
+    got = ctx.gather(ta, bad, 1).cpu().numpy()
+    assert np.all(got[0, 1] == 0) and np.all(got[1, 0] == 0) and np.array_equal(got[0, 0], a[:, 0]) and np.array_equal(got[1, 1], a[:, 2])
+    ctx.sync_check()
+
+
+def test_small_operators_in_a_graph(ctx):
+    from pet_b200.graph import Graph
+    from pet_b200 import PetError
+    rng = np.random.default_rng(18)
+    g = Graph(ctx)
+    x = g.tensor([4, 6, 8])
+    s_ = g.tensor([8])
+    table = g.tensor([10, 8])
+    ids = g.tensor([4, 6], dtype="INT32")
+    g.setInputs([x, s_, table, ids])
+    y = g.reduceMean(g.pow(g.div(x, s_), 2), 2)        # mean of (x / s)^2 over the last axis
+    e = g.gather(table, ids, 0)                          # embedding lookup [4,6,8]
+    z = g.add([x, e])
+    g.setOutputs([y, z])
+    g.compile()
+    assert g.updateConnection()
+    xs, ss = rng.uniform(1, 2, (4, 6, 8)).astype(np.float32), rng.uniform(1, 2, 8).astype(np.float32)
+    tb, ii = rng.standard_normal((10, 8)).astype(np.float32), rng.integers(0, 10, (4, 6)).astype(np.int32)
+    for t, a in ((x, xs), (s_, ss), (table, tb), (ids, ii)):
+        g.set_data(t, a)
+    g.run()
+    g.run()
+    torch.cuda.synchronize()
+    ctx.sync_check()
+    assert tuple(y.dims) == (4, 6, 1) and tuple(e.dims) == (4, 6, 8)
+    q = xs / ss
+    assert np.allclose(g.get_data(y), (q * q).astype(np.float64).mean(-1, keepdims=True), rtol=1e-6)
+    assert np.array_equal(g.get_data(z), xs + tb[ii])
+    assert sorted(n for n, _ in g.getOperators()) == ["add", "div", "gather", "pow", "reduce_mean"]
+    with pytest.raises(PetError):
+        g.resize(x)
