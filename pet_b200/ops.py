@@ -242,15 +242,23 @@ class Context:
         p.out_shape = (b, m, n)
         return p
 
+    def matmul_set_weights(self, plan, b):
+        """B is a weight: do its preprocessing once (ref: the weight-only operators hoisted by src/Graph/code_engine.cc:187-193);
+        matmul_run then takes b=None."""
+        plan._b = _f32(b)
+        self.check(self.lib.petb200_matmul_set_weights(plan.h, _ptr(plan._b), _stream()))
+
     def matmul_run(self, plan, a, b, bias=None, out=None, residual=None):
         c = out if out is not None else torch.empty(plan.out_shape, device=a.device, dtype=torch.float32)
         if residual is not None:
             if tuple(residual.shape) != tuple(plan.out_shape):
                 raise L.PetError(L.ERR_INVALID, "residual must have the shape of the output")
-            self.check(self.lib.petb200_matmul_run_residual(plan.h, _ptr(_f32(a)), _ptr(_f32(b)), _ptr(bias), _ptr(_f32(residual)),
+            self.check(self.lib.petb200_matmul_run_residual(plan.h, _ptr(_f32(a)), _ptr(_f32(b) if b is not None else None), _ptr(bias),
+                                                            _ptr(_f32(residual)),
                                                             _ptr(c), _stream()))
         else:
-            self.check(self.lib.petb200_matmul_run(plan.h, _ptr(_f32(a)), _ptr(_f32(b)), _ptr(bias), _ptr(c), _stream()))
+            self.check(self.lib.petb200_matmul_run(plan.h, _ptr(_f32(a)), _ptr(_f32(b) if b is not None else None), _ptr(bias), _ptr(c),
+                                                   _stream()))
         return c
 
     def matmul(self, a, b, transA=False, transB=False, bias=None, act="none", algo="auto", residual=None):

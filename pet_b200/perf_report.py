@@ -132,11 +132,17 @@ def main(argv):
             print(f"conv    {name:38s} {plan.kernel:14s} {ms * 1e3:9.1f} us {tf:7.1f} TFLOP/s fp32-equivalent, "
                   f"{3 * tf:7.1f} TF32 issued = {3 * tf / (pk['bf16_tflops'] / 2):.2f} of bf16/2")
     if "matmul" in groups:
+        import torch
         for name, b, m, n, k, ta, tb in MATMUL:
-            plan = ctx.matmul_plan((b, k, m) if ta else (b, m, k), (b, n, k) if tb else (b, k, n), ta, tb)
-            ms = plan.time(50, 10)
-            tf = 2.0 * b * m * n * k / ms / 1e9
-            print(f"matmul  {name:30s} {plan.kernel:14s} {ms * 1e3:9.1f} us {tf:7.1f} TFLOP/s fp32-equivalent")
+            ashape, bshape = ((b, k, m) if ta else (b, m, k)), ((b, n, k) if tb else (b, k, n))
+            plan = ctx.matmul_plan(ashape, bshape, ta, tb)
+            ms = plan.time(50, 10)  # both operands activations: B is split on every launch
+            a, w = torch.rand(ashape, device="cuda") - 0.5, torch.rand(bshape, device="cuda") - 0.5
+            ctx.matmul_set_weights(plan, w)  # B as a weight: split once, outside the replayed part
+            us_w = _graph_time(lambda: ctx.matmul_run(plan, a, None))
+            tf = 2.0 * b * m * n * k / 1e6
+            print(f"matmul  {name:30s} {plan.kernel:14s} {ms * 1e3:9.1f} us {tf / (ms * 1e3):7.1f} TFLOP/s with B an activation; "
+                  f"{us_w:8.1f} us {tf / us_w:7.1f} TFLOP/s with B a pre-split weight (graph replay)")
     if "convtrans" in groups:
         import torch
         for name, xs, ws, (ph, pw, sh, sw, oph, opw) in CONVTRANS:
