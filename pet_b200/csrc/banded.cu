@@ -6,8 +6,8 @@
 //   GBMML  y[b,i,k] = sum_j p[b,i,j] * v[b, i + d*(j-w), k]       p [b,n,2w+1], y [b,n,m]
 // Both kernels work on one dilation residue class at a time: rows i = rho + d*R only meet keys rho + d*(R + j - w), so
 // inside a class the problem has dilation 1 and a tile of TI rows x TJ band columns touches TI+TJ-1 consecutive keys.
-// Exact fp32 on the CUDA cores (fmaf), any shape.  At the reference's shape G2BMM is bound by writing y and GBMML by
-// reading p (both 80 MB against 2.6 GFLOP).
+// Exact fp32 on the CUDA cores (fmaf), any shape.  At the reference's shape the band tensor is 80 MB against 2.6 GFLOP:
+// 32 flops per byte, which puts both kernels on the compute side of the CUDA cores' roofline (the FMA pipe, not HBM).
 #include "common.h"
 #include <algorithm>
 
