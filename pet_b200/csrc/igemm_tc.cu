@@ -8,18 +8,21 @@
 //   warp 2   : TMA producer for the RAW activation tile of one channel chunk (all taps share it): a 5-D box
 //              [images, channels, depth, rows, cols] of the NC(D)HW input, zero-filled outside the tensor, which
 //              is exactly the convolution's zero padding.  Box start along W is rounded down to 16 bytes.
-//   warps 3-6: transform.  Thread p owns pixel p of the tile: for every K stage it gathers its 32 values from the
+//   warps 3-6, 7-10: two transform sets taking alternate K stages.  Thread p owns pixel p of the tile: for every K stage it gathers its 32 values from the
 //              raw tile through a precomputed offset table (tap shift, dilation, channel plane), splits each fp32
 //              into hi (top 19 bits) and lo = x - hi, and writes the two K-major operand tiles — into swizzled
 //              shared memory (SS variant) or directly into TMEM with tcgen05.st (TS variant, which leaves the
 //              shared-memory read port to B alone).  The same warps run the epilogue.
-//   warp 1   : one thread issues, per K=8 step, three MMAs  lo*hi + hi*lo + hi*hi  (3xTF32) and commits stage
+//   warp 1   : issues, per K=8 step, the three products of 3xTF32 as two MMAs — A_hi x [B_hi;B_lo] (one MMA of width
+//              2*BN: the hi*hi sum and the hi*lo sum in adjacent accumulators) and A_lo x B_hi — and commits the stage
 //              release barriers.
 // Epilogue: tcgen05.ld -> +bias -> activation -> global stores, coalesced across the 32 pixels of a warp (conv)
 // or 128-bit per thread (row-major matmul output).
 //
+// Split-K: the ksplit CTAs of one output tile form a thread-block cluster and exchange their partial sums through
+// distributed shared memory (pushes into the owner's landing area, one cluster barrier, reduction in rank order).
 // Every wait on an mbarrier is bounded (~2 s) and reports through a status word instead of hanging the GPU.
-// No cluster launch, no multicast.
+// TMA loads are per CTA (no cluster-wide loads of any kind).
 #include "common.h"
 #include "tc_ptx.cuh"
 #include <algorithm>
