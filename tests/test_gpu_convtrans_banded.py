@@ -211,3 +211,41 @@ def test_banded_reference_shape_properties(ctx):
         assert float(o[0, n - shift:].abs().max()) == 0.0
     assert 0 < ctx.banded_time("g2bmm", 1, n, m, w, 1, rounds=5, warmup=2) < 50.0
     assert 0 < ctx.banded_time("gbmml", 1, n, m, w, 1, rounds=5, warmup=2) < 50.0
+
+
+def test_convtrans_random_shapes_exact(ctx, oracle, monkeypatch):
+    """Seeded sweep over small ragged shapes, strides up to 3, padding up to the filter extent, output padding: both the
+    zero-insertion and the phase path reproduce the oracle exactly on small integers."""
+    rng = np.random.default_rng(123)
+    ran = 0
+    for _ in range(60):
+        n, h, w = int(rng.integers(1, 4)), int(rng.integers(1, 12)), int(rng.integers(1, 12))
+        f, c = int(rng.choice([1, 3, 8, 16, 33])), int(rng.choice([1, 4, 7, 16, 40]))
+        r, s, sh, sw = int(rng.integers(1, 6)), int(rng.integers(1, 6)), int(rng.integers(1, 4)), int(rng.integers(1, 4))
+        ph, pw, oph, opw = int(rng.integers(0, r + 1)), int(rng.integers(0, s + 1)), int(rng.integers(0, sh)), int(rng.integers(0, sw))
+        if (h - 1) * sh - 2 * ph + r + oph <= 0 or (w - 1) * sw - 2 * pw + s + opw <= 0:
+            continue
+        x = rng.integers(0, 8, (n, h, w, f)).astype(np.float32)
+        wt = rng.integers(0, 8, (r, s, f, c)).astype(np.float32)
+        want = oracle.convtrans(x, wt, (ph, pw), (sh, sw), (1, 1), (oph, opw), wide=False)
+        for phases in ("0", "1"):
+            monkeypatch.setenv("PETB200_CONVTRANS_PHASES", phases)
+            plan = ctx.convtrans_plan(x.shape, wt.shape, ph, pw, sh, sw, 1, 1, oph, opw)
+            y = ctx.convtrans_run(plan, dev(x), dev(wt)).cpu().numpy()
+            assert np.array_equal(y, want), (phases, n, h, w, f, r, s, c, ph, pw, sh, sw, oph, opw)
+            ran += 1
+    ctx.sync_check()
+    assert ran >= 80
+
+
+def test_banded_random_shapes_exact(ctx, oracle):
+    rng = np.random.default_rng(7)
+    for _ in range(40):
+        b, n, m = int(rng.integers(1, 4)), int(rng.integers(1, 400)), int(rng.choice([1, 3, 8, 20, 64, 100]))
+        w, d = int(rng.integers(0, 130)), int(rng.integers(1, 6))
+        q = rng.integers(0, 4, (b, n, m)).astype(np.float32)
+        k = rng.integers(0, 4, (b, n, m)).astype(np.float32)
+        p = rng.integers(0, 4, (b, n, 2 * w + 1)).astype(np.float32)
+        assert np.array_equal(ctx.g2bmm(dev(q), dev(k), w, d).cpu().numpy(), oracle.g2bmm(q, k, w, d, wide=False)), (b, n, m, w, d)
+        assert np.array_equal(ctx.gbmml(dev(p), dev(k), d).cpu().numpy(), oracle.gbmml(p, k, d, wide=False)), (b, n, m, w, d)
+    ctx.sync_check()

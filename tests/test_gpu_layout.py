@@ -166,3 +166,28 @@ def test_transposes_match_the_reference_tests_reshape_definitions(ctx):
     for name, x, (split, after, factor), want in gc.reshape_transpose_definitions():
         got = host(ctx.transpose(dev(x), split, after, factor))
         assert got.shape == want.shape and np.array_equal(got, want), name
+
+
+def test_halo_transpose_random_shapes(ctx, oracle):
+    """Seeded sweep: the four parameters on H and on W, amounts 1-3, ragged extents, two or three merged blocks."""
+    rng = np.random.default_rng(7)
+    for _ in range(60):
+        mode, amt = str(rng.choice(["copys", "dels", "pad", "extr"])), int(rng.integers(1, 4))
+        n_, c_, on_h = int(rng.integers(1, 4)), int(rng.integers(1, 5)), bool(rng.integers(0, 2))
+        half, other, blocks = int(rng.integers(amt + 1, 20)), int(rng.integers(1, 40)), int(rng.integers(2, 4))
+        split_hw = (2, [[0, 2], 1, -1, 3]) if on_h else (3, [[0, 3], 1, 2, -1])
+        merge_hw = (0, [0, 1, [-1, 2], 3]) if on_h else (0, [0, 1, 2, [-1, 3]])
+        place = (lambda e: (e, other)) if on_h else (lambda e: (other, e))
+        if mode == "copys":
+            shape, args = (n_, c_) + place(2 * half), split_hw + (-2,)
+        elif mode == "dels":
+            shape, args = (2 * n_, c_) + place(half), merge_hw + (2,)
+        elif mode == "pad":
+            shape, args = (blocks * n_, c_) + place(half), merge_hw + (blocks,)
+        else:
+            shape, args = (n_, c_) + place(blocks * (half + amt) - amt), split_hw + (half,)
+        x = gc.words(shape, 900 + amt)
+        want = oracle.transpose_halo(x, *args, mode, amt)
+        got = host(ctx.transpose_halo(dev(x), *args, mode, amt))
+        assert got.shape == want.shape and np.array_equal(got, want), (mode, amt, shape)
+    ctx.sync_check()
