@@ -268,3 +268,27 @@ def test_single_pass_tf32_option(ctx, oracle):
     b = (rng.standard_normal((1, 768, 256)) / 27.7).astype(np.float32)
     got = ctx.matmul(dev(a), dev(b), algo="tc_1xtf32").cpu().numpy()
     assert rel_err(got, oracle.matmul(a, b)) <= 5e-3
+
+
+def test_conv_random_shapes_exact(ctx, oracle):
+    """Seeded sweep over ragged shapes (groups, strides, dilations, paddings, odd widths, 1..64 channels per group): on
+    small integers both the tensor-core and the CUDA-core kernels reproduce the oracle exactly."""
+    rng = np.random.default_rng(2024)
+    ran = 0
+    for _ in range(90):
+        g, cpg, fpg = int(rng.choice([1, 1, 1, 2, 4])), int(rng.choice([1, 3, 8, 16, 32, 40, 64])), int(rng.choice([1, 5, 8, 32, 48]))
+        n, h, w = int(rng.integers(1, 4)), int(rng.integers(1, 30)), int(rng.integers(1, 30))
+        r, s, sh, sw = int(rng.integers(1, 6)), int(rng.integers(1, 6)), int(rng.integers(1, 3)), int(rng.integers(1, 3))
+        dh, dw, ph, pw = int(rng.integers(1, 3)), int(rng.integers(1, 3)), int(rng.integers(0, 4)), int(rng.integers(0, 4))
+        oh, ow = (h - (r - sh) * dh + 2 * ph) // sh, (w - (s - sw) * dw + 2 * pw) // sw
+        if oh <= 0 or ow <= 0 or (r - 1) * dh + 1 > h + 2 * ph or (s - 1) * dw + 1 > w + 2 * pw:
+            continue
+        x = rng.integers(0, 4, (n, g * cpg, h, w)).astype(np.float32)
+        wt = rng.integers(0, 4, (g * fpg, cpg, r, s)).astype(np.float32)
+        want = oracle.conv2d(x, wt, None, pad=(ph, pw), stride=(sh, sw), dil=(dh, dw), wide=False)
+        for algo in ("tc_3xtf32", "simt_fp32"):
+            y = ctx.conv2d(dev(x), dev(wt), ph, pw, sh, sw, dh, dw, algo=algo).cpu().numpy()
+            assert y.shape == want.shape and np.array_equal(y, want), (algo, x.shape, wt.shape, ph, pw, sh, sw, dh, dw)
+            ran += 1
+    ctx.sync_check()
+    assert ran >= 100

@@ -202,3 +202,17 @@ def test_small_operators_in_a_graph(ctx):
     assert sorted(n for n, _ in g.getOperators()) == ["add", "div", "gather", "pow", "reduce_mean"]
     with pytest.raises(PetError):
         g.resize(x)
+
+
+def test_matmul_random_shapes_exact(ctx, oracle):
+    rng = np.random.default_rng(2025)
+    for _ in range(50):
+        b, m, n, k = int(rng.integers(1, 5)), int(rng.integers(1, 200)), int(rng.integers(1, 200)), int(rng.integers(1, 200))
+        ta, tb = bool(rng.integers(0, 2)), bool(rng.integers(0, 2))
+        a = rng.integers(0, 4, (b, k, m) if ta else (b, m, k)).astype(np.float32)
+        bm = rng.integers(0, 4, (b, n, k) if tb else (b, k, n)).astype(np.float32)
+        want = oracle.matmul(a, bm, None, ta, tb, wide=False)
+        for algo in ("tc_3xtf32", "simt_fp32", "auto"):
+            y = ctx.matmul(torch.from_numpy(a).cuda(), torch.from_numpy(bm).cuda(), ta, tb, algo=algo).cpu().numpy()
+            assert np.array_equal(y, want), (algo, b, m, n, k, ta, tb)
+    ctx.sync_check()
