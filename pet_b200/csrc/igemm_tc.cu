@@ -1157,7 +1157,7 @@ static int raise_smem_limit(petb200_ctx *ctx) {
 
 static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int oh0, int ohn, int ow0, int own,
                         int z_is_batch, int images, long long ys_n, long long ys_f, long long ys_p, int has_bias, int act,
-                        int force_bc = 0, int force_ksplit = 0, int force_bn = 0, int flat = 0) {
+                        int force_bc = 0, int force_ksplit = 0, int force_bn = 0, int flat = 0, int max_ipt = 0) {
     IgemmParams &P = core.P;
     const int cpg = g.C / g.groups, Fg = g.F / g.groups;
     if (!flat && g.Wst % 4 != 0)
@@ -1204,6 +1204,8 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
                 }
         }
     }
+    if (max_ipt > 0) // a caller that must keep another plan's chunk size may not afford several images per raw tile
+        P.ipt = std::min(P.ipt, max_ipt);
     P.tpi = (P.Pw + kTileM - 1) / kTileM;
     P.wide = (own > kTileM) ? 1 : 0;
     P.row_tiles = (own + kTileM - 1) / kTileM;
@@ -1556,6 +1558,13 @@ int tc_conv_run(void *h, const float *x, const float *bias, const float *res, fl
         // two would round differently; the raw box only shrinks for a window, so the full plan's BC always fits.
         int rc = tc_configure(wc->ctx, *wc, g, win[0], win[1], win[2], win[3], 0, g.N, t->ys[0], t->ys[1], t->ys[2],
                               t->has_bias, t->act, t->full.P.BC, t->full.P.ksplit, t->full.P.BN, t->full.P.flat);
+        if (rc == PETB200_ERR_UNSUPPORTED) {
+            // A small window packs several images into one tile, and with the full plan's chunk size forced the raw tile
+            // of that many images may not fit: one image per tile always does (it is the full plan's raw tile or less).
+            memset(&wc->P, 0, sizeof wc->P);
+            rc = tc_configure(wc->ctx, *wc, g, win[0], win[1], win[2], win[3], 0, g.N, t->ys[0], t->ys[1], t->ys[2], t->has_bias,
+                              t->act, t->full.P.BC, t->full.P.ksplit, t->full.P.BN, t->full.P.flat, std::max(1, t->full.P.ipt));
+        }
         if (rc == PETB200_OK && (wc->P.BN != t->full.P.BN || wc->P.BC != t->full.P.BC || wc->Ktot != t->full.Ktot || wc->P.ksplit != t->full.P.ksplit))
             rc = fail(wc->ctx, PETB200_ERR_UNSUPPORTED, "window plan diverged from the full plan");
         if (rc) {

@@ -292,3 +292,51 @@ def test_conv_random_shapes_exact(ctx, oracle):
             ran += 1
     ctx.sync_check()
     assert ran >= 100
+
+
+def test_conv3d_random_shapes_exact(ctx, oracle):
+    rng = np.random.default_rng(77)
+    ran = 0
+    for _ in range(40):
+        g, cpg, fpg = int(rng.choice([1, 1, 2])), int(rng.choice([1, 3, 8, 16, 32])), int(rng.choice([1, 5, 8, 32]))
+        n, dims = int(rng.integers(1, 3)), [int(rng.integers(1, 8)), int(rng.integers(1, 14)), int(rng.integers(1, 14))]
+        k, st = [int(rng.integers(1, 4)) for _ in range(3)], [int(rng.integers(1, 3)) for _ in range(3)]
+        dl, pd = [int(rng.integers(1, 3)) for _ in range(3)], [int(rng.integers(0, 3)) for _ in range(3)]
+        o = [(dims[i] - (k[i] - st[i]) * dl[i] + 2 * pd[i]) // st[i] for i in range(3)]
+        if min(o) <= 0 or any((k[i] - 1) * dl[i] + 1 > dims[i] + 2 * pd[i] for i in range(3)):
+            continue
+        x = rng.integers(0, 4, (n, g * cpg, *dims)).astype(np.float32)
+        wt = rng.integers(0, 4, (g * fpg, cpg, *k)).astype(np.float32)
+        want = oracle.conv3d(x, wt, None, pad=tuple(pd), stride=tuple(st), dil=tuple(dl), wide=False)
+        for algo in ("tc_3xtf32", "simt_fp32"):
+            y = ctx.conv3d(dev(x), dev(wt), pd, st, dl, algo=algo).cpu().numpy()
+            assert y.shape == want.shape and np.array_equal(y, want), (algo, x.shape, wt.shape, pd, st, dl)
+            ran += 1
+    ctx.sync_check()
+    assert ran >= 40
+
+
+def test_correction_windows_random_bit_identical(ctx):
+    """Seeded sweep of correction windows (any rows x columns, batches of 1-3 images, odd widths, 1x1 to dilated 5x5 filters):
+    the window equals the same region of the full convolution bit for bit and nothing outside it is written.  Small
+    windows of multi-image batches used to fail to plan (several images per tile with the full plan's chunk size)."""
+    rng = np.random.default_rng(78)
+    for _ in range(40):
+        cpg, f, n = int(rng.choice([3, 16, 32, 64])), int(rng.choice([8, 32, 48, 128])), int(rng.integers(1, 4))
+        h, w, r, dh = int(rng.integers(4, 40)), int(rng.integers(4, 40)), int(rng.choice([1, 3, 5])), int(rng.integers(1, 3))
+        ph = (r - 1) * dh // 2
+        x = dev(rng.uniform(-1, 1, (n, cpg, h, w)).astype(np.float32))
+        wt = dev(rng.uniform(-1, 1, (f, cpg, r, r)).astype(np.float32))
+        plan = ctx.conv2d_plan(x.shape, wt.shape, ph, ph, 1, 1, dh, dh)
+        ctx.conv2d_set_weights(plan, wt)
+        y0 = ctx.conv2d_run(plan, x)
+        oh, ow = y0.shape[2], y0.shape[3]
+        r0, c0 = int(rng.integers(0, oh)), int(rng.integers(0, ow))
+        rn, cn = int(rng.integers(1, oh - r0 + 1)), int(rng.integers(1, ow - c0 + 1))
+        y1 = torch.full_like(y0, 7.0)
+        ctx.conv2d_correct(plan, x, y1, r0, rn, c0, cn)
+        ctx.sync_check()
+        case = (tuple(x.shape), tuple(wt.shape), dh, r0, rn, c0, cn)
+        assert torch.equal(y1[:, :, r0:r0 + rn, c0:c0 + cn], y0[:, :, r0:r0 + rn, c0:c0 + cn]), case
+        y1[:, :, r0:r0 + rn, c0:c0 + cn] = 7.0
+        assert bool((y1 == 7.0).all()), case
