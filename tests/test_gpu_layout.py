@@ -191,3 +191,44 @@ def test_halo_transpose_random_shapes(ctx, oracle):
         got = host(ctx.transpose_halo(dev(x), *args, mode, amt))
         assert got.shape == want.shape and np.array_equal(got, want), (mode, amt, shape)
     ctx.sync_check()
+
+
+def _random_transpose(rng, shape):
+    """A random valid TransposeOp on `shape`: optional split by a divisor (either sign convention), a random permutation
+    of the resulting dims, one merged group of up to three neighbours."""
+    nd = len(shape)
+    split, factor = int(rng.integers(-1, nd)), 2
+    if split >= 0:
+        f = int(rng.choice([d for d in range(1, shape[split] + 1) if shape[split] % d == 0]))
+        factor = f if rng.integers(0, 2) else -f
+    items = list(range(nd)) + ([-1] if split >= 0 else [])
+    perm = [items[i] for i in rng.permutation(len(items))]
+    gsz = int(rng.integers(1, min(3, len(perm)) + 1))
+    gpos = int(rng.integers(0, len(perm) - gsz + 1))
+    after = perm[:gpos] + ([perm[gpos:gpos + gsz]] if gsz > 1 else perm[gpos:gpos + 1]) + perm[gpos + gsz:]
+    return split, after, factor
+
+
+def test_random_transposes_and_fused_pairs_bit_exact(ctx, oracle):
+    from pet_b200 import PetError
+    rng = np.random.default_rng(99)
+    singles = pairs = 0
+    for _ in range(120):
+        shape = tuple(int(rng.choice([1, 2, 3, 4, 6, 8, 12, 16, 33])) for _ in range(int(rng.integers(2, 6))))
+        x = gc.words(shape, 1234)
+        t1 = _random_transpose(rng, shape)
+        want = oracle.transpose(x, *t1)
+        got = host(ctx.transpose(dev(x), *t1))
+        assert got.shape == want.shape and np.array_equal(got, want), (shape, t1)
+        singles += 1
+        t2 = _random_transpose(rng, want.shape)
+        want2 = oracle.transpose(want, *t2)
+        try:
+            got2 = host(ctx.transpose_chain(dev(x), [t1, t2]))
+        except PetError as e:  # a pair that is not one index map stays two steps in the graph layer
+            assert "not expressible" in str(e), (shape, t1, t2, str(e))
+            continue
+        assert got2.shape == want2.shape and np.array_equal(got2, want2), (shape, t1, t2)
+        pairs += 1
+    ctx.sync_check()
+    assert singles == 120 and pairs >= 60
