@@ -340,3 +340,26 @@ def test_correction_windows_random_bit_identical(ctx):
         assert torch.equal(y1[:, :, r0:r0 + rn, c0:c0 + cn], y0[:, :, r0:r0 + rn, c0:c0 + cn]), case
         y1[:, :, r0:r0 + rn, c0:c0 + cn] = 7.0
         assert bool((y1 == 7.0).all()), case
+
+
+def test_conv_epilogue_combinations_exact(ctx, oracle):
+    """Seeded sweep over bias / ReLU / folded residual on shapes that reach every tiling regime (deep K with few tiles:
+    split-K through the cluster; many tiles; stride 2): exact on small integers for both kernel families."""
+    rng = np.random.default_rng(5)
+    for _ in range(40):
+        c, f, n = int(rng.choice([16, 64, 128, 256, 512])), int(rng.choice([8, 32, 64, 100, 256])), int(rng.integers(1, 3))
+        hw, r, st = int(rng.choice([4, 7, 8, 14, 28])), int(rng.choice([1, 3])), int(rng.choice([1, 2]))
+        p = r // 2
+        x = rng.integers(-2, 3, (n, c, hw, hw)).astype(np.float32)
+        wt = rng.integers(-2, 3, (f, c, r, r)).astype(np.float32)
+        b = rng.integers(-3, 4, f).astype(np.float32)
+        act, use_b, use_res = str(rng.choice(["none", "relu"])), bool(rng.integers(0, 2)), bool(rng.integers(0, 2))
+        want = oracle.conv2d(x, wt, b if use_b else None, pad=(p, p), stride=(st, st), wide=False)
+        res = rng.integers(-3, 4, want.shape).astype(np.float32)
+        want = want + res if use_res else want
+        want = np.maximum(want, 0) if act == "relu" else want
+        for algo in ("tc_3xtf32", "simt_fp32"):
+            y = ctx.conv2d(dev(x), dev(wt), p, p, st, st, 1, 1, bias=dev(b) if use_b else None, act=act, algo=algo,
+                           residual=dev(res) if use_res else None).cpu().numpy()
+            assert np.array_equal(y, want), (algo, x.shape, wt.shape, st, act, use_b, use_res)
+    ctx.sync_check()

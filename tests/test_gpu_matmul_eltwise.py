@@ -216,3 +216,24 @@ def test_matmul_random_shapes_exact(ctx, oracle):
             y = ctx.matmul(torch.from_numpy(a).cuda(), torch.from_numpy(bm).cuda(), ta, tb, algo=algo).cpu().numpy()
             assert np.array_equal(y, want), (algo, b, m, n, k, ta, tb)
     ctx.sync_check()
+
+
+def test_matmul_epilogue_combinations_exact(ctx, oracle):
+    rng = np.random.default_rng(6)
+    for _ in range(40):
+        bs, m = int(rng.choice([1, 1, 2, 12])), int(rng.choice([1, 4, 16, 128, 200]))
+        n, k = int(rng.choice([8, 64, 100, 768, 1000])), int(rng.choice([8, 64, 512, 768, 3072]))
+        ta, tb = bool(rng.integers(0, 2)), bool(rng.integers(0, 2))
+        a = rng.integers(-2, 3, (bs, k, m) if ta else (bs, m, k)).astype(np.float32)
+        bm = rng.integers(-2, 3, (bs, n, k) if tb else (bs, k, n)).astype(np.float32)
+        b = rng.integers(-3, 4, n).astype(np.float32)
+        act, use_b, use_res = str(rng.choice(["none", "relu"])), bool(rng.integers(0, 2)), bool(rng.integers(0, 2))
+        want = oracle.matmul(a, bm, b if use_b else None, ta, tb, wide=False)
+        res = rng.integers(-3, 4, want.shape).astype(np.float32)
+        want = want + res if use_res else want
+        want = np.maximum(want, 0) if act == "relu" else want
+        for algo in ("auto", "tc_3xtf32", "simt_fp32"):
+            y = ctx.matmul(torch.from_numpy(a).cuda(), torch.from_numpy(bm).cuda(), ta, tb, bias=torch.from_numpy(b).cuda() if use_b else None,
+                           act=act, algo=algo, residual=torch.from_numpy(res).cuda() if use_res else None).cpu().numpy()
+            assert np.array_equal(y, want), (algo, bs, m, n, k, ta, tb, act, use_b, use_res)
+    ctx.sync_check()
