@@ -242,3 +242,45 @@ def test_graph_rejects_invalid_operators(ctx):
         g.gbmml(g.tensor([1, 8, 4]), g.tensor([1, 8, 4]))          # band extent must be odd
     with pytest.raises(PetError):
         g.run()                                          # not compiled
+
+
+def test_random_residual_block_graphs_fused_equals_unfused(ctx):
+    """Seeded sweep of small residual networks (1-3 basic blocks, identity or 1x1 strided shortcuts, Add operands in either
+    order, optional final ReLU): the compiled graph with every rewrite on (activation and residual folding, shortcut on a
+    side stream, CUDA-graph capture) gives the same bits as the operator-by-operator execution."""
+    from pet_b200.graph import Graph
+    rng = np.random.default_rng(11)
+    for it in range(20):
+        n, c, f = int(rng.integers(1, 3)), int(rng.choice([8, 16, 64])), int(rng.choice([8, 16, 64, 128]))
+        hw, st, nblocks = int(rng.choice([7, 8, 14, 28])), int(rng.choice([1, 2])), int(rng.integers(1, 4))
+        outs = []
+        for fuse in (True, False):
+            g = Graph(ctx)
+            r2 = np.random.default_rng(1000 + it)
+            x = g.tensor([n, c, hw, hw])
+            data = {x: r2.integers(-2, 3, (n, c, hw, hw)).astype(np.float32)}
+
+            def weight(shape):
+                t = g.tensor(list(shape), weight=True)
+                data[t] = r2.integers(-1, 2, shape).astype(np.float32)
+                return t
+
+            t, cin = x, c
+            for b in range(nblocks):
+                cout, s_ = (f, st) if b == 0 else (cin, 1)
+                y = g.conv(g.relu(g.conv(t, weight((cout, cin, 3, 3)), 1, 1, s_, s_)), weight((cout, cout, 3, 3)), 1, 1)
+                sc = g.conv(t, weight((cout, cin, 1, 1)), 0, 0, s_, s_) if (cout != cin or s_ != 1) else t
+                y = g.add([y, sc]) if r2.integers(0, 2) else g.add([sc, y])
+                t = g.relu(y) if r2.integers(0, 4) else y
+                cin = cout
+            g.setOutputs([t])
+            g.compile(fuse=fuse, cuda_graph=fuse)
+            for k_, v in data.items():
+                g.set_data(k_, v)
+            g.run()
+            g.run()
+            torch.cuda.synchronize()
+            ctx.sync_check()
+            outs.append((g.get_data(t), [nm for nm, _ in g.steps()]))
+        assert np.array_equal(outs[0][0], outs[1][0]), (it, n, c, f, hw, st, nblocks, outs[0][1])
+        assert len(outs[0][1]) < len(outs[1][1])
