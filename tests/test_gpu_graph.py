@@ -284,3 +284,18 @@ def test_random_residual_block_graphs_fused_equals_unfused(ctx):
             outs.append((g.get_data(t), [nm for nm, _ in g.steps()]))
         assert np.array_equal(outs[0][0], outs[1][0]), (it, n, c, f, hw, st, nblocks, outs[0][1])
         assert len(outs[0][1]) < len(outs[1][1])
+
+
+def test_random_encoder_graphs_fused_vs_unfused_vs_oracle(ctx):
+    """Seeded sweep of small transformer encoders (1-6 heads, head sizes 8-64, ragged sequence lengths): transposes folded
+    into matmul strides and merged Q/K/V projections agree with the operator-by-operator graph and with the oracle."""
+    from pet_b200 import configs
+    rng = np.random.default_rng(3)
+    for _ in range(8):
+        heads, hd = int(rng.choice([1, 2, 4, 6])), int(rng.choice([8, 16, 32, 64]))
+        kw = dict(layers=int(rng.integers(1, 3)), seq=int(rng.choice([8, 20, 32, 77, 128])), hidden=heads * hd, heads=heads,
+                  ffn=int(rng.choice([32, 96, 256])))
+        _, _, y = run_config(ctx, configs.bert_encoder, **kw)
+        _, _, y2 = run_config(ctx, configs.bert_encoder, fuse=False, cuda_graph=False, **kw)
+        assert rel_err(y, y2) <= 1e-5, kw
+        assert rel_err(y, oracle_config(configs.bert_encoder, **kw)) <= TOL, kw
