@@ -237,3 +237,39 @@ def test_matmul_epilogue_combinations_exact(ctx, oracle):
                            act=act, algo=algo, residual=torch.from_numpy(res).cuda() if use_res else None).cpu().numpy()
             assert np.array_equal(y, want), (algo, bs, m, n, k, ta, tb, act, use_b, use_res)
     ctx.sync_check()
+
+
+def test_pool_softmax_layernorm_eltwise_random_shapes(ctx, oracle):
+    """Seeded sweep: pooling windows / strides / paddings on ragged planes (max exact, average to rounding), global
+    windows, softmax and LayerNorm rows of 1..3000 columns, element-wise operators with the modulo broadcast."""
+    rng = np.random.default_rng(41)
+    T = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    for _ in range(50):
+        n, c, h, w = int(rng.integers(1, 4)), int(rng.integers(1, 9)), int(rng.integers(1, 40)), int(rng.integers(1, 40))
+        kh, kw = int(rng.integers(1, min(h, 8) + 1)), int(rng.integers(1, min(w, 8) + 1))
+        sh, sw = int(rng.integers(1, 4)), int(rng.integers(1, 4))
+        ph, pw = int(rng.integers(0, kh // 2 + 1)), int(rng.integers(0, kw // 2 + 1))
+        if (h - (kh - sh) + 2 * ph) // sh <= 0 or (w - (kw - sw) + 2 * pw) // sw <= 0:
+            continue
+        x = rng.integers(-50, 50, (n, c, h, w)).astype(np.float32)
+        case = (x.shape, kh, kw, ph, pw, sh, sw)
+        assert np.array_equal(ctx.maxpool(T(x), kh, kw, 1, 1, ph, pw, sh, sw).cpu().numpy(), oracle.maxpool(x, (kh, kw), (ph, pw), (sh, sw))), case
+        assert np.allclose(ctx.avgpool(T(x), kh, kw, ph, pw, sh, sw).cpu().numpy(), oracle.avgpool(x, (kh, kw), (ph, pw), (sh, sw)),
+                           rtol=1e-6, atol=1e-5), case
+    for _ in range(6):
+        hw = int(rng.integers(6, 30))
+        x = rng.standard_normal((2, 5, hw, hw)).astype(np.float32)
+        assert np.allclose(ctx.avgpool(T(x), hw, hw, 0, 0, 1, 1).cpu().numpy()[:, :, 0, 0], x.astype(np.float64).mean((2, 3)), rtol=1e-5, atol=1e-6)
+    for _ in range(40):
+        rows, cols = int(rng.integers(1, 300)), int(rng.choice([1, 2, 7, 32, 64, 100, 128, 257, 768, 1000, 3000]))
+        x = (rng.standard_normal((rows, cols)) * 3).astype(np.float32)
+        g_, b_ = rng.standard_normal(cols).astype(np.float32), rng.standard_normal(cols).astype(np.float32)
+        assert np.allclose(ctx.softmax(T(x)).cpu().numpy(), oracle.softmax(x), rtol=2e-5, atol=1e-7), (rows, cols)
+        assert np.allclose(ctx.layernorm(T(x), T(g_), T(b_)).cpu().numpy(), oracle.layernorm(x, g_, b_), rtol=1e-4, atol=1e-4), (rows, cols)
+    for _ in range(40):
+        shape = tuple(int(rng.integers(1, 12)) for _ in range(int(rng.integers(1, 5))))
+        a = rng.integers(-9, 10, shape).astype(np.float32)
+        b = rng.integers(-9, 10, shape[int(rng.integers(0, len(shape))):]).astype(np.float32)
+        for kind in ("add", "sub", "mul"):
+            assert np.array_equal(ctx.eltwise(kind, [T(a), T(b)]).cpu().numpy(), oracle.eltwise(kind, [a, b])), (kind, shape, b.shape)
+    ctx.sync_check()
