@@ -273,3 +273,37 @@ def test_pool_softmax_layernorm_eltwise_random_shapes(ctx, oracle):
         for kind in ("add", "sub", "mul"):
             assert np.array_equal(ctx.eltwise(kind, [T(a), T(b)]).cpu().numpy(), oracle.eltwise(kind, [a, b])), (kind, shape, b.shape)
     ctx.sync_check()
+
+
+def test_strided_matmul_random_views_exact(ctx):
+    """Seeded sweep of operands and results that are strided views of larger buffers (row pitches and batch strides with
+    gaps, B stored either way): exact on small integers, and nothing outside the result view is written."""
+    rng = np.random.default_rng(61)
+    as_view = np.lib.stride_tricks.as_strided
+    for _ in range(40):
+        bs, m, n = int(rng.integers(1, 5)), int(rng.integers(1, 150)), int(rng.integers(1, 150))
+        k, tb = int(rng.choice([4, 8, 32, 64, 100, 128])), bool(rng.integers(0, 2))
+        a_row = k + 4 * int(rng.integers(0, 4))
+        a_batch = m * a_row + 4 * int(rng.integers(0, 5))
+        brows, blen = (n, k) if tb else (k, n)
+        b_row = blen + int(rng.integers(0, 5))
+        b_batch = brows * b_row + int(rng.integers(0, 7))
+        c_row = n + int(rng.integers(0, 5))
+        c_batch = m * c_row + int(rng.integers(0, 9))
+        A = rng.integers(-2, 3, bs * a_batch + 8).astype(np.float32)
+        B = rng.integers(-2, 3, bs * b_batch + 8).astype(np.float32)
+        av = as_view(A, (bs, m, k), (4 * a_batch, 4 * a_row, 4))
+        bv = as_view(B, (bs, brows, blen), (4 * b_batch, 4 * b_row, 4))
+        want = np.einsum("bmk,bnk->bmn" if tb else "bmk,bkn->bmn", av.astype(np.float64), bv.astype(np.float64)).astype(np.float32)
+        plan = ctx.matmul_plan((bs, m, k), (bs, n, k) if tb else (bs, k, n), False, tb,
+                               strides=(a_batch, a_row, b_batch, b_row, c_batch, c_row))
+        ta, tbm = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()  # kept alive until the result has been read
+        tc = torch.full((bs * c_batch + 8,), 7.0, device="cuda")
+        ctx.check(ctx.lib.petb200_matmul_run(plan.h, ta.data_ptr(), tbm.data_ptr(), None, tc.data_ptr(), None))
+        torch.cuda.synchronize()
+        out = tc.cpu().numpy()
+        case = (bs, m, n, k, tb, a_batch, a_row, b_batch, b_row, c_batch, c_row)
+        assert np.array_equal(as_view(out, (bs, m, n), (4 * c_batch, 4 * c_row, 4)), want), case
+        as_view(out, (bs, m, n), (4 * c_batch, 4 * c_row, 4))[...] = 7.0
+        assert (out == 7.0).all(), case
+    ctx.sync_check()
