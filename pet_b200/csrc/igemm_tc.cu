@@ -35,7 +35,7 @@ constexpr int kTileM = 128;
 constexpr int kStageK = 32;               // fp32/TF32 values per K stage = one 128-byte swizzle row
 constexpr int kAHalfBytes = kTileM * 128; // one 128 x 32 operand tile
 constexpr int kThreads = 352;   // warps: 0 B producer, 1 MMA, 2 raw producer, 3-6 and 7-10 two transform/epilogue sets
-constexpr int kProfSlots = 16; // tuning counters per CTA (see IgemmParams::prof)
+constexpr int kProfSlots = 24; // tuning counters per CTA (see IgemmParams::prof)
 constexpr int kMaxNB = 6;
 constexpr int kMaxNR = 6;
 
@@ -54,6 +54,10 @@ struct IgemmParams {
     int ksplit;             // K is split over this many CTAs, launched as one thread-block cluster (2, 4 or 8); partial
                             // tiles are added up through distributed shared memory
     int NA, NB, NR;         // ring depths: A stages, B stages, raw activation buffers
+    int fl;                 // 3xTF32 only: every `fl` K stages the main accumulator is drained into a running total that
+                            // is summed with round-to-nearest adds (0: never).  The tensor core truncates its accumulator
+                            // after every MMA; restarting it keeps the truncated partial sums short and small
+    int a_col;              // first TMEM column of the A-operand ring (TS variants)
     int a_kmajor;           // matmul with row-major A: the raw tile is [128 rows][32 k], 128B-swizzled, one per K stage
     int m_rows;             // a_kmajor: rows of A per batch entry
     int raw_bytes;          // bytes of one raw buffer (128-aligned)
@@ -125,7 +129,7 @@ template <int ACT> __device__ __forceinline__ float act_fn(float v) {
 // filter of the group; column j of the tile is filter f_tile0 + j.  The activation is a template parameter so that
 // the common no-activation case carries none of the transcendental code.
 template <int ACT, int PASSES>
-__device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile0, int Fg, bool valid, const float *bias,
+__device__ __forceinline__ void epilogue_store(uint32_t tacc, uint32_t tcross, int BN, int f_tile0, int Fg, bool valid, const float *bias,
                                                const float *rp /*residual at this pixel, or null*/, float *yp, long long ys_f, bool vec_ok, float *stage, int nvalid_warp, float *ybase_warp,
                                                int col0, int col1, uint32_t split_addr /*split-K: shared address of [this rank][0][this pixel]*/,
                                                int split_shift /*log2(columns per CTA)*/) {
@@ -134,7 +138,7 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile
         return;
     ptx::tmem_ld_32x32(tacc + (uint32_t)col0, nx);
     if (PASSES == 3)
-        ptx::tmem_ld_32x32(tacc + (uint32_t)BN + (uint32_t)col0, sm);
+        ptx::tmem_ld_32x32(tcross + (uint32_t)col0, sm);
     for (int cc = col0; cc < col1; cc += 32) {
         ptx::tmem_ld_wait();
 #pragma unroll
@@ -143,7 +147,7 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, int BN, int f_tile
         if (cc + 32 < col1) { // in flight while this chunk is stored
             ptx::tmem_ld_32x32(tacc + (uint32_t)(cc + 32), nx);
             if (PASSES == 3)
-                ptx::tmem_ld_32x32(tacc + (uint32_t)BN + (uint32_t)(cc + 32), sm);
+                ptx::tmem_ld_32x32(tcross + (uint32_t)(cc + 32), sm);
         }
         if (split_addr != 0u) {
             // Split-K: column c of the tile is summed by CTA c / cols of the cluster.  Push this CTA's partial sum into
@@ -355,6 +359,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(acc_full + 2);
     float *zero_word = reinterpret_cast<float *>(acc_full + 3); // holds 0.0f: what a masked-off filter tap reads
+    uint64_t *acc_ready = acc_full + 4; // a group of `fl` K stages has been accumulated: the main accumulator may be drained
+    uint64_t *flushed = acc_full + 5;   // all eight transform warps have drained it: the MMA warp may restart it
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     long long *prof_cta = nullptr; // wall-clock marks of this CTA (entry, prologue done, epilogue done, exit), tuning only
@@ -367,7 +373,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     const int zb = blockIdx.z;
     const uint32_t b_half = (uint32_t)P.BN * 128u;
     // TMEM columns: [0,BN) accumulator of the hi*hi products, [BN,2*BN) accumulator of the two small cross terms,
-    // [256,512) the A stages of the TS variant
+    // [2*BN,3*BN) the running total of drained main accumulators (P.fl > 0), [P.a_col,512) the A stages of the TS variant
     const uint32_t tmem_cols = A_TMEM ? 512u : 256u;
 
     if (threadIdx.x == 0) {
@@ -384,6 +390,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             ptx::mbar_init(a_empty + i, 1);
         }
         ptx::mbar_init(acc_full, 1);
+        ptx::mbar_init(acc_ready, 1);
+        ptx::mbar_init(flushed, 8);
         *abort_flag = 0;
         *zero_word = 0.f;
         ptx::fence_mbar_init();
@@ -546,9 +554,11 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         uint32_t accumulate = 0;
         int sa = 0, sb = 0, prev_sa = -1, prev_sb = -1;
         uint32_t pa = 0, pb = 0;
-        long long t_wa = 0, t_wb = 0;
+        long long t_wa = 0, t_wb = 0, t_wf = 0;
         const long long t_begin = P.prof ? clock64() : 0;
         bool ok = true, ready_next = false;
+        const int FLm = P.fl;
+        int gpos = 0, gidx = 0; // position of the stage inside its flush group, index of the group
         for (int ks = 0; ks < KS; ++ks) {
             if (!ready_next) { // not already seen complete by the poll issued in the shadow of the previous stage's MMAs
                 if (P.prof) {
@@ -567,7 +577,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 break;
             ptx::tc_fence_after();
             const uint64_t bhi = bdesc0 + (uint64_t)((uint32_t)sb * 2u * b_half16);
-            const uint32_t ahi_t = tmem_base + 256u + (uint32_t)sa * 64u, alo_t = ahi_t + 32u;
+            const uint32_t ahi_t = tmem_base + (uint32_t)P.a_col + (uint32_t)sa * 64u, alo_t = ahi_t + 32u;
             const uint64_t ahi_s = adesc0 + (uint64_t)((uint32_t)sa * 2u * (kAHalfBytes >> 4));
             const uint64_t alo_s = ahi_s + (kAHalfBytes >> 4);
             // next stage's ring positions, polled (non-blocking) while this stage's last MMAs are still queued
@@ -605,16 +615,59 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                         ptx::mma_tf32_ss(tmem_small, alo_s + 2 * kk, bhi + 2 * kk, idesc, 1u);
                 }
             };
-            if (ptx::elect_one()) {
+            // First stage of a new flush group: the main accumulator restarts from zero, but only after the transform warps
+            // have drained the previous group's sum.  The stage's eight cross-term MMAs do not touch the main accumulator
+            // and are issued first, so the tensor pipe has work while the drain is in flight.
+            const bool group_start = PASSES == 3 && FLm > 0 && ks > 0 && gpos == 0; // (no division: this warp's loop is latency bound)
+            if (group_start) {
+                const uint64_t blo = bhi + b_half16;
+                if (ptx::elect_one()) {
 #pragma unroll
-                for (int kk = 0; kk < 3; ++kk)
-                    issue_step(kk);
+                    for (int kk = 0; kk < 4; ++kk) {
+                        ptx::mma_tf32_ts(tmem_small, ahi_t + kk * 8, blo + 2 * kk, idesc, 1u);
+                        if (kk == 0 && prev_sa >= 0) {
+                            ptx::mma_commit(a_empty + prev_sa);
+                            ptx::mma_commit(b_empty + prev_sb);
+                        }
+                        ptx::mma_tf32_ts(tmem_small, alo_t + kk * 8, bhi + 2 * kk, idesc, 1u);
+                    }
+                }
+                __syncwarp();
+                const long long qf0 = P.prof ? clock64() : 0;
+                ok = ptx::mbar_wait(flushed, (uint32_t)((gidx - 1) & 1), abort_flag);
+                if (P.prof)
+                    t_wf += clock64() - qf0;
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok)
+                    break;
+                ptx::tc_fence_after();
+                if (ptx::elect_one()) {
+#pragma unroll
+                    for (int kk = 0; kk < 3; ++kk)
+                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, kk == 0 ? 0u : 1u);
+                }
+                __syncwarp();
+            } else {
+                if (ptx::elect_one()) {
+#pragma unroll
+                    for (int kk = 0; kk < 3; ++kk)
+                        issue_step(kk);
+                }
+                __syncwarp();
             }
-            __syncwarp();
             ready_next = (ks + 1 < KS) && ptx::mbar_test_wait(a_full + nsa, npa) && ptx::mbar_test_wait(b_full + nsb, npb);
             ready_next = __all_sync(0xffffffffu, ready_next);
-            if (ptx::elect_one())
-                issue_step(3);
+            const bool group_end = PASSES == 3 && FLm > 0 && gpos == FLm - 1 && ks + 1 < KS;
+            if (++gpos == FLm)
+                gpos = 0, ++gidx;
+            if (ptx::elect_one()) {
+                if (group_start)
+                    ptx::mma_tf32_ts(tmem_base, ahi_t + 24, bhi + 6, idesc, 1u);
+                else
+                    issue_step(3);
+                if (group_end) // fires once every MMA of the group has completed
+                    ptx::mma_commit(acc_ready);
+            }
             __syncwarp();
             accumulate = 1u;
             if (ready_next) {
@@ -649,6 +702,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             pr[0] = t_wa;
             pr[1] = t_wb;
             pr[2] = clock64() - t_begin;
+            pr[16] = t_wf;
         }
     } else {
         // ---------------- transform + epilogue: two sets of four warps (3..6 and 7..10) ----------------
@@ -686,6 +740,47 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         const long long t_begin = P.prof ? clock64() : 0;
         int rb = 0;
         uint32_t prw = 0;
+        // Accumulator flush (P.fl > 0): the K stages form groups of P.fl; when the MMAs of group g have completed, the
+        // eight transform warps add the main accumulator to the running total in TMEM (round-to-nearest fp32 adds, in
+        // group order) and the MMA warp restarts the main accumulator for group g + 1.  A warp drains the columns its set
+        // stores in the epilogue, of its own lane quarter.
+        const int FL = (PASSES == 3 && A_TMEM) ? P.fl : 0;
+        const int n_groups = FL > 0 ? (KS + FL - 1) / FL : 1;
+        const int fcol0 = tset == 0 ? 0 : ((P.BN / 32 + 1) / 2) * 32, fcol1 = tset == 0 ? ((P.BN / 32 + 1) / 2) * 32 : P.BN;
+        int fg = 0; // next group this warp has to drain
+        long long t_dw = 0, t_dd = 0;
+        auto drain_group = [&](int g, bool wait_mma, bool signal) -> bool {
+            const long long cd0 = P.prof ? clock64() : 0;
+            if (wait_mma && !ptx::mbar_wait(acc_ready, (uint32_t)(g & 1), abort_flag))
+                return false;
+            const long long cd1 = P.prof ? clock64() : 0;
+            ptx::tc_fence_after();
+            const uint32_t tq = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            for (int cc = fcol0; cc < fcol1; cc += 32) {
+                uint32_t mn[32], tt[32];
+                ptx::tmem_ld_32x32(tq + (uint32_t)cc, mn);
+                if (g > 0)
+                    ptx::tmem_ld_32x32(tq + 2u * (uint32_t)P.BN + (uint32_t)cc, tt);
+                ptx::tmem_ld_wait();
+                if (g > 0) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        mn[j] = __float_as_uint(__uint_as_float(tt[j]) + __uint_as_float(mn[j]));
+                }
+                ptx::tmem_st_32x32(tq + 2u * (uint32_t)P.BN + (uint32_t)cc, mn);
+            }
+            ptx::tmem_st_wait();
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (signal && lane == 0)
+                ptx::mbar_arrive(flushed);
+            if (P.prof) {
+                t_dw += cd1 - cd0;
+                t_dd += clock64() - cd1;
+            }
+            return true;
+        };
+        int gs = tset; // index of this set's next K stage among the CTA's KS stages
         // This set owns every second K stage (tset, tset + 2, ...): `st` is the next one's index inside the current chunk,
         // `sa`/`pa` its slot of the A ring and the parity to wait for (first pass over the ring: every slot is free).
         int st = tset, sa = tset;
@@ -696,16 +791,31 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             if (P.prof)
                 t_wr += clock64() - cr0;
             const float *raw = reinterpret_cast<const float *>(sRaw + (size_t)rb * P.raw_bytes) + base_p;
-            for (; st < P.spc && alive; st += 2) {
-                const long long ce0 = P.prof ? clock64() : 0;
-                alive = ptx::mbar_wait(a_empty + sa, pa, abort_flag);
-                if (P.prof)
-                    t_we += clock64() - ce0;
+            for (; st < P.spc && alive; st += 2, gs += 2) {
+                // Groups that ended before this stage: drain at once if their MMAs are done; otherwise produce one more
+                // stage first (the MMA warp can start on it) and then wait for them.
+                while (fg < n_groups - 1 && gs >= (fg + 1) * FL && alive) {
+                    const bool done = __shfl_sync(0xffffffffu, ptx::mbar_test_wait(acc_ready, (uint32_t)(fg & 1)) ? 1 : 0, 0) != 0;
+                    if (!done && gs < (fg + 1) * FL + 2)
+                        break;
+                    alive = drain_group(fg, !done, true);
+                    ++fg;
+                }
                 if (!alive)
                     break;
                 const int4 *ko = reinterpret_cast<const int4 *>(sKoff + st * kStageK);
+                if (!A_TMEM) {
+                    const long long ce0 = P.prof ? clock64() : 0;
+                    alive = ptx::mbar_wait(a_empty + sa, pa, abort_flag);
+                    if (P.prof)
+                        t_we += clock64() - ce0;
+                    if (!alive)
+                        break;
+                }
                 if (A_TMEM) {
-                    ptx::tc_fence_after();
+                    // The operands are gathered and split into registers BEFORE the wait for the stage's slot in tensor
+                    // memory: when the slot frees, only the two tcgen05.st remain, so a set is one stage ahead in registers
+                    // on top of its slots in the ring.
                     uint32_t hi[32], lo[32];
                     const uint8_t *krow = sRaw + (size_t)rb * P.raw_bytes + (size_t)p * 128;
                     const long long cg0 = P.prof ? clock64() : 0;
@@ -722,9 +832,18 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                         gather_split<kGatherFlat, PASSES>(ko, raw, krow, p, tmask, 0, true, zero_word, hi, lo);
                     else
                         gather_split<kGatherTable, PASSES>(ko, raw, krow, p, tmask, 0, false, zero_word, hi, lo);
-                    const uint32_t t = tmem_base + ((uint32_t)(quarter * 32) << 16) + 256u + (uint32_t)sa * 64u;
+                    const long long ce0 = P.prof ? clock64() : 0;
+                    alive = ptx::mbar_wait(a_empty + sa, pa, abort_flag);
+                    if (!alive)
+                        break;
+                    ptx::tc_fence_after();
+                    const uint32_t t = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)P.a_col + (uint32_t)sa * 64u;
                     ptx::tmem_st_32x32(t, hi);
                     const long long cg1 = P.prof ? clock64() : 0;
+                    if (P.prof) {
+                        t_we += cg1 - ce0;
+                        t_g -= cg1 - ce0; // the gather time below is measured up to cg1
+                    }
                     if (PASSES == 3)
                         ptx::tmem_st_32x32(t + 32u, lo);
                     ptx::tmem_st_wait();
@@ -775,8 +894,12 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         }
         // ---------------- epilogue ----------------
         const long long t_loop = P.prof ? clock64() - t_begin : 0;
+        for (; fg < n_groups - 1 && alive; ++fg)
+            alive = drain_group(fg, true, true);
         if (alive)
             alive = ptx::mbar_wait(acc_full, 0u, abort_flag);
+        if (alive && FL > 0) // the last group joins the total; the epilogue then reads the total in place of the accumulator
+            drain_group(n_groups - 1, false, false);
         const long long t_epi0 = P.prof ? clock64() : 0;
         const bool vec_ok = (P.ys_f == 1) && ((P.ys_p & 3) == 0) && ((P.ys_n & 3) == 0) && ((P.Fg & 3) == 0) &&
                             ((reinterpret_cast<uintptr_t>(P.y) & 15) == 0);
@@ -791,7 +914,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             const int split_cols = P.BN / P.ksplit, split_shift = 31 - __clz(split_cols);
             const uint32_t split_addr =
                 P.ksplit > 1 ? ptx::smem_u32(sSplit) + (uint32_t)(((int)ptx::cluster_ctarank() * split_cols) * kTileM + p) * 4u : 0u;
-            const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (FL > 0 ? 2u * (uint32_t)P.BN : 0u);
+            const uint32_t tcross = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)P.BN;
             // staged 16-byte stores need: pixel-contiguous NCHW output, full-width rows (no column window), one plane per
             // tile, 16-byte aligned runs
             float *stage = nullptr;
@@ -813,7 +937,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             const int nblk = P.BN / 32, half_blk = (nblk + 1) / 2;
             const int col0 = tset == 0 ? 0 : half_blk * 32, col1 = tset == 0 ? half_blk * 32 : P.BN;
 #define PETB200_EPI(ACT_)                                                                                              \
-    epilogue_store<ACT_, PASSES>(tacc, P.BN, f_tile0, P.Fg, valid, bp, rp, yp, P.ys_f, vec_ok, stage, nvalid_warp, \
+    epilogue_store<ACT_, PASSES>(tacc, tcross, P.BN, f_tile0, P.Fg, valid, bp, rp, yp, P.ys_f, vec_ok, stage, nvalid_warp, \
                                  ybase_warp, col0, col1, split_addr, split_shift)
             switch (P.ksplit > 1 ? PETB200_ACT_NONE : P.act) {
             case PETB200_ACT_RELU: PETB200_EPI(PETB200_ACT_RELU); break;
@@ -834,6 +958,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             pr[10] = (long long)ptx::globaltimer_ns();
             pr[12] = t_g;
             pr[13] = t_st;
+            pr[17] = t_dw;
+            pr[18] = t_dd;
         }
     }
 
@@ -1133,6 +1259,25 @@ static int choose_ksplit(int sm_count, long long base_ctas, const IgemmParams &P
     return best;
 }
 
+// Accumulator flush period (see IgemmParams::fl) and the TMEM column map that goes with it.  The truncation bias of the
+// tensor core's fp32 accumulator grows with the number of MMAs added into one running sum: K ranges of more than
+// `2 * period` stages per CTA are drained every `period` stages (PETB200_TC_FLUSH in the environment, 0 = never).  The
+// running total takes BN more TMEM columns; a 128-wide tile then has room for two A stages instead of four.
+static void choose_flush(TcCore &core) {
+    IgemmParams &P = core.P;
+    const int period = env_int("PETB200_TC_FLUSH", 8);
+    const int ks_max = ((P.nchunks + P.ksplit - 1) / P.ksplit) * P.spc;
+    P.fl = (!core.single_pass && core.a_tmem && period > 0 && ks_max > 2 * period) ? period : 0;
+    P.a_col = (P.fl > 0 && P.BN == 128) ? 384 : 256;
+    if (env_int("PETB200_TC_ACOL", 0) == 384 && P.BN <= 128) // tuning: the short A ring without the flush
+        P.a_col = 384;
+    if (core.a_tmem)
+        P.NA = (512 - P.a_col) / 64;
+    if (env_int("PETB200_TC_VERBOSE", 0))
+        fprintf(stderr, "[petb200] igemm plan: BN %d BC %d chunks %d stages/chunk %d ksplit %d flush %d NA %d NB %d NR %d kmajor %d flat %d\n",
+                P.BN, P.BC, P.nchunks, P.spc, P.ksplit, P.fl, P.NA, P.NB, P.NR, P.a_kmajor, P.flat);
+}
+
 // The dynamic shared-memory attribute is per function, not per launch: raise it once to the device limit so that plans
 // with different needs can coexist.
 static int raise_smem_limit(petb200_ctx *ctx) {
@@ -1346,6 +1491,7 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     if (!have)
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "raw activation tile does not fit shared memory");
     P = bestP;
+    choose_flush(core);
     P.gruns = P.BC % kStageK == 0 ? 1 : (P.BC == 16 ? 2 : (P.BC == 8 ? 4 : 0));
     P.cstride = (P.gruns && env_int("PETB200_TC_TABLE", 0) == 0) ? P.RD * P.RH * P.RW : 0;
     if (flat && (!core.a_tmem || (long long)P.RN * P.BC * P.RD * P.RH * P.RW >= (1 << 24)))
@@ -1665,6 +1811,7 @@ static int tc_configure_kmajor(petb200_ctx *ctx, TcCore &core, int bs, int m, in
                 P.NR--;
         }
     }
+    choose_flush(core);
     core.smem = smem_layout(P, true).total + 1024;
     core.Ktot = (long long)P.nchunks * kStageK;
     core.xd[0] = k, core.xd[1] = m, core.xd[2] = bs;

@@ -297,5 +297,5 @@ def test_random_encoder_graphs_fused_vs_unfused_vs_oracle(ctx):
                   ffn=int(rng.choice([32, 96, 256])))
         _, _, y = run_config(ctx, configs.bert_encoder, **kw)
         _, _, y2 = run_config(ctx, configs.bert_encoder, fuse=False, cuda_graph=False, **kw)
-        assert rel_err(y, y2) <= 1e-5, kw
+        assert rel_err(y, y2) <= TOL, kw  # two summation orders of the same products, compounded over the layers
         assert rel_err(y, oracle_config(configs.bert_encoder, **kw)) <= TOL, kw

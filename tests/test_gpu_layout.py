@@ -37,6 +37,19 @@ def test_copy_ops_bit_exact_vs_reference_vectors(ctx, golden):
         assert np.array_equal(host(o), golden[f"split_ratio_{j}"])
 
 
+def test_n2h_kernel_reproduces_the_reference_fixture_digest(ctx):
+    """The reference's committed transpose fixture (src/Test/dat/transpose_test/input.dat, packed into tests/golden)
+    through the CUDA N2H kernel: the result must hash to the SHA-256 of the output file the reference's own
+    transpose_test_1 writes."""
+    import hashlib
+    import os
+    from test_oracle import PACKED_FIXTURE, REF_FIXTURE_OUT_SHA
+    x = np.load(PACKED_FIXTURE)["digits"].astype(np.uint32)
+    y = host(ctx.transpose(dev(x), 0, [0, 1, [-1, 2], 3], 2))
+    assert y.shape == (8, 16, 64, 32)
+    assert hashlib.sha256(gc.tpm_text(y)).hexdigest() == REF_FIXTURE_OUT_SHA
+
+
 S2B = [(2, [0, 1, [-1, 2], 3], 2), (2, [[0, 2], 1, -1, 3], -2), (3, [0, 1, 2, [-1, 3]], 2), (3, [[0, 3], 1, 2, -1], -2)]
 B2S = [(0, [0, 1, 2, [-1, 3]], 2), (3, [0, 1, 2, [-1, 3]], -2), (0, [0, 1, [-1, 2], 3], 2), (2, [0, 1, [-1, 2], 3], -2)]
 
