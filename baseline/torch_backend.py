@@ -1,11 +1,13 @@
 """Evaluates a configuration from pet_b200.configs with the vendor libraries through torch (cuDNN / cuBLAS on the GPU,
-TF32 switched off: true fp32 math) — the library execution of the same graph that the parity contract names.  Test
-harness only; layout operators go through the CPU oracle (they are bit-exact copies either way)."""
+TF32 switched off: true fp32 math; or on: the libraries' default math mode on this GPU) — the library execution of the
+same graph that the parity contract names, and the timing baseline of the benchmark.  torch's bindings stand in for the
+reference's direct calls (cudnnConvolutionForward, ref: src/Graph/operator.cc:296-515; cublasGemmStridedBatchedEx,
+ref: :728-832).  Harness only, never on the product path; layout operators other than plain permutations go through the
+CPU oracle (bit-exact copies either way; parity tests only).  The product (pet_b200/) must not import this."""
 import numpy as np
 import torch
 import torch.nn.functional as F
 
-from oracle import pet_oracle as po
 
 
 def _t(a):
@@ -45,15 +47,14 @@ class TorchBuilder:
         y = torch.matmul(a.transpose(1, 2) if transA else a, b.transpose(1, 2) if transB else b)
         return _act(y if bias is None else y + bias, act)
 
-    def _np(self, fn, x, *args):
-        if self.dtype != torch.float32:  # layout operators move words: do them on 64-bit values as two halves is overkill
-            raise NotImplementedError
-        return _t(fn(x.cpu().numpy(), *args))
+    def _np(self, name, x, *args):
+        from oracle import pet_oracle as po  # only the parity tests reach this
+        return _t(getattr(po, name)(x.cpu().numpy(), *args))
 
     def transpose(self, x, split, after, factor=2):
         if split == -1 and all(not isinstance(g, (list, tuple)) for g in after):
             return x.permute(*after).contiguous()
-        return self._np(po.transpose, x, split, after, factor)
+        return self._np("transpose", x, split, after, factor)
 
     def add(self, xs):
         y = xs[0]

@@ -91,6 +91,16 @@ int petb200_graph_get_data(petb200_graph *g, int tensor, float *host, size_t n, 
 void *petb200_graph_device_ptr(petb200_graph *g, int tensor);
 /* One forward pass on `stream` (a CUDA-graph launch unless compiled with bit 1). */
 int petb200_graph_run(petb200_graph *g, petb200_stream stream);
+/* One forward pass issued step by step on `stream` (no CUDA graph), instrumented for the roofline accounting of a
+ * benchmark: a CUDA event is recorded on the stream before and after every step that is NOT a tensor-core launch (pooling,
+ * element-wise, softmax, LayerNorm, layout, small-m matmul ...), into slot `slot` of `nslots` event sets, so that `nslots`
+ * consecutive passes can be issued back to back without reading anything in between.  Tensor-core steps run exactly as
+ * in petb200_graph_run, chained by programmatic dependent launch.  petb200_graph_profile_other_ms then returns the summed
+ * duration of those other steps over the slots run since its previous call (it waits for them): the time of a region made of such passes, minus this sum, is the time the
+ * tensor-core kernel was running.  The counterpart in the reference is the per-operator timing inside Operator::perf
+ * (ref: src/Graph/operator.cc:416-467); the reference times whole programs only with wall clock (ref: code_engine.cc:195-217). */
+int petb200_graph_run_profiled(petb200_graph *g, petb200_stream stream, int slot, int nslots);
+int petb200_graph_profile_other_ms(petb200_graph *g, int nslots, float *other_ms);
 /* Kernel launches one pass issues; operators left after fusion. */
 int petb200_graph_num_launches(const petb200_graph *g);
 int petb200_graph_num_steps(const petb200_graph *g);

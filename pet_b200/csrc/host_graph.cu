@@ -111,6 +111,10 @@ struct petb200_graph {
     bool hoisted_done = false;
     PerfEngine perf;
     std::string err;
+    // petb200_graph_run_profiled: per slot, one event pair around every replayed step that is not a tensor-core launch
+    std::vector<cudaEvent_t> prof_events;
+    std::vector<char> prof_recorded; // per slot: run since the last read
+    int prof_slots = 0, prof_pairs = 0;
 
     int fail(int status, const char *fmt, ...) {
         char buf[512];
@@ -150,6 +154,8 @@ struct petb200_graph {
         return id;
     }
     ~petb200_graph() {
+        for (cudaEvent_t e : prof_events)
+            cudaEventDestroy(e);
         for (auto &s : steps)
             if (s.plan)
                 petb200_plan_destroy(s.plan);
@@ -171,7 +177,7 @@ struct petb200_graph {
     }
 
     int run_step(Step &s, cudaStream_t st);
-    int run_all(cudaStream_t st, bool include_hoisted);
+    int run_all(cudaStream_t st, bool include_hoisted, int prof_slot = -1);
     int compile(int flags);
     int capture();
 };
@@ -308,10 +314,14 @@ int petb200_graph::run_step(Step &s, cudaStream_t st) {
     return PETB200_ERR_UNSUPPORTED;
 }
 
-int petb200_graph::run_all(cudaStream_t st, bool include_hoisted) {
+int petb200_graph::run_all(cudaStream_t st, bool include_hoisted, int prof_slot) {
+    int pair = 0;
     for (auto &s : steps) {
         if (s.weight_only && !include_hoisted)
             continue;
+        const bool timed = prof_slot >= 0 && !s.side && strncmp(s.kernel, "tc_", 3) != 0;
+        if (timed && cudaEventRecord(prof_events[((size_t)prof_slot * prof_pairs + pair) * 2], st) != cudaSuccess)
+            return fail(PETB200_ERR_CUDA, "profile event record failed");
         const unsigned long long before = petb200_launch_count(ctx);
         cudaStream_t where = st;
         if (s.side && side_stream) { // fork: everything issued so far precedes the side step
@@ -326,6 +336,8 @@ int petb200_graph::run_all(cudaStream_t st, bool include_hoisted) {
             return rc;
         if (where != st && cudaEventRecord(s.ev_join, side_stream) != cudaSuccess)
             return fail(PETB200_ERR_CUDA, "side-branch join record failed");
+        if (timed && cudaEventRecord(prof_events[((size_t)prof_slot * prof_pairs + pair++) * 2 + 1], st) != cudaSuccess)
+            return fail(PETB200_ERR_CUDA, "profile event record failed");
         s.launches = (int)(petb200_launch_count(ctx) - before); // what the step really launches (plans decide, e.g. a per-call operand pack)
     }
     return PETB200_OK;
@@ -1545,6 +1557,58 @@ extern "C" int petb200_graph_run(petb200_graph *g, petb200_stream stream) {
     }
     if (cudaGraphLaunch(g->exec, st) != cudaSuccess)
         return g->fail(PETB200_ERR_CUDA, "graph launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return PETB200_OK;
+}
+
+extern "C" int petb200_graph_run_profiled(petb200_graph *g, petb200_stream stream, int slot, int nslots) {
+    if (!g || slot < 0 || nslots <= 0 || slot >= nslots)
+        return PETB200_ERR_INVALID;
+    if (!g->compiled)
+        return g->fail(PETB200_ERR_INVALID, "run before compile");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!g->hoisted_done) {
+        int rc = prepare_weights(g, st);
+        if (rc)
+            return rc;
+        g->hoisted_done = true;
+    }
+    int pairs = 0;
+    for (auto &s : g->steps)
+        if (!s.weight_only && !s.side && strncmp(s.kernel, "tc_", 3) != 0)
+            ++pairs;
+    if (nslots != g->prof_slots || pairs != g->prof_pairs) {
+        for (cudaEvent_t e : g->prof_events)
+            cudaEventDestroy(e);
+        g->prof_events.assign((size_t)nslots * pairs * 2, nullptr);
+        for (auto &e : g->prof_events)
+            if (cudaEventCreate(&e) != cudaSuccess)
+                return g->fail(PETB200_ERR_CUDA, "profile event creation failed");
+        g->prof_slots = nslots;
+        g->prof_pairs = pairs;
+        g->prof_recorded.assign((size_t)nslots, 0);
+    }
+    g->prof_recorded[(size_t)slot] = 1;
+    return g->run_all(st, false, slot);
+}
+
+extern "C" int petb200_graph_profile_other_ms(petb200_graph *g, int nslots, float *other_ms) {
+    if (!g || !other_ms || nslots != g->prof_slots)
+        return PETB200_ERR_INVALID;
+    double total = 0;
+    for (int slot = 0; slot < nslots; ++slot) {
+        if (!g->prof_recorded[(size_t)slot])
+            continue;
+        g->prof_recorded[(size_t)slot] = 0;
+        for (int pair = 0; pair < g->prof_pairs; ++pair) {
+            const size_t i = ((size_t)slot * g->prof_pairs + pair) * 2;
+            float ms = 0.f;
+            if (cudaEventSynchronize(g->prof_events[i + 1]) != cudaSuccess ||
+                cudaEventElapsedTime(&ms, g->prof_events[i], g->prof_events[i + 1]) != cudaSuccess)
+                return g->fail(PETB200_ERR_CUDA, "profile event read failed");
+            total += ms;
+        }
+    }
+    *other_ms = (float)total;
     return PETB200_OK;
 }
 

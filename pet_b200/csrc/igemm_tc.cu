@@ -58,6 +58,9 @@ struct IgemmParams {
                             // is summed with round-to-nearest adds (0: never).  The tensor core truncates its accumulator
                             // after every MMA; restarting it keeps the truncated partial sums short and small
     int a_col;              // first TMEM column of the A-operand ring (TS variants)
+    int fl_regs;            // 128-wide tiles: the running total lives in the registers of the second transform set, whose
+                            // warps then do nothing but drain (the first set produces every A stage); narrower tiles
+                            // keep the total in TMEM columns [2*BN,3*BN) and both sets drain between their stages
     int a_kmajor;           // matmul with row-major A: the raw tile is [128 rows][32 k], 128B-swizzled, one per K stage
     int m_rows;             // a_kmajor: rows of A per batch entry
     int raw_bytes;          // bytes of one raw buffer (128-aligned)
@@ -379,7 +382,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     if (threadIdx.x == 0) {
         for (int i = 0; i < kMaxNR; ++i) {
             ptx::mbar_init(raw_full + i, 1);
-            ptx::mbar_init(raw_empty + i, 8);
+            ptx::mbar_init(raw_empty + i, P.fl_regs ? 4 : 8);
         }
         for (int i = 0; i < kMaxNB; ++i) {
             ptx::mbar_init(b_full + i, 1);
@@ -391,7 +394,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         }
         ptx::mbar_init(acc_full, 1);
         ptx::mbar_init(acc_ready, 1);
-        ptx::mbar_init(flushed, 8);
+        ptx::mbar_init(flushed, P.fl_regs ? 4 : 8);
         *abort_flag = 0;
         *zero_word = 0.f;
         ptx::fence_mbar_init();
@@ -744,7 +747,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         // eight transform warps add the main accumulator to the running total in TMEM (round-to-nearest fp32 adds, in
         // group order) and the MMA warp restarts the main accumulator for group g + 1.  A warp drains the columns its set
         // stores in the epilogue, of its own lane quarter.
-        const int FL = (PASSES == 3 && A_TMEM) ? P.fl : 0;
+        const bool reg_total = PASSES == 3 && A_TMEM && P.fl > 0 && P.fl_regs != 0;
+        const int FL = (PASSES == 3 && A_TMEM && !reg_total) ? P.fl : 0;
         const int n_groups = FL > 0 ? (KS + FL - 1) / FL : 1;
         const int fcol0 = tset == 0 ? 0 : ((P.BN / 32 + 1) / 2) * 32, fcol1 = tset == 0 ? ((P.BN / 32 + 1) / 2) * 32 : P.BN;
         int fg = 0; // next group this warp has to drain
@@ -780,18 +784,70 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             }
             return true;
         };
-        int gs = tset; // index of this set's next K stage among the CTA's KS stages
+        // Register-total mode: set 1 only drains.  Its threads keep the 128 columns of their tile row in registers, add the
+        // main accumulator of every completed group to them, and at the end write total + last group back over the main
+        // accumulator, which the epilogue of both sets then reads as if nothing had happened.
+        if (reg_total && tset == 1) {
+            float racc[128];
+#pragma unroll
+            for (int j = 0; j < 128; ++j)
+                racc[j] = 0.f;
+            const uint32_t tq = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            const int groups = (KS + P.fl - 1) / P.fl;
+            for (int g = 0; g < groups && alive; ++g) {
+                const bool last = g == groups - 1;
+                const long long cd0 = P.prof ? clock64() : 0;
+                alive = last ? ptx::mbar_wait(acc_full, 0u, abort_flag) : ptx::mbar_wait(acc_ready, (uint32_t)(g & 1), abort_flag);
+                if (!alive)
+                    break;
+                const long long cd1 = P.prof ? clock64() : 0;
+                ptx::tc_fence_after();
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    uint32_t v0[16], v1[16];
+                    ptx::tmem_ld_32x16(tq + (uint32_t)(b * 32), v0);
+                    ptx::tmem_ld_32x16(tq + (uint32_t)(b * 32 + 16), v1);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        racc[b * 32 + j] += __uint_as_float(v0[j]);
+                        racc[b * 32 + 16 + j] += __uint_as_float(v1[j]);
+                    }
+                    if (last) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            v0[j] = __float_as_uint(racc[b * 32 + j]);
+                            v1[j] = __float_as_uint(racc[b * 32 + 16 + j]);
+                        }
+                        ptx::tmem_st_32x16(tq + (uint32_t)(b * 32), v0);
+                        ptx::tmem_st_32x16(tq + (uint32_t)(b * 32 + 16), v1);
+                    }
+                }
+                if (last)
+                    ptx::tmem_st_wait();
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (!last && lane == 0)
+                    ptx::mbar_arrive(flushed);
+                if (P.prof) {
+                    t_dw += cd1 - cd0;
+                    t_dd += clock64() - cd1;
+                }
+            }
+        }
+        const int sstep = reg_total ? 1 : 2; // stages between two stages of one set
+        int gs = reg_total ? 0 : tset; // index of this set's next K stage among the CTA's KS stages
         // This set owns every second K stage (tset, tset + 2, ...): `st` is the next one's index inside the current chunk,
         // `sa`/`pa` its slot of the A ring and the parity to wait for (first pass over the ring: every slot is free).
-        int st = tset, sa = tset;
+        int st = reg_total ? 0 : tset, sa = st;
         uint32_t pa = 1;
-        for (int ch = 0; ch < c1 - c0 && alive; ++ch, st -= P.spc) {
+        for (int ch = 0; ch < ((reg_total && tset == 1) ? 0 : c1 - c0) && alive; ++ch, st -= P.spc) {
             const long long cr0 = P.prof ? clock64() : 0;
             alive = ptx::mbar_wait(raw_full + rb, prw, abort_flag); // also by a set without a stage in this chunk
             if (P.prof)
                 t_wr += clock64() - cr0;
             const float *raw = reinterpret_cast<const float *>(sRaw + (size_t)rb * P.raw_bytes) + base_p;
-            for (; st < P.spc && alive; st += 2, gs += 2) {
+            for (; st < P.spc && alive; st += sstep, gs += sstep) {
                 // Groups that ended before this stage: drain at once if their MMAs are done; otherwise produce one more
                 // stage first (the MMA warp can start on it) and then wait for them.
                 while (fg < n_groups - 1 && gs >= (fg + 1) * FL && alive) {
@@ -878,7 +934,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 __syncwarp();
                 if (lane == 0)
                     ptx::mbar_arrive(a_full + sa);
-                sa += 2;
+                sa += sstep;
                 if (sa >= P.NA) {
                     sa -= P.NA;
                     pa ^= 1u;
@@ -900,6 +956,10 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             alive = ptx::mbar_wait(acc_full, 0u, abort_flag);
         if (alive && FL > 0) // the last group joins the total; the epilogue then reads the total in place of the accumulator
             drain_group(n_groups - 1, false, false);
+        if (reg_total) { // set 1 has written total + last group over the main accumulator: both sets meet before reading it
+            ptx::named_bar_sync(1, 256);
+            ptx::tc_fence_after();
+        }
         const long long t_epi0 = P.prof ? clock64() : 0;
         const bool vec_ok = (P.ys_f == 1) && ((P.ys_p & 3) == 0) && ((P.ys_n & 3) == 0) && ((P.Fg & 3) == 0) &&
                             ((reinterpret_cast<uintptr_t>(P.y) & 15) == 0);
@@ -1268,14 +1328,13 @@ static void choose_flush(TcCore &core) {
     const int period = env_int("PETB200_TC_FLUSH", 8);
     const int ks_max = ((P.nchunks + P.ksplit - 1) / P.ksplit) * P.spc;
     P.fl = (!core.single_pass && core.a_tmem && period > 0 && ks_max > 2 * period) ? period : 0;
-    P.a_col = (P.fl > 0 && P.BN == 128) ? 384 : 256;
-    if (env_int("PETB200_TC_ACOL", 0) == 384 && P.BN <= 128) // tuning: the short A ring without the flush
-        P.a_col = 384;
+    P.fl_regs = (P.fl > 0 && P.BN == 128 && env_int("PETB200_TC_FLUSH_REGS", 1)) ? 1 : 0;
+    P.a_col = (P.fl > 0 && P.BN == 128 && !P.fl_regs) ? 384 : 256;
     if (core.a_tmem)
         P.NA = (512 - P.a_col) / 64;
     if (env_int("PETB200_TC_VERBOSE", 0))
-        fprintf(stderr, "[petb200] igemm plan: BN %d BC %d chunks %d stages/chunk %d ksplit %d flush %d NA %d NB %d NR %d kmajor %d flat %d\n",
-                P.BN, P.BC, P.nchunks, P.spc, P.ksplit, P.fl, P.NA, P.NB, P.NR, P.a_kmajor, P.flat);
+        fprintf(stderr, "[petb200] igemm plan: BN %d BC %d chunks %d stages/chunk %d ksplit %d flush %d (regs %d) NA %d NB %d NR %d kmajor %d flat %d\n",
+                P.BN, P.BC, P.nchunks, P.spc, P.ksplit, P.fl, P.fl_regs, P.NA, P.NB, P.NR, P.a_kmajor, P.flat);
 }
 
 // The dynamic shared-memory attribute is per function, not per launch: raise it once to the device limit so that plans

@@ -59,6 +59,8 @@ GRAPH_SYMBOLS = {
     "petb200_graph_step_kernel": (C.c_char_p, [_vp, _i]),
     "petb200_graph_perf": (_i, [_vp, _i, _i, C.POINTER(_fp), C.POINTER(_fp)]),
     "petb200_graph_time": (_i, [_vp, _i, _i, C.POINTER(_fp), _vp]),
+    "petb200_graph_run_profiled": (_i, [_vp, _vp, _i, _i]),
+    "petb200_graph_profile_other_ms": (_i, [_vp, _i, C.POINTER(_fp)]),
 }
 
 _bound = False
@@ -310,6 +312,17 @@ class Graph:
 
     def run(self, stream=None):
         self._check(self.lib.petb200_graph_run(self.h, stream))
+
+    def run_profiled(self, slot, nslots, stream=None):
+        """One pass issued step by step with CUDA events around every step that is not a tensor-core launch (slot of nslots
+        event sets); see profile_other_ms."""
+        self._check(self.lib.petb200_graph_run_profiled(self.h, stream, slot, nslots))
+
+    def profile_other_ms(self, nslots):
+        """Summed duration (ms) of the non-tensor-core steps over the `nslots` profiled passes."""
+        ms = C.c_float()
+        self._check(self.lib.petb200_graph_profile_other_ms(self.h, nslots, C.byref(ms)))
+        return ms.value
 
     def steps(self):
         n = self.lib.petb200_graph_num_steps(self.h)

@@ -7,8 +7,8 @@ import re
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "petb200.h")).read()
+def declared_symbols(header="petb200.h"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(petb200_[a-z0-9_]+)\s*\(", text)))
 
@@ -24,6 +24,12 @@ def test_library_builds_and_exports_every_declared_symbol():
         assert hasattr(handle, name), f"{name} is declared in include/petb200.h but not exported"
     # the Python binding covers the same set
     assert sorted(lib.SYMBOLS) == names
+    graph_names = declared_symbols("petb200_graph.h")
+    assert len(graph_names) >= 40
+    for name in graph_names:
+        assert hasattr(handle, name), f"{name} is declared in include/petb200_graph.h but not exported"
+    from pet_b200 import graph
+    assert sorted(graph.GRAPH_SYMBOLS) == graph_names
 
 
 def test_status_strings_and_ctx_create_without_gpu():

@@ -125,6 +125,8 @@ def test_r3d18_layer_full_size(ctx, oracle, layer):
 # ---- whole graphs at full size ----------------------------------------------------------------------------------------
 def _whole(ctx, build, **kw):
     from test_gpu_graph import run_config, oracle_config
+    import os, sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline"))
     from torch_backend import TorchBuilder
     _, _, y = run_config(ctx, build, **kw)
     want = oracle_config(build, **kw)
