@@ -186,6 +186,10 @@ int petb200_pool2d_run(petb200_ctx *ctx, int kind, const float *x, float *y, int
 int petb200_rowmean_run(petb200_ctx *ctx, const float *x, float *y, size_t rows, int cols, petb200_stream stream);
 /* SoftmaxOp over the last axis (ref: online_softmax, src/Graph/code_engine.cc:424-486,1707-1731). */
 int petb200_softmax_run(petb200_ctx *ctx, const float *x, float *y, size_t rows, int cols, petb200_stream stream);
+/* SoftmaxOp over any axis (the operator carries one, ref: include/operator.h:1887-1938; the reference's emitted kernel
+ * only serves the last): x viewed as [outer, len, inner], normalised over len.  inner == 1 is petb200_softmax_run. */
+int petb200_softmax_axis_run(petb200_ctx *ctx, const float *x, float *y, size_t outer, int len, size_t inner,
+                             petb200_stream stream);
 /* LayerNorm over the last axis (no counterpart in the reference). gamma/beta may be NULL. */
 int petb200_layernorm_run(petb200_ctx *ctx, const float *x, const float *gamma, const float *beta, float *y,
                           size_t rows, int cols, float eps, petb200_stream stream);
@@ -248,8 +252,10 @@ int petb200_banded_time(petb200_ctx *ctx, int kind, int bs, int n, int m, int w,
  * Sharing: all calls on a device use the same array and it keeps the last call's contents; nothing needs clearing,
  * because each call writes every word it later reads.  Calls that overlap on one GPU (two streams, two threads) race
  * on that array — issue them one after the other.
- * First call: the first call on each device looks up the array's device address; make that call before starting a
- * stream capture.
+ * First call: the first call on each device looks up the array's device address and, since device code is loaded lazily,
+ * makes the driver load the module that holds the array (the 8 MiB are reserved then, and the driver may synchronise).
+ * Make one call on each device before entering the region where allocating or synchronising is not allowed, and before
+ * starting a stream capture.  The address cache is safe against several host threads making that first call at once.
  * `err` (may be NULL) receives the reason when the status is not PETB200_OK. */
 #define PETB200_NOALLOC_SCRATCH_FLOATS (2u * 1024u * 1024u)
 int petb200_matmul_splitk_noalloc(int transA, int transB, int b, int m, int n, int k, int ksplit, const float *a_dev,

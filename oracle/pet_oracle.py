@@ -313,9 +313,14 @@ def avgpool(x, k, pad, stride):
     return _pool(lib().oracle_avgpool_f32, x, k, pad, stride)
 
 
-def softmax(x):
-    """Last-axis softmax as the reference's online_softmax kernel defines it (src/Graph/code_engine.cc:424-486)."""
+def softmax(x, axis=-1):
+    """Softmax as the reference's online_softmax kernel defines it for the last axis (src/Graph/code_engine.cc:424-486);
+    any other axis is the same computation on the tensor with that axis moved last (SoftmaxOp carries an axis,
+    include/operator.h:1887-1938)."""
     x = _f32(x)
+    axis = axis + x.ndim if axis < 0 else axis
+    if axis != x.ndim - 1:
+        return np.ascontiguousarray(np.moveaxis(softmax(np.ascontiguousarray(np.moveaxis(x, axis, -1))), -1, axis))
     y = np.empty_like(x)
     lib().oracle_softmax_f32(_p(x), _p(y), C.c_size_t(x.size // x.shape[-1]), x.shape[-1])
     return y

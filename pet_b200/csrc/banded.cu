@@ -311,8 +311,13 @@ extern "C" int petb200_gbmml_run(petb200_ctx *ctx, const float *p, const float *
     const size_t total = (size_t)bs * n * m;
     float *dst = y;
     if (splits > 1) {
-        if (ctx->band_scratch.bytes < total * splits * 4 && ctx->band_scratch.alloc(total * splits * 4) != cudaSuccess)
-            return fail(ctx, PETB200_ERR_NOMEM, "gbmml: scratch for %d partial sums failed", splits);
+        if (ctx->band_scratch.bytes < total * splits * 4) {
+            // the outgrown buffer is retired, not freed: an earlier captured graph may still hold its address
+            if (ctx->band_scratch.p)
+                ctx->band_retired.push_back(ctx->band_scratch.release());
+            if (ctx->band_scratch.alloc(total * splits * 4) != cudaSuccess)
+                return fail(ctx, PETB200_ERR_NOMEM, "gbmml: scratch for %d partial sums failed", splits);
+        }
         dst = (float *)ctx->band_scratch.p;
     }
     const dim3 grid((unsigned)(g.mtiles * splits), (unsigned)ytiles, (unsigned)bs);

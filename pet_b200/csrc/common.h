@@ -17,6 +17,12 @@ struct DevBuf {
         if (p)
             cudaFree(p);
     }
+    void *release() { // hands the memory to the caller
+        void *q = p;
+        p = nullptr;
+        bytes = 0;
+        return q;
+    }
     cudaError_t alloc(size_t n) {
         if (p) {
             cudaFree(p);
@@ -41,6 +47,13 @@ struct petb200_ctx {
     int *d_status = nullptr; // device word kernels write when a bounded wait expires
     bool band_attr_set = false;   // the banded-product kernel's shared-memory limit was raised on this device
     petb200::DevBuf band_scratch; // partial sums of a banded product split over its band columns (grown on demand)
+    // Buffers band_scratch outgrew.  They stay allocated until the context goes: a CUDA graph captured while one of them
+    // was current has its address baked into its kernel nodes and may still be replayed.
+    std::vector<void *> band_retired;
+    ~petb200_ctx() {
+        for (void *p : band_retired)
+            cudaFree(p);
+    }
 };
 
 struct petb200_plan {

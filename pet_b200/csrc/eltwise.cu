@@ -185,6 +185,29 @@ __global__ void __launch_bounds__(256) k_softmax(const float *__restrict__ x, fl
     }
 }
 
+// Softmax along an axis that is not the innermost one: x viewed as [outer, len, inner], normalised over `len`.  One
+// thread per (outer, inner) column; neighbouring threads hold neighbouring `inner` positions, so every step of the walk
+// along `len` is one coalesced row of the tensor.  Same arithmetic per column as k_softmax (max, sum of exp, scale).
+__global__ void __launch_bounds__(256) k_softmax_strided(const float *__restrict__ x, float *__restrict__ y, size_t outer, int len,
+                                                         size_t inner) {
+    pdl_prologue();
+    const size_t cols = outer * inner;
+    for (size_t c = blockIdx.x * (size_t)blockDim.x + threadIdx.x; c < cols; c += (size_t)gridDim.x * blockDim.x) {
+        const size_t o = c / inner, i = c - o * inner;
+        const float *xp = x + o * (size_t)len * inner + i;
+        float *yp = y + o * (size_t)len * inner + i;
+        float mx = -INFINITY;
+        for (int l = 0; l < len; ++l)
+            mx = fmaxf(mx, __ldg(xp + (size_t)l * inner));
+        float den = 0.f;
+        for (int l = 0; l < len; ++l)
+            den += expf(__ldg(xp + (size_t)l * inner) - mx);
+        const float inv = 1.f / den;
+        for (int l = 0; l < len; ++l)
+            yp[(size_t)l * inner] = expf(__ldg(xp + (size_t)l * inner) - mx) * inv;
+    }
+}
+
 __global__ void __launch_bounds__(256) k_layernorm(const float *__restrict__ x, const float *__restrict__ gamma,
                                                    const float *__restrict__ beta, float *__restrict__ y, size_t rows,
                                                    int cols, float eps) {
@@ -393,6 +416,18 @@ extern "C" int petb200_softmax_run(petb200_ctx *ctx, const float *x, float *y, s
     }
     launch_pdl(k_softmax, grid_for(ctx, rows, 8), 256, 0, (cudaStream_t)stream, x, y, rows, cols);
     return launched(ctx, "k_softmax");
+}
+
+extern "C" int petb200_softmax_axis_run(petb200_ctx *ctx, const float *x, float *y, size_t outer, int len, size_t inner,
+                                        petb200_stream stream) {
+    if (!ctx || !x || !y || len <= 0)
+        return fail(ctx, PETB200_ERR_INVALID, "softmax_axis_run: bad arguments");
+    if (!outer || !inner)
+        return PETB200_OK;
+    if (inner == 1)
+        return petb200_softmax_run(ctx, x, y, outer, len, stream);
+    launch_pdl(k_softmax_strided, grid_for(ctx, outer * inner, 256), 256, 0, (cudaStream_t)stream, x, y, outer, len, inner);
+    return launched(ctx, "k_softmax_strided");
 }
 
 extern "C" int petb200_layernorm_run(petb200_ctx *ctx, const float *x, const float *gamma, const float *beta, float *y,

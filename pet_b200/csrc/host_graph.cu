@@ -67,6 +67,11 @@ struct Operator {
     // Leader of a group of matmuls that share their A operand and were merged into one (weights side by side along N):
     std::vector<int> merged_w, merged_b; // the members' weight / bias tensors, in column order
     int merged_out = -1, merged_wt = -1, merged_bias = -1; // the wide result, weight and bias tensors of the merged matmul
+    // Conv between a Pre/Post pair of seam transposes (H->N before, N->H after; or the W pair), folded into the conv itself:
+    // the conv reads `seam_in` (the pair's input, in the original layout) and writes the output of operator `seam_out_op`
+    // (the second transpose), both through reshaped views; 'H' or 'W', 0 = not folded.
+    char seam_axis = 0;
+    int seam_in = -1, seam_out_op = -1;
 };
 
 // One executable step after fusion.
@@ -198,8 +203,8 @@ int petb200_graph::run_step(Step &s, cudaStream_t st) {
     switch (s.type) {
     case Conv:
     case Conv3d:
-        return pass(petb200_conv_run_residual(s.plan, dev_of(this, op.inputs[0]), dev_of(this, op.bias), dev_of(this, s.residual),
-                                              dev_of(this, ops[s.ops.back()].outputs[0]), st));
+        return pass(petb200_conv_run_residual(s.plan, dev_of(this, op.seam_axis ? op.seam_in : op.inputs[0]), dev_of(this, op.bias),
+                                              dev_of(this, s.residual), dev_of(this, ops[s.ops.back()].outputs[0]), st));
     case ConvTrans:
         return pass(petb200_convtrans_run(s.plan, dev_of(this, op.inputs[0]), dev_of(this, op.bias), dev_of(this, op.outputs[0]), st));
     case G2BMM:
@@ -290,8 +295,12 @@ int petb200_graph::run_step(Step &s, cudaStream_t st) {
     }
     case Softmax: {
         const Dim &d = tensors[op.inputs[0]].dims;
-        return pass(petb200_softmax_run(ctx, dev_of(this, op.inputs[0]), dev_of(this, op.outputs[0]), tensors[op.inputs[0]].size() / d.back(),
-                                        d.back(), st));
+        size_t outer = 1, inner = 1;
+        for (int i = 0; i < op.axis; ++i)
+            outer *= (size_t)d[i];
+        for (size_t i = (size_t)op.axis + 1; i < d.size(); ++i)
+            inner *= (size_t)d[i];
+        return pass(petb200_softmax_axis_run(ctx, dev_of(this, op.inputs[0]), dev_of(this, op.outputs[0]), outer, d[op.axis], inner, st));
     }
     case LayerNorm: {
         const Dim &d = tensors[op.inputs[0]].dims;
@@ -471,6 +480,10 @@ int petb200_graph::compile(int flags) {
             if (o.type != Matmul || o.fused_away || o.mm_strided || o.inputs[0] != xt || o.transA || o.transB || o.act != 0 ||
                 !tensors[o.inputs[1]].weight || (o.bias >= 0 && !tensors[o.bias].weight) || is_output(o.outputs[0]))
                 continue;
+            // one weight matrix shared by the whole batch (the wide weight is laid out as [1, k, ntot])
+            if (tensors[o.inputs[1]].dims.size() != 3 || tensors[o.inputs[1]].dims[0] != 1)
+                continue;
+            const Dim &od = tensors[o.outputs[0]].dims; // [bs, m, ni]
             bool ok_out = !tensors[o.outputs[0]].inputOf.empty();
             for (int rc_ : tensors[o.outputs[0]].inputOf) { // every reader: Reshape -> folded transpose -> strided matmul operand
                 const Operator &r = ops[rc_];
@@ -479,6 +492,10 @@ int petb200_graph::compile(int flags) {
                     break;
                 }
                 const int R = r.outputs[0];
+                // The reshape must keep the rows of the result intact — [bs*m rows] x [row split in two] — because the
+                // readers are re-addressed by giving exactly those rows the pitch of the wide result.
+                const Dim &rd = tensors[R].dims;
+                ok_out = ok_out && rd.size() == 3 && rd[1] * rd[2] == od[2] && rd[0] == od[0] * od[1];
                 ok_out = ok_out && !is_output(R) && !tensors[R].inputOf.empty();
                 for (int tc : tensors[R].inputOf) {
                     const Operator &tr = ops[tc];
@@ -520,6 +537,80 @@ int petb200_graph::compile(int flags) {
             if (c != grp[0])
                 o.fused_away = true;
             off += ni;
+        }
+    }
+
+    // ---- fold a seam-transpose pair into the convolution between them ----
+    // PET's H->N rewrite is  TransposeOp(2, {{0,2},1,-1,3}, -2) -> Conv -> TransposeOp(0, {0,1,{-1,2},3}, 2)  (ref:
+    // src/Mutant/generator.cc:1027-1046; the pair is what markTransType labels Pre/Post, :1889-1958).  Both transposes are
+    // pure re-indexings of N and H: the contiguous [N,C,H,W] input IS the 5-D tensor [N,C,2,H/2,W], the two halves being
+    // two depth slices, so "H->N, conv2d, N->H" is one 3-D convolution with a 1 x R x S filter on that view, whose
+    // [N,F,2,OH/2,OW] result is the [N,F,OH,OW] tensor the second transpose would have produced.  The W pair
+    // (TransposeOp(3, {{0,3},1,2,-1}, -2) ... TransposeOp(0, {0,1,2,{-1,3}}, 2)) views [N,C,H,W] as [N,C,2H,W/2] — row
+    // 2h+p holds half p of row h — and becomes a 2-D convolution with the row dilation and row padding doubled (row
+    // stride 1 only).  Same products in the same order as the three-operator form; no copy, one launch.
+    auto is_tr = [&](const Operator &t, int split, int factor, std::initializer_list<int> sizes, std::initializer_list<int> flat) {
+        if (t.type != Transpose || t.fused_away || t.halo[0] || t.halo[1] || t.halo[2] || t.halo[3] || t.tr.split != split ||
+            t.tr.factor != factor || t.tr.ngroups != (int)sizes.size())
+            return false;
+        int i = 0;
+        for (int v : sizes)
+            if (t.tr.group_sizes[i++] != v)
+                return false;
+        i = 0;
+        for (int v : flat)
+            if (t.tr.flat[i++] != v)
+                return false;
+        return true;
+    };
+    for (int id = 0; id < n && fuse; ++id) {
+        Operator &op = ops[id];
+        if (op.type != Conv || op.fused_away || tensors[op.inputs[0]].dims.size() != 4)
+            continue;
+        const int pre = tensors[op.inputs[0]].outputOf, post = sole_consumer(op.outputs[0]);
+        if (pre < 0 || post < 0 || sole_consumer(op.inputs[0]) != id || tensors[ops[pre].inputs[0]].dims.size() != 4)
+            continue;
+        // Space-to-batch: D2H, H2N, D2W, W2N -> dense conv -> N2W, D2W^-1, N2H, D2H^-1 (the rewrite of a dilated conv, ref:
+        // src/Mutant/generator.cc:1085-1092) is the convolution with dilation and padding doubled on the untouched tensor:
+        // phase (p_h, p_w) of the input only ever meets phase (p_h, p_w) of the output.  Stride 1 only.
+        int pre4[4], post4[4];
+        bool ok = op.sh == 1 && op.sw == 1;
+        int t = op.inputs[0];
+        for (int i = 3; i >= 0 && ok; --i) { // walk up: W2N, D2W, H2N, D2H
+            pre4[i] = tensors[t].outputOf;
+            ok = pre4[i] >= 0 && sole_consumer(t) == (i == 3 ? id : pre4[i + 1]) && tensors[ops[pre4[i]].inputs[0]].dims.size() == 4;
+            if (ok)
+                t = ops[pre4[i]].inputs[0];
+        }
+        ok = ok && is_tr(ops[pre4[0]], 2, 2, {1, 1, 2, 1}, {0, 1, -1, 2, 3}) && is_tr(ops[pre4[1]], 2, -2, {2, 1, 1, 1}, {0, 2, 1, -1, 3}) &&
+             is_tr(ops[pre4[2]], 3, 2, {1, 1, 1, 2}, {0, 1, 2, -1, 3}) && is_tr(ops[pre4[3]], 3, -2, {2, 1, 1, 1}, {0, 3, 1, 2, -1});
+        t = op.outputs[0];
+        for (int i = 0; i < 4 && ok; ++i) { // walk down: N2W, D2W^-1, N2H, D2H^-1
+            post4[i] = sole_consumer(t);
+            ok = post4[i] >= 0;
+            if (ok)
+                t = ops[post4[i]].outputs[0];
+        }
+        ok = ok && is_tr(ops[post4[0]], 0, 2, {1, 1, 1, 2}, {0, 1, 2, -1, 3}) && is_tr(ops[post4[1]], 3, -2, {1, 1, 1, 2}, {0, 1, 2, -1, 3}) &&
+             is_tr(ops[post4[2]], 0, 2, {1, 1, 2, 1}, {0, 1, -1, 2, 3}) && is_tr(ops[post4[3]], 2, -2, {1, 1, 2, 1}, {0, 1, -1, 2, 3});
+        if (ok) {
+            op.seam_axis = 'S';
+            op.seam_in = ops[pre4[0]].inputs[0];
+            op.seam_out_op = post4[3];
+            for (int i = 0; i < 4; ++i)
+                ops[pre4[i]].fused_away = ops[post4[i]].fused_away = true;
+            continue;
+        }
+        char axis = 0;
+        if (is_tr(ops[pre], 2, -2, {2, 1, 1, 1}, {0, 2, 1, -1, 3}) && is_tr(ops[post], 0, 2, {1, 1, 2, 1}, {0, 1, -1, 2, 3}))
+            axis = 'H';
+        else if (is_tr(ops[pre], 3, -2, {2, 1, 1, 1}, {0, 3, 1, 2, -1}) && is_tr(ops[post], 0, 2, {1, 1, 1, 2}, {0, 1, 2, -1, 3}) && op.sh == 1)
+            axis = 'W';
+        if (axis) {
+            op.seam_axis = axis;
+            op.seam_in = ops[pre].inputs[0];
+            op.seam_out_op = post;
+            ops[pre].fused_away = ops[post].fused_away = true;
         }
     }
 
@@ -566,7 +657,35 @@ int petb200_graph::compile(int flags) {
                 }
             }
             const Dim &x = tensors[op.inputs[0]].dims, &w = tensors[op.inputs[1]].dims;
-            if (op.type == Conv) {
+            if (op.type == Conv && op.seam_axis) {
+                const Dim &x0 = tensors[op.seam_in].dims; // the original layout [N, C, H, W]
+                if (op.seam_axis == 'H') {
+                    int a[21] = {x0[0], x0[1], 2, x0[2] / 2, x0[3], w[0], 1, w[2], w[3], 0, op.ph, op.pw, 1, op.sh, op.sw, 1, op.dh, op.dw,
+                                 x[1] / w[1], op.bias >= 0, act};
+                    rc = petb200_conv3d_plan(ctx, a, PETB200_ALGO_AUTO, &s.plan);
+                } else if (op.seam_axis == 'W') {
+                    int a[16] = {x0[0], x0[1], 2 * x0[2], x0[3] / 2, w[0], w[2], w[3], 2 * op.ph, op.pw, 1, op.sw, 2 * op.dh, op.dw, x[1] / w[1],
+                                 op.bias >= 0, act};
+                    rc = petb200_conv2d_plan(ctx, a, PETB200_ALGO_AUTO, &s.plan);
+                } else { // space-to-batch pair: the dilated convolution itself
+                    int a[16] = {x0[0], x0[1], x0[2], x0[3], w[0], w[2], w[3], 2 * op.ph, 2 * op.pw, 1, 1, 2 * op.dh, 2 * op.dw, x[1] / w[1],
+                                 op.bias >= 0, act};
+                    rc = petb200_conv2d_plan(ctx, a, PETB200_ALGO_AUTO, &s.plan);
+                }
+                s.name = "conv_seam_folded";
+                // the step covers the transposes too (fused_away): the ones before the conv, then the ones after it, the last
+                // of which names the step's result
+                for (int t = op.inputs[0]; tensors[t].outputOf >= 0 && ops[tensors[t].outputOf].fused_away && t != op.seam_in;
+                     t = ops[tensors[t].outputOf].inputs[0])
+                    s.ops.insert(s.ops.begin() + 1, tensors[t].outputOf);
+                for (int t = op.outputs[0];;) {
+                    const int c = tensors[t].inputOf[0];
+                    s.ops.push_back(c);
+                    if (c == op.seam_out_op)
+                        break;
+                    t = ops[c].outputs[0];
+                }
+            } else if (op.type == Conv) {
                 int a[16] = {x[0], x[1], x[2], x[3], w[0], w[2], w[3], op.ph, op.pw, op.sh, op.sw, op.dh, op.dw, x[1] / w[1], op.bias >= 0, act};
                 rc = petb200_conv2d_plan(ctx, a, PETB200_ALGO_AUTO, &s.plan);
                 s.name = "conv";
@@ -1281,8 +1400,8 @@ extern "C" int petb200_graph_softmax(petb200_graph *g, int x, int axis, int *out
     const int nd = (int)g->tensors[x].dims.size();
     if (axis < 0)
         axis += nd;
-    if (axis != nd - 1) // the reference's kernel also only handles the last axis (src/Graph/code_engine.cc:1707-1731)
-        return g->fail(PETB200_ERR_UNSUPPORTED, "softmax over axis %d of %d: only the last axis is built", axis, nd);
+    if (axis < 0 || axis >= nd) // ref: SoftmaxOp::checkValid, include/operator.h:1890-1892
+        return g->fail(PETB200_ERR_INVALID, "softmax over axis %d of a %d-D tensor", axis, nd);
     Operator op;
     op.type = Softmax;
     op.inputs = {x};
@@ -1655,7 +1774,19 @@ extern "C" int petb200_graph_perf(petb200_graph *g, int rounds, int warmup, floa
                 key.insert(key.end(), op.stride3, op.stride3 + 3);
                 key.insert(key.end(), op.begin.begin(), op.begin.end());
                 key.insert(key.end(), op.end.begin(), op.end.end());
+                // what else decides the plan: 3-D dilation, strided (folded-transpose) operands, a merged wide result
+                key.insert(key.end(), op.dil3, op.dil3 + 3);
+                key.push_back((int)op.seam_axis);
+                key.push_back(op.mm_strided ? 1 : 0);
+                for (int j = 0; j < 6; ++j) {
+                    key.push_back((int)(op.mm_strides[j] & 0x7fffffff));
+                    key.push_back((int)(op.mm_strides[j] >> 31));
+                }
+                if (op.merged_out >= 0)
+                    key.insert(key.end(), g->tensors[op.merged_out].dims.begin(), g->tensors[op.merged_out].dims.end());
+                key.push_back(-7); // separator: variable-length fields above
             }
+            key.push_back(s.residual >= 0 ? 1 : 0);
             if (g->perf.check(key)) {
                 ms = g->perf.get(key);
             } else {

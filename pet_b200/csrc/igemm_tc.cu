@@ -26,6 +26,7 @@
 #include "common.h"
 #include "tc_ptx.cuh"
 #include <algorithm>
+#include <array>
 #include <cstdlib>
 #include <map>
 
@@ -1591,7 +1592,7 @@ struct TcConv {
     ConvGeom g{};
     int has_bias = 0, act = 0;
     long long ys[3] = {0, 0, 0}; // output strides {image, filter, pixel}: {F*plane, plane, 1} (NCHW) or {F*plane, 1, F} (channels last)
-    std::map<long long, TcCore *> windows; // correction windows, keyed by (oh0,ohn,ow0,own)
+    std::map<std::array<int, 4>, TcCore *> windows; // correction windows, keyed by (oh0,ohn,ow0,own)
     ~TcConv() {
         for (auto &kv : windows)
             delete kv.second;
@@ -1753,7 +1754,7 @@ int tc_conv_run(void *h, const float *x, const float *bias, const float *res, fl
     const ConvGeom &g = t->g;
     if (win[0] < 0 || win[1] <= 0 || win[0] + win[1] > g.OH || win[2] < 0 || win[3] <= 0 || win[2] + win[3] > g.OW)
         return fail(t->full.ctx, PETB200_ERR_INVALID, "correction window outside the output");
-    long long key = (((long long)win[0] * 4096 + win[1]) * 4096 + win[2]) * 4096 + win[3];
+    const std::array<int, 4> key = {win[0], win[1], win[2], win[3]};
     TcCore *&wc = t->windows[key];
     if (!wc) {
         wc = new TcCore();

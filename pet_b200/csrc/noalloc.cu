@@ -13,10 +13,14 @@
 // overlap on the same GPU (different streams, or different host threads) would write the same words and race; run
 // them one after the other.
 //
-// The first call on each device looks up the array's device address; do that first call before starting any stream
-// capture.
+// The first call on each device does the set-up: it looks up the array's device address, and — because CUDA loads a
+// library's device code lazily — it is also the moment the driver loads the module that holds the array, i.e. reserves
+// the array's 8 MiB on that GPU and possibly synchronises.  So make one call on every device you will use BEFORE entering
+// the region where allocation or synchronisation is not allowed (and before starting any stream capture); every later
+// call only launches two kernels.  The per-device address cache may be filled by several host threads at once.
 #include "../../include/petb200.h"
 #include <cuda_runtime.h>
+#include <atomic>
 #include <cstdio>
 
 namespace {
@@ -26,7 +30,8 @@ constexpr size_t kScratchFloats = PETB200_NOALLOC_SCRATCH_FLOATS;
 static __device__ __align__(256) float g_splitk_scratch[kScratchFloats];
 
 constexpr int kMaxDevices = 64;
-float *g_scratch_addr[kMaxDevices] = {nullptr}; // device address of the array, looked up once per device
+std::atomic<float *> g_scratch_addr[kMaxDevices]; // device address of the array per device (zero-initialised: not looked up yet);
+                                                   // threads that race on the first call all store the same value
 // Writes the reason into the caller's buffer (if one was given) and passes the status through.
 int fail(char *err, size_t err_len, int status, const char *fmt, const char *a = "", long long b = 0, long long c = 0) {
     if (err && err_len)
@@ -95,24 +100,26 @@ extern "C" int petb200_matmul_splitk_noalloc(int transA, int transB, int bs, int
         return fail(err, err_len, PETB200_ERR_INVALID, "matmul_splitk_noalloc: extents must be positive and 1 <= ksplit <= k%s");
     if (act < 0 || act > PETB200_ACT_GELU)
         return fail(err, err_len, PETB200_ERR_INVALID, "matmul_splitk_noalloc: unknown activation%s");
-    const long long outs = (long long)bs * m * n;
-    if (outs * ksplit > (long long)kScratchFloats)
+    // ksplit * bs * m * n against the array's size, by division: the product of four ints can overflow 64 bits' worth of
+    // caller mistakes long before it means anything
+    const long long cap = (long long)kScratchFloats;
+    if (bs > cap || m > cap / bs || n > cap / ((long long)bs * m) || ksplit > cap / ((long long)bs * m * n))
         return fail(err, err_len, PETB200_ERR_UNSUPPORTED,
-                    "matmul_splitk_noalloc:%s ksplit*b*m*n = %lld partial sums exceed the fixed scratch of %lld floats; "
+                    "matmul_splitk_noalloc:%s ksplit*b*m*n partial sums (b*m = %lld) exceed the fixed scratch of %lld floats; "
                     "use a smaller ksplit or the plan-based petb200_matmul_run",
-                    "", outs * ksplit, (long long)kScratchFloats);
+                    "", (long long)bs * m, cap);
+    const long long outs = (long long)bs * m * n;
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices)
         return fail(err, err_len, PETB200_ERR_CUDA, "matmul_splitk_noalloc: cudaGetDevice failed: %s", cudaGetErrorString(e));
-    if (!g_scratch_addr[dev]) { // once per device, with that device current
-        float *p = nullptr;
-        e = cudaGetSymbolAddress((void **)&p, g_splitk_scratch);
-        if (e != cudaSuccess || !p)
+    float *scratch = g_scratch_addr[dev].load(std::memory_order_acquire);
+    if (!scratch) { // first call on this device (with that device current): the host-side symbol is not a device address
+        e = cudaGetSymbolAddress((void **)&scratch, g_splitk_scratch);
+        if (e != cudaSuccess || !scratch)
             return fail(err, err_len, PETB200_ERR_CUDA, "matmul_splitk_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
-        g_scratch_addr[dev] = p;
+        g_scratch_addr[dev].store(scratch, std::memory_order_release);
     }
-    float *scratch = g_scratch_addr[dev];
     cudaStream_t s = (cudaStream_t)stream;
     const long long total = outs * ksplit;
     const int g1 = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);

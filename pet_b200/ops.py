@@ -464,10 +464,16 @@ class Context:
         self.check(self.lib.petb200_rowmean_run(self.h, _ptr(x), _ptr(y), rows, cols, _stream()))
         return y
 
-    def softmax(self, x):
+    def softmax(self, x, axis=-1):
+        """SoftmaxOp over `axis` (ref: include/operator.h:1887-1938)."""
         x = _f32(x)
         y = torch.empty_like(x)
-        self.check(self.lib.petb200_softmax_run(self.h, _ptr(x), _ptr(y), x.numel() // x.shape[-1], x.shape[-1], _stream()))
+        axis = axis + x.dim() if axis < 0 else axis
+        if not 0 <= axis < x.dim():
+            raise L.PetError(L.ERR_INVALID, "softmax axis out of range")
+        outer = int(np.prod(x.shape[:axis], dtype=np.int64))
+        inner = int(np.prod(x.shape[axis + 1:], dtype=np.int64))
+        self.check(self.lib.petb200_softmax_axis_run(self.h, _ptr(x), _ptr(y), outer, x.shape[axis], inner, _stream()))
         return y
 
     def layernorm(self, x, gamma=None, beta=None, eps=1e-5):

@@ -249,3 +249,35 @@ def test_banded_random_shapes_exact(ctx, oracle):
         assert np.array_equal(ctx.g2bmm(dev(q), dev(k), w, d).cpu().numpy(), oracle.g2bmm(q, k, w, d, wide=False)), (b, n, m, w, d)
         assert np.array_equal(ctx.gbmml(dev(p), dev(k), d).cpu().numpy(), oracle.gbmml(p, k, d, wide=False)), (b, n, m, w, d)
     ctx.sync_check()
+
+
+def test_captured_gbmml_graph_survives_a_later_larger_gbmml_on_the_same_context(ctx, oracle):
+    """The split-band scratch belongs to the context and grows on demand.  A graph captured while a smaller buffer was
+    current keeps that buffer's address in its kernel nodes: the buffer must stay valid when a larger product on the same
+    context makes the scratch grow."""
+    from pet_b200.graph import Graph
+    rng = np.random.default_rng(12)
+
+    def build(n, m, w):
+        g = Graph(ctx)
+        p, v = g.tensor([1, n, 2 * w + 1]), g.tensor([1, n, m])
+        y = g.gbmml(p, v, 1)
+        g.setOutputs([y])
+        g.compile()
+        pa = rng.integers(-3, 4, (1, n, 2 * w + 1)).astype(np.float32)   # small integers: exact, whatever the split order
+        va = rng.integers(-3, 4, (1, n, m)).astype(np.float32)
+        g.set_data(p, pa)
+        g.set_data(v, va)
+        g.run()
+        g.run()  # replay of the captured CUDA graph
+        torch.cuda.synchronize()
+        return g, y, oracle.gbmml(pa, va, 1, wide=False)
+
+    g1, y1, want1 = build(700, 64, 400)          # a band wide enough to be split over blocks: uses the scratch
+    assert np.array_equal(g1.get_data(y1), want1)
+    g2, y2, want2 = build(5000, 64, 1200)        # a much larger product on the same context: the scratch grows
+    assert np.array_equal(g2.get_data(y2), want2)
+    g1.run()                                     # the first graph again, with the buffer address it captured
+    torch.cuda.synchronize()
+    ctx.sync_check()
+    assert np.array_equal(g1.get_data(y1), want1)

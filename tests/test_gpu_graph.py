@@ -40,8 +40,12 @@ def test_c1_rewrite_with_correction_is_bit_identical_to_original(ctx):
     _, _, y2 = run_config(ctx, configs.c1_rewrite, x, w, correct=False)
     bad = np.unique(np.nonzero(y0 != y2)[2])
     assert list(bad) == [27, 28]
-    names = [n for n, _ in g.steps()]
-    assert names == ["transpose", "conv", "transpose", "correction"]
+    # both seam transposes are folded into the convolution (a 1x3x3 convolution on the [1,64,2,28,56] view of the input):
+    # the rewrite plus its correction is two launches
+    assert [n for n, _ in g.steps()] == ["conv_seam_folded", "correction"] and g.num_launches() == 2
+    g3, _, y3 = run_config(ctx, configs.c1_rewrite, x, w, correct=True, fuse=False, cuda_graph=False)
+    assert [n for n, _ in g3.steps()] == ["transpose", "conv", "transpose", "correction"]
+    assert np.array_equal(y1, y3)  # operator by operator: the same bits
     want = oracle_config(configs.c1_original, x, w)
     assert rel_err(y0, want) <= TOL and scale_err(y0, want) <= TOL_SCALE
 
@@ -92,11 +96,12 @@ def test_c2_rewrite_fuses_chains_and_matches_original(ctx):
     x, w = configs.c2_tensors(c=64, hw=32, k=96)
     _, _, y0 = run_config(ctx, configs.c2_original, x, w)
     g, _, y1 = run_config(ctx, configs.c2_rewrite, x, w)
-    assert [n for n, _ in g.steps()] == ["transpose_chain", "conv", "transpose_chain"]
-    assert g.num_launches() == 3
+    # space-to-batch, dense conv, batch-to-space: folded back into the dilated convolution on the untouched tensor
+    assert [n for n, _ in g.steps()] == ["conv_seam_folded"] and g.num_launches() == 1
     assert np.array_equal(y0, y1)
-    _, _, y2 = run_config(ctx, configs.c2_rewrite, x, w, fuse=False, cuda_graph=False)
-    assert np.array_equal(y1, y2)  # 9 kernels op by op give the same bits as 3 fused ones
+    g2, _, y2 = run_config(ctx, configs.c2_rewrite, x, w, fuse=False, cuda_graph=False)
+    assert g2.num_launches() == 9
+    assert np.array_equal(y1, y2)  # 9 kernels op by op give the same bits as the folded one
     want = oracle_config(configs.c2_rewrite, x, w)
     assert rel_err(y1, want) <= TOL and scale_err(y1, want) <= TOL_SCALE
 
@@ -209,9 +214,9 @@ def test_convtrans_and_banded_attention_in_a_graph(ctx, oracle, phases, monkeypa
 def test_perf_and_time_entry_points(ctx):
     from pet_b200 import configs
     x, w = configs.c2_tensors(c=64, hw=32, k=64)
-    g, _, _ = run_config(ctx, configs.c2_rewrite, x, w)
+    g, _, _ = run_config(ctx, configs.c2_rewrite, x, w, fuse=False)   # nine operators, one step each
     total, per = g.perf(rounds=20, warmup=5)
-    assert len(per) == 3 and all(p > 0 for p in per) and abs(total - sum(per)) < 1e-4
+    assert len(per) == 9 and all(p > 0 for p in per) and abs(total - sum(per)) < 1e-4
     total2, per2 = g.perf(rounds=20, warmup=5)
     assert per2 == per  # second call is served from the memo table
     ms = g.time(rounds=50, warmup=10)
@@ -233,7 +238,7 @@ def test_graph_rejects_invalid_operators(ctx):
     with pytest.raises(PetError):
         g.reshape(x, [5, -1])
     with pytest.raises(PetError):
-        g.softmax(x, 1)                                  # only the last axis is built
+        g.softmax(x, 4)                                  # axis outside the tensor
     with pytest.raises(PetError):
         g.convTrans(x, g.tensor([3, 3, 8, 4]), 1, 1, 1, 1, 2, 2)  # dilated transposed convolution
     with pytest.raises(PetError):
@@ -299,3 +304,61 @@ def test_random_encoder_graphs_fused_vs_unfused_vs_oracle(ctx):
         _, _, y2 = run_config(ctx, configs.bert_encoder, fuse=False, cuda_graph=False, **kw)
         assert rel_err(y, y2) <= TOL, kw  # two summation orders of the same products, compounded over the layers
         assert rel_err(y, oracle_config(configs.bert_encoder, **kw)) <= TOL, kw
+
+
+def test_softmax_over_any_axis(ctx, oracle):
+    """SoftmaxOp carries an axis (ref: include/operator.h:1887-1938): every axis of a ragged 4-D tensor, through the operator
+    entry point and through a graph, against the oracle."""
+    from pet_b200.graph import Graph
+    rng = np.random.default_rng(8)
+    x = (rng.standard_normal((3, 5, 7, 9)) * 3).astype(np.float32)
+    for axis in (0, 1, 2, 3, -2):
+        want = oracle.softmax(x, axis)
+        got = ctx.softmax(torch.from_numpy(x).cuda(), axis).cpu().numpy()
+        assert rel_err(got, want) <= 1e-5, axis
+        assert np.allclose(got.sum(axis), 1.0, atol=1e-5)
+        g = Graph(ctx)
+        t = g.tensor(list(x.shape))
+        y = g.softmax(t, axis)
+        g.setOutputs([y])
+        g.compile()
+        g.set_data(t, x)
+        g.run()
+        torch.cuda.synchronize()
+        assert np.array_equal(g.get_data(y), got)
+    ctx.sync_check()
+
+
+@pytest.mark.parametrize("case", [("H", (2, 16, 28, 24), (24, 16, 3, 3), dict(ph=1, pw=1)),
+                                  ("H", (1, 8, 20, 12), (8, 8, 3, 3), dict(ph=2, pw=2, dh=2, dw=2)),          # dilated
+                                  ("H", (1, 8, 24, 16), (16, 4, 3, 3), dict(ph=1, pw=1, sh=2, sw=2)),         # strided, 2 groups
+                                  ("W", (2, 16, 12, 40), (24, 16, 3, 3), dict(ph=1, pw=1)),
+                                  ("W", (1, 8, 10, 32), (8, 8, 5, 3), dict(ph=2, pw=1, sw=2))],
+                         ids=["H", "H_dilated", "H_strided_grouped", "W", "W_5x3_stride_w"])
+def test_seam_transpose_pair_folds_into_the_conv_bit_for_bit(ctx, case):
+    """Pre transpose -> conv -> Post transpose (the H or the W pair of the reference's generator) as one launch on a view
+    of the untouched tensor, against the three operators executed one by one: small integers, so equality is exact
+    whatever tile shapes the two plans pick."""
+    from pet_b200 import configs
+    from pet_b200.graph import Graph
+    axis, xs, ws, kw = case
+    rng = np.random.default_rng(len(xs) + xs[2])
+    x = rng.integers(-4, 5, xs).astype(np.float32)
+    w = rng.integers(-3, 4, ws).astype(np.float32)
+    pre, post = (configs.H2N, configs.N2H) if axis == "H" else (configs.W2N, configs.N2W)
+    outs = []
+    for fuse in (True, False):
+        g = Graph(ctx)
+        xi, wi = g.tensor(list(xs)), g.tensor(list(ws), weight=True)
+        y = g.transpose(g.conv(g.transpose(xi, *pre), wi, kw["ph"], kw["pw"], kw.get("sh", 1), kw.get("sw", 1), kw.get("dh", 1), kw.get("dw", 1)), *post)
+        g.setOutputs([y])
+        g.compile(fuse=fuse, cuda_graph=False)
+        g.set_data(xi, x)
+        g.set_data(wi, w)
+        g.run()
+        torch.cuda.synchronize()
+        ctx.sync_check()
+        names = [n for n, _ in g.steps()]
+        assert names == (["conv_seam_folded"] if fuse else ["transpose", "conv", "transpose"])
+        outs.append(g.get_data(y))
+    assert outs[0].shape == outs[1].shape and np.array_equal(outs[0], outs[1])

@@ -1,6 +1,6 @@
 """GPU: the allocation-free matmul entry point, for callers that may not allocate device memory (no context, no plan;
 its only scratch is a fixed array inside the library).  Checked through the C ABI against the plan-based entry point
-on two calls in a row — the second with other shapes and data, so anything left in the shared array by the first call
+and against the CPU oracle on two calls in a row — the second with other shapes and data, so anything left in the shared array by the first call
 would show.  Collected last on purpose: a failure here leaves every other test already run."""
 import ctypes as C
 
@@ -23,7 +23,7 @@ def call(lib, a, b, bias, transA, transB, bs, m, n, k, ksplit, act):
     return rc, err.value.decode(), c
 
 
-def test_two_calls_in_a_row_match_the_plan_based_entry_point(ctx):
+def test_two_calls_in_a_row_match_the_plan_based_entry_point(ctx, oracle):
     from pet_b200 import lib as L
     lib = L.load()
     g = torch.Generator().manual_seed(77)
@@ -41,6 +41,13 @@ def test_two_calls_in_a_row_match_the_plan_based_entry_point(ctx):
         torch.cuda.synchronize()
         assert rel_err(got.cpu().numpy(), want.cpu().numpy()) <= TOL
         assert scale_err(got.cpu().numpy(), want.cpu().numpy()) <= TOL_SCALE
+        # and against the oracle: the sums themselves (no activation) under the contract metric, then the activation as a
+        # function of those sums
+        rc, msg, lin = call(lib, a, bm, bias, ta, tb, b, m, n, k, ks, L.ACT["none"])
+        assert rc == 0, msg
+        ref = oracle.matmul(a.cpu().numpy(), bm.cpu().numpy(), bias.cpu().numpy(), ta, tb, wide=True)
+        assert rel_err(lin.cpu().numpy(), ref) <= TOL
+        assert np.allclose(got.cpu().numpy(), oracle.activation(lin.cpu().numpy(), act), rtol=2e-6, atol=2e-7)
 
 
 def test_sizes_beyond_the_fixed_array_are_rejected():
