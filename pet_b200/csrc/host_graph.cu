@@ -612,6 +612,24 @@ int petb200_graph::compile(int flags) {
             op.seam_out_op = post;
             ops[pre].fused_away = ops[post].fused_away = true;
         }
+        // H pair followed by the correction of its seam: when the correction window holds every output row the split got
+        // wrong (rows of the upper half whose filter reaches into the lower half, rows of the lower half whose filter
+        // reaches back up), rewrite + correction IS the unsplit convolution on the untouched tensor — one launch.
+        const int cor = axis == 'H' ? sole_consumer(ops[post].outputs[0]) : -1;
+        if (cor >= 0 && ops[cor].type == Correction && !ops[cor].fused_away) {
+            const Operator &c = ops[cor];
+            const Dim &x0 = tensors[op.seam_in].dims, &wd = tensors[op.inputs[1]].dims, &od = tensors[c.outputs[0]].dims;
+            const int half = x0[2] / 2, ohh = od[2] / 2, r = wd[2];
+            const int top_first = std::max(0, (half + op.ph - (r - 1) * op.dh + op.sh - 1) / op.sh);
+            const int bottom_end = ohh + (op.ph + op.sh - 1) / op.sh;
+            if (c.inputs[0] == op.seam_in && c.inputs[1] == op.inputs[1] && c.inputs[2] == ops[post].outputs[0] && c.bias == op.bias &&
+                c.ph == op.ph && c.pw == op.pw && c.sh == op.sh && c.sw == op.sw && c.dh == op.dh && c.dw == op.dw && c.act == op.act &&
+                ohh * op.sh == half && c.win[2] == 0 && c.win[3] == od[3] && c.win[0] <= top_first && c.win[0] + c.win[1] >= bottom_end) {
+                op.seam_axis = 'X';
+                op.seam_out_op = cor;
+                ops[cor].fused_away = true;
+            }
+        }
     }
 
     // ---- build steps with fusion ----
@@ -667,12 +685,16 @@ int petb200_graph::compile(int flags) {
                     int a[16] = {x0[0], x0[1], 2 * x0[2], x0[3] / 2, w[0], w[2], w[3], 2 * op.ph, op.pw, 1, op.sw, 2 * op.dh, op.dw, x[1] / w[1],
                                  op.bias >= 0, act};
                     rc = petb200_conv2d_plan(ctx, a, PETB200_ALGO_AUTO, &s.plan);
+                } else if (op.seam_axis == 'X') { // H pair + its correction: the unsplit convolution
+                    int a[16] = {x0[0], x0[1], x0[2], x0[3], w[0], w[2], w[3], op.ph, op.pw, op.sh, op.sw, op.dh, op.dw, x[1] / w[1], op.bias >= 0,
+                                 act};
+                    rc = petb200_conv2d_plan(ctx, a, PETB200_ALGO_AUTO, &s.plan);
                 } else { // space-to-batch pair: the dilated convolution itself
                     int a[16] = {x0[0], x0[1], x0[2], x0[3], w[0], w[2], w[3], 2 * op.ph, 2 * op.pw, 1, 1, 2 * op.dh, 2 * op.dw, x[1] / w[1],
                                  op.bias >= 0, act};
                     rc = petb200_conv2d_plan(ctx, a, PETB200_ALGO_AUTO, &s.plan);
                 }
-                s.name = "conv_seam_folded";
+                s.name = op.seam_axis == 'X' ? "conv_seam_healed" : "conv_seam_folded";
                 // the step covers the transposes too (fused_away): the ones before the conv, then the ones after it, the last
                 // of which names the step's result
                 for (int t = op.inputs[0]; tensors[t].outputOf >= 0 && ops[tensors[t].outputOf].fused_away && t != op.seam_in;

@@ -563,6 +563,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         bool ok = true, ready_next = false;
         const int FLm = P.fl;
         int gpos = 0, gidx = 0; // position of the stage inside its flush group, index of the group
+        bool cross_prepaid = false; // the current stage's cross-term MMAs were issued ahead, during the previous stage
         for (int ks = 0; ks < KS; ++ks) {
             if (!ready_next) { // not already seen complete by the poll issued in the shadow of the previous stage's MMAs
                 if (P.prof) {
@@ -622,7 +623,16 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             // First stage of a new flush group: the main accumulator restarts from zero, but only after the transform warps
             // have drained the previous group's sum.  The stage's eight cross-term MMAs do not touch the main accumulator
             // and are issued first, so the tensor pipe has work while the drain is in flight.
+            auto issue_main_only = [&](int kk) {
+                ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, 1u);
+                if (kk == 0 && prev_sa >= 0) {
+                    ptx::mma_commit(a_empty + prev_sa);
+                    ptx::mma_commit(b_empty + prev_sb);
+                }
+            };
             const bool group_start = PASSES == 3 && FLm > 0 && ks > 0 && gpos == 0; // (no division: this warp's loop is latency bound)
+            const bool prepaid_now = cross_prepaid;
+            cross_prepaid = false;
             if (group_start) {
                 const uint64_t blo = bhi + b_half16;
                 if (ptx::elect_one()) {
@@ -637,6 +647,24 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                     }
                 }
                 __syncwarp();
+                // ... and, if the stage after this one is already there, its eight cross-term MMAs as well: 2 x 8 MMAs of
+                // cover for the drain (that stage then only issues its four main MMAs)
+                bool pre = (ks + 1 < KS) && FLm >= 2 && ptx::mbar_test_wait(a_full + nsa, npa) && ptx::mbar_test_wait(b_full + nsb, npb);
+                pre = __all_sync(0xffffffffu, pre);
+                if (pre) {
+                    ptx::tc_fence_after();
+                    const uint64_t nbhi = bdesc0 + (uint64_t)((uint32_t)nsb * 2u * b_half16), nblo = nbhi + b_half16;
+                    const uint32_t nahi = tmem_base + (uint32_t)P.a_col + (uint32_t)nsa * 64u, nalo = nahi + 32u;
+                    if (ptx::elect_one()) {
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            ptx::mma_tf32_ts(tmem_small, nahi + kk * 8, nblo + 2 * kk, idesc, 1u);
+                            ptx::mma_tf32_ts(tmem_small, nalo + kk * 8, nbhi + 2 * kk, idesc, 1u);
+                        }
+                    }
+                    __syncwarp();
+                    cross_prepaid = true;
+                }
                 const long long qf0 = P.prof ? clock64() : 0;
                 ok = ptx::mbar_wait(flushed, (uint32_t)((gidx - 1) & 1), abort_flag);
                 if (P.prof)
@@ -649,6 +677,13 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
 #pragma unroll
                     for (int kk = 0; kk < 3; ++kk)
                         ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, kk == 0 ? 0u : 1u);
+                }
+                __syncwarp();
+            } else if (prepaid_now) { // the cross terms of this stage were issued with the previous stage's
+                if (ptx::elect_one()) {
+#pragma unroll
+                    for (int kk = 0; kk < 3; ++kk)
+                        issue_main_only(kk);
                 }
                 __syncwarp();
             } else {
@@ -667,6 +702,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             if (ptx::elect_one()) {
                 if (group_start)
                     ptx::mma_tf32_ts(tmem_base, ahi_t + 24, bhi + 6, idesc, 1u);
+                else if (prepaid_now)
+                    issue_main_only(3);
                 else
                     issue_step(3);
                 if (group_end) // fires once every MMA of the group has completed
@@ -1329,7 +1366,11 @@ static void choose_flush(TcCore &core) {
     const int period = env_int("PETB200_TC_FLUSH", 8);
     const int ks_max = ((P.nchunks + P.ksplit - 1) / P.ksplit) * P.spc;
     P.fl = (!core.single_pass && core.a_tmem && period > 0 && ks_max > 2 * period) ? period : 0;
-    P.fl_regs = (P.fl > 0 && P.BN == 128 && env_int("PETB200_TC_FLUSH_REGS", 1)) ? 1 : 0;
+    // register totals make one transform set do all the A stages: only where the gather is the cheap kind (whole 32-channel
+    // stages of one tap, or row-major matmul tiles); slower gathers need both sets and keep the total in TMEM
+    const bool fast_gather = P.a_kmajor || (P.cstride != 0 && P.gruns == 1);
+    const int regs_env = env_int("PETB200_TC_FLUSH_REGS", -1);
+    P.fl_regs = (P.fl > 0 && P.BN == 128 && (regs_env < 0 ? fast_gather : regs_env != 0)) ? 1 : 0;
     P.a_col = (P.fl > 0 && P.BN == 128 && !P.fl_regs) ? 384 : 256;
     if (core.a_tmem)
         P.NA = (512 - P.a_col) / 64;
@@ -1551,9 +1592,9 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     if (!have)
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "raw activation tile does not fit shared memory");
     P = bestP;
-    choose_flush(core);
     P.gruns = P.BC % kStageK == 0 ? 1 : (P.BC == 16 ? 2 : (P.BC == 8 ? 4 : 0));
     P.cstride = (P.gruns && env_int("PETB200_TC_TABLE", 0) == 0) ? P.RD * P.RH * P.RW : 0;
+    choose_flush(core);
     if (flat && (!core.a_tmem || (long long)P.RN * P.BC * P.RD * P.RH * P.RW >= (1 << 24)))
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "flat raw tiles need the TS kernel variant");
     const int BN = P.BN;

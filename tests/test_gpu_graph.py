@@ -40,9 +40,18 @@ def test_c1_rewrite_with_correction_is_bit_identical_to_original(ctx):
     _, _, y2 = run_config(ctx, configs.c1_rewrite, x, w, correct=False)
     bad = np.unique(np.nonzero(y0 != y2)[2])
     assert list(bad) == [27, 28]
-    # both seam transposes are folded into the convolution (a 1x3x3 convolution on the [1,64,2,28,56] view of the input):
-    # the rewrite plus its correction is two launches
-    assert [n for n, _ in g.steps()] == ["conv_seam_folded", "correction"] and g.num_launches() == 2
+    # The seam transposes fold into the convolution (a 1x3x3 convolution on the [1,64,2,28,56] view of the input), and
+    # because the correction window holds every row the split gets wrong, rewrite + correction is recognised as the
+    # unsplit convolution: one launch.  With a window that misses one of those rows the correction stays its own launch.
+    assert [n for n, _ in g.steps()] == ["conv_seam_healed"] and g.num_launches() == 1
+
+    def partial(b, x, w):
+        xi, wi = b.input(x), b.const(w)
+        y = b.transpose(b.conv(b.transpose(xi, *configs.H2N), wi, 1, 1), *configs.N2H)
+        return b.correction(xi, wi, y, 1, 1, rows=(27, 1))   # row 28 stays wrong
+    g4, _, y4 = run_config(ctx, partial, x, w)
+    assert [n for n, _ in g4.steps()] == ["conv_seam_folded", "correction"] and g4.num_launches() == 2
+    assert list(np.unique(np.nonzero(y0 != y4)[2])) == [28]
     g3, _, y3 = run_config(ctx, configs.c1_rewrite, x, w, correct=True, fuse=False, cuda_graph=False)
     assert [n for n, _ in g3.steps()] == ["transpose", "conv", "transpose", "correction"]
     assert np.array_equal(y1, y3)  # operator by operator: the same bits
