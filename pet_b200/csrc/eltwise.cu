@@ -66,6 +66,71 @@ __global__ void __launch_bounds__(256) k_batchnorm(const float *__restrict__ x, 
     }
 }
 
+// The same with one (outer, channel) plane per block iteration: scale / sqrt(var + eps) — a double-precision division and
+// square root — is formed once per plane instead of once per element, and the plane is streamed with coalesced accesses.
+__global__ void __launch_bounds__(256) k_batchnorm_plane(const float *__restrict__ x, const float *__restrict__ scale,
+                                                         const float *__restrict__ bias, const float *__restrict__ mean,
+                                                         const float *__restrict__ var, float *__restrict__ y, size_t planes, int c,
+                                                         size_t inner, float eps) {
+    pdl_prologue();
+    for (size_t p = blockIdx.x; p < planes; p += gridDim.x) {
+        const int cc = (int)(p % (size_t)c);
+        const double k = (double)__ldg(scale + cc) / sqrt((double)__ldg(var + cc) + (double)eps);
+        const double m = (double)__ldg(mean + cc), b = (double)__ldg(bias + cc);
+        const float *xp = x + p * inner;
+        float *yp = y + p * inner;
+        for (size_t i = threadIdx.x; i < inner; i += 256)
+            yp[i] = (float)(((double)__ldg(xp + i) - m) * k + b);
+    }
+}
+
+// Pooling with small windows, the input rows of a band of output rows staged in shared memory: the band is one contiguous
+// run of the plane, so it is fetched with fully coalesced loads once, and the window walks (strided, overlapping) hit
+// shared memory instead of L1.  blockIdx.x = band of `ohb` output rows, blockIdx.y walks the planes.
+__global__ void __launch_bounds__(256) k_pool2d_tiled(int kind, const float *__restrict__ x, float *__restrict__ y, int nc, int h,
+                                                      int w, int oh, int ow, int kh, int kw, int ph, int pw, int sh, int sw,
+                                                      int ohb, int rows_in) {
+    pdl_prologue();
+    extern __shared__ __align__(16) float tile[];
+    const int o0 = blockIdx.x * ohb, on = min(ohb, oh - o0);
+    const int y0 = o0 * sh - ph;                        // first input row of the band (may be negative: padding)
+    const int ylo = max(y0, 0), yhi = min(y0 + rows_in, h); // rows that exist
+    const int count = max(yhi - ylo, 0) * w;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int plane = blockIdx.y; plane < nc; plane += gridDim.y) {
+        const float *src = x + ((size_t)plane * h + ylo) * w;
+        float *dst = tile + (ylo - y0) * w;
+        // 16-byte copies need BOTH ends aligned: the global run and its place in the tile (rows skipped as padding shift it)
+        if ((((uintptr_t)src) & 15) == 0 && (count & 3) == 0 && ((((ylo - y0) * w) & 3) == 0)) {
+            for (int i = threadIdx.x; i < count / 4; i += 256)
+                reinterpret_cast<float4 *>(dst)[i] = __ldg(reinterpret_cast<const float4 *>(src) + i);
+        } else {
+            for (int i = threadIdx.x; i < count; i += 256)
+                dst[i] = __ldg(src + i);
+        }
+        __syncthreads();
+        for (int ii = warp; ii < on; ii += 8) {
+            for (int j = lane; j < ow; j += 32) {
+                // the window clipped to the input once, then two plain loops
+                const int ys = (o0 + ii) * sh - ph, xs = j * sw - pw;
+                const int a0 = max(0, -ys), a1 = min(kh, h - ys), b0 = max(0, -xs), b1 = min(kw, w - xs);
+                float best = -INFINITY, acc = 0.f;
+                for (int a = a0; a < a1; ++a) {
+                    const float *row = tile + (ys + a - y0) * w + xs;
+                    for (int b = b0; b < b1; ++b) {
+                        const float v = row[b];
+                        best = fmaxf(best, v);
+                        acc += v;
+                    }
+                }
+                const int cnt = max(a1 - a0, 0) * max(b1 - b0, 0);
+                y[((size_t)plane * oh + o0 + ii) * ow + j] = kind == 0 ? best : (cnt ? acc / (float)cnt : 0.f);
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // One thread per output; blockIdx.z walks the (image, channel) planes and a 32x8 thread block covers a patch of one
 // plane's outputs, so there is no division anywhere and neighbouring threads read neighbouring inputs.
 __global__ void __launch_bounds__(256) k_pool2d(int kind, const float *__restrict__ x, float *__restrict__ y, int nc,
@@ -146,6 +211,37 @@ __global__ void __launch_bounds__(256) k_pool2d_warp(int kind, const float *__re
     }
 }
 
+// Short rows (global average pooling of 7x7 planes: 49 values): a block stages `rb` whole rows — one contiguous run of the
+// tensor — in shared memory with coalesced loads, then every thread adds up one row.  Thread r starts at column r so that
+// the threads of a warp hit different banks whatever the row length.
+__global__ void __launch_bounds__(256) k_rowmean_staged(const float *__restrict__ x, float *__restrict__ y, size_t rows, int cols, int rb) {
+    pdl_prologue();
+    extern __shared__ __align__(16) float stage[];
+    for (size_t r0 = (size_t)blockIdx.x * rb; r0 < rows; r0 += (size_t)gridDim.x * rb) {
+        const int nr = (int)min((size_t)rb, rows - r0), count = nr * cols;
+        const float *src = x + r0 * (size_t)cols;
+        if ((((uintptr_t)src) & 15) == 0 && (count & 3) == 0) {
+            for (int i = threadIdx.x; i < count / 4; i += 256)
+                reinterpret_cast<float4 *>(stage)[i] = __ldg(reinterpret_cast<const float4 *>(src) + i);
+        } else {
+            for (int i = threadIdx.x; i < count; i += 256)
+                stage[i] = __ldg(src + i);
+        }
+        __syncthreads();
+        for (int r = threadIdx.x; r < nr; r += 256) {
+            const float *row = stage + r * cols;
+            float s = 0.f;
+            int c = r % cols;
+            for (int i = 0; i < cols; ++i) {
+                s += row[c];
+                c = c + 1 == cols ? 0 : c + 1;
+            }
+            y[r0 + r] = s / (float)cols;
+        }
+        __syncthreads();
+    }
+}
+
 // One warp per row; rows are short (<= a few thousand) in every PET workload, so the row stays in registers/L1.
 __global__ void __launch_bounds__(256) k_rowmean(const float *__restrict__ x, float *__restrict__ y, size_t rows, int cols) {
     pdl_prologue();
@@ -160,6 +256,85 @@ __global__ void __launch_bounds__(256) k_rowmean(const float *__restrict__ x, fl
         s = warp_sum(s);
         if (lane == 0)
             y[r] = s / (float)cols;
+    }
+}
+
+// Rows of at most 32 * NPL values: one warp per row keeps the row in registers, so the tensor is read once and written
+// once (8 bytes per element) and every exponential is evaluated once.  Same sums in the same order as k_softmax below.
+template <int NPL>
+__global__ void __launch_bounds__(256) k_softmax_reg(const float *__restrict__ x, float *__restrict__ y, size_t rows, int cols) {
+    pdl_prologue();
+    const size_t warp = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    for (size_t r = warp; r < rows; r += nwarps) {
+        const float *xp = x + r * (size_t)cols;
+        float *yp = y + r * (size_t)cols;
+        float v[NPL];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) {
+            const int c = lane + 32 * i;
+            v[i] = c < cols ? __ldg(xp + c) : -INFINITY;
+            mx = fmaxf(mx, v[i]);
+        }
+        mx = warp_max(mx);
+        float den = 0.f;
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) {
+            const int c = lane + 32 * i;
+            v[i] = c < cols ? expf(v[i] - mx) : 0.f;
+            den += v[i];
+        }
+        den = warp_sum(den);
+        const float inv = 1.f / den;
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) {
+            const int c = lane + 32 * i;
+            if (c < cols)
+                yp[c] = v[i] * inv;
+        }
+    }
+}
+
+template <int NPL>
+__global__ void __launch_bounds__(256) k_layernorm_reg(const float *__restrict__ x, const float *__restrict__ gamma,
+                                                       const float *__restrict__ beta, float *__restrict__ y, size_t rows, int cols,
+                                                       float eps) {
+    pdl_prologue();
+    const size_t warp = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    for (size_t r = warp; r < rows; r += nwarps) {
+        const float *xp = x + r * (size_t)cols;
+        float *yp = y + r * (size_t)cols;
+        float v[NPL];
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) {
+            const int c = lane + 32 * i;
+            v[i] = c < cols ? __ldg(xp + c) : 0.f;
+            s += v[i];
+        }
+        const float mean = warp_sum(s) / (float)cols;
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) {
+            const int c = lane + 32 * i;
+            const float d = c < cols ? v[i] - mean : 0.f;
+            q += d * d;
+        }
+        const float inv = rsqrtf(warp_sum(q) / (float)cols + eps);
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) {
+            const int c = lane + 32 * i;
+            if (c < cols) {
+                float o = (v[i] - mean) * inv;
+                if (gamma)
+                    o *= __ldg(gamma + c);
+                if (beta)
+                    o += __ldg(beta + c);
+                yp[c] = o;
+            }
+        }
     }
 }
 
@@ -185,26 +360,46 @@ __global__ void __launch_bounds__(256) k_softmax(const float *__restrict__ x, fl
     }
 }
 
-// Softmax along an axis that is not the innermost one: x viewed as [outer, len, inner], normalised over `len`.  One
-// thread per (outer, inner) column; neighbouring threads hold neighbouring `inner` positions, so every step of the walk
-// along `len` is one coalesced row of the tensor.  Same arithmetic per column as k_softmax (max, sum of exp, scale).
+// Softmax along an axis that is not the innermost one: x viewed as [outer, len, inner], normalised over `len`.  A 32 x 8
+// block owns 32 neighbouring `inner` positions of one `outer` index: threadIdx.x walks `inner` (every access of a warp is
+// one contiguous 128-byte piece of a row), the 8 values of threadIdx.y split `len`, and the maxima / sums of the 8 parts
+// meet in shared memory.  Per column the same arithmetic as k_softmax: max, sum of exp(x - max), scale.
 __global__ void __launch_bounds__(256) k_softmax_strided(const float *__restrict__ x, float *__restrict__ y, size_t outer, int len,
                                                          size_t inner) {
     pdl_prologue();
-    const size_t cols = outer * inner;
-    for (size_t c = blockIdx.x * (size_t)blockDim.x + threadIdx.x; c < cols; c += (size_t)gridDim.x * blockDim.x) {
-        const size_t o = c / inner, i = c - o * inner;
+    __shared__ float red[8][33];
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    const size_t tiles_in = (inner + 31) / 32, tiles = outer * tiles_in;
+    for (size_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const size_t o = t / tiles_in, i = (t - o * tiles_in) * 32 + tx;
+        const bool live = i < inner;
         const float *xp = x + o * (size_t)len * inner + i;
         float *yp = y + o * (size_t)len * inner + i;
         float mx = -INFINITY;
-        for (int l = 0; l < len; ++l)
-            mx = fmaxf(mx, __ldg(xp + (size_t)l * inner));
+        if (live)
+            for (int l = ty; l < len; l += 8)
+                mx = fmaxf(mx, __ldg(xp + (size_t)l * inner));
+        red[ty][tx] = mx;
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            mx = fmaxf(mx, red[k][tx]);
+        __syncthreads();
         float den = 0.f;
-        for (int l = 0; l < len; ++l)
-            den += expf(__ldg(xp + (size_t)l * inner) - mx);
+        if (live)
+            for (int l = ty; l < len; l += 8)
+                den += expf(__ldg(xp + (size_t)l * inner) - mx);
+        red[ty][tx] = den;
+        __syncthreads();
+        den = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            den += red[k][tx];
+        __syncthreads();
         const float inv = 1.f / den;
-        for (int l = 0; l < len; ++l)
-            yp[(size_t)l * inner] = expf(__ldg(xp + (size_t)l * inner) - mx) * inv;
+        if (live)
+            for (int l = ty; l < len; l += 8)
+                yp[(size_t)l * inner] = expf(__ldg(xp + (size_t)l * inner) - mx) * inv;
     }
 }
 
@@ -370,6 +565,12 @@ extern "C" int petb200_batchnorm_run(petb200_ctx *ctx, const float *x, const flo
     size_t total = outer * (size_t)c * inner;
     if (!total)
         return PETB200_OK;
+    if (inner >= 256) {
+        const size_t planes = outer * (size_t)c;
+        launch_pdl(k_batchnorm_plane, (int)std::min<size_t>(planes, (size_t)ctx->sm_count * 16), 256, 0, (cudaStream_t)stream, x, scale, bias, mean,
+                   var, y, planes, c, inner, eps);
+        return launched(ctx, "k_batchnorm_plane");
+    }
     launch_pdl(k_batchnorm, grid_for(ctx, total, 256), 256, 0, (cudaStream_t)stream, x, scale, bias, mean, var, y, total, c,
                                                                              inner, eps);
     return launched(ctx, "k_batchnorm");
@@ -384,6 +585,18 @@ extern "C" int petb200_pool2d_run(petb200_ctx *ctx, int kind, const float *x, fl
     if (oh <= 0 || ow <= 0)
         return fail(ctx, PETB200_ERR_INVALID, "pool2d_run: empty output");
     size_t total = (size_t)n * c * oh * ow;
+    if (kind == 1 && kh == h && kw == w && ph == 0 && pw == 0) // global average: the mean of each contiguous plane
+        return petb200_rowmean_run(ctx, x, y, (size_t)n * c, h * w, stream);
+    if (kh * kw < 32) { // small windows: stage a band of input rows in shared memory when one fits in 24 KB
+        const int ohb = std::min(16, (6144 / w - kh) / sh + 1);
+        if (ohb >= 1) {
+            const int rows_in = (ohb - 1) * sh + kh;
+            launch_pdl(k_pool2d_tiled, dim3((unsigned)((oh + ohb - 1) / ohb), (unsigned)std::min(n * c, 16384)), dim3(256),
+                       (size_t)rows_in * w * sizeof(float), (cudaStream_t)stream, kind, x, y, n * c, h, w, oh, ow, kh, kw, ph, pw, sh, sw, ohb,
+                       rows_in);
+            return launched(ctx, "k_pool2d_tiled");
+        }
+    }
     if (kh * kw >= 32) {
         launch_pdl(k_pool2d_warp, grid_for(ctx, total, 8), 256, 0, (cudaStream_t)stream, kind, x, y, n * c, h, w, oh, ow, kh, kw, ph,
                                                                                   pw, sh, sw);
@@ -400,6 +613,12 @@ extern "C" int petb200_rowmean_run(petb200_ctx *ctx, const float *x, float *y, s
         return fail(ctx, PETB200_ERR_INVALID, "rowmean_run: bad arguments");
     if (!rows)
         return PETB200_OK;
+    if (cols <= 96 && rows >= 1024) { // short rows, many of them
+        const int rb = std::min(256, 8192 / cols);
+        launch_pdl(k_rowmean_staged, (int)std::min<size_t>((rows + rb - 1) / rb, (size_t)ctx->sm_count * 8), 256, (size_t)rb * cols * sizeof(float),
+                   (cudaStream_t)stream, x, y, rows, cols, rb);
+        return launched(ctx, "k_rowmean_staged");
+    }
     launch_pdl(k_rowmean, grid_for(ctx, rows, 8), 256, 0, (cudaStream_t)stream, x, y, rows, cols);
     return launched(ctx, "k_rowmean");
 }
@@ -414,7 +633,19 @@ extern "C" int petb200_softmax_run(petb200_ctx *ctx, const float *x, float *y, s
         launch_pdl(k_softmax_block, (int)std::min<size_t>(rows, (size_t)ctx->sm_count * 8), 256, 0, (cudaStream_t)stream, x, y, rows, cols);
         return launched(ctx, "k_softmax_block");
     }
-    launch_pdl(k_softmax, grid_for(ctx, rows, 8), 256, 0, (cudaStream_t)stream, x, y, rows, cols);
+    const int grid = grid_for(ctx, rows, 8);
+    if (cols <= 128)
+        launch_pdl(k_softmax_reg<4>, grid, 256, 0, (cudaStream_t)stream, x, y, rows, cols);
+    else if (cols <= 256)
+        launch_pdl(k_softmax_reg<8>, grid, 256, 0, (cudaStream_t)stream, x, y, rows, cols);
+    else if (cols <= 512)
+        launch_pdl(k_softmax_reg<16>, grid, 256, 0, (cudaStream_t)stream, x, y, rows, cols);
+    else if (cols <= 768)
+        launch_pdl(k_softmax_reg<24>, grid, 256, 0, (cudaStream_t)stream, x, y, rows, cols);
+    else if (cols <= 1024)
+        launch_pdl(k_softmax_reg<32>, grid, 256, 0, (cudaStream_t)stream, x, y, rows, cols);
+    else
+        launch_pdl(k_softmax, grid, 256, 0, (cudaStream_t)stream, x, y, rows, cols);
     return launched(ctx, "k_softmax");
 }
 
@@ -426,7 +657,9 @@ extern "C" int petb200_softmax_axis_run(petb200_ctx *ctx, const float *x, float 
         return PETB200_OK;
     if (inner == 1)
         return petb200_softmax_run(ctx, x, y, outer, len, stream);
-    launch_pdl(k_softmax_strided, grid_for(ctx, outer * inner, 256), 256, 0, (cudaStream_t)stream, x, y, outer, len, inner);
+    const size_t tiles = outer * ((inner + 31) / 32);
+    launch_pdl(k_softmax_strided, (int)std::min<size_t>(tiles, (size_t)ctx->sm_count * 16), dim3(32, 8), 0, (cudaStream_t)stream, x, y, outer, len,
+               inner);
     return launched(ctx, "k_softmax_strided");
 }
 
@@ -441,6 +674,18 @@ extern "C" int petb200_layernorm_run(petb200_ctx *ctx, const float *x, const flo
                                                                                                            cols, eps);
         return launched(ctx, "k_layernorm_block");
     }
-    launch_pdl(k_layernorm, grid_for(ctx, rows, 8), 256, 0, (cudaStream_t)stream, x, gamma, beta, y, rows, cols, eps);
+    const int grid = grid_for(ctx, rows, 8);
+    if (cols <= 128)
+        launch_pdl(k_layernorm_reg<4>, grid, 256, 0, (cudaStream_t)stream, x, gamma, beta, y, rows, cols, eps);
+    else if (cols <= 256)
+        launch_pdl(k_layernorm_reg<8>, grid, 256, 0, (cudaStream_t)stream, x, gamma, beta, y, rows, cols, eps);
+    else if (cols <= 512)
+        launch_pdl(k_layernorm_reg<16>, grid, 256, 0, (cudaStream_t)stream, x, gamma, beta, y, rows, cols, eps);
+    else if (cols <= 768)
+        launch_pdl(k_layernorm_reg<24>, grid, 256, 0, (cudaStream_t)stream, x, gamma, beta, y, rows, cols, eps);
+    else if (cols <= 1024)
+        launch_pdl(k_layernorm_reg<32>, grid, 256, 0, (cudaStream_t)stream, x, gamma, beta, y, rows, cols, eps);
+    else
+        launch_pdl(k_layernorm, grid, 256, 0, (cudaStream_t)stream, x, gamma, beta, y, rows, cols, eps);
     return launched(ctx, "k_layernorm");
 }

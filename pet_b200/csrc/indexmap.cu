@@ -90,6 +90,77 @@ __global__ void __launch_bounds__(256) k_gather(const uint32_t *__restrict__ in,
     }
 }
 
+// Long rows (innermost digit contiguous on both sides): a warp takes a piece of ONE row, decodes the outer digits once for
+// it, and then only adds lane offsets — no division per 16-byte element.  kPiece4 uint4 (2 KB) per warp step, four loads
+// in flight per lane.
+constexpr int kPiece4 = 128;
+template <typename I>
+__global__ void __launch_bounds__(256) k_rowcopy_rows_v4(const uint4 *__restrict__ in, uint4 *__restrict__ out, MapParams p) {
+    pdl_prologue();
+    const I inner4 = (I)(p.ext[p.nd - 1] >> 2);
+    const I pieces = (inner4 + kPiece4 - 1) / kPiece4;
+    const I rows = (I)(p.total / p.ext[p.nd - 1]);
+    const I units = rows * pieces;
+    const int lane = threadIdx.x & 31;
+    const I nwarps = ((I)gridDim.x * blockDim.x) >> 5;
+    for (I u = ((I)blockIdx.x * blockDim.x + threadIdx.x) >> 5; u < units; u += nwarps) {
+        const I row = u / pieces;
+        const I c0 = (u - row * pieces) * kPiece4;
+        long long io = p.ibase, oo = p.obase;
+        bool inside = true;
+        decode<I, 1>(p, row, io, oo, inside);
+        const uint4 *src = in + (io >> 2) + c0;
+        uint4 *dst = out + (oo >> 2) + c0;
+        const int n = (int)min((I)kPiece4, inner4 - c0);
+        uint4 v[kPiece4 / 32];
+#pragma unroll
+        for (int j = 0; j < kPiece4 / 32; ++j)
+            if (lane + 32 * j < n)
+                v[j] = __ldg(src + lane + 32 * j);
+#pragma unroll
+        for (int j = 0; j < kPiece4 / 32; ++j)
+            if (lane + 32 * j < n)
+                dst[lane + 32 * j] = v[j];
+    }
+}
+
+// Rows whose innermost digit is contiguous on both sides but not 16-byte friendly (odd extents or offsets: Pad and Slice
+// of the innermost dimension) or carries a guard: the same warp-per-row-piece scheme with 32-bit accesses; the guard of
+// the innermost digit is a comparison, those of the outer digits are decided once per row.
+constexpr int kPieceW = 256;
+template <typename I>
+__global__ void __launch_bounds__(256) k_rowgather(const uint32_t *__restrict__ in, uint32_t *__restrict__ out, MapParams p) {
+    pdl_prologue();
+    const int last = p.nd - 1;
+    const I inner = (I)p.ext[last];
+    const I pieces = (inner + kPieceW - 1) / kPieceW;
+    const I rows = (I)(p.total / p.ext[last]);
+    const I units = rows * pieces;
+    const int lane = threadIdx.x & 31;
+    const I nwarps = ((I)gridDim.x * blockDim.x) >> 5;
+    const int glo = p.guarded ? p.glo[last] : 0, ghi = p.guarded ? p.ghi[last] : p.ext[last];
+    for (I u = ((I)blockIdx.x * blockDim.x + threadIdx.x) >> 5; u < units; u += nwarps) {
+        const I row = u / pieces;
+        const int c0 = (int)((u - row * pieces) * kPieceW);
+        long long io = p.ibase, oo = p.obase;
+        bool inside = true;
+        decode<I, 1>(p, row, io, oo, inside);
+        const uint32_t *src = in + io;
+        uint32_t *dst = out + oo;
+        const int n = (int)min((I)kPieceW, inner - c0);
+        uint32_t v[kPieceW / 32];
+#pragma unroll
+        for (int j = 0; j < kPieceW / 32; ++j) {
+            const int c = c0 + lane + 32 * j;
+            v[j] = (lane + 32 * j < n && inside && c >= glo && c < ghi) ? __ldg(src + c) : 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < kPieceW / 32; ++j)
+            if (lane + 32 * j < n)
+                dst[c0 + lane + 32 * j] = v[j];
+    }
+}
+
 constexpr int kMaxTileDigits = 4;
 constexpr int kTileElems = 2048;
 constexpr int kTileEPT = kTileElems / 256; // elements per thread
@@ -390,6 +461,8 @@ using DigitList = std::vector<Digit>;
 
 struct LayoutPlan : petb200_plan {
     int mode = 0; // 0 rowcopy, 1 tile, 2 gather
+    bool long_rows = false;  // rowcopy: rows of at least 64 uint4, one decode per row piece (k_rowcopy_rows_v4)
+    bool row_gather = false; // gather whose innermost digit is contiguous on both sides (k_rowgather)
     bool tile_vi = false, tile_vo = false; // tile mode: 16-byte global loads / stores are possible
     MapParams mp{};
     TileParams tp{};
@@ -473,6 +546,8 @@ static int finalize_plan(petb200_ctx *ctx, LayoutPlan *pl, std::vector<Digit> di
     if (v4) {
         pl->mode = 0;
         pl->kernel = "rowcopy";
+        pl->long_rows = m.ext[last] / 4 >= 64; // decode once per 2 KB row piece instead of once per 16 bytes
+        pl->row_gather = m.ext[last] >= 32;    // (fallback for caller buffers that are not 16-byte aligned)
         long long blocks = (m.total / 16 + 255) / 256;
         pl->grid = (int)std::max<long long>(1, std::min<long long>(blocks, (long long)sms * 8));
         pl->grid_gather = (int)std::max<long long>(1, std::min<long long>((m.total + 255) / 256, (long long)sms * 16));
@@ -668,12 +743,20 @@ static int finalize_plan(petb200_ctx *ctx, LayoutPlan *pl, std::vector<Digit> di
     }
     pl->mode = 2;
     pl->kernel = "gather";
+    pl->row_gather = m.istr[last] == 1 && m.ostr[last] == 1 && m.ext[last] >= 32;
     long long blocks = (m.total + 255) / 256;
     pl->grid = pl->grid_gather = (int)std::max<long long>(1, std::min<long long>(blocks, (long long)sms * 16));
     return PETB200_OK;
 }
 
 static void launch_gather(LayoutPlan *pl, const void *in, void *out, cudaStream_t s) {
+    if (pl->row_gather) {
+        if (pl->mp.total < (1ll << 31))
+            launch_pdl(k_rowgather<unsigned>, pl->grid_gather, 256, 0, s, (const uint32_t *)in, (uint32_t *)out, pl->mp);
+        else
+            launch_pdl(k_rowgather<unsigned long long>, pl->grid_gather, 256, 0, s, (const uint32_t *)in, (uint32_t *)out, pl->mp);
+        return;
+    }
     if (pl->mp.total < (1ll << 31))
         launch_pdl(k_gather<unsigned>, pl->grid_gather, 256, 0, s, (const uint32_t *)in, (uint32_t *)out, pl->mp);
     else
@@ -692,6 +775,13 @@ static int layout_launch(LayoutPlan *pl, const void *in, void *out, cudaStream_t
         if ((((uintptr_t)in) | ((uintptr_t)out)) & 15) { // unaligned caller buffers: fall back to the word kernel
             launch_gather(pl, in, out, s);
             return launched(pl->ctx, "k_gather");
+        }
+        if (pl->long_rows) {
+            if (pl->mp.total < (1ll << 31))
+                launch_pdl(k_rowcopy_rows_v4<unsigned>, pl->grid, 256, 0, s, (const uint4 *)in, (uint4 *)out, pl->mp);
+            else
+                launch_pdl(k_rowcopy_rows_v4<unsigned long long>, pl->grid, 256, 0, s, (const uint4 *)in, (uint4 *)out, pl->mp);
+            return launched(pl->ctx, "k_rowcopy_rows_v4");
         }
         if (pl->mp.total < (1ll << 31))
             launch_pdl(k_rowcopy_v4<unsigned>, pl->grid, 256, 0, s, (const uint4 *)in, (uint4 *)out, pl->mp);

@@ -3,7 +3,12 @@
 Groups: `layout` (index-map kernels at sizes far beyond L2: achieved HBM GB/s), `conv` / `matmul` (tensor-core kernels:
 achieved fp32-equivalent TFLOP/s and the TF32 issue rate), `convtrans` (transposed convolution), `banded` (G2BMM / GBMML
 at the one shape the reference ships kernels for, and a short-sequence one), `rewrite` (config 1's H->N rewrite restored by
-the correction kernel and by halo transposes, each route replayed as a CUDA graph).  Times come from the C ABI's timing entry point
+the correction kernel and by halo transposes, each route replayed as a CUDA graph).  The `once_*` groups launch every kernel
+of a family exactly once (after one warm-up launch) at a size beyond the L2 and print the algorithmic bytes / flops of
+each launch: they exist to be run under a profiler, which supplies the durations and the DRAM traffic (`once_ops`: element-wise,
+activation, BatchNorm, pooling, softmax, LayerNorm, row mean, small-m matmul, pad / slice / concat; `once_matmul`: the
+BERT-base matmul shapes; `once_conv`: the dilated-conv layer, a correction window, a transposed convolution;
+`once_rn18 [batch]`: one ResNet-18 forward pass, operator by operator).  Times come from the C ABI's timing entry point
 (CUDA events around repeated launches on plan-owned operands).  Peaks are read from MEASURED_PEAKS.json at the
 repository root when present.
 """
@@ -111,6 +116,94 @@ def rewrite_routes(ctx):
         print(f"rewrite {name:46s} {_graph_time(fn):8.1f} us per replay")
 
 
+def once_ops(ctx):
+    """One launch of every HBM-bound operator kernel at a size far beyond the L2, each preceded by one warm-up launch."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(3)
+    r = lambda *shape: torch.rand(shape, device="cuda", generator=g) - 0.5
+    MB = lambda n: f"{n / 1e6:9.1f} MB algorithmic"
+    x = r(64, 64, 112, 112)   # 205 MB
+    y = r(64, 64, 112, 112)
+    runs = [("eltwise add + relu (2 in, 1 out)", lambda: ctx.eltwise("add", [x, y], act="relu"), 12 * x.numel()),
+            ("activation gelu", lambda: ctx.activation(x, "gelu"), 8 * x.numel()),
+            ("batchnorm", lambda: ctx.batchnorm(x, r(64), r(64), r(64), r(64).abs() + 1), 8 * x.numel()),
+            ("maxpool 3x3 s2 p1 (ResNet stem)", lambda: ctx.maxpool(x, 3, 3, 1, 1, 1, 1, 2, 2), 4 * x.numel() * 1.25),
+            ("avgpool 7x7 global", lambda: ctx.avgpool(r(2048, 512, 7, 7), 7, 7, 0, 0, 1, 1), 4 * 2048 * 512 * 50),
+            ("rowmean 12544 cols", lambda: ctx.rowmean(x.view(64 * 64, 12544), 12544), 4 * x.numel()),
+            ("softmax last axis 128 cols", lambda: ctx.softmax(r(12 * 512, 128, 128)), 8 * 12 * 512 * 128 * 128),
+            ("softmax last axis 1000 cols", lambda: ctx.softmax(r(65536, 1000)), 8 * 65536 * 1000),
+            ("softmax axis 1 of [64,1000,784]", lambda: ctx.softmax(r(64, 1000, 784), 1), 8 * 64 * 1000 * 784),
+            ("layernorm 768 cols", lambda: ctx.layernorm(r(65536, 768), r(768), r(768)), 8 * 65536 * 768),
+            ("matmul m=1 (classifier head 512 -> 1000)", lambda: ctx.matmul(r(1, 1, 512), r(1, 512, 1000)), 4 * 512 * 1000),
+            ("matmul m=8, 4096 x 16384 weights", lambda: ctx.matmul(r(1, 8, 4096), r(1, 4096, 16384)), 4 * 4096 * 16384),
+            ("pad [64,64,112,112] by 1", lambda: ctx.pad(x, [0, 0, 1, 1], [0, 0, 1, 1]), 8 * x.numel()),
+            ("slice [64,64,112,112] by 1", lambda: ctx.slice(x, [0, 0, 1, 1], [0, 0, 1, 1]), 8 * x.numel() * 0.96),
+            ("concat 2 x [64,64,112,112] on C", lambda: ctx.concat([x, y], 1), 16 * x.numel())]
+    for name, fn, nbytes in runs:
+        fn()
+        torch.cuda.synchronize()
+        fn()
+        torch.cuda.synchronize()
+        print(f"once_ops  {name:44s} {MB(nbytes)}")
+
+
+def once_matmul(ctx):
+    import torch
+    for name, b, m, n, k, ta, tb in MATMUL[:4]:
+        a = torch.rand((b, m, k), device="cuda") - 0.5
+        w = torch.rand((b, n, k) if tb else (b, k, n), device="cuda") - 0.5
+        plan = ctx.matmul_plan(a.shape, w.shape, ta, tb)
+        ctx.matmul_set_weights(plan, w)
+        for _ in range(2):
+            ctx.matmul_run(plan, a, None)
+            torch.cuda.synchronize()
+        print(f"once_matmul  {name:30s} {2.0 * b * m * n * k / 1e9:8.3f} GFLOP, {4.0 * b * (m * k + k * n + m * n) / 1e6:7.2f} MB algorithmic")
+
+
+def once_conv(ctx):
+    import torch
+    x = torch.randn((4, 512, 32, 32), device="cuda")
+    w = torch.randn((512, 512, 3, 3), device="cuda") * 0.02
+    plan = ctx.conv2d_plan(x.shape, w.shape, 1, 1)
+    ctx.conv2d_set_weights(plan, w)
+    for _ in range(2):
+        ctx.conv2d_run(plan, x)
+        torch.cuda.synchronize()
+    print(f"once_conv  dense conv of the dilated layer [4,512,32,32] x [512,512,3,3]: 19.327 GFLOP, 26.21 MB algorithmic")
+    x1, w1 = torch.randn((1, 64, 56, 56), device="cuda"), torch.randn((64, 64, 3, 3), device="cuda")
+    p1 = ctx.conv2d_plan(x1.shape, w1.shape, 1, 1)
+    ctx.conv2d_set_weights(p1, w1)
+    y1 = ctx.conv2d_run(p1, x1)
+    for _ in range(2):
+        ctx.conv2d_correct(p1, x1, y1, 27, 2)
+        torch.cuda.synchronize()
+    print("once_conv  correction window rows 27-28 of config 1: 8.26 MFLOP, 0.233 MB algorithmic")
+    name, xs, ws, (ph, pw, sh, sw, oph, opw) = CONVTRANS[1]
+    pt = ctx.convtrans_plan(xs, ws, ph, pw, sh, sw, 1, 1, oph, opw)
+    xt, wt = torch.rand(xs, device="cuda") - 0.5, torch.rand(ws, device="cuda") - 0.5
+    ctx.convtrans_run(pt, xt, wt)
+    torch.cuda.synchronize()
+    ctx.convtrans_run(pt, xt)
+    torch.cuda.synchronize()
+    print(f"once_conv  transposed conv {name}: {2.0 * np.prod(xs) * ws[0] * ws[1] * ws[3] / 1e9:.3f} GFLOP useful")
+
+
+def once_rn18(ctx, batch):
+    """One ResNet-18 forward pass at `batch`, operator by operator (no CUDA graph), after one warm-up pass."""
+    import torch
+    from . import configs
+    from .graph import Graph
+    g = Graph(ctx)
+    b = configs.GraphBuilder(g)
+    g.setOutputs([configs.resnet18(b, batch=batch)])
+    g.compile(cuda_graph=False)
+    b.load()
+    for _ in range(2):
+        g.run()
+        torch.cuda.synchronize()
+    print(f"once_rn18  batch {batch}: {g.num_launches()} launches per pass, {batch * 3.628146688:.2f} GFLOP algorithmic (conv + FC)")
+
+
 def main(argv):
     groups = argv or ["layout", "conv", "matmul"]
     pk, kind = peaks()
@@ -163,6 +256,15 @@ def main(argv):
                       f"{by / ms / 1e6:6.0f} GB/s = {by / ms / 1e6 / pk['hbm_gbs']:.2f} of {pk_kind} HBM peak")
     if "rewrite" in groups:
         rewrite_routes(ctx)
+    if "once_ops" in groups:
+        once_ops(ctx)
+    if "once_matmul" in groups:
+        once_matmul(ctx)
+    if "once_conv" in groups:
+        once_conv(ctx)
+    if "once_rn18" in groups:
+        i = groups.index("once_rn18")
+        once_rn18(ctx, int(groups[i + 1]) if i + 1 < len(groups) and groups[i + 1].isdigit() else 64)
     ctx.sync_check()
     ctx.close()
 
