@@ -14,6 +14,8 @@ int tc_conv_set_weights(void *h, const float *w, cudaStream_t s);
 int tc_conv_run(void *h, const float *x, const float *bias, const float *res, float *y, const int *win, cudaStream_t s);
 int tc_conv_row_pitch(void *h);
 void tc_conv_set_prof(void *h, long long *p);
+void tc_conv_set_starve(void *h, int on);
+int tc_set_wait_limit_ns(unsigned long long ns);
 void tc_matmul_set_prof(void *h, long long *p);
 const char *tc_conv_variant(void *h);
 int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, int transB, int has_bias, int act, int passes,
@@ -605,5 +607,19 @@ extern "C" int petb200_debug_conv_prof(petb200_plan *plan, long long *dev_counte
     if (!pl || !pl->tc)
         return PETB200_ERR_INVALID;
     petb200::tc_conv_set_prof(pl->tc, dev_counters);
+    return PETB200_OK;
+}
+
+// Test hooks for the give-up path of the tensor-core kernel's bounded waits (not part of the public header).
+// set_wait_limit: how long a wait on an mbarrier may last on the current device (default 2 s).  conv_starve: while on,
+// the plan's filter producer announces 64 bytes more per stage than it loads — a flag that nothing sets — so the MMA
+// warp's wait runs out, every role leaves through its abort path, and petb200_check_device_status reports
+// PETB200_ERR_DEVICE.  Nothing faults and nothing hangs: the kernel returns after the limit.
+extern "C" int petb200_debug_set_wait_limit(unsigned long long ns) { return petb200::tc_set_wait_limit_ns(ns); }
+extern "C" int petb200_debug_conv_starve(petb200_plan *plan, int on) {
+    auto *pl = dynamic_cast<petb200::ConvPlan *>(plan);
+    if (!pl || !pl->tc)
+        return PETB200_ERR_INVALID;
+    petb200::tc_conv_set_starve(pl->tc, on);
     return PETB200_OK;
 }

@@ -81,6 +81,7 @@ struct IgemmParams {
     float *y;
     int *status;
     long long *prof; // optional per-CTA counters (kProfSlots per CTA), for tuning only
+    int starve;      // test hook: the filter producer announces more bytes than it loads, so the stage never completes
 };
 
 struct SmemLayout {
@@ -500,7 +501,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 if (!ptx::mbar_wait(b_empty + sb, pb, abort_flag))
                     break;
                 uint8_t *dst = sB + (size_t)sb * 2 * b_half;
-                ptx::mbar_expect_tx(b_full + sb, (PASSES == 3 ? 2u : 1u) * b_half);
+                ptx::mbar_expect_tx(b_full + sb, (PASSES == 3 ? 2u : 1u) * b_half + (P.starve ? 64u : 0u));
                 ptx::tma_load_2d(dst, &tmap_bhi, b_full + sb, (c0 * P.spc + ks) * kStageK, row0);
                 if (PASSES == 3)
                     ptx::tma_load_2d(dst + b_half, &tmap_blo, b_full + sb, (c0 * P.spc + ks) * kStageK, row0);
@@ -1193,6 +1194,7 @@ struct TcCore {
     const void *map_x_ptr = nullptr;
     bool weights_ready = false;
     long long *prof = nullptr;
+    int starve = 0;
 
     void (*kernel() const)(CUtensorMap, CUtensorMap, CUtensorMap, IgemmParams) {
         if (single_pass)
@@ -1275,6 +1277,7 @@ struct TcCore {
         p.koff = (const int *)koff.p;
         p.status = ctx->d_status;
         p.prof = prof;
+        p.starve = starve;
         p.has_bias = (P.has_bias && bias) ? 1 : 0;
         void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, IgemmParams) = kernel();
         cudaLaunchConfig_t cfg{};
@@ -1835,6 +1838,10 @@ void tc_conv_out_dims(void *h, int *d5) {
     d5[4] = t->g.OW;
 }
 void tc_conv_set_prof(void *h, long long *p) { ((TcConv *)h)->full.prof = p; }
+void tc_conv_set_starve(void *h, int on) { ((TcConv *)h)->full.starve = on; }
+int tc_set_wait_limit_ns(unsigned long long ns) {
+    return cudaMemcpyToSymbol(ptx::g_mbar_wait_limit_ns, &ns, sizeof ns) == cudaSuccess ? PETB200_OK : PETB200_ERR_CUDA;
+}
 int tc_conv_row_pitch(void *h) { return ((TcConv *)h)->g.Wst; }
 const char *tc_conv_variant(void *h) {
     const TcCore &c = ((TcConv *)h)->full;

@@ -161,6 +161,15 @@ __global__ void __launch_bounds__(256) k_rowgather(const uint32_t *__restrict__ 
     }
 }
 
+// Resident tile blocks per SM (PETB200_TILE_BLOCKS for tuning): each block has one 8 KB tile in flight.
+// Measured on B200 at >= 384 MiB: maps whose tiles take 16-byte accesses on both sides (plain permutations such as
+// NCHW -> NHWC) run best with 6 resident blocks, one-sided ones (space-to-batch and its inverse) with 8.
+static int env_tile_blocks(bool both_sides_v4) {
+    const char *e = getenv("PETB200_TILE_BLOCKS");
+    const int v = e ? atoi(e) : (both_sides_v4 ? 6 : 8);
+    return v >= 1 && v <= 8 ? v : 8;
+}
+
 constexpr int kMaxTileDigits = 4;
 constexpr int kTileElems = 2048;
 constexpr int kTileEPT = kTileElems / 256; // elements per thread
@@ -737,7 +746,7 @@ static int finalize_plan(petb200_ctx *ctx, LayoutPlan *pl, std::vector<Digit> di
             pl->mode = 1;
             pl->kernel = "tile";
             pl->smem = 0;
-            pl->grid = (int)std::min<long long>(t.m.total, (long long)sms * 4);
+            pl->grid = (int)std::min<long long>(t.m.total, (long long)sms * env_tile_blocks(pl->tile_vi && pl->tile_vo));
             return PETB200_OK;
         }
     }

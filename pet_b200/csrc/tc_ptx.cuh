@@ -50,8 +50,12 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-// Bounded wait: gives up after ~2 s (or as soon as another thread of the CTA raised *abort), so a protocol bug
-// turns into an error status instead of a hung GPU.  Returns false on give-up.
+// How long a wait on an mbarrier may last before the kernel gives up (nanoseconds).  2 s by default; a test shortens it to
+// milliseconds to watch the give-up path run (petb200_debug_set_wait_limit).
+__device__ unsigned long long g_mbar_wait_limit_ns = 2000000000ull;
+
+// Bounded wait: gives up after the limit above (or as soon as another thread of the CTA raised *abort), so a protocol
+// bug turns into an error status instead of a hung GPU.  Returns false on give-up.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
     if (mbar_try_wait(bar, parity))
         return true;
@@ -61,7 +65,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
         if ((++spins & 0x3ff) == 0) {
             if (*abort_flag)
                 return false;
-            if (globaltimer_ns() - t0 > 2000000000ull) {
+            if (globaltimer_ns() - t0 > g_mbar_wait_limit_ns) {
                 *abort_flag = 1;
                 return false;
             }

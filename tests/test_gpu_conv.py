@@ -370,3 +370,35 @@ def test_conv_epilogue_combinations_exact(ctx, oracle):
                            residual=dev(res) if use_res else None).cpu().numpy()
             assert np.array_equal(y, want), (algo, x.shape, wt.shape, st, act, use_b, use_res)
     ctx.sync_check()
+
+
+def test_bounded_wait_gives_up_and_reports_instead_of_hanging(ctx):
+    """Every wait of the tensor-core kernel has a limit after which the kernel leaves through its abort path and sets a
+    status word.  Here the limit is shortened to 5 ms and one plan's filter producer is told to announce more bytes per
+    stage than it loads (a completion that never comes): the launch returns, petb200_check_device_status reports
+    PETB200_ERR_DEVICE, and the next launches on the same context — the same plan with the hook off — are correct."""
+    import ctypes as C
+    from pet_b200 import lib as L
+    lib = L.load()
+    lib.petb200_debug_set_wait_limit.argtypes = [C.c_ulonglong]
+    lib.petb200_debug_conv_starve.argtypes = [C.c_void_p, C.c_int]
+    x = torch.randn((1, 64, 28, 28), device="cuda")
+    w = torch.randn((64, 64, 3, 3), device="cuda") * 0.05
+    plan = ctx.conv2d_plan(x.shape, w.shape, 1, 1)
+    assert plan.kernel.startswith("tc_")
+    ctx.conv2d_set_weights(plan, w)
+    good = ctx.conv2d_run(plan, x)
+    ctx.sync_check()
+    assert lib.petb200_debug_set_wait_limit(5_000_000) == 0
+    try:
+        assert lib.petb200_debug_conv_starve(plan.h, 1) == 0
+        ctx.conv2d_run(plan, x)
+        with pytest.raises(L.PetError) as e:
+            ctx.sync_check()
+        assert e.value.status == L.ERR_DEVICE
+    finally:
+        lib.petb200_debug_conv_starve(plan.h, 0)
+        assert lib.petb200_debug_set_wait_limit(2_000_000_000) == 0
+    again = ctx.conv2d_run(plan, x)
+    ctx.sync_check()                      # the status word was cleared by the failed check; the context is usable
+    assert torch.equal(again, good)
