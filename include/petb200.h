@@ -41,7 +41,9 @@ enum {
     PETB200_ALGO_AUTO = 0,
     PETB200_ALGO_TC_3XTF32 = 1, /* tcgen05 implicit GEMM, error-compensated TF32 (fp32-grade accuracy) */
     PETB200_ALGO_SIMT_FP32 = 2, /* CUDA-core FFMA, exact fp32 products */
-    PETB200_ALGO_TC_1XTF32 = 3  /* tcgen05, single TF32 pass (what cuDNN's default math mode does) */
+    PETB200_ALGO_TC_1XTF32 = 3, /* tcgen05, single TF32 pass (what cuDNN's default math mode does) */
+    PETB200_ALGO_TC_BF16X3 = 4  /* tcgen05, error-compensated bf16: x = hi + lo in bf16, hi*hi + hi*lo + lo*hi with fp32
+                                   accumulation; per-product error ~2^-17, half the tensor-core instructions of 3xTF32 */
 };
 
 /* ---- context ------------------------------------------------------------------------------------------------

@@ -96,6 +96,25 @@ inline int launched(petb200_ctx *ctx, const char *what) {
 }
 
 // ---- programmatic dependent launch ---------------------------------------------------------------------------------
+// Kernel families that run on the tensor-core kernel, and the arithmetic ("passes") each one asks of it: 3 = error-compensated
+// TF32, 1 = one TF32 product, 16 = error-compensated bf16.  PETB200_ALGO_AUTO takes PETB200_TC_MATH from the environment
+// ("3xtf32", "bf16x3"), else the default below.
+inline bool tc_is_tc_algo(int algo) {
+    return algo == PETB200_ALGO_AUTO || algo == PETB200_ALGO_TC_3XTF32 || algo == PETB200_ALGO_TC_1XTF32 || algo == PETB200_ALGO_TC_BF16X3;
+}
+inline int tc_passes_for(int algo) {
+    if (algo == PETB200_ALGO_TC_1XTF32)
+        return 1;
+    if (algo == PETB200_ALGO_TC_BF16X3)
+        return 16;
+    if (algo == PETB200_ALGO_TC_3XTF32)
+        return 3;
+    const char *v = getenv("PETB200_TC_MATH");
+    if (v && !strcmp(v, "bf16x3"))
+        return 16;
+    return 3;
+}
+
 // Every kernel of the library starts with pdl_prologue() and is launched through launch_pdl(): a kernel's CTAs may then
 // be placed on free SMs while the kernel before it in the stream is still finishing, and wait (griddepcontrol.wait)
 // until that kernel has completed and its writes are visible before they touch global memory.  PETB200_PDL=0 in the

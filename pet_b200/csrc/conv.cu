@@ -331,9 +331,9 @@ int make_conv_plan(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const i
     }
     c.oh0 = 0, c.ohn = c.OH, c.ow0 = 0, c.own = c.OW;
     int rc = PETB200_ERR_UNSUPPORTED;
-    if (algo == PETB200_ALGO_AUTO || algo == PETB200_ALGO_TC_3XTF32 || algo == PETB200_ALGO_TC_1XTF32) {
+    if (tc_is_tc_algo(algo)) {
         size_t bytes = 0;
-        rc = tc_conv_create(ctx, nsp, in_dims, f, k, pad, stride, dil, groups, has_bias, act, algo == PETB200_ALGO_TC_1XTF32 ? 1 : 3,
+        rc = tc_conv_create(ctx, nsp, in_dims, f, k, pad, stride, dil, groups, has_bias, act, tc_passes_for(algo),
                             &pl->tc, &bytes, c.cl_out);
         if (rc == PETB200_OK) {
             pl->algo = PETB200_ALGO_TC_3XTF32;
@@ -482,13 +482,13 @@ int make_matmul_plan(petb200_ctx *ctx, int transA, int transB, int b, int m, int
         *out = pl;
         return PETB200_OK;
     }
-    if (algo == PETB200_ALGO_AUTO || algo == PETB200_ALGO_TC_3XTF32 || algo == PETB200_ALGO_TC_1XTF32) {
+    if (tc_is_tc_algo(algo)) {
         size_t bytes = 0;
-        rc = tc_matmul_create(ctx, b, m, n, k, pl->transA, pl->transB, has_bias, act, algo == PETB200_ALGO_TC_1XTF32 ? 1 : 3, strides,
+        rc = tc_matmul_create(ctx, b, m, n, k, pl->transA, pl->transB, has_bias, act, tc_passes_for(algo), strides,
                               &pl->tc, &bytes);
         if (rc == PETB200_OK) {
             pl->algo = PETB200_ALGO_TC_3XTF32;
-            pl->kernel = algo == PETB200_ALGO_TC_1XTF32 ? "tc_1xtf32_ts" : "tc_3xtf32_ts";
+            pl->kernel = tc_passes_for(algo) == 1 ? "tc_1xtf32_ts" : (tc_passes_for(algo) == 16 ? "tc_bf16x3_ts" : "tc_3xtf32_ts");
             pl->device_bytes = bytes;
             pl->native_a = tc_matmul_native_a(pl->tc) != 0;
             if (!pl->native_a && (!pl->transA || m % 4 != 0)) {

@@ -188,7 +188,7 @@ int make_convtrans_plan(petb200_ctx *ctx, const int *a /*n,c,h,w,f,r,s,ph,pw,sh,
     // of ~8 us per launch).  Needs taps in every phase and a row stride of y that is a whole number of phase pixels.
     const double issued = 2.0 * n * c * (double)oh * ow * f * r * s;
     const double us_inserted = issued / 100e6, us_phased = sh * sw * std::max(8.0, issued / (sh * sw) / 170e6);
-    const bool tc_algo = algo == PETB200_ALGO_AUTO || algo == PETB200_ALGO_TC_3XTF32 || algo == PETB200_ALGO_TC_1XTF32;
+    const bool tc_algo = tc_is_tc_algo(algo);
     const char *env = getenv("PETB200_CONVTRANS_PHASES");
     const int want = env ? atoi(env) : -1; // 0 never, 1 whenever possible, unset: by size
     if (tc_algo && sh * sw > 1 && r >= sh && s >= sw && ((long long)sh * ow) % sw == 0 && want != 0 && (want == 1 || us_phased < us_inserted) &&
@@ -211,7 +211,7 @@ int make_convtrans_plan(petb200_ctx *ctx, const int *a /*n,c,h,w,f,r,s,ph,pw,sh,
                 size_t bytes = 0;
                 int prc = tc_conv_create_view(ctx, n, f, h, w, c, ps->Ta, ps->Tb, -off_a, -off_b, Ua, Vb, (int)(((long long)sh * ow) / sw),
                                               (long long)oh * ow * c, 1, (long long)sw * c, has_bias, act,
-                                              algo == PETB200_ALGO_TC_1XTF32 ? 1 : 3, &ps->tc, &bytes);
+                                              tc_passes_for(algo), &ps->tc, &bytes);
                 if (prc != PETB200_OK || ps->wsub.alloc((size_t)c * f * ps->Ta * ps->Tb * 4) != cudaSuccess)
                     ok = false;
                 extra += bytes + ps->wsub.bytes;

@@ -33,7 +33,10 @@
 namespace petb200 {
 
 constexpr int kTileM = 128;
-constexpr int kStageK = 32;               // fp32/TF32 values per K stage = one 128-byte swizzle row
+constexpr int kStageK = 32;               // 32-bit words per K stage = one 128-byte swizzle row (32 TF32 values or 64 bf16)
+// values of the kernel's PASSES parameter: error-compensated TF32 (three products per multiply), one TF32 product, and
+// error-compensated bf16 (hi/lo bf16 halves, three products, K = 16 per instruction: half the MMAs of 3xTF32 per K)
+constexpr int kMathTf32x3 = 3, kMathTf32x1 = 1, kMathBf16x3 = 16;
 constexpr int kAHalfBytes = kTileM * 128; // one 128 x 32 operand tile
 constexpr int kThreads = 352;   // warps: 0 B producer, 1 MMA, 2 raw producer, 3-6 and 7-10 two transform/epilogue sets
 constexpr int kProfSlots = 24; // tuning counters per CTA (see IgemmParams::prof)
@@ -48,6 +51,7 @@ struct IgemmParams {
     int x0;                 // box origin along W (multiple of 4, may be negative)
     int RN, RD, RH, RW, BC; // raw box extents
     int nchunks, spc;       // channel chunks; K stages per chunk
+    int ke;                 // K elements per stage: 32 (TF32) or 64 (bf16, two per 32-bit word)
     int cpg, Fg, BN;        // channels per group, filters per group, tile N
     int z_is_batch;         // blockIdx.z: 0 = conv group, 1 = matmul batch
     int wide, row_tiles;    // wide mode: a tile is 128 consecutive pixels of ONE output row (rows wider than a tile)
@@ -81,6 +85,7 @@ struct IgemmParams {
     float *y;
     int *status;
     long long *prof; // optional per-CTA counters (kProfSlots per CTA), for tuning only
+    int epi_direct;  // tuning: store the epilogue straight from registers (no transposition through shared memory)
     int starve;      // test hook: the filter producer announces more bytes than it loads, so the stage never completes
 };
 
@@ -97,7 +102,7 @@ __host__ __device__ inline SmemLayout smem_layout(const IgemmParams &P, bool a_t
     L.raw_off = o;
     o += (uint32_t)P.NR * (uint32_t)P.raw_bytes;
     L.koff_off = o;
-    o += (uint32_t)P.spc * kStageK * 4;
+    o += (uint32_t)P.spc * (uint32_t)P.ke * 4;
     // split-K: landing area for the cluster's partial sums of this CTA's columns, [rank][BN/ksplit][128] floats.  Its
     // own region: peers push into it while this CTA may still be in its main loop.
     L.split_off = (o + 127) & ~127u;
@@ -136,22 +141,22 @@ template <int ACT> __device__ __forceinline__ float act_fn(float v) {
 template <int ACT, int PASSES>
 __device__ __forceinline__ void epilogue_store(uint32_t tacc, uint32_t tcross, int BN, int f_tile0, int Fg, bool valid, const float *bias,
                                                const float *rp /*residual at this pixel, or null*/, float *yp, long long ys_f, bool vec_ok, float *stage, int nvalid_warp, float *ybase_warp,
-                                               int col0, int col1, uint32_t split_addr /*split-K: shared address of [this rank][0][this pixel]*/,
+                                               const float *rbase_warp /*residual at the warp's first pixel, or null*/, int col0, int col1, uint32_t split_addr /*split-K: shared address of [this rank][0][this pixel]*/,
                                                int split_shift /*log2(columns per CTA)*/) {
     uint32_t r[32], nx[32], sm[32];
     if (col0 >= col1)
         return;
     ptx::tmem_ld_32x32(tacc + (uint32_t)col0, nx);
-    if (PASSES == 3)
+    if (PASSES != kMathTf32x1)
         ptx::tmem_ld_32x32(tcross + (uint32_t)col0, sm);
     for (int cc = col0; cc < col1; cc += 32) {
         ptx::tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) // hi*hi sum + (lo*hi + hi*lo) sum, one rounded fp32 add
-            r[j] = PASSES == 3 ? __float_as_uint(__uint_as_float(nx[j]) + __uint_as_float(sm[j])) : nx[j];
+            r[j] = PASSES != kMathTf32x1 ? __float_as_uint(__uint_as_float(nx[j]) + __uint_as_float(sm[j])) : nx[j];
         if (cc + 32 < col1) { // in flight while this chunk is stored
             ptx::tmem_ld_32x32(tacc + (uint32_t)(cc + 32), nx);
-            if (PASSES == 3)
+            if (PASSES != kMathTf32x1)
                 ptx::tmem_ld_32x32(tcross + (uint32_t)(cc + 32), sm);
         }
         if (split_addr != 0u) {
@@ -167,14 +172,23 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, uint32_t tcross, i
         if (stage == nullptr && !valid)
             continue;
         const int f0 = f_tile0 + cc;
+        // bias / residual / activation: each behind ONE test per block (a test per column costs more than the sums)
+        if (bias != nullptr) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            float v = __uint_as_float(r[j]);
-            if (bias != nullptr && f0 + j < Fg)
-                v += __ldg(bias + f0 + j);
-            if (rp != nullptr && f0 + j < Fg) // only reached by valid rows (no staging with a residual)
-                v += __ldg(rp + (long long)(f0 + j) * ys_f);
-            r[j] = __float_as_uint(act_fn<ACT>(v));
+            for (int j = 0; j < 32; ++j)
+                if (f0 + j < Fg)
+                    r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldg(bias + f0 + j));
+        }
+        if (rp != nullptr && stage == nullptr) { // (only valid rows get here; the staged path adds the residual 16 bytes at a time)
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (f0 + j < Fg)
+                    r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldg(rp + (long long)(f0 + j) * ys_f));
+        }
+        if (ACT != PETB200_ACT_NONE && (stage == nullptr || rbase_warp == nullptr)) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                r[j] = __float_as_uint(act_fn<ACT>(__uint_as_float(r[j])));
         }
         if (stage != nullptr) {
             // NCHW output, the warp's 32 pixels contiguous in memory: transpose the 32x32 block through shared memory so
@@ -185,14 +199,28 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, uint32_t tcross, i
             for (int j = 0; j < 32; ++j)
                 stage[j * 32 + lane] = __uint_as_float(r[j]);
             __syncwarp();
-            const int px = (lane & 7) * 4;
-            float *ybase = ybase_warp; // address of the warp's first pixel, filter 0 of the group
+            const int px = (lane & 7) * 4, cq = lane >> 3;
+            const long long off = (long long)(f0 + cq) * ys_f + px; // from the warp's first pixel: filter f0 + cq, 4 filters apart per step
+            float *dst = ybase_warp + off;
+            const float *rsd = rbase_warp != nullptr ? rbase_warp + off : nullptr;
+            const float *src = stage + cq * 32 + px;
+            const int fmax = Fg - f0 - cq; // filters left from this lane's first one
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int c = (lane >> 3) + 4 * i;
-                if (f0 + c < Fg) {
-                    const float4 v = *reinterpret_cast<const float4 *>(stage + c * 32 + px);
-                    float *dst = ybase + (long long)(f0 + c) * ys_f + px;
+            for (int i = 0; i < 8; ++i, dst += 4 * ys_f, src += 128) {
+                if (4 * i < fmax) {
+                    float4 v = *reinterpret_cast<const float4 *>(src);
+                    if (rsd != nullptr) { // y = act(sum + bias + residual): the residual's four pixels sit where y's will
+                        float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+                        const float *rs = rsd + (long long)(4 * i) * ys_f;
+                        if (px + 3 < nvalid_warp) {
+                            q = __ldg(reinterpret_cast<const float4 *>(rs));
+                        } else {
+                            if (px < nvalid_warp) q.x = __ldg(rs);
+                            if (px + 1 < nvalid_warp) q.y = __ldg(rs + 1);
+                            if (px + 2 < nvalid_warp) q.z = __ldg(rs + 2);
+                        }
+                        v.x = act_fn<ACT>(v.x + q.x), v.y = act_fn<ACT>(v.y + q.y), v.z = act_fn<ACT>(v.z + q.z), v.w = act_fn<ACT>(v.w + q.w);
+                    }
                     if (px + 3 < nvalid_warp) {
                         *reinterpret_cast<float4 *>(dst) = v;
                     } else {
@@ -216,21 +244,23 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, uint32_t tcross, i
     }
 }
 
-// One K stage of one tile row: fetch the 32 operands and split them into the TF32 hi/lo parts (or round them, for a
-// single pass).  Where the operands come from:
+// One K stage of one tile row: fetch the stage's operands (32, or 64 for bf16) and split them into hi/lo parts — TF32:
+// hi = top 19 bits, lo = x - hi, one value per word; bf16: hi = bf16(x), lo = bf16(x - hi), two values per word, the
+// lower K index in the low half; a single pass rounds instead.  Where the operands come from:
 //   kGatherTable   im2col through the offset table of the stage (entry < 0: no such element);
 //   kGatherFlat    the same for unpadded whole-plane raw tiles: entries carry the filter tap in bits 24..30 and `tmask`
 //                  tells which taps fall inside the input for this pixel;
-//   kGatherStride  chunks of a multiple of 32 channels: a stage is 32 consecutive channels of ONE tap, so the operands
-//                  sit `cstride` floats apart from the stage's first table entry - no table reads, no per-element tests;
-//                  chunks of 16 or 8 channels: the same with RUNS = 2 or 4 taps per stage (one table entry per run);
-//   kGatherKMajor  matmul with row-major A: row p of the 128B-swizzled [128][32] tile.
+//   kGatherStride  the stage is RUNS runs of consecutive channels, each of ONE tap, so the operands of a run sit
+//                  `cstride` floats apart from the run's first table entry - no table reads, no per-element tests;
+//   kGatherKMajor  matmul with row-major A: row p of the 128B-swizzled [128][32] tile (two tiles for a 64-wide stage).
 enum { kGatherTable = 0, kGatherFlat = 1, kGatherStride = 2, kGatherKMajor = 3 };
 template <int MODE, int PASSES, int RUNS = 1>
 __device__ __forceinline__ void gather_split(const int4 *ko, const float *raw, const uint8_t *krow, int p, uint32_t tmask,
                                              int cstride, bool flat, const float *zero_word, uint32_t (&hi)[32],
                                              uint32_t (&lo)[32]) {
-    constexpr int kRun = 32 / RUNS; // channels per run
+    constexpr bool BF = PASSES == kMathBf16x3;
+    constexpr int KE = BF ? 64 : 32;  // operands per stage
+    constexpr int kRun = KE / RUNS;   // channels per run
     const float *q[RUNS];
     int cs[RUNS];
 #pragma unroll
@@ -246,10 +276,10 @@ __device__ __forceinline__ void gather_split(const int4 *ko, const float *raw, c
         }
     }
 #pragma unroll
-    for (int c4 = 0; c4 < 8; ++c4) {
+    for (int c4 = 0; c4 < KE / 4; ++c4) {
         float v[4];
-        if (MODE == kGatherKMajor) { // 16-byte chunk c4 of row p sits at c4 ^ (p & 7)
-            const float4 t4 = *reinterpret_cast<const float4 *>(krow + ((c4 ^ (p & 7)) << 4));
+        if (MODE == kGatherKMajor) { // 16-byte chunk c of row p sits at c ^ (p & 7); the second tile follows the first
+            const float4 t4 = *reinterpret_cast<const float4 *>(krow + (c4 >> 3) * kAHalfBytes + (((c4 & 7) ^ (p & 7)) << 4));
             v[0] = t4.x, v[1] = t4.y, v[2] = t4.z, v[3] = t4.w;
         } else if (MODE == kGatherStride) {
 #pragma unroll
@@ -266,13 +296,22 @@ __device__ __forceinline__ void gather_split(const int4 *ko, const float *raw, c
                     v[i] = o[i] >= 0 ? raw[o[i]] : 0.f;
             }
         }
+        if (BF) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            if (PASSES == 3) {
-                hi[4 * c4 + i] = __float_as_uint(v[i]) & 0xffffe000u;
-                lo[4 * c4 + i] = __float_as_uint(v[i] - __uint_as_float(hi[4 * c4 + i]));
-            } else { // single pass: round to nearest TF32 instead of letting the tensor core truncate
-                hi[4 * c4 + i] = ptx::cvt_rna_tf32(v[i]);
+            for (int i = 0; i < 4; i += 2) {
+                const uint32_t h = ptx::pack_bf16x2(v[i], v[i + 1]);
+                hi[2 * c4 + i / 2] = h;
+                lo[2 * c4 + i / 2] = ptx::pack_bf16x2(v[i] - __uint_as_float(h << 16), v[i + 1] - __uint_as_float(h & 0xffff0000u));
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (PASSES == kMathTf32x3) {
+                    hi[4 * c4 + i] = __float_as_uint(v[i]) & 0xffffe000u;
+                    lo[4 * c4 + i] = __float_as_uint(v[i] - __uint_as_float(hi[4 * c4 + i]));
+                } else { // single pass: round to nearest TF32 instead of letting the tensor core truncate
+                    hi[4 * c4 + i] = ptx::cvt_rna_tf32(v[i]);
+                }
             }
         }
     }
@@ -367,6 +406,9 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     uint64_t *acc_ready = acc_full + 4; // a group of `fl` K stages has been accumulated: the main accumulator may be drained
     uint64_t *flushed = acc_full + 5;   // all eight transform warps have drained it: the MMA warp may restart it
 
+    constexpr bool SPLIT = PASSES != kMathTf32x1; // hi/lo operands, two accumulators
+    constexpr bool BF = PASSES == kMathBf16x3;
+    constexpr int KE = BF ? 64 : 32;              // K elements per stage
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     long long *prof_cta = nullptr; // wall-clock marks of this CTA (entry, prologue done, epilogue done, exit), tuning only
     if (P.prof && threadIdx.x == 96) {
@@ -404,7 +446,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         ptx::prefetch_tmap(&tmap_bhi);
         ptx::prefetch_tmap(&tmap_blo);
     }
-    for (int i = threadIdx.x; i < P.spc * kStageK; i += kThreads)
+    for (int i = threadIdx.x; i < P.spc * KE; i += kThreads)
         sKoff[i] = P.koff[i];
     if (warp == 2) {
         ptx::tmem_alloc(tmem_slot, tmem_cols);
@@ -501,10 +543,10 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 if (!ptx::mbar_wait(b_empty + sb, pb, abort_flag))
                     break;
                 uint8_t *dst = sB + (size_t)sb * 2 * b_half;
-                ptx::mbar_expect_tx(b_full + sb, (PASSES == 3 ? 2u : 1u) * b_half + (P.starve ? 64u : 0u));
-                ptx::tma_load_2d(dst, &tmap_bhi, b_full + sb, (c0 * P.spc + ks) * kStageK, row0);
-                if (PASSES == 3)
-                    ptx::tma_load_2d(dst + b_half, &tmap_blo, b_full + sb, (c0 * P.spc + ks) * kStageK, row0);
+                ptx::mbar_expect_tx(b_full + sb, (SPLIT ? 2u : 1u) * b_half + (P.starve ? 64u : 0u));
+                ptx::tma_load_2d(dst, &tmap_bhi, b_full + sb, (c0 * P.spc + ks) * KE, row0);
+                if (SPLIT)
+                    ptx::tma_load_2d(dst + b_half, &tmap_blo, b_full + sb, (c0 * P.spc + ks) * KE, row0);
                 if (++sb == P.NB) {
                     sb = 0;
                     pb ^= 1u;
@@ -522,10 +564,11 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             for (int ch = 0; ch < c1 - c0; ++ch) {
                 if (!ptx::mbar_wait(raw_empty + rb, pr, abort_flag))
                     break;
-                if (A_KMAJOR) {
-                    ptx::mbar_expect_tx(raw_full + rb, (uint32_t)kAHalfBytes);
-                    ptx::tma_load_3d(sRaw + (size_t)rb * P.raw_bytes, &tmap_x, raw_full + rb, (c0 + ch) * kStageK,
-                                     (int)blockIdx.x * kTileM, zb);
+                if (A_KMAJOR) { // one [128 rows][32 k] tile per 32 K elements of the stage (columns past K read as zero)
+                    ptx::mbar_expect_tx(raw_full + rb, (uint32_t)kAHalfBytes * (KE / 32));
+                    for (int h = 0; h < KE / 32; ++h)
+                        ptx::tma_load_3d(sRaw + (size_t)rb * P.raw_bytes + (size_t)h * kAHalfBytes, &tmap_x, raw_full + rb,
+                                         (c0 + ch) * KE + h * 32, (int)blockIdx.x * kTileM, zb);
                 } else if (P.flat) {
                     ptx::mbar_expect_tx(raw_full + rb, bytes);
                     ptx::tma_load_3d(sRaw + (size_t)rb * P.raw_bytes, &tmap_x, raw_full + rb, 0,
@@ -550,8 +593,15 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         // memory, i.e. one K-major tile of 2*BN rows, so  A_hi x [B_hi ; B_lo]  is ONE MMA of width 2*BN whose result columns
         // [0,BN) are the main accumulator and [BN,2BN) the accumulator of the cross terms; A_lo x B_hi then adds to the
         // latter.  Same tensor-pipe work, a third fewer instructions from the warp that every stage waits for.
-        const uint32_t idesc = ptx::idesc_tf32(kTileM, P.BN);
-        const uint32_t idesc_wide = ptx::idesc_tf32(kTileM, 2 * P.BN);
+        const uint32_t idesc = BF ? ptx::idesc_bf16(kTileM, P.BN) : ptx::idesc_tf32(kTileM, P.BN);
+        const uint32_t idesc_wide = BF ? ptx::idesc_bf16(kTileM, 2 * P.BN) : ptx::idesc_tf32(kTileM, 2 * P.BN);
+        // A from TMEM; per instruction K = 8 TF32 values or 16 bf16 values, either way 8 columns of A and 32 bytes of a B row
+        auto mma_ts = [](uint32_t d, uint32_t a, uint64_t b, uint32_t id, uint32_t acc) {
+            if (BF)
+                ptx::mma_bf16_ts(d, a, b, id, acc);
+            else
+                ptx::mma_tf32_ts(d, a, b, id, acc);
+        };
         const uint64_t bdesc0 = ptx::smem_desc_k128(ptx::smem_u32(sB));
         const uint64_t adesc0 = A_TMEM ? 0ull : ptx::smem_desc_k128(ptx::smem_u32(sA));
         const uint32_t b_half16 = b_half >> 4;
@@ -602,21 +652,21 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             // away from the big sum removes most of those truncations from it.
             auto issue_step = [&](int kk) {
                 const uint32_t acc_kk = kk == 0 ? accumulate : 1u;
-                if (PASSES == 3) {
+                if (SPLIT) {
                     if (A_TMEM)
-                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc_wide, acc_kk);
+                        mma_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc_wide, acc_kk);
                     else
                         ptx::mma_tf32_ss(tmem_base, ahi_s + 2 * kk, bhi + 2 * kk, idesc_wide, acc_kk);
                 } else {
-                    ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, acc_kk); // single TF32 pass
+                    mma_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, acc_kk); // single TF32 pass
                 }
                 if (kk == 0 && prev_sa >= 0) { // release the previous stage once this stage's first MMA is queued
                     ptx::mma_commit(a_empty + prev_sa);
                     ptx::mma_commit(b_empty + prev_sb);
                 }
-                if (PASSES == 3) {
+                if (SPLIT) {
                     if (A_TMEM)
-                        ptx::mma_tf32_ts(tmem_small, alo_t + kk * 8, bhi + 2 * kk, idesc, 1u);
+                        mma_ts(tmem_small, alo_t + kk * 8, bhi + 2 * kk, idesc, 1u);
                     else
                         ptx::mma_tf32_ss(tmem_small, alo_s + 2 * kk, bhi + 2 * kk, idesc, 1u);
                 }
@@ -625,13 +675,13 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             // have drained the previous group's sum.  The stage's eight cross-term MMAs do not touch the main accumulator
             // and are issued first, so the tensor pipe has work while the drain is in flight.
             auto issue_main_only = [&](int kk) {
-                ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, 1u);
+                mma_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, 1u);
                 if (kk == 0 && prev_sa >= 0) {
                     ptx::mma_commit(a_empty + prev_sa);
                     ptx::mma_commit(b_empty + prev_sb);
                 }
             };
-            const bool group_start = PASSES == 3 && FLm > 0 && ks > 0 && gpos == 0; // (no division: this warp's loop is latency bound)
+            const bool group_start = SPLIT && FLm > 0 && ks > 0 && gpos == 0; // (no division: this warp's loop is latency bound)
             const bool prepaid_now = cross_prepaid;
             cross_prepaid = false;
             if (group_start) {
@@ -639,12 +689,12 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 if (ptx::elect_one()) {
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
-                        ptx::mma_tf32_ts(tmem_small, ahi_t + kk * 8, blo + 2 * kk, idesc, 1u);
+                        mma_ts(tmem_small, ahi_t + kk * 8, blo + 2 * kk, idesc, 1u);
                         if (kk == 0 && prev_sa >= 0) {
                             ptx::mma_commit(a_empty + prev_sa);
                             ptx::mma_commit(b_empty + prev_sb);
                         }
-                        ptx::mma_tf32_ts(tmem_small, alo_t + kk * 8, bhi + 2 * kk, idesc, 1u);
+                        mma_ts(tmem_small, alo_t + kk * 8, bhi + 2 * kk, idesc, 1u);
                     }
                 }
                 __syncwarp();
@@ -659,8 +709,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                     if (ptx::elect_one()) {
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk) {
-                            ptx::mma_tf32_ts(tmem_small, nahi + kk * 8, nblo + 2 * kk, idesc, 1u);
-                            ptx::mma_tf32_ts(tmem_small, nalo + kk * 8, nbhi + 2 * kk, idesc, 1u);
+                            mma_ts(tmem_small, nahi + kk * 8, nblo + 2 * kk, idesc, 1u);
+                            mma_ts(tmem_small, nalo + kk * 8, nbhi + 2 * kk, idesc, 1u);
                         }
                     }
                     __syncwarp();
@@ -677,7 +727,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 if (ptx::elect_one()) {
 #pragma unroll
                     for (int kk = 0; kk < 3; ++kk)
-                        ptx::mma_tf32_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, kk == 0 ? 0u : 1u);
+                        mma_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, kk == 0 ? 0u : 1u);
                 }
                 __syncwarp();
             } else if (prepaid_now) { // the cross terms of this stage were issued with the previous stage's
@@ -697,12 +747,12 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             }
             ready_next = (ks + 1 < KS) && ptx::mbar_test_wait(a_full + nsa, npa) && ptx::mbar_test_wait(b_full + nsb, npb);
             ready_next = __all_sync(0xffffffffu, ready_next);
-            const bool group_end = PASSES == 3 && FLm > 0 && gpos == FLm - 1 && ks + 1 < KS;
+            const bool group_end = SPLIT && FLm > 0 && gpos == FLm - 1 && ks + 1 < KS;
             if (++gpos == FLm)
                 gpos = 0, ++gidx;
             if (ptx::elect_one()) {
                 if (group_start)
-                    ptx::mma_tf32_ts(tmem_base, ahi_t + 24, bhi + 6, idesc, 1u);
+                    mma_ts(tmem_base, ahi_t + 24, bhi + 6, idesc, 1u);
                 else if (prepaid_now)
                     issue_main_only(3);
                 else
@@ -786,8 +836,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         // eight transform warps add the main accumulator to the running total in TMEM (round-to-nearest fp32 adds, in
         // group order) and the MMA warp restarts the main accumulator for group g + 1.  A warp drains the columns its set
         // stores in the epilogue, of its own lane quarter.
-        const bool reg_total = PASSES == 3 && A_TMEM && P.fl > 0 && P.fl_regs != 0;
-        const int FL = (PASSES == 3 && A_TMEM && !reg_total) ? P.fl : 0;
+        const bool reg_total = SPLIT && A_TMEM && P.fl > 0 && P.fl_regs != 0;
+        const int FL = (SPLIT && A_TMEM && !reg_total) ? P.fl : 0;
         const int n_groups = FL > 0 ? (KS + FL - 1) / FL : 1;
         const int fcol0 = tset == 0 ? 0 : ((P.BN / 32 + 1) / 2) * 32, fcol1 = tset == 0 ? ((P.BN / 32 + 1) / 2) * 32 : P.BN;
         int fg = 0; // next group this warp has to drain
@@ -898,7 +948,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 }
                 if (!alive)
                     break;
-                const int4 *ko = reinterpret_cast<const int4 *>(sKoff + st * kStageK);
+                const int4 *ko = reinterpret_cast<const int4 *>(sKoff + st * KE);
                 if (!A_TMEM) {
                     const long long ce0 = P.prof ? clock64() : 0;
                     alive = ptx::mbar_wait(a_empty + sa, pa, abort_flag);
@@ -916,13 +966,15 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                     const long long cg0 = P.prof ? clock64() : 0;
                     if (A_KMAJOR)
                         gather_split<kGatherKMajor, PASSES>(ko, raw, krow, p, tmask, 0, false, zero_word, hi, lo);
-                    else if (P.cstride)
-                        if (P.gruns == 1)
+                    else if (P.cstride) // runs per stage: 1, 2 or 4 of 32 TF32 values; 2, 4 or 8 of 64 bf16 values
+                        if (!BF && P.gruns == 1)
                             gather_split<kGatherStride, PASSES, 1>(ko, raw, krow, p, tmask, P.cstride, P.flat != 0, zero_word, hi, lo);
                         else if (P.gruns == 2)
                             gather_split<kGatherStride, PASSES, 2>(ko, raw, krow, p, tmask, P.cstride, P.flat != 0, zero_word, hi, lo);
-                        else
+                        else if (!BF || P.gruns == 4)
                             gather_split<kGatherStride, PASSES, 4>(ko, raw, krow, p, tmask, P.cstride, P.flat != 0, zero_word, hi, lo);
+                        else
+                            gather_split<kGatherStride, PASSES, 8>(ko, raw, krow, p, tmask, P.cstride, P.flat != 0, zero_word, hi, lo);
                     else if (P.flat)
                         gather_split<kGatherFlat, PASSES>(ko, raw, krow, p, tmask, 0, true, zero_word, hi, lo);
                     else
@@ -939,7 +991,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                         t_we += cg1 - ce0;
                         t_g -= cg1 - ce0; // the gather time below is measured up to cg1
                     }
-                    if (PASSES == 3)
+                    if (SPLIT)
                         ptx::tmem_st_32x32(t + 32u, lo);
                     ptx::tmem_st_wait();
                     ptx::tc_fence_before();
@@ -989,6 +1041,41 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         }
         // ---------------- epilogue ----------------
         const long long t_loop = P.prof ? clock64() - t_begin : 0;
+        // Addresses and store mode first: the MMA warp is still working through the last stages, so this costs nothing.
+        const bool vec_ok = (P.ys_f == 1) && ((P.ys_p & 3) == 0) && ((P.ys_n & 3) == 0) && ((P.Fg & 3) == 0) &&
+                            ((reinterpret_cast<uintptr_t>(P.y) & 15) == 0);
+        const int f_tile0 = ntile * P.BN;
+        const long long f_glob0 = P.z_is_batch ? 0 : (long long)zb * P.Fg;
+        float *yp = P.y + y_off + f_glob0 * P.ys_f;
+        const float *bp = (P.has_bias && P.ksplit == 1) ? P.bias + f_glob0 : nullptr;
+        const float *rp = (P.res != nullptr && P.ksplit == 1) ? P.res + y_off + f_glob0 * P.ys_f : nullptr;
+        // split-K: partial sums go to the landing areas of the cluster's CTAs, summed after the role branches
+        const int split_cols = P.BN / P.ksplit, split_shift = 31 - __clz(split_cols);
+        const uint32_t split_addr =
+            P.ksplit > 1 ? ptx::smem_u32(sSplit) + (uint32_t)(((int)ptx::cluster_ctarank() * split_cols) * kTileM + p) * 4u : 0u;
+        const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (FL > 0 ? 2u * (uint32_t)P.BN : 0u);
+        const uint32_t tcross = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)P.BN;
+        // staged 16-byte stores need: pixel-contiguous NCHW output, full-width rows (no column window), one plane per
+        // tile, 16-byte aligned runs (of y and of the residual, which is laid out like y)
+        float *stage = nullptr;
+        int nvalid_warp = 0;
+        const long long plane_elems = (long long)P.OD * P.OH * P.OW;
+        const long long y_off0 = __shfl_sync(0xffffffffu, y_off, 0);
+        float *ybase_warp = yp - y_off + y_off0;
+        const float *rbase_warp = rp != nullptr ? rp - y_off + y_off0 : nullptr;
+        if (P.ys_p == 1 && P.ipt == 1 && P.own == P.OW && P.ow0 == 0 && (plane_elems & 3) == 0 && (P.ys_n & 3) == 0 &&
+            ((P.OH * P.OW) & 3) == 0 && (!P.wide || (P.OW & 3) == 0) &&
+            (P.ys_f & 3) == 0 && ((P.oh0 * P.OW) & 3) == 0 && P.ksplit == 1 &&
+            (reinterpret_cast<uintptr_t>(P.y) & 15) == 0 && (reinterpret_cast<uintptr_t>(P.res) & 15) == 0 && !P.epi_direct) {
+            nvalid_warp = __popc(__ballot_sync(0xffffffffu, valid));
+            if (nvalid_warp > 0)
+                stage = reinterpret_cast<float *>(sB) + (warp - 3) * 1024; // B stages are idle once the accumulator is complete
+            if ((uint32_t)(warp - 3 + 1) * 4096u > (uint32_t)P.NB * (SPLIT ? 2u : 1u) * b_half)
+                stage = nullptr; // not enough idle shared memory for this warp's block
+        }
+        // the two sets split the tile's columns (whole 32-column blocks)
+        const int nblk = P.BN / 32, half_blk = (nblk + 1) / 2;
+        const int col0 = tset == 0 ? 0 : half_blk * 32, col1 = tset == 0 ? half_blk * 32 : P.BN;
         for (; fg < n_groups - 1 && alive; ++fg)
             alive = drain_group(fg, true, true);
         if (alive)
@@ -1000,44 +1087,11 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             ptx::tc_fence_after();
         }
         const long long t_epi0 = P.prof ? clock64() : 0;
-        const bool vec_ok = (P.ys_f == 1) && ((P.ys_p & 3) == 0) && ((P.ys_n & 3) == 0) && ((P.Fg & 3) == 0) &&
-                            ((reinterpret_cast<uintptr_t>(P.y) & 15) == 0);
         if (alive) {
             ptx::tc_fence_after();
-            const int f_tile0 = ntile * P.BN;
-            const long long f_glob0 = P.z_is_batch ? 0 : (long long)zb * P.Fg;
-            float *yp = P.y + y_off + f_glob0 * P.ys_f;
-            const float *bp = (P.has_bias && P.ksplit == 1) ? P.bias + f_glob0 : nullptr;
-            const float *rp = (P.res != nullptr && P.ksplit == 1) ? P.res + y_off + f_glob0 * P.ys_f : nullptr;
-            // split-K: partial sums go to the landing areas of the cluster's CTAs, summed after the role branches
-            const int split_cols = P.BN / P.ksplit, split_shift = 31 - __clz(split_cols);
-            const uint32_t split_addr =
-                P.ksplit > 1 ? ptx::smem_u32(sSplit) + (uint32_t)(((int)ptx::cluster_ctarank() * split_cols) * kTileM + p) * 4u : 0u;
-            const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (FL > 0 ? 2u * (uint32_t)P.BN : 0u);
-            const uint32_t tcross = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)P.BN;
-            // staged 16-byte stores need: pixel-contiguous NCHW output, full-width rows (no column window), one plane per
-            // tile, 16-byte aligned runs
-            float *stage = nullptr;
-            int nvalid_warp = 0;
-            const long long plane_elems = (long long)P.OD * P.OH * P.OW;
-            const long long y_off0 = __shfl_sync(0xffffffffu, y_off, 0);
-            float *ybase_warp = yp - y_off + y_off0;
-            if (P.ys_p == 1 && P.ipt == 1 && P.own == P.OW && P.ow0 == 0 && (plane_elems & 3) == 0 && (P.ys_n & 3) == 0 &&
-                ((P.OH * P.OW) & 3) == 0 && (!P.wide || (P.OW & 3) == 0) &&
-                (P.ys_f & 3) == 0 && ((P.oh0 * P.OW) & 3) == 0 && P.ksplit == 1 && P.res == nullptr &&
-                (reinterpret_cast<uintptr_t>(P.y) & 15) == 0) {
-                nvalid_warp = __popc(__ballot_sync(0xffffffffu, valid));
-                if (nvalid_warp > 0)
-                    stage = reinterpret_cast<float *>(sB) + (warp - 3) * 1024; // B stages are idle once the accumulator is complete
-                if ((uint32_t)(warp - 3 + 1) * 4096u > (uint32_t)P.NB * (PASSES == 3 ? 2u : 1u) * b_half)
-                    stage = nullptr; // not enough idle shared memory for this warp's block
-            }
-            // the two sets split the tile's columns (whole 32-column blocks)
-            const int nblk = P.BN / 32, half_blk = (nblk + 1) / 2;
-            const int col0 = tset == 0 ? 0 : half_blk * 32, col1 = tset == 0 ? half_blk * 32 : P.BN;
 #define PETB200_EPI(ACT_)                                                                                              \
     epilogue_store<ACT_, PASSES>(tacc, tcross, P.BN, f_tile0, P.Fg, valid, bp, rp, yp, P.ys_f, vec_ok, stage, nvalid_warp, \
-                                 ybase_warp, col0, col1, split_addr, split_shift)
+                                 ybase_warp, rbase_warp, col0, col1, split_addr, split_shift)
             switch (P.ksplit > 1 ? PETB200_ACT_NONE : P.act) {
             case PETB200_ACT_RELU: PETB200_EPI(PETB200_ACT_RELU); break;
             case PETB200_ACT_SIGMOID: PETB200_EPI(PETB200_ACT_SIGMOID); break;
@@ -1118,8 +1172,22 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
 // weight packing: W[F][cpg][T] (conv) or B[b][k][n] / B[b][n][k] (matmul) -> hi/lo [rows][Ktot], K ordered as the
 // kernel consumes it: k = chunk*Kc_pad + tap*BC + ci, zero where there is no such element.
 // -------------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) k_pack_conv_w(const float *__restrict__ w, float *__restrict__ hi,
-                                                     float *__restrict__ lo, int F, int cpg, int T, int BC, int Kc_pad,
+// hi/lo parts of one packed value: TF32 (hi = top 19 bits, or rounded for a single pass) as fp32 words, or bf16 halves
+template <bool BF> __device__ __forceinline__ void store_split(void *hi, void *lo, long long i, float v, int rna) {
+    if (BF) {
+        const uint32_t h = ptx::pack_bf16x2(v, 0.f) & 0xffffu;
+        reinterpret_cast<uint16_t *>(hi)[i] = (uint16_t)h;
+        reinterpret_cast<uint16_t *>(lo)[i] = (uint16_t)(ptx::pack_bf16x2(v - __uint_as_float(h << 16), 0.f) & 0xffffu);
+    } else {
+        const float h = rna ? __uint_as_float(ptx::cvt_rna_tf32(v)) : __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+        reinterpret_cast<float *>(hi)[i] = h;
+        reinterpret_cast<float *>(lo)[i] = v - h;
+    }
+}
+
+template <bool BF>
+__global__ void __launch_bounds__(256) k_pack_conv_w(const float *__restrict__ w, void *__restrict__ hi,
+                                                     void *__restrict__ lo, int F, int cpg, int T, int BC, int Kc_pad,
                                                      int nchunks, int rna) {
     const long long Ktot = (long long)Kc_pad * nchunks;
     const long long total = (long long)F * Ktot;
@@ -1132,14 +1200,13 @@ __global__ void __launch_bounds__(256) k_pack_conv_w(const float *__restrict__ w
         float v = 0.f;
         if (tap < T && c < cpg)
             v = __ldg(w + ((long long)f * cpg + c) * T + tap);
-        const float h = rna ? __uint_as_float(ptx::cvt_rna_tf32(v)) : __uint_as_float(__float_as_uint(v) & 0xffffe000u);
-        hi[i] = h;
-        lo[i] = v - h;
+        store_split<BF>(hi, lo, i, v, rna);
     }
 }
 
-__global__ void __launch_bounds__(256) k_pack_mm_b(const float *__restrict__ b, float *__restrict__ hi,
-                                                   float *__restrict__ lo, int bs, int n, int k, int Kpad, int transB, int rna,
+template <bool BF>
+__global__ void __launch_bounds__(256) k_pack_mm_b(const float *__restrict__ b, void *__restrict__ hi,
+                                                   void *__restrict__ lo, int bs, int n, int k, int Kpad, int transB, int rna,
                                                    long long sb_batch, long long sb_row) {
     pdl_prologue();
     const long long total = (long long)bs * n * Kpad;
@@ -1151,9 +1218,7 @@ __global__ void __launch_bounds__(256) k_pack_mm_b(const float *__restrict__ b, 
         float v = 0.f;
         if (kk < k)
             v = transB ? __ldg(b + bb * sb_batch + nn * sb_row + kk) : __ldg(b + bb * sb_batch + kk * sb_row + nn);
-        const float h = rna ? __uint_as_float(ptx::cvt_rna_tf32(v)) : __uint_as_float(__float_as_uint(v) & 0xffffe000u);
-        hi[i] = h;
-        lo[i] = v - h;
+        store_split<BF>(hi, lo, i, v, rna);
     }
 }
 
@@ -1176,11 +1241,17 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
+static int env_int_early(const char *name, int dflt) {
+    const char *v = getenv(name);
+    return v ? atoi(v) : dflt;
+}
+
 struct TcCore {
     petb200_ctx *ctx = nullptr;
     IgemmParams P{};
     bool a_tmem = false;
     int single_pass = 0;
+    int bf16 = 0; // error-compensated bf16 (64 K elements per stage) instead of TF32
     dim3 grid;
     size_t smem = 0;
     // geometry needed to (re)encode the activation map
@@ -1198,10 +1269,12 @@ struct TcCore {
 
     void (*kernel() const)(CUtensorMap, CUtensorMap, CUtensorMap, IgemmParams) {
         if (single_pass)
-            return P.a_kmajor ? k_igemm<true, true, 1> : k_igemm<true, false, 1>;
+            return P.a_kmajor ? k_igemm<true, true, kMathTf32x1> : k_igemm<true, false, kMathTf32x1>;
+        if (bf16)
+            return P.a_kmajor ? k_igemm<true, true, kMathBf16x3> : k_igemm<true, false, kMathBf16x3>;
         if (P.a_kmajor)
-            return k_igemm<true, true, 3>;
-        return a_tmem ? k_igemm<true, false, 3> : k_igemm<false, false, 3>;
+            return k_igemm<true, true, kMathTf32x3>;
+        return a_tmem ? k_igemm<true, false, kMathTf32x3> : k_igemm<false, false, kMathTf32x3>;
     }
     int encode_x(const float *x) {
         if (x == map_x_ptr)
@@ -1254,11 +1327,12 @@ struct TcCore {
         if (!enc)
             return fail(ctx, PETB200_ERR_CUDA, "cuTensorMapEncodeTiled entry point unavailable");
         cuuint64_t dims[2] = {(cuuint64_t)Ktot, (cuuint64_t)rows_b};
-        cuuint64_t str[1] = {(cuuint64_t)Ktot * 4};
-        cuuint32_t box[2] = {(cuuint32_t)kStageK, (cuuint32_t)P.BN};
+        cuuint64_t str[1] = {(cuuint64_t)Ktot * (bf16 ? 2 : 4)};
+        cuuint32_t box[2] = {(cuuint32_t)P.ke, (cuuint32_t)P.BN}; // one 128-byte row of K per filter
         cuuint32_t es[2] = {1, 1};
         for (int i = 0; i < 2; ++i) {
-            CUresult r = enc(i ? &map_blo : &map_bhi, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, i ? wlo.p : whi.p, dims, str, box,
+            CUresult r = enc(i ? &map_blo : &map_bhi, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                             i ? wlo.p : whi.p, dims, str, box,
                              es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r != CUDA_SUCCESS)
@@ -1278,6 +1352,7 @@ struct TcCore {
         p.status = ctx->d_status;
         p.prof = prof;
         p.starve = starve;
+        p.epi_direct = env_int_early("PETB200_TC_EPI_DIRECT", 0);
         p.has_bias = (P.has_bias && bias) ? 1 : 0;
         void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, IgemmParams) = kernel();
         cudaLaunchConfig_t cfg{};
@@ -1371,7 +1446,7 @@ static void choose_flush(TcCore &core) {
     P.fl = (!core.single_pass && core.a_tmem && period > 0 && ks_max > 2 * period) ? period : 0;
     // register totals make one transform set do all the A stages: only where the gather is the cheap kind (whole 32-channel
     // stages of one tap, or row-major matmul tiles); slower gathers need both sets and keep the total in TMEM
-    const bool fast_gather = P.a_kmajor || (P.cstride != 0 && P.gruns == 1);
+    const bool fast_gather = P.a_kmajor || (P.cstride != 0 && P.gruns == (core.bf16 ? 2 : 1));
     const int regs_env = env_int("PETB200_TC_FLUSH_REGS", -1);
     P.fl_regs = (P.fl > 0 && P.BN == 128 && (regs_env < 0 ? fast_gather : regs_env != 0)) ? 1 : 0;
     P.a_col = (P.fl > 0 && P.BN == 128 && !P.fl_regs) ? 384 : 256;
@@ -1398,6 +1473,10 @@ static int raise_smem_limit(petb200_ctx *ctx) {
         e = cudaFuncSetAttribute(k_igemm<true, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(k_igemm<true, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(k_igemm<true, false, kMathBf16x3>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(k_igemm<true, true, kMathBf16x3>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
     if (e != cudaSuccess)
         return fail(ctx, PETB200_ERR_CUDA, "cudaFuncSetAttribute(%d bytes) failed: %s", lim, cudaGetErrorString(e));
     attr_set = true;
@@ -1412,6 +1491,7 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     if (!flat && g.Wst % 4 != 0)
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "the TMA box needs a row pitch divisible by 4, got %d", g.Wst);
     P.flat = flat ? 1 : 0;
+    P.ke = core.bf16 ? 64 : kStageK;
     P.xD = g.D, P.xH = g.H, P.xW = g.W;
     for (int i = 0; i < 3; ++i)
         P.T3[i] = g.T3[i], P.dil[i] = g.dil[i];
@@ -1493,7 +1573,7 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "raw activation box %dx%dx%dx%d exceeds the TMA box limit", P.RN, P.RD, P.RH, P.RW);
     }
     const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 1024; // alignment slack
-    core.a_tmem = core.single_pass || env_int("PETB200_TC_A_TMEM", 1) != 0; // the single-pass variant exists for TS only
+    core.a_tmem = core.single_pass || core.bf16 || env_int("PETB200_TC_A_TMEM", 1) != 0; // other variants exist for TS only
     const int forced_bc = force_bc > 0 ? force_bc : env_int("PETB200_TC_BC", 0);
     // Channels per chunk (32, or more for filters with few taps so that one raw tile still feeds several K stages) and
     // ring depths for a given tile width; false if not even one channel's raw tile fits.
@@ -1507,7 +1587,7 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
             BC = std::min(forced_bc, cpg);
         for (;; BC = std::max(1, BC / 2)) {
             P.BC = BC;
-            P.spc = (T * BC + kStageK - 1) / kStageK;
+            P.spc = (T * BC + P.ke - 1) / P.ke;
             P.nchunks = (cpg + BC - 1) / BC;
             size_t raw = (size_t)P.RN * BC * P.RD * P.RH * P.RW * 4;
             P.raw_bytes = (int)((raw + 127) / 128 * 128);
@@ -1595,7 +1675,8 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     if (!have)
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "raw activation tile does not fit shared memory");
     P = bestP;
-    P.gruns = P.BC % kStageK == 0 ? 1 : (P.BC == 16 ? 2 : (P.BC == 8 ? 4 : 0));
+    // runs of consecutive channels (of one filter tap) per K stage, when the chunk size allows that kind of gather
+    P.gruns = P.BC % kStageK == 0 ? P.ke / kStageK : (P.BC == 16 ? P.ke / 16 : (P.BC == 8 ? P.ke / 8 : 0));
     P.cstride = (P.gruns && env_int("PETB200_TC_TABLE", 0) == 0) ? P.RD * P.RH * P.RW : 0;
     choose_flush(core);
     if (flat && (!core.a_tmem || (long long)P.RN * P.BC * P.RD * P.RH * P.RW >= (1 << 24)))
@@ -1609,14 +1690,14 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     if (z_is_batch)
         core.y_elems = (long long)images * ys_n;
     core.grid = dim3((unsigned)mtiles, (unsigned)(ntiles * P.ksplit), (unsigned)gz);
-    core.Ktot = (long long)P.nchunks * P.spc * kStageK;
+    core.Ktot = (long long)P.nchunks * P.spc * P.ke;
     core.xd[0] = g.Wst;
     core.xd[1] = g.H;
     core.xd[2] = g.D;
     core.xd[3] = g.C;
     core.xd[4] = g.N;
     // offset table for one chunk
-    std::vector<int> koff((size_t)P.spc * kStageK, -1);
+    std::vector<int> koff((size_t)P.spc * P.ke, -1);
     const int plane_w = P.RW, plane_h = P.RH * P.RW, plane_d = P.RD * plane_h;
     for (int tap = 0; tap < T; ++tap) {
         int t = tap / (g.T3[1] * g.T3[2]), r = (tap / g.T3[2]) % g.T3[1], s = tap % g.T3[2];
@@ -1686,7 +1767,8 @@ int tc_conv_create(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const i
     t->has_bias = has_bias;
     t->act = act;
     t->full.ctx = ctx;
-    t->full.single_pass = passes == 1;
+    t->full.single_pass = passes == kMathTf32x1;
+    t->full.bf16 = passes == kMathBf16x3;
     const long long plane = (long long)g.OD * g.OH * g.OW;
     t->ys[0] = (long long)g.F * plane;
     t->ys[1] = channels_last_out ? 1 : plane;
@@ -1709,7 +1791,7 @@ int tc_conv_create(petb200_ctx *ctx, int nsp, const int *in_dims, int f, const i
     }
     TcCore &c = t->full;
     c.rows_b = g.F;
-    size_t wbytes = (size_t)g.F * c.Ktot * 4;
+    size_t wbytes = (size_t)g.F * c.Ktot * (c.bf16 ? 2 : 4);
     if (c.whi.alloc(wbytes) != cudaSuccess || c.wlo.alloc(wbytes) != cudaSuccess) {
         delete t;
         return fail(ctx, PETB200_ERR_NOMEM, "packed weight allocation (%zu bytes) failed", 2 * wbytes);
@@ -1747,7 +1829,8 @@ int tc_conv_create_view(petb200_ctx *ctx, int n, int c, int h, int w, int f, int
     t->has_bias = has_bias;
     t->act = act;
     t->full.ctx = ctx;
-    t->full.single_pass = passes == 1;
+    t->full.single_pass = passes == kMathTf32x1;
+    t->full.bf16 = passes == kMathBf16x3;
     t->ys[0] = ys_n, t->ys[1] = ys_f, t->ys[2] = ys_p;
     int rc = PETB200_ERR_UNSUPPORTED;
     if (w % 4 != 0)
@@ -1760,7 +1843,7 @@ int tc_conv_create_view(petb200_ctx *ctx, int n, int c, int h, int w, int f, int
     }
     TcCore &core = t->full;
     core.rows_b = f;
-    const size_t wbytes = (size_t)f * core.Ktot * 4;
+    const size_t wbytes = (size_t)f * core.Ktot * (core.bf16 ? 2 : 4);
     if (core.whi.alloc(wbytes) != cudaSuccess || core.wlo.alloc(wbytes) != cudaSuccess) {
         delete t;
         return fail(ctx, PETB200_ERR_NOMEM, "packed weight allocation (%zu bytes) failed", 2 * wbytes);
@@ -1783,8 +1866,11 @@ int tc_conv_set_weights(void *h, const float *w, cudaStream_t s) {
     const int cpg = t->g.C / t->g.groups, T = t->g.T3[0] * t->g.T3[1] * t->g.T3[2];
     long long total = (long long)t->g.F * c.Ktot;
     int blocks = (int)std::min<long long>((total + 255) / 256, (long long)c.ctx->sm_count * 16);
-    k_pack_conv_w<<<blocks, 256, 0, s>>>(w, (float *)c.whi.p, (float *)c.wlo.p, t->g.F, cpg, T, c.P.BC, c.P.spc * kStageK,
-                                         c.P.nchunks, c.single_pass);
+    if (c.bf16)
+        k_pack_conv_w<true><<<blocks, 256, 0, s>>>(w, c.whi.p, c.wlo.p, t->g.F, cpg, T, c.P.BC, c.P.spc * c.P.ke, c.P.nchunks, 0);
+    else
+        k_pack_conv_w<false><<<blocks, 256, 0, s>>>(w, c.whi.p, c.wlo.p, t->g.F, cpg, T, c.P.BC, c.P.spc * c.P.ke, c.P.nchunks,
+                                                    c.single_pass);
     c.weights_ready = true;
     return launched(c.ctx, "k_pack_conv_w");
 }
@@ -1804,6 +1890,7 @@ int tc_conv_run(void *h, const float *x, const float *bias, const float *res, fl
         wc = new TcCore();
         wc->ctx = t->full.ctx;
         wc->single_pass = t->full.single_pass;
+        wc->bf16 = t->full.bf16;
         // A window must consume K in exactly the order of the full operator (same BC / chunking), otherwise the
         // two would round differently; the raw box only shrinks for a window, so the full plan's BC always fits.
         int rc = tc_configure(wc->ctx, *wc, g, win[0], win[1], win[2], win[3], 0, g.N, t->ys[0], t->ys[1], t->ys[2],
@@ -1845,7 +1932,7 @@ int tc_set_wait_limit_ns(unsigned long long ns) {
 int tc_conv_row_pitch(void *h) { return ((TcConv *)h)->g.Wst; }
 const char *tc_conv_variant(void *h) {
     const TcCore &c = ((TcConv *)h)->full;
-    return c.single_pass ? "tc_1xtf32_ts" : (c.a_tmem ? "tc_3xtf32_ts" : "tc_3xtf32_ss");
+    return c.single_pass ? "tc_1xtf32_ts" : (c.bf16 ? "tc_bf16x3_ts" : (c.a_tmem ? "tc_3xtf32_ts" : "tc_3xtf32_ss"));
 }
 
 // ---- matmul on the same kernel ------------------------------------------------------------------------------
@@ -1866,14 +1953,15 @@ static int tc_configure_kmajor(petb200_ctx *ctx, TcCore &core, int bs, int m, in
     memset(&P, 0, sizeof P);
     core.a_tmem = true;
     P.a_kmajor = 1;
+    P.ke = core.bf16 ? 64 : kStageK;
     P.m_rows = m;
     P.z_is_batch = 1;
     P.OD = P.OH = 1, P.OW = m, P.ohn = 1, P.own = m, P.Pw = m, P.units = 1, P.ipt = 1, P.tpi = (m + kTileM - 1) / kTileM;
     P.sd = P.sh = P.sw = 1;
     P.cpg = k, P.Fg = n;
-    P.BC = kStageK, P.spc = 1, P.nchunks = (k + kStageK - 1) / kStageK;
+    P.BC = P.ke, P.spc = 1, P.nchunks = (k + P.ke - 1) / P.ke;
     P.RN = P.RD = 1, P.RH = kTileM, P.RW = kStageK;
-    P.raw_bytes = kAHalfBytes;
+    P.raw_bytes = kAHalfBytes * (P.ke / kStageK); // one [128][32] fp32 tile per 32 K elements of a stage
     P.ys_n = st[4], P.ys_f = 1, P.ys_p = st[5];
     core.a_batch = st[0], core.a_row = st[1];
     P.has_bias = has_bias, P.act = act;
@@ -1921,9 +2009,9 @@ static int tc_configure_kmajor(petb200_ctx *ctx, TcCore &core, int bs, int m, in
     }
     choose_flush(core);
     core.smem = smem_layout(P, true).total + 1024;
-    core.Ktot = (long long)P.nchunks * kStageK;
+    core.Ktot = (long long)P.nchunks * P.ke;
     core.xd[0] = k, core.xd[1] = m, core.xd[2] = bs;
-    std::vector<int> koff(kStageK, -1); // unused in this mode; the kernel still copies one stage worth of table
+    std::vector<int> koff(P.ke, -1); // unused in this mode; the kernel still copies one stage worth of table
     if (core.koff.alloc(koff.size() * 4) != cudaSuccess)
         return fail(ctx, PETB200_ERR_NOMEM, "koff allocation failed");
     PETB200_CUDA(ctx, cudaMemcpy(core.koff.p, koff.data(), koff.size() * 4, cudaMemcpyHostToDevice));
@@ -1944,7 +2032,8 @@ int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, 
     t->k = k;
     t->transB = transB;
     t->core.ctx = ctx;
-    t->core.single_pass = passes == 1;
+    t->core.single_pass = passes == kMathTf32x1;
+    t->core.bf16 = passes == kMathBf16x3;
     const long long dense[6] = {(long long)m * k, transA ? m : k, (long long)k * n, transB ? k : n, (long long)m * n, n};
     for (int i = 0; i < 6; ++i)
         t->st[i] = strides ? strides[i] : dense[i];
@@ -1981,13 +2070,13 @@ int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, 
         return rc;
     }
     TcCore &c = t->core;
-    if (c.P.nchunks > 1 && c.P.spc * kStageK != c.P.BC) { // the packing below assumes k = chunk * BC + ci
+    if (c.P.nchunks > 1 && c.P.spc * c.P.ke != c.P.BC) { // the packing below assumes k = chunk * BC + ci
         delete t;
         return fail(ctx, PETB200_ERR_UNSUPPORTED, "matmul K chunking diverged from the packing order");
     }
     c.rows_b = bs * n;
     // rows of different batch entries are adjacent: Fg = n rows per z
-    size_t wbytes = (size_t)bs * n * c.Ktot * 4;
+    size_t wbytes = (size_t)bs * n * c.Ktot * (c.bf16 ? 2 : 4);
     if (c.whi.alloc(wbytes) != cudaSuccess || c.wlo.alloc(wbytes) != cudaSuccess) {
         delete t;
         return fail(ctx, PETB200_ERR_NOMEM, "packed B allocation failed");
@@ -2009,8 +2098,11 @@ int tc_matmul_pack_b(void *h, const float *b, cudaStream_t s) {
     TcCore &c = t->core;
     long long total = (long long)t->bs * t->n * c.Ktot;
     int blocks = (int)std::min<long long>((total + 255) / 256, (long long)c.ctx->sm_count * 16);
-    launch_pdl(k_pack_mm_b, blocks, 256, 0, s, b, (float *)c.whi.p, (float *)c.wlo.p, t->bs, t->n, t->k, (int)c.Ktot, t->transB, c.single_pass,
-               t->st[2], t->st[3]);
+    if (c.bf16)
+        launch_pdl(k_pack_mm_b<true>, blocks, 256, 0, s, b, c.whi.p, c.wlo.p, t->bs, t->n, t->k, (int)c.Ktot, t->transB, 0, t->st[2], t->st[3]);
+    else
+        launch_pdl(k_pack_mm_b<false>, blocks, 256, 0, s, b, c.whi.p, c.wlo.p, t->bs, t->n, t->k, (int)c.Ktot, t->transB, c.single_pass,
+                   t->st[2], t->st[3]);
     c.weights_ready = true;
     return launched(c.ctx, "k_pack_mm_b");
 }

@@ -173,6 +173,14 @@ __device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, ui
                  ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
                  : "memory");
 }
+// The same with 16-bit inputs (kind::f16; the instruction descriptor says bf16): K = 16 per instruction, two K elements
+// per 32-bit TMEM column of A (lower index in the low half).
+__device__ __forceinline__ void mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
 // Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -241,6 +249,17 @@ __device__ __forceinline__ uint64_t smem_desc_k128(uint32_t smem_addr) {
 // kind::tf32, fp32 accumulate, both operands K-major, shape M x N (K = 8 per instruction).
 __host__ __device__ inline uint32_t idesc_tf32(int M, int N) {
     return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// kind::f16 with bf16 inputs (format code 1), fp32 accumulate, both operands K-major (K = 16 per instruction).
+__host__ __device__ inline uint32_t idesc_bf16(int M, int N) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+// Two fp32 values rounded to nearest bf16 and packed, `a` in the low half.
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a)); // first source -> upper half
+    return r;
 }
 
 } // namespace ptx

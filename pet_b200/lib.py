@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(_HERE, "libpetb200.so")
 
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_NOMEM, ERR_DEVICE = range(6)
 ACT = {"none": 0, None: 0, "relu": 1, "sigmoid": 2, "tanh": 3, "gelu": 4}
-ALGO = {"auto": 0, "tc_3xtf32": 1, "simt_fp32": 2, "tc_1xtf32": 3}
+ALGO = {"auto": 0, "tc_3xtf32": 1, "simt_fp32": 2, "tc_1xtf32": 3, "tc_bf16x3": 4}
 
 # every symbol include/petb200.h declares, with (restype, argtypes)
 _vp, _i, _sz, _fp = C.c_void_p, C.c_int, C.c_size_t, C.c_float
