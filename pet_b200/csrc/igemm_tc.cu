@@ -85,12 +85,17 @@ struct IgemmParams {
     float *y;
     int *status;
     long long *prof; // optional per-CTA counters (kProfSlots per CTA), for tuning only
+    int pp;          // persistent "ping-pong" mode: the grid's x extent is smaller than the number of pixel tiles (mtiles); a CTA
+                     // walks tiles blockIdx.x, + gridDim.x, ...; the two transform sets take alternate TILES (each set produces
+                     // every A stage of its tile and then stores it) and the accumulators alternate between two TMEM
+                     // regions, so one tile's epilogue and the next tile's start-up hide behind the MMAs of the other
+    int mtiles;      // pixel tiles along x
     int epi_direct;  // tuning: store the epilogue straight from registers (no transposition through shared memory)
     int starve;      // test hook: the filter producer announces more bytes than it loads, so the stage never completes
 };
 
 struct SmemLayout {
-    uint32_t a_off, b_off, raw_off, koff_off, split_off, bar_off, total;
+    uint32_t a_off, b_off, raw_off, koff_off, split_off, stage_off, bar_off, total;
 };
 __host__ __device__ inline SmemLayout smem_layout(const IgemmParams &P, bool a_tmem) {
     SmemLayout L;
@@ -107,8 +112,11 @@ __host__ __device__ inline SmemLayout smem_layout(const IgemmParams &P, bool a_t
     // own region: peers push into it while this CTA may still be in its main loop.
     L.split_off = (o + 127) & ~127u;
     o = L.split_off + (P.ksplit > 1 ? 512u * (uint32_t)P.BN + 1024u : 0u); // + each tile row's offset in y (-1: none)
+    // ping-pong mode: the epilogue's 32x32 transposition blocks need their own room (the B ring is never idle), one per warp
+    L.stage_off = (o + 127) & ~127u;
+    o = L.stage_off + (P.pp ? 8u * 4096u : 0u);
     L.bar_off = (o + 15) & ~15u;
-    L.total = L.bar_off + 320;
+    L.total = L.bar_off + 384;
     return L;
 }
 
@@ -293,7 +301,7 @@ __device__ __forceinline__ void gather_split(const int4 *ko, const float *raw, c
                 if (MODE == kGatherFlat)
                     v[i] = (o[i] >= 0 && ((tmask >> (o[i] >> 24)) & 1u)) ? raw[o[i] & 0xffffff] : 0.f;
                 else
-                    v[i] = o[i] >= 0 ? raw[o[i]] : 0.f;
+                    v[i] = raw[o[i]]; // plain table mode has no negative entries
             }
         }
         if (BF) {
@@ -380,7 +388,60 @@ __device__ __forceinline__ void cluster_reduce_store(const float *stage, int ksp
     }
 }
 
-template <bool A_TMEM, bool A_KMAJOR, int PASSES>
+// Register-total flush mode, transform set 1: its threads keep the 128 columns of their tile row in registers, add the main
+// accumulator of every completed group of K stages to them (round-to-nearest adds, in group order), and at the end write
+// total + last group back over the main accumulator, which the epilogue of both sets then reads as if nothing had happened.
+// Returns false if a wait gave up.
+__device__ __noinline__ bool drain_only_set(uint32_t tq /*TMEM address of this warp's lane quarter, column 0*/, int groups,
+                                            uint64_t *acc_ready, uint64_t *acc_full, uint64_t *flushed, volatile int *abort_flag,
+                                            int lane, long long *t_wait, long long *t_work) {
+    float racc[128];
+#pragma unroll
+    for (int j = 0; j < 128; ++j)
+        racc[j] = 0.f;
+    for (int g = 0; g < groups; ++g) {
+        const bool last = g == groups - 1;
+        const long long cd0 = t_wait ? clock64() : 0;
+        if (!(last ? ptx::mbar_wait(acc_full, 0u, abort_flag) : ptx::mbar_wait(acc_ready, (uint32_t)(g & 1), abort_flag)))
+            return false;
+        const long long cd1 = t_wait ? clock64() : 0;
+        ptx::tc_fence_after();
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            uint32_t v0[16], v1[16];
+            ptx::tmem_ld_32x16(tq + (uint32_t)(b * 32), v0);
+            ptx::tmem_ld_32x16(tq + (uint32_t)(b * 32 + 16), v1);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                racc[b * 32 + j] += __uint_as_float(v0[j]);
+                racc[b * 32 + 16 + j] += __uint_as_float(v1[j]);
+            }
+            if (last) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    v0[j] = __float_as_uint(racc[b * 32 + j]);
+                    v1[j] = __float_as_uint(racc[b * 32 + 16 + j]);
+                }
+                ptx::tmem_st_32x16(tq + (uint32_t)(b * 32), v0);
+                ptx::tmem_st_32x16(tq + (uint32_t)(b * 32 + 16), v1);
+            }
+        }
+        if (last)
+            ptx::tmem_st_wait();
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (!last && lane == 0)
+            ptx::mbar_arrive(flushed);
+        if (t_wait) {
+            *t_wait += cd1 - cd0;
+            *t_work += clock64() - cd1;
+        }
+    }
+    return true;
+}
+
+template <bool A_TMEM, bool A_KMAJOR, int PASSES, bool PP = false>
 __global__ void __launch_bounds__(kThreads, 1)
 k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_bhi,
         const __grid_constant__ CUtensorMap tmap_blo, const IgemmParams P) {
@@ -405,6 +466,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     float *zero_word = reinterpret_cast<float *>(acc_full + 3); // holds 0.0f: what a masked-off filter tap reads
     uint64_t *acc_ready = acc_full + 4; // a group of `fl` K stages has been accumulated: the main accumulator may be drained
     uint64_t *flushed = acc_full + 5;   // all eight transform warps have drained it: the MMA warp may restart it
+    uint64_t *acc_full1 = acc_full + 6; // ping-pong mode: the second accumulator region is complete
+    uint64_t *acc_empty = acc_full + 7; // [2]: the owning transform set has read accumulator region 0 / 1 out
 
     constexpr bool SPLIT = PASSES != kMathTf32x1; // hi/lo operands, two accumulators
     constexpr bool BF = PASSES == kMathBf16x3;
@@ -439,6 +502,9 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         ptx::mbar_init(acc_full, 1);
         ptx::mbar_init(acc_ready, 1);
         ptx::mbar_init(flushed, P.fl_regs ? 4 : 8);
+        ptx::mbar_init(acc_full1, 1);
+        ptx::mbar_init(acc_empty, 4);
+        ptx::mbar_init(acc_empty + 1, 4);
         *abort_flag = 0;
         *zero_word = 0.f;
         ptx::fence_mbar_init();
@@ -463,40 +529,48 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     if (prof_cta)
         prof_cta[9] = (long long)ptx::globaltimer_ns();
 
-    // Tile origin in the input: first image, depth slice, row and (16-byte aligned) column of the raw box.
-    int n_lo = 0, q0 = 0, unit0 = 0, z_start, y_start, x_start, w_zl = 0, w_yl = 0, w_tx = 0;
-    if (A_KMAJOR) {
-        z_start = y_start = x_start = 0; // the tile is rows [blockIdx.x*128, +128) of A[zb]
-    } else if (P.wide) {
-        const int row = blockIdx.x / P.row_tiles;
-        w_tx = blockIdx.x - row * P.row_tiles;
-        n_lo = row / (P.OD * P.ohn);
-        w_zl = (row / P.ohn) % P.OD;
-        w_yl = row % P.ohn;
-        z_start = w_zl * P.sd - P.pd;
-        y_start = (P.oh0 + w_yl) * P.sh - P.ph;
-        const int xs = (P.ow0 + w_tx * kTileM) * P.sw - P.pw;
-        x_start = (xs >= 0) ? (xs & ~3) : -(((-xs) + 3) & ~3);
-    } else {
-        const int tu = blockIdx.x / P.tpi;
-        q0 = (blockIdx.x - tu * P.tpi) * kTileM;
-        unit0 = tu * P.ipt;
-        n_lo = unit0 / P.OD;
-        int yl_lo, yl_hi;
-        tile_rows(P, q0, min(q0 + kTileM, P.Pw) - 1, P.ipt > 1, yl_lo, yl_hi);
-        z_start = (unit0 - n_lo * P.OD) * P.sd - P.pd;
-        y_start = (P.oh0 + yl_lo) * P.sh - P.ph;
-        x_start = P.x0;
-    }
-    if (!A_KMAJOR && P.flat)
-        z_start = y_start = x_start = 0; // the raw tile holds whole planes
+    // Tile origin in the input: first image, depth slice, row and (16-byte aligned) column of the raw box.  `bx` is the
+    // pixel-tile index: blockIdx.x, or in ping-pong mode every gridDim.x-th tile from there.
+    int bx = (int)blockIdx.x;
+    const int ntl = PP ? (P.mtiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 1; // tiles of this CTA
+    int n_lo = 0, q0 = 0, unit0 = 0, z_start = 0, y_start = 0, x_start = 0, w_zl = 0, w_yl = 0, w_tx = 0;
+    auto set_tile = [&](int tile) {
+        bx = tile;
+        n_lo = 0, q0 = 0, unit0 = 0, w_zl = 0, w_yl = 0, w_tx = 0;
+        if (A_KMAJOR) {
+            z_start = y_start = x_start = 0; // the tile is rows [bx*128, +128) of A[zb]
+        } else if (P.wide) {
+            const int row = bx / P.row_tiles;
+            w_tx = bx - row * P.row_tiles;
+            n_lo = row / (P.OD * P.ohn);
+            w_zl = (row / P.ohn) % P.OD;
+            w_yl = row % P.ohn;
+            z_start = w_zl * P.sd - P.pd;
+            y_start = (P.oh0 + w_yl) * P.sh - P.ph;
+            const int xs = (P.ow0 + w_tx * kTileM) * P.sw - P.pw;
+            x_start = (xs >= 0) ? (xs & ~3) : -(((-xs) + 3) & ~3);
+        } else {
+            const int tu = bx / P.tpi;
+            q0 = (bx - tu * P.tpi) * kTileM;
+            unit0 = tu * P.ipt;
+            n_lo = unit0 / P.OD;
+            int yl_lo, yl_hi;
+            tile_rows(P, q0, min(q0 + kTileM, P.Pw) - 1, P.ipt > 1, yl_lo, yl_hi);
+            z_start = (unit0 - n_lo * P.OD) * P.sd - P.pd;
+            y_start = (P.oh0 + yl_lo) * P.sh - P.ph;
+            x_start = P.x0;
+        }
+        if (!A_KMAJOR && P.flat)
+            z_start = y_start = x_start = 0; // the raw tile holds whole planes
+    };
+    set_tile((int)blockIdx.x);
     // Row p of this CTA's tile: is it an output pixel, where does its receptive field start in the raw tile, where does
     // it go in y.
     auto pixel_geom = [&](int p, bool &valid, int &base_p, long long &y_off) {
         base_p = 0;
         y_off = 0;
         if (A_KMAJOR) {
-            const int row = (int)blockIdx.x * kTileM + p;
+            const int row = bx * kTileM + p;
             valid = row < P.m_rows;
             y_off = (long long)zb * P.ys_n + (long long)row * P.ys_p;
         } else if (P.wide) {
@@ -539,14 +613,15 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             const int row0 = zb * P.Fg + ntile * P.BN;
             int sb = 0;
             uint32_t pb = 1; // first pass over the ring: every slot is free
-            for (int ks = 0; ks < KS; ++ks) {
+            for (int ks = 0; ks < KS * ntl; ++ks) { // the same KS filter tiles for every pixel tile of this CTA
                 if (!ptx::mbar_wait(b_empty + sb, pb, abort_flag))
                     break;
                 uint8_t *dst = sB + (size_t)sb * 2 * b_half;
                 ptx::mbar_expect_tx(b_full + sb, (SPLIT ? 2u : 1u) * b_half + (P.starve ? 64u : 0u));
-                ptx::tma_load_2d(dst, &tmap_bhi, b_full + sb, (c0 * P.spc + ks) * KE, row0);
+                const int kst = ntl > 1 ? ks % KS : ks;
+                ptx::tma_load_2d(dst, &tmap_bhi, b_full + sb, (c0 * P.spc + kst) * KE, row0);
                 if (SPLIT)
-                    ptx::tma_load_2d(dst + b_half, &tmap_blo, b_full + sb, (c0 * P.spc + ks) * KE, row0);
+                    ptx::tma_load_2d(dst + b_half, &tmap_blo, b_full + sb, (c0 * P.spc + kst) * KE, row0);
                 if (++sb == P.NB) {
                     sb = 0;
                     pb ^= 1u;
@@ -556,19 +631,25 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     } else if (warp == 2) {
         // ---------------- raw activation producer ----------------
         const int c_base = P.z_is_batch ? 0 : zb * P.cpg;
-        const int n_start = P.z_is_batch ? zb : n_lo;
         if (lane == 0) {
             const uint32_t bytes = (uint32_t)P.RN * P.BC * P.RD * P.RH * P.RW * 4u;
             int rb = 0;
             uint32_t pr = 1; // first pass over the ring: every buffer is free
+            bool go = true;
+            for (int tl = 0; tl < ntl && go; ++tl) {
+            if (tl > 0)
+                set_tile((int)blockIdx.x + tl * (int)gridDim.x);
+            const int n_start = P.z_is_batch ? zb : n_lo;
             for (int ch = 0; ch < c1 - c0; ++ch) {
-                if (!ptx::mbar_wait(raw_empty + rb, pr, abort_flag))
+                if (!ptx::mbar_wait(raw_empty + rb, pr, abort_flag)) {
+                    go = false;
                     break;
+                }
                 if (A_KMAJOR) { // one [128 rows][32 k] tile per 32 K elements of the stage (columns past K read as zero)
                     ptx::mbar_expect_tx(raw_full + rb, (uint32_t)kAHalfBytes * (KE / 32));
                     for (int h = 0; h < KE / 32; ++h)
                         ptx::tma_load_3d(sRaw + (size_t)rb * P.raw_bytes + (size_t)h * kAHalfBytes, &tmap_x, raw_full + rb,
-                                         (c0 + ch) * KE + h * 32, (int)blockIdx.x * kTileM, zb);
+                                         (c0 + ch) * KE + h * 32, bx * kTileM, zb);
                 } else if (P.flat) {
                     ptx::mbar_expect_tx(raw_full + rb, bytes);
                     ptx::tma_load_3d(sRaw + (size_t)rb * P.raw_bytes, &tmap_x, raw_full + rb, 0,
@@ -582,6 +663,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                     rb = 0;
                     pr ^= 1u;
                 }
+            }
             }
         }
     } else if (warp == 1) {
@@ -605,17 +687,40 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         const uint64_t bdesc0 = ptx::smem_desc_k128(ptx::smem_u32(sB));
         const uint64_t adesc0 = A_TMEM ? 0ull : ptx::smem_desc_k128(ptx::smem_u32(sA));
         const uint32_t b_half16 = b_half >> 4;
-        const uint32_t tmem_small = tmem_base + (uint32_t)P.BN;
+        uint32_t tmem_acc = tmem_base, tmem_small = tmem_base + (uint32_t)P.BN; // main and cross-term accumulators of the tile
         uint32_t accumulate = 0;
         int sa = 0, sb = 0, prev_sa = -1, prev_sb = -1;
         uint32_t pa = 0, pb = 0;
         long long t_wa = 0, t_wb = 0, t_wf = 0;
         const long long t_begin = P.prof ? clock64() : 0;
         bool ok = true, ready_next = false;
-        const int FLm = P.fl;
+        const int FLm = PP ? 0 : P.fl;
         int gpos = 0, gidx = 0; // position of the stage inside its flush group, index of the group
         bool cross_prepaid = false; // the current stage's cross-term MMAs were issued ahead, during the previous stage
+        // Ping-pong mode: each transform set fills its own half of the A ring (slots 2*set, 2*set + 1, alternately), so every
+        // slot's barriers see one producer in order; bit i of `apar` is the parity of slot i's next completed fill.
+        uint32_t apar = 0;
+        for (int tl = 0; tl < ntl && ok; ++tl) {
+        if (PP) {
+            // accumulators alternate between two TMEM regions; before reusing one, its previous tile must have been read out
+            tmem_acc = tmem_base + (uint32_t)((tl & 1) * 2 * P.BN);
+            tmem_small = tmem_acc + (uint32_t)P.BN;
+            if (tl >= 2) {
+                ok = ptx::mbar_wait(acc_empty + (tl & 1), (uint32_t)(((tl >> 1) - 1) & 1), abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok)
+                    break;
+                ptx::tc_fence_after();
+            }
+            accumulate = 0;
+            ready_next = false;
+            prev_sa = -1;
+        }
         for (int ks = 0; ks < KS; ++ks) {
+            if (PP) {
+                sa = (tl & 1) * 2 + (ks & 1);
+                pa = (apar >> sa) & 1u;
+            }
             if (!ready_next) { // not already seen complete by the poll issued in the shadow of the previous stage's MMAs
                 if (P.prof) {
                     const long long q0c = clock64();
@@ -643,6 +748,11 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 nsa = 0;
                 npa ^= 1u;
             }
+            if (PP) { // the next stage of this tile sits in the set's other slot
+                nsa = (tl & 1) * 2 + ((ks + 1) & 1);
+                npa = (apar >> nsa) & 1u;
+                apar ^= 1u << sa;
+            }
             if (nsb == P.NB) {
                 nsb = 0;
                 npb ^= 1u;
@@ -654,11 +764,11 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 const uint32_t acc_kk = kk == 0 ? accumulate : 1u;
                 if (SPLIT) {
                     if (A_TMEM)
-                        mma_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc_wide, acc_kk);
+                        mma_ts(tmem_acc, ahi_t + kk * 8, bhi + 2 * kk, idesc_wide, acc_kk);
                     else
-                        ptx::mma_tf32_ss(tmem_base, ahi_s + 2 * kk, bhi + 2 * kk, idesc_wide, acc_kk);
+                        ptx::mma_tf32_ss(tmem_acc, ahi_s + 2 * kk, bhi + 2 * kk, idesc_wide, acc_kk);
                 } else {
-                    mma_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, acc_kk); // single TF32 pass
+                    mma_ts(tmem_acc, ahi_t + kk * 8, bhi + 2 * kk, idesc, acc_kk); // single TF32 pass
                 }
                 if (kk == 0 && prev_sa >= 0) { // release the previous stage once this stage's first MMA is queued
                     ptx::mma_commit(a_empty + prev_sa);
@@ -675,7 +785,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             // have drained the previous group's sum.  The stage's eight cross-term MMAs do not touch the main accumulator
             // and are issued first, so the tensor pipe has work while the drain is in flight.
             auto issue_main_only = [&](int kk) {
-                mma_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, 1u);
+                mma_ts(tmem_acc, ahi_t + kk * 8, bhi + 2 * kk, idesc, 1u);
                 if (kk == 0 && prev_sa >= 0) {
                     ptx::mma_commit(a_empty + prev_sa);
                     ptx::mma_commit(b_empty + prev_sb);
@@ -727,7 +837,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 if (ptx::elect_one()) {
 #pragma unroll
                     for (int kk = 0; kk < 3; ++kk)
-                        mma_ts(tmem_base, ahi_t + kk * 8, bhi + 2 * kk, idesc, kk == 0 ? 0u : 1u);
+                        mma_ts(tmem_acc, ahi_t + kk * 8, bhi + 2 * kk, idesc, kk == 0 ? 0u : 1u);
                 }
                 __syncwarp();
             } else if (prepaid_now) { // the cross terms of this stage were issued with the previous stage's
@@ -752,7 +862,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 gpos = 0, ++gidx;
             if (ptx::elect_one()) {
                 if (group_start)
-                    mma_ts(tmem_base, ahi_t + 24, bhi + 6, idesc, 1u);
+                    mma_ts(tmem_acc, ahi_t + 24, bhi + 6, idesc, 1u);
                 else if (prepaid_now)
                     issue_main_only(3);
                 else
@@ -786,9 +896,10 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 ptx::mma_commit(b_empty + prev_sb);
             }
             if (ok)
-                ptx::mma_commit(acc_full);
+                ptx::mma_commit((PP && (tl & 1)) ? acc_full1 : acc_full);
         }
         __syncwarp();
+        }
         if (lane == 0 && P.prof) {
             long long *pr = P.prof + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * kProfSlots;
             pr[0] = t_wa;
@@ -803,6 +914,33 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         const int tset = (warp - 3) >> 2;     // 0 or 1
         const int quarter = warp & 3;         // TMEM lane quarter this warp may access
         const int p = quarter * 32 + lane;    // pixel row inside the tile
+        bool alive = true;
+        long long t_we = 0, t_wr = 0, t_g = 0, t_st = 0, t_dw = 0, t_dd = 0, t_loop = 0, t_epi0 = 0;
+        const long long t_begin = P.prof ? clock64() : 0;
+        const bool reg_total = !PP && SPLIT && A_TMEM && P.fl > 0 && P.fl_regs != 0; // (ping-pong plans never flush)
+        const int FL = (!PP && SPLIT && A_TMEM && !reg_total) ? P.fl : 0;
+        // Register-total mode: set 1 only drains (a function of its own: its 128 totals per thread want the whole register file)
+        if (reg_total && tset == 1)
+            alive = drain_only_set(tmem_base + ((uint32_t)(quarter * 32) << 16), (KS + P.fl - 1) / P.fl, acc_ready, acc_full, flushed,
+                                   abort_flag, lane, P.prof ? &t_dw : nullptr, P.prof ? &t_dd : nullptr);
+        // Ping-pong mode: this set takes every second TILE of the CTA (set 0 the even ones) and produces all of its stages;
+        // otherwise there is one tile and the sets take alternate stages of it.
+        // Ping-pong mode: parities of this set's two A slots (free at first), and how many raw chunks of the CTA (all tiles,
+        // in load order) this set has seen complete.  The raw ring is shared by both sets and a parity wait cannot tell a fill
+        // from the one two fills earlier, so BOTH sets wait for every fill in order and release it: a set does that for the
+        // other set's tiles (which it does not read) in the pauses of its own work.
+        uint32_t own_apar = 3u;
+        int rseen = 0;
+        auto observe_until = [&](int limit) {
+            for (; rseen < limit && alive; ++rseen) {
+                alive = ptx::mbar_wait(raw_full + rseen % P.NR, (uint32_t)((rseen / P.NR) & 1), abort_flag);
+                __syncwarp();
+                if (lane == 0 && alive)
+                    ptx::mbar_arrive(raw_empty + rseen % P.NR);
+            }
+        };
+        for (int tl = PP ? tset : 0; tl < ntl && alive; tl += PP ? 2 : 1) {
+        set_tile((int)blockIdx.x + tl * (int)gridDim.x); // (also for the only tile: nothing of it stays live across the code above)
         bool valid;
         int base_p;
         long long y_off;
@@ -827,21 +965,23 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                             tmask |= 1u << tap;
                     }
         }
-        bool alive = true;
-        long long t_we = 0, t_wr = 0, t_g = 0, t_st = 0;
-        const long long t_begin = P.prof ? clock64() : 0;
-        int rb = 0;
-        uint32_t prw = 0;
+        if (PP) {
+            observe_until(tl * (c1 - c0)); // fills that belong to the other set's tiles
+            if (!alive)
+                break;
+            rseen += c1 - c0; // this tile's own chunks, waited for and released below
+        }
+        // raw buffer of the tile's first chunk and the parity of its fill
+        const int chunk0 = PP ? tl * (c1 - c0) : 0;
+        int rb = chunk0 % P.NR;
+        uint32_t prw = (uint32_t)((chunk0 / P.NR) & 1);
         // Accumulator flush (P.fl > 0): the K stages form groups of P.fl; when the MMAs of group g have completed, the
         // eight transform warps add the main accumulator to the running total in TMEM (round-to-nearest fp32 adds, in
         // group order) and the MMA warp restarts the main accumulator for group g + 1.  A warp drains the columns its set
         // stores in the epilogue, of its own lane quarter.
-        const bool reg_total = SPLIT && A_TMEM && P.fl > 0 && P.fl_regs != 0;
-        const int FL = (SPLIT && A_TMEM && !reg_total) ? P.fl : 0;
         const int n_groups = FL > 0 ? (KS + FL - 1) / FL : 1;
         const int fcol0 = tset == 0 ? 0 : ((P.BN / 32 + 1) / 2) * 32, fcol1 = tset == 0 ? ((P.BN / 32 + 1) / 2) * 32 : P.BN;
         int fg = 0; // next group this warp has to drain
-        long long t_dw = 0, t_dd = 0;
         auto drain_group = [&](int g, bool wait_mma, bool signal) -> bool {
             const long long cd0 = P.prof ? clock64() : 0;
             if (wait_mma && !ptx::mbar_wait(acc_ready, (uint32_t)(g & 1), abort_flag))
@@ -873,63 +1013,15 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             }
             return true;
         };
-        // Register-total mode: set 1 only drains.  Its threads keep the 128 columns of their tile row in registers, add the
-        // main accumulator of every completed group to them, and at the end write total + last group back over the main
-        // accumulator, which the epilogue of both sets then reads as if nothing had happened.
-        if (reg_total && tset == 1) {
-            float racc[128];
-#pragma unroll
-            for (int j = 0; j < 128; ++j)
-                racc[j] = 0.f;
-            const uint32_t tq = tmem_base + ((uint32_t)(quarter * 32) << 16);
-            const int groups = (KS + P.fl - 1) / P.fl;
-            for (int g = 0; g < groups && alive; ++g) {
-                const bool last = g == groups - 1;
-                const long long cd0 = P.prof ? clock64() : 0;
-                alive = last ? ptx::mbar_wait(acc_full, 0u, abort_flag) : ptx::mbar_wait(acc_ready, (uint32_t)(g & 1), abort_flag);
-                if (!alive)
-                    break;
-                const long long cd1 = P.prof ? clock64() : 0;
-                ptx::tc_fence_after();
-#pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    uint32_t v0[16], v1[16];
-                    ptx::tmem_ld_32x16(tq + (uint32_t)(b * 32), v0);
-                    ptx::tmem_ld_32x16(tq + (uint32_t)(b * 32 + 16), v1);
-                    ptx::tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        racc[b * 32 + j] += __uint_as_float(v0[j]);
-                        racc[b * 32 + 16 + j] += __uint_as_float(v1[j]);
-                    }
-                    if (last) {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            v0[j] = __float_as_uint(racc[b * 32 + j]);
-                            v1[j] = __float_as_uint(racc[b * 32 + 16 + j]);
-                        }
-                        ptx::tmem_st_32x16(tq + (uint32_t)(b * 32), v0);
-                        ptx::tmem_st_32x16(tq + (uint32_t)(b * 32 + 16), v1);
-                    }
-                }
-                if (last)
-                    ptx::tmem_st_wait();
-                ptx::tc_fence_before();
-                __syncwarp();
-                if (!last && lane == 0)
-                    ptx::mbar_arrive(flushed);
-                if (P.prof) {
-                    t_dw += cd1 - cd0;
-                    t_dd += clock64() - cd1;
-                }
-            }
-        }
-        const int sstep = reg_total ? 1 : 2; // stages between two stages of one set
-        int gs = reg_total ? 0 : tset; // index of this set's next K stage among the CTA's KS stages
-        // This set owns every second K stage (tset, tset + 2, ...): `st` is the next one's index inside the current chunk,
-        // `sa`/`pa` its slot of the A ring and the parity to wait for (first pass over the ring: every slot is free).
-        int st = reg_total ? 0 : tset, sa = st;
-        uint32_t pa = 1;
+        const bool all_stages = reg_total || PP; // this set produces every stage of the tile
+        const int sstep = all_stages ? 1 : 2;  // stages between two stages of one set
+        int gs = all_stages ? 0 : tset; // index of this set's next K stage among the tile's KS stages
+        // This set owns every second K stage (tset, tset + 2, ...) or all of them: `st` is the next one's index inside the
+        // current chunk, `sa`/`pa` its slot of the A ring and the parity to wait for (first pass over the ring: every slot is
+        // free; ping-pong: the tile's first stage follows the tl * KS stages of the earlier tiles).
+        int st = all_stages ? 0 : tset;
+        int sa = PP ? 2 * tset : st;
+        uint32_t pa = PP ? (own_apar & 1u) : 1u;
         for (int ch = 0; ch < ((reg_total && tset == 1) ? 0 : c1 - c0) && alive; ++ch, st -= P.spc) {
             const long long cr0 = P.prof ? clock64() : 0;
             alive = ptx::mbar_wait(raw_full + rb, prw, abort_flag); // also by a set without a stage in this chunk
@@ -1025,10 +1117,16 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 __syncwarp();
                 if (lane == 0)
                     ptx::mbar_arrive(a_full + sa);
-                sa += sstep;
-                if (sa >= P.NA) {
-                    sa -= P.NA;
-                    pa ^= 1u;
+                if (PP) { // the set's other slot next; a slot's parity flips with every use
+                    own_apar ^= 1u << (sa & 1);
+                    sa ^= 1;
+                    pa = (own_apar >> (sa & 1)) & 1u;
+                } else {
+                    sa += sstep;
+                    if (sa >= P.NA) {
+                        sa -= P.NA;
+                        pa ^= 1u;
+                    }
                 }
             }
             __syncwarp();
@@ -1040,7 +1138,9 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             }
         }
         // ---------------- epilogue ----------------
-        const long long t_loop = P.prof ? clock64() - t_begin : 0;
+        t_loop = P.prof ? clock64() - t_begin : 0;
+        if (PP) // the next tile's fills (the other set's): their loads only wait for buffers this tile has already released
+            observe_until(min((tl + 2) * (c1 - c0), ntl * (c1 - c0)));
         // Addresses and store mode first: the MMA warp is still working through the last stages, so this costs nothing.
         const bool vec_ok = (P.ys_f == 1) && ((P.ys_p & 3) == 0) && ((P.ys_n & 3) == 0) && ((P.Fg & 3) == 0) &&
                             ((reinterpret_cast<uintptr_t>(P.y) & 15) == 0);
@@ -1053,8 +1153,9 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         const int split_cols = P.BN / P.ksplit, split_shift = 31 - __clz(split_cols);
         const uint32_t split_addr =
             P.ksplit > 1 ? ptx::smem_u32(sSplit) + (uint32_t)(((int)ptx::cluster_ctarank() * split_cols) * kTileM + p) * 4u : 0u;
-        const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (FL > 0 ? 2u * (uint32_t)P.BN : 0u);
-        const uint32_t tcross = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)P.BN;
+        const uint32_t tacc0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (PP ? (uint32_t)((tl & 1) * 2 * P.BN) : 0u);
+        const uint32_t tacc = tacc0 + (FL > 0 ? 2u * (uint32_t)P.BN : 0u);
+        const uint32_t tcross = tacc0 + (uint32_t)P.BN;
         // staged 16-byte stores need: pixel-contiguous NCHW output, full-width rows (no column window), one plane per
         // tile, 16-byte aligned runs (of y and of the residual, which is laid out like y)
         float *stage = nullptr;
@@ -1068,25 +1169,25 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             (P.ys_f & 3) == 0 && ((P.oh0 * P.OW) & 3) == 0 && P.ksplit == 1 &&
             (reinterpret_cast<uintptr_t>(P.y) & 15) == 0 && (reinterpret_cast<uintptr_t>(P.res) & 15) == 0 && !P.epi_direct) {
             nvalid_warp = __popc(__ballot_sync(0xffffffffu, valid));
-            if (nvalid_warp > 0)
-                stage = reinterpret_cast<float *>(sB) + (warp - 3) * 1024; // B stages are idle once the accumulator is complete
-            if ((uint32_t)(warp - 3 + 1) * 4096u > (uint32_t)P.NB * (SPLIT ? 2u : 1u) * b_half)
+            if (nvalid_warp > 0) // B stages are idle once the accumulator is complete; in ping-pong mode they never are
+                stage = reinterpret_cast<float *>(PP ? smem + L.stage_off : sB) + (warp - 3) * 1024;
+            if (!PP && (uint32_t)(warp - 3 + 1) * 4096u > (uint32_t)P.NB * (SPLIT ? 2u : 1u) * b_half)
                 stage = nullptr; // not enough idle shared memory for this warp's block
         }
         // the two sets split the tile's columns (whole 32-column blocks)
         const int nblk = P.BN / 32, half_blk = (nblk + 1) / 2;
-        const int col0 = tset == 0 ? 0 : half_blk * 32, col1 = tset == 0 ? half_blk * 32 : P.BN;
+        const int col0 = (PP || tset == 0) ? 0 : half_blk * 32, col1 = (!PP && tset == 0) ? half_blk * 32 : P.BN;
         for (; fg < n_groups - 1 && alive; ++fg)
             alive = drain_group(fg, true, true);
         if (alive)
-            alive = ptx::mbar_wait(acc_full, 0u, abort_flag);
+            alive = ptx::mbar_wait((PP && (tl & 1)) ? acc_full1 : acc_full, PP ? (uint32_t)((tl >> 1) & 1) : 0u, abort_flag);
         if (alive && FL > 0) // the last group joins the total; the epilogue then reads the total in place of the accumulator
             drain_group(n_groups - 1, false, false);
         if (reg_total) { // set 1 has written total + last group over the main accumulator: both sets meet before reading it
             ptx::named_bar_sync(1, 256);
             ptx::tc_fence_after();
         }
-        const long long t_epi0 = P.prof ? clock64() : 0;
+        t_epi0 = P.prof ? clock64() : 0;
         if (alive) {
             ptx::tc_fence_after();
 #define PETB200_EPI(ACT_)                                                                                              \
@@ -1100,7 +1201,16 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             default: PETB200_EPI(PETB200_ACT_NONE); break;
             }
 #undef PETB200_EPI
+            if (PP) { // this tile's accumulators are in registers or stored: the MMA warp may reuse the region
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    ptx::mbar_arrive(acc_empty + (tl & 1));
+            }
         }
+        } // tiles of this set
+        if (PP)
+            observe_until(ntl * (c1 - c0)); // fills of tiles after this set's last one
         if (P.prof && threadIdx.x == 96) { // lane 0 of warp 3 (transform set 0)
             long long *pr = P.prof + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * kProfSlots;
             pr[3] = t_we;
@@ -1268,6 +1378,11 @@ struct TcCore {
     int starve = 0;
 
     void (*kernel() const)(CUtensorMap, CUtensorMap, CUtensorMap, IgemmParams) {
+        if (P.pp) { // conv plans on the TS variant only
+            if (single_pass)
+                return k_igemm<true, false, kMathTf32x1, true>;
+            return bf16 ? k_igemm<true, false, kMathBf16x3, true> : k_igemm<true, false, kMathTf32x3, true>;
+        }
         if (single_pass)
             return P.a_kmajor ? k_igemm<true, true, kMathTf32x1> : k_igemm<true, false, kMathTf32x1>;
         if (bf16)
@@ -1437,13 +1552,14 @@ static int choose_ksplit(int sm_count, long long base_ctas, const IgemmParams &P
 
 // Accumulator flush period (see IgemmParams::fl) and the TMEM column map that goes with it.  The truncation bias of the
 // tensor core's fp32 accumulator grows with the number of MMAs added into one running sum: K ranges of more than
-// `2 * period` stages per CTA are drained every `period` stages (PETB200_TC_FLUSH in the environment, 0 = never).  The
+// `3 * period` stages per CTA are drained every `period` stages (PETB200_TC_FLUSH in the environment, 0 = never; measured
+// without a flush: 2.4e-4 of the contract's 1e-3 at 18 stages, 3e-4..4e-4 at 36, 2e-3 at 54).  The
 // running total takes BN more TMEM columns; a 128-wide tile then has room for two A stages instead of four.
 static void choose_flush(TcCore &core) {
     IgemmParams &P = core.P;
     const int period = env_int("PETB200_TC_FLUSH", 8);
     const int ks_max = ((P.nchunks + P.ksplit - 1) / P.ksplit) * P.spc;
-    P.fl = (!core.single_pass && core.a_tmem && period > 0 && ks_max > 2 * period) ? period : 0;
+    P.fl = (!core.single_pass && core.a_tmem && period > 0 && ks_max > 3 * period) ? period : 0;
     // register totals make one transform set do all the A stages: only where the gather is the cheap kind (whole 32-channel
     // stages of one tap, or row-major matmul tiles); slower gathers need both sets and keep the total in TMEM
     const bool fast_gather = P.a_kmajor || (P.cstride != 0 && P.gruns == (core.bf16 ? 2 : 1));
@@ -1453,8 +1569,9 @@ static void choose_flush(TcCore &core) {
     if (core.a_tmem)
         P.NA = (512 - P.a_col) / 64;
     if (env_int("PETB200_TC_VERBOSE", 0))
-        fprintf(stderr, "[petb200] igemm plan: BN %d BC %d chunks %d stages/chunk %d ksplit %d flush %d (regs %d) NA %d NB %d NR %d kmajor %d flat %d\n",
-                P.BN, P.BC, P.nchunks, P.spc, P.ksplit, P.fl, P.fl_regs, P.NA, P.NB, P.NR, P.a_kmajor, P.flat);
+        fprintf(stderr, "[petb200] igemm plan: BN %d BC %d chunks %d stages/chunk %d ksplit %d flush %d (regs %d) NA %d NB %d NR %d kmajor %d flat %d math %s\n",
+                P.BN, P.BC, P.nchunks, P.spc, P.ksplit, P.fl, P.fl_regs, P.NA, P.NB, P.NR, P.a_kmajor, P.flat,
+                core.single_pass ? "1xtf32" : (core.bf16 ? "bf16x3" : "3xtf32"));
 }
 
 // The dynamic shared-memory attribute is per function, not per launch: raise it once to the device limit so that plans
@@ -1477,6 +1594,12 @@ static int raise_smem_limit(petb200_ctx *ctx) {
         e = cudaFuncSetAttribute(k_igemm<true, false, kMathBf16x3>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(k_igemm<true, true, kMathBf16x3>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(k_igemm<true, false, kMathTf32x3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(k_igemm<true, false, kMathBf16x3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(k_igemm<true, false, kMathTf32x1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
     if (e != cudaSuccess)
         return fail(ctx, PETB200_ERR_CUDA, "cudaFuncSetAttribute(%d bytes) failed: %s", lim, cudaGetErrorString(e));
     attr_set = true;
@@ -1684,12 +1807,32 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     const int BN = P.BN;
     if (core.a_tmem && BN > 256)
         return fail(ctx, PETB200_ERR_INVALID, "TS variant supports BN <= 256");
-    core.smem = smem_layout(P, core.a_tmem).total + 1024;
     const int ntiles = (Fg + BN - 1) / BN;
+    // Persistent ping-pong mode (see IgemmParams::pp) where every SM would otherwise run several CTAs in sequence: narrow
+    // tiles (two accumulator regions must fit beside the A ring), no K split, no accumulator flush.
+    P.mtiles = mtiles;
+    P.pp = 0;
+    int grid_x = mtiles;
+    {
+        const int slots = std::max(1, ctx->sm_count / (ntiles * gz));
+        const int tiles_per_cta = (mtiles + slots - 1) / slots;
+        if (core.a_tmem && env_int("PETB200_TC_PINGPONG", 1) && P.ksplit == 1 && P.fl == 0 && BN <= 64 && tiles_per_cta >= 2) {
+            const int nb_was = P.NB;
+            P.pp = 1;
+            // (NA is 4 without a flush: two A slots per transform set)
+            while (smem_layout(P, true).total > budget && P.NB > 2)
+                P.NB--;
+            if (smem_layout(P, true).total > budget || P.NA != 4)
+                P.pp = 0, P.NB = nb_was;
+            else
+                grid_x = (mtiles + tiles_per_cta - 1) / tiles_per_cta;
+        }
+    }
+    core.smem = smem_layout(P, core.a_tmem).total + 1024;
     core.y_elems = (z_is_batch ? (long long)images : (long long)n_img) * g.F * g.OD * g.OH * g.OW;
     if (z_is_batch)
         core.y_elems = (long long)images * ys_n;
-    core.grid = dim3((unsigned)mtiles, (unsigned)(ntiles * P.ksplit), (unsigned)gz);
+    core.grid = dim3((unsigned)grid_x, (unsigned)(ntiles * P.ksplit), (unsigned)gz);
     core.Ktot = (long long)P.nchunks * P.spc * P.ke;
     core.xd[0] = g.Wst;
     core.xd[1] = g.H;
@@ -1697,7 +1840,10 @@ static int tc_configure(petb200_ctx *ctx, TcCore &core, const ConvGeom &g, int o
     core.xd[3] = g.C;
     core.xd[4] = g.N;
     // offset table for one chunk
-    std::vector<int> koff((size_t)P.spc * P.ke, -1);
+    // Entries past the end of the chunk's K range (their packed weights are zero): -1 where the gather tests for it; in
+    // plain table mode the pixel's own first element instead, so that the gather needs no test per element (the value only
+    // ever meets a zero weight, and a NaN there would poison this pixel's sum anyway).
+    std::vector<int> koff((size_t)P.spc * P.ke, (!flat && P.cstride == 0) ? 0 : -1);
     const int plane_w = P.RW, plane_h = P.RH * P.RW, plane_d = P.RD * plane_h;
     for (int tap = 0; tap < T; ++tap) {
         int t = tap / (g.T3[1] * g.T3[2]), r = (tap / g.T3[2]) % g.T3[1], s = tap % g.T3[2];
