@@ -251,7 +251,10 @@ def library_baseline(ctx, ours_ms):
     reference's direct calls; cudnn.benchmark picks the fastest algorithm the way ConvOp::perf's sweep does), replayed as
     CUDA graphs: `default_math` = what the reference's conv calls get on this GPU (TF32 allowed), `fp32` = TF32 off (what
     its cuBLAS calls, issued with fp32 compute, get; and the accuracy class of this backend).  `max_err_vs_fp32` is the
-    parity metric between this backend's output and the library's fp32 output on the same seeded tensors."""
+    parity metric between this backend's output and the library's fp32 output on the same seeded tensors;
+    `default_math_err_vs_fp32` the same metric for the library's own default-math output.  `bf16x3_*`: this backend with
+    its opt-in error-compensated bf16 arithmetic (PETB200_ALGO_TC_BF16X3; every plan of the graph), an accuracy class between
+    the library's two."""
     import torch
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
     from torch_backend import TorchBuilder
@@ -265,7 +268,7 @@ def library_baseline(ctx, ours_ms):
              ("c4_bert_base_seq128", configs.bert_encoder, (), {}, 30), ("c5_r3d18", configs.r3d18, (), {}, 20)]
     for name, build, a, kw, rounds in cases:
         row = {}
-        lib_out = None
+        lib_out = lib_out_default = None
         for mode, tf32 in (("default_math", True), ("fp32", False)):
             tb = TorchBuilder(tf32=tf32)
             consts = []
@@ -300,13 +303,24 @@ def library_baseline(ctx, ours_ms):
             row[mode + "_ms"] = time_cuda_graph(fn, rounds)
             if not tf32:
                 lib_out = fn().cpu().numpy()
+            else:
+                lib_out_default = fn().cpu().numpy()
+        row["default_math_err_vs_fp32"] = contract_metric(lib_out_default, lib_out)
         if name in ours_ms:
             row["ours_ms"] = ours_ms[name]["ms"]
             g, _, o = build_graph(ctx, build, **kw) if not a else _build_with_args(ctx, build, a)
-            import torch as _t
-            _t.cuda.synchronize()
+            torch.cuda.synchronize()
             row["max_err_vs_fp32"] = contract_metric(g.get_data(o), lib_out)
             del g
+        os.environ["PETB200_TC_MATH"] = "bf16x3"  # read when a plan is created
+        try:
+            g, _, o = build_graph(ctx, build, **kw) if not a else _build_with_args(ctx, build, a)
+            torch.cuda.synchronize()
+            row["bf16x3_ms"] = g.time(rounds=rounds, warmup=5)
+            row["bf16x3_max_err_vs_fp32"] = contract_metric(g.get_data(o), lib_out)
+            del g
+        finally:
+            del os.environ["PETB200_TC_MATH"]
         out[name] = row
     return out
 

@@ -1317,16 +1317,17 @@ __global__ void __launch_bounds__(256) k_pack_conv_w(const float *__restrict__ w
 template <bool BF>
 __global__ void __launch_bounds__(256) k_pack_mm_b(const float *__restrict__ b, void *__restrict__ hi,
                                                    void *__restrict__ lo, int bs, int n, int k, int Kpad, int transB, int rna,
-                                                   long long sb_batch, long long sb_row) {
+                                                   long long sb_batch, long long sb_row, int BC, int Kc_pad) {
     pdl_prologue();
     const long long total = (long long)bs * n * Kpad;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const int kk = (int)(i % Kpad);
+        const int kp = (int)(i % Kpad); // packed position: chunk * Kc_pad + element of the chunk (BC of them, then padding)
+        const int ch = kp / Kc_pad, kc = kp - ch * Kc_pad, kk = ch * BC + kc;
         const long long row = i / Kpad;
         const int nn = (int)(row % n);
         const int bb = (int)(row / n);
         float v = 0.f;
-        if (kk < k)
+        if (kc < BC && kk < k)
             v = transB ? __ldg(b + bb * sb_batch + nn * sb_row + kk) : __ldg(b + bb * sb_batch + kk * sb_row + nn);
         store_split<BF>(hi, lo, i, v, rna);
     }
@@ -1557,7 +1558,8 @@ static int choose_ksplit(int sm_count, long long base_ctas, const IgemmParams &P
 // running total takes BN more TMEM columns; a 128-wide tile then has room for two A stages instead of four.
 static void choose_flush(TcCore &core) {
     IgemmParams &P = core.P;
-    const int period = env_int("PETB200_TC_FLUSH", 8);
+    // (bf16: twice the K per stage and an accuracy class that the split, not the truncation, dominates: half as often)
+    const int period = env_int("PETB200_TC_FLUSH", core.bf16 ? 16 : 8);
     const int ks_max = ((P.nchunks + P.ksplit - 1) / P.ksplit) * P.spc;
     P.fl = (!core.single_pass && core.a_tmem && period > 0 && ks_max > 3 * period) ? period : 0;
     // register totals make one transform set do all the A stages: only where the gather is the cheap kind (whole 32-channel
@@ -2216,10 +2218,6 @@ int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, 
         return rc;
     }
     TcCore &c = t->core;
-    if (c.P.nchunks > 1 && c.P.spc * c.P.ke != c.P.BC) { // the packing below assumes k = chunk * BC + ci
-        delete t;
-        return fail(ctx, PETB200_ERR_UNSUPPORTED, "matmul K chunking diverged from the packing order");
-    }
     c.rows_b = bs * n;
     // rows of different batch entries are adjacent: Fg = n rows per z
     size_t wbytes = (size_t)bs * n * c.Ktot * (c.bf16 ? 2 : 4);
@@ -2245,10 +2243,11 @@ int tc_matmul_pack_b(void *h, const float *b, cudaStream_t s) {
     long long total = (long long)t->bs * t->n * c.Ktot;
     int blocks = (int)std::min<long long>((total + 255) / 256, (long long)c.ctx->sm_count * 16);
     if (c.bf16)
-        launch_pdl(k_pack_mm_b<true>, blocks, 256, 0, s, b, c.whi.p, c.wlo.p, t->bs, t->n, t->k, (int)c.Ktot, t->transB, 0, t->st[2], t->st[3]);
+        launch_pdl(k_pack_mm_b<true>, blocks, 256, 0, s, b, c.whi.p, c.wlo.p, t->bs, t->n, t->k, (int)c.Ktot, t->transB, 0, t->st[2], t->st[3],
+                   c.P.BC, c.P.spc * c.P.ke);
     else
         launch_pdl(k_pack_mm_b<false>, blocks, 256, 0, s, b, c.whi.p, c.wlo.p, t->bs, t->n, t->k, (int)c.Ktot, t->transB, c.single_pass,
-                   t->st[2], t->st[3]);
+                   t->st[2], t->st[3], c.P.BC, c.P.spc * c.P.ke);
     c.weights_ready = true;
     return launched(c.ctx, "k_pack_mm_b");
 }
