@@ -8,8 +8,9 @@
 //   warp 2   : TMA producer for the RAW activation tile of one channel chunk (all taps share it): a 5-D box
 //              [images, channels, depth, rows, cols] of the NC(D)HW input, zero-filled outside the tensor, which
 //              is exactly the convolution's zero padding.  Box start along W is rounded down to 16 bytes.
-//   warps 3-6, 7-10: two transform sets taking alternate K stages.  Thread p owns pixel p of the tile: for every K stage it gathers its 32 values from the
-//              raw tile through a precomputed offset table (tap shift, dilation, channel plane), splits each fp32
+//   warps 3-6, 7-10: two transform sets taking alternate K stages.  Thread p owns pixel p of the tile: for every K stage it
+//              gathers its 32 values from the raw tile (fixed strides where the channel chunk allows, else through a
+//              precomputed offset table: tap shift, dilation, channel plane), splits each fp32
 //              into hi (top 19 bits) and lo = x - hi, and writes the two K-major operand tiles — into swizzled
 //              shared memory (SS variant) or directly into TMEM with tcgen05.st (TS variant, which leaves the
 //              shared-memory read port to B alone).  The same warps run the epilogue.
@@ -19,6 +20,10 @@
 // Epilogue: tcgen05.ld -> +bias -> activation -> global stores, coalesced across the 32 pixels of a warp (conv)
 // or 128-bit per thread (row-major matmul output).
 //
+// Variants (template parameters): 3xTF32 (default), one TF32 pass, error-compensated bf16 (64 K elements per stage, K = 16 per
+// MMA); persistent "ping-pong" tiles for narrow filter tiles (a CTA walks several pixel tiles, the transform sets take
+// alternate tiles, accumulators alternate between two TMEM regions).  Long K ranges drain the main accumulator into a
+// running total every few stages (the tensor core truncates its fp32 accumulator after every MMA).
 // Split-K: the ksplit CTAs of one output tile form a thread-block cluster and exchange their partial sums through
 // distributed shared memory (pushes into the owner's landing area, one cluster barrier, reduction in rank order).
 // Every wait on an mbarrier is bounded (~2 s) and reports through a status word instead of hanging the GPU.
@@ -1518,13 +1523,38 @@ static int env_int(const char *name, int dflt) {
 // with 128-wide tiles.  Constants are measured on B200: a K stage costs its MMAs (N/2 cycles each, 12 per stage for
 // 3xTF32, 4 for one pass) or, if larger, the transform chain of the stage (~330 cycles with two warp sets); a CTA pays
 // ~3000 cycles before its first MMA and 1700 + 44*BN cycles of epilogue (split-K: the exchange through the cluster instead).
+// How many clusters of `ks` CTAs of this kernel (one CTA per SM) the device can hold at once: asked of the driver once
+// per size (clusters stay inside a GPC, which leaves some SMs of every GPC without a cluster).
+static int cluster_slots(int sm_count, int ks) {
+    static int cached[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+    if (ks <= 1)
+        return sm_count;
+    if (cached[ks] == 0) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(1, (unsigned)ks * 64, 1);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = 200 * 1024; // enough that two CTAs never share an SM, as in every real plan
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1, attr[0].val.clusterDim.y = (unsigned)ks, attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr, cfg.numAttrs = 1;
+        int n = 0;
+        (void)cudaFuncSetAttribute(k_igemm<true, false, kMathTf32x3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (cudaOccupancyMaxActiveClusters(&n, k_igemm<true, false, kMathTf32x3, false>, &cfg) != cudaSuccess || n <= 0) {
+            (void)cudaGetLastError();
+            n = std::max(1, (sm_count * (ks <= 2 ? 96 : 86) / 100) / ks); // what B200 was measured to hold
+        }
+        cached[ks] = n;
+    }
+    return cached[ks];
+}
+
 static double est_cycles(int sm_count, long long base_ctas, int nchunks, int spc, int BN, int passes, int ks) {
     const double stage = std::max<double>((passes == 3 ? 12.0 : 4.0) * (BN / 2), 520.0);
     const long long stages = (long long)((nchunks + ks - 1) / ks) * spc;
     // split-K: (ks-1)/ks of the 512*BN-byte tile crosses to other SMs at ~10 bytes per cycle, then barrier + local sums
     const double per_cta = 3000.0 + (double)stages * stage + 1700.0 + (ks > 1 ? 1500.0 + 50.0 * BN * (ks - 1) / ks : 44.0 * BN);
-    // clusters are placed inside one GPC, which leaves a few SMs of each GPC unused
-    const long long slots = ks == 1 ? sm_count : std::max(1, (sm_count * (ks <= 2 ? 96 : 86) / 100) / ks);
+    const long long slots = cluster_slots(sm_count, ks);
     const long long waves = (base_ctas + slots - 1) / slots;
     return (double)waves * per_cta;
 }
