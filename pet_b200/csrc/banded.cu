@@ -272,7 +272,43 @@ int check_band(petb200_ctx *ctx, const void *a, const void *b, const void *y, in
 } // namespace
 } // namespace petb200
 
+// implemented in igemm_tc.cu
+namespace petb200 {
+int tc_g2bmm_create(petb200_ctx *ctx, int bs, int n, int m, int w, void **out);
+void tc_matmul_destroy(void *h);
+int tc_matmul_pack_b(void *h, const float *b, cudaStream_t s);
+int tc_matmul_run(void *h, const float *a_t, const float *bias, const float *res, float *cmat, cudaStream_t s);
+} // namespace petb200
+
 using namespace petb200;
+
+// The tensor-core plan of a banded product of this shape, made on first use; null where that path does not apply (then the
+// CUDA-core kernels below run): dilation 1, m a multiple of 4, 16-byte aligned operands, PETB200_BANDED_TC=0 not set.
+static void *band_tc_plan(petb200_ctx *ctx, int kind, const void *a, const void *b, int bs, int n, int m, int w, int d) {
+    static const bool enabled = !(getenv("PETB200_BANDED_TC") && atoi(getenv("PETB200_BANDED_TC")) == 0);
+    if (!enabled || kind != 0 || d != 1 || w < 1 || ctx->cc_major != 10 || (m & 3) || (((size_t)a | (size_t)b) & 15))
+        return nullptr;
+    for (auto &e : ctx->band_tc)
+        if (e.key[0] == kind && e.key[1] == bs && e.key[2] == n && e.key[3] == m && e.key[4] == w)
+            return e.plan;
+    void *plan = nullptr;
+    if (tc_g2bmm_create(ctx, bs, n, m, w, &plan) != PETB200_OK)
+        plan = nullptr; // remembered as "not on this path"
+    ctx->band_tc_destroy = tc_matmul_destroy;
+    ctx->band_tc.push_back({{kind, bs, n, m, w}, plan});
+    return plan;
+}
+
+// Tuning only: per-CTA counters of the tensor-core plans made so far (see IgemmParams::prof), null to stop.
+namespace petb200 {
+void tc_matmul_set_prof(void *h, long long *p);
+}
+extern "C" int petb200_debug_band_prof(petb200_ctx *ctx, long long *dev_counters) {
+    for (auto &e : ctx->band_tc)
+        if (e.plan)
+            tc_matmul_set_prof(e.plan, dev_counters);
+    return PETB200_OK;
+}
 
 // Argument order of the reference's launchers: _sg2bmm(q, k, y, bs, n, m, w, d), src/custom_ops.cu:6-9.
 extern "C" int petb200_g2bmm_run(petb200_ctx *ctx, const float *q, const float *k, float *y, int bs, int n, int m, int w, int d,
@@ -282,6 +318,11 @@ extern "C" int petb200_g2bmm_run(petb200_ctx *ctx, const float *q, const float *
     int rc = check_band(ctx, q, k, y, bs, n, m, w, d, &g, &ytiles);
     if (rc)
         return rc;
+    if (void *plan = band_tc_plan(ctx, 0, q, k, bs, n, m, w, d)) {
+        // keys split into hi/lo once per call (they are an activation), then the tensor-core kernel with the banded epilogue
+        rc = tc_matmul_pack_b(plan, k, (cudaStream_t)stream);
+        return rc ? rc : tc_matmul_run(plan, q, nullptr, nullptr, y, (cudaStream_t)stream);
+    }
     const dim3 grid((unsigned)((2 * w + 1 + kTJ - 1) / kTJ), (unsigned)ytiles, (unsigned)bs);
     launch_pdl(k_g2bmm, grid, dim3(128), 0, (cudaStream_t)stream, q, k, y, g);
     return launched(ctx, "k_g2bmm");

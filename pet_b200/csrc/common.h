@@ -50,9 +50,19 @@ struct petb200_ctx {
     // Buffers band_scratch outgrew.  They stay allocated until the context goes: a CUDA graph captured while one of them
     // was current has its address baked into its kernel nodes and may still be replayed.
     std::vector<void *> band_retired;
+    // Tensor-core plans of banded products, made on first use of a shape (kind, bs, n, m, w) and kept until the context goes.
+    struct BandTcPlan {
+        int key[5];
+        void *plan;
+    };
+    std::vector<BandTcPlan> band_tc;
+    void (*band_tc_destroy)(void *) = nullptr;
     ~petb200_ctx() {
         for (void *p : band_retired)
             cudaFree(p);
+        for (auto &e : band_tc)
+            if (band_tc_destroy && e.plan)
+                band_tc_destroy(e.plan);
     }
 };
 

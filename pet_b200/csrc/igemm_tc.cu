@@ -95,6 +95,11 @@ struct IgemmParams {
                      // every A stage of its tile and then stores it) and the accumulators alternate between two TMEM
                      // regions, so one tile's epilogue and the next tile's start-up hide behind the MMAs of the other
     int mtiles;      // pixel tiles along x
+    int band_w;      // > 0: banded product y[b,i,j] = q[b,i,:] . k[b,i+j-w,:] (row-major A = q, "filters" = the keys of the window
+                     // [128*tile - w, 128*tile + 127 + w] of the tile's rows, blockIdx.y = 64-key piece of that window); the
+                     // epilogue stores the band entries of each row at their skewed positions, zero where the key is outside [0,n)
+    int band_nt;     // banded product: 64-key pieces per row tile; the x tile index runs over (row tile, piece) pairs, piece fastest,
+                     // so that the cheap pieces at the band's edges are spread over all CTAs
     int epi_direct;  // tuning: store the epilogue straight from registers (no transposition through shared memory)
     int starve;      // test hook: the filter producer announces more bytes than it loads, so the stage never completes
 };
@@ -253,6 +258,50 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, uint32_t tcross, i
             for (int j = 0; j < 32; ++j)
                 if (f0 + j < Fg)
                     yp[(long long)(f0 + j) * ys_f] = __uint_as_float(r[j]);
+        }
+    }
+}
+
+// Banded product: the tile holds rows [128*bx, +128) x keys [128*bx - w + col_base, + BN) of q . k^T.  Entry (row pr, column c)
+// is band column jb = col_base + c - pr of row i = 128*bx + pr (key i + jb - w); entries with jb outside [0, 2w] are not part
+// of the band, entries whose key is outside [0, n) are stored as zero.  A warp passes 32 rows x 32 columns through shared
+// memory (XOR-swizzled, conflict-free both ways) so that each store instruction writes 32 consecutive band columns of one row.
+template <int PASSES>
+__device__ __forceinline__ void epilogue_banded(uint32_t tacc, uint32_t tcross, int BN, int col_base, int p0, int bx, int zb, int n, int w,
+                                                float *y, float *stage, int lane) {
+    uint32_t nx[32], sm[32];
+    const int bw = 2 * w + 1;
+    const int i0 = bx * kTileM + p0;    // first row of this warp
+    const int rows = min(32, n - i0);   // rows of it inside the tensor
+    for (int cc = 0; cc < BN; cc += 32) {
+        const int lo = col_base + cc - p0; // jb of (row 0, lane 0); the block spans jb in [lo - 31, lo + 31]
+        if (rows <= 0 || lo + 31 < 0 || lo - 31 >= bw)
+            continue; // nothing of this block lies in the band
+        ptx::tmem_ld_32x32(tacc + (uint32_t)cc, nx);
+        if (PASSES != kMathTf32x1)
+            ptx::tmem_ld_32x32(tcross + (uint32_t)cc, sm);
+        // this lane's column: band column of warp row r is jb0 - r, the key is the same for every row
+        const int jb0 = col_base + cc + lane - p0, key = i0 + jb0 - w;
+        const bool key_ok = key >= 0 && key < n;
+        float *dst = y + ((long long)zb * n + i0) * bw + jb0; // row r: dst + r * (bw - 1)
+        ptx::tmem_ld_wait();
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float v = PASSES != kMathTf32x1 ? __uint_as_float(nx[j]) + __uint_as_float(sm[j]) : __uint_as_float(nx[j]);
+            stage[lane * 32 + (j ^ lane)] = v;
+        }
+        __syncwarp();
+        // every entry of the block inside the band and the tensor (the common case): no tests per store
+        if (rows == 32 && lo - 31 >= 0 && lo + 31 < bw && __all_sync(0xffffffffu, key_ok)) {
+#pragma unroll
+            for (int r = 0; r < 32; ++r, dst += bw - 1)
+                *dst = stage[r * 32 + (lane ^ r)];
+        } else {
+#pragma unroll 4
+            for (int r = 0; r < 32; ++r, dst += bw - 1)
+                if (r < rows && (unsigned)(jb0 - r) < (unsigned)bw)
+                    *dst = key_ok ? stage[r * 32 + (lane ^ r)] : 0.f;
         }
     }
 }
@@ -539,8 +588,13 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     int bx = (int)blockIdx.x;
     const int ntl = PP ? (P.mtiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 1; // tiles of this CTA
     int n_lo = 0, q0 = 0, unit0 = 0, z_start = 0, y_start = 0, x_start = 0, w_zl = 0, w_yl = 0, w_tx = 0;
+    int nt_cur = ntile; // filter tile of the current pixel tile (differs per tile only for banded products)
     auto set_tile = [&](int tile) {
         bx = tile;
+        if (PP && A_KMAJOR && P.band_w > 0) {
+            bx = tile / P.band_nt;
+            nt_cur = tile - bx * P.band_nt;
+        }
         n_lo = 0, q0 = 0, unit0 = 0, w_zl = 0, w_yl = 0, w_tx = 0;
         if (A_KMAJOR) {
             z_start = y_start = x_start = 0; // the tile is rows [bx*128, +128) of A[zb]
@@ -615,7 +669,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     if (warp == 0) {
         // ---------------- packed-weight producer (one thread) ----------------
         if (lane == 0) {
-            const int row0 = zb * P.Fg + ntile * P.BN;
+            int row0 = zb * P.Fg + ntile * P.BN;
             int sb = 0;
             uint32_t pb = 1; // first pass over the ring: every slot is free
             for (int ks = 0; ks < KS * ntl; ++ks) { // the same KS filter tiles for every pixel tile of this CTA
@@ -624,6 +678,10 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 uint8_t *dst = sB + (size_t)sb * 2 * b_half;
                 ptx::mbar_expect_tx(b_full + sb, (SPLIT ? 2u : 1u) * b_half + (P.starve ? 64u : 0u));
                 const int kst = ntl > 1 ? ks % KS : ks;
+                if (PP && A_KMAJOR && P.band_w > 0) { // the key window moves with the row tile (rows before the tensor or past it read as zero / are masked)
+                    const int tile = (int)blockIdx.x + (ks / KS) * (int)gridDim.x, rt = tile / P.band_nt;
+                    row0 = zb * P.m_rows + rt * kTileM - P.band_w + (tile - rt * P.band_nt) * P.BN;
+                }
                 ptx::tma_load_2d(dst, &tmap_bhi, b_full + sb, (c0 * P.spc + kst) * KE, row0);
                 if (SPLIT)
                     ptx::tma_load_2d(dst + b_half, &tmap_blo, b_full + sb, (c0 * P.spc + kst) * KE, row0);
@@ -1198,6 +1256,10 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
 #define PETB200_EPI(ACT_)                                                                                              \
     epilogue_store<ACT_, PASSES>(tacc, tcross, P.BN, f_tile0, P.Fg, valid, bp, rp, yp, P.ys_f, vec_ok, stage, nvalid_warp, \
                                  ybase_warp, rbase_warp, col0, col1, split_addr, split_shift)
+            if (PP && A_KMAJOR && P.band_w > 0) // (only that variant carries the code)
+                epilogue_banded<PASSES>(tacc, tcross, P.BN, nt_cur * P.BN, (warp & 3) * 32, bx, zb, P.m_rows, P.band_w, P.y,
+                                        reinterpret_cast<float *>(smem + L.stage_off) + (warp - 3) * 1024, lane);
+            else
             switch (P.ksplit > 1 ? PETB200_ACT_NONE : P.act) {
             case PETB200_ACT_RELU: PETB200_EPI(PETB200_ACT_RELU); break;
             case PETB200_ACT_SIGMOID: PETB200_EPI(PETB200_ACT_SIGMOID); break;
@@ -1384,7 +1446,9 @@ struct TcCore {
     int starve = 0;
 
     void (*kernel() const)(CUtensorMap, CUtensorMap, CUtensorMap, IgemmParams) {
-        if (P.pp) { // conv plans on the TS variant only
+        if (P.pp) { // conv plans on the TS variant, and banded products (row-major A)
+            if (P.a_kmajor)
+                return k_igemm<true, true, kMathTf32x3, true>;
             if (single_pass)
                 return k_igemm<true, false, kMathTf32x1, true>;
             return bf16 ? k_igemm<true, false, kMathBf16x3, true> : k_igemm<true, false, kMathTf32x3, true>;
@@ -1632,6 +1696,8 @@ static int raise_smem_limit(petb200_ctx *ctx) {
         e = cudaFuncSetAttribute(k_igemm<true, false, kMathBf16x3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(k_igemm<true, false, kMathTf32x1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(k_igemm<true, true, kMathTf32x3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
     if (e != cudaSuccess)
         return fail(ctx, PETB200_ERR_CUDA, "cudaFuncSetAttribute(%d bytes) failed: %s", lim, cudaGetErrorString(e));
     attr_set = true;
@@ -2264,6 +2330,87 @@ int tc_matmul_create(petb200_ctx *ctx, int bs, int m, int n, int k, int transA, 
     *out = t;
     return PETB200_OK;
 }
+// G2BMM on the tensor-core kernel (dilation 1): q [bs][n][m] is the row-major A operand, the keys k [bs][n][m] are packed like
+// a matmul's B operand ([bs*n rows][K]); a CTA column (blockIdx.y) is one 64-key piece of the 2w + 128 keys a row tile can
+// meet, and CTAs walk the row tiles in ping-pong mode.  `y` [bs][n][2w+1] is written by the banded epilogue.
+int tc_g2bmm_create(petb200_ctx *ctx, int bs, int n, int m, int w, void **out) {
+    if (ctx->cc_major != 10)
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "tcgen05 kernels need compute capability 10.x");
+    if (m % 4 != 0 || w <= 0)
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "tensor-core g2bmm needs m divisible by 4");
+    auto *t = new TcMatmul();
+    t->bs = bs, t->m = n, t->n = n, t->k = m, t->transB = 1;
+    t->st[2] = (long long)n * m, t->st[3] = m; // keys: batch and row strides
+    t->native_a = true;
+    TcCore &core = t->core;
+    core.ctx = ctx;
+    IgemmParams &P = core.P;
+    memset(&P, 0, sizeof P);
+    core.a_tmem = true;
+    P.a_kmajor = 1, P.ke = kStageK, P.m_rows = n, P.z_is_batch = 1, P.band_w = w;
+    P.OD = P.OH = 1, P.OW = n, P.ohn = 1, P.own = n, P.Pw = n, P.units = 1, P.ipt = 1, P.tpi = (n + kTileM - 1) / kTileM;
+    P.sd = P.sh = P.sw = 1;
+    P.cpg = m, P.Fg = n, P.BN = 64, P.ksplit = 1;
+    P.BC = P.ke, P.spc = 1, P.nchunks = (m + P.ke - 1) / P.ke;
+    P.RN = P.RD = 1, P.RH = kTileM, P.RW = kStageK, P.raw_bytes = kAHalfBytes;
+    P.ys_n = (long long)n * (2 * w + 1), P.ys_f = 1, P.ys_p = 2 * w + 1;
+    core.a_batch = (long long)n * m, core.a_row = m;
+    P.NA = 4, P.a_col = 256, P.fl = 0, P.fl_regs = 0;
+    const int key_tiles = (2 * w + kTileM + P.BN - 1) / P.BN;
+    P.pp = 1, P.band_nt = key_tiles, P.mtiles = P.tpi * key_tiles;
+    const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 1024;
+    P.NB = 2, P.NR = 2;
+    if (smem_layout(P, true).total > budget) {
+        delete t;
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "g2bmm tile does not fit shared memory");
+    }
+    for (bool grew = true; grew;) {
+        grew = false;
+        if (P.NB < kMaxNB) {
+            P.NB++;
+            if (smem_layout(P, true).total <= budget)
+                grew = true;
+            else
+                P.NB--;
+        }
+        if (P.NR < kMaxNR) {
+            P.NR++;
+            if (smem_layout(P, true).total <= budget)
+                grew = true;
+            else
+                P.NR--;
+        }
+    }
+    core.smem = smem_layout(P, true).total + 1024;
+    core.Ktot = (long long)P.nchunks * P.ke;
+    core.xd[0] = m, core.xd[1] = n, core.xd[2] = bs;
+    std::vector<int> koff(P.ke, -1);
+    if (core.koff.alloc(koff.size() * 4) != cudaSuccess) {
+        delete t;
+        return fail(ctx, PETB200_ERR_NOMEM, "koff allocation failed");
+    }
+    cudaMemcpy(core.koff.p, koff.data(), koff.size() * 4, cudaMemcpyHostToDevice);
+    const int slots = std::max(1, ctx->sm_count / bs);
+    const int tiles_per_cta = (P.mtiles + slots - 1) / slots;
+    core.grid = dim3((unsigned)((P.mtiles + tiles_per_cta - 1) / tiles_per_cta), 1u, (unsigned)bs);
+    core.y_elems = (long long)bs * n * (2 * w + 1);
+    core.rows_b = bs * n;
+    const size_t wbytes = (size_t)bs * n * core.Ktot * 4;
+    int rc = raise_smem_limit(ctx);
+    if (rc == PETB200_OK && (core.whi.alloc(wbytes) != cudaSuccess || core.wlo.alloc(wbytes) != cudaSuccess))
+        rc = fail(ctx, PETB200_ERR_NOMEM, "packed key allocation failed");
+    if (rc == PETB200_OK)
+        rc = core.encode_b();
+    if (rc) {
+        delete t;
+        return rc;
+    }
+    if (env_int("PETB200_TC_VERBOSE", 0))
+        fprintf(stderr, "[petb200] g2bmm plan: grid %u x %u x %u, NB %d NR %d\n", core.grid.x, core.grid.y, core.grid.z, P.NB, P.NR);
+    *out = t;
+    return PETB200_OK;
+}
+
 void tc_matmul_set_prof(void *h, long long *p) { ((TcMatmul *)h)->core.prof = p; }
 int tc_matmul_native_a(void *h) { return ((TcMatmul *)h)->native_a ? 1 : 0; }
 void tc_matmul_destroy(void *h) { delete (TcMatmul *)h; }
