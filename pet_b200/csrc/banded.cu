@@ -275,6 +275,8 @@ int check_band(petb200_ctx *ctx, const void *a, const void *b, const void *y, in
 // implemented in igemm_tc.cu
 namespace petb200 {
 int tc_g2bmm_create(petb200_ctx *ctx, int bs, int n, int m, int w, void **out);
+int tc_gbmml_create(petb200_ctx *ctx, int bs, int n, int m, int w, void **out);
+int tc_gbmml_run(void *h, const float *p, float *y, cudaStream_t s);
 void tc_matmul_destroy(void *h);
 int tc_matmul_pack_b(void *h, const float *b, cudaStream_t s);
 int tc_matmul_run(void *h, const float *a_t, const float *bias, const float *res, float *cmat, cudaStream_t s);
@@ -286,13 +288,13 @@ using namespace petb200;
 // CUDA-core kernels below run): dilation 1, m a multiple of 4, 16-byte aligned operands, PETB200_BANDED_TC=0 not set.
 static void *band_tc_plan(petb200_ctx *ctx, int kind, const void *a, const void *b, int bs, int n, int m, int w, int d) {
     static const bool enabled = !(getenv("PETB200_BANDED_TC") && atoi(getenv("PETB200_BANDED_TC")) == 0);
-    if (!enabled || kind != 0 || d != 1 || w < 1 || ctx->cc_major != 10 || (m & 3) || (((size_t)a | (size_t)b) & 15))
+    if (!enabled || d != 1 || w < 1 || ctx->cc_major != 10 || (m & 3) || (((size_t)a | (size_t)b) & 15))
         return nullptr;
     for (auto &e : ctx->band_tc)
         if (e.key[0] == kind && e.key[1] == bs && e.key[2] == n && e.key[3] == m && e.key[4] == w)
             return e.plan;
     void *plan = nullptr;
-    if (tc_g2bmm_create(ctx, bs, n, m, w, &plan) != PETB200_OK)
+    if ((kind == 0 ? tc_g2bmm_create(ctx, bs, n, m, w, &plan) : tc_gbmml_create(ctx, bs, n, m, w, &plan)) != PETB200_OK)
         plan = nullptr; // remembered as "not on this path"
     ctx->band_tc_destroy = tc_matmul_destroy;
     ctx->band_tc.push_back({{kind, bs, n, m, w}, plan});
@@ -336,6 +338,11 @@ extern "C" int petb200_gbmml_run(petb200_ctx *ctx, const float *p, const float *
     int rc = check_band(ctx, p, v, y, bs, n, m, w, d, &g, &ytiles);
     if (rc)
         return rc;
+    if (void *plan = band_tc_plan(ctx, 1, p, v, bs, n, m, w, d)) {
+        // value rows split into hi/lo once per call, then the tensor-core kernel gathering the band from global memory
+        rc = tc_matmul_pack_b(plan, v, (cudaStream_t)stream);
+        return rc ? rc : tc_gbmml_run(plan, p, y, (cudaStream_t)stream);
+    }
     // Split the band columns over blocks so that the last wave of blocks is not nearly empty: cost of a choice = waves of
     // resident blocks (four per SM) x chunks per block, plus a little per split for the reduction pass.
     const int chunks = (2 * w + 1 + kGJ - 1) / kGJ;

@@ -98,6 +98,9 @@ struct IgemmParams {
     int band_w;      // > 0: banded product y[b,i,j] = q[b,i,:] . k[b,i+j-w,:] (row-major A = q, "filters" = the keys of the window
                      // [128*tile - w, 128*tile + 127 + w] of the tile's rows, blockIdx.y = 64-key piece of that window); the
                      // epilogue stores the band entries of each row at their skewed positions, zero where the key is outside [0,n)
+    const float *band_p; // non-null: GBMML y[b,i,c] = sum_j p[b,i,j] * v[b,i+j-w,c]: the A operand is the band p [bs][n][2w+1] read
+                     // straight from global memory by the transform threads (row i of the tile meets key k through p[i][k-i+w]),
+                     // the "filters" are v's columns with the keys as K (window of the tile's rows, start rounded down to 4)
     int band_nt;     // banded product: 64-key pieces per row tile; the x tile index runs over (row tile, piece) pairs, piece fastest,
                      // so that the cheap pieces at the band's edges are spread over all CTAs
     int epi_direct;  // tuning: store the epilogue straight from registers (no transposition through shared memory)
@@ -124,7 +127,7 @@ __host__ __device__ inline SmemLayout smem_layout(const IgemmParams &P, bool a_t
     o = L.split_off + (P.ksplit > 1 ? 512u * (uint32_t)P.BN + 1024u : 0u); // + each tile row's offset in y (-1: none)
     // ping-pong mode: the epilogue's 32x32 transposition blocks need their own room (the B ring is never idle), one per warp
     L.stage_off = (o + 127) & ~127u;
-    o = L.stage_off + (P.pp ? 8u * 4096u : 0u);
+    o = L.stage_off + ((P.pp || (P.a_kmajor && P.band_w > 0)) ? 8u * 4096u : 0u); // (also GBMML's operand fetch)
     L.bar_off = (o + 15) & ~15u;
     L.total = L.bar_off + 384;
     return L;
@@ -379,6 +382,39 @@ __device__ __forceinline__ void gather_split(const int4 *ko, const float *raw, c
     }
 }
 
+// GBMML's operand fetch: one K stage = keys k0 .. k0 + 31; row i of the tile meets key k through the band entry p[i][k - i + w].
+// The 32 entries of a row are contiguous in global memory but every row starts elsewhere, so the warp fetches them row by
+// row (lane = key: one coalesced 128-byte read per row; entries outside the band, the row range or the sequence count as
+// zero) into an XOR-swizzled 32 x 32 block of shared memory, from which each thread then takes its own row.
+template <int PASSES>
+__device__ __forceinline__ void gather_band(const float *pb /*band of this batch entry*/, int n, int w, int i0 /*first row of the warp*/, int k0,
+                                            float *stage, int lane, uint32_t (&hi)[32], uint32_t (&lo)[32]) {
+    const int bw = 2 * w + 1, key = k0 + lane;
+    const bool key_ok = key >= 0 && key < n;
+    const float *src = pb + (long long)i0 * bw + (key - i0 + w); // row r: src + r * (bw - 1)
+    float v[32];
+#pragma unroll
+    for (int r = 0; r < 32; ++r, src += bw - 1) {
+        const int j = key - (i0 + r) + w;
+        v[r] = (key_ok && i0 + r < n && j >= 0 && j < bw) ? __ldg(src) : 0.f;
+    }
+    __syncwarp(); // the previous stage's reads of the block are done
+#pragma unroll
+    for (int r = 0; r < 32; ++r)
+        stage[r * 32 + (lane ^ r)] = v[r];
+    __syncwarp();
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+        const float x = stage[lane * 32 + (e ^ lane)];
+        if (PASSES == kMathTf32x3) {
+            hi[e] = __float_as_uint(x) & 0xffffe000u;
+            lo[e] = __float_as_uint(x - __uint_as_float(hi[e]));
+        } else {
+            hi[e] = ptx::cvt_rna_tf32(x);
+        }
+    }
+}
+
 // Split-K reduction inside a thread-block cluster.  The ksplit CTAs of one output tile form a cluster; CTA `rank` owns
 // BN/ksplit columns of the tile, and every CTA has pushed its partial sums of those columns into this CTA's shared memory
 // as [source rank][column][pixel].  A thread adds the ksplit copies of an element in rank order (the sum does not depend
@@ -495,7 +531,9 @@ __device__ __noinline__ bool drain_only_set(uint32_t tq /*TMEM address of this w
     return true;
 }
 
-template <bool A_TMEM, bool A_KMAJOR, int PASSES, bool PP = false>
+// BAND: 0 ordinary operands; 1 G2BMM (banded epilogue, key windows per tile; persistent row-major mode only); 2 GBMML (A operand
+// gathered from the band in global memory; row-major mode only).  Kernels of their own, so that the others carry none of it.
+template <bool A_TMEM, bool A_KMAJOR, int PASSES, bool PP = false, int BAND = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_bhi,
         const __grid_constant__ CUtensorMap tmap_blo, const IgemmParams P) {
@@ -591,7 +629,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     int nt_cur = ntile; // filter tile of the current pixel tile (differs per tile only for banded products)
     auto set_tile = [&](int tile) {
         bx = tile;
-        if (PP && A_KMAJOR && P.band_w > 0) {
+        if (BAND == 1) {
             bx = tile / P.band_nt;
             nt_cur = tile - bx * P.band_nt;
         }
@@ -678,13 +716,16 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 uint8_t *dst = sB + (size_t)sb * 2 * b_half;
                 ptx::mbar_expect_tx(b_full + sb, (SPLIT ? 2u : 1u) * b_half + (P.starve ? 64u : 0u));
                 const int kst = ntl > 1 ? ks % KS : ks;
-                if (PP && A_KMAJOR && P.band_w > 0) { // the key window moves with the row tile (rows before the tensor or past it read as zero / are masked)
+                int kx = (c0 * P.spc + kst) * KE; // first K element of the stage
+                if (BAND == 2) // the key window of the row tile, start rounded down to a multiple of 4
+                    kx += (((int)blockIdx.x * kTileM - P.band_w) & ~3);
+                if (BAND == 1) { // the key window moves with the row tile (rows before the tensor or past it read as zero / are masked)
                     const int tile = (int)blockIdx.x + (ks / KS) * (int)gridDim.x, rt = tile / P.band_nt;
                     row0 = zb * P.m_rows + rt * kTileM - P.band_w + (tile - rt * P.band_nt) * P.BN;
                 }
-                ptx::tma_load_2d(dst, &tmap_bhi, b_full + sb, (c0 * P.spc + kst) * KE, row0);
+                ptx::tma_load_2d(dst, &tmap_bhi, b_full + sb, kx, row0);
                 if (SPLIT)
-                    ptx::tma_load_2d(dst + b_half, &tmap_blo, b_full + sb, (c0 * P.spc + kst) * KE, row0);
+                    ptx::tma_load_2d(dst + b_half, &tmap_blo, b_full + sb, kx, row0);
                 if (++sb == P.NB) {
                     sb = 0;
                     pb ^= 1u;
@@ -699,7 +740,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             int rb = 0;
             uint32_t pr = 1; // first pass over the ring: every buffer is free
             bool go = true;
-            for (int tl = 0; tl < ntl && go; ++tl) {
+            for (int tl = 0; tl < ntl && go && !(BAND == 2); ++tl) { // (GBMML reads its A operand from global memory)
             if (tl > 0)
                 set_tile((int)blockIdx.x + tl * (int)gridDim.x);
             const int n_start = P.z_is_batch ? zb : n_lo;
@@ -1087,7 +1128,9 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         uint32_t pa = PP ? (own_apar & 1u) : 1u;
         for (int ch = 0; ch < ((reg_total && tset == 1) ? 0 : c1 - c0) && alive; ++ch, st -= P.spc) {
             const long long cr0 = P.prof ? clock64() : 0;
-            alive = ptx::mbar_wait(raw_full + rb, prw, abort_flag); // also by a set without a stage in this chunk
+            const bool band_gather = BAND == 2; // no raw tiles: the operands come from global memory
+            if (!band_gather)
+                alive = ptx::mbar_wait(raw_full + rb, prw, abort_flag); // also by a set without a stage in this chunk
             if (P.prof)
                 t_wr += clock64() - cr0;
             const float *raw = reinterpret_cast<const float *>(sRaw + (size_t)rb * P.raw_bytes) + base_p;
@@ -1119,7 +1162,14 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                     uint32_t hi[32], lo[32];
                     const uint8_t *krow = sRaw + (size_t)rb * P.raw_bytes + (size_t)p * 128;
                     const long long cg0 = P.prof ? clock64() : 0;
-                    if (A_KMAJOR)
+                    if (BAND == 2) {
+                        // stage (c0 + ch) of the tile covers keys k0 .. k0 + 31 of the row tile's window
+                        const int k0 = ((bx * kTileM - P.band_w) & ~3) + (c0 + ch) * kStageK;
+                        if (PASSES != kMathBf16x3)
+                            gather_band<PASSES>(P.band_p + (long long)zb * P.m_rows * (2 * P.band_w + 1), P.m_rows, P.band_w,
+                                                bx * kTileM + (warp & 3) * 32, k0, reinterpret_cast<float *>(smem + L.stage_off) + (warp - 3) * 1024,
+                                                lane, hi, lo);
+                    } else if (A_KMAJOR)
                         gather_split<kGatherKMajor, PASSES>(ko, raw, krow, p, tmask, 0, false, zero_word, hi, lo);
                     else if (P.cstride) // runs per stage: 1, 2 or 4 of 32 TF32 values; 2, 4 or 8 of 64 bf16 values
                         if (!BF && P.gruns == 1)
@@ -1193,7 +1243,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                 }
             }
             __syncwarp();
-            if (lane == 0 && alive)
+            if (lane == 0 && alive && !band_gather)
                 ptx::mbar_arrive(raw_empty + rb);
             if (++rb == P.NR) {
                 rb = 0;
@@ -1256,7 +1306,7 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
 #define PETB200_EPI(ACT_)                                                                                              \
     epilogue_store<ACT_, PASSES>(tacc, tcross, P.BN, f_tile0, P.Fg, valid, bp, rp, yp, P.ys_f, vec_ok, stage, nvalid_warp, \
                                  ybase_warp, rbase_warp, col0, col1, split_addr, split_shift)
-            if (PP && A_KMAJOR && P.band_w > 0) // (only that variant carries the code)
+            if (BAND == 1) // (only that variant carries the code)
                 epilogue_banded<PASSES>(tacc, tcross, P.BN, nt_cur * P.BN, (warp & 3) * 32, bx, zb, P.m_rows, P.band_w, P.y,
                                         reinterpret_cast<float *>(smem + L.stage_off) + (warp - 3) * 1024, lane);
             else
@@ -1446,9 +1496,9 @@ struct TcCore {
     int starve = 0;
 
     void (*kernel() const)(CUtensorMap, CUtensorMap, CUtensorMap, IgemmParams) {
-        if (P.pp) { // conv plans on the TS variant, and banded products (row-major A)
-            if (P.a_kmajor)
-                return k_igemm<true, true, kMathTf32x3, true>;
+        if (P.a_kmajor && P.band_w > 0) // banded products: G2BMM in persistent mode with its own epilogue, GBMML with its own operand fetch
+            return P.pp ? k_igemm<true, true, kMathTf32x3, true, 1> : k_igemm<true, true, kMathTf32x3, false, 2>;
+        if (P.pp) { // conv plans on the TS variant
             if (single_pass)
                 return k_igemm<true, false, kMathTf32x1, true>;
             return bf16 ? k_igemm<true, false, kMathBf16x3, true> : k_igemm<true, false, kMathTf32x3, true>;
@@ -1697,7 +1747,9 @@ static int raise_smem_limit(petb200_ctx *ctx) {
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(k_igemm<true, false, kMathTf32x1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(k_igemm<true, true, kMathTf32x3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+        e = cudaFuncSetAttribute(k_igemm<true, true, kMathTf32x3, true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(k_igemm<true, true, kMathTf32x3, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
     if (e != cudaSuccess)
         return fail(ctx, PETB200_ERR_CUDA, "cudaFuncSetAttribute(%d bytes) failed: %s", lim, cudaGetErrorString(e));
     attr_set = true;
@@ -2409,6 +2461,77 @@ int tc_g2bmm_create(petb200_ctx *ctx, int bs, int n, int m, int w, void **out) {
         fprintf(stderr, "[petb200] g2bmm plan: grid %u x %u x %u, NB %d NR %d\n", core.grid.x, core.grid.y, core.grid.z, P.NB, P.NR);
     *out = t;
     return PETB200_OK;
+}
+
+// GBMML on the tensor-core kernel (dilation 1): y [bs][n][m] = band p [bs][n][2w+1] times the value rows v [bs][n][m] it points at.
+// Rows are the M dimension, v's columns the filters (packed like a matmul's B operand with the keys as K), and the K range
+// of a row tile is the key window [128*tile - w, 128*tile + 127 + w]; the transform threads read the band from global memory.
+int tc_gbmml_create(petb200_ctx *ctx, int bs, int n, int m, int w, void **out) {
+    if (ctx->cc_major != 10)
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "tcgen05 kernels need compute capability 10.x");
+    if (m % 4 != 0 || m > 128 || w <= 0)
+        return fail(ctx, PETB200_ERR_UNSUPPORTED, "tensor-core gbmml needs m divisible by 4 and at most 128");
+    auto *t = new TcMatmul();
+    t->bs = bs, t->m = n, t->n = m, t->k = n, t->transB = 0;
+    t->st[2] = (long long)n * m, t->st[3] = m; // v: batch stride, stride of a key row
+    t->native_a = true;
+    TcCore &core = t->core;
+    core.ctx = ctx;
+    IgemmParams &P = core.P;
+    memset(&P, 0, sizeof P);
+    core.a_tmem = true;
+    P.a_kmajor = 1, P.ke = kStageK, P.m_rows = n, P.z_is_batch = 1, P.band_w = w;
+    P.OD = P.OH = 1, P.OW = n, P.ohn = 1, P.own = n, P.Pw = n, P.units = 1, P.ipt = 1, P.tpi = (n + kTileM - 1) / kTileM;
+    P.sd = P.sh = P.sw = 1;
+    P.cpg = n, P.Fg = m, P.BN = m <= 32 ? 32 : (m <= 64 ? 64 : 128), P.ksplit = 1;
+    P.BC = P.ke, P.spc = 1, P.nchunks = (2 * w + kTileM + 3 + P.ke - 1) / P.ke; // K stages of one row tile's key window
+    P.RN = P.RD = 1, P.RH = kTileM, P.RW = kStageK, P.raw_bytes = 128; // no raw tiles
+    P.ys_n = (long long)n * m, P.ys_f = 1, P.ys_p = m;
+    P.NA = 4, P.NB = 2, P.NR = 2;
+    P.mtiles = P.tpi;
+    const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 1024;
+    for (bool grew = true; grew;) {
+        grew = false;
+        if (P.NB < kMaxNB) {
+            P.NB++;
+            if (smem_layout(P, true).total <= budget)
+                grew = true;
+            else
+                P.NB--;
+        }
+    }
+    choose_flush(core);
+    core.smem = smem_layout(P, true).total + 1024;
+    core.Ktot = ((long long)n + P.ke - 1) / P.ke * P.ke; // the packed operand covers all keys; a tile reads its window of them
+    core.xd[0] = kStageK, core.xd[1] = kTileM, core.xd[2] = 1; // (the activation map is not used: any valid extents)
+    core.a_batch = kStageK * kTileM, core.a_row = kStageK;
+    std::vector<int> koff(P.ke, -1);
+    if (core.koff.alloc(koff.size() * 4) != cudaSuccess) {
+        delete t;
+        return fail(ctx, PETB200_ERR_NOMEM, "koff allocation failed");
+    }
+    cudaMemcpy(core.koff.p, koff.data(), koff.size() * 4, cudaMemcpyHostToDevice);
+    core.grid = dim3((unsigned)P.tpi, (unsigned)((m + P.BN - 1) / P.BN), (unsigned)bs);
+    core.y_elems = (long long)bs * n * m;
+    core.rows_b = bs * m;
+    const size_t wbytes = (size_t)bs * m * core.Ktot * 4;
+    int rc = raise_smem_limit(ctx);
+    if (rc == PETB200_OK && (core.whi.alloc(wbytes) != cudaSuccess || core.wlo.alloc(wbytes) != cudaSuccess))
+        rc = fail(ctx, PETB200_ERR_NOMEM, "packed value allocation failed");
+    if (rc == PETB200_OK)
+        rc = core.encode_b();
+    if (rc) {
+        delete t;
+        return rc;
+    }
+    *out = t;
+    return PETB200_OK;
+}
+// runs a GBMML plan: `p` is the band, `y` the result (the values v were packed by tc_matmul_pack_b)
+int tc_gbmml_run(void *h, const float *p, float *y, cudaStream_t s) {
+    auto *t = (TcMatmul *)h;
+    t->core.P.band_p = p;
+    return t->core.launch(p, nullptr, nullptr, y, s); // (the activation map is encoded over p but never used by this mode)
 }
 
 void tc_matmul_set_prof(void *h, long long *p) { ((TcMatmul *)h)->core.prof = p; }

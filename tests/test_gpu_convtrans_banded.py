@@ -207,7 +207,8 @@ def test_banded_reference_shape_properties(ctx):
         p[:, :, j0] = 1.0
         o = ctx.gbmml(p, k, d)
         shift = d * (j0 - w)
-        assert torch.equal(o[0, : n - shift], k[0, shift:])
+        # (times 1.0 on the tensor cores: hi + lo of the split value, each kept to TF32's 11 bits -> 2^-21 relative)
+        assert bool(((o[0, : n - shift] - k[0, shift:]).abs() <= 1e-6 * k[0, shift:].abs()).all())
         assert float(o[0, n - shift:].abs().max()) == 0.0
     assert 0 < ctx.banded_time("g2bmm", 1, n, m, w, 1, rounds=5, warmup=2) < 50.0
     assert 0 < ctx.banded_time("gbmml", 1, n, m, w, 1, rounds=5, warmup=2) < 50.0
