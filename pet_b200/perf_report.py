@@ -196,6 +196,22 @@ def once_conv(ctx):
     print(f"once_conv  transposed conv {name}: {2.0 * np.prod(xs) * ws[0] * ws[1] * ws[3] / 1e9:.3f} GFLOP useful")
 
 
+def once_banded(ctx):
+    """G2BMM and GBMML at the shape the reference ships kernels for, each launched twice (warm-up + one)."""
+    import torch
+    b, n, m, w, d = BANDED[0]
+    q, k = torch.randn((b, n, m), device="cuda"), torch.randn((b, n, m), device="cuda")
+    p = torch.randn((b, n, 2 * w + 1), device="cuda")
+    for _ in range(2):
+        ctx.g2bmm(q, k, w, d)
+        torch.cuda.synchronize()
+    for _ in range(2):
+        ctx.gbmml(p, k, d)
+        torch.cuda.synchronize()
+    fl, by = 2.0 * b * n * (2 * w + 1) * m, 4.0 * b * n * (2 * m + 2 * w + 1)
+    print(f"once_banded  g2bmm / gbmml b{b} n{n} m{m} w{w} d{d}: {fl / 1e9:.3f} GFLOP, {by / 1e6:.1f} MB algorithmic each")
+
+
 def once_rn18(ctx, batch):
     """One ResNet-18 forward pass at `batch`, operator by operator (no CUDA graph), after one warm-up pass."""
     import torch
@@ -270,6 +286,8 @@ def main(argv):
         once_matmul(ctx)
     if "once_conv" in groups:
         once_conv(ctx)
+    if "once_banded" in groups:
+        once_banded(ctx)
     if "once_rn18" in groups:
         i = groups.index("once_rn18")
         once_rn18(ctx, int(groups[i + 1]) if i + 1 < len(groups) and groups[i + 1].isdigit() else 64)
