@@ -86,7 +86,9 @@ __global__ void __launch_bounds__(256) k_batchnorm_plane(const float *__restrict
 
 // Pooling with small windows, the input rows of a band of output rows staged in shared memory: the band is one contiguous
 // run of the plane, so it is fetched with fully coalesced loads once, and the window walks (strided, overlapping) hit
-// shared memory instead of L1.  blockIdx.x = band of `ohb` output rows, blockIdx.y walks the planes.
+// shared memory instead of L1.  blockIdx.x = band of `ohb` output rows, blockIdx.y walks the planes.  MAX3S2: the window is
+// 3x3, the stride 2 and the operator max (ResNet's stem pool), all at compile time: nine unrolled, predicated compares.
+template <bool MAX3S2>
 __global__ void __launch_bounds__(256) k_pool2d_tiled(int kind, const float *__restrict__ x, float *__restrict__ y, int nc, int h,
                                                       int w, int oh, int ow, int kh, int kw, int ph, int pw, int sh, int sw,
                                                       int ohb, int rows_in) {
@@ -115,7 +117,7 @@ __global__ void __launch_bounds__(256) k_pool2d_tiled(int kind, const float *__r
                 const int ys = (o0 + ii) * sh - ph, xs = j * sw - pw;
                 const int a0 = max(0, -ys), a1 = min(kh, h - ys), b0 = max(0, -xs), b1 = min(kw, w - xs);
                 float best = -INFINITY, acc = 0.f;
-                for (int a = a0; a < a1; ++a) {
+                for (int a = a0; a < a1 && !MAX3S2; ++a) {
                     const float *row = tile + (ys + a - y0) * w + xs;
                     for (int b = b0; b < b1; ++b) {
                         const float v = row[b];
@@ -124,6 +126,18 @@ __global__ void __launch_bounds__(256) k_pool2d_tiled(int kind, const float *__r
                     }
                 }
                 const int cnt = max(a1 - a0, 0) * max(b1 - b0, 0);
+                if (MAX3S2) {
+                    best = -INFINITY;
+                    const float *row = tile + (ys - y0) * w + xs;
+#pragma unroll
+                    for (int a = 0; a < 3; ++a)
+#pragma unroll
+                        for (int b = 0; b < 3; ++b)
+                            if (a >= a0 && a < a1 && b >= b0 && b < b1)
+                                best = fmaxf(best, row[a * w + b]);
+                    y[((size_t)plane * oh + o0 + ii) * ow + j] = best;
+                    continue;
+                }
                 y[((size_t)plane * oh + o0 + ii) * ow + j] = kind == 0 ? best : (cnt ? acc / (float)cnt : 0.f);
             }
         }
@@ -591,9 +605,14 @@ extern "C" int petb200_pool2d_run(petb200_ctx *ctx, int kind, const float *x, fl
         const int ohb = std::min(16, (6144 / w - kh) / sh + 1);
         if (ohb >= 1) {
             const int rows_in = (ohb - 1) * sh + kh;
-            launch_pdl(k_pool2d_tiled, dim3((unsigned)((oh + ohb - 1) / ohb), (unsigned)std::min(n * c, 16384)), dim3(256),
-                       (size_t)rows_in * w * sizeof(float), (cudaStream_t)stream, kind, x, y, n * c, h, w, oh, ow, kh, kw, ph, pw, sh, sw, ohb,
-                       rows_in);
+            if (kind == 0 && kh == 3 && kw == 3 && sh == 2 && sw == 2)
+                launch_pdl(k_pool2d_tiled<true>, dim3((unsigned)((oh + ohb - 1) / ohb), (unsigned)std::min(n * c, 16384)), dim3(256),
+                           (size_t)rows_in * w * sizeof(float), (cudaStream_t)stream, kind, x, y, n * c, h, w, oh, ow, kh, kw, ph, pw, sh, sw,
+                           ohb, rows_in);
+            else
+                launch_pdl(k_pool2d_tiled<false>, dim3((unsigned)((oh + ohb - 1) / ohb), (unsigned)std::min(n * c, 16384)), dim3(256),
+                           (size_t)rows_in * w * sizeof(float), (cudaStream_t)stream, kind, x, y, n * c, h, w, oh, ow, kh, kw, ph, pw, sh, sw,
+                           ohb, rows_in);
             return launched(ctx, "k_pool2d_tiled");
         }
     }
