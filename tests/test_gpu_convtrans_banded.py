@@ -175,6 +175,31 @@ def test_banded_products_vs_oracle(ctx, oracle, case):
     assert np.array_equal(ctx.gbmml(dev(p_bad), dev(k), d).cpu().numpy(), o)
 
 
+def test_banded_tensor_core_path_agrees_with_the_cuda_core_kernels(ctx, oracle):
+    """Dilation 1 with 16-byte aligned operands runs on the tensor-core kernel (3xTF32); operands that start 4 bytes off an
+    aligned address take the exact-fp32 CUDA-core kernels.  Same definition, two implementations: they agree within the
+    contract's bound, both meet it against the oracle, and masked positions are exact zeros on both."""
+    b, n, m, w = 2, 700, 64, 150
+    rng = np.random.default_rng(77)
+    q, k = (rng.standard_normal((b, n, m)).astype(np.float32) for _ in range(2))
+    p = rng.standard_normal((b, n, 2 * w + 1)).astype(np.float32)
+
+    def shifted(a):  # the same values at an address that is 4 bytes off a 16-byte boundary
+        flat = torch.empty(a.size + 1, device="cuda", dtype=torch.float32)
+        flat[1:] = torch.from_numpy(a.reshape(-1)).cuda()
+        return flat[1:].view(a.shape)
+
+    s_tc, s_cc = ctx.g2bmm(dev(q), dev(k), w, 1).cpu().numpy(), ctx.g2bmm(shifted(q), shifted(k), w, 1).cpu().numpy()
+    o_tc, o_cc = ctx.gbmml(dev(p), dev(k), 1).cpu().numpy(), ctx.gbmml(shifted(p), shifted(k), 1).cpu().numpy()
+    ctx.sync_check()
+    want_s, want_o = oracle.g2bmm(q, k, w, 1, wide=True), oracle.gbmml(p, k, 1, wide=True)
+    for got, want in ((s_tc, want_s), (s_cc, want_s), (o_tc, want_o), (o_cc, want_o)):
+        assert rel_err(got, want) <= 1e-3
+    assert not np.array_equal(s_tc, s_cc) and rel_err(s_tc, s_cc) <= 1e-3 and rel_err(o_tc, o_cc) <= 1e-3
+    i = np.arange(n)[:, None] + (np.arange(2 * w + 1)[None, :] - w)
+    assert np.all(s_tc[:, (i < 0) | (i >= n)] == 0) and np.all(s_cc[:, (i < 0) | (i >= n)] == 0)
+
+
 def test_banded_products_small_integers_exact(ctx, oracle):
     rng = np.random.default_rng(8)
     q = rng.integers(0, 16, (2, 90, 24)).astype(np.float32)
