@@ -270,13 +270,13 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, uint32_t tcross, i
 // of the band, entries whose key is outside [0, n) are stored as zero.  A warp passes 32 rows x 32 columns through shared
 // memory (XOR-swizzled, conflict-free both ways) so that each store instruction writes 32 consecutive band columns of one row.
 template <int PASSES>
-__device__ __forceinline__ void epilogue_banded(uint32_t tacc, uint32_t tcross, int BN, int col_base, int p0, int bx, int zb, int n, int w,
-                                                float *y, float *stage, int lane) {
+__device__ __forceinline__ void epilogue_banded(uint32_t tacc, uint32_t tcross, int c_lo, int c_hi /*columns of the tile to store*/, int col_base,
+                                                int p0, int bx, int zb, int n, int w, float *y, float *stage, int lane) {
     uint32_t nx[32], sm[32];
     const int bw = 2 * w + 1;
     const int i0 = bx * kTileM + p0;    // first row of this warp
     const int rows = min(32, n - i0);   // rows of it inside the tensor
-    for (int cc = 0; cc < BN; cc += 32) {
+    for (int cc = c_lo; cc < c_hi; cc += 32) {
         const int lo = col_base + cc - p0; // jb of (row 0, lane 0); the block spans jb in [lo - 31, lo + 31]
         if (rows <= 0 || lo + 31 < 0 || lo - 31 >= bw)
             continue; // nothing of this block lies in the band
@@ -392,6 +392,11 @@ __device__ __forceinline__ void gather_band(const float *pb /*band of this batch
     const int bw = 2 * w + 1, key = k0 + lane;
     const bool key_ok = key >= 0 && key < n;
     const float *src = pb + (long long)i0 * bw + (key - i0 + w); // row r: src + r * (bw - 1)
+    {   // the band streams from DRAM: ask for the segment this warp will want four K stages on (lane = row), so that the
+        // loads below find theirs in the L2
+        const int ip = min(i0 + lane, n - 1), jp = min(max(k0 + 4 * kStageK - ip + w, 0), bw - 1);
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(pb + (long long)ip * bw + jp));
+    }
     float v[32];
 #pragma unroll
     for (int r = 0; r < 32; ++r, src += bw - 1) {
@@ -595,8 +600,8 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
         ptx::mbar_init(acc_ready, 1);
         ptx::mbar_init(flushed, P.fl_regs ? 4 : 8);
         ptx::mbar_init(acc_full1, 1);
-        ptx::mbar_init(acc_empty, 4);
-        ptx::mbar_init(acc_empty + 1, 4);
+        ptx::mbar_init(acc_empty, BAND == 1 ? 8 : 4); // (G2BMM: both sets read every tile out)
+        ptx::mbar_init(acc_empty + 1, BAND == 1 ? 8 : 4);
         *abort_flag = 0;
         *zero_word = 0.f;
         ptx::fence_mbar_init();
@@ -1043,6 +1048,69 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                     ptx::mbar_arrive(raw_empty + rseen % P.NR);
             }
         };
+        if (BAND == 1) {
+            // G2BMM: a tile is two K stages and 32 KB of skewed stores, so the epilogue is the long part: both sets store half
+            // of EVERY tile (32 of its 64 key columns each), and the set that owns tile t + 2's operands produces them right
+            // after its half of tile t, i.e. while the MMA warp is on tile t + 1.
+            const int nch = c1 - c0;
+            auto produce = [&](int tl) {
+                observe_until(tl * nch); // fills of the other set's tiles
+                if (!alive)
+                    return;
+                rseen += nch;
+                const int chunk0 = tl * nch;
+                int rb = chunk0 % P.NR, sa = 2 * tset;
+                uint32_t prw = (uint32_t)((chunk0 / P.NR) & 1);
+                for (int ch = 0; ch < nch && alive; ++ch) {
+                    alive = ptx::mbar_wait(raw_full + rb, prw, abort_flag);
+                    if (!alive)
+                        break;
+                    uint32_t hi[32], lo[32];
+                    gather_split<kGatherKMajor, PASSES>(nullptr, nullptr, sRaw + (size_t)rb * P.raw_bytes + (size_t)p * 128, p, 0u, 0, false,
+                                                        zero_word, hi, lo);
+                    alive = ptx::mbar_wait(a_empty + sa, (own_apar >> (sa & 1)) & 1u, abort_flag);
+                    if (!alive)
+                        break;
+                    ptx::tc_fence_after();
+                    const uint32_t t = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)P.a_col + (uint32_t)sa * 64u;
+                    ptx::tmem_st_32x32(t, hi);
+                    ptx::tmem_st_32x32(t + 32u, lo);
+                    ptx::tmem_st_wait();
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::mbar_arrive(a_full + sa);
+                        ptx::mbar_arrive(raw_empty + rb);
+                    }
+                    own_apar ^= 1u << (sa & 1);
+                    sa ^= 1;
+                    if (++rb == P.NR) {
+                        rb = 0;
+                        prw ^= 1u;
+                    }
+                }
+            };
+            if (tset < ntl)
+                produce(tset);
+            for (int tl = 0; tl < ntl && alive; ++tl) {
+                alive = ptx::mbar_wait((tl & 1) ? acc_full1 : acc_full, (uint32_t)((tl >> 1) & 1), abort_flag);
+                if (!alive)
+                    break;
+                ptx::tc_fence_after();
+                set_tile((int)blockIdx.x + tl * (int)gridDim.x);
+                const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((tl & 1) * 2 * P.BN);
+                epilogue_banded<PASSES>(tacc, tacc + (uint32_t)P.BN, tset * 32, tset * 32 + 32, nt_cur * P.BN, (warp & 3) * 32, bx, zb, P.m_rows,
+                                        P.band_w, P.y, reinterpret_cast<float *>(smem + L.stage_off) + (warp - 3) * 1024, lane);
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    ptx::mbar_arrive(acc_empty + (tl & 1));
+                if ((tl & 1) == tset && tl + 2 < ntl)
+                    produce(tl + 2);
+            }
+            observe_until(ntl * nch);
+        }
+        if (BAND != 1)
         for (int tl = PP ? tset : 0; tl < ntl && alive; tl += PP ? 2 : 1) {
         set_tile((int)blockIdx.x + tl * (int)gridDim.x); // (also for the only tile: nothing of it stays live across the code above)
         bool valid;
@@ -1306,10 +1374,6 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
 #define PETB200_EPI(ACT_)                                                                                              \
     epilogue_store<ACT_, PASSES>(tacc, tcross, P.BN, f_tile0, P.Fg, valid, bp, rp, yp, P.ys_f, vec_ok, stage, nvalid_warp, \
                                  ybase_warp, rbase_warp, col0, col1, split_addr, split_shift)
-            if (BAND == 1) // (only that variant carries the code)
-                epilogue_banded<PASSES>(tacc, tcross, P.BN, nt_cur * P.BN, (warp & 3) * 32, bx, zb, P.m_rows, P.band_w, P.y,
-                                        reinterpret_cast<float *>(smem + L.stage_off) + (warp - 3) * 1024, lane);
-            else
             switch (P.ksplit > 1 ? PETB200_ACT_NONE : P.act) {
             case PETB200_ACT_RELU: PETB200_EPI(PETB200_ACT_RELU); break;
             case PETB200_ACT_SIGMOID: PETB200_EPI(PETB200_ACT_SIGMOID); break;
