@@ -229,7 +229,11 @@ int petb200_convtrans_out_dims(const petb200_plan *plan, int out_nhwc[4]);
  * _sg2bmm / _sgbmml(a, b, y, bs, n, m, w, d) (ref: src/custom_ops.cu:6-14), any shape:
  *   g2bmm  y[b,i,j] = sum_k q[b,i,k] * k[b, i + d*(j-w), k]   q,k [bs,n,m] -> y [bs,n,2w+1]
  *   gbmml  y[b,i,k] = sum_j p[b,i,j] * v[b, i + d*(j-w), k]   p [bs,n,2w+1], v [bs,n,m] -> y [bs,n,m]
- * (ref: src/nnet/iterator_table.cc:597-633); rows outside [0,n) count as zero. */
+ * (ref: src/nnet/iterator_table.cc:597-633); rows outside [0,n) count as zero.
+ * Dilation 1 with m a multiple of 4 and 16-byte aligned operands runs on the tensor cores (error-compensated TF32, the accuracy
+ * of conv / matmul); the context then keeps one plan per shape, whose split copy of k / v is rewritten by every call: calls of
+ * one shape on one context must not overlap (one stream, or one after the other).  Everything else runs the exact-fp32
+ * CUDA-core kernels.  PETB200_BANDED_TC=0 in the environment keeps every call there. */
 int petb200_g2bmm_run(petb200_ctx *ctx, const float *q, const float *k, float *y, int bs, int n, int m, int w, int d,
                       petb200_stream stream);
 int petb200_gbmml_run(petb200_ctx *ctx, const float *p, const float *v, float *y, int bs, int n, int m, int w, int d,
