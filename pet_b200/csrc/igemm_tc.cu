@@ -127,7 +127,8 @@ __host__ __device__ inline SmemLayout smem_layout(const IgemmParams &P, bool a_t
     o = L.split_off + (P.ksplit > 1 ? 512u * (uint32_t)P.BN + 1024u : 0u); // + each tile row's offset in y (-1: none)
     // ping-pong mode: the epilogue's 32x32 transposition blocks need their own room (the B ring is never idle), one per warp
     L.stage_off = (o + 127) & ~127u;
-    o = L.stage_off + ((P.pp || (P.a_kmajor && P.band_w > 0)) ? 8u * 4096u : 0u); // (also GBMML's operand fetch)
+    // (GBMML's operand fetch, which is not in ping-pong mode, keeps two blocks per warp: one stage in flight)
+    o = L.stage_off + (P.pp ? 8u * 4096u : ((P.a_kmajor && P.band_w > 0) ? 16u * 4096u : 0u));
     L.bar_off = (o + 15) & ~15u;
     L.total = L.bar_off + 384;
     return L;
@@ -385,29 +386,33 @@ __device__ __forceinline__ void gather_split(const int4 *ko, const float *raw, c
 // GBMML's operand fetch: one K stage = keys k0 .. k0 + 31; row i of the tile meets key k through the band entry p[i][k - i + w].
 // The 32 entries of a row are contiguous in global memory but every row starts elsewhere, so the warp fetches them row by
 // row (lane = key: one coalesced 128-byte read per row; entries outside the band, the row range or the sequence count as
-// zero) into an XOR-swizzled 32 x 32 block of shared memory, from which each thread then takes its own row.
-template <int PASSES>
-__device__ __forceinline__ void gather_band(const float *pb /*band of this batch entry*/, int n, int w, int i0 /*first row of the warp*/, int k0,
-                                            float *stage, int lane, uint32_t (&hi)[32], uint32_t (&lo)[32]) {
+// zero) into an XOR-swizzled 32 x 32 block of shared memory, from which each thread then takes its own row.  The fetch is
+// asynchronous (cp.async, zero-filling what does not exist): band_issue starts the copies of a stage and closes a group,
+// band_take waits for the group and splits; the caller keeps one stage in flight while it works on the one before.
+__device__ __forceinline__ void band_issue(const float *pb /*band of this batch entry*/, int n, int w, int i0 /*first row of the warp*/, int k0,
+                                           float *stage, int lane) {
     const int bw = 2 * w + 1, key = k0 + lane;
     const bool key_ok = key >= 0 && key < n;
     const float *src = pb + (long long)i0 * bw + (key - i0 + w); // row r: src + r * (bw - 1)
-    {   // the band streams from DRAM: ask for the segment this warp will want four K stages on (lane = row), so that the
-        // loads below find theirs in the L2
-        const int ip = min(i0 + lane, n - 1), jp = min(max(k0 + 4 * kStageK - ip + w, 0), bw - 1);
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(pb + (long long)ip * bw + jp));
-    }
-    float v[32];
+    const uint32_t dst = ptx::smem_u32(stage);
 #pragma unroll
     for (int r = 0; r < 32; ++r, src += bw - 1) {
         const int j = key - (i0 + r) + w;
-        v[r] = (key_ok && i0 + r < n && j >= 0 && j < bw) ? __ldg(src) : 0.f;
+        const bool ok = key_ok && i0 + r < n && j >= 0 && j < bw;
+        // 4 bytes per lane; a source size of 0 writes zeros and reads nothing (the address is then a harmless valid one)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst + (uint32_t)(r * 32 + (lane ^ r)) * 4u), "l"(ok ? src : pb),
+                     "r"(ok ? 4 : 0)
+                     : "memory");
     }
-    __syncwarp(); // the previous stage's reads of the block are done
-#pragma unroll
-    for (int r = 0; r < 32; ++r)
-        stage[r * 32 + (lane ^ r)] = v[r];
-    __syncwarp();
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int PASSES>
+__device__ __forceinline__ void band_take(const float *stage, bool newer_in_flight, int lane, uint32_t (&hi)[32], uint32_t (&lo)[32]) {
+    if (newer_in_flight)
+        asm volatile("cp.async.wait_group 1;" ::: "memory"); // all but the newest group: this stage has landed
+    else
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp(); // every lane's copies
 #pragma unroll
     for (int e = 0; e < 32; ++e) {
         const float x = stage[lane * 32 + (e ^ lane)];
@@ -418,6 +423,7 @@ __device__ __forceinline__ void gather_band(const float *pb /*band of this batch
             hi[e] = ptx::cvt_rna_tf32(x);
         }
     }
+    __syncwarp(); // the block may be overwritten by a later stage's copies
 }
 
 // Split-K reduction inside a thread-block cluster.  The ksplit CTAs of one output tile form a cluster; CTA `rank` owns
@@ -1231,12 +1237,19 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
                     const uint8_t *krow = sRaw + (size_t)rb * P.raw_bytes + (size_t)p * 128;
                     const long long cg0 = P.prof ? clock64() : 0;
                     if (BAND == 2) {
-                        // stage (c0 + ch) of the tile covers keys k0 .. k0 + 31 of the row tile's window
-                        const int k0 = ((bx * kTileM - P.band_w) & ~3) + (c0 + ch) * kStageK;
-                        if (PASSES != kMathBf16x3)
-                            gather_band<PASSES>(P.band_p + (long long)zb * P.m_rows * (2 * P.band_w + 1), P.m_rows, P.band_w,
-                                                bx * kTileM + (warp & 3) * 32, k0, reinterpret_cast<float *>(smem + L.stage_off) + (warp - 3) * 1024,
-                                                lane, hi, lo);
+                        // stage (c0 + ch) of the tile covers keys k0 .. k0 + 31 of the row tile's window; this set's next stage
+                        // (two on) is fetched while this one is split and written
+                        if (PASSES != kMathBf16x3) {
+                            const int k0 = ((bx * kTileM - P.band_w) & ~3) + (c0 + ch) * kStageK, i0w = bx * kTileM + (warp & 3) * 32;
+                            const float *pb = P.band_p + (long long)zb * P.m_rows * (2 * P.band_w + 1);
+                            float *blk = reinterpret_cast<float *>(smem + L.stage_off) + (warp - 3) * 2048; // two blocks per warp
+                            const bool more = ch + sstep < c1 - c0;
+                            if (ch < sstep) // the set's first stage of the tile
+                                band_issue(pb, P.m_rows, P.band_w, i0w, k0, blk + ((ch / sstep) & 1) * 1024, lane);
+                            if (more)
+                                band_issue(pb, P.m_rows, P.band_w, i0w, k0 + sstep * kStageK, blk + ((ch / sstep + 1) & 1) * 1024, lane);
+                            band_take<PASSES>(blk + ((ch / sstep) & 1) * 1024, more, lane, hi, lo);
+                        }
                     } else if (A_KMAJOR)
                         gather_split<kGatherKMajor, PASSES>(ko, raw, krow, p, tmask, 0, false, zero_word, hi, lo);
                     else if (P.cstride) // runs per stage: 1, 2 or 4 of 32 TF32 values; 2, 4 or 8 of 64 bf16 values
