@@ -322,6 +322,63 @@ def library_baseline(ctx, ours_ms):
         finally:
             del os.environ["PETB200_TC_MATH"]
         out[name] = row
+    out["reference_calls"] = reference_calls(ctx)
+    return out
+
+
+def reference_calls(ctx):
+    """The reference's OWN library calls for single operators (baseline/ref_calls.cu: the descriptor set-up and the algorithm
+    sweeps of ConvOp::perf and MatmulOp::perf, restated), on the same seeded tensors as this backend: best time of the
+    sweep and the parity metric between the two outputs and against an exact (float64) product."""
+    import ctypes as C
+    import torch
+    from pet_b200 import configs
+    path = os.path.join(ROOT, "baseline", "libref_calls.so")
+    if not os.path.exists(path):
+        return {"unavailable": "baseline/libref_calls.so not built (make -C baseline)"}
+    lib = C.CDLL(path)
+    out = {"how": "baseline/ref_calls.cu: cudnnConvolutionForward over the reference's 8 algorithms with default math; "
+                  "cublasGemmStridedBatchedEx / cublasGemmEx with fp32 compute over the default and legacy algorithm ids; "
+                  "CUDA events over 100 launches after 20 warm-ups"}
+    ptr = lambda t: C.c_void_p(t.data_ptr())
+    x1, w1 = configs.c1_tensors()
+    x2, w2 = configs.c2_tensors()
+    for name, x, w, pad, dil in (("c1_conv3x3", x1, w1, 1, 1), ("c2_dilated_conv", x2, w2, 2, 2)):
+        xd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+        n, c, h, wdt = x.shape
+        f, cpg, r, s = w.shape
+        y = torch.empty((n, f, h, wdt), device="cuda")
+        ms, algo = C.c_float(), C.c_int()
+        # ConvOp::perf sets CUDNN_CONVOLUTION mode (the filter is flipped); hand it the flipped filter so that both arms
+        # compute the same cross-correlation and the outputs can be compared
+        wflip = wd.flip(2, 3).contiguous()
+        rc = lib.refcalls_conv2d(ptr(xd), ptr(wflip), ptr(y), n, c, h, wdt, f, cpg, r, s, pad, pad, 1, 1, dil, dil, 100, 20, C.byref(ms), C.byref(algo))
+        if rc != 0:
+            out[name] = {"unavailable": "no cuDNN algorithm ran"}
+            continue
+        ours = ctx.conv2d(xd, wd, pad, pad, 1, 1, dil, dil)
+        plan = ctx.conv2d_plan(x.shape, w.shape, pad, pad, 1, 1, dil, dil)
+        exact = torch.nn.functional.conv2d(xd.double(), wd.double(), padding=pad, dilation=dil).cpu().numpy()
+        out[name] = {"library_best_ms": ms.value, "library_algo_index": algo.value, "ours_ms": plan.time(100, 20),
+                     "library_err_vs_exact": contract_metric(y.cpu().numpy(), exact), "ours_err_vs_exact": contract_metric(ours.cpu().numpy(), exact)}
+    g = torch.Generator(device="cuda").manual_seed(5)
+    for name, b, m, n, k in (("bert_qkv_128x768x768", 1, 128, 768, 768), ("bert_ffn1_128x3072x768", 1, 128, 3072, 768),
+                             ("bert_ffn2_128x768x3072", 1, 128, 768, 3072), ("bert_scores_12x128x128x64", 12, 128, 128, 64)):
+        a = torch.randn((b, m, k), device="cuda", generator=g)
+        bm = torch.randn((b, k, n), device="cuda", generator=g) / k ** 0.5
+        cm = torch.empty((b, m, n), device="cuda")
+        ms, algo = C.c_float(), C.c_int()
+        rc = lib.refcalls_matmul(ptr(a), ptr(bm), ptr(cm), b, m, n, k, 0, 0, 100, 20, C.byref(ms), C.byref(algo))
+        if rc != 0:
+            out[name] = {"unavailable": "no cuBLAS algorithm ran"}
+            continue
+        plan = ctx.matmul_plan(a.shape, bm.shape)
+        ctx.matmul_set_weights(plan, bm)
+        ours = ctx.matmul_run(plan, a, None)
+        torch.cuda.synchronize()
+        exact = (a.double() @ bm.double()).cpu().numpy()
+        out[name] = {"library_best_ms": ms.value, "library_algo": algo.value, "ours_ms": time_cuda_graph(lambda: ctx.matmul_run(plan, a, None), 100),
+                     "library_err_vs_exact": contract_metric(cm.cpu().numpy(), exact), "ours_err_vs_exact": contract_metric(ours.cpu().numpy(), exact)}
     return out
 
 
