@@ -188,6 +188,15 @@ int petb200_pool2d_run(petb200_ctx *ctx, int kind, const float *x, float *y, int
 int petb200_rowmean_run(petb200_ctx *ctx, const float *x, float *y, size_t rows, int cols, petb200_stream stream);
 /* SoftmaxOp over the last axis (ref: online_softmax, src/Graph/code_engine.cc:424-486,1707-1731). */
 int petb200_softmax_run(petb200_ctx *ctx, const float *x, float *y, size_t rows, int cols, petb200_stream stream);
+/* The chain MatmulOp (transB) -> SoftmaxOp (last axis) -> MatmulOp of an attention head in one launch (ref: the three
+ * operators' compute, src/Graph/operator.cc:632-651 and src/Graph/code_engine.cc:424-486): out[b] = softmax_rows(q[b] k[b]^T) v[b]
+ * with q [bs, m, kd], k [bs, n, kd], v [bs, n, d], out [bs, m, d], in plain fp32 (no TF32), the softmax with the sums of
+ * petb200_softmax_run.  strides = {q batch, q row, k batch, k row, v batch, v row, out batch, out row} in elements (rows
+ * themselves contiguous), NULL for dense tensors.  Serves n, kd, d <= 128 (petb200_attention_supported returns 1);
+ * anything else is PETB200_ERR_UNSUPPORTED and the caller runs the three operators. */
+int petb200_attention_supported(int m, int n, int kd, int d);
+int petb200_attention_run(petb200_ctx *ctx, const float *q, const float *k, const float *v, float *out, int bs, int m, int n,
+                          int kd, int d, const long long *strides, petb200_stream stream);
 /* SoftmaxOp over any axis (the operator carries one, ref: include/operator.h:1887-1938; the reference's emitted kernel
  * only serves the last): x viewed as [outer, len, inner], normalised over len.  inner == 1 is petb200_softmax_run. */
 int petb200_softmax_axis_run(petb200_ctx *ctx, const float *x, float *y, size_t outer, int len, size_t inner,

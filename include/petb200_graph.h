@@ -83,7 +83,8 @@ int petb200_graph_correction(petb200_graph *g, int x, int w, int bias, int y, in
 int petb200_graph_set_outputs(petb200_graph *g, int n, const int *tensors);
 
 /* Orders, fuses, plans, allocates device memory.  flags: bit 0 = do not fuse; bit 1 = do not capture a CUDA graph;
- * bit 2 = keep every step on the caller's stream (no side stream for shortcut branches). */
+ * bit 2 = keep every step on the caller's stream (no side stream for shortcut branches); bit 3 = keep an attention head
+ * (Matmul(transB) -> Softmax -> Matmul) as three steps instead of one petb200_attention_run launch. */
 int petb200_graph_compile(petb200_graph *g, int flags);
 /* Host <-> device transfer of one tensor (n floats). set_data on a weight re-runs the weight preprocessing. */
 int petb200_graph_set_data(petb200_graph *g, int tensor, const float *host, size_t n, petb200_stream stream);

@@ -19,7 +19,8 @@ using Dim = std::vector<int>;
 
 // OpType values follow the reference's enum names (ref: include/operator.h:19-51) for the operators that exist there.
 enum OpType { Conv, Matmul, Transpose, Pad, Slice, Concat, Split, Extend, Add, Sub, Mul, Activation, MaxPool, AvgPool,
-              Softmax, BatchNorm, Reshape, Conv3d, LayerNorm, Correction, ConvTrans, G2BMM, GBMML, Div, Pow, ReduceMean, Gather };
+              Softmax, BatchNorm, Reshape, Conv3d, LayerNorm, Correction, ConvTrans, G2BMM, GBMML, Div, Pow, ReduceMean, Gather,
+              Attention /* a step only: Matmul(transB) -> Softmax -> Matmul fused by the executor */ };
 
 struct Tensor {
     Dim dims;
@@ -88,6 +89,9 @@ struct Step {
     // second stream beside the steps between it and that reader:
     bool side = false;
     int join_from = -1;        // index of the side step this step has to wait for, or -1
+    // Attention step: extents {bs, m, n, kd, d}, the tensors read as q, k, v and written, their batch / row strides
+    int att_dims[5] = {0, 0, 0, 0, 0}, att_t[4] = {-1, -1, -1, -1};
+    long long att_st[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 };
 
@@ -317,6 +321,9 @@ int petb200_graph::run_step(Step &s, cudaStream_t st) {
                                           dev_of(this, op.inputs[3]), dev_of(this, op.inputs[4]), dev_of(this, op.outputs[0]), (size_t)d[0], d[1],
                                           inner, op.eps, st));
     }
+    case Attention:
+        return pass(petb200_attention_run(ctx, dev_of(this, s.att_t[0]), dev_of(this, s.att_t[1]), dev_of(this, s.att_t[2]), dev_of(this, s.att_t[3]),
+                                          s.att_dims[0], s.att_dims[1], s.att_dims[2], s.att_dims[3], s.att_dims[4], s.att_st, st));
     case Reshape:
         return PETB200_OK;
     }
@@ -634,10 +641,70 @@ int petb200_graph::compile(int flags) {
 
     // ---- build steps with fusion ----
     std::vector<char> emitted(n, 0); // operators already covered by a step
+    // An attention head, Matmul(q, k^T) -> Softmax(last axis) -> Matmul(p, v) with no other reader of the scores or of the
+    // probabilities, becomes one launch.  The step is emitted at the position of the SECOND product (by then v exists too);
+    // the first product and the softmax are remembered here, keyed by the second product's id.
+    static const bool fuse_attention = [] { const char *e = getenv("PETB200_FUSE_ATTENTION"); return !e || atoi(e) != 0; }();
+    std::map<int, int> attn_first; // second matmul -> first matmul
+    auto attention_tail = [&](const Operator &m1) -> int { // id of the second product if m1 starts such a chain, else -1
+        if (m1.type != Matmul || m1.transA || !m1.transB || m1.bias >= 0 || m1.act != 0 || m1.merged_out >= 0 || m1.mm_out_op >= 0 ||
+            tensors[m1.inputs[0]].weight || tensors[m1.inputs[1]].weight)
+            return -1;
+        const int sm = sole_consumer(m1.outputs[0]);
+        if (sm < 0 || ops[sm].type != Softmax || ops[sm].fused_away || tensors[ops[sm].inputs[0]].dims.size() != 3 || ops[sm].axis != 2)
+            return -1;
+        const int c2 = sole_consumer(ops[sm].outputs[0]);
+        if (c2 < 0)
+            return -1;
+        const Operator &m2 = ops[c2];
+        if (m2.type != Matmul || m2.fused_away || m2.inputs[0] != ops[sm].outputs[0] || m2.transA || m2.transB || m2.bias >= 0 || m2.act != 0 ||
+            m2.merged_out >= 0 || m2.mm_in[0] >= 0 || tensors[m2.inputs[1]].weight)
+            return -1;
+        const Dim &sd = tensors[m1.outputs[0]].dims, &qd = tensors[m1.inputs[0]].dims, &od = tensors[m2.outputs[0]].dims; // [bs,m,n] [bs,m,kd] [bs,m,d]
+        if (od[0] != sd[0] || !petb200_attention_supported(sd[1], sd[2], qd[2], od[2]))
+            return -1;
+        return c2;
+    };
     for (int id : order) {
         Operator &op = ops[id];
         if (op.fused_away)
             continue;
+        if (fuse && fuse_attention && !(flags & 8) && op.type == Matmul) {
+            const int tail = attention_tail(op);
+            if (tail >= 0) { // deferred to the second product
+                attn_first[tail] = id;
+                op.fused_away = true;
+                ops[sole_consumer(op.outputs[0])].fused_away = true;
+                continue;
+            }
+        }
+        if (op.type == Matmul && attn_first.count(id)) {
+            const Operator &m1 = ops[attn_first[id]];
+            const int sm = tensors[m1.outputs[0]].inputOf[0];
+            const Dim &sd = tensors[m1.outputs[0]].dims, &qd = tensors[m1.inputs[0]].dims, &od = tensors[op.outputs[0]].dims;
+            Step a;
+            a.type = Attention;
+            a.name = "attention";
+            a.kernel = "k_attention";
+            a.ops = {attn_first[id], sm, id};
+            if (op.mm_out_op >= 0)
+                a.ops.push_back(op.mm_out_op); // the step's result is the transposed tensor
+            const int dims5[5] = {sd[0], sd[1], sd[2], qd[2], od[2]};
+            std::copy(dims5, dims5 + 5, a.att_dims);
+            const long long m = sd[1], nk = sd[2], kd = qd[2], d = od[2];
+            const long long dense1[6] = {m * kd, kd, nk * kd, kd, 0, 0}, dense2[6] = {0, 0, nk * d, d, m * d, d};
+            const long long *s1 = m1.mm_strided ? m1.mm_strides : dense1, *s2 = op.mm_strided ? op.mm_strides : dense2;
+            const long long st8[8] = {s1[0], s1[1], s1[2], s1[3], s2[2], s2[3], s2[4], s2[5]};
+            std::copy(st8, st8 + 8, a.att_st);
+            a.att_t[0] = m1.mm_in[0] >= 0 ? m1.mm_in[0] : m1.inputs[0];
+            a.att_t[1] = m1.mm_in[1] >= 0 ? m1.mm_in[1] : m1.inputs[1];
+            a.att_t[2] = op.mm_in[1] >= 0 ? op.mm_in[1] : op.inputs[1];
+            a.att_t[3] = ops[a.ops.back()].outputs[0];
+            for (int o : a.ops)
+                emitted[o] = 1;
+            steps.push_back(a);
+            continue;
+        }
         Step s;
         s.type = op.type;
         s.ops.push_back(id);

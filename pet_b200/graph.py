@@ -288,8 +288,8 @@ class Graph:
         self._check(self.lib.petb200_graph_set_outputs(self.h, len(outputs), L.ints([t.id for t in outputs])))
 
     # ---- execution (replaces CodeEngine.genCode + the emitted program) ----
-    def compile(self, fuse=True, cuda_graph=True):
-        self._check(self.lib.petb200_graph_compile(self.h, (0 if fuse else 1) | (0 if cuda_graph else 2)))
+    def compile(self, fuse=True, cuda_graph=True, fuse_attention=True):
+        self._check(self.lib.petb200_graph_compile(self.h, (0 if fuse else 1) | (0 if cuda_graph else 2) | (0 if fuse_attention else 8)))
         return self
 
     def set_data(self, tensor, array, stream=None):

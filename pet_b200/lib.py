@@ -74,6 +74,8 @@ SYMBOLS = {
     "petb200_softmax_run": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
     "petb200_softmax_axis_run": (_i, [_vp, _vp, _vp, _sz, _i, _sz, _vp]),
     "petb200_layernorm_run": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _i, _fp, _vp]),
+    "petb200_attention_supported": (_i, [_i, _i, _i, _i]),
+    "petb200_attention_run": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
     "petb200_matmul_splitk_noalloc": (_i, [_i] * 7 + [_vp, _vp, _vp, _vp, _i, _vp, C.c_char_p, _sz]),
     "petb200_plan_time": (_i, [_vp, _i, _i, C.POINTER(_fp), _vp]),
 }

@@ -476,6 +476,18 @@ class Context:
         self.check(self.lib.petb200_softmax_axis_run(self.h, _ptr(x), _ptr(y), outer, x.shape[axis], inner, _stream()))
         return y
 
+    def attention(self, q, k, v):
+        """softmax_rows(q k^T) v per batch entry in one launch: q [bs, m, kd], k [bs, n, kd], v [bs, n, d] -> [bs, m, d]
+        (the reference's MatmulOp(transB) -> SoftmaxOp -> MatmulOp chain; n, kd, d <= 128)."""
+        q, k, v = _f32(q), _f32(k), _f32(v)
+        if q.dim() != 3 or k.dim() != 3 or v.dim() != 3 or k.shape[0] != q.shape[0] or v.shape[0] != q.shape[0] or \
+                k.shape[2] != q.shape[2] or v.shape[1] != k.shape[1]:
+            raise L.PetError(L.ERR_INVALID, "attention: q [bs,m,kd], k [bs,n,kd], v [bs,n,d] expected")
+        y = torch.empty((q.shape[0], q.shape[1], v.shape[2]), device=q.device, dtype=torch.float32)
+        self.check(self.lib.petb200_attention_run(self.h, _ptr(q), _ptr(k), _ptr(v), _ptr(y), q.shape[0], q.shape[1], k.shape[1],
+                                                   q.shape[2], v.shape[2], None, _stream()))
+        return y
+
     def layernorm(self, x, gamma=None, beta=None, eps=1e-5):
         x = _f32(x)
         y = torch.empty_like(x)

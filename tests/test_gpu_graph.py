@@ -144,10 +144,25 @@ def test_bert_reduced(ctx):
     assert "transpose" not in names and "add" not in names
     g2, _, y2 = run_config(ctx, configs.bert_encoder, fuse=False, cuda_graph=False, **kw)
     assert [n for n, _ in g2.steps()].count("transpose") == 8
-    # the Q/K/V projections of a layer were merged into one wide matmul (2 layers x (8 - 2) matmuls)
-    assert names.count("matmul") == 12 and [n for n, _ in g2.steps()].count("matmul") == 16
+    # the Q/K/V projections of a layer were merged into one wide matmul, and scores -> softmax -> context became one
+    # attention launch per layer (2 layers x (8 - 2 - 2) matmuls)
+    assert names.count("matmul") == 8 and names.count("attention") == 2 and "softmax" not in names
+    assert [n for n, _ in g2.steps()].count("matmul") == 16
+    # the same graph with the attention chain kept as three steps: the fused launch computes the chain in plain fp32
+    from pet_b200.graph import Graph
+    g3 = Graph(ctx)
+    b3 = configs.GraphBuilder(g3)
+    o3 = configs.bert_encoder(b3, **kw)
+    g3.setOutputs([o3])
+    g3.compile(fuse_attention=False)
+    b3.load()
+    g3.run()
+    torch.cuda.synchronize()
+    names3 = [n for n, _ in g3.steps()]
+    assert names3.count("matmul") == 12 and names3.count("softmax") == 2 and "attention" not in names3
+    assert rel_err(g3.get_data(o3), want) <= TOL and rel_err(y, g3.get_data(o3)) <= TOL
     # same products; the wide matmul may split K differently from the three narrow ones, so sums can round differently
-    assert rel_err(y, y2) <= 1e-5
+    assert rel_err(g3.get_data(o3), y2) <= 1e-5 and rel_err(y, y2) <= TOL
 
 
 def test_r3d18_reduced(ctx):

@@ -1,4 +1,6 @@
 """GPU: matmul, elementwise, activation, pooling, softmax, LayerNorm, batch-norm through the C ABI vs the oracle."""
+import ctypes as C
+
 import numpy as np
 import pytest
 import torch
@@ -307,3 +309,58 @@ def test_strided_matmul_random_views_exact(ctx):
         as_view(out, (bs, m, n), (4 * c_batch, 4 * c_row, 4))[...] = 7.0
         assert (out == 7.0).all(), case
     ctx.sync_check()
+
+
+@pytest.mark.parametrize("shape", [(12, 128, 128, 64, 64),   # BERT-base: heads, queries, keys, head width (q/k), head width (v)
+                                   (3, 50, 100, 40, 72),     # ragged everywhere
+                                   (1, 7, 1, 1, 1), (2, 33, 128, 128, 128), (5, 200, 31, 8, 33), (40, 16, 64, 32, 96)])
+def test_attention_rows_against_oracle(ctx, oracle, shape):
+    """One launch for MatmulOp(transB) -> SoftmaxOp -> MatmulOp: against the oracle evaluating the three operators, and
+    against this backend's own three operators (the fused kernel is plain fp32, so it sits closer to the oracle)."""
+    bs, m, n, kd, d = shape
+    rng = np.random.default_rng(sum(shape))
+    q = (rng.standard_normal((bs, m, kd)) / np.sqrt(kd)).astype(np.float32)  # the 1/sqrt(d) of attention, folded into q
+    k = rng.standard_normal((bs, n, kd)).astype(np.float32)
+    v = rng.standard_normal((bs, n, d)).astype(np.float32)
+    want = oracle.matmul(oracle.softmax(oracle.matmul(q, k, transB=True), 2), v)
+    got = ctx.attention(dev(q), dev(k), dev(v)).cpu().numpy()
+    assert got.shape == want.shape == (bs, m, d)
+    # (the metric judges outputs that cancel to ~0 against a thousandth of the largest one, so fp32 rounding of the scores
+    # alone shows up at 1e-4)
+    assert rel_err(got, want) <= TOL and scale_err(got, want) <= 2e-6, shape
+    three = ctx.matmul(ctx.softmax(ctx.matmul(dev(q), dev(k), transB=True), 2), dev(v)).cpu().numpy()
+    assert rel_err(three, want) <= TOL and rel_err(got, three) <= TOL
+    # operands off the 16-byte grid take the generic kernel, aligned ones the tiled kernel: same sums in the same order
+    shifted = []
+    for t in (q, k, v):
+        buf = torch.zeros(t.size + 1, device="cuda")
+        buf[1:].copy_(dev(t).reshape(-1))
+        shifted.append(buf[1:].view(*t.shape))
+    assert shifted[0].data_ptr() % 16 == 4
+    assert np.array_equal(ctx.attention(*shifted).cpu().numpy(), got)
+    # rows of a wider matrix as operands (the head split of a merged Q/K/V projection): same result bit for bit
+    if kd == d:
+        wide = torch.zeros((max(m, n), bs, 3, kd + 4), device="cuda")
+        wide[:m, :, 0, :kd] = dev(q).transpose(0, 1)
+        wide[:n, :, 1, :kd] = dev(k).transpose(0, 1)
+        wide[:n, :, 2, :kd] = dev(v).transpose(0, 1)
+        out = torch.zeros((m, bs, d), device="cuda")
+        row, bat = wide.stride(0), wide.stride(1)
+        st = (C.c_longlong * 8)(bat, row, bat, row, bat, row, out.stride(1), out.stride(0))
+        ctx.check(ctx.lib.petb200_attention_run(ctx.h, wide[:, :, 0].data_ptr(), wide[:, :, 1].data_ptr(), wide[:, :, 2].data_ptr(), out.data_ptr(),
+                                                bs, m, n, kd, d, st, None))
+        torch.cuda.synchronize()
+        assert np.array_equal(out.transpose(0, 1).cpu().numpy(), got)
+    ctx.sync_check()
+
+
+def test_attention_rows_limits(ctx):
+    from pet_b200 import lib as L
+    z = lambda *s: torch.zeros(s, device="cuda")
+    with pytest.raises(L.PetError) as e:
+        ctx.attention(z(1, 8, 16), z(1, 129, 16), z(1, 129, 16))  # 129 keys
+    assert e.value.status == L.ERR_UNSUPPORTED
+    with pytest.raises(L.PetError):
+        ctx.attention(z(1, 8, 16), z(1, 16, 8), z(1, 16, 8))            # head widths of q and k differ
+    assert ctx.lib.petb200_attention_supported(128, 128, 64, 64) == 1
+    assert ctx.lib.petb200_attention_supported(128, 256, 64, 64) == 0
