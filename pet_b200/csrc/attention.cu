@@ -239,16 +239,18 @@ __device__ __forceinline__ void attn_cp16(float *dst, const float *src, bool val
                  : "memory");
 }
 
-template <int CW>
+// KD, DD: the head widths when known at compile time (64, BERT-base and most encoders), else 0 and read from the arguments.
+template <int CW, int KD, int DD>
 __global__ void __launch_bounds__(256) k_attention_tiled(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                                                          float *__restrict__ o, AttnArgs a) {
     pdl_prologue();
     extern __shared__ __align__(16) float attn_sm[];
-    const int KP = a.kd + 4, n16 = (a.n + 15) & ~15, kq = a.kd >> 2, dq = a.d >> 2;
+    const int kd = KD ? KD : a.kd, dd = DD ? DD : a.d;
+    const int KP = kd + 4, n16 = (a.n + 15) & ~15, kq = kd >> 2, dq = dd >> 2;
     float *Qs = attn_sm;                       // [16][KP]
     float *Ks = Qs + kAttnRows * KP;           // [n16][KP], rows past n zero
     float *Ss = Ks + (size_t)n16 * KP;         // [16][kAttnSP]
-    float *Vs = Ss + kAttnRows * kAttnSP;      // [n16][d], rows past n zero
+    float *Vs = Ss + kAttnRows * kAttnSP;      // [n16][dd], rows past n zero
     const int tid = (int)threadIdx.x, warp = tid >> 5, lane = tid & 31, lr = lane >> 2, lc = lane & 3;
     const int z = (int)blockIdx.y, row0 = (int)blockIdx.x * kAttnRows;
     const float *kz = k + (long long)z * a.kb, *vz = v + (long long)z * a.vb, *qz = q + (long long)z * a.qb;
@@ -279,7 +281,7 @@ __global__ void __launch_bounds__(256) k_attention_tiled(const float *__restrict
             if (j >= dq)
                 j -= dq, ++c;
             if (c < n16)
-                attn_cp16(Vs + c * a.d + 4 * j, c < a.n ? vz + (long long)c * a.vr + 4 * j : vz, c < a.n);
+                attn_cp16(Vs + c * dd + 4 * j, c < a.n ? vz + (long long)c * a.vr + 4 * j : vz, c < a.n);
         }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -293,7 +295,7 @@ __global__ void __launch_bounds__(256) k_attention_tiled(const float *__restrict
             acc[0][j] = acc[1][j] = 0.f;
         const float *q0 = Qs + lr * KP, *q1 = q0 + 8 * KP, *kb = Ks + (warp * 16 + lc) * KP;
 #pragma unroll 4
-        for (int kk = 0; kk < a.kd; kk += 4) {
+        for (int kk = 0; kk < kd; kk += 4) {
             const float4 x0 = *reinterpret_cast<const float4 *>(q0 + kk), x1 = *reinterpret_cast<const float4 *>(q1 + kk);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -334,7 +336,7 @@ __global__ void __launch_bounds__(256) k_attention_tiled(const float *__restrict
     __syncthreads();
 
     const int col = CW * (warp * 4 + lc);
-    if (col < a.d) {
+    if (col < dd) {
         float acc[2][CW];
 #pragma unroll
         for (int j = 0; j < CW; ++j)
@@ -347,7 +349,7 @@ __global__ void __launch_bounds__(256) k_attention_tiled(const float *__restrict
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 float y[CW];
-                attn_ld<CW>(vb + (size_t)(c + u) * a.d, y);
+                attn_ld<CW>(vb + (c + u) * dd, y);
 #pragma unroll
                 for (int j = 0; j < CW; ++j) {
                     acc[0][j] = fmaf(w0[u], y[j], acc[0][j]);
@@ -427,7 +429,7 @@ extern "C" int petb200_attention_run(petb200_ctx *ctx, const float *q, const flo
     static const int tiled = [] { const char *e = getenv("PETB200_ATTN_TILED"); return e ? atoi(e) : 1; }();
     if (a.vec && tiled) {
         const size_t smem = attn_tiled_smem_floats(n, kd, d) * sizeof(float);
-        auto kern = d <= 64 ? k_attention_tiled<2> : k_attention_tiled<4>;
+        auto kern = (kd == 64 && d == 64) ? k_attention_tiled<2, 64, 64> : (d <= 64 ? k_attention_tiled<2, 0, 0> : k_attention_tiled<4, 0, 0>);
         if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
             (void)cudaGetLastError();
             return fail(ctx, PETB200_ERR_UNSUPPORTED, "attention_run: %zu bytes of shared memory refused", smem);

@@ -1852,8 +1852,10 @@ extern "C" int petb200_graph_perf(petb200_graph *g, int rounds, int warmup, floa
             std::vector<int> key = {(int)s.type, (int)s.ops.size()};
             for (int o : s.ops) {
                 const Operator &op = g->ops[o];
-                for (int t : op.inputs)
+                for (int t : op.inputs) {
                     key.insert(key.end(), g->tensors[t].dims.begin(), g->tensors[t].dims.end());
+                    key.push_back(g->tensors[t].weight ? -1 : -2); // (a constant operand is packed once, outside the timed launch)
+                }
                 int attrs[] = {op.ph, op.pw, op.sh, op.sw, op.dh, op.dw, op.act, op.bias >= 0, op.transA, op.transB, op.dim, op.num,
                                op.tr.split, op.tr.factor, op.tr.ngroups, op.win[0], op.win[1], op.win[2], op.win[3], op.oph, op.opw, op.width, op.dilation, op.halo[0], op.halo[1], op.halo[2], op.halo[3]};
                 key.insert(key.end(), attrs, attrs + sizeof attrs / sizeof attrs[0]);

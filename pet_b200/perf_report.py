@@ -8,7 +8,8 @@ of a family exactly once (after one warm-up launch) at a size beyond the L2 and 
 each launch: they exist to be run under a profiler, which supplies the durations and the DRAM traffic (`once_ops`: element-wise,
 activation, BatchNorm, pooling, softmax, LayerNorm, row mean, small-m matmul, pad / slice / concat; `once_matmul`: the
 BERT-base matmul shapes; `once_conv`: the dilated-conv layer, a correction window, a transposed convolution;
-`once_rn18 [batch]`: one ResNet-18 forward pass, operator by operator).  Times come from the C ABI's timing entry point
+`once_attention`: the fused attention launch on BERT-base's heads; `once_rn18 [batch]`: one ResNet-18 forward pass, operator
+by operator).  Times come from the C ABI's timing entry point
 (CUDA events around repeated launches on plan-owned operands).  Peaks are read from MEASURED_PEAKS.json at the
 repository root when present.
 """
@@ -212,6 +213,21 @@ def once_banded(ctx):
     print(f"once_banded  g2bmm / gbmml b{b} n{n} m{m} w{w} d{d}: {fl / 1e9:.3f} GFLOP, {by / 1e6:.1f} MB algorithmic each")
 
 
+ATTENTION = [(12, 128, 128, 64, 64), (96, 128, 128, 64, 64)]  # BERT-base heads at batch 1 and 8: bs, queries, keys, head widths
+
+
+def once_attention(ctx):
+    """The fused attention launch on BERT-base's heads, twice (warm-up + one)."""
+    import torch
+    bs, m, n, kd, d = ATTENTION[0]
+    q, k, v = (torch.randn(s, device="cuda") for s in ((bs, m, kd), (bs, n, kd), (bs, n, d)))
+    for _ in range(2):
+        ctx.attention(q, k, v)
+        torch.cuda.synchronize()
+    print(f"once_attention  bs{bs} m{m} n{n} kd{kd} d{d}: {2.0 * bs * m * n * (kd + d) / 1e6:.1f} MFLOP, "
+          f"{4.0 * bs * (m * kd + n * kd + n * d + m * d) / 1e6:.2f} MB algorithmic")
+
+
 def once_rn18(ctx, batch):
     """One ResNet-18 forward pass at `batch`, operator by operator (no CUDA graph), after one warm-up pass."""
     import torch
@@ -278,6 +294,13 @@ def main(argv):
                 ms = ctx.banded_time(kind, b, n, m, w, d, rounds=20, warmup=3)
                 print(f"banded  {kind} b{b} n{n} m{m} w{w} d{d}: {ms * 1e3:9.1f} us {fl / ms / 1e9:6.1f} TFLOP/s fp32, "
                       f"{by / ms / 1e6:6.0f} GB/s = {by / ms / 1e6 / pk['hbm_gbs']:.2f} of {pk_kind} HBM peak")
+    if "attention" in groups:
+        import torch
+        for bs, m, n, kd, d in ATTENTION:
+            q, k, v = (torch.randn(s, device="cuda") for s in ((bs, m, kd), (bs, n, kd), (bs, n, d)))
+            us = _graph_time(lambda: ctx.attention(q, k, v))
+            us3 = _graph_time(lambda: ctx.matmul(ctx.softmax(ctx.matmul(q, k, transB=True), 2), v))
+            print(f"attention  bs{bs} m{m} n{n} kd{kd} d{d}: one launch {us:7.1f} us; matmul -> softmax -> matmul {us3:7.1f} us (graph replays)")
     if "rewrite" in groups:
         rewrite_routes(ctx)
     if "once_ops" in groups:
@@ -288,6 +311,8 @@ def main(argv):
         once_conv(ctx)
     if "once_banded" in groups:
         once_banded(ctx)
+    if "once_attention" in groups:
+        once_attention(ctx)
     if "once_rn18" in groups:
         i = groups.index("once_rn18")
         once_rn18(ctx, int(groups[i + 1]) if i + 1 < len(groups) and groups[i + 1].isdigit() else 64)
