@@ -445,26 +445,42 @@ __device__ __forceinline__ void cluster_reduce_store(const float *stage, int ksp
             if (f >= Fg)
                 break;
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int r = 0; r < 8; ++r)
+            // (kept as a loop: this code runs once per CTA, straight out of a cold instruction cache, so its length is its cost)
+            const float *sp = stage + c0 * kTileM + px;
+#pragma unroll 1
+            for (int r = 0; r < ksplit; ++r, sp += cols * kTileM)
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    if (r < ksplit && j < nv)
-                        acc[j] += stage[(r * cols + c0 + j) * kTileM + px]; // rank order for every element
+                    if (j < nv)
+                        acc[j] += sp[j * kTileM]; // rank order for every element
+            if (nv == 4) { // Fg % 4 == 0 and f % 4 == 0 here: the whole quad is inside the row, and 16-byte aligned in y / residual
+                if (bias != nullptr) {
+                    float4 b;
+                    if ((reinterpret_cast<uintptr_t>(bias) & 15) == 0)
+                        b = __ldg(reinterpret_cast<const float4 *>(bias + f));
+                    else
+                        b = make_float4(__ldg(bias + f), __ldg(bias + f + 1), __ldg(bias + f + 2), __ldg(bias + f + 3));
+                    acc[0] += b.x, acc[1] += b.y, acc[2] += b.z, acc[3] += b.w;
+                }
+                if (rp != nullptr) {
+                    const float4 r4 = __ldg(reinterpret_cast<const float4 *>(rp + f));
+                    acc[0] += r4.x, acc[1] += r4.y, acc[2] += r4.z, acc[3] += r4.w;
+                }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (j < nv && f + j < Fg) {
+                for (int j = 0; j < 4; ++j)
+                    acc[j] = act_fn<ACT>(acc[j]);
+                *reinterpret_cast<float4 *>(yp + f) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
                     if (bias != nullptr)
                         acc[j] += __ldg(bias + f + j);
                     if (rp != nullptr)
                         acc[j] += __ldg(rp + f + j);
                     acc[j] = act_fn<ACT>(acc[j]);
                 }
-            }
-            if (nv == 4) // Fg % 4 == 0 and f % 4 == 0 here: the whole quad is inside the row
-                *reinterpret_cast<float4 *>(yp + f) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-            else
                 *reinterpret_cast<float2 *>(yp + f) = make_float2(acc[0], acc[1]);
+            }
         }
         return;
     }
@@ -1423,6 +1439,22 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
     // ---------------- split-K: reduction across the cluster ----------------
     // Every thread of every CTA of the cluster reaches the barrier (all waits above are bounded).
     if (P.ksplit > 1) {
+        if (warp >= 3 && warp < 7) {
+            // The bias / residual values the reduction below adds start their way to L1 while the cluster meets.  Set 0's
+            // threads do it, for the row each of them wrote into sYoff itself (both halves of the CTA's column slice).
+            const int et = threadIdx.x - 96, cols = P.BN / P.ksplit;
+            const long long y_off = sYoff[et];
+            const int f = ntile * P.BN + (int)ptx::cluster_ctarank() * cols;
+            const long long f_glob0 = P.z_is_batch ? 0 : (long long)zb * P.Fg;
+            if (y_off >= 0 && P.ys_f == 1) {
+                if (P.res != nullptr)
+                    for (int i = 0; i < cols && f + i < P.Fg; i += 8)
+                        asm volatile("prefetch.global.L1 [%0];" ::"l"(P.res + y_off + f_glob0 + f + i));
+                if (P.has_bias && et == 0)
+                    for (int i = 0; i < cols && f + i < P.Fg; i += 8)
+                        asm volatile("prefetch.global.L1 [%0];" ::"l"(P.bias + f_glob0 + f + i));
+            }
+        }
         ptx::cluster_sync_all(); // every CTA's pushes have landed; nothing touches a peer's memory after this
         if (prof_cta)
             prof_cta[14] = (long long)ptx::globaltimer_ns();
