@@ -184,6 +184,23 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, uint32_t tcross, i
         if (split_addr != 0u) {
             // Split-K: column c of the tile is summed by CTA c / cols of the cluster.  Push this CTA's partial sum into
             // that CTA's shared memory, slot [this rank][c % cols][pixel] (consecutive lanes = consecutive words).
+            if (split_shift >= 5) {
+                // at least 32 columns per CTA: the whole block has one owner — one address translation, and the block this
+                // CTA owns itself stays out of the cluster network
+                const int owner = cc >> split_shift, lc0 = cc & ((1 << split_shift) - 1);
+                const uint32_t local = split_addr + (uint32_t)(lc0 * kTileM) * 4u;
+                if (owner == (int)ptx::cluster_ctarank()) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        ptx::st_shared_f32(local + (uint32_t)(j * kTileM) * 4u, __uint_as_float(r[j]));
+                } else {
+                    const uint32_t remote = ptx::map_to_cta(local, (uint32_t)owner);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        ptx::st_dsmem_f32(remote + (uint32_t)(j * kTileM) * 4u, __uint_as_float(r[j]));
+                }
+                continue;
+            }
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
                 const int col = cc + j, owner = col >> split_shift, lc = col & ((1 << split_shift) - 1);

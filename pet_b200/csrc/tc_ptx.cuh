@@ -97,6 +97,9 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
     asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
     return r;
 }
+__device__ __forceinline__ void st_shared_f32(uint32_t cta_addr, float v) {
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(cta_addr), "f"(v) : "memory");
+}
 __device__ __forceinline__ void st_dsmem_f32(uint32_t cluster_addr, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
 }
