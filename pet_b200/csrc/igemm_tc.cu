@@ -157,6 +157,27 @@ template <int ACT> __device__ __forceinline__ float act_fn(float v) {
     return v;
 }
 
+// Split-K, COLS (< 32) columns per CTA: the 32 columns in r[] belong to 32 / COLS consecutive CTAs of the cluster, starting
+// with `owner0`; each group goes to its owner's landing area [this rank][column][pixel] (this CTA's own group by a plain
+// shared-memory store).
+template <int COLS>
+__device__ __forceinline__ void push_groups(const uint32_t (&r)[32], uint32_t split_addr, int owner0, int me) {
+#pragma unroll
+    for (int g = 0; g < 32 / COLS; ++g) {
+        const int owner = owner0 + g;
+        if (owner == me) {
+#pragma unroll
+            for (int j = 0; j < COLS; ++j)
+                ptx::st_shared_f32(split_addr + (uint32_t)(j * kTileM) * 4u, __uint_as_float(r[g * COLS + j]));
+        } else {
+            const uint32_t remote = ptx::map_to_cta(split_addr, (uint32_t)owner);
+#pragma unroll
+            for (int j = 0; j < COLS; ++j)
+                ptx::st_dsmem_f32(remote + (uint32_t)(j * kTileM) * 4u, __uint_as_float(r[g * COLS + j]));
+        }
+    }
+}
+
 // TMEM accumulator rows -> (+bias, activation) -> global.  `yp` already points at this thread's pixel and the first
 // filter of the group; column j of the tile is filter f_tile0 + j.  The activation is a template parameter so that
 // the common no-activation case carries none of the transcendental code.
@@ -199,6 +220,14 @@ __device__ __forceinline__ void epilogue_store(uint32_t tacc, uint32_t tcross, i
                     for (int j = 0; j < 32; ++j)
                         ptx::st_dsmem_f32(remote + (uint32_t)(j * kTileM) * 4u, __uint_as_float(r[j]));
                 }
+                continue;
+            }
+            if (split_shift == 4 || split_shift == 3) { // 16 or 8 columns per CTA: one translation per owner, not per column
+                const int me = (int)ptx::cluster_ctarank(), owner0 = cc >> split_shift;
+                if (split_shift == 4)
+                    push_groups<16>(r, split_addr, owner0, me);
+                else
+                    push_groups<8>(r, split_addr, owner0, me);
                 continue;
             }
 #pragma unroll
