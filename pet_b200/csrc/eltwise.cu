@@ -523,6 +523,29 @@ __global__ void __launch_bounds__(256) k_layernorm_block(const float *__restrict
     }
 }
 
+// Rows of 256..1024 values on 16-byte boundaries (a transformer's hidden width): one CTA per row, one quad per thread held
+// in registers, so the row is read once and gamma / beta are in flight during the two reductions.
+__global__ void __launch_bounds__(256) k_layernorm_row4(const float *__restrict__ x, const float *__restrict__ gamma,
+                                                        const float *__restrict__ beta, float *__restrict__ y, size_t rows,
+                                                        int cols, float eps) {
+    pdl_prologue();
+    __shared__ float red[8];
+    const int t = (int)threadIdx.x;
+    const bool on = t < (cols >> 2);
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 g = (on && gamma) ? __ldg(reinterpret_cast<const float4 *>(gamma) + t) : make_float4(1.f, 1.f, 1.f, 1.f);
+    const float4 b = (on && beta) ? __ldg(reinterpret_cast<const float4 *>(beta) + t) : zero;
+    for (size_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const float4 v = on ? __ldg(reinterpret_cast<const float4 *>(x + r * (size_t)cols) + t) : zero;
+        const float mean = block_sum((v.x + v.y) + (v.z + v.w), red) / (float)cols;
+        const float dx = on ? v.x - mean : 0.f, dy = on ? v.y - mean : 0.f, dz = on ? v.z - mean : 0.f, dw = on ? v.w - mean : 0.f;
+        const float inv = rsqrtf(block_sum((dx * dx + dy * dy) + (dz * dz + dw * dw), red) / (float)cols + eps);
+        if (on)
+            reinterpret_cast<float4 *>(y + r * (size_t)cols)[t] =
+                make_float4(dx * inv * g.x + b.x, dy * inv * g.y + b.y, dz * inv * g.z + b.z, dw * inv * g.w + b.w);
+    }
+}
+
 static int grid_for(petb200_ctx *ctx, size_t work_items, int per_block) {
     size_t blocks = (work_items + per_block - 1) / per_block;
     size_t cap = (size_t)ctx->sm_count * 16;
@@ -688,6 +711,12 @@ extern "C" int petb200_layernorm_run(petb200_ctx *ctx, const float *x, const flo
         return fail(ctx, PETB200_ERR_INVALID, "layernorm_run: bad arguments");
     if (!rows)
         return PETB200_OK;
+    auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (cols >= 256 && cols <= 1024 && cols % 4 == 0 && rows <= (size_t)ctx->sm_count * 64 && al16(x) && al16(y) && al16(gamma) && al16(beta)) {
+        launch_pdl(k_layernorm_row4, (int)std::min<size_t>(rows, (size_t)ctx->sm_count * 8), 256, 0, (cudaStream_t)stream, x, gamma, beta, y, rows, cols,
+                   eps);
+        return launched(ctx, "k_layernorm_row4");
+    }
     if (cols >= 256 && rows <= (size_t)ctx->sm_count * 64) {
         launch_pdl(k_layernorm_block, (int)std::min<size_t>(rows, (size_t)ctx->sm_count * 8), 256, 0, (cudaStream_t)stream, x, gamma, beta, y, rows,
                                                                                                            cols, eps);
