@@ -1495,10 +1495,10 @@ k_igemm(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUte
             if (y_off >= 0 && P.ys_f == 1) {
                 if (P.res != nullptr)
                     for (int i = 0; i < cols && f + i < P.Fg; i += 8)
-                        asm volatile("prefetch.global.L1 [%0];" ::"l"(P.res + y_off + f_glob0 + f + i));
+                        ptx::prefetch_l1(P.res + y_off + f_glob0 + f + i);
                 if (P.has_bias && et == 0)
                     for (int i = 0; i < cols && f + i < P.Fg; i += 8)
-                        asm volatile("prefetch.global.L1 [%0];" ::"l"(P.bias + f_glob0 + f + i));
+                        ptx::prefetch_l1(P.bias + f_glob0 + f + i);
             }
         }
         ptx::cluster_sync_all(); // every CTA's pushes have landed; nothing touches a peer's memory after this

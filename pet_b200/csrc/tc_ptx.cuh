@@ -97,6 +97,8 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
     asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
     return r;
 }
+// Hint: start bringing the line that holds `p` into L1 (no register, no dependency, nothing to wait for).
+__device__ __forceinline__ void prefetch_l1(const void *p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
 __device__ __forceinline__ void st_shared_f32(uint32_t cta_addr, float v) {
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(cta_addr), "f"(v) : "memory");
 }
