@@ -322,7 +322,10 @@ def library_baseline(ctx, ours_ms):
         finally:
             del os.environ["PETB200_TC_MATH"]
         out[name] = row
-    out["reference_calls"] = reference_calls(ctx)
+    try:
+        out["reference_calls"] = reference_calls(ctx)
+    except Exception as e:  # (the rows above stand without it)
+        out["reference_calls"] = {"error": repr(e)}
     return out
 
 
@@ -336,7 +339,10 @@ def reference_calls(ctx):
     path = os.path.join(ROOT, "baseline", "libref_calls.so")
     if not os.path.exists(path):
         return {"unavailable": "baseline/libref_calls.so not built (make -C baseline)"}
-    lib = C.CDLL(path)
+    try:
+        lib = C.CDLL(path)
+    except OSError as e:  # (cuDNN / cuBLAS not loadable on this box)
+        return {"unavailable": f"baseline/libref_calls.so did not load: {e}"}
     out = {"how": "baseline/ref_calls.cu: cudnnConvolutionForward over the reference's 8 algorithms with default math; "
                   "cublasGemmStridedBatchedEx / cublasGemmEx with fp32 compute over the default and legacy algorithm ids; "
                   "CUDA events over 100 launches after 20 warm-ups"}
