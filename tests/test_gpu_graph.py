@@ -330,6 +330,16 @@ def test_random_encoder_graphs_fused_vs_unfused_vs_oracle(ctx):
         assert rel_err(y, oracle_config(configs.bert_encoder, **kw)) <= TOL, kw
 
 
+def test_encoder_longer_than_the_attention_launch_serves(ctx):
+    """160 keys per head is past what the one-launch attention takes: the chain stays three steps and still matches."""
+    from pet_b200 import configs
+    kw = dict(layers=1, seq=160, hidden=64, heads=2, ffn=96)
+    g, _, y = run_config(ctx, configs.bert_encoder, **kw)
+    names = [n for n, _ in g.steps()]
+    assert "attention" not in names and names.count("softmax") == 1
+    assert rel_err(y, oracle_config(configs.bert_encoder, **kw)) <= TOL
+
+
 def test_softmax_over_any_axis(ctx, oracle):
     """SoftmaxOp carries an axis (ref: include/operator.h:1887-1938): every axis of a ragged 4-D tensor, through the operator
     entry point and through a graph, against the oracle."""
