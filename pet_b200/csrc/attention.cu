@@ -423,6 +423,8 @@ extern "C" int petb200_attention_run(petb200_ctx *ctx, const float *q, const flo
     if (strides) {
         a.qb = strides[0], a.qr = strides[1], a.kb = strides[2], a.kr = strides[3];
         a.vb = strides[4], a.vr = strides[5], a.ob = strides[6], a.orow = strides[7];
+        if (a.qr < kd || a.kr < kd || a.vr < d || a.orow < d || a.qb < 0 || a.kb < 0 || a.vb < 0 || a.ob < 0)
+            return fail(ctx, PETB200_ERR_INVALID, "attention_run: a row stride shorter than its row, or a negative batch stride");
     }
     auto al = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
     a.vec = (kd % 4 == 0 && d % 4 == 0 && al(q) && al(k) && al(v) && ((a.qb | a.qr | a.kb | a.kr | a.vb | a.vr) & 3) == 0) ? 1 : 0;

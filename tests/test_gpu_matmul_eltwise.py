@@ -362,5 +362,8 @@ def test_attention_rows_limits(ctx):
     assert e.value.status == L.ERR_UNSUPPORTED
     with pytest.raises(L.PetError):
         ctx.attention(z(1, 8, 16), z(1, 16, 8), z(1, 16, 8))            # head widths of q and k differ
+    bad = (C.c_longlong * 8)(64, 8, 64, 16, 64, 16, 64, 16)  # q rows 8 apart but 16 long
+    t = z(1, 4, 16)
+    assert ctx.lib.petb200_attention_run(ctx.h, t.data_ptr(), t.data_ptr(), t.data_ptr(), z(1, 4, 16).data_ptr(), 1, 4, 4, 16, 16, bad, None) == L.ERR_INVALID
     assert ctx.lib.petb200_attention_supported(128, 128, 64, 64) == 1
     assert ctx.lib.petb200_attention_supported(128, 256, 64, 64) == 0
