@@ -274,6 +274,7 @@ __global__ void __launch_bounds__(256) k_attention_tiled(const float *__restrict
             if (c < n16)
                 attn_cp16(Ks + c * KP + 4 * j, c < a.n ? kz + (long long)c * a.kr + 4 * j : kz, c < a.n);
         }
+        asm volatile("cp.async.commit_group;" ::: "memory"); // q and k: all the scores need; v follows as a second group
         const int er = 256 / dq, ej = 256 - er * dq;
         c = tid / dq;
         j = tid - c * dq;
@@ -285,7 +286,7 @@ __global__ void __launch_bounds__(256) k_attention_tiled(const float *__restrict
         }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory"); // q and k have landed; v keeps arriving behind the scores
     __syncthreads();
 
     if (warp * 16 < n16) { // scores of rows lr, lr + 8 at columns 16 warp + lc + 4 j
@@ -333,6 +334,7 @@ __global__ void __launch_bounds__(256) k_attention_tiled(const float *__restrict
         for (int i = 0; i < 4; ++i)
             row[lane + 32 * i] = e[i] * inv;
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory"); // this thread's pieces of v; the barrier makes everyone's visible
     __syncthreads();
 
     const int col = CW * (warp * 4 + lc);
