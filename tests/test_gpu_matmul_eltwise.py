@@ -313,7 +313,8 @@ def test_strided_matmul_random_views_exact(ctx):
 
 @pytest.mark.parametrize("shape", [(12, 128, 128, 64, 64),   # BERT-base: heads, queries, keys, head width (q/k), head width (v)
                                    (3, 50, 100, 40, 72),     # ragged everywhere
-                                   (1, 7, 1, 1, 1), (2, 33, 128, 128, 128), (5, 200, 31, 8, 33), (40, 16, 64, 32, 96)])
+                                   (1, 7, 1, 1, 1), (2, 33, 128, 128, 128), (5, 200, 31, 8, 33), (40, 16, 64, 32, 96),
+                                   (40, 60, 64, 32, 96), (160, 16, 128, 64, 64)])  # enough CTAs for the 16-row variant
 def test_attention_rows_against_oracle(ctx, oracle, shape):
     """One launch for MatmulOp(transB) -> SoftmaxOp -> MatmulOp: against the oracle evaluating the three operators, and
     against this backend's own three operators (the fused kernel is plain fp32, so it sits closer to the oracle)."""
