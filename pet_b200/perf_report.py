@@ -8,7 +8,7 @@ of a family exactly once (after one warm-up launch) at a size beyond the L2 and 
 each launch: they exist to be run under a profiler, which supplies the durations and the DRAM traffic (`once_ops`: element-wise,
 activation, BatchNorm, pooling, softmax, LayerNorm, row mean, small-m matmul, pad / slice / concat; `once_matmul`: the
 BERT-base matmul shapes; `once_conv`: the dilated-conv layer, a correction window, a transposed convolution;
-`once_attention`: the fused attention launch on BERT-base's heads; `once_rn18 [batch]`: one ResNet-18 forward pass, operator
+`once_attention`: the fused attention launch on BERT-base's heads; `once_bert`: one BERT-base forward pass; `once_rn18 [batch]`: one ResNet-18 forward pass, operator
 by operator).  Times come from the C ABI's timing entry point
 (CUDA events around repeated launches on plan-owned operands).  Peaks are read from MEASURED_PEAKS.json at the
 repository root when present.
@@ -244,6 +244,22 @@ def once_rn18(ctx, batch):
     print(f"once_rn18  batch {batch}: {g.num_launches()} launches per pass, {batch * 3.628146688:.2f} GFLOP algorithmic (conv + FC)")
 
 
+def once_bert(ctx):
+    """One BERT-base (seq 128) forward pass, operator by operator (no CUDA graph), after one warm-up pass."""
+    import torch
+    from . import configs
+    from .graph import Graph
+    g = Graph(ctx)
+    b = configs.GraphBuilder(g)
+    g.setOutputs([configs.bert_encoder(b)])
+    g.compile(cuda_graph=False)
+    b.load()
+    for _ in range(2):
+        g.run()
+        torch.cuda.synchronize()
+    print(f"once_bert  {g.num_launches()} launches per pass")
+
+
 def main(argv):
     groups = argv or ["layout", "conv", "matmul"]
     pk, kind = peaks()
@@ -313,6 +329,8 @@ def main(argv):
         once_banded(ctx)
     if "once_attention" in groups:
         once_attention(ctx)
+    if "once_bert" in groups:
+        once_bert(ctx)
     if "once_rn18" in groups:
         i = groups.index("once_rn18")
         once_rn18(ctx, int(groups[i + 1]) if i + 1 < len(groups) and groups[i + 1].isdigit() else 64)
