@@ -61,7 +61,7 @@ struct IgemmParams {
     int z_is_batch;         // blockIdx.z: 0 = conv group, 1 = matmul batch
     int wide, row_tiles;    // wide mode: a tile is 128 consecutive pixels of ONE output row (rows wider than a tile)
     int tpi, ipt;           // otherwise: tiles per plane (plane larger than a tile) or whole planes per tile
-    int ksplit;             // K is split over this many CTAs, launched as one thread-block cluster (2, 4 or 8); partial
+    int ksplit;             // K is split over this many CTAs, launched as one thread-block cluster (2, 4, 8 or 16); partial
                             // tiles are added up through distributed shared memory
     int NA, NB, NR;         // ring depths: A stages, B stages, raw activation buffers
     int fl;                 // 3xTF32 only: every `fl` K stages the main accumulator is drained into a running total that
@@ -535,14 +535,11 @@ __device__ __forceinline__ void cluster_reduce_store(const float *stage, int ksp
         const int f = f_tile0 + rank * cols + cl;
         if (f >= Fg)
             break;
-        float v[8]; // all copies fetched before the first add
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-            v[r] = r < ksplit ? stage[(r * cols + cl) * kTileM + px] : 0.f;
-        float acc = v[0];
-#pragma unroll
-        for (int r = 1; r < 8; ++r)
-            acc += v[r];
+        const float *sp = stage + cl * kTileM + px;
+        float acc = sp[0]; // rank order, as in the 16-byte path
+#pragma unroll 1
+        for (int r = 1; r < ksplit; ++r)
+            acc += sp[r * cols * kTileM];
         if (bias != nullptr)
             acc += __ldg(bias + f);
         if (rp != nullptr)
@@ -1752,6 +1749,10 @@ struct TcCore {
         cfg.stream = s;
         cudaLaunchAttribute attr[2] = {};
         int nattr = 0;
+        if (P.ksplit > 8 && cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return fail(ctx, PETB200_ERR_UNSUPPORTED, "clusters of %d CTAs are not allowed on this device", P.ksplit);
+        }
         if (P.ksplit > 1) { // the splits of one output tile are consecutive in blockIdx.y: one cluster
             attr[nattr].id = cudaLaunchAttributeClusterDimension;
             attr[nattr].val.clusterDim.x = 1;
@@ -1795,7 +1796,7 @@ static int env_int(const char *name, int dflt) {
 // How many clusters of `ks` CTAs of this kernel (one CTA per SM) the device can hold at once: asked of the driver once
 // per size (clusters stay inside a GPC, which leaves some SMs of every GPC without a cluster).
 static int cluster_slots(int sm_count, int ks) {
-    static int cached[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+    static int cached[17] = {0};
     if (ks <= 1)
         return sm_count;
     if (cached[ks] == 0) {
@@ -1809,9 +1810,12 @@ static int cluster_slots(int sm_count, int ks) {
         cfg.attrs = attr, cfg.numAttrs = 1;
         int n = 0;
         (void)cudaFuncSetAttribute(k_igemm<true, false, kMathTf32x3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (ks > 8) // clusters of 16 are beyond the portable size: allowed per function
+            (void)cudaFuncSetAttribute(k_igemm<true, false, kMathTf32x3, false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (cudaOccupancyMaxActiveClusters(&n, k_igemm<true, false, kMathTf32x3, false>, &cfg) != cudaSuccess || n <= 0) {
             (void)cudaGetLastError();
-            n = std::max(1, (sm_count * (ks <= 2 ? 96 : 86) / 100) / ks); // what B200 was measured to hold
+            // what B200 was measured to hold; a cluster of 16 is only used where the driver itself says it fits
+            n = ks > 8 ? -1 : std::max(1, (sm_count * (ks <= 2 ? 96 : 86) / 100) / ks);
         }
         cached[ks] = n;
     }
@@ -1824,20 +1828,24 @@ static double est_cycles(int sm_count, long long base_ctas, int nchunks, int spc
     // split-K: (ks-1)/ks of the 512*BN-byte tile crosses to other SMs at ~10 bytes per cycle, then barrier + local sums
     const double per_cta = 3000.0 + (double)stages * stage + 1700.0 + (ks > 1 ? 1500.0 + 50.0 * BN * (ks - 1) / ks : 44.0 * BN);
     const long long slots = cluster_slots(sm_count, ks);
+    if (slots <= 0)
+        return 1e30; // this cluster size cannot be launched here
     const long long waves = (base_ctas + slots - 1) / slots;
     return (double)waves * per_cta;
 }
-// Split K over 1, 2, 4 or 8 CTAs (a cluster): the split must divide the tile width and leave every CTA a chunk.
+// Split K over 1, 2, 4, 8 or 16 CTAs (a cluster; 16 is beyond the portable cluster size and allowed per function): the
+// split must divide the tile width and leave every CTA a chunk.
 static int choose_ksplit(int sm_count, long long base_ctas, const IgemmParams &P, int passes, int want, double *cycles) {
     auto ok = [&](int ks) { return ks == 1 || (ks <= P.nchunks && P.BN % ks == 0); };
     int best = 1;
     double best_c = est_cycles(sm_count, base_ctas, P.nchunks, P.spc, P.BN, passes, 1);
+    static const int ks_cap = std::min(16, std::max(1, env_int_early("PETB200_TC_KSPLIT_MAX", 16)));
     if (want > 0) {
-        for (best = 8; best > 1 && !(best <= want && ok(best)); best /= 2) {
+        for (best = 16; best > 1 && !(best <= want && ok(best) && cluster_slots(sm_count, best) > 0); best /= 2) {
         }
         best_c = est_cycles(sm_count, base_ctas, P.nchunks, P.spc, P.BN, passes, best);
     } else {
-        for (int ks = 2; ks <= 8; ks *= 2) {
+        for (int ks = 2; ks <= ks_cap; ks *= 2) {
             if (!ok(ks))
                 continue;
             const double c = est_cycles(sm_count, base_ctas, P.nchunks, P.spc, P.BN, passes, ks);
